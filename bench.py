@@ -1,0 +1,369 @@
+#!/usr/bin/env python
+"""Benchmark of the fused dw-conv + BN-inference + quantize path.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl own|reference]
+                  [--workload cfg1|cfg0|cfg2|cfg3|cfg4] [--batch B]
+
+A "step" is one pass of the workload's layer stack over one batch of seeded synthetic
+input (cfg1: the 17 depthwise layers of MobileNetV2 at 224x224, batch 256 per GPU, fp32,
+each layer followed by BN-inference and FixedPointQuantize(unsigned, n=8, delta=2^-3)).
+The batch is sharded by image: with N GPUs every rank runs its own 256 images (weak
+scaling), no data-path collective except cfg3's per-channel min/max all-reduce.
+
+One JSON line is printed by rank 0:
+  value      whole-job images/s with inputs resident in HBM (CUDA events, max over ranks)
+  e2e        the same through the public call with HOST buffers: pinned-host -> device copy
+             of every layer input and device -> host copy of every layer output inside the
+             timed region
+  roofline   algorithmic bytes of the fused kernels of one step / their measured duration,
+             against the measured HBM copy bandwidth (MEASURED_PEAKS.json)
+  cpu_baseline  the CPU oracle (a port of the reference's CPU algorithm; nnabla core is not
+             installable here) on a bounded sample, all host cores
+--impl reference times that CPU path alone, on the same workload definition.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "nnabla-ext-cuda_b200", "python")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np  # noqa: E402
+
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_stack_images_per_s(specs, sample_n, nthreads, repeats=1):
+    """Times the unfused CPU chain (dw-conv, BN, quantizer: three passes, like the
+    reference's CPU functions) of the whole layer stack on `sample_n` images."""
+    from dwbnq import workloads
+    from oracle import oracle
+    datas = []
+    for s in specs:
+        small = workloads.LayerSpec(s.name, sample_n, s.c, s.h, s.w, s.k, s.stride, s.pad, s.quant, s.seed, s.x_dist)
+        datas.append((small, workloads.make_layer_data(small)))
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        for small, d in datas:
+            q = workloads.quant_for_ops(small, d)
+            oracle.fused_layer(d["x"], d["w"], d["b"], d["beta"], d["gamma"], d["mean"], d["var"], small.bn_eps,
+                               (small.stride,) * 2, (small.pad,) * 2, q, nthreads=nthreads)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return sample_n / best, best
+
+
+def run_reference(args):
+    """The reference arm: the reference's CPU algorithm (oracle port) on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from dwbnq import workloads
+    from oracle import oracle
+    oracle.build()
+    specs = workloads.workload(args.workload, args.batch)
+    nthreads = oracle.max_threads()
+    sample_n = args.cpu_sample
+    times = []
+    for i in range(args.warmup + args.steps):
+        _, dt = cpu_stack_images_per_s(specs, sample_n, nthreads)
+        if i >= args.warmup:
+            times.append(dt)
+    total = sum(times)
+    value = sample_n * len(times) / total
+    bytes_per_image = sum(s.algorithmic_bytes(4, 1) for s in specs)
+    line = {
+        "impl": "reference", "metric": "images_per_s", "value": value, "unit": "images/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args), "sample": "%d images per step" % sample_n},
+        "cpu_baseline": {"value": value, "unit": "images/s", "cores": nthreads, "kind": "port",
+                         "sample": "%d images of the layer stack per step, unfused 3-function chain" % sample_n,
+                         "effective_gbs": value * bytes_per_image / 1e9},
+        "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_name(args):
+    names = {"cfg0": "cfg0 single layer [B,64,56,56] 3x3 s1 + BN + FixedPointQuantize(sign,n=8,2^-4)",
+             "cfg1": "cfg1 MobileNetV2 17 depthwise 3x3 layers @224 + BN + FixedPointQuantize(unsigned,n=8,2^-3)",
+             "cfg2": "cfg2 [B,144,56,56] 5x5 s1 + BN + Pow2Quantize(sign,with_zero,n=8,m=1)",
+             "cfg3": "cfg3 [B,192,28,28] 3x3 s2 + BN + MinMaxQuantize(per-channel, batch-inclusive)",
+             "cfg4": "cfg4 = cfg1 in fp16"}
+    return names[args.workload]
+
+
+def run_own(args):
+    import torch
+    import torch.distributed as dist
+    from dwbnq import ops, workloads
+    from dwbnq.comm import Communicator
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the dwbnq path has no CPU fallback")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    half = args.workload == "cfg4" or args.dtype == "f16"
+    tdtype = torch.float16 if half else torch.float32
+    itemsize = 2 if half else 4
+    batch = args.batch
+    specs = workloads.workload(args.workload, batch)
+    need_comm = any(s.quant["kind"] == "minmax" for s in specs) and world > 1
+    comm = Communicator.from_torch_distributed(device) if need_comm else None
+
+    # ---- seeded inputs: this rank's images of the global batch, in pinned host memory ----
+    layers = []
+    for s in specs:
+        d = workloads.make_layer_data(s, n=batch, first_image=rank * batch)
+        host = {k: torch.from_numpy(v).to(tdtype).pin_memory() for k, v in d.items()}
+        devt = {k: v.to(device, non_blocking=True) for k, v in host.items()}
+        y = torch.empty((batch, s.c, s.ho, s.wo), dtype=tdtype, device=device)
+        y_host = torch.empty(y.shape, dtype=tdtype).pin_memory()
+        q = workloads.quant_for_ops(s, devt)
+        ws = ops.workspace(s.c, device) if s.quant["kind"] == "minmax" else None
+        layers.append((s, host, devt, y, y_host, q, ws))
+    torch.cuda.synchronize()
+
+    def launch(layer, x=None):
+        s, _, t, y, _, q, ws = layer
+        ops.fused_dw_bn_quant(t["x"] if x is None else x, t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"],
+                              s.bn_eps, pad=(s.pad, s.pad), stride=(s.stride, s.stride), quant=q, comm=comm, ws=ws,
+                              out=y)
+
+    def step():
+        for layer in layers:
+            launch(layer)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    launches_per_step = sum(2 if s.quant["kind"] == "minmax" else 1 for s in specs)
+
+    # ---- device-resident timing ---------------------------------------------------------
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    elapsed_ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop() if rank == 0 else None
+    ops.check_device_flag()
+
+    # ---- per-layer durations (separate pass, same launches; for the roofline breakdown) ----
+    per_layer = []
+    for layer in layers:
+        s = layer[0]
+        reps = max(3, min(args.steps, 10))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ts = []
+        for _ in range(reps):
+            flush_l2(torch, device)
+            e0.record()
+            launch(layer)
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        ms = float(np.median(ts))
+        per_layer.append({"layer": s.name, "c": s.c, "hw": s.h, "stride": s.stride, "ms": ms,
+                          "gbs": s.algorithmic_bytes(itemsize, batch) / ms / 1e6})
+
+    # ---- end to end: host buffers in, host buffers out ------------------------------------
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+    copy_stream = torch.cuda.current_stream(device)
+
+    def e2e_step():
+        for layer in layers:
+            s, host, t, y, y_host, q, ws = layer
+            t["x"].copy_(host["x"], non_blocking=True)
+            launch(layer)
+            y_host.copy_(y, non_blocking=True)
+        copy_stream.synchronize()
+
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = max(e0.elapsed_time(e1), 0.0)
+    e2e_wall_ms = 1e3 * (time.perf_counter() - t0)
+    h2d = sum(l[1]["x"].numel() * itemsize for l in layers)
+    d2h = sum(l[3].numel() * itemsize for l in layers)
+
+    # ---- max over ranks ---------------------------------------------------------------------
+    if world > 1:
+        tt = torch.tensor([elapsed_ms, e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        elapsed_ms, e2e_ms = float(tt[0]), float(tt[1])
+
+    if rank == 0:
+        images = batch * world * args.steps
+        value = images / (elapsed_ms / 1e3)
+        bytes_per_step = sum(s.algorithmic_bytes(itemsize, batch) for s in specs)
+        peak, peak_kind = measured_peak()
+        ms_per_step = elapsed_ms / args.steps
+        achieved = bytes_per_step / (ms_per_step / 1e3) / 1e9
+        from oracle import oracle
+        oracle.build()
+        nthreads = oracle.max_threads()
+        cpu_ips, cpu_dt = cpu_stack_images_per_s(specs, args.cpu_sample, nthreads)
+        bytes_per_image = sum(s.algorithmic_bytes(4, 1) for s in specs)
+        line = {
+            "metric": "images_per_s", "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16" if half else "f32", "data": "synthetic",
+            "config": {"workload": workload_name(args), "batch_per_gpu": batch, "global_batch": batch * world,
+                       "layers": len(specs), "parallelism": "batch-sharded x%d" % world,
+                       "l2": "per-step working set %.1f GB >> 126 MB L2; every layer has its own buffers"
+                             % (bytes_per_step / 1e9)},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_kind": peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
+                         "kernel": "fused_tiled_kernel (all %d launches of a step)" % launches_per_step,
+                         "algorithmic_bytes_per_step": bytes_per_step},
+            "cpu_baseline": {"value": cpu_ips, "unit": "images/s", "cores": nthreads, "kind": "port",
+                             "sample": "%d images of the layer stack, unfused 3-function chain, %.1f s"
+                                       % (args.cpu_sample, cpu_dt),
+                             "effective_gbs": cpu_ips * bytes_per_image / 1e9},
+            "e2e": {"value": batch * world * e2e_steps / (e2e_ms / 1e3), "unit": "images/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                    "wall_ms_per_step": e2e_wall_ms / e2e_steps},
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+            "layers": per_layer,
+        }
+        print(json.dumps(line), flush=True)
+    if comm is not None:
+        comm.destroy()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+_flush_buf = {}
+
+
+def flush_l2(torch, device):
+    """Overwrites a 512 MB buffer (4x the 126 MB L2) so the next launch starts cold."""
+    b = _flush_buf.get(device)
+    if b is None:
+        b = torch.empty(512 * 1024 * 1024, dtype=torch.uint8, device=device)
+        _flush_buf[device] = b
+    b.fill_(1)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--workload", default="cfg1", choices=["cfg0", "cfg1", "cfg2", "cfg3", "cfg4"])
+    ap.add_argument("--batch", type=int, default=None, help="images per GPU (default: the workload's batch)")
+    ap.add_argument("--dtype", default="f32", choices=["f32", "f16"])
+    ap.add_argument("--cpu-sample", type=int, default=None, help="images per CPU-baseline pass")
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    args = ap.parse_args()
+    defaults = {"cfg0": 32, "cfg1": 256, "cfg2": 128, "cfg3": 512, "cfg4": 256}
+    if args.batch is None:
+        args.batch = defaults[args.workload]
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.cpu_sample is None:
+        args.cpu_sample = {"cfg0": 32, "cfg1": 64, "cfg2": 32, "cfg3": 128, "cfg4": 64}[args.workload]
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_own(args)
+
+
+if __name__ == "__main__":
+    main()

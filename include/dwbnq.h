@@ -1,0 +1,229 @@
+/*
+ * dwbnq - C ABI of the B200 (sm_100a) quantized depthwise-CNN inference path:
+ * DepthwiseConvolution forward -> BatchNormalization (batch_stat=false) ->
+ * FixedPointQuantize | Pow2Quantize | MinMaxQuantize forward.
+ *
+ * Conventions (they mirror how nnabla-ext-cuda's function classes touch memory):
+ *  - every data pointer is a DEVICE pointer owned by the caller and valid for the
+ *    duration of the call (the reference obtains them with
+ *    Variable::get_data_pointer<Tc>(ctx) / cast_data_and_get_pointer<Tc>(ctx, true),
+ *    src/nbla/cuda/function/generic/depthwise_convolution.cu:445-449);
+ *  - nothing is allocated or freed on the caller's behalf; ops that need scratch take a
+ *    caller-provided workspace whose size dwbnq_workspace_bytes() reports;
+ *  - `device` is the CUDA device ordinal the pointers live on (-1 = the calling
+ *    thread's current device); the call makes it current like the reference's
+ *    cuda_set_device(device_) (src/nbla/cuda/common.cpp:20-26);
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream the
+ *    reference launches on, include/nbla/cuda/common.hpp:377-382); calls are
+ *    asynchronous with respect to the host unless stated otherwise;
+ *  - every function returns a dwbnq_status; on failure dwbnq_last_error_string() gives
+ *    the message for the calling thread. No C++ exception crosses this boundary (the
+ *    reference raises nbla::Exception through NBLA_CHECK / NBLA_CUDA_CHECK,
+ *    include/nbla/cuda/common.hpp:70-85; the plugin shim converts a status to one);
+ *  - there is no CPU fallback: without a usable CUDA device compute calls fail with
+ *    DWBNQ_ERR_CUDA.
+ *  - dtype DWBNQ_F16: tensors and parameters are IEEE binary16 in memory, arithmetic is
+ *    fp32 and the result is rounded to binary16 once at the store.
+ */
+#ifndef DWBNQ_H_
+#define DWBNQ_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default) /* the library is built with hidden visibility */
+#endif
+
+#define DWBNQ_ABI_VERSION 1
+
+typedef enum dwbnq_status {
+  DWBNQ_OK = 0,
+  DWBNQ_ERR_INVALID_ARG = 1, /* null pointer, non-positive size, bad enum ...        */
+  DWBNQ_ERR_UNSUPPORTED = 2, /* a configuration the reference rejects too             */
+  DWBNQ_ERR_CUDA = 3,        /* a CUDA runtime/driver call failed (message has why)   */
+  DWBNQ_ERR_NCCL = 4,        /* NCCL missing or a collective failed                   */
+  DWBNQ_ERR_TIMEOUT = 5,     /* a bounded wait ran out (collective or device barrier) */
+  DWBNQ_ERR_DEVICE_FLAG = 6  /* a kernel recorded an internal error (bounded wait)    */
+} dwbnq_status;
+
+typedef enum dwbnq_dtype { DWBNQ_F32 = 0, DWBNQ_F16 = 1 } dwbnq_dtype;
+
+typedef enum dwbnq_quant_kind {
+  DWBNQ_Q_NONE = 0,  /* conv (+BN) only                                   */
+  DWBNQ_Q_FPQ = 1,   /* FixedPointQuantize                                */
+  DWBNQ_Q_POW2 = 2,  /* Pow2Quantize                                      */
+  DWBNQ_Q_MINMAX = 3 /* MinMaxQuantize with per-channel ranges [1,C,1,1]  */
+} dwbnq_quant_kind;
+
+/* Geometry of a DepthwiseConvolution, i.e. the constructor arguments of
+ * DepthwiseConvolutionCuda(ctx, base_axis, pad, stride, dilation, multiplier)
+ * (include/nbla/cuda/function/depthwise_convolution.hpp:27-32) plus the input shape the
+ * base class derives in setup_impl. Layout is NCHW; a 1-D convolution is h = kh = 1. */
+typedef struct dwbnq_conv_desc {
+  int32_t dtype;      /* dwbnq_dtype                                          */
+  int32_t c;          /* input channels                                       */
+  int64_t n;          /* product of the axes before base_axis (the batch)     */
+  int32_t h, w;       /* input spatial size                                   */
+  int32_t kh, kw;     /* kernel                                               */
+  int32_t stride_h, stride_w;
+  int32_t pad_h, pad_w;
+  int32_t dil_h, dil_w;
+  int32_t multiplier; /* output channels = c * multiplier                     */
+} dwbnq_conv_desc;
+
+/* Quantizer constructor arguments.
+ *  FPQ   : FixedPointQuantizeCuda(ctx, sign, n, delta, ste_fine_grained)
+ *          (include/nbla/cuda/function/fixed_point_quantize.hpp:35-38)
+ *  POW2  : Pow2QuantizeCuda(ctx, sign, with_zero, n, m, ste_fine_grained)
+ *          (include/nbla/cuda/function/pow2_quantize.hpp:34-37)
+ *  MINMAX: MinMaxQuantizeCuda(ctx, decay, x_min_max, ema, ste_fine_grained, eps)
+ *          (include/nbla/cuda/function/min_max_quantize.hpp:27-30)
+ * ste_fine_grained only affects backward and is not carried. */
+typedef struct dwbnq_quant_desc {
+  int32_t kind; /* dwbnq_quant_kind */
+  int32_t sign;
+  int32_t n;
+  float delta;       /* FPQ                      */
+  int32_t with_zero; /* POW2                     */
+  int32_t m;         /* POW2                     */
+  float decay;       /* MINMAX (used when ema)   */
+  float eps;         /* MINMAX range nudge       */
+  int32_t x_min_max; /* MINMAX                   */
+  int32_t ema;       /* MINMAX                   */
+} dwbnq_quant_desc;
+
+/* Per-channel MinMaxQuantize tensors (inputs 1..4 of the function; qr_min / qr_max are
+ * updated in place when x_min_max is set, like the reference writes them back,
+ * src/nbla/cuda/function/generic/min_max_quantize.cu:63-69). All hold `channels`
+ * elements of the call's dtype. */
+typedef struct dwbnq_minmax_ptrs {
+  void *qr_min;
+  void *qr_max;
+  const void *ql_min;
+  const void *ql_max;
+} dwbnq_minmax_ptrs;
+
+/* ---- library ------------------------------------------------------------------ */
+
+int dwbnq_version(void);
+const char *dwbnq_last_error_string(void);
+/* Number of CUDA devices visible (0 when there is no driver/GPU). Never fails. */
+int dwbnq_device_count(void);
+/* Reads and clears the per-device flag kernels set when one of their bounded waits ran
+ * out. Synchronises the device. DWBNQ_OK when clear, DWBNQ_ERR_DEVICE_FLAG when set. */
+int dwbnq_check_device_flag(int device);
+
+/* ---- shape / parameter helpers (host only, no CUDA) ----------------------------- */
+
+/* Output spatial size the base class computes in setup_impl:
+ * o = (i + 2p - d(k-1) - 1) / s + 1. Fails with DWBNQ_ERR_INVALID_ARG on a bad desc
+ * and DWBNQ_ERR_UNSUPPORTED when c*multiplier*kh*kw > 65536, the limit the reference
+ * enforces (depthwise_convolution.cu:381). */
+int dwbnq_conv_out_shape(const dwbnq_conv_desc *desc, int32_t *ho, int32_t *wo);
+/* max_ / min_ members of FixedPointQuantize for (sign, n, delta). */
+int dwbnq_fpq_range(int sign, int n, float delta, float *max_out, float *min_out);
+/* p_max_ / p_min_ / pruning_threshold_ members of Pow2Quantize. */
+int dwbnq_pow2q_range(int sign, int with_zero, int n, int m, float *p_max, float *p_min,
+                      float *pruning_threshold);
+/* Pow2Quantize needs round(log2f(|x|)) exactly as the host libm rounds it. The library
+ * keeps, per binade e in [-149, 127], the smallest float bit pattern whose rounded
+ * log2 is e+1 (found with the host libm by bisection) and decides with integer
+ * compares on the device. This copies the 277-entry table (index e+149). */
+int dwbnq_pow2q_threshold_table(uint32_t *table277);
+/* Bytes of device scratch the MINMAX entry points need for `channels` channels. */
+size_t dwbnq_workspace_bytes(int32_t channels);
+
+/* ---- the five registered function classes, one entry point each ------------------ */
+
+/* DepthwiseConvolutionCuda<T>::forward_impl
+ * (src/nbla/cuda/function/generic/depthwise_convolution.cu:435-489).
+ * x [n,c,h,w]; w [c*mult,kh,kw]; b [c*mult] or NULL; y [n,c*mult,ho,wo]. */
+int dwbnq_dwconv_fwd(const dwbnq_conv_desc *desc, const void *x, const void *w,
+                     const void *b, void *y, int device, void *stream);
+
+/* BatchNormalizationCuda<T>::forward_impl_global, i.e. batch_stat=false
+ * (src/nbla/cuda/function/generic/batch_normalization.cu:174-199). x is viewed as
+ * [size0, size1, size2] with the channel axis = size1; beta / gamma may be NULL
+ * (no_bias / no_scale); mean, var (and beta, gamma) hold size1 elements. */
+int dwbnq_bn_infer_fwd(int dtype, int64_t size0, int64_t size1, int64_t size2, float eps,
+                       const void *x, const void *beta, const void *gamma, const void *mean,
+                       const void *var, void *y, int device, void *stream);
+
+/* FixedPointQuantizeCuda<T>::forward_impl
+ * (src/nbla/cuda/function/generic/fixed_point_quantize.cu:51-61). y may alias x. */
+int dwbnq_fpq_fwd(int dtype, int64_t size, int sign, int n, float delta, const void *x,
+                  void *y, int device, void *stream);
+
+/* Pow2QuantizeCuda<T>::forward_impl
+ * (src/nbla/cuda/function/generic/pow2_quantize.cu:65-77). y may alias x. */
+int dwbnq_pow2q_fwd(int dtype, int64_t size, int sign, int with_zero, int n, int m,
+                    const void *x, void *y, int device, void *stream);
+
+/* MinMaxQuantize forward (core composite + the MinMaxQuantizeCuda hooks,
+ * src/nbla/cuda/function/generic/min_max_quantize.cu:29-90) for x viewed as
+ * [size0, channels, size2] and ranges of shape [1, channels, 1, 1].
+ * `workspace`: dwbnq_workspace_bytes(channels) bytes of device memory, 256-byte
+ * aligned, contents irrelevant on entry. `comm`: NULL, or a dwbnq communicator over
+ * which the per-channel min/max are all-reduced (for a batch sharded across GPUs) when
+ * q->x_min_max is set. y may alias x. */
+int dwbnq_minmaxq_fwd(int dtype, int64_t size0, int32_t channels, int64_t size2,
+                      const dwbnq_quant_desc *q, const void *x, const dwbnq_minmax_ptrs *mm,
+                      void *y, void *workspace, void *comm, int device, void *stream);
+
+/* ---- the fused layer: what the graph pass rewrites dw-conv -> BN -> quantizer into -- */
+
+/* y = Quantize(BN_inference(DepthwiseConvolution(x))). No counterpart kernel exists in
+ * the reference (it runs the three classes above back to back); the arithmetic is the
+ * exact composition of the three, so the result is bit-identical to the unfused chain.
+ * bn_mean == NULL skips BatchNormalization (then bn_var / beta / gamma are ignored);
+ * q == NULL or kind NONE skips the quantizer. For MINMAX `mm` and `workspace` are
+ * required and `comm` is as in dwbnq_minmaxq_fwd; the activation is reduced in a first
+ * pass over x and quantized in a second one (nothing but `workspace` is written
+ * besides y and qr_min / qr_max). */
+int dwbnq_fused_fwd(const dwbnq_conv_desc *desc, float bn_eps, const dwbnq_quant_desc *q,
+                    const void *x, const void *w, const void *b, const void *bn_beta,
+                    const void *bn_gamma, const void *bn_mean, const void *bn_var,
+                    const dwbnq_minmax_ptrs *mm, void *y, void *workspace, void *comm,
+                    int device, void *stream);
+
+/* Which kernel family the fused / dw-conv entry points would use for `desc` given the
+ * pointer alignment: 0 = generic direct kernel, 1 = shared-memory tile filled by
+ * cooperative loads, 2 = shared-memory tile filled by TMA. Diagnostic only. */
+int dwbnq_fused_plan(const dwbnq_conv_desc *desc, const void *x, const void *y,
+                     int *path_out, int *planes_per_cta, int *rows_per_tile,
+                     int *threads, int64_t *ctas, int *smem_bytes);
+/* Environment switch DWBNQ_FORCE_PATH=generic|coop|tma (read at each call) and this
+ * setter (-1 = automatic) restrict that choice; used by the tests to cover every path. */
+int dwbnq_set_forced_path(int path);
+/* Planner overrides for tuning runs (0 = automatic): planes per CTA, 7-row blocks per
+ * tile, threads per CTA. Values that do not fit the shared-memory budget fall back to the
+ * generic kernel. */
+int dwbnq_set_tuning(int planes_per_cta, int row_blocks_per_tile, int threads);
+
+/* ---- communicator: the one exchange the path needs (per-channel min/max) ----------- */
+
+/* NCCL is loaded with dlopen at first use, like the reference does
+ * (src/nbla/cuda/communicator/dl_nccl.cpp.tmpl). The reference's communicator offers
+ * only sum/avg (multi_process_data_parallel_communicator.cu:790); this one issues a
+ * single ncclAllReduce(ncclMax) on the packed vector [max_c..., -min_c...]. */
+#define DWBNQ_UNIQUE_ID_BYTES 128
+int dwbnq_comm_get_unique_id(void *id128);
+int dwbnq_comm_create(const void *id128, int nranks, int rank, int device, void **comm);
+int dwbnq_comm_destroy(void *comm);
+/* All-reduce(max) of `count` fp32 values in place; waits at most timeout_ms for
+ * completion when timeout_ms > 0 (then aborts the communicator and returns
+ * DWBNQ_ERR_TIMEOUT), otherwise only enqueues. */
+int dwbnq_comm_allreduce_max_f32(void *comm, float *buf, int64_t count, void *stream,
+                                 int timeout_ms);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* DWBNQ_H_ */

@@ -1,0 +1,367 @@
+// extern "C" surface of libdwbnq (include/dwbnq.h): argument validation, error strings
+// and the operator-level sequencing. No kernel lives here.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "dwbnq_internal.h"
+
+namespace dwbnq {
+
+namespace {
+thread_local char g_err[512] = "";
+}
+
+void clear_error() { g_err[0] = '\0'; }
+
+int fail(int status, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return status;
+}
+
+int fail_cuda(cudaError_t e, const char *what) {
+  (void)cudaGetLastError();  // clear the sticky-less error state
+  return fail(DWBNQ_ERR_CUDA, "%s failed: (%s) %s", what, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+int enter_device(int device, int *out) {
+  cudaError_t e;
+  if (device >= 0) {
+    e = cudaSetDevice(device);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaSetDevice");
+    *out = device;
+    return DWBNQ_OK;
+  }
+  int cur = 0;
+  e = cudaGetDevice(&cur);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaGetDevice");
+  *out = cur;
+  return DWBNQ_OK;
+}
+
+namespace {
+
+int check_dtype(int dtype) {
+  if (dtype != DWBNQ_F32 && dtype != DWBNQ_F16)
+    return fail(DWBNQ_ERR_INVALID_ARG, "dtype %d is neither DWBNQ_F32 nor DWBNQ_F16", dtype);
+  return DWBNQ_OK;
+}
+
+int check_mm(const dwbnq_quant_desc *q, const dwbnq_minmax_ptrs *mm, const void *workspace) {
+  if (!mm || !mm->qr_min || !mm->qr_max || !mm->ql_min || !mm->ql_max)
+    return fail(DWBNQ_ERR_INVALID_ARG, "MinMaxQuantize needs qr_min, qr_max, ql_min and ql_max");
+  if (!workspace) return fail(DWBNQ_ERR_INVALID_ARG, "MinMaxQuantize needs a workspace");
+  if (reinterpret_cast<uintptr_t>(workspace) % 256)
+    return fail(DWBNQ_ERR_INVALID_ARG, "workspace must be 256-byte aligned");
+  if (q->ema && !(q->decay >= 0.0f && q->decay <= 1.0f))
+    return fail(DWBNQ_ERR_INVALID_ARG, "decay %g is not in [0, 1]", q->decay);
+  return DWBNQ_OK;
+}
+
+// The range part of MinMaxQuantize once the encoded per-channel min/max are in the
+// workspace: optional all-reduce across shards, then the range derivation.
+int mm_finish_ranges(int dtype, int channels, const dwbnq_quant_desc &q, const dwbnq_minmax_ptrs &mm,
+                     const MmWorkspace &w, void *comm, cudaStream_t stream) {
+  int st;
+  int from_packed = 0;
+  if (q.x_min_max && comm) {
+    st = launch_mm_pack(w, channels, stream);
+    if (st != DWBNQ_OK) return st;
+    st = comm_allreduce_max(comm, w.packed, 2LL * channels, stream, 0);
+    if (st != DWBNQ_OK) return st;
+    from_packed = 1;
+  }
+  return launch_mm_ranges(dtype, channels, q, mm, w, from_packed, stream);
+}
+
+void fill_args(FusedArgs *a, const dwbnq_conv_desc &d, int ho, int wo, float eps, const void *x,
+               const void *w, const void *b, const void *beta, const void *gamma, const void *mean,
+               const void *var, void *y) {
+  std::memset(a, 0, sizeof(*a));
+  a->x = x;
+  a->w = w;
+  a->b = b;
+  a->beta = beta;
+  a->gamma = gamma;
+  a->mean = mean;
+  a->var = var;
+  a->y = y;
+  a->eps = eps;
+  a->has_bn = mean != nullptr;
+  a->n = d.n;
+  a->C = d.c;
+  a->H = d.h;
+  a->W = d.w;
+  a->OC = d.c * d.multiplier;
+  a->Ho = ho;
+  a->Wo = wo;
+  a->kh = d.kh;
+  a->kw = d.kw;
+  a->sh = d.stride_h;
+  a->sw = d.stride_w;
+  a->ph = d.pad_h;
+  a->pw = d.pad_w;
+  a->dh = d.dil_h;
+  a->dw = d.dil_w;
+  a->mult = d.multiplier;
+}
+
+}  // namespace
+}  // namespace dwbnq
+
+using namespace dwbnq;
+
+extern "C" {
+
+int dwbnq_version(void) { return DWBNQ_ABI_VERSION; }
+
+const char *dwbnq_last_error_string(void) { return g_err; }
+
+int dwbnq_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+int dwbnq_check_device_flag(int device) {
+  clear_error();
+  int dev;
+  int st = enter_device(device, &dev);
+  if (st != DWBNQ_OK) return st;
+  int *p = nullptr;
+  st = device_flag_ptr(dev, &p);
+  if (st != DWBNQ_OK) return st;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail_cuda(e, "cudaDeviceSynchronize");
+  int v = 0;
+  e = cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaMemcpy(device flag)");
+  if (v) {
+    const int zero = 0;
+    cudaMemcpy(p, &zero, sizeof(int), cudaMemcpyHostToDevice);
+    return fail(DWBNQ_ERR_DEVICE_FLAG, "a kernel gave up a bounded wait on device %d (flag %d)", dev, v);
+  }
+  return DWBNQ_OK;
+}
+
+int dwbnq_conv_out_shape(const dwbnq_conv_desc *desc, int32_t *ho, int32_t *wo) {
+  clear_error();
+  int h, w;
+  int st = validate_conv(desc, &h, &w);
+  if (st != DWBNQ_OK) return st;
+  if (ho) *ho = h;
+  if (wo) *wo = w;
+  return DWBNQ_OK;
+}
+
+int dwbnq_fpq_range(int sign, int n, float delta, float *max_out, float *min_out) {
+  clear_error();
+  if (!max_out || !min_out) return fail(DWBNQ_ERR_INVALID_ARG, "output pointer is null");
+  QuantArgs q;
+  int st = fill_fpq(&q, sign, n, delta);
+  if (st != DWBNQ_OK) return st;
+  *max_out = q.fpq_max;
+  *min_out = q.fpq_min;
+  return DWBNQ_OK;
+}
+
+int dwbnq_pow2q_range(int sign, int with_zero, int n, int m, float *p_max, float *p_min,
+                      float *pruning_threshold) {
+  clear_error();
+  if (!p_max || !p_min || !pruning_threshold) return fail(DWBNQ_ERR_INVALID_ARG, "output pointer is null");
+  if (n < 1 || n > 31) return fail(DWBNQ_ERR_INVALID_ARG, "Pow2Quantize: bit width n=%d out of range", n);
+  pow2q_range(sign, with_zero, n, m, p_max, p_min, pruning_threshold);
+  return DWBNQ_OK;
+}
+
+int dwbnq_pow2q_threshold_table(uint32_t *table277) {
+  clear_error();
+  if (!table277) return fail(DWBNQ_ERR_INVALID_ARG, "table pointer is null");
+  std::memcpy(table277, pow2_table_host(), 277 * sizeof(uint32_t));
+  return DWBNQ_OK;
+}
+
+size_t dwbnq_workspace_bytes(int32_t channels) {
+  if (channels <= 0) return 0;
+  const size_t b = (size_t)channels * 7 * 4;
+  return (b + 255) / 256 * 256;
+}
+
+int dwbnq_set_forced_path(int path) {
+  clear_error();
+  if (path < PATH_AUTO || path > PATH_TMA) return fail(DWBNQ_ERR_INVALID_ARG, "path %d is not -1..2", path);
+  set_forced_path(path);
+  return DWBNQ_OK;
+}
+
+int dwbnq_fused_plan(const dwbnq_conv_desc *desc, const void *x, const void *y, int *path_out,
+                     int *planes_per_cta, int *rows_per_tile, int *threads, int64_t *ctas,
+                     int *smem_bytes) {
+  clear_error();
+  if (!desc) return fail(DWBNQ_ERR_INVALID_ARG, "conv desc is null");
+  Plan p;
+  int st = make_plan(*desc, x, y, &p);
+  if (st != DWBNQ_OK) return st;
+  if (path_out) *path_out = p.path;
+  if (planes_per_cta) *planes_per_cta = p.cfg.P;
+  if (rows_per_tile) *rows_per_tile = p.cfg.TH;
+  if (threads) *threads = p.threads;
+  if (ctas) *ctas = p.ctas;
+  if (smem_bytes) *smem_bytes = (int)p.smem;
+  return DWBNQ_OK;
+}
+
+int dwbnq_fused_fwd(const dwbnq_conv_desc *desc, float bn_eps, const dwbnq_quant_desc *q,
+                    const void *x, const void *w, const void *b, const void *bn_beta,
+                    const void *bn_gamma, const void *bn_mean, const void *bn_var,
+                    const dwbnq_minmax_ptrs *mm, void *y, void *workspace, void *comm, int device,
+                    void *stream) {
+  clear_error();
+  int ho, wo;
+  int st = validate_conv(desc, &ho, &wo);
+  if (st != DWBNQ_OK) return st;
+  if (!x || !w || !y) return fail(DWBNQ_ERR_INVALID_ARG, "x, w and y must not be null");
+  if ((bn_mean == nullptr) != (bn_var == nullptr))
+    return fail(DWBNQ_ERR_INVALID_ARG, "bn_mean and bn_var must be given together");
+  const int kind = q ? q->kind : DWBNQ_Q_NONE;
+  if (kind < DWBNQ_Q_NONE || kind > DWBNQ_Q_MINMAX)
+    return fail(DWBNQ_ERR_INVALID_ARG, "quantizer kind %d unknown", kind);
+  if (kind == DWBNQ_Q_MINMAX) {
+    st = check_mm(q, mm, workspace);
+    if (st != DWBNQ_OK) return st;
+  }
+  int dev;
+  st = enter_device(device, &dev);
+  if (st != DWBNQ_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  FusedArgs a;
+  fill_args(&a, *desc, ho, wo, bn_eps, x, w, b, bn_beta, bn_gamma, bn_mean, bn_var, y);
+  switch (kind) {
+    case DWBNQ_Q_NONE:
+      return launch_fused(*desc, a, QM_NONE, dev, s);
+    case DWBNQ_Q_FPQ:
+      st = fill_fpq(&a.q, q->sign, q->n, q->delta);
+      if (st != DWBNQ_OK) return st;
+      return launch_fused(*desc, a, QM_FPQ, dev, s);
+    case DWBNQ_Q_POW2:
+      st = fill_pow2(&a.q, q->sign, q->with_zero, q->n, q->m, dev);
+      if (st != DWBNQ_OK) return st;
+      return launch_fused(*desc, a, QM_POW2, dev, s);
+    default:
+      break;
+  }
+  // MinMaxQuantize: first pass reduces the (never stored) activation to per-channel
+  // min / max, second pass recomputes it and quantizes with the derived ranges.
+  const int channels = a.OC;
+  const MmWorkspace ws = mm_workspace(workspace, channels);
+  a.q.mm_enc_min = ws.enc_min;
+  a.q.mm_enc_max = ws.enc_max;
+  a.q.mm_scale = ws.scale;
+  a.q.mm_lo = ws.lo;
+  a.q.mm_hi = ws.hi;
+  if (q->x_min_max) {
+    st = launch_mm_init(ws, channels, s);
+    if (st != DWBNQ_OK) return st;
+    st = launch_fused(*desc, a, QM_MM_REDUCE, dev, s);
+    if (st != DWBNQ_OK) return st;
+  }
+  st = mm_finish_ranges(desc->dtype, channels, *q, *mm, ws, comm, s);
+  if (st != DWBNQ_OK) return st;
+  return launch_fused(*desc, a, QM_MM_APPLY, dev, s);
+}
+
+int dwbnq_dwconv_fwd(const dwbnq_conv_desc *desc, const void *x, const void *w, const void *b,
+                     void *y, int device, void *stream) {
+  return dwbnq_fused_fwd(desc, 0.0f, nullptr, x, w, b, nullptr, nullptr, nullptr, nullptr, nullptr, y,
+                         nullptr, nullptr, device, stream);
+}
+
+int dwbnq_bn_infer_fwd(int dtype, int64_t size0, int64_t size1, int64_t size2, float eps,
+                       const void *x, const void *beta, const void *gamma, const void *mean,
+                       const void *var, void *y, int device, void *stream) {
+  clear_error();
+  int st = check_dtype(dtype);
+  if (st != DWBNQ_OK) return st;
+  if (size0 < 0 || size1 <= 0 || size2 < 0)
+    return fail(DWBNQ_ERR_INVALID_ARG, "view [%lld,%lld,%lld] is not a valid shape", (long long)size0,
+                (long long)size1, (long long)size2);
+  if (!x || !y || !mean || !var) return fail(DWBNQ_ERR_INVALID_ARG, "x, y, mean and var must not be null");
+  int dev;
+  st = enter_device(device, &dev);
+  if (st != DWBNQ_OK) return st;
+  return launch_bn_infer(dtype, size0, size1, size2, eps, x, beta, gamma, mean, var, y,
+                         static_cast<cudaStream_t>(stream));
+}
+
+int dwbnq_fpq_fwd(int dtype, int64_t size, int sign, int n, float delta, const void *x, void *y,
+                  int device, void *stream) {
+  clear_error();
+  int st = check_dtype(dtype);
+  if (st != DWBNQ_OK) return st;
+  if (size < 0) return fail(DWBNQ_ERR_INVALID_ARG, "negative size");
+  if (!x || !y) return fail(DWBNQ_ERR_INVALID_ARG, "x and y must not be null");
+  QuantArgs q;
+  std::memset(&q, 0, sizeof(q));
+  st = fill_fpq(&q, sign, n, delta);
+  if (st != DWBNQ_OK) return st;
+  int dev;
+  st = enter_device(device, &dev);
+  if (st != DWBNQ_OK) return st;
+  return launch_fpq(dtype, size, q, x, y, static_cast<cudaStream_t>(stream));
+}
+
+int dwbnq_pow2q_fwd(int dtype, int64_t size, int sign, int with_zero, int n, int m, const void *x,
+                    void *y, int device, void *stream) {
+  clear_error();
+  int st = check_dtype(dtype);
+  if (st != DWBNQ_OK) return st;
+  if (size < 0) return fail(DWBNQ_ERR_INVALID_ARG, "negative size");
+  if (!x || !y) return fail(DWBNQ_ERR_INVALID_ARG, "x and y must not be null");
+  if (n < 1 || n > 31) return fail(DWBNQ_ERR_INVALID_ARG, "Pow2Quantize: bit width n=%d out of range", n);
+  int dev;
+  st = enter_device(device, &dev);
+  if (st != DWBNQ_OK) return st;
+  QuantArgs q;
+  std::memset(&q, 0, sizeof(q));
+  st = fill_pow2(&q, sign, with_zero, n, m, dev);
+  if (st != DWBNQ_OK) return st;
+  return launch_pow2q(dtype, size, q, x, y, static_cast<cudaStream_t>(stream));
+}
+
+int dwbnq_minmaxq_fwd(int dtype, int64_t size0, int32_t channels, int64_t size2,
+                      const dwbnq_quant_desc *q, const void *x, const dwbnq_minmax_ptrs *mm, void *y,
+                      void *workspace, void *comm, int device, void *stream) {
+  clear_error();
+  int st = check_dtype(dtype);
+  if (st != DWBNQ_OK) return st;
+  if (size0 < 0 || channels <= 0 || size2 < 0)
+    return fail(DWBNQ_ERR_INVALID_ARG, "view [%lld,%d,%lld] is not a valid shape", (long long)size0, channels,
+                (long long)size2);
+  if (!q) return fail(DWBNQ_ERR_INVALID_ARG, "quantizer desc is null");
+  if (!x || !y) return fail(DWBNQ_ERR_INVALID_ARG, "x and y must not be null");
+  st = check_mm(q, mm, workspace);
+  if (st != DWBNQ_OK) return st;
+  int dev;
+  st = enter_device(device, &dev);
+  if (st != DWBNQ_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const MmWorkspace ws = mm_workspace(workspace, channels);
+  if (q->x_min_max) {
+    st = launch_mm_init(ws, channels, s);
+    if (st != DWBNQ_OK) return st;
+    st = launch_mm_reduce(dtype, size0, channels, size2, x, ws, s);
+    if (st != DWBNQ_OK) return st;
+  }
+  st = mm_finish_ranges(dtype, channels, *q, *mm, ws, comm, s);
+  if (st != DWBNQ_OK) return st;
+  return launch_mm_apply(dtype, size0, channels, size2, x, y, ws, s);
+}
+
+}  // extern "C"

@@ -1,0 +1,89 @@
+// Host-side declarations shared by the translation units of libdwbnq.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/dwbnq.h"
+#include "dwbnq_fused.cuh"
+
+namespace dwbnq {
+
+// ---- errors (thread-local message behind dwbnq_last_error_string) ----------------------
+int fail(int status, const char *fmt, ...) __attribute__((format(printf, 2, 3)));
+int fail_cuda(cudaError_t e, const char *what);
+void clear_error();
+
+// Makes `device` current (-1 keeps the current one) and returns its ordinal in *out.
+int enter_device(int device, int *out);
+
+// ---- fused / dw-conv family (fused.cu) --------------------------------------------------
+enum FusedPath : int { PATH_AUTO = -1, PATH_GENERIC = 0, PATH_COOP = 1, PATH_TMA = 2 };
+
+struct Plan {
+  int path;
+  TileCfg cfg;
+  long long ctas;
+  int threads;
+  size_t smem;
+};
+
+// Chooses kernel family and tile geometry for a convolution. `x` / `y` are only
+// inspected for alignment.
+int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan);
+// Launches the fused kernel in mode `qm` (QMode). a.q must already be filled.
+int launch_fused(const dwbnq_conv_desc &d, FusedArgs &a, int qm, int device, cudaStream_t stream);
+int forced_path();
+void set_forced_path(int p);
+// Address of the per-device word kernels set when a bounded wait runs out.
+int device_flag_ptr(int device, int **ptr);
+
+int validate_conv(const dwbnq_conv_desc *d, int *ho, int *wo);
+
+// ---- element-wise family (elementwise.cu) -----------------------------------------------
+int launch_bn_infer(int dtype, long long size0, long long size1, long long size2, float eps,
+                    const void *x, const void *beta, const void *gamma, const void *mean,
+                    const void *var, void *y, cudaStream_t stream);
+int launch_fpq(int dtype, long long size, const QuantArgs &q, const void *x, void *y,
+               cudaStream_t stream);
+int launch_pow2q(int dtype, long long size, const QuantArgs &q, const void *x, void *y,
+                 cudaStream_t stream);
+
+// MinMaxQuantize pieces. Workspace layout (4-byte words, C = channels):
+//   [0,C) encoded min | [C,2C) encoded max | [2C,3C) scale | [3C,4C) m' | [4C,5C) M' |
+//   [5C,7C) packed [max..., -min...] for the all-reduce.
+struct MmWorkspace {
+  unsigned int *enc_min, *enc_max;
+  float *scale, *lo, *hi, *packed;
+};
+MmWorkspace mm_workspace(void *ws, int channels);
+int launch_mm_init(const MmWorkspace &w, int channels, cudaStream_t stream);
+int launch_mm_reduce(int dtype, long long size0, int channels, long long size2, const void *x,
+                     const MmWorkspace &w, cudaStream_t stream);
+int launch_mm_pack(const MmWorkspace &w, int channels, cudaStream_t stream);
+// Updates qr_min / qr_max (when x_min_max) and derives scale, m', M'. `from_packed`
+// selects the all-reduced packed vector instead of the encoded slots as the source.
+int launch_mm_ranges(int dtype, int channels, const dwbnq_quant_desc &q,
+                     const dwbnq_minmax_ptrs &mm, const MmWorkspace &w, int from_packed,
+                     cudaStream_t stream);
+int launch_mm_apply(int dtype, long long size0, int channels, long long size2, const void *x,
+                    void *y, const MmWorkspace &w, cudaStream_t stream);
+
+// ---- quantizer parameters (quant_params.cpp, host only) ----------------------------------
+void fpq_range(int sign, int n, float delta, float *mx, float *mn);
+void pow2q_range(int sign, int with_zero, int n, int m, float *p_max, float *p_min, float *thr);
+int fill_fpq(QuantArgs *q, int sign, int n, float delta);
+// Host threshold table (277 entries) and the mantissa window around sqrt(2) outside of
+// which the decision needs no table.
+const uint32_t *pow2_table_host();
+int pow2_table_window();
+// Fills the Pow2 part of q, uploading the table to `device` on first use.
+int fill_pow2(QuantArgs *q, int sign, int with_zero, int n, int m, int device);
+// Device copy of the table (pow2_table_dev.cu).
+int pow2_table_device(int device, const uint32_t **ptr);
+
+// ---- communicator (comm.cpp) --------------------------------------------------------------
+int comm_allreduce_max(void *comm, float *buf, long long count, cudaStream_t stream,
+                       int timeout_ms);
+
+}  // namespace dwbnq

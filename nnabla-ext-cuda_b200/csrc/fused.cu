@@ -1,0 +1,246 @@
+// Host side of the fused dw-conv -> BN -> quantizer family: validation, the tile planner,
+// TMA descriptor construction and kernel dispatch; plus the generic kernel instantiations.
+#include <atomic>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "dwbnq_internal.h"
+
+namespace dwbnq {
+
+__device__ int g_device_flag = 0;
+
+namespace {
+
+std::atomic<int> g_forced_path{PATH_AUTO};
+// Planner overrides for tuning runs: planes per CTA, row blocks per tile, threads (0 = auto).
+std::atomic<int> g_tune_p{0}, g_tune_rb{0}, g_tune_threads{0};
+
+constexpr int kMaxDevices = 64;
+int *g_flag_ptr[kMaxDevices] = {nullptr};
+std::mutex g_flag_mutex;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      p = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+inline int round_up(int a, int b) { return ceil_div(a, b) * b; }
+
+template <typename T>
+cudaError_t launch_generic_t(int qm, const FusedArgs &a, long long total, cudaStream_t stream) {
+  const int threads = 256;
+  long long blocks = (total + threads - 1) / threads;
+  const long long cap = 148LL * 64;  // grid-stride beyond 64 CTAs per SM
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  switch (qm) {
+    case QM_NONE: fused_generic_kernel<T, QM_NONE><<<(unsigned)blocks, threads, 0, stream>>>(a, total); break;
+    case QM_FPQ: fused_generic_kernel<T, QM_FPQ><<<(unsigned)blocks, threads, 0, stream>>>(a, total); break;
+    case QM_POW2: fused_generic_kernel<T, QM_POW2><<<(unsigned)blocks, threads, 0, stream>>>(a, total); break;
+    case QM_MM_APPLY: fused_generic_kernel<T, QM_MM_APPLY><<<(unsigned)blocks, threads, 0, stream>>>(a, total); break;
+    case QM_MM_REDUCE: fused_generic_kernel<T, QM_MM_REDUCE><<<(unsigned)blocks, threads, 0, stream>>>(a, total); break;
+    default: return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+int forced_path() {
+  const char *e = std::getenv("DWBNQ_FORCE_PATH");
+  if (e && *e) {
+    if (!std::strcmp(e, "generic")) return PATH_GENERIC;
+    if (!std::strcmp(e, "coop")) return PATH_COOP;
+    if (!std::strcmp(e, "tma")) return PATH_TMA;
+  }
+  return g_forced_path.load();
+}
+void set_forced_path(int p) { g_forced_path.store(p); }
+
+int device_flag_ptr(int device, int **ptr) {
+  if (device < 0 || device >= kMaxDevices) return fail(DWBNQ_ERR_INVALID_ARG, "device %d out of range", device);
+  std::lock_guard<std::mutex> lock(g_flag_mutex);
+  if (!g_flag_ptr[device]) {
+    void *p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_device_flag);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress(device flag)");
+    g_flag_ptr[device] = static_cast<int *>(p);
+  }
+  *ptr = g_flag_ptr[device];
+  return DWBNQ_OK;
+}
+
+int validate_conv(const dwbnq_conv_desc *d, int *ho, int *wo) {
+  if (!d) return fail(DWBNQ_ERR_INVALID_ARG, "conv desc is null");
+  if (d->dtype != DWBNQ_F32 && d->dtype != DWBNQ_F16)
+    return fail(DWBNQ_ERR_INVALID_ARG, "dtype %d is neither DWBNQ_F32 nor DWBNQ_F16", d->dtype);
+  if (d->n < 0 || d->c <= 0 || d->h <= 0 || d->w <= 0)
+    return fail(DWBNQ_ERR_INVALID_ARG, "input shape [%lld,%d,%d,%d] is not positive", (long long)d->n, d->c, d->h, d->w);
+  if (d->kh <= 0 || d->kw <= 0 || d->stride_h <= 0 || d->stride_w <= 0 || d->dil_h <= 0 || d->dil_w <= 0)
+    return fail(DWBNQ_ERR_INVALID_ARG, "kernel / stride / dilation must be positive");
+  if (d->pad_h < 0 || d->pad_w < 0) return fail(DWBNQ_ERR_INVALID_ARG, "negative padding");
+  if (d->multiplier <= 0) return fail(DWBNQ_ERR_INVALID_ARG, "multiplier must be positive");
+  const long long eh = (long long)d->h + 2LL * d->pad_h - (long long)d->dil_h * (d->kh - 1) - 1;
+  const long long ew = (long long)d->w + 2LL * d->pad_w - (long long)d->dil_w * (d->kw - 1) - 1;
+  if (eh < 0 || ew < 0)
+    return fail(DWBNQ_ERR_INVALID_ARG, "kernel %dx%d (dilation %d,%d) does not fit input %dx%d with pad %d,%d",
+                d->kh, d->kw, d->dil_h, d->dil_w, d->h, d->w, d->pad_h, d->pad_w);
+  // Limit of the reference implementation: output-channels x filter-size <= 65536.
+  if ((long long)d->c * d->multiplier * d->kh * d->kw > 65536)
+    return fail(DWBNQ_ERR_UNSUPPORTED,
+                "GPU implementation limit reached: output-channels x filter-size can not be more than 65536");
+  if (ho) *ho = (int)(eh / d->stride_h + 1);
+  if (wo) *wo = (int)(ew / d->stride_w + 1);
+  return DWBNQ_OK;
+}
+
+int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan) {
+  int Ho, Wo;
+  int st = validate_conv(&d, &Ho, &Wo);
+  if (st != DWBNQ_OK) return st;
+  std::memset(plan, 0, sizeof(*plan));
+  plan->path = PATH_GENERIC;
+  const int forced = forced_path();
+  const int B = d.dtype == DWBNQ_F32 ? 4 : 2;
+  const int S = 16 / B;
+  const int K = d.kh;
+  const int s = d.stride_h;
+  const bool tileable = d.kh == d.kw && (K == 3 || K == 5) && d.stride_h == d.stride_w &&
+                        (s == 1 || s == 2) && d.pad_h == K / 2 && d.pad_w == K / 2 &&
+                        d.dil_h == 1 && d.dil_w == 1 && d.multiplier == 1 && d.n > 0;
+  if (!tileable || forced == PATH_GENERIC) return DWBNQ_OK;
+
+  const int R = kRowsPerPatch;
+  const int pad = K / 2;
+  const int n_strips = ceil_div(Wo, S);
+  const int WS = round_up(S + (n_strips * S - 1) * s + K - pad, S);
+  const int n_rb_total = ceil_div(Ho, R);
+  // Row blocks per tile: aim at ~256 patches per CTA, split the plane evenly.
+  int rb_per_tile = 256 / n_strips;
+  if (rb_per_tile < 1) rb_per_tile = 1;
+  if (rb_per_tile > n_rb_total) rb_per_tile = n_rb_total;
+  if (g_tune_rb.load() > 0) rb_per_tile = std::min(g_tune_rb.load(), n_rb_total);
+  int n_row_tiles = ceil_div(n_rb_total, rb_per_tile);
+  rb_per_tile = ceil_div(n_rb_total, n_row_tiles);
+  const int TH = rb_per_tile * R;
+  const int TR = (TH - 1) * s + K;
+  // A TMA box has at most 256 rows and its shared-memory destination must be 128-byte
+  // aligned: with several boxes per plane the rows per box are a multiple of 8.
+  int n_boxes = ceil_div(TR, 256);
+  int box_rows = n_boxes == 1 ? TR : round_up(ceil_div(TR, n_boxes), 8);
+  const int tile_elems = round_up(box_rows * n_boxes * WS * B, 128) / B;
+  const long long tile_bytes = (long long)tile_elems * B;
+  const int ipp = n_strips * rb_per_tile;
+  // Planes per CTA: fill ~256 patches, stay within the shared-memory budget.
+  const long long smem_budget = 64 * 1024;
+  int P = 1;
+  if (n_row_tiles == 1) {
+    P = std::max(1, 256 / ipp);
+    while (P > 1 && (long long)P * tile_bytes > smem_budget) --P;
+  }
+  if (g_tune_p.load() > 0) P = g_tune_p.load();
+  const long long n_planes = d.n * d.c;
+  if (P > n_planes) P = (int)std::max(1LL, n_planes);
+  const size_t smem = tiled_smem_bytes(P, tile_elems, B, K);
+  if (smem > 200 * 1024 || WS > 256) return DWBNQ_OK;  // too wide for one tile row: generic
+  const long long ctas = ((n_planes + P - 1) / P) * n_row_tiles;
+  if (ctas > 0x7fffffffLL || n_planes > 0x7fffffffLL) return DWBNQ_OK;
+  int items = P * ipp;
+  int iters = ceil_div(items, 256);
+  int threads = round_up(ceil_div(items, iters), 32);
+  if (threads > 256) threads = 256;
+  if (g_tune_threads.load() > 0) threads = g_tune_threads.load();
+
+  const bool x_al = (reinterpret_cast<uintptr_t>(x) % 16) == 0;
+  const bool y_al = (reinterpret_cast<uintptr_t>(y) % 16) == 0;
+  const bool tma_ok = x_al && ((long long)d.w * B) % 16 == 0 && encode_tiled_fn() != nullptr;
+
+  TileCfg &c = plan->cfg;
+  c.P = P;
+  c.TH = TH;
+  c.n_row_tiles = n_row_tiles;
+  c.n_strips = n_strips;
+  c.n_rb = rb_per_tile;
+  c.WS = WS;
+  c.TR = TR;
+  c.box_rows = box_rows;
+  c.n_boxes = n_boxes;
+  c.tile_elems = tile_elems;
+  c.vec_store = (y_al && Wo % S == 0) ? 1 : 0;
+  c.vec_fill = (x_al && d.w % S == 0) ? 1 : 0;
+  plan->ctas = ctas;
+  plan->threads = threads;
+  plan->smem = smem;
+  if (forced == PATH_COOP) plan->path = PATH_COOP;
+  else if (forced == PATH_TMA) plan->path = tma_ok ? PATH_TMA : PATH_COOP;
+  else plan->path = tma_ok ? PATH_TMA : PATH_COOP;
+  return DWBNQ_OK;
+}
+
+int launch_fused(const dwbnq_conv_desc &d, FusedArgs &a, int qm, int device, cudaStream_t stream) {
+  Plan plan;
+  int st = make_plan(d, a.x, a.y, &plan);
+  if (st != DWBNQ_OK) return st;
+  if (d.n == 0) return DWBNQ_OK;
+  st = device_flag_ptr(device, &a.flag);
+  if (st != DWBNQ_OK) return st;
+  const long long total = d.n * (long long)a.OC * a.Ho * a.Wo;
+  cudaError_t e;
+  if (plan.path == PATH_GENERIC) {
+    e = d.dtype == DWBNQ_F32 ? launch_generic_t<float>(qm, a, total, stream)
+                             : launch_generic_t<__half>(qm, a, total, stream);
+    if (e != cudaSuccess) return fail_cuda(e, "fused_generic_kernel launch");
+    return DWBNQ_OK;
+  }
+  CUtensorMap tmap;
+  std::memset(&tmap, 0, sizeof(tmap));
+  const bool use_tma = plan.path == PATH_TMA;
+  if (use_tma) {
+    const int B = d.dtype == DWBNQ_F32 ? 4 : 2;
+    const cuuint64_t gdim[3] = {(cuuint64_t)d.w, (cuuint64_t)d.h, (cuuint64_t)(d.n * d.c)};
+    const cuuint64_t gstride[2] = {(cuuint64_t)d.w * B, (cuuint64_t)d.w * d.h * B};
+    const cuuint32_t box[3] = {(cuuint32_t)plan.cfg.WS, (cuuint32_t)plan.cfg.box_rows, 1u};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    const CUresult r = encode_tiled_fn()(
+        &tmap, d.dtype == DWBNQ_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+        3, const_cast<void *>(a.x), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(DWBNQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  }
+  if (d.dtype == DWBNQ_F32) {
+    e = d.kh == 3 ? launch_tiled<float, 3>(d.stride_h, qm, use_tma, tmap, a, plan.cfg, plan.ctas, plan.threads, plan.smem, stream)
+                  : launch_tiled<float, 5>(d.stride_h, qm, use_tma, tmap, a, plan.cfg, plan.ctas, plan.threads, plan.smem, stream);
+  } else {
+    e = d.kh == 3 ? launch_tiled<__half, 3>(d.stride_h, qm, use_tma, tmap, a, plan.cfg, plan.ctas, plan.threads, plan.smem, stream)
+                  : launch_tiled<__half, 5>(d.stride_h, qm, use_tma, tmap, a, plan.cfg, plan.ctas, plan.threads, plan.smem, stream);
+  }
+  if (e != cudaSuccess) return fail_cuda(e, "fused_tiled_kernel launch");
+  return DWBNQ_OK;
+}
+
+}  // namespace dwbnq
+
+extern "C" int dwbnq_set_tuning(int planes_per_cta, int row_blocks_per_tile, int threads) {
+  dwbnq::g_tune_p.store(planes_per_cta);
+  dwbnq::g_tune_rb.store(row_blocks_per_tile);
+  dwbnq::g_tune_threads.store(threads);
+  return DWBNQ_OK;
+}

@@ -1,0 +1,161 @@
+"""The benchmark / parity workloads and their seeded synthetic inputs.
+
+No dataset is involved: activations, weights and BN statistics are drawn from the
+distributions the workload definitions state, with ``numpy.random.default_rng(seed)``
+and a fixed draw order per layer (x, W, b, mean, var, gamma, beta, then MinMax outliers),
+all in float32. ``N(mu, v)`` below means variance ``v``.
+
+Workloads (ids follow the benchmark's config list):
+  cfg0  single layer  x[32,64,56,56]~N(0,1), 3x3 s1 p1, BN, FixedPointQuantize(sign, n=8, delta=2^-4)
+  cfg1  the 17 depthwise layers of MobileNetV2 at 224x224, batch 256, each with its own
+        input x~ReLU6(N(0,1)), BN, FixedPointQuantize(unsigned, n=8, delta=2^-3)
+  cfg2  x[128,144,56,56]~N(0,1), 5x5 s1 p2, BN, Pow2Quantize(sign, with_zero, n=8, m=1)
+  cfg3  x[512,192,28,28]~N(0,2) with 0.1% outliers~U(-20,20), 3x3 s2 p1, BN,
+        MinMaxQuantize(per-channel over axes (0,2,3), ql=[0,255], x_min_max, no ema)
+  cfg4  cfg1 cast to float16
+"""
+import os
+from concurrent.futures import ThreadPoolExecutor
+from dataclasses import dataclass, field
+
+import numpy as np
+
+# (channels, input height = width, stride) of the 17 depthwise 3x3 layers of MobileNetV2.
+MOBILENETV2_DW = ([(32, 112, 1), (96, 112, 2), (144, 56, 1), (144, 56, 2)] + [(192, 28, 1)] * 2 +
+                  [(192, 28, 2)] + [(384, 14, 1)] * 4 + [(576, 14, 1)] * 2 + [(576, 14, 2)] +
+                  [(960, 7, 1)] * 3)
+
+FPQ_CFG0 = {"kind": "fpq", "sign": True, "n": 8, "delta": 2.0 ** -4}
+FPQ_CFG1 = {"kind": "fpq", "sign": False, "n": 8, "delta": 2.0 ** -3}
+POW2_CFG2 = {"kind": "pow2", "sign": True, "with_zero": True, "n": 8, "m": 1}
+MINMAX_CFG3 = {"kind": "minmax", "decay": 0.999, "x_min_max": True, "ema": False, "eps": 0.01,
+               "ql_min": 0.0, "ql_max": 255.0}
+
+
+@dataclass
+class LayerSpec:
+    name: str
+    n: int
+    c: int
+    h: int
+    w: int
+    k: int = 3
+    stride: int = 1
+    pad: int = 1
+    quant: dict = field(default_factory=lambda: dict(FPQ_CFG1))
+    seed: int = 0
+    x_dist: str = "normal"  # "normal" | "relu6" | "normal2_outliers"
+    bn_eps: float = 1e-5
+
+    @property
+    def ho(self):
+        return (self.h + 2 * self.pad - (self.k - 1) - 1) // self.stride + 1
+
+    @property
+    def wo(self):
+        return (self.w + 2 * self.pad - (self.k - 1) - 1) // self.stride + 1
+
+    def elems_in(self, n=None):
+        return (self.n if n is None else n) * self.c * self.h * self.w
+
+    def elems_out(self, n=None):
+        return (self.n if n is None else n) * self.c * self.ho * self.wo
+
+    def algorithmic_bytes(self, itemsize=4, n=None):
+        """Read x once, write the quantized y once (parameter vectors are < 0.01 %)."""
+        return itemsize * (self.elems_in(n) + self.elems_out(n))
+
+
+def cfg0(n=32):
+    return [LayerSpec("cfg0", n, 64, 56, 56, 3, 1, 1, dict(FPQ_CFG0), seed=0)]
+
+
+def cfg1(n=256):
+    return [LayerSpec("cfg1.l%02d" % i, n, c, hw, hw, 3, s, 1, dict(FPQ_CFG1), seed=i, x_dist="relu6")
+            for i, (c, hw, s) in enumerate(MOBILENETV2_DW)]
+
+
+def cfg2(n=128):
+    return [LayerSpec("cfg2", n, 144, 56, 56, 5, 1, 2, dict(POW2_CFG2), seed=0)]
+
+
+def cfg3(n=512):
+    return [LayerSpec("cfg3", n, 192, 28, 28, 3, 2, 1, dict(MINMAX_CFG3), seed=0, x_dist="normal2_outliers")]
+
+
+def workload(name, n=None):
+    table = {"cfg0": cfg0, "cfg1": cfg1, "cfg2": cfg2, "cfg3": cfg3, "cfg4": cfg1}
+    return table[name]() if n is None else table[name](n)
+
+
+def _normal(rng, shape, var):
+    a = rng.standard_normal(shape, dtype=np.float32)
+    if var != 1.0:
+        a *= np.float32(np.sqrt(var))
+    return a
+
+
+def _uniform(rng, shape, lo, hi):
+    return (rng.random(shape, dtype=np.float32) * np.float32(hi - lo) + np.float32(lo)).astype(np.float32)
+
+
+def make_layer_data(spec, n=None, first_image=0, dtype=np.float32):
+    """Seeded tensors of one layer: dict with x, w, b, mean, var, gamma, beta (and, for
+    MinMax, qr_min, qr_max, ql_min, ql_max). ``n`` / ``first_image`` select a batch shard:
+    image i of the full batch is the same whatever shard it is drawn in (one generator per
+    image), so ranks of a sharded job and the single-device oracle see identical data."""
+    n = spec.n if n is None else n
+    rng = np.random.default_rng(spec.seed)
+    # Parameters first from the layer generator so they do not depend on the shard.
+    k = spec.k
+    d = {}
+    d["w"] = _normal(rng, (spec.c, k, k), 1.0 / (k * k))
+    d["b"] = _normal(rng, (spec.c,), 0.1)
+    d["mean"] = _normal(rng, (spec.c,), 0.1)
+    d["var"] = _uniform(rng, (spec.c,), 0.5, 1.5)
+    d["gamma"] = _uniform(rng, (spec.c,), 0.8, 1.2)
+    d["beta"] = _normal(rng, (spec.c,), 0.1)
+    x = np.empty((n, spec.c, spec.h, spec.w), dtype=np.float32)
+
+    def one_image(i):
+        irng = np.random.default_rng([spec.seed, 1 + first_image + i])
+        if spec.x_dist == "normal":
+            x[i] = irng.standard_normal((spec.c, spec.h, spec.w), dtype=np.float32)
+        elif spec.x_dist == "relu6":
+            xi = irng.standard_normal((spec.c, spec.h, spec.w), dtype=np.float32)
+            np.clip(xi, 0.0, 6.0, out=xi)
+            x[i] = xi
+        elif spec.x_dist == "normal2_outliers":
+            xi = _normal(irng, (spec.c, spec.h, spec.w), 2.0)
+            mask = irng.random((spec.c, spec.h, spec.w), dtype=np.float32) < np.float32(0.001)
+            out = _uniform(irng, (spec.c, spec.h, spec.w), -20.0, 20.0)
+            xi[mask] = out[mask]
+            x[i] = xi
+        else:
+            raise ValueError(spec.x_dist)
+
+    workers = min(16, os.cpu_count() or 1)
+    if n >= 8 and workers > 1:
+        with ThreadPoolExecutor(workers) as pool:
+            list(pool.map(one_image, range(n)))
+    else:
+        for i in range(n):
+            one_image(i)
+    d["x"] = x
+    if spec.quant["kind"] == "minmax":
+        d["qr_min"] = np.zeros(spec.c, np.float32)
+        d["qr_max"] = np.ones(spec.c, np.float32)
+        d["ql_min"] = np.full(spec.c, spec.quant["ql_min"], np.float32)
+        d["ql_max"] = np.full(spec.c, spec.quant["ql_max"], np.float32)
+    if dtype != np.float32:
+        d = {k_: v.astype(dtype) for k_, v in d.items()}
+    return d
+
+
+def quant_for_ops(spec, tensors=None):
+    """The quantizer dict in the form dwbnq.ops / the oracle take (MinMax: with tensors)."""
+    q = {k_: v for k_, v in spec.quant.items() if k_ not in ("ql_min", "ql_max")}
+    if q["kind"] == "minmax" and tensors is not None:
+        for k_ in ("qr_min", "qr_max", "ql_min", "ql_max"):
+            q[k_] = tensors[k_]
+    return q

@@ -1,0 +1,188 @@
+"""CPU-only checks of the C ABI: the library loads, exports what include/dwbnq.h declares,
+validates arguments like the reference does, derives quantizer parameters and the Pow2
+threshold table correctly, and refuses to compute without a GPU (no CPU fallback)."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
+
+
+def _desc(L, **kw):
+    base = dict(dtype=L.F32, c=8, n=2, h=16, w=16, kh=3, kw=3, stride_h=1, stride_w=1, pad_h=1, pad_w=1,
+                dil_h=1, dil_w=1, multiplier=1)
+    base.update(kw)
+    return L.ConvDesc(**base)
+
+
+def test_header_symbols_are_exported_and_bound(dwlib):
+    text = open(os.path.join(ROOT, "include", "dwbnq.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    declared = set(re.findall(r"\b(dwbnq_[a-z0-9_]+)\s*\(", text))
+    assert len(declared) >= 20
+    lib = dwlib.lib()
+    for name in declared:
+        assert hasattr(lib, name), "%s declared in dwbnq.h but not exported" % name
+        assert name in dwlib.SIGNATURES, "%s has no ctypes signature" % name
+    assert set(dwlib.SIGNATURES) == declared
+    assert lib.dwbnq_version() == 1
+
+
+def test_out_shape_and_validation(dwlib):
+    lib = dwlib.lib()
+    ho, wo = ctypes.c_int32(), ctypes.c_int32()
+    cases = [((112, 112, 3, 1, 1, 1), (112, 112)), ((112, 112, 3, 2, 1, 1), (56, 56)),
+             ((7, 7, 3, 1, 1, 1), (7, 7)), ((14, 14, 3, 2, 1, 1), (7, 7)), ((56, 56, 5, 1, 2, 1), (56, 56)),
+             ((10, 9, 3, 2, 0, 2), (3, 3))]
+    for (h, w, k, s, p, d), want in cases:
+        desc = _desc(dwlib, h=h, w=w, kh=k, kw=k, stride_h=s, stride_w=s, pad_h=p, pad_w=p, dil_h=d, dil_w=d)
+        assert lib.dwbnq_conv_out_shape(ctypes.byref(desc), ctypes.byref(ho), ctypes.byref(wo)) == dwlib.OK
+        assert (ho.value, wo.value) == want
+    bad = [dict(dtype=7), dict(c=0), dict(h=0), dict(kh=0), dict(stride_w=0), dict(pad_h=-1), dict(multiplier=0),
+           dict(h=2, w=2, kh=5, kw=5, pad_h=0, pad_w=0)]
+    for kw in bad:
+        desc = _desc(dwlib, **kw)
+        assert lib.dwbnq_conv_out_shape(ctypes.byref(desc), None, None) == dwlib.ERR_INVALID_ARG
+        assert lib.dwbnq_last_error_string()
+    assert lib.dwbnq_conv_out_shape(None, None, None) == dwlib.ERR_INVALID_ARG
+    # the reference's limit: output-channels x filter-size <= 65536
+    ok = _desc(dwlib, c=7281, kh=3, kw=3)
+    assert lib.dwbnq_conv_out_shape(ctypes.byref(ok), None, None) == dwlib.OK
+    over = _desc(dwlib, c=7282, kh=3, kw=3)
+    assert lib.dwbnq_conv_out_shape(ctypes.byref(over), None, None) == dwlib.ERR_UNSUPPORTED
+    assert b"65536" in lib.dwbnq_last_error_string()
+
+
+def test_quantizer_parameters_match_oracle(dwlib, oracle):
+    lib = dwlib.lib()
+    a, b, c = ctypes.c_float(), ctypes.c_float(), ctypes.c_float()
+    for sign in (0, 1):
+        for n in (2, 4, 8, 16):
+            for delta in (2.0 ** -4, 2.0 ** -3, 0.1, 1.0):
+                assert lib.dwbnq_fpq_range(sign, n, delta, ctypes.byref(a), ctypes.byref(b)) == dwlib.OK
+                assert (a.value, b.value) == oracle.fpq_params(sign, n, delta)
+    assert lib.dwbnq_fpq_range(1, 1, 0.5, ctypes.byref(a), ctypes.byref(b)) == dwlib.ERR_INVALID_ARG
+    assert lib.dwbnq_fpq_range(0, 8, 0.0, ctypes.byref(a), ctypes.byref(b)) == dwlib.ERR_INVALID_ARG
+    for sign in (0, 1):
+        for wz in (0, 1):
+            for n in (2, 4, 8, 10):
+                for m in (-2, 0, 1, 3):
+                    assert lib.dwbnq_pow2q_range(sign, wz, n, m, ctypes.byref(a), ctypes.byref(b),
+                                                 ctypes.byref(c)) == dwlib.OK
+                    assert (a.value, b.value, c.value) == oracle.pow2q_params(sign, wz, n, m)
+    assert lib.dwbnq_workspace_bytes(192) >= 192 * 7 * 4 and lib.dwbnq_workspace_bytes(192) % 256 == 0
+    assert lib.dwbnq_workspace_bytes(0) == 0
+
+
+def _table_k(bits, table):
+    """round(log2f(x)) for positive finite float bit patterns the way the device decides it."""
+    bits = bits.astype(np.uint32)
+    normal = bits >= 0x00800000
+    e = np.where(normal, (bits >> 23).astype(np.int64) - 127, 0)
+    sub = np.where(normal, 1, bits).astype(np.uint32)
+    e_sub = np.floor(np.log2(sub.astype(np.float64))).astype(np.int64) - 149
+    e = np.where(normal, e, e_sub)
+    thr = table[e + 149]
+    return (e + (bits >= thr)).astype(np.float32)
+
+
+def test_pow2_threshold_table_reproduces_libm(dwlib, oracle):
+    lib = dwlib.lib()
+    table = np.zeros(277, np.uint32)
+    assert lib.dwbnq_pow2q_threshold_table(table.ctypes.data_as(ctypes.POINTER(ctypes.c_uint32))) == dwlib.OK
+    assert lib.dwbnq_pow2q_threshold_table(None) == dwlib.ERR_INVALID_ARG
+    # the [1, 2) binade flips at the first float above sqrt(2)
+    assert table[149] == 0x3fb504f4
+    nthreads = oracle.max_threads()
+    # every pattern within +-4096 of each binade's threshold, all denormals' binade edges
+    chunks = []
+    for e in range(-149, 128):
+        lo = (e + 127) << 23 if e >= -126 else 1 << (e + 149)
+        hi = lo + (1 << 23) if e >= -126 else 1 << (e + 150)
+        t = int(table[e + 149])
+        a, b = max(lo, t - 4096), min(hi, t + 4096)
+        chunks.append(np.arange(a, b, dtype=np.uint32))
+        chunks.append(np.arange(lo, min(hi, lo + 64), dtype=np.uint32))
+        chunks.append(np.arange(max(lo, hi - 64), hi, dtype=np.uint32))
+    rng = np.random.default_rng(0)
+    chunks.append(rng.integers(1, 0x7f800000, size=1 << 24, dtype=np.uint32))
+    bits = np.concatenate(chunks)
+    want = oracle.round_log2(bits.view(np.float32), nthreads)
+    np.testing.assert_array_equal(_table_k(bits, table), want)
+
+
+def test_plan_selects_kernel_family(dwlib):
+    lib = dwlib.lib()
+    path, p, th, thr, smem = (ctypes.c_int() for _ in range(5))
+    ctas = ctypes.c_int64()
+
+    def plan(**kw):
+        d = _desc(dwlib, **kw)
+        st = lib.dwbnq_fused_plan(ctypes.byref(d), ctypes.c_void_p(4096), ctypes.c_void_p(8192), ctypes.byref(path),
+                                  ctypes.byref(p), ctypes.byref(th), ctypes.byref(thr), ctypes.byref(ctas),
+                                  ctypes.byref(smem))
+        assert st == dwlib.OK, lib.dwbnq_last_error_string()
+        return path.value
+
+    for kw in (dict(dil_h=2, dil_w=2, pad_h=2, pad_w=2), dict(multiplier=2), dict(kh=7, kw=7, pad_h=3, pad_w=3),
+               dict(pad_h=0, pad_w=0), dict(stride_h=3, stride_w=3), dict(h=1, kh=1, pad_h=0, stride_h=1)):
+        assert plan(**kw) == dwlib.PATH_GENERIC
+    for c, hw, s in ((32, 112, 1), (96, 112, 2), (144, 56, 1), (192, 28, 2), (384, 14, 1), (576, 14, 2), (960, 7, 1)):
+        for dt in (dwlib.F32, dwlib.F16):
+            assert plan(dtype=dt, n=4, c=c, h=hw, w=hw, stride_h=s, stride_w=s) in (dwlib.PATH_COOP, dwlib.PATH_TMA)
+            assert 32 <= thr.value <= 256 and thr.value % 32 == 0
+            assert smem.value <= 200 * 1024 and p.value >= 1 and th.value % 7 == 0
+            planes = 4 * c
+            n_row_tiles = -(-(-(-((hw + 2 - 3) // s + 1) // 7)) // (th.value // 7))
+            assert ctas.value == -(-planes // p.value) * n_row_tiles
+    assert lib.dwbnq_set_forced_path(dwlib.PATH_GENERIC) == dwlib.OK
+    assert plan(n=4, c=32, h=112, w=112) == dwlib.PATH_GENERIC
+    assert lib.dwbnq_set_forced_path(dwlib.PATH_AUTO) == dwlib.OK
+    assert lib.dwbnq_set_forced_path(9) == dwlib.ERR_INVALID_ARG
+
+
+def test_argument_errors_before_any_cuda_call(dwlib):
+    lib = dwlib.lib()
+    d = _desc(dwlib)
+    fake = ctypes.c_void_p(4096)
+    assert lib.dwbnq_dwconv_fwd(ctypes.byref(d), None, fake, None, fake, -1, None) == dwlib.ERR_INVALID_ARG
+    assert lib.dwbnq_fpq_fwd(5, 16, 1, 8, 0.5, fake, fake, -1, None) == dwlib.ERR_INVALID_ARG
+    assert lib.dwbnq_fpq_fwd(dwlib.F32, -1, 1, 8, 0.5, fake, fake, -1, None) == dwlib.ERR_INVALID_ARG
+    assert lib.dwbnq_fpq_fwd(dwlib.F32, 16, 1, 8, -0.5, fake, fake, -1, None) == dwlib.ERR_INVALID_ARG
+    assert lib.dwbnq_pow2q_fwd(dwlib.F32, 16, 1, 1, 0, 1, fake, fake, -1, None) == dwlib.ERR_INVALID_ARG
+    assert lib.dwbnq_bn_infer_fwd(dwlib.F32, 2, 0, 4, 1e-5, fake, None, None, fake, fake, fake, -1,
+                                  None) == dwlib.ERR_INVALID_ARG
+    assert lib.dwbnq_bn_infer_fwd(dwlib.F32, 2, 3, 4, 1e-5, fake, None, None, None, fake, fake, -1,
+                                  None) == dwlib.ERR_INVALID_ARG
+    q = dwlib.QuantDesc(kind=dwlib.Q_MINMAX, x_min_max=1, eps=0.01)
+    mm = dwlib.MinMaxPtrs(4096, 4096, 4096, 4096)
+    # MinMax without a workspace / with a misaligned one
+    assert lib.dwbnq_minmaxq_fwd(dwlib.F32, 2, 3, 4, ctypes.byref(q), fake, ctypes.byref(mm), fake, None, None, -1,
+                                 None) == dwlib.ERR_INVALID_ARG
+    assert lib.dwbnq_minmaxq_fwd(dwlib.F32, 2, 3, 4, ctypes.byref(q), fake, ctypes.byref(mm), fake,
+                                 ctypes.c_void_p(4100), None, -1, None) == dwlib.ERR_INVALID_ARG
+    qb = dwlib.QuantDesc(kind=9)
+    assert lib.dwbnq_fused_fwd(ctypes.byref(d), 1e-5, ctypes.byref(qb), fake, fake, None, None, None, None, None,
+                               None, fake, None, None, -1, None) == dwlib.ERR_INVALID_ARG
+    # bn_mean without bn_var
+    assert lib.dwbnq_fused_fwd(ctypes.byref(d), 1e-5, None, fake, fake, None, None, None, fake, None, None, fake,
+                               None, None, -1, None) == dwlib.ERR_INVALID_ARG
+
+
+def test_no_cpu_fallback_without_a_gpu(dwlib):
+    lib = dwlib.lib()
+    if lib.dwbnq_device_count() > 0:
+        pytest.skip("a GPU is present; the refusal path is for GPU-less hosts")
+    fake = ctypes.c_void_p(4096)
+    st = lib.dwbnq_fpq_fwd(dwlib.F32, 16, 1, 8, 0.5, fake, fake, -1, None)
+    assert st == dwlib.ERR_CUDA
+    assert lib.dwbnq_last_error_string()
+    d = _desc(dwlib)
+    assert lib.dwbnq_dwconv_fwd(ctypes.byref(d), fake, fake, None, fake, -1, None) == dwlib.ERR_CUDA
+    import torch
+    from dwbnq import ops
+    with pytest.raises(ValueError):
+        ops.fixed_point_quantize(torch.zeros(4))
