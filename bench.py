@@ -184,6 +184,8 @@ def run_own(args):
     itemsize = 2 if half else 4
     batch = args.batch
     specs = workloads.workload(args.workload, batch)
+    if args.only_layers:
+        specs = [specs[int(i)] for i in args.only_layers.split(",")]
     need_comm = any(s.quant["kind"] == "minmax" for s in specs) and world > 1
     comm = Communicator.from_torch_distributed(device) if need_comm else None
 
@@ -238,7 +240,7 @@ def run_own(args):
 
     # ---- per-layer durations (separate pass, same launches; for the roofline breakdown) ----
     per_layer = []
-    for layer in layers:
+    for layer in ([] if args.no_layer_pass else layers):
         s = layer[0]
         reps = max(3, min(args.steps, 10))
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -266,12 +268,13 @@ def run_own(args):
             y_host.copy_(y, non_blocking=True)
         copy_stream.synchronize()
 
-    e2e_step()
+    if not args.no_e2e:
+        e2e_step()
     barrier()
     t0 = time.perf_counter()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(e2e_steps):
+    for _ in range(0 if args.no_e2e else e2e_steps):
         e2e_step()
     e1.record()
     barrier()
@@ -296,7 +299,7 @@ def run_own(args):
         from oracle import oracle
         oracle.build()
         nthreads = oracle.max_threads()
-        cpu_ips, cpu_dt = cpu_stack_images_per_s(specs, args.cpu_sample, nthreads)
+        cpu_ips, cpu_dt = (0.0, 0.0) if args.no_cpu else cpu_stack_images_per_s(specs, args.cpu_sample, nthreads)
         bytes_per_image = sum(s.algorithmic_bytes(4, 1) for s in specs)
         line = {
             "metric": "images_per_s", "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
@@ -314,7 +317,7 @@ def run_own(args):
                              "sample": "%d images of the layer stack, unfused 3-function chain, %.1f s"
                                        % (args.cpu_sample, cpu_dt),
                              "effective_gbs": cpu_ips * bytes_per_image / 1e9},
-            "e2e": {"value": batch * world * e2e_steps / (e2e_ms / 1e3), "unit": "images/s",
+            "e2e": {"value": None if args.no_e2e else batch * world * e2e_steps / (e2e_ms / 1e3), "unit": "images/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "wall_ms_per_step": e2e_wall_ms / e2e_steps},
             "gpu_launches": launches_per_step * args.steps,
@@ -351,6 +354,11 @@ def main():
     ap.add_argument("--dtype", default="f32", choices=["f32", "f16"])
     ap.add_argument("--cpu-sample", type=int, default=None, help="images per CPU-baseline pass")
     ap.add_argument("--e2e-steps", type=int, default=3)
+    # reduced runs for profiling a single kernel (the printed line is then not a bench result)
+    ap.add_argument("--only-layers", default="", help="comma-separated layer indices of the workload")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-layer-pass", action="store_true")
     args = ap.parse_args()
     defaults = {"cfg0": 32, "cfg1": 256, "cfg2": 128, "cfg3": 512, "cfg4": 256}
     if args.batch is None:

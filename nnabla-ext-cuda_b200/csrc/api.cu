@@ -226,6 +226,7 @@ int dwbnq_fused_fwd(const dwbnq_conv_desc *desc, float bn_eps, const dwbnq_quant
   int ho, wo;
   int st = validate_conv(desc, &ho, &wo);
   if (st != DWBNQ_OK) return st;
+  if (desc->n == 0) return DWBNQ_OK;  // empty batch: nothing to read or write
   if (!x || !w || !y) return fail(DWBNQ_ERR_INVALID_ARG, "x, w and y must not be null");
   if ((bn_mean == nullptr) != (bn_var == nullptr))
     return fail(DWBNQ_ERR_INVALID_ARG, "bn_mean and bn_var must be given together");
@@ -306,7 +307,7 @@ int dwbnq_fpq_fwd(int dtype, int64_t size, int sign, int n, float delta, const v
   int st = check_dtype(dtype);
   if (st != DWBNQ_OK) return st;
   if (size < 0) return fail(DWBNQ_ERR_INVALID_ARG, "negative size");
-  if (!x || !y) return fail(DWBNQ_ERR_INVALID_ARG, "x and y must not be null");
+  if (size > 0 && (!x || !y)) return fail(DWBNQ_ERR_INVALID_ARG, "x and y must not be null");
   QuantArgs q;
   std::memset(&q, 0, sizeof(q));
   st = fill_fpq(&q, sign, n, delta);
@@ -314,6 +315,7 @@ int dwbnq_fpq_fwd(int dtype, int64_t size, int sign, int n, float delta, const v
   int dev;
   st = enter_device(device, &dev);
   if (st != DWBNQ_OK) return st;
+  if (size == 0) return DWBNQ_OK;
   return launch_fpq(dtype, size, q, x, y, static_cast<cudaStream_t>(stream));
 }
 
@@ -323,8 +325,9 @@ int dwbnq_pow2q_fwd(int dtype, int64_t size, int sign, int with_zero, int n, int
   int st = check_dtype(dtype);
   if (st != DWBNQ_OK) return st;
   if (size < 0) return fail(DWBNQ_ERR_INVALID_ARG, "negative size");
-  if (!x || !y) return fail(DWBNQ_ERR_INVALID_ARG, "x and y must not be null");
+  if (size > 0 && (!x || !y)) return fail(DWBNQ_ERR_INVALID_ARG, "x and y must not be null");
   if (n < 1 || n > 31) return fail(DWBNQ_ERR_INVALID_ARG, "Pow2Quantize: bit width n=%d out of range", n);
+  if (size == 0) return DWBNQ_OK;
   int dev;
   st = enter_device(device, &dev);
   if (st != DWBNQ_OK) return st;

@@ -234,6 +234,149 @@ __device__ __forceinline__ float mm_apply(float x, const MmCoef &c) {
   return __fadd_rn(t, c.lo);
 }
 
+// ---- packed fp32 pairs (sm_100 f32x2) ---------------------------------------------------
+// mul / add / fma on two floats per instruction, each lane rounded to nearest exactly like
+// the scalar instruction: twice the arithmetic per issue slot. A pair lives in an aligned
+// 64-bit register pair; pack / unpack are register moves (free when the allocator can
+// place the halves).
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 splat2(float v) { return pack2(v, v); }
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+// Rounded product. Written as fma(a, b, -0.0): RN(a * b + (-0.0)) is RN(a * b) bit for
+// bit (signed zeros included), and unlike mul.rn.f32x2 followed by add.rn.f32x2 - which
+// ptxas 12.9 contracts into one fused multiply-add even under --fmad=false, measured on
+// B200 - an fma feeding an add cannot be contracted.
+// The -0.0 addend is read from constant memory so the compiler cannot fold the fma back
+// into a multiply (with an immediate it does, and then contracts again).
+static __constant__ unsigned long long k_negzero2 = 0x8000000080000000ull;
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) { return fma2(a, b, k_negzero2); }
+// min / max that propagate NaN (x > hi ? hi : x keeps a NaN x, unlike fminf).
+__device__ __forceinline__ float min_nan(float a, float b) {
+  float r;
+  asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float max_nan(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+__device__ __forceinline__ float min3f(float a, float b, float c) {
+  float r;
+  asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+// ---- BatchNormalization on packed pairs ---------------------------------------------------
+// Same four rounded steps as bn_apply. The IEEE division by the per-channel constant
+// stdvar is evaluated as q0 = RN(a * r), then two residual corrections
+// q <- RN(q + RN_exact(a - q * stdvar) * r) with r = RN(1 / stdvar): after the first
+// correction q is within a fraction of an ulp of a / stdvar, and the second one then
+// yields the correctly rounded quotient (Markstein's theorem) provided no intermediate
+// leaves the normal range. That holds for 2^-100 < |a| < 2^100 and 2^-30 <= stdvar <=
+// 2^30; everything else (zeros, infinities, NaN, extreme magnitudes) takes __fdiv_rn.
+struct BnPacked {
+  f32x2 nmean, scale, rcp, nstd, beta;
+  float stdvar;  // for the out-of-range path
+  float glo;     // lower guard on |a|: 2^-100, or +inf when stdvar itself is out of range
+};
+#define DWBNQ_DIV_GUARD_LO 7.888609052e-31f /* 2^-100 */
+#define DWBNQ_DIV_GUARD_HI 1.267650600e30f  /* 2^100  */
+
+__device__ __forceinline__ BnPacked make_bn_packed(const BnCoef &c) {
+  BnPacked b;
+  b.nmean = splat2(-c.mean);
+  b.scale = splat2(c.scale);
+  b.rcp = splat2(__frcp_rn(c.stdvar));
+  b.nstd = splat2(-c.stdvar);
+  b.beta = splat2(c.beta);
+  b.stdvar = c.stdvar;
+  const bool safe = c.stdvar >= 9.31322574615478515625e-10f && c.stdvar <= 1073741824.0f;
+  b.glo = safe ? DWBNQ_DIV_GUARD_LO : __uint_as_float(0x7f800000u);
+  return b;
+}
+
+// In-place BN of NP pairs.
+template <int NP>
+__device__ __forceinline__ void bn_apply_packed(f32x2 *v, const BnPacked &b) {
+  f32x2 a[NP];
+  float mx = 0.0f, mn = __uint_as_float(0x7f800000u);
+#pragma unroll
+  for (int p = 0; p < NP; ++p) {
+    a[p] = mul2(add2(v[p], b.nmean), b.scale);
+    float lo, hi;
+    unpack2(a[p], lo, hi);
+    mx = max3f(mx, fabsf(lo), fabsf(hi));
+    mn = min3f(mn, fabsf(lo), fabsf(hi));
+    f32x2 q = mul2(a[p], b.rcp);
+    f32x2 e = fma2(q, b.nstd, a[p]);
+    q = fma2(e, b.rcp, q);
+    e = fma2(q, b.nstd, a[p]);
+    v[p] = fma2(e, b.rcp, q);
+  }
+  if (!(mn > b.glo && mx < DWBNQ_DIV_GUARD_HI)) {
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+      float lo, hi;
+      unpack2(a[p], lo, hi);
+      v[p] = pack2(__fdiv_rn(lo, b.stdvar), __fdiv_rn(hi, b.stdvar));
+    }
+  }
+#pragma unroll
+  for (int p = 0; p < NP; ++p) v[p] = add2(v[p], b.beta);
+}
+
+// ---- FixedPointQuantize on packed pairs (power-of-two delta) --------------------------------
+// Clamp first (max and min lie on the grid, so clamping commutes with the rounding and a
+// NaN stays NaN), then floor(t + 0.5) through two round-down adds as in fpq_apply.
+template <int NP>
+__device__ __forceinline__ void fpq_apply_packed_fast(f32x2 *v, const QuantArgs &q, bool is_signed) {
+  const f32x2 inv = splat2(q.fpq_inv_delta);
+  const f32x2 del = splat2(q.fpq_delta);
+  const f32x2 nmagic = splat2(-8388608.0f);
+#pragma unroll
+  for (int p = 0; p < NP; ++p) {
+    float lo, hi;
+    unpack2(v[p], lo, hi);
+    lo = max_nan(min_nan(lo, q.fpq_max), q.fpq_min);
+    hi = max_nan(min_nan(hi, q.fpq_max), q.fpq_min);
+    float t0, t1;
+    unpack2(mul2(pack2(fabsf(lo), fabsf(hi)), inv), t0, t1);
+    const float k0 = __fadd_rd(__fadd_rd(t0, 0.5f), 8388608.0f);
+    const float k1 = __fadd_rd(__fadd_rd(t1, 0.5f), 8388608.0f);
+    const f32x2 r = mul2(add2(pack2(k0, k1), nmagic), del);
+    if (is_signed) {
+      float r0, r1;
+      unpack2(r, r0, r1);
+      v[p] = pack2(lo < 0.0f ? -r0 : r0, hi < 0.0f ? -r1 : r1);
+    } else {
+      v[p] = r;
+    }
+  }
+}
+
 // One epilogue for all modes (QM_MM_REDUCE does not come here).
 template <int QM>
 __device__ __forceinline__ float quant_apply(float v, const QuantArgs &q, const MmCoef &mm) {

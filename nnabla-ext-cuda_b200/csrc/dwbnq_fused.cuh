@@ -247,18 +247,19 @@ __device__ __forceinline__ void load_window(const T *base, float *v) {
 
 // Per-plane parameter record in shared memory: K*K weights, bias, BN (mean, scale,
 // stdvar, beta), MinMax (scale, lo, hi).
+constexpr int kParamExtra = 8;
 template <int K> struct ParamLayout {
   static constexpr int KK = K * K;
   static constexpr int BIAS = KK;
   static constexpr int BN = KK + 1;
   static constexpr int MM = KK + 5;
-  static constexpr int COUNT = KK + 8;
+  static constexpr int COUNT = KK + kParamExtra;
 };
 
 // Shared-memory carve-up, also used by the host planner to size the launch.
 __host__ __device__ inline size_t tiled_smem_bytes(int P, int tile_elems, int elem_size, int K) {
   size_t s = (size_t)P * tile_elems * elem_size;         // tiles (each a multiple of 128 B)
-  s += (size_t)P * (K * K + 8) * sizeof(float);           // parameter records
+  s += (size_t)P * (K * K + kParamExtra) * sizeof(float);  // parameter records
   s += (size_t)P * 2 * sizeof(unsigned int);              // per-plane encoded min / max
   s = (s + 15) / 16 * 16;
   s += 16;                                                // mbarrier + fall-back flag
@@ -419,6 +420,13 @@ __global__ void __launch_bounds__(256)
   }
 
   // ---- consumer: R x S output patches from a rolling K-row register window ---------------
+  // Arithmetic runs on packed pairs of horizontally adjacent outputs (f32x2). With stride 1
+  // the window of a row is kept as its NV-1 consecutive pairs (v[i], v[i+1]) so every tap of
+  // an output pair is one packed multiply and one packed add; with stride 2 (and for the
+  // register-heavy 5x5 half case) the taps stay scalar and only BN / quantizer are packed.
+  constexpr bool PACKED_CONV = (STRIDE == 1) && !(K == 5 && S == 8);
+  constexpr int NPR = S / 2;   // output pairs per patch row
+  constexpr int NWP = NV - 1;  // consecutive pairs of a window row
   const int ipp = c.n_strips * c.n_rb;  // items per plane
   const int n_items = pv * ipp;
   for (int it = tid; it < n_items; it += nthr) {
@@ -428,11 +436,9 @@ __global__ void __launch_bounds__(256)
     const int st = rem - rb * c.n_strips;
 
     const float *pp = prm + pl * PL::COUNT;
-    float wr[PL::KK];
-#pragma unroll
-    for (int i = 0; i < PL::KK; ++i) wr[i] = pp[i];
     const float bias = pp[PL::BIAS];
     const BnCoef bn{pp[PL::BN], pp[PL::BN + 1], pp[PL::BN + 2], pp[PL::BN + 3]};
+    const BnPacked bnp = make_bn_packed(bn);
     const MmCoef mm{pp[PL::MM], pp[PL::MM + 1], pp[PL::MM + 2]};
 
     // 16-byte aligned position of the first output's centre tap column in tile row 0 of
@@ -445,56 +451,91 @@ __global__ void __launch_bounds__(256)
     const bool full_vec = c.vec_store && (ox0 + S <= a.Wo);
 
     float lo = __uint_as_float(0x7f800000u), hi = __uint_as_float(0xff800000u);
-    float win[K][NV];
+    // window storage: packed pairs or scalars, whichever the conv uses
+    f32x2 wp[PACKED_CONV ? K : 1][PACKED_CONV ? NWP : 1];
+    float win[PACKED_CONV ? 1 : K][PACKED_CONV ? 1 : NV];
+    f32x2 w2[PACKED_CONV ? PL::KK : 1];
+    float wr[PACKED_CONV ? 1 : PL::KK];
+#pragma unroll
+    for (int i = 0; i < PL::KK; ++i) {
+      if (PACKED_CONV) w2[i] = splat2(pp[i]);
+      else wr[i] = pp[i];
+    }
+    auto load_row = [&](int row) {
+      if (PACKED_CONV) {
+        float v[NV];
+        load_window<T, PAD, NV>(tp + (size_t)row * c.WS, v);
+#pragma unroll
+        for (int i = 0; i < NWP; ++i) wp[row % K][i] = pack2(v[i], v[i + 1]);
+      } else {
+        load_window<T, PAD, NV>(tp + (size_t)row * c.WS, win[row % K]);
+      }
+    };
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       if (r == 0) {
 #pragma unroll
-        for (int i = 0; i < K; ++i) load_window<T, PAD, NV>(tp + (size_t)i * c.WS, win[i % K]);
+        for (int i = 0; i < K; ++i) load_row(i);
       } else {
 #pragma unroll
-        for (int i = 0; i < STRIDE; ++i) {
-          const int row = (r - 1) * STRIDE + K + i;
-          load_window<T, PAD, NV>(tp + (size_t)row * c.WS, win[row % K]);
-        }
+        for (int i = 0; i < STRIDE; ++i) load_row((r - 1) * STRIDE + K + i);
       }
-      float acc[S];
+      f32x2 acc[NPR];
+      if (PACKED_CONV) {
+        const f32x2 bias2 = splat2(bias);
 #pragma unroll
-      for (int j = 0; j < S; ++j) acc[j] = bias;
+        for (int p = 0; p < NPR; ++p) acc[p] = bias2;
 #pragma unroll
-      for (int ky = 0; ky < K; ++ky) {
+        for (int ky = 0; ky < K; ++ky) {
 #pragma unroll
-        for (int kx = 0; kx < K; ++kx) {
+          for (int kx = 0; kx < K; ++kx) {
 #pragma unroll
-          for (int j = 0; j < S; ++j) {
-            acc[j] = __fadd_rn(acc[j],
-                               __fmul_rn(wr[ky * K + kx], win[(r * STRIDE + ky) % K][j * STRIDE + kx]));
+            for (int p = 0; p < NPR; ++p)
+              acc[p] = add2(acc[p], mul2(w2[ky * K + kx], wp[(r * STRIDE + ky) % K][2 * p + kx]));
           }
         }
-      }
-      if (a.has_bn) {
+      } else {
+        float sa[S];
 #pragma unroll
-        for (int j = 0; j < S; ++j) acc[j] = bn_apply(acc[j], bn);
+        for (int j = 0; j < S; ++j) sa[j] = bias;
+#pragma unroll
+        for (int ky = 0; ky < K; ++ky) {
+#pragma unroll
+          for (int kx = 0; kx < K; ++kx) {
+#pragma unroll
+            for (int j = 0; j < S; ++j)
+              sa[j] = __fadd_rn(sa[j], __fmul_rn(wr[ky * K + kx], win[(r * STRIDE + ky) % K][j * STRIDE + kx]));
+          }
+        }
+#pragma unroll
+        for (int p = 0; p < NPR; ++p) acc[p] = pack2(sa[2 * p], sa[2 * p + 1]);
       }
+      if (a.has_bn) bn_apply_packed<NPR>(acc, bnp);
+      if (QM == QM_FPQ && a.q.fpq_fast) fpq_apply_packed_fast<NPR>(acc, a.q, a.q.fpq_min < 0.0f);
+      float out[S];
+#pragma unroll
+      for (int p = 0; p < NPR; ++p) unpack2(acc[p], out[2 * p], out[2 * p + 1]);
       const bool row_ok = oyb + r < a.Ho;
       if (QM == QM_MM_REDUCE) {
 #pragma unroll
         for (int j = 0; j < S; ++j) {
           if (row_ok && ox0 + j < a.Wo) {
-            lo = fminf(lo, acc[j]);
-            hi = fmaxf(hi, acc[j]);
+            lo = fminf(lo, out[j]);
+            hi = fmaxf(hi, out[j]);
           }
         }
       } else {
+        if (!(QM == QM_FPQ && a.q.fpq_fast)) {
 #pragma unroll
-        for (int j = 0; j < S; ++j) acc[j] = quant_apply<QM>(acc[j], a.q, mm);
+          for (int j = 0; j < S; ++j) out[j] = quant_apply<QM>(out[j], a.q, mm);
+        }
         if (row_ok) {
           if (full_vec) {
-            Vec16<T>::store_stream(yp + (size_t)r * a.Wo, acc);
+            Vec16<T>::store_stream(yp + (size_t)r * a.Wo, out);
           } else {
 #pragma unroll
             for (int j = 0; j < S; ++j) {
-              if (ox0 + j < a.Wo) yp[(size_t)r * a.Wo + j] = Elem<T>::from_f32(acc[j]);
+              if (ox0 + j < a.Wo) yp[(size_t)r * a.Wo + j] = Elem<T>::from_f32(out[j]);
             }
           }
         }

@@ -271,8 +271,11 @@ def test_parameters_where_zero_padding_is_not_a_skipped_tap(oracle, cuda_device,
     n, c, h, w = 2, 6, 14, 14
     spec = workloads.LayerSpec("patho", n, c, h, w, 3, 1, 1, None)
     d = _rand_layer(rng, n, c, h, w, 3)
-    d["x"][:, 0] = 0.0
-    d["b"][0] = -0.0          # all-zero accumulation must stay -0.0
+    # channel 0: x = -0.0, w > 0, bias = -0.0: every in-bounds product is -0.0 and the sum
+    # stays -0.0, while a padding zero would contribute +0.0 and flip the sign at the border
+    d["x"][:, 0] = -0.0
+    d["w"][0] = np.abs(d["w"][0]) + np.float32(0.1)
+    d["b"][0] = -0.0
     d["w"][1, 0, 0] = np.inf  # inf * padding-zero would be NaN
     d["w"][2, 2, 2] = np.nan
     d["w"][3, 1, 1] = -np.inf
