@@ -204,6 +204,13 @@ def run_own(args):
 
     def launch(layer, x=None):
         s, _, t, y, _, q, ws = layer
+        if args.ablate:  # profiling only: drop BN and / or the quantizer to attribute instruction counts
+            bn = None if "bn" in args.ablate else t
+            qq = None if "quant" in args.ablate else q
+            ops.fused_dw_bn_quant(t["x"], t["w"], t["b"], bn and bn["beta"], bn and bn["gamma"], bn and bn["mean"],
+                                  bn and bn["var"], s.bn_eps, pad=(s.pad, s.pad), stride=(s.stride, s.stride),
+                                  quant=qq, out=y)
+            return
         ops.fused_dw_bn_quant(t["x"] if x is None else x, t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"],
                               s.bn_eps, pad=(s.pad, s.pad), stride=(s.stride, s.stride), quant=q, comm=comm, ws=ws,
                               out=y)
@@ -218,6 +225,9 @@ def run_own(args):
         torch.cuda.synchronize()
 
     launches_per_step = sum(2 if s.quant["kind"] == "minmax" else 1 for s in specs)
+
+    if args.tune:
+        ops.set_tuning(*[int(v) for v in args.tune.split(",")])
 
     # ---- device-resident timing ---------------------------------------------------------
     for _ in range(args.warmup):
@@ -359,6 +369,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-layer-pass", action="store_true")
+    ap.add_argument("--ablate", default="", help="profiling only: 'bn', 'quant' or 'bn,quant' are left out")
+    ap.add_argument("--tune", default="", help="profiling only: planner override P,row_blocks,threads,rows_per_patch")
     args = ap.parse_args()
     defaults = {"cfg0": 32, "cfg1": 256, "cfg2": 128, "cfg3": 512, "cfg4": 256}
     if args.batch is None:

@@ -24,6 +24,7 @@ struct QuantArgs {
   // power of two in the normal range and max/delta < 2^22: then |x|/delta is the exact
   // product |x| * inv_delta and floor(t + 0.5) can be taken with two directed adds.
   float fpq_max, fpq_min, fpq_delta, fpq_inv_delta;
+  float fpq_nmagic_delta;  // -2^23 * delta (fast form only)
   int fpq_fast;
   // Pow2Quantize.
   float p_max, p_min, prune_thr;
@@ -151,10 +152,9 @@ __device__ __forceinline__ float fpq_apply(float x, const QuantArgs &q) {
     const float ax = fabsf(x);
     float k;
     if (q.fpq_fast) {
-      const float t = __fmul_rn(ax, q.fpq_inv_delta);
-      const float s = __fadd_rd(t, 0.5f);
-      // 0 <= s < 2^22: RD(s + 2^23) - 2^23 == floor(s); NaN propagates.
-      k = __fsub_rn(__fadd_rd(s, 8388608.0f), 8388608.0f);
+      // 0 <= t < 2^22: RD(RD(t + 0.5) + 2^23) - 2^23 == floor(t + 0.5); NaN propagates.
+      const float u = __fmaf_rd(ax, q.fpq_inv_delta, 0.5f);
+      k = __fsub_rn(__fadd_rd(u, 8388608.0f), 8388608.0f);
     } else {
       const float t = __fdiv_rn(ax, q.fpq_delta);
       k = floorf(__fadd_rd(t, 0.5f));
@@ -263,10 +263,20 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
 // bit (signed zeros included), and unlike mul.rn.f32x2 followed by add.rn.f32x2 - which
 // ptxas 12.9 contracts into one fused multiply-add even under --fmad=false, measured on
 // B200 - an fma feeding an add cannot be contracted.
-// The -0.0 addend is read from constant memory so the compiler cannot fold the fma back
-// into a multiply (with an immediate it does, and then contracts again).
+// The -0.0 addend must be opaque to the compiler (with an immediate it folds the fma back
+// into a multiply and then contracts again): negzero2() reads it from constant memory
+// once and pins it in a register pair; callers hand that register to mul2.
 static __constant__ unsigned long long k_negzero2 = 0x8000000080000000ull;
-__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) { return fma2(a, b, k_negzero2); }
+// Keeps a value in its registers: the compiler can neither rematerialise it (re-load it
+// from shared / constant memory at each use) nor see through it.
+__device__ __forceinline__ void pin(f32x2 &v) { asm volatile("" : "+l"(v)); }
+__device__ __forceinline__ void pin(float &v) { asm volatile("" : "+f"(v)); }
+__device__ __forceinline__ f32x2 negzero2() {
+  f32x2 z = k_negzero2;
+  pin(z);
+  return z;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b, f32x2 nz) { return fma2(a, b, nz); }
 // min / max that propagate NaN (x > hi ? hi : x keeps a NaN x, unlike fminf).
 __device__ __forceinline__ float min_nan(float a, float b) {
   float r;
@@ -298,7 +308,7 @@ __device__ __forceinline__ float min3f(float a, float b, float c) {
 // leaves the normal range. That holds for 2^-100 < |a| < 2^100 and 2^-30 <= stdvar <=
 // 2^30; everything else (zeros, infinities, NaN, extreme magnitudes) takes __fdiv_rn.
 struct BnPacked {
-  f32x2 nmean, scale, rcp, nstd, beta;
+  f32x2 nmean, scale, rcp, nstd, beta, nz;
   float stdvar;  // for the out-of-range path
   float glo;     // lower guard on |a|: 2^-100, or +inf when stdvar itself is out of range
 };
@@ -312,6 +322,7 @@ __device__ __forceinline__ BnPacked make_bn_packed(const BnCoef &c) {
   b.rcp = splat2(__frcp_rn(c.stdvar));
   b.nstd = splat2(-c.stdvar);
   b.beta = splat2(c.beta);
+  b.nz = negzero2();
   b.stdvar = c.stdvar;
   const bool safe = c.stdvar >= 9.31322574615478515625e-10f && c.stdvar <= 1073741824.0f;
   b.glo = safe ? DWBNQ_DIV_GUARD_LO : __uint_as_float(0x7f800000u);
@@ -325,12 +336,12 @@ __device__ __forceinline__ void bn_apply_packed(f32x2 *v, const BnPacked &b) {
   float mx = 0.0f, mn = __uint_as_float(0x7f800000u);
 #pragma unroll
   for (int p = 0; p < NP; ++p) {
-    a[p] = mul2(add2(v[p], b.nmean), b.scale);
+    a[p] = mul2(add2(v[p], b.nmean), b.scale, b.nz);
     float lo, hi;
     unpack2(a[p], lo, hi);
     mx = max3f(mx, fabsf(lo), fabsf(hi));
     mn = min3f(mn, fabsf(lo), fabsf(hi));
-    f32x2 q = mul2(a[p], b.rcp);
+    f32x2 q = mul2(a[p], b.rcp, b.nz);
     f32x2 e = fma2(q, b.nstd, a[p]);
     q = fma2(e, b.rcp, q);
     e = fma2(q, b.nstd, a[p]);
@@ -348,33 +359,21 @@ __device__ __forceinline__ void bn_apply_packed(f32x2 *v, const BnPacked &b) {
   for (int p = 0; p < NP; ++p) v[p] = add2(v[p], b.beta);
 }
 
-// ---- FixedPointQuantize on packed pairs (power-of-two delta) --------------------------------
-// Clamp first (max and min lie on the grid, so clamping commutes with the rounding and a
-// NaN stays NaN), then floor(t + 0.5) through two round-down adds as in fpq_apply.
-template <int NP>
-__device__ __forceinline__ void fpq_apply_packed_fast(f32x2 *v, const QuantArgs &q, bool is_signed) {
-  const f32x2 inv = splat2(q.fpq_inv_delta);
-  const f32x2 del = splat2(q.fpq_delta);
-  const f32x2 nmagic = splat2(-8388608.0f);
-#pragma unroll
-  for (int p = 0; p < NP; ++p) {
-    float lo, hi;
-    unpack2(v[p], lo, hi);
-    lo = max_nan(min_nan(lo, q.fpq_max), q.fpq_min);
-    hi = max_nan(min_nan(hi, q.fpq_max), q.fpq_min);
-    float t0, t1;
-    unpack2(mul2(pack2(fabsf(lo), fabsf(hi)), inv), t0, t1);
-    const float k0 = __fadd_rd(__fadd_rd(t0, 0.5f), 8388608.0f);
-    const float k1 = __fadd_rd(__fadd_rd(t1, 0.5f), 8388608.0f);
-    const f32x2 r = mul2(add2(pack2(k0, k1), nmagic), del);
-    if (is_signed) {
-      float r0, r1;
-      unpack2(r, r0, r1);
-      v[p] = pack2(lo < 0.0f ? -r0 : r0, hi < 0.0f ? -r1 : r1);
-    } else {
-      v[p] = r;
-    }
-  }
+// FixedPointQuantize, power-of-two delta, one value, five instructions when unsigned:
+//  - clamp first: max and min lie on the grid, so clamping commutes with the rounding, and
+//    min.NaN / max.NaN keep a NaN;
+//  - u = RD(|xc| * inv_delta + 0.5) in one round-down fma (the product is exact);
+//  - kp = RD(u + 2^23) = floor(u) + 2^23;
+//  - v = kp * delta - 2^23 * delta in one fma: both terms and the result k * delta are
+//    exactly representable, so nothing is rounded.
+template <bool SIGNED>
+__device__ __forceinline__ float fpq_apply_fast(float x, const QuantArgs &q) {
+  const float xc = max_nan(min_nan(x, q.fpq_max), q.fpq_min);
+  // unsigned: xc >= 0 (or -0.0, which the arithmetic below maps to +0.0 as well)
+  const float u = __fmaf_rd(SIGNED ? fabsf(xc) : xc, q.fpq_inv_delta, 0.5f);
+  const float kp = __fadd_rd(u, 8388608.0f);
+  const float v = __fmaf_rn(kp, q.fpq_delta, q.fpq_nmagic_delta);
+  return (SIGNED && xc < 0.0f) ? -v : v;
 }
 
 // One epilogue for all modes (QM_MM_REDUCE does not come here).

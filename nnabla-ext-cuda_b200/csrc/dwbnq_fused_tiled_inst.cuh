@@ -7,47 +7,62 @@ namespace dwbnq {
 
 namespace {
 
-template <typename T, int K, int STRIDE, int QM, bool USE_TMA>
-cudaError_t launch_one(const CUtensorMap &tmap, const FusedArgs &a, const TileCfg &c,
-                       long long ctas, int threads, size_t smem, cudaStream_t stream) {
-  auto kern = fused_tiled_kernel<T, K, STRIDE, kRowsPerPatch, QM, USE_TMA>;
+typedef void (*TiledKernel)(const CUtensorMap, const FusedArgs, const TileCfg);
+
+template <typename T, int K, int STRIDE, int MODE>
+TiledKernel pick_qm(int qm) {
+  switch (qm) {
+    case QM_NONE: return fused_tiled_kernel<T, K, STRIDE, QM_NONE, MODE>;
+    case QM_FPQ: return fused_tiled_kernel<T, K, STRIDE, QM_FPQ, MODE>;
+    case QM_POW2: return fused_tiled_kernel<T, K, STRIDE, QM_POW2, MODE>;
+    case QM_MM_APPLY: return fused_tiled_kernel<T, K, STRIDE, QM_MM_APPLY, MODE>;
+    case QM_MM_REDUCE: return fused_tiled_kernel<T, K, STRIDE, QM_MM_REDUCE, MODE>;
+  }
+  return nullptr;
+}
+
+template <typename T, int K, int STRIDE>
+TiledKernel pick_mode(int qm, int mode) {
+  switch (mode) {
+    case TM_TMA: return pick_qm<T, K, STRIDE, TM_TMA>(qm);
+    case TM_COOP: return pick_qm<T, K, STRIDE, TM_COOP>(qm);
+    case TM_RAW: return pick_qm<T, K, STRIDE, TM_RAW>(qm);
+  }
+  return nullptr;
+}
+
+template <typename T, int K>
+TiledKernel pick(int stride, int qm, int mode) {
+  if (stride == 1) return pick_mode<T, K, 1>(qm, mode);
+  if (stride == 2) return pick_mode<T, K, 2>(qm, mode);
+  return nullptr;
+}
+
+}  // namespace
+
+template <>
+cudaError_t launch_tiled<DWBNQ_INST_T, DWBNQ_INST_K>(int stride, int qm, int mode, const CUtensorMap &tmap,
+                                                     const FusedArgs &a, const TileCfg &c, int ctas,
+                                                     int threads, size_t smem, cudaStream_t stream) {
+  TiledKernel kern = pick<DWBNQ_INST_T, DWBNQ_INST_K>(stride, qm, mode);
+  if (!kern) return cudaErrorInvalidValue;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   kern<<<(unsigned int)ctas, threads, smem, stream>>>(tmap, a, c);
   return cudaGetLastError();
 }
 
-template <typename T, int K, int STRIDE, bool USE_TMA>
-cudaError_t launch_qm(int qm, const CUtensorMap &tmap, const FusedArgs &a, const TileCfg &c,
-                      long long ctas, int threads, size_t smem, cudaStream_t stream) {
-  switch (qm) {
-    case QM_NONE: return launch_one<T, K, STRIDE, QM_NONE, USE_TMA>(tmap, a, c, ctas, threads, smem, stream);
-    case QM_FPQ: return launch_one<T, K, STRIDE, QM_FPQ, USE_TMA>(tmap, a, c, ctas, threads, smem, stream);
-    case QM_POW2: return launch_one<T, K, STRIDE, QM_POW2, USE_TMA>(tmap, a, c, ctas, threads, smem, stream);
-    case QM_MM_APPLY: return launch_one<T, K, STRIDE, QM_MM_APPLY, USE_TMA>(tmap, a, c, ctas, threads, smem, stream);
-    case QM_MM_REDUCE: return launch_one<T, K, STRIDE, QM_MM_REDUCE, USE_TMA>(tmap, a, c, ctas, threads, smem, stream);
-  }
-  return cudaErrorInvalidValue;
-}
-
-}  // namespace
-
 template <>
-cudaError_t launch_tiled<DWBNQ_INST_T, DWBNQ_INST_K>(int stride, int qm, bool use_tma,
-                                                     const CUtensorMap &tmap, const FusedArgs &a,
-                                                     const TileCfg &c, long long ctas, int threads,
-                                                     size_t smem, cudaStream_t stream) {
-  using T = DWBNQ_INST_T;
-  constexpr int K = DWBNQ_INST_K;
-  if (stride == 1) {
-    return use_tma ? launch_qm<T, K, 1, true>(qm, tmap, a, c, ctas, threads, smem, stream)
-                   : launch_qm<T, K, 1, false>(qm, tmap, a, c, ctas, threads, smem, stream);
-  }
-  if (stride == 2) {
-    return use_tma ? launch_qm<T, K, 2, true>(qm, tmap, a, c, ctas, threads, smem, stream)
-                   : launch_qm<T, K, 2, false>(qm, tmap, a, c, ctas, threads, smem, stream);
-  }
-  return cudaErrorInvalidValue;
+cudaError_t tiled_occupancy<DWBNQ_INST_T, DWBNQ_INST_K>(int stride, int qm, int mode, int threads,
+                                                        size_t smem, int *ctas_per_sm) {
+  TiledKernel kern = pick<DWBNQ_INST_T, DWBNQ_INST_K>(stride, qm, mode);
+  if (!kern) return cudaErrorInvalidValue;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  // all of the unified L1 / shared memory as shared memory: the tiles are the working set
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  if (e != cudaSuccess) return e;
+  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(ctas_per_sm, kern, threads, smem);
 }
 
 }  // namespace dwbnq

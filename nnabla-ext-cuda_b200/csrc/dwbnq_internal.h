@@ -18,7 +18,7 @@ void clear_error();
 int enter_device(int device, int *out);
 
 // ---- fused / dw-conv family (fused.cu) --------------------------------------------------
-enum FusedPath : int { PATH_AUTO = -1, PATH_GENERIC = 0, PATH_COOP = 1, PATH_TMA = 2 };
+enum FusedPath : int { PATH_AUTO = -1, PATH_GENERIC = 0, PATH_COOP = 1, PATH_TMA = 2, PATH_RAW = 3 };
 
 struct Plan {
   int path;

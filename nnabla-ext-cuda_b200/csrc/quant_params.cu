@@ -41,6 +41,7 @@ int fill_fpq(QuantArgs *q, int sign, int n, float delta) {
   // delta = 2^(ex-1) exactly, far from the range ends, and max/delta = 2^n_eff - 1 < 2^22.
   q->fpq_fast = (mant == 0.5f && ex > -100 && ex < 100 && n_eff <= 22) ? 1 : 0;
   q->fpq_inv_delta = q->fpq_fast ? 1.0f / delta : 0.0f;
+  q->fpq_nmagic_delta = q->fpq_fast ? -8388608.0f * delta : 0.0f;
   return DWBNQ_OK;
 }
 

@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(_PKG_ROOT, "libdwbnq.so")
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_DEVICE_FLAG = range(7)
 F32, F16 = 0, 1
 Q_NONE, Q_FPQ, Q_POW2, Q_MINMAX = 0, 1, 2, 3
-PATH_AUTO, PATH_GENERIC, PATH_COOP, PATH_TMA = -1, 0, 1, 2
+PATH_AUTO, PATH_GENERIC, PATH_COOP, PATH_TMA, PATH_RAW = -1, 0, 1, 2, 3
 UNIQUE_ID_BYTES = 128
 
 
@@ -67,7 +67,7 @@ SIGNATURES = {
     "dwbnq_fused_plan": (_int, [_P(ConvDesc), _vp, _vp, _P(_int), _P(_int), _P(_int), _P(_int),
                                 _P(_i64), _P(_int)]),
     "dwbnq_set_forced_path": (_int, [_int]),
-    "dwbnq_set_tuning": (_int, [_int, _int, _int]),
+    "dwbnq_set_tuning": (_int, [_int, _int, _int, _int]),
     "dwbnq_comm_get_unique_id": (_int, [_vp]),
     "dwbnq_comm_create": (_int, [_vp, _int, _int, _int, _P(_vp)]),
     "dwbnq_comm_destroy": (_int, [_vp]),

@@ -225,8 +225,9 @@ def set_forced_path(path):
     L.check(L.lib().dwbnq_set_forced_path(int(path)))
 
 
-def set_tuning(planes_per_cta=0, row_blocks_per_tile=0, threads=0):
-    L.check(L.lib().dwbnq_set_tuning(int(planes_per_cta), int(row_blocks_per_tile), int(threads)))
+def set_tuning(planes_per_cta=0, row_blocks_per_tile=0, threads=0, rows_per_patch=0):
+    L.check(L.lib().dwbnq_set_tuning(int(planes_per_cta), int(row_blocks_per_tile), int(threads),
+                                     int(rows_per_patch)))
 
 
 def check_device_flag(device=-1):

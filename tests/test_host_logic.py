@@ -132,12 +132,13 @@ def test_plan_selects_kernel_family(dwlib):
         assert plan(**kw) == dwlib.PATH_GENERIC
     for c, hw, s in ((32, 112, 1), (96, 112, 2), (144, 56, 1), (192, 28, 2), (384, 14, 1), (576, 14, 2), (960, 7, 1)):
         for dt in (dwlib.F32, dwlib.F16):
-            assert plan(dtype=dt, n=4, c=c, h=hw, w=hw, stride_h=s, stride_w=s) in (dwlib.PATH_COOP, dwlib.PATH_TMA)
-            assert 32 <= thr.value <= 256 and thr.value % 32 == 0
-            assert smem.value <= 200 * 1024 and p.value >= 1 and th.value % 7 == 0
+            assert plan(dtype=dt, n=4, c=c, h=hw, w=hw, stride_h=s, stride_w=s) in (dwlib.PATH_COOP, dwlib.PATH_TMA, dwlib.PATH_RAW)
+            assert 64 <= thr.value <= 288 and thr.value % 32 == 0  # consumer warps + the producer warp
+            assert smem.value <= 200 * 1024 and p.value >= 1 and th.value >= 1
             planes = 4 * c
-            n_row_tiles = -(-(-(-((hw + 2 - 3) // s + 1) // 7)) // (th.value // 7))
-            assert ctas.value == -(-planes // p.value) * n_row_tiles
+            ho = (hw + 2 - 3) // s + 1
+            assert ctas.value % (-(-planes // p.value)) == 0          # tiles = plane groups x row tiles
+            assert (ctas.value // (-(-planes // p.value))) * th.value >= ho
     assert lib.dwbnq_set_forced_path(dwlib.PATH_GENERIC) == dwlib.OK
     assert plan(n=4, c=32, h=112, w=112) == dwlib.PATH_GENERIC
     assert lib.dwbnq_set_forced_path(dwlib.PATH_AUTO) == dwlib.OK

@@ -13,15 +13,15 @@ from dwbnq import ops, workloads
 
 pytestmark = pytest.mark.gpu
 
-PATHS = [L.PATH_AUTO, L.PATH_COOP, L.PATH_GENERIC]
-PATH_IDS = ["auto", "coop", "generic"]
+PATHS = [L.PATH_AUTO, L.PATH_COOP, L.PATH_RAW, L.PATH_GENERIC]
+PATH_IDS = ["auto", "coop", "raw", "generic"]
 
 
 @pytest.fixture(autouse=True)
 def _reset_path():
     yield
     ops.set_forced_path(L.PATH_AUTO)
-    ops.set_tuning(0, 0, 0)
+    ops.set_tuning(0, 0, 0, 0)
 
 
 def dev(a, device):
@@ -186,7 +186,7 @@ def _rand_layer(rng, n, c, h, w, k):
             "beta": rng.standard_normal(c).astype(np.float32) * 0.3}
 
 
-@pytest.mark.parametrize("path", [L.PATH_AUTO, L.PATH_COOP], ids=["auto", "coop"])
+@pytest.mark.parametrize("path", [L.PATH_AUTO, L.PATH_COOP, L.PATH_RAW], ids=["auto", "coop", "raw"])
 @pytest.mark.parametrize("k,stride", [(3, 1), (3, 2), (5, 1), (5, 2)])
 def test_edge_shapes(oracle, cuda_device, path, k, stride):
     """Planes smaller than a patch, widths that are not a vector multiple, heights that are
@@ -222,11 +222,11 @@ def test_row_tiled_planes_and_tuning_overrides(oracle, cuda_device, dtype):
         else:
             want = oracle_fused(oracle, d, spec, q)[0]
             inp = d
-        for tune in ((0, 0, 0), (1, 1, 64), (2, 3, 128), (1, 2, 256)):
+        for tune in ((0, 0, 0, 0), (1, 1, 64, 7), (2, 3, 128, 4), (1, 2, 256, 14), (1, 5, 96, 3), (3, 1, 32, 1)):
             ops.set_tuning(*tune)
             got, _ = run_fused(inp, spec, cuda_device, q, dtype=dtype)
             assert_same_bits(got, want, "tall %s tune %s" % ((h, w, k, s), tune))
-        ops.set_tuning(0, 0, 0)
+        ops.set_tuning(0, 0, 0, 0)
 
 
 def test_generic_geometries(oracle, cuda_device):
@@ -263,7 +263,7 @@ def test_generic_geometries(oracle, cuda_device):
     assert_same_bits(got, want, "1-D")
 
 
-@pytest.mark.parametrize("path", [L.PATH_AUTO, L.PATH_COOP], ids=["auto", "coop"])
+@pytest.mark.parametrize("path", [L.PATH_AUTO, L.PATH_COOP, L.PATH_RAW], ids=["auto", "coop", "raw"])
 def test_parameters_where_zero_padding_is_not_a_skipped_tap(oracle, cuda_device, path):
     """bias == -0.0 and non-finite weights: the reference skips out-of-bounds taps, a
     zero-padded tile would add w * 0; the tiled family must fall back to exact evaluation."""
