@@ -194,17 +194,16 @@ int dwbnq_fused_fwd(const dwbnq_conv_desc *desc, float bn_eps, const dwbnq_quant
  * pointer alignment: 0 = generic direct kernel, 1 = zero-padded shared-memory tile filled
  * by cooperative loads, 2 = zero-padded tile filled by TMA tiled loads, 3 = whole planes
  * copied by the bulk copy engine (planes whose row pitch is not a multiple of 16 bytes).
- * *ctas is the number of tiles; the launch uses min(tiles, resident CTAs) persistent
- * CTAs. Diagnostic only. */
+ * *ctas is the number of tiles = CTAs of the launch. Diagnostic only. */
 int dwbnq_fused_plan(const dwbnq_conv_desc *desc, const void *x, const void *y,
                      int *path_out, int *planes_per_cta, int *rows_per_tile,
                      int *threads, int64_t *ctas, int *smem_bytes);
 /* Environment switch DWBNQ_FORCE_PATH=generic|coop|tma|raw (read at each call) and this
  * setter (-1 = automatic) restrict that choice; used by the tests to cover every path. */
 int dwbnq_set_forced_path(int path);
-/* Planner overrides for tuning runs (0 = automatic): planes per tile, patch rows (row
- * blocks) per tile, threads per CTA, output rows per patch. Values that do not fit the
- * shared-memory budget fall back to the generic kernel. */
+/* Planner overrides for tuning runs (0 = automatic): planes per tile, 7-row patch blocks
+ * per tile, threads per CTA; the fourth value is reserved (pass 0). Values that do not fit
+ * the shared-memory budget fall back to the generic kernel. */
 int dwbnq_set_tuning(int planes_per_cta, int row_blocks_per_tile, int threads, int rows_per_patch);
 
 /* ---- communicator: the one exchange the path needs (per-channel min/max) ----------- */

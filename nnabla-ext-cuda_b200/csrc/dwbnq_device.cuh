@@ -315,14 +315,14 @@ struct BnPacked {
 #define DWBNQ_DIV_GUARD_LO 7.888609052e-31f /* 2^-100 */
 #define DWBNQ_DIV_GUARD_HI 1.267650600e30f  /* 2^100  */
 
-__device__ __forceinline__ BnPacked make_bn_packed(const BnCoef &c) {
+__device__ __forceinline__ BnPacked make_bn_packed(const BnCoef &c, f32x2 nz) {
   BnPacked b;
   b.nmean = splat2(-c.mean);
   b.scale = splat2(c.scale);
   b.rcp = splat2(__frcp_rn(c.stdvar));
   b.nstd = splat2(-c.stdvar);
   b.beta = splat2(c.beta);
-  b.nz = negzero2();
+  b.nz = nz;
   b.stdvar = c.stdvar;
   const bool safe = c.stdvar >= 9.31322574615478515625e-10f && c.stdvar <= 1073741824.0f;
   b.glo = safe ? DWBNQ_DIV_GUARD_LO : __uint_as_float(0x7f800000u);

@@ -6,14 +6,15 @@
 //    (any kernel size, stride, pad, dilation, multiplier, 1-D) and is also the in-kernel
 //    fall-back of the tiled family for the parameter values where "skip the tap" and
 //    "add w * 0" differ (bias == -0.0, non-finite weights).
-//  * fused_tiled_kernel: persistent CTAs walk over tiles of `P` (n, c) planes x a band of
-//    output rows. The input of a tile is staged in shared memory through a two-stage
-//    ring, the load of tile i+1 in flight while tile i is computed: one TMA tiled box
-//    load per plane (halo rows / columns arrive as zeros), or - where the row pitch is
-//    not a multiple of 16 bytes (14x14, 7x7 planes) - one bulk async copy of the
-//    contiguous planes with the halo masked when the window is read. Each thread
-//    computes R x VEC output patches from a rolling register window on packed f32x2
-//    pairs, applies BN and the quantizer in registers and stores 16-byte vectors.
+//  * fused_tiled_kernel: a CTA owns one tile of `P` (n, c) planes x a band of output rows.
+//    The input of the tile is staged in shared memory by the copy engines - one TMA tiled
+//    box load per plane (halo rows / columns arrive as zeros), or, where the row pitch is
+//    not a multiple of 16 bytes (14x14, 7x7 planes), one bulk async copy of the contiguous
+//    planes with the halo masked when the window is read - while the threads build the
+//    per-plane parameter records; several resident CTAs per SM overlap one tile's
+//    arithmetic with the next tile's copy. Each thread computes R x VEC output patches
+//    from a rolling register window on packed f32x2 pairs, applies BN and the quantizer in
+//    registers and stores 16-byte vectors.
 //
 // Arithmetic contract (identical in both families): accumulator starts at the bias,
 // taps in ky-major / kx-minor order, product and sum rounded separately (no FMA),
@@ -272,10 +273,11 @@ __device__ __forceinline__ void static_loop(F &&f) {
 
 // ---- the tiled kernel ----------------------------------------------------------------
 
-// Per-plane parameter record in shared memory, laid out so the consumer can fetch packed
-// operands with 16-byte loads and no register shuffling:
+// Per-plane parameter record in shared memory, built once per CTA by one thread per plane
+// and laid out so the consumer fetches packed operands with 8/16-byte loads and no register
+// shuffling:
 //   [0, 2*KK)  weight pairs (w, w)
-//   PAIRS + 0  (bias, bias)      + 2 (-mean, -mean)   + 4 (scale, scale)
+//   PAIRS + 0  (bias, bias)      + 2 (-mean, -mean)     + 4 (scale, scale)
 //         + 6  (rcp, rcp)        + 8 (-stdvar, -stdvar) + 10 (beta, beta)
 //   SCAL  + 0  stdvar  1 guard_lo  2 mm_scale  3 mm_lo  4 mm_hi  5 exact-evaluation flag
 template <int K> struct ParamLayout {
@@ -283,24 +285,18 @@ template <int K> struct ParamLayout {
   static constexpr int PAIRS = 2 * KK + (2 * KK) % 4;  // 16-byte aligned
   static constexpr int SCAL = PAIRS + 12;
   static constexpr int COUNT = SCAL + 8;
-  static constexpr int JOBS = KK + 3;  // producer jobs per plane: weights, bias+flag, BN, MinMax
 };
-constexpr int kStages = 3;
 
 // Shared-memory carve-up, also used by the host planner to size the launch.
 __host__ __device__ inline size_t tiled_smem_bytes(int P, int stage_elems, int elem_size, int K) {
   const int kk2 = 2 * K * K;
   const int count = kk2 + kk2 % 4 + 20;
-  size_t s = (size_t)kStages * stage_elems * elem_size;   // stage buffers (128 B multiples)
-  s += (size_t)kStages * P * count * sizeof(float);        // parameter records
-  s += (size_t)kStages * P * 2 * sizeof(unsigned int);     // per-plane encoded min / max
+  size_t s = (size_t)stage_elems * elem_size;       // the tile (128 B multiple)
+  s += (size_t)P * count * sizeof(float);           // parameter records
+  s += (size_t)P * 2 * sizeof(unsigned int);        // per-plane encoded min / max
   s = (s + 15) / 16 * 16;
-  s += 2 * kStages * 8;                                    // full / empty mbarriers
+  s += 16;                                          // mbarrier
   return s;
-}
-
-__device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
 // One bulk async copy global -> shared (16-byte aligned, size a multiple of 16).
@@ -322,141 +318,121 @@ __device__ __forceinline__ void load_window_raw(const T *p, const unsigned int *
     v[i] = __uint_as_float(__float_as_uint(Elem<T>::to_f32(p[i])) & mask[i]);
 }
 
-template <typename T, int K, int STRIDE, int QM, int MODE>
-__global__ void __launch_bounds__(288, 2)
+// Resident CTAs per SM the kernel is compiled for: the 3x3 float kernels fit 64 registers
+// (4 x 256 threads), the wider windows of the other instantiations get twice as many.
+__host__ __device__ constexpr int tiled_min_blocks(int elem_size, int K, int mode) {
+  return (elem_size == 4 && K == 3 && mode != TM_RAW) ? 4 : 2;
+}
+
+// One CTA = one tile: P planes x R*n_rb output rows. The tile copy (TMA / bulk) is issued
+// first and flies while the per-plane parameter records are built; several CTAs per SM give
+// the overlap between one tile's arithmetic and the next tile's copy.
+template <typename T, int K, int STRIDE, int R, int QM, int MODE>
+__global__ void __launch_bounds__(256, tiled_min_blocks(sizeof(T), K, MODE))
     fused_tiled_kernel(const __grid_constant__ CUtensorMap tmap, const FusedArgs a,
                        const TileCfg c) {
-  constexpr int S = Elem<T>::VEC;
+  constexpr int S = Elem<T>::VEC;  // outputs per thread and patch row = one 16-byte vector
   constexpr int PAD = K / 2;
-  constexpr int NV = (S - 1) * STRIDE + K;
+  constexpr int NV = (S - 1) * STRIDE + K;  // window elements per row
   constexpr bool ASYNC = MODE != TM_COOP;
   using PL = ParamLayout<K>;
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  T *stage_base = reinterpret_cast<T *>(smem_raw);
-  float *prm_base = reinterpret_cast<float *>(smem_raw + (size_t)kStages * c.stage_elems * sizeof(T));
-  unsigned int *red_base = reinterpret_cast<unsigned int *>(prm_base + kStages * c.P * PL::COUNT);
-  unsigned long long *full = reinterpret_cast<unsigned long long *>(
-      (reinterpret_cast<uintptr_t>(red_base + kStages * 2 * c.P) + 15) / 16 * 16);
-  unsigned long long *empty = full + kStages;
+  T *tiles = reinterpret_cast<T *>(smem_raw);
+  float *prm = reinterpret_cast<float *>(smem_raw + (size_t)c.stage_elems * sizeof(T));
+  unsigned int *red = reinterpret_cast<unsigned int *>(prm + c.P * PL::COUNT);
+  unsigned long long *bar = reinterpret_cast<unsigned long long *>(
+      (reinterpret_cast<uintptr_t>(red + 2 * c.P) + 15) / 16 * 16);
 
-  // Warp roles: the last warp produces (parameters + tile copies), the others consume.
   const int tid = threadIdx.x;
-  const int lane = tid & 31;
-  const int n_cwarps = (blockDim.x >> 5) - 1;
-  const bool is_producer = (tid >> 5) == n_cwarps;
+  const int nthr = blockDim.x;
   const int n_planes = (int)(a.n * a.OC);  // multiplier == 1; the planner keeps it below 2^31
-  const int rows_alloc = c.box_rows * c.n_boxes;
   const T *x = static_cast<const T *>(a.x);
   T *y = static_cast<T *>(a.y);
   const int plane_elems = a.H * a.W;
 
-  if (tid == 0) {
-    for (int st = 0; st < kStages; ++st) {
-      mbar_init(&full[st], 1);          // the producer's arrive (+ the copies' bytes)
-      mbar_init(&empty[st], n_cwarps);  // one arrive per consumer warp
-    }
+  // this CTA's tile
+  const int grp = blockIdx.x / c.n_row_tiles;
+  const int plane0 = grp * c.P;
+  const int pv = min(c.P, n_planes - plane0);
+  const int oy0 = (blockIdx.x - grp * c.n_row_tiles) * c.TH;
+  // TM_RAW: a tile whose byte span is not a multiple of 16 (the ragged last group, or an
+  // unaligned tensor) is copied by the threads instead of by the bulk engine.
+  const bool async_tile = MODE == TM_TMA || (MODE == TM_RAW && c.vec_fill != 0 &&
+                                            ((pv * plane_elems * (int)sizeof(T)) % 16) == 0);
+
+  if (ASYNC && tid == 0) {
+    mbar_init(bar, 1);
     mbar_fence_init();
-  }
-  if (QM == QM_MM_REDUCE) {
-    for (int i = tid; i < kStages * c.P; i += blockDim.x) {
-      red_base[2 * i] = DWBNQ_ENC_POS_INF;
-      red_base[2 * i + 1] = DWBNQ_ENC_NEG_INF;
-    }
-  }
-  __syncthreads();  // the only CTA-wide barrier: from here the warps run decoupled
-
-  // Tile t -> (first plane, planes in the tile, first output row).
-  struct Tile {
-    int plane0, pv, oy0;
-    bool async;
-  };
-  auto tile_of = [&](int t) {
-    Tile r;
-    const int grp = t / c.n_row_tiles;
-    r.plane0 = grp * c.P;
-    r.pv = min(c.P, n_planes - r.plane0);
-    r.oy0 = (t - grp * c.n_row_tiles) * c.TH;
-    // TM_RAW: a tile whose byte span is not a multiple of 16 (the ragged last group, or an
-    // unaligned tensor) is copied by the threads instead of by the bulk engine.
-    r.async = MODE == TM_TMA ||
-              (MODE == TM_RAW && c.vec_fill != 0 && ((r.pv * plane_elems * (int)sizeof(T)) % 16) == 0);
-    return r;
-  };
-
-  // Asynchronous tiles: one producer lane arms the stage's full barrier and issues the copies.
-  auto issue_load = [&](int st, const Tile &tl) {
-    if (!ASYNC || !tl.async) return;
-    T *dst = stage_base + (size_t)st * c.stage_elems;
-    if (MODE == TM_TMA) {
-      mbar_expect_tx(&full[st], (unsigned int)((size_t)tl.pv * rows_alloc * c.WS * sizeof(T)));
-      const int iy0 = tl.oy0 * STRIDE - PAD;
-      for (int pl = 0; pl < tl.pv; ++pl)
-        for (int bx = 0; bx < c.n_boxes; ++bx)
-          tma_load_3d(dst + (size_t)pl * c.tile_elems + (size_t)bx * c.box_rows * c.WS, &tmap, -S,
-                      iy0 + bx * c.box_rows, tl.plane0 + pl, &full[st]);
-    } else {
-      const unsigned int bytes = (unsigned int)(tl.pv * plane_elems * sizeof(T));
-      mbar_expect_tx(&full[st], bytes);
-      bulk_load_1d(dst + c.raw_lead, x + (long long)tl.plane0 * plane_elems, bytes, &full[st]);
-    }
-  };
-
-  // Per-plane parameter records of a tile: JOBS small jobs per plane spread over the producer lanes.
-  auto load_params = [&](int st, const Tile &tl) {
-    const T *w = static_cast<const T *>(a.w);
-    const T *b = static_cast<const T *>(a.b);
-    float *prm = prm_base + (size_t)st * c.P * PL::COUNT;
-    for (int i = lane; i < tl.pv * PL::JOBS; i += 32) {
-      const int pl = i / PL::JOBS;
-      const int j = i - pl * PL::JOBS;
-      const int ch = (tl.plane0 + pl) % a.OC;
-      float *rec = prm + pl * PL::COUNT;
-      if (j < PL::KK) {
-        const float wv = Elem<T>::to_f32(w[ch * PL::KK + j]);
-        rec[2 * j] = wv;
-        rec[2 * j + 1] = wv;
-      } else if (j == PL::KK) {
-        const float bv = b ? Elem<T>::to_f32(b[ch]) : 0.0f;
-        rec[PL::PAIRS] = bv;
-        rec[PL::PAIRS + 1] = bv;
-        // The tile treats out-of-bounds taps as w * (+0.0) added to the accumulator, the
-        // contract is "skip the tap". They differ only when w * 0 is not +-0 (non-finite
-        // weight) or when the accumulator can be -0.0 (bias == -0.0): flag the plane for
-        // exact evaluation.
-        bool exact = __float_as_uint(bv) == 0x80000000u;
-        for (int q = 0; q < PL::KK; ++q)
-          exact = exact || !(fabsf(Elem<T>::to_f32(w[ch * PL::KK + q])) <= 3.402823466e38f);
-        rec[PL::SCAL + 5] = exact ? 1.0f : 0.0f;
-      } else if (j == PL::KK + 1) {
-        if (a.has_bn) {
-          const BnCoef bc = load_bn<T>(a, ch);
-          const float rcp = __frcp_rn(bc.stdvar);
-          const bool safe = bc.stdvar >= 9.31322574615478515625e-10f && bc.stdvar <= 1073741824.0f;
-          float *pr = rec + PL::PAIRS + 2;
-          pr[0] = pr[1] = -bc.mean;
-          pr[2] = pr[3] = bc.scale;
-          pr[4] = pr[5] = rcp;
-          pr[6] = pr[7] = -bc.stdvar;
-          pr[8] = pr[9] = bc.beta;
-          rec[PL::SCAL] = bc.stdvar;
-          rec[PL::SCAL + 1] = safe ? DWBNQ_DIV_GUARD_LO : __uint_as_float(0x7f800000u);
-        }
-      } else if (QM == QM_MM_APPLY) {
-        rec[PL::SCAL + 2] = a.q.mm_scale[ch];
-        rec[PL::SCAL + 3] = a.q.mm_lo[ch];
-        rec[PL::SCAL + 4] = a.q.mm_hi[ch];
+    if (async_tile) {
+      if (MODE == TM_TMA) {
+        const int rows_alloc = c.box_rows * c.n_boxes;
+        mbar_expect_tx(bar, (unsigned int)((size_t)pv * rows_alloc * c.WS * sizeof(T)));
+        const int iy0 = oy0 * STRIDE - PAD;
+        for (int pl = 0; pl < pv; ++pl)
+          for (int bx = 0; bx < c.n_boxes; ++bx)
+            tma_load_3d(tiles + (size_t)pl * c.tile_elems + (size_t)bx * c.box_rows * c.WS, &tmap, -S,
+                        iy0 + bx * c.box_rows, plane0 + pl, bar);
+      } else {
+        const unsigned int bytes = (unsigned int)(pv * plane_elems * sizeof(T));
+        mbar_expect_tx(bar, bytes);
+        bulk_load_1d(tiles + c.raw_lead, x + (long long)plane0 * plane_elems, bytes, bar);
       }
     }
-  };
+  }
 
-  // TM_COOP: every 16-byte group of the zero-padded tile is produced by one producer lane.
-  auto coop_fill = [&](int st, const Tile &tl) {
-    const int iy0 = tl.oy0 * STRIDE - PAD;
-    T *dst = stage_base + (size_t)st * c.stage_elems;
+  // ---- per-plane parameter records: one thread per plane (the copy above is in flight) -----
+  for (int pl = tid; pl < pv; pl += nthr) {
+    const T *w = static_cast<const T *>(a.w);
+    const int ch = (plane0 + pl) % a.OC;
+    float *rec = prm + pl * PL::COUNT;
+    // The tile treats out-of-bounds taps as w * (+0.0) added to the accumulator, the
+    // contract is "skip the tap". They differ only when w * 0 is not +-0 (non-finite
+    // weight) or when the accumulator can be -0.0 (bias == -0.0): flag the plane for exact
+    // evaluation.
+    bool exact = false;
+#pragma unroll
+    for (int i = 0; i < PL::KK; ++i) {
+      const float wv = Elem<T>::to_f32(w[ch * PL::KK + i]);
+      rec[2 * i] = wv;
+      rec[2 * i + 1] = wv;
+      exact = exact || !(fabsf(wv) <= 3.402823466e38f);
+    }
+    const float bv = a.b ? Elem<T>::to_f32(static_cast<const T *>(a.b)[ch]) : 0.0f;
+    exact = exact || __float_as_uint(bv) == 0x80000000u;
+    rec[PL::PAIRS] = rec[PL::PAIRS + 1] = bv;
+    if (a.has_bn) {
+      const BnCoef bc = load_bn<T>(a, ch);
+      const float rcp = __frcp_rn(bc.stdvar);
+      const bool safe = bc.stdvar >= 9.31322574615478515625e-10f && bc.stdvar <= 1073741824.0f;
+      float *pr = rec + PL::PAIRS + 2;
+      pr[0] = pr[1] = -bc.mean;
+      pr[2] = pr[3] = bc.scale;
+      pr[4] = pr[5] = rcp;
+      pr[6] = pr[7] = -bc.stdvar;
+      pr[8] = pr[9] = bc.beta;
+      rec[PL::SCAL] = bc.stdvar;
+      rec[PL::SCAL + 1] = safe ? DWBNQ_DIV_GUARD_LO : __uint_as_float(0x7f800000u);
+    }
+    if (QM == QM_MM_APPLY) {
+      rec[PL::SCAL + 2] = a.q.mm_scale[ch];
+      rec[PL::SCAL + 3] = a.q.mm_lo[ch];
+      rec[PL::SCAL + 4] = a.q.mm_hi[ch];
+    }
+    rec[PL::SCAL + 5] = exact ? 1.0f : 0.0f;
+    if (QM == QM_MM_REDUCE) {
+      red[2 * pl] = DWBNQ_ENC_POS_INF;
+      red[2 * pl + 1] = DWBNQ_ENC_NEG_INF;
+    }
+  }
+
+  // ---- tiles the copy engines do not take -----------------------------------------------
+  if (MODE == TM_COOP) {
+    // every 16-byte group of the zero-padded tile is produced by one thread
+    const int iy0 = oy0 * STRIDE - PAD;
     const int gpr = c.WS / S;
-    const int n_groups = tl.pv * c.TR * gpr;
-    for (int g = lane; g < n_groups; g += 32) {
+    const int n_groups = pv * c.TR * gpr;
+    for (int g = tid; g < n_groups; g += nthr) {
       const int pl = g / (c.TR * gpr);
       const int rem = g - pl * (c.TR * gpr);
       const int tr = rem / gpr;
@@ -467,7 +443,7 @@ __global__ void __launch_bounds__(288, 2)
 #pragma unroll
       for (int j = 0; j < S; ++j) v[j] = 0.0f;
       if (iy >= 0 && iy < a.H && ix0 + S > 0 && ix0 < a.W) {
-        const T *src = x + ((long long)(tl.plane0 + pl) * a.H + iy) * a.W + ix0;
+        const T *src = x + ((long long)(plane0 + pl) * a.H + iy) * a.W + ix0;
         if (c.vec_fill && ix0 >= 0 && ix0 + S <= a.W) {
           Vec16<T>::load_stream(src, v);
         } else {
@@ -476,315 +452,238 @@ __global__ void __launch_bounds__(288, 2)
             if (ix0 + j >= 0 && ix0 + j < a.W) v[j] = Elem<T>::to_f32(src[j]);
         }
       }
-      Vec16<T>::store(dst + (size_t)pl * c.tile_elems + (size_t)tr * c.WS + gc * S, v);
+      Vec16<T>::store(tiles + (size_t)pl * c.tile_elems + (size_t)tr * c.WS + gc * S, v);
     }
-  };
-  // TM_RAW, tile the bulk engine cannot take: plain element copy of the planes.
-  auto raw_copy = [&](int st, const Tile &tl) {
-    const int n = tl.pv * plane_elems;
-    T *dst = stage_base + (size_t)st * c.stage_elems + c.raw_lead;
-    const T *src = x + (long long)tl.plane0 * plane_elems;
-    for (int i = lane; i < n; i += 32) dst[i] = src[i];
-  };
+  } else if (MODE == TM_RAW && !async_tile) {
+    const int n = pv * plane_elems;
+    T *dst = tiles + c.raw_lead;
+    const T *src = x + (long long)plane0 * plane_elems;
+    for (int i = tid; i < n; i += nthr) dst[i] = src[i];
+  }
+  __syncthreads();  // records, thread-copied data and the barrier initialisation are visible
 
-  const int t_first = blockIdx.x;
-  const int t_step = gridDim.x;
-  if (t_first >= c.n_tiles) return;
-  const int n_my = (c.n_tiles - t_first + t_step - 1) / t_step;  // tiles of this CTA
-
-  if (is_producer) {
-    // ---- producer warp ------------------------------------------------------------------
-    // Waits (lane 0 polls, bounded) until every consumer warp has released the stage.
-    auto wait_empty = [&](int st, unsigned int parity) {
-      int ok = 1;
-      if (lane == 0) ok = mbar_wait_bounded(&empty[st], parity) ? 1 : 0;
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok && lane == 0 && a.flag) atomicExch(a.flag, 2);
-      return ok != 0;
-    };
-    // Moves a finished tile's per-plane min / max to the per-channel slots and re-arms them.
-    auto flush_red = [&](int st, const Tile &tl) {
-      unsigned int *red = red_base + (size_t)st * 2 * c.P;
-      for (int i = lane; i < tl.pv; i += 32) {
-        const int ch = (tl.plane0 + i) % a.OC;
-        atomicMin(a.q.mm_enc_min + ch, red[2 * i]);
-        atomicMax(a.q.mm_enc_max + ch, red[2 * i + 1]);
-        red[2 * i] = DWBNQ_ENC_POS_INF;
-        red[2 * i + 1] = DWBNQ_ENC_NEG_INF;
-      }
-    };
-    for (int i = 0; i < n_my; ++i) {
-      const int st = i % kStages;
-      const int use = i / kStages;
-      const Tile tl = tile_of(t_first + i * t_step);
-      if (use > 0) {
-        if (!wait_empty(st, (unsigned int)(use - 1) & 1u)) return;
-        if (QM == QM_MM_REDUCE) flush_red(st, tile_of(t_first + (i - kStages) * t_step));
-      }
-      load_params(st, tl);
-      if (ASYNC && tl.async) {
-        __syncwarp();  // the record stores of all lanes precede lane 0's releasing arrive
-        if (lane == 0) issue_load(st, tl);
-      } else {
-        if (MODE == TM_COOP) coop_fill(st, tl);
-        else raw_copy(st, tl);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&full[st]);
-      }
-    }
-    if (QM == QM_MM_REDUCE) {
-      // the last kStages tiles have not been flushed yet
-      for (int i = max(0, n_my - kStages); i < n_my; ++i) {
-        const int st = i % kStages;
-        if (!wait_empty(st, (unsigned int)(i / kStages) & 1u)) return;
-        flush_red(st, tile_of(t_first + i * t_step));
-      }
-    }
+  // Every lane waits itself with the hardware parking it (a one-lane poll would leave its
+  // warp split in two for the rest of the kernel).
+  if (ASYNC && async_tile && !mbar_wait_bounded(bar, 0)) {
+    if (a.flag) atomicExch(a.flag, 1);
     return;
   }
 
-  // ---- consumer warps ---------------------------------------------------------------------
+  // ---- consumer ---------------------------------------------------------------------------
+  // R x S output patches from a rolling K-row register window, fully unrolled. Arithmetic
+  // runs on packed pairs of horizontally adjacent outputs (f32x2). With stride 1 the window
+  // of a row is kept as its NV-1 consecutive pairs (v[i], v[i+1]) so every tap of an output
+  // pair is one packed multiply and one packed add; with stride 2 (and for the
+  // register-heavy 5x5 half case) the taps stay scalar and only BN is packed.
+  constexpr bool PACKED_CONV = (STRIDE == 1) && !(K == 5 && sizeof(T) == 2);
+  constexpr int NPR = S / 2;   // output pairs per patch row
+  constexpr int NWP = NV - 1;  // consecutive pairs of a window row
   const f32x2 nz = negzero2();
-  const int nthr = n_cwarps * 32;
-  for (int ti = 0; ti < n_my; ++ti) {
-    const int st = ti % kStages;
-    // Every lane waits itself (the hardware parks it): a lane-0-only poll would leave the
-    // warp split in two for the whole tile.
-    if (!mbar_wait_bounded(&full[st], (unsigned int)(ti / kStages) & 1u)) {
-      if (a.flag) atomicExch(a.flag, 1);
-      return;
-    }
-    const Tile cur = tile_of(t_first + ti * t_step);
-    const int plane0 = cur.plane0;
-    const int pv = cur.pv;
-    const int oy0 = cur.oy0;
-    const T *tiles = stage_base + (size_t)st * c.stage_elems;
-    const float *prm = prm_base + (size_t)st * c.P * PL::COUNT;
-    unsigned int *red = red_base + (size_t)st * 2 * c.P;
+  const int ipp = c.n_strips * c.n_rb;  // items per plane
+  const int n_items = pv * ipp;
+  for (int it = tid; it < n_items; it += nthr) {
+    const int pl = it / ipp;
+    const int rem = it - pl * ipp;
+    const int rb = rem / c.n_strips;
+    const int sx = rem - rb * c.n_strips;
+    const int ox0 = sx * S;
+    const int oyb = oy0 + rb * R;
+    const int plane = plane0 + pl;
+    T *yp = y + ((long long)plane * a.Ho + oyb) * a.Wo + ox0;
+    const float *pp = prm + pl * PL::COUNT;
 
-    // ---- consumer: R x S output patches from a rolling K-row register window -------------
-    // Arithmetic runs on packed pairs of horizontally adjacent outputs (f32x2). With stride
-    // 1 the window of a row is kept as its NV-1 consecutive pairs (v[i], v[i+1]) so every
-    // tap of an output pair is one packed multiply and one packed add; with stride 2 (and
-    // for the register-heavy 5x5 half case) the taps stay scalar and only BN is packed.
-    // The rows of a patch are walked in groups of K so the window slots (row mod K) are
-    // compile-time constants while the patch height R stays a run-time value.
-    constexpr bool PACKED_CONV = (STRIDE == 1) && !(K == 5 && S == 8);
-    constexpr int NPR = S / 2;   // output pairs per patch row
-    constexpr int NWP = NV - 1;  // consecutive pairs of a window row
-    const int ipp = c.n_strips * c.n_rb;  // items per plane
-    const int n_items = pv * ipp;
-    for (int it = tid; it < n_items; it += nthr) {
-      const int pl = it / ipp;
-      const int rem = it - pl * ipp;
-      const int rb = rem / c.n_strips;
-      const int sx = rem - rb * c.n_strips;
-      const int ox0 = sx * S;
-      const int oyb = oy0 + rb * c.R;
-      const int plane = plane0 + pl;
-      T *yp = y + ((long long)plane * a.Ho + oyb) * a.Wo + ox0;
-      const float *pp = prm + pl * PL::COUNT;
-
-      if (pp[PL::SCAL + 5] != 0.0f) {
-        // exact evaluation of this patch (see load_params)
-        const int oc = plane % a.OC;
-        float lo = __uint_as_float(0x7f800000u), hi = __uint_as_float(0xff800000u);
-        for (int r = 0; r < c.R; ++r) {
-          for (int j = 0; j < S; ++j) {
-            if (oyb + r >= a.Ho || ox0 + j >= a.Wo) continue;
-            const float v = prequant_point<T>(a, plane / a.OC, oc, oyb + r, ox0 + j);
-            if (QM == QM_MM_REDUCE) {
-              lo = fminf(lo, v);
-              hi = fmaxf(hi, v);
-            } else {
-              yp[(size_t)r * a.Wo + j] = Elem<T>::from_f32(quant_apply<QM>(v, a.q, load_mm<QM>(a, oc)));
-            }
-          }
-        }
-        if (QM == QM_MM_REDUCE) {
-          atomicMin(red + 2 * pl, enc_ordered(lo));
-          atomicMax(red + 2 * pl + 1, enc_ordered(hi));
-        }
-        continue;
-      }
-
-      // packed operands straight from the record
-      const f32x2 *pq = reinterpret_cast<const f32x2 *>(pp);
-      f32x2 w2[PACKED_CONV ? PL::KK : 1];
-      float wr[PACKED_CONV ? 1 : PL::KK];
-#pragma unroll
-      for (int i = 0; i < PL::KK; ++i) {
-        if (PACKED_CONV) {
-          w2[i] = pq[i];
-          pin(w2[i]);
-        } else {
-          wr[i] = pp[2 * i];
-          pin(wr[i]);
-        }
-      }
-      f32x2 bias2 = pq[PL::PAIRS / 2];
-      pin(bias2);
-      BnPacked bnp;
-      bnp.nmean = pq[PL::PAIRS / 2 + 1];
-      bnp.scale = pq[PL::PAIRS / 2 + 2];
-      bnp.rcp = pq[PL::PAIRS / 2 + 3];
-      bnp.nstd = pq[PL::PAIRS / 2 + 4];
-      bnp.beta = pq[PL::PAIRS / 2 + 5];
-      bnp.nz = nz;
-      bnp.stdvar = pp[PL::SCAL];
-      bnp.glo = pp[PL::SCAL + 1];
-      pin(bnp.nmean);
-      pin(bnp.scale);
-      pin(bnp.rcp);
-      pin(bnp.nstd);
-      pin(bnp.beta);
-      pin(bnp.glo);
-      const MmCoef mm{pp[PL::SCAL + 2], pp[PL::SCAL + 3], pp[PL::SCAL + 4]};
-      const bool full_vec = c.vec_store && (ox0 + S <= a.Wo);
-
-      // Window source. Padded modes: 16-byte aligned position of the first output's centre
-      // tap column in tile row 0 of this row block. Raw mode: element (row 0, column of
-      // window position 0) of the plane, any alignment, plus the per-position halo masks.
-      const T *tp;
-      unsigned int cmask[MODE == TM_RAW ? NV : 1];
-      int iy_first = 0;
-      int row_pitch;
-      if (MODE == TM_RAW) {
-        const int c0 = ox0 * STRIDE - PAD;
-        iy_first = rb * c.R * STRIDE - PAD;
-        row_pitch = a.W;
-        tp = tiles + c.raw_lead + pl * c.tile_elems + iy_first * a.W + c0;
-#pragma unroll
-        for (int i = 0; i < NV; ++i) cmask[i] = (c0 + i >= 0 && c0 + i < a.W) ? 0xffffffffu : 0u;
-      } else {
-        row_pitch = c.WS;
-        tp = tiles + pl * c.tile_elems + (rb * c.R * STRIDE) * c.WS + S + sx * (S * STRIDE);
-      }
-
+    if (pp[PL::SCAL + 5] != 0.0f) {
+      // exact evaluation of this patch, tap by tap from global memory
+      const int oc = plane % a.OC;
       float lo = __uint_as_float(0x7f800000u), hi = __uint_as_float(0xff800000u);
-      // window storage: packed pairs or scalars, whichever the conv uses
-      f32x2 wp[PACKED_CONV ? K : 1][PACKED_CONV ? NWP : 1];
-      float win[PACKED_CONV ? 1 : K][PACKED_CONV ? 1 : NV];
-      // loads tile row `row` of this item into window slot `slot` (compile-time)
-      auto load_row = [&](int row, auto slot_c) {
-        constexpr int slot = decltype(slot_c)::value;
-        float v[NV];
-        if (MODE == TM_RAW) {
-          const int iy = iy_first + row;
-          if (iy >= 0 && iy < a.H) {
-            load_window_raw<T, NV>(tp + row * row_pitch, cmask, v);
+      for (int r = 0; r < R; ++r) {
+        for (int j = 0; j < S; ++j) {
+          if (oyb + r >= a.Ho || ox0 + j >= a.Wo) continue;
+          const float v = prequant_point<T>(a, plane / a.OC, oc, oyb + r, ox0 + j);
+          if (QM == QM_MM_REDUCE) {
+            lo = fminf(lo, v);
+            hi = fmaxf(hi, v);
           } else {
-#pragma unroll
-            for (int i = 0; i < NV; ++i) v[i] = 0.0f;
+            yp[(size_t)r * a.Wo + j] = Elem<T>::from_f32(quant_apply<QM>(v, a.q, load_mm<QM>(a, oc)));
           }
-        } else {
-          load_window<T, PAD, NV>(tp + row * row_pitch, v);
         }
-        if (PACKED_CONV) {
-#pragma unroll
-          for (int i = 0; i < NWP; ++i) wp[slot][i] = pack2(v[i], v[i + 1]);
-        } else {
-#pragma unroll
-          for (int i = 0; i < NV; ++i) win[slot][i] = v[i];
-        }
-      };
-      // rows 0 .. K-STRIDE-1 are needed by the first output row and not loaded in the loop
-      static_loop<K - STRIDE>([&](auto i) { load_row(decltype(i)::value, i); });
-
-      for (int g = 0; g < c.R; g += K) {
-        static_loop<K>([&](auto u_c) {
-          constexpr int u = decltype(u_c)::value;
-          const int r = g + u;
-          if (r < c.R) {
-            // the STRIDE new rows of output row r: tile rows r*STRIDE + K-STRIDE + i
-            static_loop<STRIDE>([&](auto i_c) {
-              constexpr int i = decltype(i_c)::value;
-              load_row(r * STRIDE + (K - STRIDE) + i, IntC<(u * STRIDE + K - STRIDE + i) % K>{});
-            });
-            f32x2 acc[NPR];
-            if (PACKED_CONV) {
-#pragma unroll
-              for (int ky = 0; ky < K; ++ky) {
-#pragma unroll
-                for (int kx = 0; kx < K; ++kx) {
-#pragma unroll
-                  for (int p = 0; p < NPR; ++p)
-                    acc[p] = add2((ky == 0 && kx == 0) ? bias2 : acc[p],
-                                  mul2(w2[ky * K + kx], wp[(u * STRIDE + ky) % K][2 * p + kx], nz));
-                }
-              }
-            } else {
-              float b0, b1;
-              unpack2(bias2, b0, b1);
-              float sa[S];
-#pragma unroll
-              for (int j = 0; j < S; ++j) sa[j] = b0;
-#pragma unroll
-              for (int ky = 0; ky < K; ++ky) {
-#pragma unroll
-                for (int kx = 0; kx < K; ++kx) {
-#pragma unroll
-                  for (int j = 0; j < S; ++j)
-                    sa[j] = __fadd_rn(sa[j], __fmul_rn(wr[ky * K + kx], win[(u * STRIDE + ky) % K][j * STRIDE + kx]));
-                }
-              }
-#pragma unroll
-              for (int p = 0; p < NPR; ++p) acc[p] = pack2(sa[2 * p], sa[2 * p + 1]);
-            }
-            if (a.has_bn) bn_apply_packed<NPR>(acc, bnp);
-            float out[S];
-#pragma unroll
-            for (int p = 0; p < NPR; ++p) unpack2(acc[p], out[2 * p], out[2 * p + 1]);
-            const bool row_ok = oyb + r < a.Ho;
-            if (QM == QM_MM_REDUCE) {
-#pragma unroll
-              for (int j = 0; j < S; ++j) {
-                if (row_ok && ox0 + j < a.Wo) {
-                  lo = fminf(lo, out[j]);
-                  hi = fmaxf(hi, out[j]);
-                }
-              }
-            } else {
-              if (QM == QM_FPQ && a.q.fpq_fast) {
-                if (a.q.fpq_min < 0.0f) {
-#pragma unroll
-                  for (int j = 0; j < S; ++j) out[j] = fpq_apply_fast<true>(out[j], a.q);
-                } else {
-#pragma unroll
-                  for (int j = 0; j < S; ++j) out[j] = fpq_apply_fast<false>(out[j], a.q);
-                }
-              } else {
-#pragma unroll
-                for (int j = 0; j < S; ++j) out[j] = quant_apply<QM>(out[j], a.q, mm);
-              }
-              if (row_ok) {
-                if (full_vec) {
-                  Vec16<T>::store_stream(yp + (size_t)r * a.Wo, out);
-                } else {
-#pragma unroll
-                  for (int j = 0; j < S; ++j)
-                    if (ox0 + j < a.Wo) yp[(size_t)r * a.Wo + j] = Elem<T>::from_f32(out[j]);
-                }
-              }
-            }
-          }
-        });
       }
       if (QM == QM_MM_REDUCE) {
         atomicMin(red + 2 * pl, enc_ordered(lo));
         atomicMax(red + 2 * pl + 1, enc_ordered(hi));
       }
+      continue;
     }
 
-    // release the stage: the producer may overwrite it once every consumer warp has arrived
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty[st]);
+    // packed operands straight from the record
+    const f32x2 *pq = reinterpret_cast<const f32x2 *>(pp);
+    f32x2 w2[PACKED_CONV ? PL::KK : 1];
+    float wr[PACKED_CONV ? 1 : PL::KK];
+#pragma unroll
+    for (int i = 0; i < PL::KK; ++i) {
+      if (PACKED_CONV) {
+        w2[i] = pq[i];
+        pin(w2[i]);
+      } else {
+        wr[i] = pp[2 * i];
+        pin(wr[i]);
+      }
+    }
+    f32x2 bias2 = pq[PL::PAIRS / 2];
+    pin(bias2);
+    BnPacked bnp;
+    bnp.nmean = pq[PL::PAIRS / 2 + 1];
+    bnp.scale = pq[PL::PAIRS / 2 + 2];
+    bnp.rcp = pq[PL::PAIRS / 2 + 3];
+    bnp.nstd = pq[PL::PAIRS / 2 + 4];
+    bnp.beta = pq[PL::PAIRS / 2 + 5];
+    bnp.nz = nz;
+    bnp.stdvar = pp[PL::SCAL];
+    bnp.glo = pp[PL::SCAL + 1];
+    const MmCoef mm{pp[PL::SCAL + 2], pp[PL::SCAL + 3], pp[PL::SCAL + 4]};
+    const bool full_vec = c.vec_store && (ox0 + S <= a.Wo);
+
+    // Window source. Padded modes: 16-byte aligned position of the first output's centre tap
+    // column in tile row 0 of this row block. Raw mode: element (row 0, column of window
+    // position 0) of the plane, any alignment, plus the per-position halo masks.
+    const T *tp;
+    unsigned int cmask[MODE == TM_RAW ? NV : 1];
+    int iy_first = 0;
+    int row_pitch;
+    if (MODE == TM_RAW) {
+      const int c0 = ox0 * STRIDE - PAD;
+      iy_first = rb * R * STRIDE - PAD;
+      row_pitch = a.W;
+      tp = tiles + c.raw_lead + pl * c.tile_elems + iy_first * a.W + c0;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) cmask[i] = (c0 + i >= 0 && c0 + i < a.W) ? 0xffffffffu : 0u;
+    } else {
+      row_pitch = c.WS;
+      tp = tiles + pl * c.tile_elems + (rb * R * STRIDE) * c.WS + S + sx * (S * STRIDE);
+    }
+
+    float lo = __uint_as_float(0x7f800000u), hi = __uint_as_float(0xff800000u);
+    // window storage: packed pairs or scalars, whichever the conv uses
+    f32x2 wp[PACKED_CONV ? K : 1][PACKED_CONV ? NWP : 1];
+    float win[PACKED_CONV ? 1 : K][PACKED_CONV ? 1 : NV];
+    // loads tile row `row` of this item into window slot row % K (row is a compile-time
+    // constant at every call site once the loops below are unrolled)
+    auto load_row = [&](int row) {
+      float v[NV];
+      if (MODE == TM_RAW) {
+        const int iy = iy_first + row;
+        if (iy >= 0 && iy < a.H) {
+          load_window_raw<T, NV>(tp + row * row_pitch, cmask, v);
+        } else {
+#pragma unroll
+          for (int i = 0; i < NV; ++i) v[i] = 0.0f;
+        }
+      } else {
+        load_window<T, PAD, NV>(tp + row * row_pitch, v);
+      }
+      if (PACKED_CONV) {
+#pragma unroll
+        for (int i = 0; i < NWP; ++i) wp[row % K][i] = pack2(v[i], v[i + 1]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) win[row % K][i] = v[i];
+      }
+    };
+#pragma unroll
+    for (int i = 0; i < K - STRIDE; ++i) load_row(i);
+
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+#pragma unroll
+      for (int i = 0; i < STRIDE; ++i) load_row(r * STRIDE + (K - STRIDE) + i);
+      f32x2 acc[NPR];
+      if (PACKED_CONV) {
+#pragma unroll
+        for (int ky = 0; ky < K; ++ky) {
+#pragma unroll
+          for (int kx = 0; kx < K; ++kx) {
+#pragma unroll
+            for (int p = 0; p < NPR; ++p)
+              acc[p] = add2((ky == 0 && kx == 0) ? bias2 : acc[p],
+                            mul2(w2[ky * K + kx], wp[(r * STRIDE + ky) % K][2 * p + kx], nz));
+          }
+        }
+      } else {
+        float b0, b1;
+        unpack2(bias2, b0, b1);
+        float sa[S];
+#pragma unroll
+        for (int j = 0; j < S; ++j) sa[j] = b0;
+#pragma unroll
+        for (int ky = 0; ky < K; ++ky) {
+#pragma unroll
+          for (int kx = 0; kx < K; ++kx) {
+#pragma unroll
+            for (int j = 0; j < S; ++j)
+              sa[j] = __fadd_rn(sa[j], __fmul_rn(wr[ky * K + kx], win[(r * STRIDE + ky) % K][j * STRIDE + kx]));
+          }
+        }
+#pragma unroll
+        for (int p = 0; p < NPR; ++p) acc[p] = pack2(sa[2 * p], sa[2 * p + 1]);
+      }
+      if (a.has_bn) bn_apply_packed<NPR>(acc, bnp);
+      float out[S];
+#pragma unroll
+      for (int p = 0; p < NPR; ++p) unpack2(acc[p], out[2 * p], out[2 * p + 1]);
+      const bool row_ok = oyb + r < a.Ho;
+      if (QM == QM_MM_REDUCE) {
+#pragma unroll
+        for (int j = 0; j < S; ++j) {
+          if (row_ok && ox0 + j < a.Wo) {
+            lo = fminf(lo, out[j]);
+            hi = fmaxf(hi, out[j]);
+          }
+        }
+      } else {
+        if (QM == QM_FPQ && a.q.fpq_fast) {
+          if (a.q.fpq_min < 0.0f) {
+#pragma unroll
+            for (int j = 0; j < S; ++j) out[j] = fpq_apply_fast<true>(out[j], a.q);
+          } else {
+#pragma unroll
+            for (int j = 0; j < S; ++j) out[j] = fpq_apply_fast<false>(out[j], a.q);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < S; ++j) out[j] = quant_apply<QM>(out[j], a.q, mm);
+        }
+        if (row_ok) {
+          T *yr = yp + (size_t)r * a.Wo;
+          if (full_vec) {
+            Vec16<T>::store_stream(yr, out);
+          } else {
+#pragma unroll
+            for (int j = 0; j < S; ++j)
+              if (ox0 + j < a.Wo) yr[j] = Elem<T>::from_f32(out[j]);
+          }
+        }
+      }
+    }
+    if (QM == QM_MM_REDUCE) {
+      atomicMin(red + 2 * pl, enc_ordered(lo));
+      atomicMax(red + 2 * pl + 1, enc_ordered(hi));
+    }
+  }
+
+  if (QM == QM_MM_REDUCE) {
+    __syncthreads();
+    for (int i = tid; i < pv; i += nthr) {
+      const int ch = (plane0 + i) % a.OC;
+      atomicMin(a.q.mm_enc_min + ch, red[2 * i]);
+      atomicMax(a.q.mm_enc_max + ch, red[2 * i + 1]);
+    }
   }
 }
 
+constexpr int kRowsPerPatch = 7;
 
 // ---- host-side entry of each instantiation family (defined in fused_tiled_*.cu) --------
-// Launches fused_tiled_kernel<T, K, STRIDE, QM, MODE> on `ctas` persistent CTAs.
+// Launches fused_tiled_kernel<T, K, STRIDE, kRowsPerPatch, QM, MODE>, one CTA per tile.
 template <typename T, int K>
 cudaError_t launch_tiled(int stride, int qm, int mode, const CUtensorMap &tmap, const FusedArgs &a,
                          const TileCfg &c, int ctas, int threads, size_t smem, cudaStream_t stream);

@@ -12,11 +12,11 @@ typedef void (*TiledKernel)(const CUtensorMap, const FusedArgs, const TileCfg);
 template <typename T, int K, int STRIDE, int MODE>
 TiledKernel pick_qm(int qm) {
   switch (qm) {
-    case QM_NONE: return fused_tiled_kernel<T, K, STRIDE, QM_NONE, MODE>;
-    case QM_FPQ: return fused_tiled_kernel<T, K, STRIDE, QM_FPQ, MODE>;
-    case QM_POW2: return fused_tiled_kernel<T, K, STRIDE, QM_POW2, MODE>;
-    case QM_MM_APPLY: return fused_tiled_kernel<T, K, STRIDE, QM_MM_APPLY, MODE>;
-    case QM_MM_REDUCE: return fused_tiled_kernel<T, K, STRIDE, QM_MM_REDUCE, MODE>;
+    case QM_NONE: return fused_tiled_kernel<T, K, STRIDE, kRowsPerPatch, QM_NONE, MODE>;
+    case QM_FPQ: return fused_tiled_kernel<T, K, STRIDE, kRowsPerPatch, QM_FPQ, MODE>;
+    case QM_POW2: return fused_tiled_kernel<T, K, STRIDE, kRowsPerPatch, QM_POW2, MODE>;
+    case QM_MM_APPLY: return fused_tiled_kernel<T, K, STRIDE, kRowsPerPatch, QM_MM_APPLY, MODE>;
+    case QM_MM_REDUCE: return fused_tiled_kernel<T, K, STRIDE, kRowsPerPatch, QM_MM_REDUCE, MODE>;
   }
   return nullptr;
 }

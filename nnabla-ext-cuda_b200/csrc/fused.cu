@@ -140,7 +140,7 @@ int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan
   plan->path = PATH_GENERIC;
   const int forced = forced_path();
   const int B = d.dtype == DWBNQ_F32 ? 4 : 2;
-  const int S = 16 / B;
+  const int S = 16 / B;  // elements per 16-byte vector = outputs per thread and patch row
   const int K = d.kh;
   const int s = d.stride_h;
   const bool tileable = d.kh == d.kw && (K == 3 || K == 5) && d.stride_h == d.stride_w &&
@@ -148,11 +148,16 @@ int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan
                         d.dil_h == 1 && d.dil_w == 1 && d.multiplier == 1 && d.n > 0;
   if (!tileable || forced == PATH_GENERIC) return DWBNQ_OK;
 
+  const int R = kRowsPerPatch;
   const int pad = K / 2;
   const long long n_planes = d.n * d.c;
   if (n_planes > 0x7fffffffLL) return DWBNQ_OK;
   const int n_strips = ceil_div(Wo, S);
-  const long long stage_budget = 44 * 1024;  // two stages per CTA, two or more CTAs per SM
+  const int n_rb_total = ceil_div(Ho, R);
+  // One tile per CTA and several CTAs per SM: the budget keeps four tiles (plus records)
+  // inside the 227 KB of shared memory of an SM.
+  const long long stage_budget = 48 * 1024;
+  const int max_threads = 256;
   const bool x_al = (reinterpret_cast<uintptr_t>(x) % 16) == 0;
   const bool y_al = (reinterpret_cast<uintptr_t>(y) % 16) == 0;
   const long long plane_bytes = (long long)d.h * d.w * B;
@@ -170,112 +175,88 @@ int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan
 
   TileCfg &c = plan->cfg;
   c.n_strips = n_strips;
+  c.R = R;
   c.vec_store = (y_al && Wo % S == 0) ? 1 : 0;
-  // Patch height R: the tallest of the candidates that still gives a tile enough patches to
-  // keep a CTA busy (taller patches amortise the per-patch set-up and halo rows).
-  const int r_cands[] = {14, 7, 4, 2, 1};
-  const int tune_r = g_tune_r.load();
-  const int enough_items = 128;
-  int best_items = -1;
-  TileCfg best = c;
-  for (int ri = 0; ri < 5; ++ri) {
-    const int R = tune_r > 0 ? tune_r : r_cands[ri];
-    TileCfg t = c;
-    t.R = R;
-    const int n_rb_total = ceil_div(Ho, R);
-    int P = 1;
-    if (path == PATH_RAW) {
-      // Whole planes, verbatim. P is a multiple of `pal` so every full tile starts on a
-      // 16-byte boundary and spans a multiple of 16 bytes (what the bulk copy engine needs).
-      const int ipp = n_strips * n_rb_total;
-      const long long pal = 16 / gcd_ll(plane_bytes, 16);
-      const long long fit = (stage_budget - (raw_lead + raw_trail) * (long long)B) / plane_bytes;
-      long long want = std::max(1, ceil_div(256, ipp));
-      if (g_tune_p.load() > 0) want = g_tune_p.load();
-      want = std::min(want, fit);
-      long long Pl = want / pal * pal;
-      if (Pl < pal) Pl = pal <= fit ? pal : want;  // cannot align: the copies fall back to threads
-      if (Pl > n_planes) Pl = n_planes;
-      if (Pl < 1) Pl = 1;
-      P = (int)Pl;
-      t.n_row_tiles = 1;
-      t.n_rb = n_rb_total;
-      t.TH = n_rb_total * R;
-      t.WS = d.w;
-      t.TR = d.h;
-      t.box_rows = d.h;
-      t.n_boxes = 1;
-      t.tile_elems = d.h * d.w;
-      t.raw_lead = raw_lead;
-      t.stage_elems = round_up((raw_lead + P * t.tile_elems + raw_trail) * B, 128) / B;
-      t.vec_fill = (x_al && (P * plane_bytes) % 16 == 0) ? 1 : 0;
-    } else {
-      const int WS = round_up(S + (n_strips * S - 1) * s + K - pad, S);
-      if (WS > 256) return DWBNQ_OK;  // wider than one TMA box: generic kernel
-      // Row blocks per tile: aim at ~256 patches per tile, split the plane evenly, and keep
-      // one plane's tile inside the stage budget.
-      int rb_per_tile = std::max(1, std::min(n_rb_total, 256 / n_strips));
-      if (g_tune_rb.load() > 0) rb_per_tile = std::min(g_tune_rb.load(), n_rb_total);
-      int n_row_tiles, TH, TR, n_boxes, box_rows, tile_elems;
-      for (;;) {
-        n_row_tiles = ceil_div(n_rb_total, rb_per_tile);
-        rb_per_tile = ceil_div(n_rb_total, n_row_tiles);
-        TH = rb_per_tile * R;
-        TR = (TH - 1) * s + K;
-        // A TMA box has at most 256 rows and its shared-memory destination must be 128-byte
-        // aligned: with several boxes per plane the rows per box are a multiple of 8.
-        n_boxes = ceil_div(TR, 256);
-        box_rows = n_boxes == 1 ? TR : round_up(ceil_div(TR, n_boxes), 8);
-        tile_elems = round_up(box_rows * n_boxes * WS * B, 128) / B;
-        if ((long long)tile_elems * B <= stage_budget || rb_per_tile == 1) break;
-        rb_per_tile = std::max(1, rb_per_tile - 1);
-      }
-      const long long tile_bytes = (long long)tile_elems * B;
-      if (tile_bytes > 96 * 1024) {
-        if (tune_r > 0) return DWBNQ_OK;
-        continue;  // a shorter patch gives a shorter tile
-      }
-      const int ipp = n_strips * rb_per_tile;
-      P = std::max(1, ceil_div(256, ipp));
-      while (P > 1 && (long long)P * tile_bytes > stage_budget) --P;
-      if (g_tune_p.load() > 0) P = g_tune_p.load();
-      if (P > n_planes) P = (int)n_planes;
-      t.n_row_tiles = n_row_tiles;
-      t.n_rb = rb_per_tile;
-      t.TH = TH;
-      t.WS = WS;
-      t.TR = TR;
-      t.box_rows = box_rows;
-      t.n_boxes = n_boxes;
-      t.tile_elems = tile_elems;
-      t.raw_lead = 0;
-      t.stage_elems = P * tile_elems;
-      t.vec_fill = (x_al && d.w % S == 0) ? 1 : 0;
+  int P = 1;
+  if (path == PATH_RAW) {
+    // Whole planes, verbatim. P is a multiple of `pal` so every full tile starts on a
+    // 16-byte boundary and spans a multiple of 16 bytes (what the bulk copy engine needs).
+    const int ipp = n_strips * n_rb_total;
+    const long long pal = 16 / gcd_ll(plane_bytes, 16);
+    const long long fit = (stage_budget - (raw_lead + raw_trail) * (long long)B) / plane_bytes;
+    long long want = std::max(1, max_threads / ipp);
+    if (g_tune_p.load() > 0) want = g_tune_p.load();
+    want = std::min(want, fit);
+    long long Pl = want / pal * pal;
+    if (Pl < pal) Pl = pal <= fit ? pal : want;  // cannot align: the copies fall back to threads
+    if (Pl > n_planes) Pl = n_planes;
+    if (Pl < 1) Pl = 1;
+    P = (int)Pl;
+    c.n_row_tiles = 1;
+    c.n_rb = n_rb_total;
+    c.TH = n_rb_total * R;
+    c.WS = d.w;
+    c.TR = d.h;
+    c.box_rows = d.h;
+    c.n_boxes = 1;
+    c.tile_elems = d.h * d.w;
+    c.raw_lead = raw_lead;
+    c.stage_elems = round_up((raw_lead + P * c.tile_elems + raw_trail) * B, 128) / B;
+    c.vec_fill = (x_al && (P * plane_bytes) % 16 == 0) ? 1 : 0;
+  } else {
+    const int WS = round_up(S + (n_strips * S - 1) * s + K - pad, S);
+    if (WS > 256) return DWBNQ_OK;  // wider than one TMA box: generic kernel
+    // Row blocks per tile: aim at one patch per thread, split the plane evenly, and keep one
+    // plane's tile inside the budget.
+    int rb_per_tile = std::max(1, std::min(n_rb_total, max_threads / n_strips));
+    if (g_tune_rb.load() > 0) rb_per_tile = std::min(g_tune_rb.load(), n_rb_total);
+    int n_row_tiles, TH, TR, n_boxes, box_rows, tile_elems;
+    for (;;) {
+      n_row_tiles = ceil_div(n_rb_total, rb_per_tile);
+      rb_per_tile = ceil_div(n_rb_total, n_row_tiles);
+      TH = rb_per_tile * R;
+      TR = (TH - 1) * s + K;
+      // A TMA box has at most 256 rows and its shared-memory destination must be 128-byte
+      // aligned: with several boxes per plane the rows per box are a multiple of 8.
+      n_boxes = ceil_div(TR, 256);
+      box_rows = n_boxes == 1 ? TR : round_up(ceil_div(TR, n_boxes), 8);
+      tile_elems = round_up(box_rows * n_boxes * WS * B, 128) / B;
+      if ((long long)tile_elems * B <= stage_budget || rb_per_tile == 1) break;
+      rb_per_tile = std::max(1, rb_per_tile - 1);
     }
-    t.P = P;
-    const long long n_tiles = ((n_planes + P - 1) / P) * t.n_row_tiles;
-    if (n_tiles > 0x7fffffffLL) continue;
-    t.n_tiles = (int)n_tiles;
-    const int items = P * n_strips * t.n_rb;
-    if (items > best_items) {
-      best_items = items;
-      best = t;
-    }
-    if (tune_r > 0 || items >= enough_items) break;
+    const long long tile_bytes = (long long)tile_elems * B;
+    if (tile_bytes > 96 * 1024) return DWBNQ_OK;
+    const int ipp = n_strips * rb_per_tile;
+    P = std::max(1, max_threads / ipp);
+    while (P > 1 && (long long)P * tile_bytes > stage_budget) --P;
+    if (g_tune_p.load() > 0) P = g_tune_p.load();
+    if (P > n_planes) P = (int)n_planes;
+    c.n_row_tiles = n_row_tiles;
+    c.n_rb = rb_per_tile;
+    c.TH = TH;
+    c.WS = WS;
+    c.TR = TR;
+    c.box_rows = box_rows;
+    c.n_boxes = n_boxes;
+    c.tile_elems = tile_elems;
+    c.raw_lead = 0;
+    c.stage_elems = P * tile_elems;
+    c.vec_fill = (x_al && d.w % S == 0) ? 1 : 0;
   }
-  if (best_items < 0) return DWBNQ_OK;
-  c = best;
-  const size_t smem = tiled_smem_bytes(c.P, c.stage_elems, B, K);
+  c.P = P;
+  const long long n_tiles = ((n_planes + P - 1) / P) * c.n_row_tiles;
+  if (n_tiles > 0x7fffffffLL) return DWBNQ_OK;
+  c.n_tiles = (int)n_tiles;
+  const size_t smem = tiled_smem_bytes(P, c.stage_elems, B, K);
   if (smem > 200 * 1024) return DWBNQ_OK;
-  const int items = c.P * n_strips * c.n_rb;
-  const int iters = ceil_div(items, 256);
-  int threads = std::min(256, round_up(ceil_div(items, iters), 32));  // consumer threads
-  if (g_tune_threads.load() > 0) threads = std::min(256, round_up(g_tune_threads.load(), 32));
-  threads += 32;  // plus the producer warp
+  const int items = P * n_strips * c.n_rb;
+  const int iters = ceil_div(items, max_threads);
+  int threads = std::min(max_threads, round_up(ceil_div(items, iters), 32));
+  if (g_tune_threads.load() > 0) threads = std::min(max_threads, round_up(g_tune_threads.load(), 32));
   plan->threads = threads;
   plan->smem = smem;
   plan->path = path;
-  plan->ctas = c.n_tiles;  // upper bound; the launch clamps to what is resident
+  plan->ctas = c.n_tiles;
   return DWBNQ_OK;
 }
 
@@ -310,17 +291,8 @@ int launch_fused(const dwbnq_conv_desc &d, FusedArgs &a, int qm, int device, cud
         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(DWBNQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   }
-  // Persistent grid: as many CTAs as are resident at once, never more than there are tiles.
-  int per_sm = 0;
   const bool f32 = d.dtype == DWBNQ_F32;
-  if (f32) e = d.kh == 3 ? tiled_occupancy<float, 3>(d.stride_h, qm, mode, plan.threads, plan.smem, &per_sm)
-                         : tiled_occupancy<float, 5>(d.stride_h, qm, mode, plan.threads, plan.smem, &per_sm);
-  else e = d.kh == 3 ? tiled_occupancy<__half, 3>(d.stride_h, qm, mode, plan.threads, plan.smem, &per_sm)
-                     : tiled_occupancy<__half, 5>(d.stride_h, qm, mode, plan.threads, plan.smem, &per_sm);
-  if (e != cudaSuccess) return fail_cuda(e, "occupancy query of fused_tiled_kernel");
-  if (per_sm < 1) return fail(DWBNQ_ERR_CUDA, "fused_tiled_kernel does not fit on an SM (%zu bytes of shared memory)", plan.smem);
-  const long long resident = (long long)per_sm * sm_count(device);
-  const int ctas = (int)std::min(resident, (long long)plan.cfg.n_tiles);
+  const int ctas = plan.cfg.n_tiles;  // one CTA per tile
   if (f32) e = d.kh == 3 ? launch_tiled<float, 3>(d.stride_h, qm, mode, tmap, a, plan.cfg, ctas, plan.threads, plan.smem, stream)
                          : launch_tiled<float, 5>(d.stride_h, qm, mode, tmap, a, plan.cfg, ctas, plan.threads, plan.smem, stream);
   else e = d.kh == 3 ? launch_tiled<__half, 3>(d.stride_h, qm, mode, tmap, a, plan.cfg, ctas, plan.threads, plan.smem, stream)
