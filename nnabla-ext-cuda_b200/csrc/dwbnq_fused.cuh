@@ -321,7 +321,7 @@ __device__ __forceinline__ void load_window_raw(const T *p, const unsigned int *
 // Resident CTAs per SM the kernel is compiled for: the 3x3 float kernels fit 64 registers
 // (4 x 256 threads), the wider windows of the other instantiations get twice as many.
 __host__ __device__ constexpr int tiled_min_blocks(int elem_size, int K, int mode) {
-  return (elem_size == 4 && K == 3 && mode != TM_RAW) ? 4 : 2;
+  return (elem_size == 4 && K == 3 && mode != TM_RAW) ? 3 : 2;
 }
 
 // One CTA = one tile: P planes x R*n_rb output rows. The tile copy (TMA / bulk) is issued
@@ -344,8 +344,8 @@ __global__ void __launch_bounds__(256, tiled_min_blocks(sizeof(T), K, MODE))
   unsigned long long *bar = reinterpret_cast<unsigned long long *>(
       (reinterpret_cast<uintptr_t>(red + 2 * c.P) + 15) / 16 * 16);
 
-  const int tid = threadIdx.x;
-  const int nthr = blockDim.x;
+  const int tid = (threadIdx.z * blockDim.y + threadIdx.y) * blockDim.x + threadIdx.x;
+  const int nthr = blockDim.x * blockDim.y * blockDim.z;
   const int n_planes = (int)(a.n * a.OC);  // multiplier == 1; the planner keeps it below 2^31
   const T *x = static_cast<const T *>(a.x);
   T *y = static_cast<T *>(a.y);
@@ -479,13 +479,13 @@ __global__ void __launch_bounds__(256, tiled_min_blocks(sizeof(T), K, MODE))
   constexpr int NPR = S / 2;   // output pairs per patch row
   constexpr int NWP = NV - 1;  // consecutive pairs of a window row
   const f32x2 nz = negzero2();
-  const int ipp = c.n_strips * c.n_rb;  // items per plane
-  const int n_items = pv * ipp;
-  for (int it = tid; it < n_items; it += nthr) {
-    const int pl = it / ipp;
-    const int rem = it - pl * ipp;
-    const int rb = rem / c.n_strips;
-    const int sx = rem - rb * c.n_strips;
+  // One patch per thread: the block is (strips, planes, row blocks), so the patch
+  // coordinates are the thread indices (no division).
+  for (int once = 0; once < 1; ++once) {
+    const int sx = threadIdx.x;
+    const int pl = threadIdx.y;
+    const int rb = threadIdx.z;
+    if (pl >= pv) break;
     const int ox0 = sx * S;
     const int oyb = oy0 + rb * R;
     const int plane = plane0 + pl;
@@ -592,78 +592,95 @@ __global__ void __launch_bounds__(256, tiled_min_blocks(sizeof(T), K, MODE))
 #pragma unroll
     for (int i = 0; i < K - STRIDE; ++i) load_row(i);
 
+    // The rows of the patch. LEAN is the common case decided once per patch - BN present,
+    // power-of-two unsigned FixedPointQuantize, every row inside the image and the stores
+    // whole vectors - so its loop carries no per-row tests; the general loop handles the
+    // rest.
+    auto run_rows = [&](auto lean_c) {
+      constexpr bool LEAN = decltype(lean_c)::value;
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
+      for (int r = 0; r < R; ++r) {
 #pragma unroll
-      for (int i = 0; i < STRIDE; ++i) load_row(r * STRIDE + (K - STRIDE) + i);
-      f32x2 acc[NPR];
-      if (PACKED_CONV) {
+        for (int i = 0; i < STRIDE; ++i) load_row(r * STRIDE + (K - STRIDE) + i);
+        f32x2 acc[NPR];
+        if (PACKED_CONV) {
 #pragma unroll
-        for (int ky = 0; ky < K; ++ky) {
+          for (int ky = 0; ky < K; ++ky) {
 #pragma unroll
-          for (int kx = 0; kx < K; ++kx) {
+            for (int kx = 0; kx < K; ++kx) {
 #pragma unroll
-            for (int p = 0; p < NPR; ++p)
-              acc[p] = add2((ky == 0 && kx == 0) ? bias2 : acc[p],
-                            mul2(w2[ky * K + kx], wp[(r * STRIDE + ky) % K][2 * p + kx], nz));
-          }
-        }
-      } else {
-        float b0, b1;
-        unpack2(bias2, b0, b1);
-        float sa[S];
-#pragma unroll
-        for (int j = 0; j < S; ++j) sa[j] = b0;
-#pragma unroll
-        for (int ky = 0; ky < K; ++ky) {
-#pragma unroll
-          for (int kx = 0; kx < K; ++kx) {
-#pragma unroll
-            for (int j = 0; j < S; ++j)
-              sa[j] = __fadd_rn(sa[j], __fmul_rn(wr[ky * K + kx], win[(r * STRIDE + ky) % K][j * STRIDE + kx]));
-          }
-        }
-#pragma unroll
-        for (int p = 0; p < NPR; ++p) acc[p] = pack2(sa[2 * p], sa[2 * p + 1]);
-      }
-      if (a.has_bn) bn_apply_packed<NPR>(acc, bnp);
-      float out[S];
-#pragma unroll
-      for (int p = 0; p < NPR; ++p) unpack2(acc[p], out[2 * p], out[2 * p + 1]);
-      const bool row_ok = oyb + r < a.Ho;
-      if (QM == QM_MM_REDUCE) {
-#pragma unroll
-        for (int j = 0; j < S; ++j) {
-          if (row_ok && ox0 + j < a.Wo) {
-            lo = fminf(lo, out[j]);
-            hi = fmaxf(hi, out[j]);
-          }
-        }
-      } else {
-        if (QM == QM_FPQ && a.q.fpq_fast) {
-          if (a.q.fpq_min < 0.0f) {
-#pragma unroll
-            for (int j = 0; j < S; ++j) out[j] = fpq_apply_fast<true>(out[j], a.q);
-          } else {
-#pragma unroll
-            for (int j = 0; j < S; ++j) out[j] = fpq_apply_fast<false>(out[j], a.q);
+              for (int p = 0; p < NPR; ++p)
+                acc[p] = add2((ky == 0 && kx == 0) ? bias2 : acc[p],
+                              mul2(w2[ky * K + kx], wp[(r * STRIDE + ky) % K][2 * p + kx], nz));
+            }
           }
         } else {
+          float b0, b1;
+          unpack2(bias2, b0, b1);
+          float sa[S];
 #pragma unroll
-          for (int j = 0; j < S; ++j) out[j] = quant_apply<QM>(out[j], a.q, mm);
+          for (int j = 0; j < S; ++j) sa[j] = b0;
+#pragma unroll
+          for (int ky = 0; ky < K; ++ky) {
+#pragma unroll
+            for (int kx = 0; kx < K; ++kx) {
+#pragma unroll
+              for (int j = 0; j < S; ++j)
+                sa[j] = __fadd_rn(sa[j], __fmul_rn(wr[ky * K + kx], win[(r * STRIDE + ky) % K][j * STRIDE + kx]));
+            }
+          }
+#pragma unroll
+          for (int p = 0; p < NPR; ++p) acc[p] = pack2(sa[2 * p], sa[2 * p + 1]);
         }
-        if (row_ok) {
-          T *yr = yp + (size_t)r * a.Wo;
-          if (full_vec) {
-            Vec16<T>::store_stream(yr, out);
+        if (LEAN || a.has_bn) bn_apply_packed<NPR>(acc, bnp);
+        float out[S];
+#pragma unroll
+        for (int p = 0; p < NPR; ++p) unpack2(acc[p], out[2 * p], out[2 * p + 1]);
+        if (LEAN) {
+#pragma unroll
+          for (int j = 0; j < S; ++j) out[j] = fpq_apply_fast<false>(out[j], a.q);
+          Vec16<T>::store_stream(yp + (size_t)r * a.Wo, out);
+          continue;
+        }
+        const bool row_ok = oyb + r < a.Ho;
+        if (QM == QM_MM_REDUCE) {
+#pragma unroll
+          for (int j = 0; j < S; ++j) {
+            if (row_ok && ox0 + j < a.Wo) {
+              lo = fminf(lo, out[j]);
+              hi = fmaxf(hi, out[j]);
+            }
+          }
+        } else {
+          if (QM == QM_FPQ && a.q.fpq_fast) {
+            if (a.q.fpq_min < 0.0f) {
+#pragma unroll
+              for (int j = 0; j < S; ++j) out[j] = fpq_apply_fast<true>(out[j], a.q);
+            } else {
+#pragma unroll
+              for (int j = 0; j < S; ++j) out[j] = fpq_apply_fast<false>(out[j], a.q);
+            }
           } else {
 #pragma unroll
-            for (int j = 0; j < S; ++j)
-              if (ox0 + j < a.Wo) yr[j] = Elem<T>::from_f32(out[j]);
+            for (int j = 0; j < S; ++j) out[j] = quant_apply<QM>(out[j], a.q, mm);
+          }
+          if (row_ok) {
+            T *yr = yp + (size_t)r * a.Wo;
+            if (full_vec) {
+              Vec16<T>::store_stream(yr, out);
+            } else {
+#pragma unroll
+              for (int j = 0; j < S; ++j)
+                if (ox0 + j < a.Wo) yr[j] = Elem<T>::from_f32(out[j]);
+            }
           }
         }
       }
-    }
+    };
+    const bool lean = QM == QM_FPQ && a.has_bn && a.q.fpq_fast && !(a.q.fpq_min < 0.0f) && full_vec &&
+                      oyb + R <= a.Ho;
+    if (QM == QM_FPQ && lean) run_rows(IntC<1>{});
+    else run_rows(IntC<0>{});
     if (QM == QM_MM_REDUCE) {
       atomicMin(red + 2 * pl, enc_ordered(lo));
       atomicMax(red + 2 * pl + 1, enc_ordered(hi));

@@ -44,11 +44,13 @@ template <>
 cudaError_t launch_tiled<DWBNQ_INST_T, DWBNQ_INST_K>(int stride, int qm, int mode, const CUtensorMap &tmap,
                                                      const FusedArgs &a, const TileCfg &c, int ctas,
                                                      int threads, size_t smem, cudaStream_t stream) {
+  (void)threads;
   TiledKernel kern = pick<DWBNQ_INST_T, DWBNQ_INST_K>(stride, qm, mode);
   if (!kern) return cudaErrorInvalidValue;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
-  kern<<<(unsigned int)ctas, threads, smem, stream>>>(tmap, a, c);
+  // block = (strips, planes, row blocks): one patch per thread
+  kern<<<(unsigned int)ctas, dim3(c.n_strips, c.P, c.n_rb), smem, stream>>>(tmap, a, c);
   return cudaGetLastError();
 }
 

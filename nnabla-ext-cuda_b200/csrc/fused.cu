@@ -243,16 +243,24 @@ int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan
     c.stage_elems = P * tile_elems;
     c.vec_fill = (x_al && d.w % S == 0) ? 1 : 0;
   }
+  // one patch per thread: block = (strips, planes, row blocks)
+  if (n_strips * c.n_rb > max_threads || c.n_rb > 64) return DWBNQ_OK;
+  while (P > 1 && P * n_strips * c.n_rb > max_threads) {
+    --P;
+    if (path == PATH_RAW) {
+      c.stage_elems = round_up((raw_lead + P * c.tile_elems + raw_trail) * B, 128) / B;
+      c.vec_fill = (x_al && (P * plane_bytes) % 16 == 0) ? 1 : 0;
+    } else {
+      c.stage_elems = P * c.tile_elems;
+    }
+  }
   c.P = P;
   const long long n_tiles = ((n_planes + P - 1) / P) * c.n_row_tiles;
   if (n_tiles > 0x7fffffffLL) return DWBNQ_OK;
   c.n_tiles = (int)n_tiles;
   const size_t smem = tiled_smem_bytes(P, c.stage_elems, B, K);
   if (smem > 200 * 1024) return DWBNQ_OK;
-  const int items = P * n_strips * c.n_rb;
-  const int iters = ceil_div(items, max_threads);
-  int threads = std::min(max_threads, round_up(ceil_div(items, iters), 32));
-  if (g_tune_threads.load() > 0) threads = std::min(max_threads, round_up(g_tune_threads.load(), 32));
+  const int threads = P * n_strips * c.n_rb;  // one patch per thread
   plan->threads = threads;
   plan->smem = smem;
   plan->path = path;
