@@ -15,7 +15,8 @@ enum QMode : int {
   QM_FPQ = 1,       // FixedPointQuantize
   QM_POW2 = 2,      // Pow2Quantize
   QM_MM_APPLY = 3,  // MinMaxQuantize, second pass: quantize with per-channel ranges
-  QM_MM_REDUCE = 4  // MinMaxQuantize, first pass: per-channel min/max only, no store
+  QM_MM_REDUCE = 4, // MinMaxQuantize, first pass: per-channel min/max only, no store
+  QM_FPQ_LEAN = 5   // FixedPointQuantize, the common case compiled without per-row tests (tiled family)
 };
 
 // Kernel-argument block of the quantizers (passed by value; uniform -> constant bank).
@@ -379,7 +380,7 @@ __device__ __forceinline__ float fpq_apply_fast(float x, const QuantArgs &q) {
 // One epilogue for all modes (QM_MM_REDUCE does not come here).
 template <int QM>
 __device__ __forceinline__ float quant_apply(float v, const QuantArgs &q, const MmCoef &mm) {
-  if (QM == QM_FPQ) return fpq_apply(v, q);
+  if (QM == QM_FPQ || QM == QM_FPQ_LEAN) return fpq_apply(v, q);
   if (QM == QM_POW2) return pow2_apply(v, q);
   if (QM == QM_MM_APPLY) return mm_apply(v, mm);
   return v;

@@ -592,12 +592,11 @@ __global__ void __launch_bounds__(256, tiled_min_blocks(sizeof(T), K, MODE))
 #pragma unroll
     for (int i = 0; i < K - STRIDE; ++i) load_row(i);
 
-    // The rows of the patch. LEAN is the common case decided once per patch - BN present,
-    // power-of-two unsigned FixedPointQuantize, every row inside the image and the stores
-    // whole vectors - so its loop carries no per-row tests; the general loop handles the
-    // rest.
-    auto run_rows = [&](auto lean_c) {
-      constexpr bool LEAN = decltype(lean_c)::value;
+    // The rows of the patch. QM_FPQ_LEAN is the common case, selected by the host for the
+    // whole launch - BN present, power-of-two unsigned FixedPointQuantize, Ho a multiple of R
+    // and Wo of the vector width with y aligned - and compiled without any per-row test.
+    {
+      constexpr bool LEAN = QM == QM_FPQ_LEAN;
 #pragma unroll
       for (int r = 0; r < R; ++r) {
 #pragma unroll
@@ -676,11 +675,7 @@ __global__ void __launch_bounds__(256, tiled_min_blocks(sizeof(T), K, MODE))
           }
         }
       }
-    };
-    const bool lean = QM == QM_FPQ && a.has_bn && a.q.fpq_fast && !(a.q.fpq_min < 0.0f) && full_vec &&
-                      oyb + R <= a.Ho;
-    if (QM == QM_FPQ && lean) run_rows(IntC<1>{});
-    else run_rows(IntC<0>{});
+    }
     if (QM == QM_MM_REDUCE) {
       atomicMin(red + 2 * pl, enc_ordered(lo));
       atomicMax(red + 2 * pl + 1, enc_ordered(hi));

@@ -17,6 +17,7 @@ TiledKernel pick_qm(int qm) {
     case QM_POW2: return fused_tiled_kernel<T, K, STRIDE, kRowsPerPatch, QM_POW2, MODE>;
     case QM_MM_APPLY: return fused_tiled_kernel<T, K, STRIDE, kRowsPerPatch, QM_MM_APPLY, MODE>;
     case QM_MM_REDUCE: return fused_tiled_kernel<T, K, STRIDE, kRowsPerPatch, QM_MM_REDUCE, MODE>;
+    case QM_FPQ_LEAN: return fused_tiled_kernel<T, K, STRIDE, kRowsPerPatch, QM_FPQ_LEAN, MODE>;
   }
   return nullptr;
 }

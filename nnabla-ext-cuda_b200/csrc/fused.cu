@@ -184,7 +184,9 @@ int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan
     const int ipp = n_strips * n_rb_total;
     const long long pal = 16 / gcd_ll(plane_bytes, 16);
     const long long fit = (stage_budget - (raw_lead + raw_trail) * (long long)B) / plane_bytes;
-    long long want = std::max(1, max_threads / ipp);
+    // small planes: many small CTAs hide the per-CTA copy / record latency better than few
+    // large ones (measured on B200): about 64 threads each
+    long long want = std::max(1, (ipp <= 64 ? 64 : max_threads) / ipp);
     if (g_tune_p.load() > 0) want = g_tune_p.load();
     want = std::min(want, fit);
     long long Pl = want / pal * pal;
@@ -227,7 +229,8 @@ int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan
     const long long tile_bytes = (long long)tile_elems * B;
     if (tile_bytes > 96 * 1024) return DWBNQ_OK;
     const int ipp = n_strips * rb_per_tile;
-    P = std::max(1, max_threads / ipp);
+    // whole small planes: about 64 threads per CTA (see above); otherwise fill the CTA
+    P = std::max(1, ((n_row_tiles == 1 && ipp <= 64) ? 64 : max_threads) / ipp);
     while (P > 1 && (long long)P * tile_bytes > stage_budget) --P;
     if (g_tune_p.load() > 0) P = g_tune_p.load();
     if (P > n_planes) P = (int)n_planes;
@@ -284,6 +287,10 @@ int launch_fused(const dwbnq_conv_desc &d, FusedArgs &a, int qm, int device, cud
     return DWBNQ_OK;
   }
   const int mode = plan.path == PATH_TMA ? TM_TMA : plan.path == PATH_RAW ? TM_RAW : TM_COOP;
+  // The common FixedPointQuantize case gets the kernel compiled without per-row tests.
+  if (qm == QM_FPQ && a.has_bn && a.q.fpq_fast && !(a.q.fpq_min < 0.0f) && plan.cfg.vec_store &&
+      a.Ho % kRowsPerPatch == 0)
+    qm = QM_FPQ_LEAN;
   CUtensorMap tmap;
   std::memset(&tmap, 0, sizeof(tmap));
   if (mode == TM_TMA) {
