@@ -288,8 +288,9 @@ int launch_fused(const dwbnq_conv_desc &d, FusedArgs &a, int qm, int device, cud
   }
   const int mode = plan.path == PATH_TMA ? TM_TMA : plan.path == PATH_RAW ? TM_RAW : TM_COOP;
   // The common FixedPointQuantize case gets the kernel compiled without per-row tests.
+  // (every patch row of every tile must lie inside the image: the tiles cover Ho exactly)
   if (qm == QM_FPQ && a.has_bn && a.q.fpq_fast && !(a.q.fpq_min < 0.0f) && plan.cfg.vec_store &&
-      a.Ho % kRowsPerPatch == 0)
+      plan.cfg.n_row_tiles * plan.cfg.n_rb * kRowsPerPatch == a.Ho)
     qm = QM_FPQ_LEAN;
   CUtensorMap tmap;
   std::memset(&tmap, 0, sizeof(tmap));
