@@ -174,6 +174,27 @@ int dwbnq_minmaxq_fwd(int dtype, int64_t size0, int32_t channels, int64_t size2,
                       const dwbnq_quant_desc *q, const void *x, const dwbnq_minmax_ptrs *mm,
                       void *y, void *workspace, void *comm, int device, void *stream);
 
+/* MinMaxQuantize forward without a workspace argument. It has no counterpart in the
+ * reference. It exists for callers that cannot supply scratch memory at the point of the
+ * call - a function object of a framework whose own allocator already holds the whole
+ * device, a serving loop that is not allowed to reach the allocator while it runs, a
+ * plugin hook that receives nothing but tensor pointers. The scratch lives in a fixed
+ * device array inside the library instead (7 words per channel, DWBNQ_STATIC_MAX_CHANNELS
+ * channels, 112 KiB on every GPU that loads the library, held until the process exits).
+ *  - channels > DWBNQ_STATIC_MAX_CHANNELS fails with DWBNQ_ERR_UNSUPPORTED;
+ *  - no cudaMalloc / cudaFree or other allocating call is made, here or in the kernels;
+ *  - the first call on each device looks up the array's device address; make that first
+ *    call before starting any stream capture on the device;
+ *  - all calls on a device share the one array: calls that may overlap on the GPU (different
+ *    streams, different host threads) race on it - serialise them or use
+ *    dwbnq_minmaxq_fwd with separate workspaces; there is no `comm` either: a batch
+ *    sharded over several GPUs needs dwbnq_minmaxq_fwd.
+ * Results are identical to dwbnq_minmaxq_fwd with comm == NULL. */
+#define DWBNQ_STATIC_MAX_CHANNELS 4096
+int dwbnq_minmaxq_fwd_static(int dtype, int64_t size0, int32_t channels, int64_t size2,
+                             const dwbnq_quant_desc *q, const void *x, const dwbnq_minmax_ptrs *mm,
+                             void *y, int device, void *stream);
+
 /* ---- the fused layer: what the graph pass rewrites dw-conv -> BN -> quantizer into -- */
 
 /* y = Quantize(BN_inference(DepthwiseConvolution(x))). No counterpart kernel exists in

@@ -14,6 +14,7 @@ F32, F16 = 0, 1
 Q_NONE, Q_FPQ, Q_POW2, Q_MINMAX = 0, 1, 2, 3
 PATH_AUTO, PATH_GENERIC, PATH_COOP, PATH_TMA, PATH_RAW = -1, 0, 1, 2, 3
 UNIQUE_ID_BYTES = 128
+STATIC_MAX_CHANNELS = 4096
 
 
 class ConvDesc(ctypes.Structure):
@@ -62,6 +63,8 @@ SIGNATURES = {
     "dwbnq_pow2q_fwd": (_int, [_int, _i64, _int, _int, _int, _int, _vp, _vp, _int, _vp]),
     "dwbnq_minmaxq_fwd": (_int, [_int, _i64, ctypes.c_int32, _i64, _P(QuantDesc), _vp, _P(MinMaxPtrs),
                                  _vp, _vp, _vp, _int, _vp]),
+    "dwbnq_minmaxq_fwd_static": (_int, [_int, _i64, ctypes.c_int32, _i64, _P(QuantDesc), _vp, _P(MinMaxPtrs),
+                                        _vp, _int, _vp]),
     "dwbnq_fused_fwd": (_int, [_P(ConvDesc), _flt, _P(QuantDesc), _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                _P(MinMaxPtrs), _vp, _vp, _vp, _int, _vp]),
     "dwbnq_fused_plan": (_int, [_P(ConvDesc), _vp, _vp, _P(_int), _P(_int), _P(_int), _P(_int),
