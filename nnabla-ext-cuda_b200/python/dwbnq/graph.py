@@ -1,0 +1,173 @@
+"""Graph pass: DepthwiseConvolution -> BatchNormalization(batch_stat=False) -> quantizer
+becomes one fused node, and a small executor that runs such graphs through libdwbnq.
+
+nnabla's graph converters (``nnabla.experimental.graph_converters``, e.g.
+BatchNormalizationFolding) walk a function list and rewrite conv -> BN chains whose
+intermediate variable has a single consumer. This pass matches the same shape of pattern
+one function further (the quantizer) but, unlike BN folding, keeps the BN parameters as
+they are: folding them into the weights changes the rounding of every output, while the
+fused kernel reproduces the three-function chain bit for bit.
+
+The IR is a plain list of nodes in topological order:
+    {"op": "DepthwiseConvolution", "inputs": ["x", "w", "b"], "outputs": ["c"],
+     "args": {"base_axis": 1, "pad": (1, 1), "stride": (1, 1), "dilation": (1, 1), "multiplier": 1}}
+with the function names and argument names of nnabla's functions.yaml. ``from_nnabla``
+builds it from a real nnabla graph when nnabla is importable.
+"""
+from collections import Counter
+
+QUANTIZERS = ("FixedPointQuantize", "Pow2Quantize", "MinMaxQuantize")
+FUSED = "FusedDwBnQuant"
+
+
+def _consumers(nodes):
+    c = Counter()
+    for n in nodes:
+        for v in n["inputs"]:
+            c[v] += 1
+    return c
+
+
+def _bn_is_fusable(bn, channel_axis):
+    a = bn["args"]
+    axes = list(a.get("axes", [1]))
+    return (not a.get("batch_stat", True)) and axes == [channel_axis] and len(bn["outputs"]) == 1
+
+
+def fuse_dw_bn_quant(nodes, graph_outputs=()):
+    """Returns a new node list where every dw-conv -> BN(inference) -> quantizer chain whose
+    intermediates have no other consumer (and are not graph outputs) is one FusedDwBnQuant
+    node. A dw-conv -> BN chain without a quantizer is fused too (quantizer "none")."""
+    nodes = list(nodes)
+    uses = _consumers(nodes)
+    keep = set(graph_outputs)
+    producer = {}
+    for i, n in enumerate(nodes):
+        for v in n["outputs"]:
+            producer[v] = i
+    consumer_of = {}
+    for i, n in enumerate(nodes):
+        for v in n["inputs"]:
+            consumer_of.setdefault(v, []).append(i)
+
+    def sole_consumer(var):
+        if var in keep or uses[var] != 1:
+            return None
+        return consumer_of[var][0]
+
+    removed = set()
+    out = []
+    for i, conv in enumerate(nodes):
+        if i in removed:
+            continue
+        if conv["op"] != "DepthwiseConvolution":
+            out.append(conv)
+            continue
+        j = sole_consumer(conv["outputs"][0])
+        base_axis = conv["args"].get("base_axis", 1)
+        if j is None or nodes[j]["op"] != "BatchNormalization" or nodes[j]["inputs"][0] != conv["outputs"][0] \
+                or not _bn_is_fusable(nodes[j], base_axis):
+            out.append(conv)
+            continue
+        bn = nodes[j]
+        fused = {"op": FUSED, "conv_args": dict(conv["args"]), "bn_args": dict(bn["args"]), "quant": None,
+                 "inputs": list(conv["inputs"]) + list(bn["inputs"][1:]), "n_conv_inputs": len(conv["inputs"]),
+                 "outputs": list(bn["outputs"])}
+        removed.add(j)
+        k = sole_consumer(bn["outputs"][0])
+        if k is not None and nodes[k]["op"] in QUANTIZERS and nodes[k]["inputs"][0] == bn["outputs"][0]:
+            qn = nodes[k]
+            if qn["op"] != "MinMaxQuantize" or _minmax_is_per_channel(qn):
+                fused["quant"] = {"op": qn["op"], "args": dict(qn["args"])}
+                fused["inputs"] += list(qn["inputs"][1:])
+                fused["outputs"] = list(qn["outputs"])
+                removed.add(k)
+        out.append(fused)
+    # keep topological order: a fused node sits where its convolution was; everything it
+    # needs (parameters) is a graph input or was produced earlier
+    return out
+
+
+def _minmax_is_per_channel(qn):
+    return qn["args"].get("per_channel_axis", 1) == 1
+
+
+def execute(nodes, tensors, comm=None):
+    """Runs the node list on torch CUDA tensors (dict name -> tensor, updated in place with
+    every produced variable). Only the operators of this library are known."""
+    from . import ops
+
+    t = tensors
+    for n in nodes:
+        a = n.get("args", {})
+        i = [t[v] if v is not None else None for v in n["inputs"]]
+        if n["op"] == "DepthwiseConvolution":
+            b = i[2] if len(i) > 2 else None
+            y = ops.depthwise_convolution(i[0], i[1], b, a.get("base_axis", 1), a.get("pad"), a.get("stride"),
+                                          a.get("dilation"), a.get("multiplier", 1))
+        elif n["op"] == "BatchNormalization":
+            beta, gamma, mean, var = _bn_inputs(i[1:], a)
+            y = ops.batch_normalization(i[0], beta, gamma, mean, var, a.get("axes", [1]), a.get("decay_rate", 0.9),
+                                        a.get("eps", 1e-5), a.get("batch_stat", True))
+        elif n["op"] == "FixedPointQuantize":
+            y = ops.fixed_point_quantize(i[0], a.get("sign", True), a.get("n", 8), a.get("delta", 2.0 ** -4))
+        elif n["op"] == "Pow2Quantize":
+            y = ops.pow2_quantize(i[0], a.get("sign", True), a.get("with_zero", True), a.get("n", 8), a.get("m", 1))
+        elif n["op"] == "MinMaxQuantize":
+            y = ops.min_max_quantize(i[0], i[1], i[2], i[3], i[4], a.get("decay", 0.999), a.get("x_min_max", False),
+                                     a.get("ema", False), True, a.get("eps", 0.01), comm=comm)
+        elif n["op"] == FUSED:
+            nc = n["n_conv_inputs"]
+            ca, ba = n["conv_args"], n["bn_args"]
+            b = i[2] if nc > 2 else None
+            n_bn = 4 - int(ba.get("no_bias", False)) - int(ba.get("no_scale", False))
+            beta, gamma, mean, var = _bn_inputs(i[nc:nc + n_bn], ba)
+            quant = None
+            if n["quant"]:
+                qa = n["quant"]["args"]
+                qi = i[nc + n_bn:]
+                if n["quant"]["op"] == "FixedPointQuantize":
+                    quant = {"kind": "fpq", "sign": qa.get("sign", True), "n": qa.get("n", 8),
+                             "delta": qa.get("delta", 2.0 ** -4)}
+                elif n["quant"]["op"] == "Pow2Quantize":
+                    quant = {"kind": "pow2", "sign": qa.get("sign", True), "with_zero": qa.get("with_zero", True),
+                             "n": qa.get("n", 8), "m": qa.get("m", 1)}
+                else:
+                    quant = {"kind": "minmax", "decay": qa.get("decay", 0.999), "x_min_max": qa.get("x_min_max", False),
+                             "ema": qa.get("ema", False), "eps": qa.get("eps", 0.01), "qr_min": qi[0], "qr_max": qi[1],
+                             "ql_min": qi[2], "ql_max": qi[3]}
+            y = ops.fused_dw_bn_quant(i[0], i[1], b, beta, gamma, mean, var, ba.get("eps", 1e-5), ca.get("pad"),
+                                      ca.get("stride"), ca.get("dilation"), ca.get("multiplier", 1), quant,
+                                      ca.get("base_axis", 1), comm=comm)
+        else:
+            raise NotImplementedError("operator %r is outside the dwbnq path" % (n["op"],))
+        t[n["outputs"][0]] = y
+    return t
+
+
+def _bn_inputs(rest, args):
+    """BatchNormalization inputs after x: [beta, gamma, mean, var] with beta / gamma absent
+    when no_bias / no_scale (src/nbla/cuda/function/generic/batch_normalization.cu:120-123)."""
+    rest = list(rest)
+    beta = None if args.get("no_bias", False) else rest.pop(0)
+    gamma = None if args.get("no_scale", False) else rest.pop(0)
+    return beta, gamma, rest[0], rest[1]
+
+
+def from_nnabla(output_variable):
+    """Builds the node list from an nnabla graph (needs nnabla; import guarded)."""
+    try:
+        import nnabla  # noqa: F401
+    except ImportError as e:  # pragma: no cover - nnabla is not installed in this environment
+        raise ImportError("from_nnabla needs the nnabla package") from e
+    nodes, names = [], {}
+
+    def name(v):
+        return names.setdefault(v, "v%d" % len(names))
+
+    def visit(f):
+        nodes.append({"op": f.info.type_name, "args": dict(f.info.args), "inputs": [name(v) for v in f.inputs],
+                      "outputs": [name(v) for v in f.outputs]})
+
+    output_variable.visit(visit)
+    return nodes, names
