@@ -195,7 +195,7 @@ size_t dwbnq_workspace_bytes(int32_t channels) {
 
 int dwbnq_set_forced_path(int path) {
   clear_error();
-  if (path < PATH_AUTO || path > PATH_RAW) return fail(DWBNQ_ERR_INVALID_ARG, "path %d is not -1..3", path);
+  if (path < PATH_AUTO || path > PATH_PLANE) return fail(DWBNQ_ERR_INVALID_ARG, "path %d is not -1..4", path);
   set_forced_path(path);
   return DWBNQ_OK;
 }

@@ -6,6 +6,7 @@
 
 #include "../../include/dwbnq.h"
 #include "dwbnq_fused.cuh"
+#include "dwbnq_plane.cuh"
 
 namespace dwbnq {
 
@@ -18,7 +19,7 @@ void clear_error();
 int enter_device(int device, int *out);
 
 // ---- fused / dw-conv family (fused.cu) --------------------------------------------------
-enum FusedPath : int { PATH_AUTO = -1, PATH_GENERIC = 0, PATH_COOP = 1, PATH_TMA = 2, PATH_RAW = 3 };
+enum FusedPath : int { PATH_AUTO = -1, PATH_GENERIC = 0, PATH_COOP = 1, PATH_TMA = 2, PATH_RAW = 3, PATH_PLANE = 4 };
 
 struct Plan {
   int path;

@@ -70,6 +70,7 @@ int forced_path() {
     if (!std::strcmp(e, "coop")) return PATH_COOP;
     if (!std::strcmp(e, "tma")) return PATH_TMA;
     if (!std::strcmp(e, "raw")) return PATH_RAW;
+    if (!std::strcmp(e, "plane")) return PATH_PLANE;
   }
   return g_forced_path.load();
 }
@@ -152,6 +153,31 @@ int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan
   const int pad = K / 2;
   const long long n_planes = d.n * d.c;
   if (n_planes > 0x7fffffffLL) return DWBNQ_OK;
+
+  // ---- small planes (7x7, 14x14), 3x3 stride 1: one warp per CTA, full-width rows ----------
+  if (K == 3 && s == 1 && plane_shape_supported(d.h, d.w) && (forced == PATH_AUTO || forced == PATH_PLANE)) {
+    const int nrb = d.h / kPlaneRows;
+    TileCfg &c = plan->cfg;
+    c.P = 32 / nrb;
+    c.R = kPlaneRows;
+    c.n_rb = nrb;
+    c.n_strips = 1;
+    c.n_row_tiles = 1;
+    c.TH = d.h;
+    c.TR = d.h;
+    c.WS = d.w;
+    c.tile_elems = d.h * d.w;
+    const bool al = (reinterpret_cast<uintptr_t>(x) % 16) == 0 && (reinterpret_cast<uintptr_t>(y) % 16) == 0;
+    c.vec_fill = al ? 1 : 0;
+    c.vec_store = al ? 1 : 0;
+    c.n_tiles = (int)((n_planes + c.P - 1) / c.P);
+    plan->path = PATH_PLANE;
+    plan->threads = 32;
+    plan->smem = plane_smem_bytes(d.w, nrb, d.dtype == DWBNQ_F32 ? 4 : 2);
+    plan->ctas = c.n_tiles;
+    return DWBNQ_OK;
+  }
+  if (forced == PATH_PLANE) return DWBNQ_OK;  // no instantiation for this shape: generic kernel
   const int n_strips = ceil_div(Wo, S);
   const int n_rb_total = ceil_div(Ho, R);
   // One tile per CTA and several CTAs per SM: the budget keeps four tiles (plus records)
@@ -284,6 +310,17 @@ int launch_fused(const dwbnq_conv_desc &d, FusedArgs &a, int qm, int device, cud
     e = d.dtype == DWBNQ_F32 ? launch_generic_t<float>(qm, a, total, stream)
                              : launch_generic_t<__half>(qm, a, total, stream);
     if (e != cudaSuccess) return fail_cuda(e, "fused_generic_kernel launch");
+    return DWBNQ_OK;
+  }
+  if (plan.path == PATH_PLANE) {
+    // BN + unsigned power-of-two FixedPointQuantize: the instantiation without mode tests
+    if (qm == QM_FPQ && a.has_bn && a.q.fpq_fast && !(a.q.fpq_min < 0.0f)) qm = QM_FPQ_LEAN;
+    PlaneCfg pc;
+    pc.P = plan.cfg.P;
+    pc.n_tiles = plan.cfg.n_tiles;
+    pc.bulk = plan.cfg.vec_fill;
+    e = launch_plane(d.dtype, d.w, qm, a, pc, stream);
+    if (e != cudaSuccess) return fail_cuda(e, "fused_plane_kernel launch");
     return DWBNQ_OK;
   }
   const int mode = plan.path == PATH_TMA ? TM_TMA : plan.path == PATH_RAW ? TM_RAW : TM_COOP;

@@ -319,6 +319,94 @@ def test_unaligned_pointers_and_optional_inputs(oracle, cuda_device):
     assert e.shape == (0, c, h, w)
 
 
+# ---- the small-plane kernel (7x7 and 14x14 planes, 3x3 stride 1) -------------------------
+
+SMALL_QUANTS = [None,
+                {"kind": "fpq", "sign": False, "n": 8, "delta": 2.0 ** -3},   # lean instantiation
+                {"kind": "fpq", "sign": True, "n": 8, "delta": 2.0 ** -4},    # signed, fast form
+                {"kind": "fpq", "sign": True, "n": 6, "delta": 0.3},          # delta not a power of two
+                {"kind": "pow2", "sign": True, "with_zero": True, "n": 6, "m": 1},
+                {"kind": "minmax", "x_min_max": True, "ema": False, "decay": 0.999, "eps": 0.01}]
+SMALL_QUANT_IDS = ["none", "fpq_lean", "fpq_signed", "fpq_0.3", "pow2", "minmax"]
+
+
+@pytest.mark.parametrize("quant", SMALL_QUANTS, ids=SMALL_QUANT_IDS)
+@pytest.mark.parametrize("hw", [7, 14])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16], ids=["f32", "f16"])
+def test_small_plane_kernel(oracle, cuda_device, dtype, hw, quant):
+    """Full tiles, a ragged last tile (37 planes: the 7x7 fp32 remainder is not a multiple of
+    16 bytes, so its tile is copied by the threads) and a batch smaller than one tile."""
+    rng = np.random.default_rng(100 + hw)
+    for n, c in ((5, 64), (1, 37), (1, 3)):
+        spec = workloads.LayerSpec("small", n, c, hw, hw, 3, 1, 1, None)
+        d = _rand_layer(rng, n, c, hw, hw, 3)
+        if quant and quant["kind"] == "minmax":
+            d.update(qr_min=np.zeros(c, np.float32), qr_max=np.ones(c, np.float32), ql_min=np.zeros(c, np.float32),
+                     ql_max=np.full(c, 255, np.float32))
+        h16, up = f16_inputs(d) if dtype == torch.float16 else (d, d)
+        plan = ops.fused_plan(dev(h16["x"], cuda_device), dev(h16["w"], cuda_device), pad=(1, 1), stride=(1, 1))
+        assert plan["path"] == L.PATH_PLANE, plan
+        want, _, extra = oracle_fused(oracle, up, spec, quant)
+        got, t = run_fused(h16, spec, cuda_device, quant, dtype=dtype)
+        if dtype == torch.float16:
+            want = oracle.to_f16_result(want)
+        assert_same_bits(got, want, "%dx%d n=%d c=%d" % (hw, hw, n, c))
+        if extra is not None and dtype == torch.float32:
+            assert_same_bits(t["qr_min"].cpu().numpy(), extra[0], "qr_min")
+            assert_same_bits(t["qr_max"].cpu().numpy(), extra[1], "qr_max")
+
+
+@pytest.mark.parametrize("hw", [7, 14])
+def test_small_plane_kernel_unaligned_and_optional(oracle, cuda_device, hw):
+    rng = np.random.default_rng(200 + hw)
+    n, c = 3, 40
+    spec = workloads.LayerSpec("small_unaligned", n, c, hw, hw, 3, 1, 1, None)
+    d = _rand_layer(rng, n, c, hw, hw, 3)
+    q = {"kind": "fpq", "sign": False, "n": 8, "delta": 2.0 ** -3}
+    want, _, _ = oracle_fused(oracle, d, spec, q)
+    xbuf = torch.empty(d["x"].size + 1, device=cuda_device)
+    xbuf[1:] = dev(d["x"].ravel(), cuda_device)
+    x = xbuf[1:].view(n, c, hw, hw)
+    ybuf = torch.empty(want.size + 1, device=cuda_device)
+    y = ybuf[1:].view(want.shape)
+    t = {k: dev(v, cuda_device) for k, v in d.items()}
+    ops.fused_dw_bn_quant(x, t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], 1e-5, (1, 1), (1, 1),
+                          quant=q, out=y)
+    assert_same_bits(y.cpu().numpy(), want, "unaligned x / y")
+    want = oracle.fpq(oracle.dwconv(d["x"], d["w"], None, (1, 1), (1, 1)), False, 8, 2.0 ** -3)
+    got = ops.fused_dw_bn_quant(t["x"], t["w"], None, None, None, None, None, 1e-5, (1, 1), (1, 1), quant=q)
+    assert_same_bits(got.cpu().numpy(), want, "no bias, no BN")
+    # the other families on the same planes give the same bits
+    for path in (L.PATH_RAW, L.PATH_COOP, L.PATH_GENERIC):
+        got_p, _ = run_fused(d, spec, cuda_device, q, path=path)
+        want_p, _, _ = oracle_fused(oracle, d, spec, q)
+        assert_same_bits(got_p, want_p, "path %d" % path)
+
+
+@pytest.mark.parametrize("hw", [7, 14])
+def test_small_plane_kernel_exact_evaluation_planes(oracle, cuda_device, hw):
+    rng = np.random.default_rng(300 + hw)
+    n, c = 2, 20
+    spec = workloads.LayerSpec("small_patho", n, c, hw, hw, 3, 1, 1, None)
+    d = _rand_layer(rng, n, c, hw, hw, 3)
+    d["x"][:, 0] = -0.0
+    d["w"][0] = np.abs(d["w"][0]) + np.float32(0.1)
+    d["b"][0] = -0.0
+    d["w"][1, 0, 0] = np.inf
+    d["w"][2, 2, 2] = np.nan
+    d["w"][3, 1, 1] = -np.inf
+    d["b"][7] = -0.0
+    want = oracle.dwconv(d["x"], d["w"], d["b"], (1, 1), (1, 1))
+    got = ops.depthwise_convolution(dev(d["x"], cuda_device), dev(d["w"], cuda_device), dev(d["b"], cuda_device), 1,
+                                    (1, 1), (1, 1)).cpu().numpy()
+    assert_same_bits(got, want, "pathological parameters")
+    assert (bits(got[:, 0]) == 0x80000000).all()
+    for q in SMALL_QUANTS[1:5]:
+        want_q, _, _ = oracle_fused(oracle, d, spec, q)
+        got_q, _ = run_fused(d, spec, cuda_device, q)
+        assert_same_bits(got_q, want_q, "pathological parameters, %s" % q["kind"])
+
+
 # ---- the five standalone operators -----------------------------------------------------
 
 def test_standalone_batch_normalization(oracle, cuda_device):
