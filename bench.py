@@ -48,6 +48,18 @@ def measured_peak():
         return FALLBACK_HBM_GBS, "fallback"
 
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum, ncu) of the 17 launches of one cfg1
+# fp32 step captured at batch 64 (profiles/cfg1_step_dram_traffic_batch64.md). Traffic is
+# proportional to the batch, so a step at batch B is this figure times B / 64.
+CFG1_F32_TRAFFIC_BATCH64 = None
+
+
+def measured_traffic(args, batch):
+    if CFG1_F32_TRAFFIC_BATCH64 is None or args.workload != "cfg1" or args.dtype != "f32" or args.only_layers:
+        return None
+    return CFG1_F32_TRAFFIC_BATCH64 * batch / 64.0
+
+
 class ClockSampler:
     """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
 
@@ -63,7 +75,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -72,9 +84,9 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
-    def stop(self):
+    def stop(self, t_begin=None, t_end=None):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -84,7 +96,10 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons, power = [], [], set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        inside = [ln for (t, ln) in self.lines if t_begin is None or (t_begin <= t <= t_end + 0.05)]
+        if len(inside) < 2:  # a very short region: fall back to everything sampled around it
+            inside = [ln for (_, ln) in self.lines]
+        for ln in inside:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -101,25 +116,37 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_stack_images_per_s(specs, sample_n, nthreads, repeats=1):
-    """Times the unfused CPU chain (dw-conv, BN, quantizer: three passes, like the
-    reference's CPU functions) of the whole layer stack on `sample_n` images."""
+def make_cpu_pass(specs, sample_n, nthreads):
+    """Returns a function that runs the unfused CPU chain (dw-conv, BN, quantizer: three
+    passes, like the reference's CPU functions) of the whole layer stack once on
+    `sample_n` seeded images and returns the seconds it took."""
     from dwbnq import workloads
     from oracle import oracle
     datas = []
     for s in specs:
         small = workloads.LayerSpec(s.name, sample_n, s.c, s.h, s.w, s.k, s.stride, s.pad, s.quant, s.seed, s.x_dist)
         datas.append((small, workloads.make_layer_data(small)))
-    best = None
-    for _ in range(repeats):
+
+    def one_pass():
         t0 = time.perf_counter()
         for small, d in datas:
             q = workloads.quant_for_ops(small, d)
             oracle.fused_layer(d["x"], d["w"], d["b"], d["beta"], d["gamma"], d["mean"], d["var"], small.bn_eps,
                                (small.stride,) * 2, (small.pad,) * 2, q, nthreads=nthreads)
-        dt = time.perf_counter() - t0
-        best = dt if best is None else min(best, dt)
-    return sample_n / best, best
+        return time.perf_counter() - t0
+
+    return one_pass
+
+
+def cpu_stack_images_per_s(specs, sample_n, nthreads, min_seconds):
+    """Repeats the CPU pass until `min_seconds` are spent; (images/s, seconds per pass, passes)."""
+    one_pass = make_cpu_pass(specs, sample_n, nthreads)
+    one_pass()  # untimed: page in the buffers, start the thread pool
+    total, passes = 0.0, 0
+    while passes == 0 or (total < min_seconds and passes < 1000):
+        total += one_pass()
+        passes += 1
+    return sample_n * passes / total, total / passes, passes
 
 
 def run_reference(args):
@@ -133,9 +160,10 @@ def run_reference(args):
     specs = workloads.workload(args.workload, args.batch)
     nthreads = oracle.max_threads()
     sample_n = args.cpu_sample
+    one_pass = make_cpu_pass(specs, sample_n, nthreads)
     times = []
     for i in range(args.warmup + args.steps):
-        _, dt = cpu_stack_images_per_s(specs, sample_n, nthreads)
+        dt = one_pass()
         if i >= args.warmup:
             times.append(dt)
     total = sum(times)
@@ -239,13 +267,15 @@ def run_own(args):
         time.sleep(0.3)
     barrier()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_begin = time.time()
     ev0.record()
     for _ in range(args.steps):
         step()
     ev1.record()
     barrier()
+    t_end = time.time()
     elapsed_ms = ev0.elapsed_time(ev1)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
     ops.check_device_flag()
 
     # ---- per-layer durations (separate pass, same launches; for the roofline breakdown) ----
@@ -267,25 +297,51 @@ def run_own(args):
                           "gbs": s.algorithmic_bytes(itemsize, batch) / ms / 1e6})
 
     # ---- end to end: host buffers in, host buffers out ------------------------------------
+    # Every layer's input comes from pinned host memory and every layer's result goes back to
+    # pinned host memory inside the timed region. Uploads, kernels and downloads run on three
+    # streams chained by events (PCIe is full duplex), the way a caller with host tensors
+    # would drive the library.
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
-    copy_stream = torch.cuda.current_stream(device)
+    compute = torch.cuda.current_stream(device)
+    up, down = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    ev_in = [torch.cuda.Event() for _ in layers]
+    ev_done = [torch.cuda.Event() for _ in layers]
+    ev_out = [torch.cuda.Event() for _ in layers]
+    first = [True]
 
     def e2e_step():
-        for layer in layers:
+        for i, layer in enumerate(layers):
             s, host, t, y, y_host, q, ws = layer
-            t["x"].copy_(host["x"], non_blocking=True)
+            with torch.cuda.stream(up):
+                if not first[0]:
+                    up.wait_event(ev_done[i])  # last step's kernel has consumed the old input
+                t["x"].copy_(host["x"], non_blocking=True)
+                ev_in[i].record(up)
+            compute.wait_event(ev_in[i])
+            if not first[0]:
+                compute.wait_event(ev_out[i])  # last step's result has left the output buffer
             launch(layer)
-            y_host.copy_(y, non_blocking=True)
-        copy_stream.synchronize()
+            ev_done[i].record(compute)
+            with torch.cuda.stream(down):
+                down.wait_event(ev_done[i])
+                y_host.copy_(y, non_blocking=True)
+                ev_out[i].record(down)
+        first[0] = False
+
+    def e2e_join():
+        compute.wait_stream(up)
+        compute.wait_stream(down)
 
     if not args.no_e2e:
         e2e_step()
+        e2e_join()
     barrier()
     t0 = time.perf_counter()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(0 if args.no_e2e else e2e_steps):
         e2e_step()
+    e2e_join()
     e1.record()
     barrier()
     e2e_ms = max(e0.elapsed_time(e1), 0.0)
@@ -309,7 +365,8 @@ def run_own(args):
         from oracle import oracle
         oracle.build()
         nthreads = oracle.max_threads()
-        cpu_ips, cpu_dt = (0.0, 0.0) if args.no_cpu else cpu_stack_images_per_s(specs, args.cpu_sample, nthreads)
+        cpu_ips, cpu_dt, cpu_passes = (0.0, 0.0, 0) if args.no_cpu else cpu_stack_images_per_s(
+            specs, args.cpu_sample, nthreads, args.cpu_seconds)
         bytes_per_image = sum(s.algorithmic_bytes(4, 1) for s in specs)
         line = {
             "metric": "images_per_s", "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
@@ -320,12 +377,14 @@ def run_own(args):
                        "l2": "per-step working set %.1f GB >> 126 MB L2; every layer has its own buffers"
                              % (bytes_per_step / 1e9)},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_kind": peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
-                         "kernel": "fused_tiled_kernel (all %d launches of a step)" % launches_per_step,
+                         "traffic": measured_traffic(args, batch), "peak_kind": peak_kind,
+                         "frac_of_nominal_8000": achieved / 8000.0,
+                         "kernel": "fused_tiled_kernel + fused_plane_kernel (all %d launches of a step)"
+                                   % launches_per_step,
                          "algorithmic_bytes_per_step": bytes_per_step},
             "cpu_baseline": {"value": cpu_ips, "unit": "images/s", "cores": nthreads, "kind": "port",
-                             "sample": "%d images of the layer stack, unfused 3-function chain, %.1f s"
-                                       % (args.cpu_sample, cpu_dt),
+                             "sample": "%d images of the layer stack, unfused 3-function chain, %d passes of %.2f s"
+                                       % (args.cpu_sample, cpu_passes, cpu_dt),
                              "effective_gbs": cpu_ips * bytes_per_image / 1e9},
             "e2e": {"value": None if args.no_e2e else batch * world * e2e_steps / (e2e_ms / 1e3), "unit": "images/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
@@ -356,13 +415,14 @@ def flush_l2(torch, device):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--workload", default="cfg1", choices=["cfg0", "cfg1", "cfg2", "cfg3", "cfg4"])
     ap.add_argument("--batch", type=int, default=None, help="images per GPU (default: the workload's batch)")
     ap.add_argument("--dtype", default="f32", choices=["f32", "f16"])
     ap.add_argument("--cpu-sample", type=int, default=None, help="images per CPU-baseline pass")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU time spent on the cpu_baseline sample")
     ap.add_argument("--e2e-steps", type=int, default=3)
     # reduced runs for profiling a single kernel (the printed line is then not a bench result)
     ap.add_argument("--only-layers", default="", help="comma-separated layer indices of the workload")

@@ -1,23 +1,28 @@
-// Fused dw-conv(3x3, stride 1, pad 1) -> BN -> quantizer for SMALL planes (7x7, 14x14),
-// where a row is narrower than a warp's worth of 16-byte vectors and its pitch is not a
-// multiple of 16 bytes, so neither the strip decomposition nor a padded TMA tile fits.
+// Fused dw-conv(3x3, pad 1) -> BN -> quantizer for SMALL planes (7x7, 14x14, 28x28), where
+// a row is narrower than a warp's worth of 16-byte vectors (and, for 7 / 14, its pitch is
+// not a multiple of 16 bytes), so the strip decomposition of the tiled family wastes most
+// of its instructions on halo tests and partial stores.
 //
 // One warp = one CTA = P consecutive (n, c) planes, which are contiguous in memory:
 //   * lane 0 brings the whole tile in with ONE bulk async copy and, at the end, sends the
 //     finished tile out with ONE bulk async store: global memory only ever sees full,
 //     contiguous lines;
-//   * a thread owns R = 7 full-width rows of one plane. Input rows stream through it one at
-//     a time: the row is loaded from shared memory once, as pairs of horizontally adjacent
-//     elements, and feeds the three output rows it touches (finishing row i-1, continuing
-//     row i, starting row i+1 - which keeps every output's summation in the ky-major /
-//     kx-minor order of the contract). Only two accumulator rows are live, the loop over
-//     rows is rolled (two steps per trip), the code is a few KB and there is no per-element
-//     halo test: the left / right zero columns are compile-time operands, the top / bottom
-//     zero rows a predicated load;
-//   * results overwrite the tile in place. The only rows read by one thread and written by
-//     another are the neighbours' edge rows: the row below a thread's block is copied to a
-//     private stash before anything is written, the row above is read in the first step,
-//     and every step ends with a warp barrier.
+//   * stride 1 (fused_plane_kernel): a thread owns a block of R = 7 rows x W (7 or 14)
+//     columns of one plane. Input rows stream through it one at a time: the row is loaded
+//     from shared memory once, as pairs of horizontally adjacent elements, and feeds the
+//     three output rows it touches (finishing row i-1, continuing row i, starting row i+1 -
+//     which keeps every output's summation in the ky-major / kx-minor order of the
+//     contract). Only two accumulator rows are live, the loop over rows is rolled (two
+//     steps per trip) and there is no per-element halo test: plane-edge columns are
+//     compile-time or per-thread predicated operands, the zero rows a predicated load.
+//     Results overwrite the tile in place. Rows / columns read by one thread and written by
+//     another are its neighbours' edges: the row below a block is copied to a private stash
+//     before anything is written, the row above is read in the first step, neighbouring
+//     columns are read one step before their owner overwrites them, and every step has a
+//     warp barrier between its reads and its writes;
+//   * stride 2 (fused_plane_s2_kernel): a thread owns a 14 x 14 input block = 7 x 7 outputs
+//     and streams two input rows per output row; the (4x smaller) result goes to its own
+//     compact tile.
 // Arithmetic contract: the one of dwbnq_fused.cuh (bias-initialised accumulator, separately
 // rounded product and sum, BN and quantizer of dwbnq_device.cuh). Halo taps enter as
 // w * (+0.0); planes where that differs from skipping the tap (bias == -0.0, non-finite
@@ -36,12 +41,21 @@ struct PlaneCfg {
 
 constexpr int kPlaneRows = 7;  // rows per thread
 
-__host__ __device__ constexpr int plane_stash_elems(int W) { return (W + 1) / 2 * 2; }
-// tile | stash (NRB > 1) | mbarrier
-__host__ __device__ constexpr size_t plane_smem_bytes(int W, int NRB, int elem_size) {
-  size_t s = (size_t)(32 / NRB) * (kPlaneRows * NRB) * W * elem_size;
+// Stash row of a thread: [2 unused | left halo | W elements | right halo | pad], even size.
+__host__ __device__ constexpr int plane_stash_elems(int W) { return (W + 4 + 1) / 2 * 2; }
+// stride 1: tile | stash (NRB > 1) | mbarrier
+__host__ __device__ constexpr size_t plane_smem_bytes(int W, int NRB, int NCB, int elem_size) {
+  size_t s = (size_t)(32 / (NRB * NCB)) * (kPlaneRows * NRB) * (W * NCB) * elem_size;
   s = (s + 15) / 16 * 16;
   if (NRB > 1) s += (size_t)32 * plane_stash_elems(W) * elem_size;
+  s = (s + 15) / 16 * 16;
+  return s + 16;
+}
+// stride 2: input tile | output tile | mbarrier
+__host__ __device__ constexpr size_t plane_s2_smem_bytes(int NB, int elem_size) {
+  size_t s = (size_t)(32 / (NB * NB)) * (14 * NB) * (14 * NB) * elem_size;
+  s = (s + 15) / 16 * 16;
+  s += (size_t)(32 / (NB * NB)) * (7 * NB) * (7 * NB) * elem_size;
   s = (s + 15) / 16 * 16;
   return s + 16;
 }
@@ -98,25 +112,25 @@ __device__ __forceinline__ void plane_store_row(T *p, const float *o) {
   }
 }
 
-// Tap-by-tap evaluation of R full-width rows of one plane from global memory (the rare
-// planes whose halo taps must be skipped rather than added as zeros). Kept out of line:
-// it is cold and several times the size of the fast path.
-template <typename T, int W, int QM>
-__device__ __noinline__ void plane_exact_rows(const FusedArgs &a, int plane, int ch, int row0,
-                                              T *rows, const MmCoef &mm, float *lo_out,
-                                              float *hi_out) {
+// Tap-by-tap evaluation of a rows x cols block of outputs of one plane from global memory
+// (the rare planes whose halo taps must be skipped rather than added as zeros). Kept out of
+// line: it is cold and several times the size of the fast path.
+template <typename T, int QM>
+__device__ __noinline__ void plane_exact_block(const FusedArgs &a, int plane, int ch, int oy0,
+                                               int ox0, int nrows, int ncols, T *dst, int pitch,
+                                               const MmCoef &mm, float *lo_out, float *hi_out) {
   float lo = __uint_as_float(0x7f800000u), hi = __uint_as_float(0xff800000u);
   const long long n = plane / a.OC;
 #pragma unroll 1
-  for (int r = 0; r < kPlaneRows; ++r) {
+  for (int r = 0; r < nrows; ++r) {
 #pragma unroll 1
-    for (int j = 0; j < W; ++j) {
-      const float v = prequant_point<T>(a, n, ch, row0 + r, j);
+    for (int j = 0; j < ncols; ++j) {
+      const float v = prequant_point<T>(a, n, ch, oy0 + r, ox0 + j);
       if (QM == QM_MM_REDUCE) {
         lo = fminf(lo, v);
         hi = fmaxf(hi, v);
       } else {
-        rows[r * W + j] = Elem<T>::from_f32(quant_apply<QM>(v, a.q, mm));
+        dst[r * pitch + j] = Elem<T>::from_f32(quant_apply<QM>(v, a.q, mm));
       }
     }
   }
@@ -124,17 +138,58 @@ __device__ __noinline__ void plane_exact_rows(const FusedArgs &a, int plane, int
   *hi_out = hi;
 }
 
-// Occupancy the kernel is compiled for: 16 one-warp CTAs per SM (128 registers).
-template <typename T, int W, int NRB, int QM>
+// Quantizer epilogue on N values held in registers (QM_MM_REDUCE does not come here).
+template <int QM, int N>
+__device__ __forceinline__ void plane_quant(float *o, const QuantArgs &q, const MmCoef &mm) {
+  if (QM == QM_FPQ_LEAN) {
+#pragma unroll
+    for (int j = 0; j < N; ++j) o[j] = fpq_apply_fast<false>(o[j], q);
+  } else if (QM == QM_FPQ && q.fpq_fast) {
+    if (q.fpq_min < 0.0f) {
+#pragma unroll
+      for (int j = 0; j < N; ++j) o[j] = fpq_apply_fast<true>(o[j], q);
+    } else {
+#pragma unroll
+      for (int j = 0; j < N; ++j) o[j] = fpq_apply_fast<false>(o[j], q);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < N; ++j) o[j] = quant_apply<QM>(o[j], q, mm);
+  }
+}
+
+// Per-plane min / max of a thread group of TPP lanes (aligned, power of two) into the
+// encoded per-channel slots. NaN never enters (fminf / fmaxf drop it), matching the
+// element-wise reduction.
+template <int TPP>
+__device__ __forceinline__ void plane_reduce_minmax(const QuantArgs &q, int ch, float lo, float hi,
+                                                    bool active, int lane) {
+#pragma unroll
+  for (int o = 1; o < TPP; o <<= 1) {
+    lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+    hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+  }
+  if (active && (lane % TPP) == 0) {
+    atomicMin(q.mm_enc_min + ch, enc_ordered(lo));
+    atomicMax(q.mm_enc_max + ch, enc_ordered(hi));
+  }
+}
+
+// ---- stride 1 ---------------------------------------------------------------------------
+// Thread block of R x W outputs; the plane is NRB blocks high and NCB blocks wide.
+// Compiled for 16 one-warp CTAs per SM (128 registers).
+template <typename T, int W, int NRB, int NCB, int QM>
 __global__ void __launch_bounds__(32, 16)
     fused_plane_kernel(const __grid_constant__ FusedArgs a, const PlaneCfg c) {
+  static_assert(NCB == 1 || W % 2 == 0, "column blocks need an even block width");
   constexpr int R = kPlaneRows;
   constexpr int H = R * NRB;
-  constexpr int PE = H * W;          // elements per plane
+  constexpr int PW = W * NCB;        // plane width
+  constexpr int PE = H * PW;         // elements per plane
   constexpr int NP = (W + 1) / 2;    // output pairs per row
-  constexpr int P = 32 / NRB;        // planes per CTA
+  constexpr int TPP = NRB * NCB;     // threads per plane
+  constexpr int P = 32 / TPP;        // planes per CTA
   constexpr int SW = plane_stash_elems(W);
-  constexpr bool LEAN = QM == QM_FPQ_LEAN;
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
   T *tile = reinterpret_cast<T *>(smem_raw);
@@ -161,12 +216,15 @@ __global__ void __launch_bounds__(32, 16)
     }
   }
 
-  // ---- this thread's plane, rows and per-channel operands (the copy is in flight) --------
-  const int pl = lane / NRB;
-  const int rb = lane - pl * NRB;
+  // ---- this thread's plane, block and per-channel operands (the copy is in flight) -------
+  const int pl = lane / TPP;
+  const int rb = (lane / NCB) % NRB;
+  const int cb = lane % NCB;
   const bool active = pl < pv;
   const int plane = active ? plane0 + pl : n_planes - 1;
   const int ch = plane % a.OC;
+  const bool has_left = NCB > 1 && cb > 0;
+  const bool has_right = NCB > 1 && cb + 1 < NCB;
   const f32x2 nz = negzero2();
   f32x2 w2[9];
   bool exact = false;
@@ -185,7 +243,7 @@ __global__ void __launch_bounds__(32, 16)
   f32x2 bias2 = splat2(bv);
   pin(bias2);
   BnPacked bnp;
-  if (LEAN || a.has_bn) bnp = make_bn_packed(load_bn<T>(a, ch), nz);
+  if (QM == QM_FPQ_LEAN || a.has_bn) bnp = make_bn_packed(load_bn<T>(a, ch), nz);
   const MmCoef mm = load_mm<QM>(a, ch);
 
   if (!async_tile) {
@@ -199,14 +257,19 @@ __global__ void __launch_bounds__(32, 16)
     return;
   }
 
-  T *rows = tile + pl * PE + rb * (R * W);  // this thread's R rows, overwritten in place
-  // the row below the block belongs to the next thread, which overwrites it early: keep a copy
-  T *my_stash = stash + lane * SW;
+  // this thread's R x W block, overwritten in place (row pitch PW)
+  T *rows = tile + pl * PE + rb * (R * PW) + cb * W;
+  // The row below the block belongs to the next thread, which overwrites it early: keep a
+  // copy, laid out like a tile row (left halo at [-1], right halo at [W]).
+  T *my_stash = stash + lane * SW + 2;
   if (NRB > 1) {
     if (rb + 1 < NRB) {
+      const T *below = rows + R * PW;
       float xv[2 * NP];
-      plane_load_row<T, W>(rows + R * W, true, xv);
+      plane_load_row<T, W>(below, true, xv);
       plane_store_row<T, W>(my_stash, xv);
+      if (has_left) my_stash[-1] = below[-1];
+      if (has_right) my_stash[W] = below[W];
     }
     __syncwarp();
   }
@@ -219,11 +282,17 @@ __global__ void __launch_bounds__(32, 16)
   auto step = [&](int k, f32x2 *fin, f32x2 *mid) {
     const int gi = rb * R - 1 + k;
     const bool valid = gi >= 0 && gi < H;
-    const T *src = (NRB > 1 && k == R + 1) ? my_stash : rows + (k - 1) * W;
+    const T *src = (NRB > 1 && k == R + 1) ? my_stash : rows + (k - 1) * PW;
     float xv[2 * NP];
     plane_load_row<T, W>(src, valid, xv);
-    // The row above the block is the upper neighbour's last row, which it overwrites in its
-    // last step; the barrier keeps every lane's first read ahead of any lane's last write.
+    float xl = 0.0f, xr = 0.0f;  // the neighbours' edge columns (zero at the plane edge)
+    if (NCB > 1) {
+      if (valid && has_left) xl = Elem<T>::to_f32(src[-1]);
+      if (valid && has_right) xr = Elem<T>::to_f32(src[W]);
+    }
+    // Reads of this step come before any write of this step: the row above the block is the
+    // upper neighbour's last row (written in its last step), and a neighbour's edge column
+    // of row k-1 is overwritten by its owner one step later.
     __syncwarp();
     // single-block planes: rows -1 and H are zero for every lane, their taps are skipped
     const bool zero_row = NRB == 1 && (k == 0 || k == R + 1);
@@ -232,7 +301,7 @@ __global__ void __launch_bounds__(32, 16)
     for (int j = 0; j < NP; ++j) E[j] = pack2(xv[2 * j], xv[2 * j + 1]);
 #pragma unroll
     for (int j = 0; j <= NP; ++j)
-      L[j] = pack2(j == 0 ? 0.0f : xv[2 * j - 1], j < NP ? xv[2 * j] : 0.0f);
+      L[j] = pack2(j == 0 ? xl : xv[2 * j - 1], j < NP ? xv[2 * j] : xr);
     constexpr bool LAST_L_ZERO = (W % 2) != 0;  // odd W: L[NP] = (0, 0)
 
     auto taps = [&](f32x2 *acc, int ky, bool init) {
@@ -248,7 +317,7 @@ __global__ void __launch_bounds__(32, 16)
 
     if (k >= 2) {
       if (!zero_row) taps(fin, 2, false);
-      if (LEAN || a.has_bn) bn_apply_packed<NP>(fin, bnp);
+      if (QM == QM_FPQ_LEAN || a.has_bn) bn_apply_packed<NP>(fin, bnp);
       float o[2 * NP];
 #pragma unroll
       for (int p = 0; p < NP; ++p) unpack2(fin[p], o[2 * p], o[2 * p + 1]);
@@ -259,22 +328,8 @@ __global__ void __launch_bounds__(32, 16)
           hi = fmaxf(hi, o[j]);
         }
       } else {
-        if (LEAN) {
-#pragma unroll
-          for (int j = 0; j < W; ++j) o[j] = fpq_apply_fast<false>(o[j], a.q);
-        } else if (QM == QM_FPQ && a.q.fpq_fast) {
-          if (a.q.fpq_min < 0.0f) {
-#pragma unroll
-            for (int j = 0; j < W; ++j) o[j] = fpq_apply_fast<true>(o[j], a.q);
-          } else {
-#pragma unroll
-            for (int j = 0; j < W; ++j) o[j] = fpq_apply_fast<false>(o[j], a.q);
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < W; ++j) o[j] = quant_apply<QM>(o[j], a.q, mm);
-        }
-        if (active) plane_store_row<T, W>(rows + (k - 2) * W, o);
+        plane_quant<QM, W>(o, a.q, mm);
+        if (active) plane_store_row<T, W>(rows + (k - 2) * PW, o);
       }
     }
     if (k >= 1 && k <= R) taps(mid, 1, false);
@@ -295,18 +350,11 @@ __global__ void __launch_bounds__(32, 16)
   }
 
   // ---- planes that need tap-skipping semantics: exact re-evaluation from global memory ----
-  if (exact && active) plane_exact_rows<T, W, QM>(a, plane, ch, rb * R, rows, mm, &lo, &hi);
+  if (exact && active)
+    plane_exact_block<T, QM>(a, plane, ch, rb * R, cb * W, R, W, rows, PW, mm, &lo, &hi);
 
   if (QM == QM_MM_REDUCE) {
-    if (NRB == 2) {
-      lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, 1));
-      hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, 1));
-    }
-    if (active && (NRB != 2 || rb == 0)) {
-      // NaN never enters (fminf / fmaxf drop it), matching the element-wise reduction
-      atomicMin(a.q.mm_enc_min + ch, enc_ordered(lo));
-      atomicMax(a.q.mm_enc_max + ch, enc_ordered(hi));
-    }
+    plane_reduce_minmax<TPP>(a.q, ch, lo, hi, active, lane);
     return;
   }
 
@@ -323,12 +371,185 @@ __global__ void __launch_bounds__(32, 16)
   }
 }
 
-// Host-side entry (fused_plane.cu): launches fused_plane_kernel<T, W, H / 7, QM>.
-cudaError_t launch_plane(int dtype, int w, int qm, const FusedArgs &a, const PlaneCfg &c,
+// ---- stride 2 ---------------------------------------------------------------------------
+// Thread block of 14 x 14 inputs = 7 x 7 outputs; the plane is NB x NB blocks (14x14 or
+// 28x28 inputs). Taps are scalar (the two outputs of a packed pair would need operands two
+// elements apart, which costs more moves than it saves), BN is packed. The traffic per
+// output is 2.5 times that of stride 1, so the arithmetic has issue slots to spare.
+template <typename T, int NB, int QM>
+__global__ void __launch_bounds__(32, 7)
+    fused_plane_s2_kernel(const __grid_constant__ FusedArgs a, const PlaneCfg c) {
+  constexpr int BW = 14;             // input block edge
+  constexpr int OB = 7;              // output block edge
+  constexpr int PW = BW * NB;        // input plane edge
+  constexpr int PE = PW * PW;
+  constexpr int OW = OB * NB;        // output plane edge
+  constexpr int OE = OW * OW;
+  constexpr int TPP = NB * NB;
+  constexpr int P = 32 / TPP;
+  constexpr int NPO = (OB + 1) / 2;  // output pairs (one dummy lane)
+
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  T *tile = reinterpret_cast<T *>(smem_raw);
+  constexpr size_t tile_bytes = ((size_t)P * PE * sizeof(T) + 15) / 16 * 16;
+  T *otile = reinterpret_cast<T *>(smem_raw + tile_bytes);
+  constexpr size_t otile_bytes = ((size_t)P * OE * sizeof(T) + 15) / 16 * 16;
+  unsigned long long *bar = reinterpret_cast<unsigned long long *>(smem_raw + tile_bytes + otile_bytes);
+
+  const int lane = threadIdx.x;
+  const int n_planes = (int)(a.n * a.OC);
+  const int plane0 = blockIdx.x * P;
+  const int pv = min(P, n_planes - plane0);
+  const T *x = static_cast<const T *>(a.x);
+  T *y = static_cast<T *>(a.y);
+  const unsigned int bytes = (unsigned int)(pv * PE * sizeof(T));
+  const unsigned int obytes = (unsigned int)(pv * OE * sizeof(T));
+  const bool async_tile = c.bulk != 0 && (bytes % 16) == 0 && (obytes % 16) == 0;
+
+  if (lane == 0) {
+    mbar_init(bar, 1);
+    mbar_fence_init();
+    if (async_tile) {
+      mbar_expect_tx(bar, bytes);
+      bulk_load_1d(tile, x + (long long)plane0 * PE, bytes, bar);
+    }
+  }
+
+  const int pl = lane / TPP;
+  const int rb = (lane / NB) % NB;
+  const int cb = lane % NB;
+  const bool active = pl < pv;
+  const int plane = active ? plane0 + pl : n_planes - 1;
+  const int ch = plane % a.OC;
+  const bool has_left = NB > 1 && cb > 0;
+  const f32x2 nz = negzero2();
+  float wr[9];
+  bool exact = false;
+  {
+    const T *w = static_cast<const T *>(a.w) + (long long)ch * 9;
+#pragma unroll
+    for (int i = 0; i < 9; ++i) {
+      wr[i] = Elem<T>::to_f32(w[i]);
+      exact = exact || !(fabsf(wr[i]) <= 3.402823466e38f);
+      pin(wr[i]);
+    }
+  }
+  float bv = a.b ? Elem<T>::to_f32(static_cast<const T *>(a.b)[ch]) : 0.0f;
+  exact = exact || __float_as_uint(bv) == 0x80000000u;
+  pin(bv);
+  BnPacked bnp;
+  if (QM == QM_FPQ_LEAN || a.has_bn) bnp = make_bn_packed(load_bn<T>(a, ch), nz);
+  const MmCoef mm = load_mm<QM>(a, ch);
+
+  if (!async_tile) {
+    const int n = pv * PE;
+    const T *src = x + (long long)plane0 * PE;
+    for (int i = lane; i < n; i += 32) tile[i] = src[i];
+  }
+  __syncwarp();
+  if (async_tile && !mbar_wait_bounded(bar, 0)) {
+    if (a.flag) atomicExch(a.flag, 1);
+    return;
+  }
+
+  const T *rows = tile + pl * PE + rb * (BW * PW) + cb * BW;  // this thread's 14 x 14 inputs
+  T *orows = otile + pl * OE + rb * (OB * OW) + cb * OB;      // its 7 x 7 outputs
+  float lo = __uint_as_float(0x7f800000u), hi = __uint_as_float(0xff800000u);
+
+  // xv[0] = the column left of the block, xv[1..14] = the block's row
+  auto load_row = [&](const T *p, bool valid, float *xv) {
+    plane_load_row<T, BW>(p, valid, xv + 1);
+    xv[0] = 0.0f;
+    if (NB > 1) {
+      if (valid && has_left) xv[0] = Elem<T>::to_f32(p[-1]);
+    }
+  };
+  auto taps = [&](float *acc, const float *xv, int ky, bool init) {
+#pragma unroll
+    for (int j = 0; j < OB; ++j) {
+      float v = init ? bv : acc[j];
+      v = __fadd_rn(v, __fmul_rn(wr[ky * 3 + 0], xv[2 * j]));
+      v = __fadd_rn(v, __fmul_rn(wr[ky * 3 + 1], xv[2 * j + 1]));
+      v = __fadd_rn(v, __fmul_rn(wr[ky * 3 + 2], xv[2 * j + 2]));
+      acc[j] = v;
+    }
+  };
+
+  float acc[OB];
+  {
+    // the row above the block: zero above the plane (skipped when no block has a row above)
+    if (NB == 1) {
+#pragma unroll
+      for (int j = 0; j < OB; ++j) acc[j] = bv;
+    } else {
+      float xv[BW + 2];
+      load_row(rows - PW, rb > 0, xv);
+      taps(acc, xv, 0, true);
+    }
+  }
+#pragma unroll 1
+  for (int t = 0; t < OB; ++t) {
+    float xv[BW + 2];
+    load_row(rows + (2 * t) * PW, true, xv);
+    taps(acc, xv, 1, false);
+    load_row(rows + (2 * t + 1) * PW, true, xv);
+    taps(acc, xv, 2, false);
+    f32x2 pr[NPO];
+#pragma unroll
+    for (int p = 0; p < NPO; ++p) pr[p] = pack2(acc[2 * p], 2 * p + 1 < OB ? acc[2 * p + 1] : acc[2 * p]);
+    if (QM == QM_FPQ_LEAN || a.has_bn) bn_apply_packed<NPO>(pr, bnp);
+    float o[2 * NPO];
+#pragma unroll
+    for (int p = 0; p < NPO; ++p) unpack2(pr[p], o[2 * p], o[2 * p + 1]);
+    if (QM == QM_MM_REDUCE) {
+#pragma unroll
+      for (int j = 0; j < OB; ++j) {
+        lo = fminf(lo, o[j]);
+        hi = fmaxf(hi, o[j]);
+      }
+    } else {
+      plane_quant<QM, OB>(o, a.q, mm);
+#pragma unroll
+      for (int j = 0; j < OB; ++j) orows[t * OW + j] = Elem<T>::from_f32(o[j]);
+    }
+    taps(acc, xv, 0, true);  // the next output row starts from this step's odd input row
+  }
+
+  if (exact && active)
+    plane_exact_block<T, QM>(a, plane, ch, rb * OB, cb * OB, OB, OB, orows, OW, mm, &lo, &hi);
+
+  if (QM == QM_MM_REDUCE) {
+    plane_reduce_minmax<TPP>(a.q, ch, lo, hi, active, lane);
+    return;
+  }
+
+  T *dst = y + (long long)plane0 * OE;
+  if (async_tile) {
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) bulk_store_1d_and_wait(dst, otile, obytes);
+  } else {
+    __syncwarp();
+    const int n = pv * OE;
+    for (int i = lane; i < n; i += 32) dst[i] = otile[i];
+  }
+}
+
+// Host-side entry (fused_plane.cu).
+cudaError_t launch_plane(int dtype, int hw, int stride, int qm, const FusedArgs &a, const PlaneCfg &c,
                          cudaStream_t stream);
-// Whether a (width, height) plane has an instantiation.
-__host__ inline bool plane_shape_supported(int h, int w) {
-  return (h == 7 && w == 7) || (h == 14 && w == 14);
+// Threads per plane of the instantiation for a square hw x hw plane and stride, 0 if none.
+__host__ inline int plane_threads_per_plane(int h, int w, int stride) {
+  if (h != w) return 0;
+  if (stride == 1) return w == 7 ? 1 : w == 14 ? 2 : w == 28 ? 8 : 0;
+  if (stride == 2) return w == 14 ? 1 : w == 28 ? 4 : 0;
+  return 0;
+}
+__host__ inline size_t plane_launch_smem(int hw, int stride, int elem_size) {
+  if (stride == 1)
+    return hw == 7 ? plane_smem_bytes(7, 1, 1, elem_size)
+                   : hw == 14 ? plane_smem_bytes(14, 2, 1, elem_size) : plane_smem_bytes(14, 4, 2, elem_size);
+  return plane_s2_smem_bytes(hw / 14, elem_size);
 }
 
 }  // namespace dwbnq

@@ -154,16 +154,16 @@ int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan
   const long long n_planes = d.n * d.c;
   if (n_planes > 0x7fffffffLL) return DWBNQ_OK;
 
-  // ---- small planes (7x7, 14x14), 3x3 stride 1: one warp per CTA, full-width rows ----------
-  if (K == 3 && s == 1 && plane_shape_supported(d.h, d.w) && (forced == PATH_AUTO || forced == PATH_PLANE)) {
-    const int nrb = d.h / kPlaneRows;
+  // ---- small planes (7x7, 14x14, 28x28): one warp per CTA, whole planes -------------------
+  const int tpp = K == 3 ? plane_threads_per_plane(d.h, d.w, s) : 0;
+  if (tpp > 0 && (forced == PATH_AUTO || forced == PATH_PLANE)) {
     TileCfg &c = plan->cfg;
-    c.P = 32 / nrb;
+    c.P = 32 / tpp;
     c.R = kPlaneRows;
-    c.n_rb = nrb;
-    c.n_strips = 1;
+    c.n_rb = s == 1 ? d.h / kPlaneRows : d.h / 14;
+    c.n_strips = s == 1 ? (d.w + 13) / 14 : d.w / 14;
     c.n_row_tiles = 1;
-    c.TH = d.h;
+    c.TH = Ho;
     c.TR = d.h;
     c.WS = d.w;
     c.tile_elems = d.h * d.w;
@@ -173,7 +173,7 @@ int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan
     c.n_tiles = (int)((n_planes + c.P - 1) / c.P);
     plan->path = PATH_PLANE;
     plan->threads = 32;
-    plan->smem = plane_smem_bytes(d.w, nrb, d.dtype == DWBNQ_F32 ? 4 : 2);
+    plan->smem = plane_launch_smem(d.w, s, d.dtype == DWBNQ_F32 ? 4 : 2);
     plan->ctas = c.n_tiles;
     return DWBNQ_OK;
   }
@@ -319,7 +319,7 @@ int launch_fused(const dwbnq_conv_desc &d, FusedArgs &a, int qm, int device, cud
     pc.P = plan.cfg.P;
     pc.n_tiles = plan.cfg.n_tiles;
     pc.bulk = plan.cfg.vec_fill;
-    e = launch_plane(d.dtype, d.w, qm, a, pc, stream);
+    e = launch_plane(d.dtype, d.w, d.stride_h, qm, a, pc, stream);
     if (e != cudaSuccess) return fail_cuda(e, "fused_plane_kernel launch");
     return DWBNQ_OK;
   }

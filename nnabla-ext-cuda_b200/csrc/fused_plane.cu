@@ -1,4 +1,4 @@
-// Instantiations and dispatch of the small-plane fused kernel (7x7 and 14x14 planes).
+// Instantiations and dispatch of the small-plane fused kernels (7x7, 14x14, 28x28 planes).
 #include "dwbnq_internal.h"
 
 namespace dwbnq {
@@ -7,31 +7,45 @@ namespace {
 
 typedef void (*PlaneKernel)(const FusedArgs, const PlaneCfg);
 
-template <typename T, int W, int NRB>
-PlaneKernel pick_qm(int qm) {
+template <typename T, int W, int NRB, int NCB>
+PlaneKernel pick_s1(int qm) {
   switch (qm) {
-    case QM_NONE: return fused_plane_kernel<T, W, NRB, QM_NONE>;
-    case QM_FPQ: return fused_plane_kernel<T, W, NRB, QM_FPQ>;
-    case QM_POW2: return fused_plane_kernel<T, W, NRB, QM_POW2>;
-    case QM_MM_APPLY: return fused_plane_kernel<T, W, NRB, QM_MM_APPLY>;
-    case QM_MM_REDUCE: return fused_plane_kernel<T, W, NRB, QM_MM_REDUCE>;
-    case QM_FPQ_LEAN: return fused_plane_kernel<T, W, NRB, QM_FPQ_LEAN>;
+    case QM_NONE: return fused_plane_kernel<T, W, NRB, NCB, QM_NONE>;
+    case QM_FPQ: return fused_plane_kernel<T, W, NRB, NCB, QM_FPQ>;
+    case QM_POW2: return fused_plane_kernel<T, W, NRB, NCB, QM_POW2>;
+    case QM_MM_APPLY: return fused_plane_kernel<T, W, NRB, NCB, QM_MM_APPLY>;
+    case QM_MM_REDUCE: return fused_plane_kernel<T, W, NRB, NCB, QM_MM_REDUCE>;
+    case QM_FPQ_LEAN: return fused_plane_kernel<T, W, NRB, NCB, QM_FPQ_LEAN>;
+  }
+  return nullptr;
+}
+
+template <typename T, int NB>
+PlaneKernel pick_s2(int qm) {
+  switch (qm) {
+    case QM_NONE: return fused_plane_s2_kernel<T, NB, QM_NONE>;
+    case QM_FPQ: return fused_plane_s2_kernel<T, NB, QM_FPQ>;
+    case QM_POW2: return fused_plane_s2_kernel<T, NB, QM_POW2>;
+    case QM_MM_APPLY: return fused_plane_s2_kernel<T, NB, QM_MM_APPLY>;
+    case QM_MM_REDUCE: return fused_plane_s2_kernel<T, NB, QM_MM_REDUCE>;
+    case QM_FPQ_LEAN: return fused_plane_s2_kernel<T, NB, QM_FPQ_LEAN>;
   }
   return nullptr;
 }
 
 template <typename T>
-cudaError_t launch_t(int w, int qm, const FusedArgs &a, const PlaneCfg &c, cudaStream_t stream) {
+cudaError_t launch_t(int hw, int stride, int qm, const FusedArgs &a, const PlaneCfg &c, cudaStream_t stream) {
   PlaneKernel kern = nullptr;
-  size_t smem = 0;
-  if (w == 7) {
-    kern = pick_qm<T, 7, 1>(qm);
-    smem = plane_smem_bytes(7, 1, sizeof(T));
-  } else if (w == 14) {
-    kern = pick_qm<T, 14, 2>(qm);
-    smem = plane_smem_bytes(14, 2, sizeof(T));
+  if (stride == 1) {
+    if (hw == 7) kern = pick_s1<T, 7, 1, 1>(qm);
+    else if (hw == 14) kern = pick_s1<T, 14, 2, 1>(qm);
+    else if (hw == 28) kern = pick_s1<T, 14, 4, 2>(qm);
+  } else if (stride == 2) {
+    if (hw == 14) kern = pick_s2<T, 1>(qm);
+    else if (hw == 28) kern = pick_s2<T, 2>(qm);
   }
   if (!kern) return cudaErrorInvalidValue;
+  const size_t smem = plane_launch_smem(hw, stride, sizeof(T));
   // all of the unified L1 / shared memory as shared memory: the tiles are the working set
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
                                        cudaSharedmemCarveoutMaxShared);
@@ -42,9 +56,10 @@ cudaError_t launch_t(int w, int qm, const FusedArgs &a, const PlaneCfg &c, cudaS
 
 }  // namespace
 
-cudaError_t launch_plane(int dtype, int w, int qm, const FusedArgs &a, const PlaneCfg &c,
+cudaError_t launch_plane(int dtype, int hw, int stride, int qm, const FusedArgs &a, const PlaneCfg &c,
                          cudaStream_t stream) {
-  return dtype == DWBNQ_F32 ? launch_t<float>(w, qm, a, c, stream) : launch_t<__half>(w, qm, a, c, stream);
+  return dtype == DWBNQ_F32 ? launch_t<float>(hw, stride, qm, a, c, stream)
+                            : launch_t<__half>(hw, stride, qm, a, c, stream);
 }
 
 }  // namespace dwbnq

@@ -330,37 +330,43 @@ SMALL_QUANTS = [None,
 SMALL_QUANT_IDS = ["none", "fpq_lean", "fpq_signed", "fpq_0.3", "pow2", "minmax"]
 
 
+SMALL_SHAPES = [(7, 1), (14, 1), (28, 1), (14, 2), (28, 2)]
+SMALL_SHAPE_IDS = ["7x7s1", "14x14s1", "28x28s1", "14x14s2", "28x28s2"]
+
+
 @pytest.mark.parametrize("quant", SMALL_QUANTS, ids=SMALL_QUANT_IDS)
-@pytest.mark.parametrize("hw", [7, 14])
+@pytest.mark.parametrize("hw,stride", SMALL_SHAPES, ids=SMALL_SHAPE_IDS)
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16], ids=["f32", "f16"])
-def test_small_plane_kernel(oracle, cuda_device, dtype, hw, quant):
+def test_small_plane_kernel(oracle, cuda_device, dtype, hw, stride, quant):
     """Full tiles, a ragged last tile (37 planes: the 7x7 fp32 remainder is not a multiple of
     16 bytes, so its tile is copied by the threads) and a batch smaller than one tile."""
-    rng = np.random.default_rng(100 + hw)
+    rng = np.random.default_rng(100 + hw + stride)
     for n, c in ((5, 64), (1, 37), (1, 3)):
-        spec = workloads.LayerSpec("small", n, c, hw, hw, 3, 1, 1, None)
+        spec = workloads.LayerSpec("small", n, c, hw, hw, 3, stride, 1, None)
         d = _rand_layer(rng, n, c, hw, hw, 3)
         if quant and quant["kind"] == "minmax":
             d.update(qr_min=np.zeros(c, np.float32), qr_max=np.ones(c, np.float32), ql_min=np.zeros(c, np.float32),
                      ql_max=np.full(c, 255, np.float32))
         h16, up = f16_inputs(d) if dtype == torch.float16 else (d, d)
-        plan = ops.fused_plan(dev(h16["x"], cuda_device), dev(h16["w"], cuda_device), pad=(1, 1), stride=(1, 1))
+        plan = ops.fused_plan(dev(h16["x"], cuda_device), dev(h16["w"], cuda_device), pad=(1, 1),
+                              stride=(stride, stride))
         assert plan["path"] == L.PATH_PLANE, plan
         want, _, extra = oracle_fused(oracle, up, spec, quant)
         got, t = run_fused(h16, spec, cuda_device, quant, dtype=dtype)
         if dtype == torch.float16:
             want = oracle.to_f16_result(want)
-        assert_same_bits(got, want, "%dx%d n=%d c=%d" % (hw, hw, n, c))
+        assert_same_bits(got, want, "%dx%d s%d n=%d c=%d" % (hw, hw, stride, n, c))
         if extra is not None and dtype == torch.float32:
             assert_same_bits(t["qr_min"].cpu().numpy(), extra[0], "qr_min")
             assert_same_bits(t["qr_max"].cpu().numpy(), extra[1], "qr_max")
 
 
-@pytest.mark.parametrize("hw", [7, 14])
-def test_small_plane_kernel_unaligned_and_optional(oracle, cuda_device, hw):
-    rng = np.random.default_rng(200 + hw)
+@pytest.mark.parametrize("hw,stride", SMALL_SHAPES, ids=SMALL_SHAPE_IDS)
+def test_small_plane_kernel_unaligned_and_optional(oracle, cuda_device, hw, stride):
+    rng = np.random.default_rng(200 + hw + stride)
     n, c = 3, 40
-    spec = workloads.LayerSpec("small_unaligned", n, c, hw, hw, 3, 1, 1, None)
+    st = (stride, stride)
+    spec = workloads.LayerSpec("small_unaligned", n, c, hw, hw, 3, stride, 1, None)
     d = _rand_layer(rng, n, c, hw, hw, 3)
     q = {"kind": "fpq", "sign": False, "n": 8, "delta": 2.0 ** -3}
     want, _, _ = oracle_fused(oracle, d, spec, q)
@@ -370,11 +376,11 @@ def test_small_plane_kernel_unaligned_and_optional(oracle, cuda_device, hw):
     ybuf = torch.empty(want.size + 1, device=cuda_device)
     y = ybuf[1:].view(want.shape)
     t = {k: dev(v, cuda_device) for k, v in d.items()}
-    ops.fused_dw_bn_quant(x, t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], 1e-5, (1, 1), (1, 1),
+    ops.fused_dw_bn_quant(x, t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], 1e-5, (1, 1), st,
                           quant=q, out=y)
     assert_same_bits(y.cpu().numpy(), want, "unaligned x / y")
-    want = oracle.fpq(oracle.dwconv(d["x"], d["w"], None, (1, 1), (1, 1)), False, 8, 2.0 ** -3)
-    got = ops.fused_dw_bn_quant(t["x"], t["w"], None, None, None, None, None, 1e-5, (1, 1), (1, 1), quant=q)
+    want = oracle.fpq(oracle.dwconv(d["x"], d["w"], None, st, (1, 1)), False, 8, 2.0 ** -3)
+    got = ops.fused_dw_bn_quant(t["x"], t["w"], None, None, None, None, None, 1e-5, (1, 1), st, quant=q)
     assert_same_bits(got.cpu().numpy(), want, "no bias, no BN")
     # the other families on the same planes give the same bits
     for path in (L.PATH_RAW, L.PATH_COOP, L.PATH_GENERIC):
@@ -383,11 +389,12 @@ def test_small_plane_kernel_unaligned_and_optional(oracle, cuda_device, hw):
         assert_same_bits(got_p, want_p, "path %d" % path)
 
 
-@pytest.mark.parametrize("hw", [7, 14])
-def test_small_plane_kernel_exact_evaluation_planes(oracle, cuda_device, hw):
-    rng = np.random.default_rng(300 + hw)
+@pytest.mark.parametrize("hw,stride", SMALL_SHAPES, ids=SMALL_SHAPE_IDS)
+def test_small_plane_kernel_exact_evaluation_planes(oracle, cuda_device, hw, stride):
+    rng = np.random.default_rng(300 + hw + stride)
     n, c = 2, 20
-    spec = workloads.LayerSpec("small_patho", n, c, hw, hw, 3, 1, 1, None)
+    st = (stride, stride)
+    spec = workloads.LayerSpec("small_patho", n, c, hw, hw, 3, stride, 1, None)
     d = _rand_layer(rng, n, c, hw, hw, 3)
     d["x"][:, 0] = -0.0
     d["w"][0] = np.abs(d["w"][0]) + np.float32(0.1)
@@ -396,9 +403,9 @@ def test_small_plane_kernel_exact_evaluation_planes(oracle, cuda_device, hw):
     d["w"][2, 2, 2] = np.nan
     d["w"][3, 1, 1] = -np.inf
     d["b"][7] = -0.0
-    want = oracle.dwconv(d["x"], d["w"], d["b"], (1, 1), (1, 1))
+    want = oracle.dwconv(d["x"], d["w"], d["b"], st, (1, 1))
     got = ops.depthwise_convolution(dev(d["x"], cuda_device), dev(d["w"], cuda_device), dev(d["b"], cuda_device), 1,
-                                    (1, 1), (1, 1)).cpu().numpy()
+                                    (1, 1), st).cpu().numpy()
     assert_same_bits(got, want, "pathological parameters")
     assert (bits(got[:, 0]) == 0x80000000).all()
     for q in SMALL_QUANTS[1:5]:
