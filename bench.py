@@ -256,6 +256,8 @@ def run_own(args):
 
     if args.tune:
         ops.set_tuning(*[int(v) for v in args.tune.split(",")])
+    if args.force_path is not None:
+        ops.set_forced_path(args.force_path)
 
     # ---- device-resident timing ---------------------------------------------------------
     for _ in range(args.warmup):
@@ -430,6 +432,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-layer-pass", action="store_true")
     ap.add_argument("--ablate", default="", help="profiling only: 'bn', 'quant' or 'bn,quant' are left out")
+    ap.add_argument("--force-path", type=int, default=None, help="profiling only: kernel family 0..4")
     ap.add_argument("--tune", default="", help="profiling only: planner override P,row_blocks,threads,rows_per_patch")
     args = ap.parse_args()
     defaults = {"cfg0": 32, "cfg1": 256, "cfg2": 128, "cfg3": 512, "cfg4": 256}

@@ -44,8 +44,8 @@ constexpr int kPlaneRows = 7;  // rows per thread
 // Stash row of a thread: [2 unused | left halo | W elements | right halo | pad], even size.
 __host__ __device__ constexpr int plane_stash_elems(int W) { return (W + 4 + 1) / 2 * 2; }
 // stride 1: tile | stash (NRB > 1) | mbarrier
-__host__ __device__ constexpr size_t plane_smem_bytes(int W, int NRB, int NCB, int elem_size) {
-  size_t s = (size_t)(32 / (NRB * NCB)) * (kPlaneRows * NRB) * (W * NCB) * elem_size;
+__host__ __device__ constexpr size_t plane_smem_bytes(int W, int NRB, int NCB, int NBND, int elem_size) {
+  size_t s = (size_t)(32 / (NRB * NCB)) * (kPlaneRows * NRB + (NBND > 1 ? 2 : 0)) * (W * NCB) * elem_size;
   s = (s + 15) / 16 * 16;
   if (NRB > 1) s += (size_t)32 * plane_stash_elems(W) * elem_size;
   s = (s + 15) / 16 * 16;
@@ -176,16 +176,23 @@ __device__ __forceinline__ void plane_reduce_minmax(const QuantArgs &q, int ch, 
 }
 
 // ---- stride 1 ---------------------------------------------------------------------------
-// Thread block of R x W outputs; the plane is NRB blocks high and NCB blocks wide.
+// Thread block of R x W outputs; a tile is NRB blocks high and NCB blocks wide. With
+// NBND == 1 the tile is a whole plane (and a CTA takes 32 / (NRB * NCB) planes); with
+// NBND > 1 a plane is cut into NBND bands of full-width rows, one band per CTA, and the
+// copy brings the row above and the row below the band along (they are contiguous with it).
 // Compiled for 16 one-warp CTAs per SM (128 registers).
-template <typename T, int W, int NRB, int NCB, int QM>
+template <typename T, int W, int NRB, int NCB, int NBND, int QM>
 __global__ void __launch_bounds__(32, 16)
     fused_plane_kernel(const __grid_constant__ FusedArgs a, const PlaneCfg c) {
   static_assert(NCB == 1 || W % 2 == 0, "column blocks need an even block width");
+  static_assert(NBND == 1 || NRB * NCB == 32, "a band is one warp's worth of blocks");
   constexpr int R = kPlaneRows;
-  constexpr int H = R * NRB;
+  constexpr int TB = R * NRB;        // rows per tile
+  constexpr int H = TB * NBND;       // plane height
   constexpr int PW = W * NCB;        // plane width
   constexpr int PE = H * PW;         // elements per plane
+  constexpr int HALO = NBND > 1 ? 1 : 0;  // row slots above / below the band
+  constexpr int TE = (TB + 2 * HALO) * PW;  // shared-memory elements per plane of the tile
   constexpr int NP = (W + 1) / 2;    // output pairs per row
   constexpr int TPP = NRB * NCB;     // threads per plane
   constexpr int P = 32 / TPP;        // planes per CTA
@@ -193,26 +200,32 @@ __global__ void __launch_bounds__(32, 16)
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
   T *tile = reinterpret_cast<T *>(smem_raw);
-  constexpr size_t tile_bytes = ((size_t)P * PE * sizeof(T) + 15) / 16 * 16;
+  constexpr size_t tile_bytes = ((size_t)P * TE * sizeof(T) + 15) / 16 * 16;
   T *stash = reinterpret_cast<T *>(smem_raw + tile_bytes);
   constexpr size_t stash_bytes = NRB > 1 ? ((size_t)32 * SW * sizeof(T) + 15) / 16 * 16 : 0;
   unsigned long long *bar = reinterpret_cast<unsigned long long *>(smem_raw + tile_bytes + stash_bytes);
 
   const int lane = threadIdx.x;
   const int n_planes = (int)(a.n * a.OC);
-  const int plane0 = blockIdx.x * P;
+  const int plane0 = (NBND > 1 ? blockIdx.x / NBND : blockIdx.x) * P;
+  const int r0 = NBND > 1 ? (blockIdx.x % NBND) * TB : 0;  // first plane row of the tile
   const int pv = min(P, n_planes - plane0);
-  const T *x = static_cast<const T *>(a.x);
   T *y = static_cast<T *>(a.y);
-  const unsigned int bytes = (unsigned int)(pv * PE * sizeof(T));
-  const bool async_tile = c.bulk != 0 && (bytes % 16) == 0;
+  // what comes in (band: with the rows above / below it that exist) and what goes out
+  const int in_first = NBND > 1 ? max(r0 - 1, 0) : 0;
+  const int in_rows = NBND > 1 ? min(r0 + TB + 1, H) - in_first : pv * H;
+  const T *in_src = static_cast<const T *>(a.x) + (long long)plane0 * PE + (long long)in_first * PW;
+  T *in_dst = tile + (NBND > 1 ? (in_first - (r0 - 1)) * PW : 0);
+  const unsigned int bytes = (unsigned int)(in_rows * PW * sizeof(T));
+  const unsigned int obytes = (unsigned int)((NBND > 1 ? TB : pv * H) * PW * sizeof(T));
+  const bool async_tile = c.bulk != 0 && (bytes % 16) == 0 && (obytes % 16) == 0;
 
   if (lane == 0) {
     mbar_init(bar, 1);
     mbar_fence_init();
     if (async_tile) {
       mbar_expect_tx(bar, bytes);
-      bulk_load_1d(tile, x + (long long)plane0 * PE, bytes, bar);
+      bulk_load_1d(in_dst, in_src, bytes, bar);
     }
   }
 
@@ -247,9 +260,8 @@ __global__ void __launch_bounds__(32, 16)
   const MmCoef mm = load_mm<QM>(a, ch);
 
   if (!async_tile) {
-    const int n = pv * PE;
-    const T *src = x + (long long)plane0 * PE;
-    for (int i = lane; i < n; i += 32) tile[i] = src[i];
+    const int n = in_rows * PW;
+    for (int i = lane; i < n; i += 32) in_dst[i] = in_src[i];
   }
   __syncwarp();  // barrier initialisation and thread-copied data are visible
   if (async_tile && !mbar_wait_bounded(bar, 0)) {
@@ -258,7 +270,7 @@ __global__ void __launch_bounds__(32, 16)
   }
 
   // this thread's R x W block, overwritten in place (row pitch PW)
-  T *rows = tile + pl * PE + rb * (R * PW) + cb * W;
+  T *rows = tile + pl * TE + (HALO + rb * R) * PW + cb * W;
   // The row below the block belongs to the next thread, which overwrites it early: keep a
   // copy, laid out like a tile row (left halo at [-1], right halo at [W]).
   T *my_stash = stash + lane * SW + 2;
@@ -280,9 +292,10 @@ __global__ void __launch_bounds__(32, 16)
   // One step = one input row k (plane row rb*R - 1 + k): finishes output row k-2 held in
   // `fin`, continues output row k-1 held in `mid`, starts output row k in `fin`.
   auto step = [&](int k, f32x2 *fin, f32x2 *mid) {
-    const int gi = rb * R - 1 + k;
+    const int gi = r0 + rb * R - 1 + k;
     const bool valid = gi >= 0 && gi < H;
-    const T *src = (NRB > 1 && k == R + 1) ? my_stash : rows + (k - 1) * PW;
+    // the row below the block: the stash, or (last block of a band) the band's extra row
+    const T *src = (NRB > 1 && k == R + 1 && rb + 1 < NRB) ? my_stash : rows + (k - 1) * PW;
     float xv[2 * NP];
     plane_load_row<T, W>(src, valid, xv);
     float xl = 0.0f, xr = 0.0f;  // the neighbours' edge columns (zero at the plane edge)
@@ -295,7 +308,7 @@ __global__ void __launch_bounds__(32, 16)
     // of row k-1 is overwritten by its owner one step later.
     __syncwarp();
     // single-block planes: rows -1 and H are zero for every lane, their taps are skipped
-    const bool zero_row = NRB == 1 && (k == 0 || k == R + 1);
+    const bool zero_row = NRB == 1 && NBND == 1 && (k == 0 || k == R + 1);
     f32x2 E[NP], L[NP + 1];
 #pragma unroll
     for (int j = 0; j < NP; ++j) E[j] = pack2(xv[2 * j], xv[2 * j + 1]);
@@ -351,7 +364,7 @@ __global__ void __launch_bounds__(32, 16)
 
   // ---- planes that need tap-skipping semantics: exact re-evaluation from global memory ----
   if (exact && active)
-    plane_exact_block<T, QM>(a, plane, ch, rb * R, cb * W, R, W, rows, PW, mm, &lo, &hi);
+    plane_exact_block<T, QM>(a, plane, ch, r0 + rb * R, cb * W, R, W, rows, PW, mm, &lo, &hi);
 
   if (QM == QM_MM_REDUCE) {
     plane_reduce_minmax<TPP>(a.q, ch, lo, hi, active, lane);
@@ -359,15 +372,16 @@ __global__ void __launch_bounds__(32, 16)
   }
 
   // ---- the finished tile leaves in one piece ------------------------------------------------
-  T *dst = y + (long long)plane0 * PE;
+  T *dst = y + (long long)plane0 * PE + (long long)r0 * PW;
+  const T *out_src = tile + HALO * PW;
   if (async_tile) {
     fence_proxy_async_smem();  // this thread's shared-memory writes, for the copy engine
     __syncwarp();
-    if (lane == 0) bulk_store_1d_and_wait(dst, tile, bytes);
+    if (lane == 0) bulk_store_1d_and_wait(dst, out_src, obytes);
   } else {
     __syncwarp();
-    const int n = pv * PE;
-    for (int i = lane; i < n; i += 32) dst[i] = tile[i];
+    const int n = (NBND > 1 ? TB : pv * H) * PW;
+    for (int i = lane; i < n; i += 32) dst[i] = out_src[i];
   }
 }
 
@@ -538,17 +552,30 @@ __global__ void __launch_bounds__(32, 7)
 // Host-side entry (fused_plane.cu).
 cudaError_t launch_plane(int dtype, int hw, int stride, int qm, const FusedArgs &a, const PlaneCfg &c,
                          cudaStream_t stream);
-// Threads per plane of the instantiation for a square hw x hw plane and stride, 0 if none.
-__host__ inline int plane_threads_per_plane(int h, int w, int stride) {
-  if (h != w) return 0;
-  if (stride == 1) return w == 7 ? 1 : w == 14 ? 2 : w == 28 ? 8 : 0;
-  if (stride == 2) return w == 14 ? 1 : w == 28 ? 4 : 0;
-  return 0;
+// Geometry of the instantiation for a square hw x hw plane and stride; tpp == 0 if none.
+struct PlaneGeom {
+  int tpp;    // threads per plane (stride 1, banded: per band)
+  int bands;  // bands per plane (1 = whole planes)
+  int w, nrb, ncb;
+};
+__host__ inline PlaneGeom plane_geom(int h, int w, int stride) {
+  PlaneGeom g = {0, 1, 0, 0, 0};
+  if (h != w) return g;
+  if (stride == 1) {
+    if (w == 7) g = {1, 1, 7, 1, 1};
+    else if (w == 14) g = {2, 1, 14, 2, 1};
+    else if (w == 28) g = {8, 1, 14, 4, 2};
+    else if (w == 56) g = {32, 1, 14, 8, 4};
+    else if (w == 112) g = {32, 4, 14, 4, 8};
+  } else if (stride == 2) {
+    if (w == 14) g = {1, 1, 14, 1, 1};
+    else if (w == 28) g = {4, 1, 14, 2, 2};
+  }
+  return g;
 }
 __host__ inline size_t plane_launch_smem(int hw, int stride, int elem_size) {
-  if (stride == 1)
-    return hw == 7 ? plane_smem_bytes(7, 1, 1, elem_size)
-                   : hw == 14 ? plane_smem_bytes(14, 2, 1, elem_size) : plane_smem_bytes(14, 4, 2, elem_size);
+  const PlaneGeom g = plane_geom(hw, hw, stride);
+  if (stride == 1) return plane_smem_bytes(g.w, g.nrb, g.ncb, g.bands, elem_size);
   return plane_s2_smem_bytes(hw / 14, elem_size);
 }
 

@@ -155,22 +155,24 @@ int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan
   if (n_planes > 0x7fffffffLL) return DWBNQ_OK;
 
   // ---- small planes (7x7, 14x14, 28x28): one warp per CTA, whole planes -------------------
-  const int tpp = K == 3 ? plane_threads_per_plane(d.h, d.w, s) : 0;
-  if (tpp > 0 && (forced == PATH_AUTO || forced == PATH_PLANE)) {
+  const PlaneGeom pg = K == 3 ? plane_geom(d.h, d.w, s) : PlaneGeom{0, 1, 0, 0, 0};
+  if (pg.tpp > 0 && (forced == PATH_AUTO || forced == PATH_PLANE)) {
     TileCfg &c = plan->cfg;
-    c.P = 32 / tpp;
+    c.P = 32 / pg.tpp;
     c.R = kPlaneRows;
     c.n_rb = s == 1 ? d.h / kPlaneRows : d.h / 14;
     c.n_strips = s == 1 ? (d.w + 13) / 14 : d.w / 14;
-    c.n_row_tiles = 1;
-    c.TH = Ho;
+    c.n_row_tiles = pg.bands;
+    c.TH = Ho / pg.bands;
     c.TR = d.h;
     c.WS = d.w;
     c.tile_elems = d.h * d.w;
     const bool al = (reinterpret_cast<uintptr_t>(x) % 16) == 0 && (reinterpret_cast<uintptr_t>(y) % 16) == 0;
     c.vec_fill = al ? 1 : 0;
     c.vec_store = al ? 1 : 0;
-    c.n_tiles = (int)((n_planes + c.P - 1) / c.P);
+    const long long nt = (n_planes + c.P - 1) / c.P * pg.bands;
+    if (nt > 0x7fffffffLL) return DWBNQ_OK;
+    c.n_tiles = (int)nt;
     plan->path = PATH_PLANE;
     plan->threads = 32;
     plan->smem = plane_launch_smem(d.w, s, d.dtype == DWBNQ_F32 ? 4 : 2);

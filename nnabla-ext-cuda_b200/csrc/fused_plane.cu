@@ -7,15 +7,15 @@ namespace {
 
 typedef void (*PlaneKernel)(const FusedArgs, const PlaneCfg);
 
-template <typename T, int W, int NRB, int NCB>
+template <typename T, int W, int NRB, int NCB, int NBND>
 PlaneKernel pick_s1(int qm) {
   switch (qm) {
-    case QM_NONE: return fused_plane_kernel<T, W, NRB, NCB, QM_NONE>;
-    case QM_FPQ: return fused_plane_kernel<T, W, NRB, NCB, QM_FPQ>;
-    case QM_POW2: return fused_plane_kernel<T, W, NRB, NCB, QM_POW2>;
-    case QM_MM_APPLY: return fused_plane_kernel<T, W, NRB, NCB, QM_MM_APPLY>;
-    case QM_MM_REDUCE: return fused_plane_kernel<T, W, NRB, NCB, QM_MM_REDUCE>;
-    case QM_FPQ_LEAN: return fused_plane_kernel<T, W, NRB, NCB, QM_FPQ_LEAN>;
+    case QM_NONE: return fused_plane_kernel<T, W, NRB, NCB, NBND, QM_NONE>;
+    case QM_FPQ: return fused_plane_kernel<T, W, NRB, NCB, NBND, QM_FPQ>;
+    case QM_POW2: return fused_plane_kernel<T, W, NRB, NCB, NBND, QM_POW2>;
+    case QM_MM_APPLY: return fused_plane_kernel<T, W, NRB, NCB, NBND, QM_MM_APPLY>;
+    case QM_MM_REDUCE: return fused_plane_kernel<T, W, NRB, NCB, NBND, QM_MM_REDUCE>;
+    case QM_FPQ_LEAN: return fused_plane_kernel<T, W, NRB, NCB, NBND, QM_FPQ_LEAN>;
   }
   return nullptr;
 }
@@ -37,9 +37,11 @@ template <typename T>
 cudaError_t launch_t(int hw, int stride, int qm, const FusedArgs &a, const PlaneCfg &c, cudaStream_t stream) {
   PlaneKernel kern = nullptr;
   if (stride == 1) {
-    if (hw == 7) kern = pick_s1<T, 7, 1, 1>(qm);
-    else if (hw == 14) kern = pick_s1<T, 14, 2, 1>(qm);
-    else if (hw == 28) kern = pick_s1<T, 14, 4, 2>(qm);
+    if (hw == 7) kern = pick_s1<T, 7, 1, 1, 1>(qm);
+    else if (hw == 14) kern = pick_s1<T, 14, 2, 1, 1>(qm);
+    else if (hw == 28) kern = pick_s1<T, 14, 4, 2, 1>(qm);
+    else if (hw == 56) kern = pick_s1<T, 14, 8, 4, 1>(qm);
+    else if (hw == 112) kern = pick_s1<T, 14, 4, 8, 4>(qm);
   } else if (stride == 2) {
     if (hw == 14) kern = pick_s2<T, 1>(qm);
     else if (hw == 28) kern = pick_s2<T, 2>(qm);

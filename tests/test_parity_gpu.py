@@ -13,8 +13,8 @@ from dwbnq import ops, workloads
 
 pytestmark = pytest.mark.gpu
 
-PATHS = [L.PATH_AUTO, L.PATH_COOP, L.PATH_RAW, L.PATH_GENERIC]
-PATH_IDS = ["auto", "coop", "raw", "generic"]
+PATHS = [L.PATH_AUTO, L.PATH_TMA, L.PATH_COOP, L.PATH_RAW, L.PATH_GENERIC]
+PATH_IDS = ["auto", "tma", "coop", "raw", "generic"]
 
 
 @pytest.fixture(autouse=True)
@@ -330,8 +330,8 @@ SMALL_QUANTS = [None,
 SMALL_QUANT_IDS = ["none", "fpq_lean", "fpq_signed", "fpq_0.3", "pow2", "minmax"]
 
 
-SMALL_SHAPES = [(7, 1), (14, 1), (28, 1), (14, 2), (28, 2)]
-SMALL_SHAPE_IDS = ["7x7s1", "14x14s1", "28x28s1", "14x14s2", "28x28s2"]
+SMALL_SHAPES = [(7, 1), (14, 1), (28, 1), (56, 1), (112, 1), (14, 2), (28, 2)]
+SMALL_SHAPE_IDS = ["7x7s1", "14x14s1", "28x28s1", "56x56s1", "112x112s1", "14x14s2", "28x28s2"]
 
 
 @pytest.mark.parametrize("quant", SMALL_QUANTS, ids=SMALL_QUANT_IDS)
@@ -341,7 +341,7 @@ def test_small_plane_kernel(oracle, cuda_device, dtype, hw, stride, quant):
     """Full tiles, a ragged last tile (37 planes: the 7x7 fp32 remainder is not a multiple of
     16 bytes, so its tile is copied by the threads) and a batch smaller than one tile."""
     rng = np.random.default_rng(100 + hw + stride)
-    for n, c in ((5, 64), (1, 37), (1, 3)):
+    for n, c in (((5, 64) if hw <= 28 else (2, 24)), (1, 37), (1, 3)):
         spec = workloads.LayerSpec("small", n, c, hw, hw, 3, stride, 1, None)
         d = _rand_layer(rng, n, c, hw, hw, 3)
         if quant and quant["kind"] == "minmax":
