@@ -48,16 +48,18 @@ def measured_peak():
         return FALLBACK_HBM_GBS, "fallback"
 
 
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum, ncu) of the 17 launches of one cfg1
-# fp32 step captured at batch 64 (profiles/cfg1_step_dram_traffic_batch64.md). Traffic is
-# proportional to the batch, so a step at batch B is this figure times B / 64.
-CFG1_F32_TRAFFIC_BATCH64 = None
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum, one ncu pass per launch) of the 17
+# launches of one cfg1 fp32 step at the bench batch of 256 images: 3832.3 MB read (1.000x the
+# algorithmic input bytes) + 1565.8 MB written before the kernels ended (the remaining
+# output lines are still in the 126 MB L2 then and are written back later). Traffic is
+# proportional to the batch.
+CFG1_F32_TRAFFIC_BATCH256 = 3832271360 + 1565840640
 
 
 def measured_traffic(args, batch):
-    if CFG1_F32_TRAFFIC_BATCH64 is None or args.workload != "cfg1" or args.dtype != "f32" or args.only_layers:
+    if args.workload != "cfg1" or args.dtype != "f32" or args.only_layers or args.force_path is not None:
         return None
-    return CFG1_F32_TRAFFIC_BATCH64 * batch / 64.0
+    return CFG1_F32_TRAFFIC_BATCH256 * batch / 256.0
 
 
 class ClockSampler:
@@ -116,6 +118,15 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def host_threads():
+    """Cores this process may run on (torchrun sets OMP_NUM_THREADS=1, which the oracle's
+    explicit thread count overrides)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def make_cpu_pass(specs, sample_n, nthreads):
     """Returns a function that runs the unfused CPU chain (dw-conv, BN, quantizer: three
     passes, like the reference's CPU functions) of the whole layer stack once on
@@ -158,7 +169,7 @@ def run_reference(args):
     from oracle import oracle
     oracle.build()
     specs = workloads.workload(args.workload, args.batch)
-    nthreads = oracle.max_threads()
+    nthreads = host_threads()
     sample_n = args.cpu_sample
     one_pass = make_cpu_pass(specs, sample_n, nthreads)
     times = []
@@ -366,7 +377,7 @@ def run_own(args):
         achieved = bytes_per_step / (ms_per_step / 1e3) / 1e9
         from oracle import oracle
         oracle.build()
-        nthreads = oracle.max_threads()
+        nthreads = host_threads()
         cpu_ips, cpu_dt, cpu_passes = (0.0, 0.0, 0) if args.no_cpu else cpu_stack_images_per_s(
             specs, args.cpu_sample, nthreads, args.cpu_seconds)
         bytes_per_image = sum(s.algorithmic_bytes(4, 1) for s in specs)
