@@ -51,11 +51,12 @@ __host__ __device__ constexpr size_t plane_smem_bytes(int W, int NRB, int NCB, i
   s = (s + 15) / 16 * 16;
   return s + 16;
 }
-// stride 2: input tile | output tile | mbarrier
-__host__ __device__ constexpr size_t plane_s2_smem_bytes(int NB, int elem_size) {
-  size_t s = (size_t)(32 / (NB * NB)) * (14 * NB) * (14 * NB) * elem_size;
+// stride 2: input tile (with the row above a band) | output tile | mbarrier
+__host__ __device__ constexpr size_t plane_s2_smem_bytes(int NRB, int NCB, int NBND, int elem_size) {
+  const int P = 32 / (NRB * NCB);
+  size_t s = (size_t)P * (14 * NRB + (NBND > 1 ? 1 : 0)) * (14 * NCB) * elem_size;
   s = (s + 15) / 16 * 16;
-  s += (size_t)(32 / (NB * NB)) * (7 * NB) * (7 * NB) * elem_size;
+  s += (size_t)P * (7 * NRB) * (7 * NCB) * elem_size;
   s = (s + 15) / 16 * 16;
   return s + 16;
 }
@@ -173,6 +174,22 @@ __device__ __forceinline__ void plane_reduce_minmax(const QuantArgs &q, int ch, 
     atomicMin(q.mm_enc_min + ch, enc_ordered(lo));
     atomicMax(q.mm_enc_max + ch, enc_ordered(hi));
   }
+}
+
+// One tap on the accumulator. The contract rounds the product and the sum separately. For
+// binary16 inputs the fp32 product of two 11-bit significands is exact (22 bits, and the
+// exponent range of half squared stays inside fp32's normal range), so the fused
+// multiply-add RN(w * x + acc) is bit for bit RN(RN(w * x) + acc) and one instruction does
+// the work of two.
+template <typename T>
+__device__ __forceinline__ float tap_add(float acc, float w, float x) {
+  if (sizeof(T) == 2) return __fmaf_rn(w, x, acc);
+  return __fadd_rn(acc, __fmul_rn(w, x));
+}
+template <typename T>
+__device__ __forceinline__ f32x2 tap_add2(f32x2 acc, f32x2 w, f32x2 x, f32x2 nz) {
+  if (sizeof(T) == 2) return fma2(w, x, acc);
+  return add2(acc, mul2(w, x, nz));
 }
 
 // ---- stride 1 ---------------------------------------------------------------------------
@@ -321,9 +338,9 @@ __global__ void __launch_bounds__(32, 16)
 #pragma unroll
       for (int p = 0; p < NP; ++p) {
         f32x2 v = init ? bias2 : acc[p];
-        v = add2(v, mul2(w2[ky * 3 + 0], L[p], nz));
-        v = add2(v, mul2(w2[ky * 3 + 1], E[p], nz));
-        if (!(LAST_L_ZERO && p == NP - 1)) v = add2(v, mul2(w2[ky * 3 + 2], L[p + 1], nz));
+        v = tap_add2<T>(v, w2[ky * 3 + 0], L[p], nz);
+        v = tap_add2<T>(v, w2[ky * 3 + 1], E[p], nz);
+        if (!(LAST_L_ZERO && p == NP - 1)) v = tap_add2<T>(v, w2[ky * 3 + 2], L[p + 1], nz);
         acc[p] = v;
       }
     };
@@ -386,38 +403,52 @@ __global__ void __launch_bounds__(32, 16)
 }
 
 // ---- stride 2 ---------------------------------------------------------------------------
-// Thread block of 14 x 14 inputs = 7 x 7 outputs; the plane is NB x NB blocks (14x14 or
-// 28x28 inputs). Taps are scalar (the two outputs of a packed pair would need operands two
+// Thread block of 14 x 14 inputs = 7 x 7 outputs; a tile is NRB x NCB blocks: whole planes
+// (NBND == 1) or one band of 14 * NRB full-width input rows plus the row above it
+// (NBND > 1). Taps are scalar (the two outputs of a packed pair would need operands two
 // elements apart, which costs more moves than it saves), BN is packed. The traffic per
 // output is 2.5 times that of stride 1, so the arithmetic has issue slots to spare.
-template <typename T, int NB, int QM>
+template <typename T, int NRB, int NCB, int NBND, int QM>
 __global__ void __launch_bounds__(32, 7)
     fused_plane_s2_kernel(const __grid_constant__ FusedArgs a, const PlaneCfg c) {
+  static_assert(NBND == 1 || NRB * NCB == 32, "a band is one warp's worth of blocks");
   constexpr int BW = 14;             // input block edge
   constexpr int OB = 7;              // output block edge
-  constexpr int PW = BW * NB;        // input plane edge
-  constexpr int PE = PW * PW;
-  constexpr int OW = OB * NB;        // output plane edge
-  constexpr int OE = OW * OW;
-  constexpr int TPP = NB * NB;
+  constexpr int PW = BW * NCB;       // input plane width
+  constexpr int TBI = BW * NRB;      // input rows per tile
+  constexpr int H = TBI * NBND;      // input plane height
+  constexpr int PE = H * PW;
+  constexpr int HALO = NBND > 1 ? 1 : 0;
+  constexpr int TE = (TBI + HALO) * PW;  // shared-memory elements per plane of the input tile
+  constexpr int OW = OB * NCB;       // output plane width
+  constexpr int TBO = OB * NRB;      // output rows per tile
+  constexpr int OE = TBO * NBND * OW;
+  constexpr int OTE = TBO * OW;      // elements per plane of the output tile
+  constexpr int TPP = NRB * NCB;
   constexpr int P = 32 / TPP;
   constexpr int NPO = (OB + 1) / 2;  // output pairs (one dummy lane)
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
   T *tile = reinterpret_cast<T *>(smem_raw);
-  constexpr size_t tile_bytes = ((size_t)P * PE * sizeof(T) + 15) / 16 * 16;
+  constexpr size_t tile_bytes = ((size_t)P * TE * sizeof(T) + 15) / 16 * 16;
   T *otile = reinterpret_cast<T *>(smem_raw + tile_bytes);
-  constexpr size_t otile_bytes = ((size_t)P * OE * sizeof(T) + 15) / 16 * 16;
+  constexpr size_t otile_bytes = ((size_t)P * OTE * sizeof(T) + 15) / 16 * 16;
   unsigned long long *bar = reinterpret_cast<unsigned long long *>(smem_raw + tile_bytes + otile_bytes);
 
   const int lane = threadIdx.x;
   const int n_planes = (int)(a.n * a.OC);
-  const int plane0 = blockIdx.x * P;
+  const int plane0 = (NBND > 1 ? blockIdx.x / NBND : blockIdx.x) * P;
+  const int band = NBND > 1 ? blockIdx.x % NBND : 0;
+  const int r0 = band * TBI;  // first input row of the tile
   const int pv = min(P, n_planes - plane0);
-  const T *x = static_cast<const T *>(a.x);
   T *y = static_cast<T *>(a.y);
-  const unsigned int bytes = (unsigned int)(pv * PE * sizeof(T));
-  const unsigned int obytes = (unsigned int)(pv * OE * sizeof(T));
+  const int in_first = NBND > 1 ? max(r0 - 1, 0) : 0;
+  const int in_rows = NBND > 1 ? r0 + TBI - in_first : pv * H;
+  const T *in_src = static_cast<const T *>(a.x) + (long long)plane0 * PE + (long long)in_first * PW;
+  T *in_dst = tile + (NBND > 1 ? (in_first - (r0 - 1)) * PW : 0);
+  const unsigned int bytes = (unsigned int)(in_rows * PW * sizeof(T));
+  const int out_elems = (NBND > 1 ? 1 : pv) * OTE;
+  const unsigned int obytes = (unsigned int)(out_elems * sizeof(T));
   const bool async_tile = c.bulk != 0 && (bytes % 16) == 0 && (obytes % 16) == 0;
 
   if (lane == 0) {
@@ -425,17 +456,17 @@ __global__ void __launch_bounds__(32, 7)
     mbar_fence_init();
     if (async_tile) {
       mbar_expect_tx(bar, bytes);
-      bulk_load_1d(tile, x + (long long)plane0 * PE, bytes, bar);
+      bulk_load_1d(in_dst, in_src, bytes, bar);
     }
   }
 
   const int pl = lane / TPP;
-  const int rb = (lane / NB) % NB;
-  const int cb = lane % NB;
+  const int rb = (lane / NCB) % NRB;
+  const int cb = lane % NCB;
   const bool active = pl < pv;
   const int plane = active ? plane0 + pl : n_planes - 1;
   const int ch = plane % a.OC;
-  const bool has_left = NB > 1 && cb > 0;
+  const bool has_left = NCB > 1 && cb > 0;
   const f32x2 nz = negzero2();
   float wr[9];
   bool exact = false;
@@ -456,9 +487,8 @@ __global__ void __launch_bounds__(32, 7)
   const MmCoef mm = load_mm<QM>(a, ch);
 
   if (!async_tile) {
-    const int n = pv * PE;
-    const T *src = x + (long long)plane0 * PE;
-    for (int i = lane; i < n; i += 32) tile[i] = src[i];
+    const int n = in_rows * PW;
+    for (int i = lane; i < n; i += 32) in_dst[i] = in_src[i];
   }
   __syncwarp();
   if (async_tile && !mbar_wait_bounded(bar, 0)) {
@@ -466,15 +496,15 @@ __global__ void __launch_bounds__(32, 7)
     return;
   }
 
-  const T *rows = tile + pl * PE + rb * (BW * PW) + cb * BW;  // this thread's 14 x 14 inputs
-  T *orows = otile + pl * OE + rb * (OB * OW) + cb * OB;      // its 7 x 7 outputs
+  const T *rows = tile + pl * TE + (HALO + rb * BW) * PW + cb * BW;  // this thread's 14 x 14 inputs
+  T *orows = otile + pl * OTE + rb * (OB * OW) + cb * OB;            // its 7 x 7 outputs
   float lo = __uint_as_float(0x7f800000u), hi = __uint_as_float(0xff800000u);
 
   // xv[0] = the column left of the block, xv[1..14] = the block's row
   auto load_row = [&](const T *p, bool valid, float *xv) {
     plane_load_row<T, BW>(p, valid, xv + 1);
     xv[0] = 0.0f;
-    if (NB > 1) {
+    if (NCB > 1) {
       if (valid && has_left) xv[0] = Elem<T>::to_f32(p[-1]);
     }
   };
@@ -482,9 +512,9 @@ __global__ void __launch_bounds__(32, 7)
 #pragma unroll
     for (int j = 0; j < OB; ++j) {
       float v = init ? bv : acc[j];
-      v = __fadd_rn(v, __fmul_rn(wr[ky * 3 + 0], xv[2 * j]));
-      v = __fadd_rn(v, __fmul_rn(wr[ky * 3 + 1], xv[2 * j + 1]));
-      v = __fadd_rn(v, __fmul_rn(wr[ky * 3 + 2], xv[2 * j + 2]));
+      v = tap_add<T>(v, wr[ky * 3 + 0], xv[2 * j]);
+      v = tap_add<T>(v, wr[ky * 3 + 1], xv[2 * j + 1]);
+      v = tap_add<T>(v, wr[ky * 3 + 2], xv[2 * j + 2]);
       acc[j] = v;
     }
   };
@@ -492,12 +522,12 @@ __global__ void __launch_bounds__(32, 7)
   float acc[OB];
   {
     // the row above the block: zero above the plane (skipped when no block has a row above)
-    if (NB == 1) {
+    if (NRB == 1 && NBND == 1) {
 #pragma unroll
       for (int j = 0; j < OB; ++j) acc[j] = bv;
     } else {
       float xv[BW + 2];
-      load_row(rows - PW, rb > 0, xv);
+      load_row(rows - PW, r0 + rb * BW > 0, xv);
       taps(acc, xv, 0, true);
     }
   }
@@ -530,22 +560,21 @@ __global__ void __launch_bounds__(32, 7)
   }
 
   if (exact && active)
-    plane_exact_block<T, QM>(a, plane, ch, rb * OB, cb * OB, OB, OB, orows, OW, mm, &lo, &hi);
+    plane_exact_block<T, QM>(a, plane, ch, band * TBO + rb * OB, cb * OB, OB, OB, orows, OW, mm, &lo, &hi);
 
   if (QM == QM_MM_REDUCE) {
     plane_reduce_minmax<TPP>(a.q, ch, lo, hi, active, lane);
     return;
   }
 
-  T *dst = y + (long long)plane0 * OE;
+  T *dst = y + (long long)plane0 * OE + (long long)band * OTE;
   if (async_tile) {
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) bulk_store_1d_and_wait(dst, otile, obytes);
   } else {
     __syncwarp();
-    const int n = pv * OE;
-    for (int i = lane; i < n; i += 32) dst[i] = otile[i];
+    for (int i = lane; i < out_elems; i += 32) dst[i] = otile[i];
   }
 }
 
@@ -570,13 +599,15 @@ __host__ inline PlaneGeom plane_geom(int h, int w, int stride) {
   } else if (stride == 2) {
     if (w == 14) g = {1, 1, 14, 1, 1};
     else if (w == 28) g = {4, 1, 14, 2, 2};
+    else if (w == 56) g = {16, 1, 14, 4, 4};
+    else if (w == 112) g = {32, 2, 14, 4, 8};
   }
   return g;
 }
 __host__ inline size_t plane_launch_smem(int hw, int stride, int elem_size) {
   const PlaneGeom g = plane_geom(hw, hw, stride);
   if (stride == 1) return plane_smem_bytes(g.w, g.nrb, g.ncb, g.bands, elem_size);
-  return plane_s2_smem_bytes(hw / 14, elem_size);
+  return plane_s2_smem_bytes(g.nrb, g.ncb, g.bands, elem_size);
 }
 
 }  // namespace dwbnq

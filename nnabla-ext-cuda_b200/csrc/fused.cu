@@ -160,8 +160,8 @@ int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan
     TileCfg &c = plan->cfg;
     c.P = 32 / pg.tpp;
     c.R = kPlaneRows;
-    c.n_rb = s == 1 ? d.h / kPlaneRows : d.h / 14;
-    c.n_strips = s == 1 ? (d.w + 13) / 14 : d.w / 14;
+    c.n_rb = pg.nrb;
+    c.n_strips = pg.ncb;
     c.n_row_tiles = pg.bands;
     c.TH = Ho / pg.bands;
     c.TR = d.h;

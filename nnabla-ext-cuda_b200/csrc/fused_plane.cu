@@ -20,15 +20,15 @@ PlaneKernel pick_s1(int qm) {
   return nullptr;
 }
 
-template <typename T, int NB>
+template <typename T, int NRB, int NCB, int NBND>
 PlaneKernel pick_s2(int qm) {
   switch (qm) {
-    case QM_NONE: return fused_plane_s2_kernel<T, NB, QM_NONE>;
-    case QM_FPQ: return fused_plane_s2_kernel<T, NB, QM_FPQ>;
-    case QM_POW2: return fused_plane_s2_kernel<T, NB, QM_POW2>;
-    case QM_MM_APPLY: return fused_plane_s2_kernel<T, NB, QM_MM_APPLY>;
-    case QM_MM_REDUCE: return fused_plane_s2_kernel<T, NB, QM_MM_REDUCE>;
-    case QM_FPQ_LEAN: return fused_plane_s2_kernel<T, NB, QM_FPQ_LEAN>;
+    case QM_NONE: return fused_plane_s2_kernel<T, NRB, NCB, NBND, QM_NONE>;
+    case QM_FPQ: return fused_plane_s2_kernel<T, NRB, NCB, NBND, QM_FPQ>;
+    case QM_POW2: return fused_plane_s2_kernel<T, NRB, NCB, NBND, QM_POW2>;
+    case QM_MM_APPLY: return fused_plane_s2_kernel<T, NRB, NCB, NBND, QM_MM_APPLY>;
+    case QM_MM_REDUCE: return fused_plane_s2_kernel<T, NRB, NCB, NBND, QM_MM_REDUCE>;
+    case QM_FPQ_LEAN: return fused_plane_s2_kernel<T, NRB, NCB, NBND, QM_FPQ_LEAN>;
   }
   return nullptr;
 }
@@ -43,8 +43,10 @@ cudaError_t launch_t(int hw, int stride, int qm, const FusedArgs &a, const Plane
     else if (hw == 56) kern = pick_s1<T, 14, 8, 4, 1>(qm);
     else if (hw == 112) kern = pick_s1<T, 14, 4, 8, 4>(qm);
   } else if (stride == 2) {
-    if (hw == 14) kern = pick_s2<T, 1>(qm);
-    else if (hw == 28) kern = pick_s2<T, 2>(qm);
+    if (hw == 14) kern = pick_s2<T, 1, 1, 1>(qm);
+    else if (hw == 28) kern = pick_s2<T, 2, 2, 1>(qm);
+    else if (hw == 56) kern = pick_s2<T, 4, 4, 1>(qm);
+    else if (hw == 112) kern = pick_s2<T, 4, 8, 2>(qm);
   }
   if (!kern) return cudaErrorInvalidValue;
   const size_t smem = plane_launch_smem(hw, stride, sizeof(T));

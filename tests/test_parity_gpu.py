@@ -330,8 +330,8 @@ SMALL_QUANTS = [None,
 SMALL_QUANT_IDS = ["none", "fpq_lean", "fpq_signed", "fpq_0.3", "pow2", "minmax"]
 
 
-SMALL_SHAPES = [(7, 1), (14, 1), (28, 1), (56, 1), (112, 1), (14, 2), (28, 2)]
-SMALL_SHAPE_IDS = ["7x7s1", "14x14s1", "28x28s1", "56x56s1", "112x112s1", "14x14s2", "28x28s2"]
+SMALL_SHAPES = [(7, 1), (14, 1), (28, 1), (56, 1), (112, 1), (14, 2), (28, 2), (56, 2), (112, 2)]
+SMALL_SHAPE_IDS = ["7x7s1", "14x14s1", "28x28s1", "56x56s1", "112x112s1", "14x14s2", "28x28s2", "56x56s2", "112x112s2"]
 
 
 @pytest.mark.parametrize("quant", SMALL_QUANTS, ids=SMALL_QUANT_IDS)
