@@ -203,6 +203,68 @@ def workload_name(args):
     return names[args.workload]
 
 
+def run_standalone_ops(args):
+    """The five standalone operators on one [B, 96, 56, 56] activation (308 MB at the default
+    B = 256, fp32): per-operator time and algorithmic GB/s (2 * B bytes per element: read
+    once, write once). One JSON line in the bench format; `layers` holds the operators."""
+    import torch
+    from dwbnq import ops
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the dwbnq path has no CPU fallback")
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    half = args.dtype == "f16"
+    tdtype = torch.float16 if half else torch.float32
+    itemsize = 2 if half else 4
+    n, c, hw = args.batch, 96, 56
+    g = torch.Generator(device="cpu").manual_seed(0)
+    x = torch.randn((n, c, hw, hw), generator=g, dtype=torch.float32).to(device).to(tdtype)
+    w = (torch.randn((c, 3, 3), generator=g) / 3).to(device).to(tdtype)
+    vec = lambda lo, hi: (torch.rand(c, generator=g) * (hi - lo) + lo).to(device).to(tdtype)
+    b, mean, var, gamma, beta = vec(-.3, .3), vec(-.3, .3), vec(.5, 1.5), vec(.8, 1.2), vec(-.3, .3)
+    y = torch.empty_like(x)
+    qr_min, qr_max = torch.zeros(c, device=device, dtype=tdtype), torch.ones(c, device=device, dtype=tdtype)
+    ql_min, ql_max = torch.zeros(c, device=device, dtype=tdtype), torch.full((c,), 255.0, device=device, dtype=tdtype)
+    ws = ops.workspace(c, device)
+    calls = [
+        ("DepthwiseConvolution 3x3 s1", lambda: ops.depthwise_convolution(x, w, b, 1, (1, 1), (1, 1), out=y)),
+        ("BatchNormalization(batch_stat=False)", lambda: ops.batch_normalization(x, beta, gamma, mean, var, out=y)),
+        ("FixedPointQuantize(sign,n=8,2^-4)", lambda: ops.fixed_point_quantize(x, True, 8, 2.0 ** -4, out=y)),
+        ("Pow2Quantize(sign,with_zero,n=8,m=1)", lambda: ops.pow2_quantize(x, True, True, 8, 1, out=y)),
+        ("MinMaxQuantize(per-channel, x_min_max)", lambda: ops.min_max_quantize(
+            x, qr_min, qr_max, ql_min, ql_max, x_min_max=True, ws=ws, out=y)),
+    ]
+    peak, peak_kind = measured_peak()
+    rows = []
+    total_ms = 0.0
+    for name, fn in calls:
+        for _ in range(args.warmup):
+            fn()
+        ts = []
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(max(3, min(args.steps, 20))):
+            flush_l2(torch, device)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        ms = float(np.median(ts))
+        total_ms += ms
+        rows.append({"layer": name, "ms": ms, "gbs": 2 * x.numel() * itemsize / ms / 1e6})
+    ops.check_device_flag()
+    bytes_all = 2 * x.numel() * itemsize * len(calls)
+    achieved = bytes_all / total_ms / 1e6
+    line = {"metric": "images_per_s", "value": n / (total_ms / 1e3), "unit": "images/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
+            "config": {"workload": "ops: the five standalone operators on [%d,%d,%d,%d]" % (n, c, hw, hw),
+                       "l2": "L2 flushed before every timed launch"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_kind": peak_kind}, "gpu_launches": None, "layers": rows}
+    print(json.dumps(line), flush=True)
+
+
 def run_own(args):
     import torch
     import torch.distributed as dist
@@ -431,7 +493,7 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
-    ap.add_argument("--workload", default="cfg1", choices=["cfg0", "cfg1", "cfg2", "cfg3", "cfg4"])
+    ap.add_argument("--workload", default="cfg1", choices=["cfg0", "cfg1", "cfg2", "cfg3", "cfg4", "ops"])
     ap.add_argument("--batch", type=int, default=None, help="images per GPU (default: the workload's batch)")
     ap.add_argument("--dtype", default="f32", choices=["f32", "f16"])
     ap.add_argument("--cpu-sample", type=int, default=None, help="images per CPU-baseline pass")
@@ -446,14 +508,16 @@ def main():
     ap.add_argument("--force-path", type=int, default=None, help="profiling only: kernel family 0..4")
     ap.add_argument("--tune", default="", help="profiling only: planner override P,row_blocks,threads,rows_per_patch")
     args = ap.parse_args()
-    defaults = {"cfg0": 32, "cfg1": 256, "cfg2": 128, "cfg3": 512, "cfg4": 256}
+    defaults = {"cfg0": 32, "cfg1": 256, "cfg2": 128, "cfg3": 512, "cfg4": 256, "ops": 256}
     if args.batch is None:
         args.batch = defaults[args.workload]
     if args.warmup < 3:
         args.warmup = 3
     if args.cpu_sample is None:
-        args.cpu_sample = {"cfg0": 32, "cfg1": 64, "cfg2": 32, "cfg3": 128, "cfg4": 64}[args.workload]
-    if args.impl == "reference":
+        args.cpu_sample = {"cfg0": 32, "cfg1": 64, "cfg2": 32, "cfg3": 128, "cfg4": 64, "ops": 0}[args.workload]
+    if args.workload == "ops":
+        run_standalone_ops(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_own(args)

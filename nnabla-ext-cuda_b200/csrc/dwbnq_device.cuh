@@ -31,6 +31,7 @@ struct QuantArgs {
   float p_max, p_min, prune_thr;
   int p_sign, p_with_zero;
   int p_window;               // |mantissa - sqrt2 mantissa| beyond which no table look-up is needed
+  int p_fast;                 // p_min >= 2^-125: zeros and subnormals need no exact exponent
   const uint32_t *p_table;    // 277 thresholds, device memory
   // MinMaxQuantize second pass: per-channel fp32 arrays in the workspace.
   const float *mm_scale, *mm_lo, *mm_hi;
@@ -178,30 +179,40 @@ __device__ __forceinline__ float pow2_of_int(int k) {
   if (k >= -149) return __uint_as_float(1u << (k + 149));
   return 0.0f;
 }
+// 2^round(log2f(a)) for a bit pattern that needs the exact treatment: zero, subnormal,
+// infinity / NaN, or a mantissa within `window` of the rounding threshold. Out of line: rare.
+static __device__ __noinline__ float pow2_round_exact(unsigned int a, const uint32_t *table, int window) {
+  if (a >= 0x7f800000u) return __uint_as_float(a);  // +inf stays +inf (clamped later); NaN passes through
+  if (a == 0u) return 0.0f;                          // log2f(0) = -inf -> 2^-inf = 0
+  int e;
+  bool up;
+  if (a >= 0x00800000u) {
+    e = (int)(a >> 23) - 127;
+    const int d = (int)(a & 0x007fffffu) - 0x3504f3;  // distance to the sqrt(2) mantissa
+    if (d > window) up = true;
+    else if (d < -window) up = false;
+    else up = a >= __ldg(table + (e + 149));
+  } else {
+    e = 31 - __clz(a) - 149;
+    up = a >= __ldg(table + (e + 149));
+  }
+  return pow2_of_int(e + (up ? 1 : 0));
+}
+
 __device__ __forceinline__ float pow2_apply(float x, const QuantArgs &p) {
   const unsigned int a = __float_as_uint(x) & 0x7fffffffu;
   const float ax = __uint_as_float(a);
   const bool neg = x < 0.0f;
-  float q;
-  if (a >= 0x7f800000u) {
-    q = ax;  // +inf stays +inf (clamped below); NaN fails every compare and passes through
-  } else if (a == 0u) {
-    q = 0.0f;  // log2f(0) = -inf -> 2^-inf = 0
-  } else {
-    int e;
-    bool up;
-    if (a >= 0x00800000u) {
-      e = (int)(a >> 23) - 127;
-      const int d = (int)(a & 0x007fffffu) - 0x3504f3;  // distance to the sqrt(2) mantissa
-      if (d > p.p_window) up = true;
-      else if (d < -p.p_window) up = false;
-      else up = a >= __ldg(p.p_table + (e + 149));
-    } else {
-      e = 31 - __clz(a) - 149;
-      up = a >= __ldg(p.p_table + (e + 149));
-    }
-    q = pow2_of_int(e + (up ? 1 : 0));
-  }
+  // Common case, branch-free: away from the threshold the rounded exponent is e + 1 exactly
+  // when the mantissa is above sqrt(2)'s, i.e. adding (2^23 - 0x3504f3) carries into the
+  // exponent field. With p_min a normal number (p_fast) zeros and subnormals need no care
+  // either: whatever tiny power of two comes out is below p_min and the rules below decide
+  // on |x| alone. Infinity carries to infinity. Only NaN and the threshold window are left.
+  const int d = (int)(a & 0x007fffffu) - 0x3504f3;
+  const bool rare = (unsigned int)(d + p.p_window) <= 2u * (unsigned int)p.p_window || a > 0x7f800000u ||
+                    !p.p_fast;
+  float q = __uint_as_float((a + 0x004afb0du) & 0x7f800000u);
+  if (rare) q = pow2_round_exact(a, p.p_table, p.p_window);
   if (q > p.p_max) {
     q = p.p_max;
   } else if (q < p.p_min && p.p_with_zero) {
@@ -330,6 +341,14 @@ __device__ __forceinline__ BnPacked make_bn_packed(const BnCoef &c, f32x2 nz) {
   return b;
 }
 
+// The IEEE quotients of the out-of-range path, out of line: the path is cold and the inline
+// expansion of a correctly rounded division is several times the size of the whole BN step.
+static __device__ __noinline__ f32x2 bn_div_cold(f32x2 a, float stdvar) {
+  float lo, hi;
+  unpack2(a, lo, hi);
+  return pack2(__fdiv_rn(lo, stdvar), __fdiv_rn(hi, stdvar));
+}
+
 // In-place BN of NP pairs.
 template <int NP>
 __device__ __forceinline__ void bn_apply_packed(f32x2 *v, const BnPacked &b) {
@@ -350,11 +369,7 @@ __device__ __forceinline__ void bn_apply_packed(f32x2 *v, const BnPacked &b) {
   }
   if (!(mn > b.glo && mx < DWBNQ_DIV_GUARD_HI)) {
 #pragma unroll
-    for (int p = 0; p < NP; ++p) {
-      float lo, hi;
-      unpack2(a[p], lo, hi);
-      v[p] = pack2(__fdiv_rn(lo, b.stdvar), __fdiv_rn(hi, b.stdvar));
-    }
+    for (int p = 0; p < NP; ++p) v[p] = bn_div_cold(a[p], b.stdvar);
   }
 #pragma unroll
   for (int p = 0; p < NP; ++p) v[p] = add2(v[p], b.beta);

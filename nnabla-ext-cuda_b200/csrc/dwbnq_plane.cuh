@@ -43,12 +43,14 @@ constexpr int kPlaneRows = 7;  // rows per thread
 
 // Stash row of a thread: [2 unused | left halo | W elements | right halo | pad], even size.
 __host__ __device__ constexpr int plane_stash_elems(int W) { return (W + 4 + 1) / 2 * 2; }
-// stride 1: tile | stash (NRB > 1) | mbarrier
-__host__ __device__ constexpr size_t plane_smem_bytes(int W, int NRB, int NCB, int NBND, int elem_size) {
-  size_t s = (size_t)(32 / (NRB * NCB)) * (kPlaneRows * NRB + (NBND > 1 ? 2 : 0)) * (W * NCB) * elem_size;
+// stride 1: tile | stash (NRB > 1) | weight pairs (5x5) | mbarrier
+__host__ __device__ constexpr size_t plane_smem_bytes(int K, int W, int NRB, int NCB, int NBND, int elem_size) {
+  const int P = 32 / (NRB * NCB);
+  size_t s = (size_t)P * (kPlaneRows * NRB + (NBND > 1 ? 2 * (K / 2) : 0)) * (W * NCB) * elem_size;
   s = (s + 15) / 16 * 16;
-  if (NRB > 1) s += (size_t)32 * plane_stash_elems(W) * elem_size;
+  if (NRB > 1) s += (size_t)32 * (K / 2) * plane_stash_elems(W) * elem_size;
   s = (s + 15) / 16 * 16;
+  if (K == 5) s += (size_t)P * 25 * 8;  // weight pairs
   return s + 16;
 }
 // stride 2: input tile (with the row above a band) | output tile | mbarrier
@@ -402,6 +404,302 @@ __global__ void __launch_bounds__(32, 16)
   }
 }
 
+// ---- stride 1, K x K ------------------------------------------------------------------
+// The same scheme for a K x K convolution (K = 3 or 5, pad K/2; instantiated for 5x5, the
+// 3x3 case keeps the hand-scheduled kernel above, which is a few percent faster): thread
+// block of R x W outputs; a tile is NRB
+// blocks high and NCB blocks wide. With NBND == 1 the tile is a whole plane (and a CTA takes
+// 32 / (NRB * NCB) planes); with NBND > 1 a plane is cut into NBND bands of full-width rows,
+// one band per CTA, and the copy brings the K/2 rows above and below the band along (they
+// are contiguous with it).
+//
+// Step k loads input row k - K/2 of the block and adds its ky = m taps to output row k - m
+// for m = K-1 .. 0: output row j starts at step j (from the bias) and is finished, BN'd,
+// quantized and stored at step j + K - 1. Row j lives in accumulator set j mod (K-1): the
+// row finished in a step hands its registers to the row started in the same step, so K-1
+// sets are live and the loop is unrolled K-1 steps per trip to keep the set indices static.
+// Compiled for 16 one-warp CTAs per SM (128 registers).
+template <typename T, int K, int W, int NRB, int NCB, int NBND, int QM>
+__global__ void __launch_bounds__(32, 16)
+    fused_plane_kxk_kernel(const __grid_constant__ FusedArgs a, const PlaneCfg c) {
+  static_assert(K == 3 || K == 5, "3x3 or 5x5");
+  static_assert(NCB == 1 || W % 2 == 0, "column blocks need an even block width");
+  static_assert(K == 3 || W % 2 == 0, "5x5 needs an even block width");
+  static_assert(NBND == 1 || NRB * NCB == 32, "a band is one warp's worth of blocks");
+  constexpr int R = kPlaneRows;
+  constexpr int PAD = K / 2;
+  constexpr int KK = K * K;
+  constexpr int NSET = K - 1;        // live accumulator rows
+  constexpr int NSTEP = R + K - 1;   // input rows a block consumes
+  constexpr int TB = R * NRB;        // rows per tile
+  constexpr int H = TB * NBND;       // plane height
+  constexpr int PW = W * NCB;        // plane width
+  constexpr int PE = H * PW;         // elements per plane
+  constexpr int HALO = NBND > 1 ? PAD : 0;  // row slots above / below the band
+  constexpr int TE = (TB + 2 * HALO) * PW;  // shared-memory elements per plane of the tile
+  constexpr int NP = (W + 1) / 2;    // output pairs per row
+  constexpr int EH = PAD / 2;        // pairs of neighbour columns at even offsets (5x5: 1)
+  constexpr int TPP = NRB * NCB;     // threads per plane
+  constexpr int P = 32 / TPP;        // planes per CTA
+  constexpr int SW = plane_stash_elems(W);
+  constexpr bool W_SMEM = K == 5;    // 5x5: the 25 weight pairs live in shared memory
+  // 5x5: one step in the loop body, accumulator rows shifted by register moves (a fourfold
+  // unrolled body would not fit the instruction cache)
+  constexpr bool ROTATE = K == 5;
+
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  T *tile = reinterpret_cast<T *>(smem_raw);
+  constexpr size_t tile_bytes = ((size_t)P * TE * sizeof(T) + 15) / 16 * 16;
+  T *stash = reinterpret_cast<T *>(smem_raw + tile_bytes);
+  constexpr size_t stash_bytes = NRB > 1 ? ((size_t)32 * PAD * SW * sizeof(T) + 15) / 16 * 16 : 0;
+  f32x2 *wsm = reinterpret_cast<f32x2 *>(smem_raw + tile_bytes + stash_bytes);
+  constexpr size_t wsm_bytes = W_SMEM ? (size_t)P * KK * sizeof(f32x2) : 0;
+  unsigned long long *bar =
+      reinterpret_cast<unsigned long long *>(smem_raw + tile_bytes + stash_bytes + wsm_bytes);
+
+  const int lane = threadIdx.x;
+  const int n_planes = (int)(a.n * a.OC);
+  const int plane0 = (NBND > 1 ? blockIdx.x / NBND : blockIdx.x) * P;
+  const int r0 = NBND > 1 ? (blockIdx.x % NBND) * TB : 0;  // first plane row of the tile
+  const int pv = min(P, n_planes - plane0);
+  T *y = static_cast<T *>(a.y);
+  // what comes in (band: with the rows above / below it that exist) and what goes out
+  const int in_first = NBND > 1 ? max(r0 - PAD, 0) : 0;
+  const int in_rows = NBND > 1 ? min(r0 + TB + PAD, H) - in_first : pv * H;
+  const T *in_src = static_cast<const T *>(a.x) + (long long)plane0 * PE + (long long)in_first * PW;
+  T *in_dst = tile + (NBND > 1 ? (in_first - (r0 - PAD)) * PW : 0);
+  const unsigned int bytes = (unsigned int)(in_rows * PW * sizeof(T));
+  const unsigned int obytes = (unsigned int)((NBND > 1 ? TB : pv * H) * PW * sizeof(T));
+  const bool async_tile = c.bulk != 0 && (bytes % 16) == 0 && (obytes % 16) == 0;
+
+  if (lane == 0) {
+    mbar_init(bar, 1);
+    mbar_fence_init();
+    if (async_tile) {
+      mbar_expect_tx(bar, bytes);
+      bulk_load_1d(in_dst, in_src, bytes, bar);
+    }
+  }
+
+  // ---- this thread's plane, block and per-channel operands (the copy is in flight) -------
+  const int pl = lane / TPP;
+  const int rb = (lane / NCB) % NRB;
+  const int cb = lane % NCB;
+  const bool active = pl < pv;
+  const int plane = active ? plane0 + pl : n_planes - 1;
+  const int ch = plane % a.OC;
+  const bool has_left = NCB > 1 && cb > 0;
+  const bool has_right = NCB > 1 && cb + 1 < NCB;
+  const f32x2 nz = negzero2();
+  f32x2 w2[W_SMEM ? 1 : KK];
+  const f32x2 *wpl = wsm + pl * KK;
+  bool exact = false;
+  {
+    const T *w = static_cast<const T *>(a.w) + (long long)ch * KK;
+    if (W_SMEM) {
+      // every thread checks all weights of its plane; the plane's threads share the stores
+      for (int i = 0; i < KK; ++i) {
+        const float wv = Elem<T>::to_f32(w[i]);
+        exact = exact || !(fabsf(wv) <= 3.402823466e38f);
+        if (i % TPP == lane % TPP) wsm[pl * KK + i] = splat2(wv);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < KK; ++i) {
+        const float wv = Elem<T>::to_f32(w[i]);
+        exact = exact || !(fabsf(wv) <= 3.402823466e38f);
+        w2[i] = splat2(wv);
+        pin(w2[i]);
+      }
+    }
+  }
+  const float bv = a.b ? Elem<T>::to_f32(static_cast<const T *>(a.b)[ch]) : 0.0f;
+  exact = exact || __float_as_uint(bv) == 0x80000000u;
+  f32x2 bias2 = splat2(bv);
+  pin(bias2);
+  BnPacked bnp;
+  if (QM == QM_FPQ_LEAN || a.has_bn) bnp = make_bn_packed(load_bn<T>(a, ch), nz);
+  const MmCoef mm = load_mm<QM>(a, ch);
+
+  if (!async_tile) {
+    const int n = in_rows * PW;
+    for (int i = lane; i < n; i += 32) in_dst[i] = in_src[i];
+  }
+  __syncwarp();  // barrier initialisation, weight pairs and thread-copied data are visible
+  if (async_tile && !mbar_wait_bounded(bar, 0)) {
+    if (a.flag) atomicExch(a.flag, 1);
+    return;
+  }
+
+  // this thread's R x W block, overwritten in place (row pitch PW)
+  T *rows = tile + pl * TE + (HALO + rb * R) * PW + cb * W;
+  // The PAD rows below the block belong to the next thread, which overwrites them early:
+  // keep a copy, laid out like tile rows (left halo at [-PAD..-1], right halo at [W..]).
+  T *my_stash = stash + lane * (PAD * SW) + 2;
+  if (NRB > 1) {
+    if (rb + 1 < NRB) {
+#pragma unroll
+      for (int h = 0; h < PAD; ++h) {
+        const T *below = rows + (R + h) * PW;
+        T *st = my_stash + h * SW;
+        float xv[2 * NP];
+        plane_load_row<T, W>(below, true, xv);
+        plane_store_row<T, W>(st, xv);
+#pragma unroll
+        for (int e = 1; e <= PAD; ++e) {
+          if (has_left) st[-e] = below[-e];
+          if (has_right) st[W - 1 + e] = below[W - 1 + e];
+        }
+      }
+    }
+    __syncwarp();
+  }
+
+  float lo = __uint_as_float(0x7f800000u), hi = __uint_as_float(0xff800000u);
+  f32x2 acc[NSET][NP];
+
+  // u = k mod NSET is a compile-time constant at every call site.
+  auto step = [&](int k, auto uc) {
+    constexpr int u = decltype(uc)::value;
+    const int gi = r0 + rb * R - PAD + k;  // plane row of this step's input row
+    const bool valid = gi >= 0 && gi < H;
+    // rows below the block: the stash, or (last block of a band) the band's extra rows
+    const T *src = (NRB > 1 && k >= R + PAD && rb + 1 < NRB) ? my_stash + (k - R - PAD) * SW
+                                                              : rows + (k - PAD) * PW;
+    // xs[PAD + j] = element j of the row, j = -PAD .. W + PAD - 1 (zeros outside the plane)
+    float xs[2 * NP + 2 * PAD + 1];
+    plane_load_row<T, W>(src, valid, xs + PAD);
+#pragma unroll
+    for (int e = 1; e <= PAD; ++e) {
+      xs[PAD - e] = 0.0f;
+      if (W % 2 == 0) xs[PAD + W - 1 + e] = 0.0f;
+      if (NCB > 1) {
+        if (valid && has_left) xs[PAD - e] = Elem<T>::to_f32(src[-e]);
+        if (valid && has_right) xs[PAD + W - 1 + e] = Elem<T>::to_f32(src[W - 1 + e]);
+      }
+    }
+    if (W % 2 != 0) xs[PAD + W + 1] = 0.0f;
+    // Reads of this step come before any write of this step: rows above the block are the
+    // upper neighbour's last rows (written in its last steps), and a neighbour's edge columns
+    // of this row are overwritten by their owner K-1 steps later.
+    __syncwarp();
+    // single-block planes: rows outside the plane are zero for every lane, their taps are skipped
+    const bool zero_row = NRB == 1 && NBND == 1 && (k < PAD || k >= R + PAD);
+    // pairs of adjacent elements: E[EH + j] = (x[2j], x[2j+1]), L[j] = (x[2j-1], x[2j])
+    f32x2 E[NP + 2 * EH], L[NP + 1];
+#pragma unroll
+    for (int j = -EH; j < NP + EH; ++j) E[EH + j] = pack2(xs[PAD + 2 * j], xs[PAD + 2 * j + 1]);
+#pragma unroll
+    for (int j = 0; j <= NP; ++j) L[j] = pack2(xs[PAD + 2 * j - 1], xs[PAD + 2 * j]);
+    constexpr bool LAST_L_ZERO = (W % 2) != 0;  // odd W (3x3 only): L[NP] = (0, 0)
+
+    // ky = m taps of this input row onto the accumulator row that started m steps ago
+    // (x[2p+d], x[2p+d+1]) for column offset d: even d -> E[p + d/2], odd d -> L[p + (d+1)/2]
+    auto taps = [&](f32x2 *ar, int ky, bool init) {
+      if (W_SMEM) {
+#pragma unroll
+        for (int kx = 0; kx < K; ++kx) {
+          const f32x2 wv = wpl[ky * K + kx];
+          const int d = kx - PAD;
+#pragma unroll
+          for (int p = 0; p < NP; ++p) {
+            const f32x2 xv2 = (d % 2 == 0) ? E[EH + p + d / 2] : L[p + (d + 1) / 2];
+            ar[p] = tap_add2<T>((init && kx == 0) ? bias2 : ar[p], wv, xv2, nz);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int p = 0; p < NP; ++p) {
+          f32x2 v = init ? bias2 : ar[p];
+#pragma unroll
+          for (int kx = 0; kx < K; ++kx) {
+            const int d = kx - PAD;
+            if (LAST_L_ZERO && p == NP - 1 && d == 1) continue;
+            const f32x2 xv2 = (d % 2 == 0) ? E[EH + p + d / 2] : L[p + (d + 1) / 2];
+            v = tap_add2<T>(v, w2[W_SMEM ? 0 : ky * K + kx], xv2, nz);
+          }
+          ar[p] = v;
+        }
+      }
+    };
+
+    if (k >= K - 1) {  // finish output row k - (K-1)
+      f32x2 *fin = acc[ROTATE ? 0 : u];
+      if (!zero_row) taps(fin, K - 1, false);
+      if (QM == QM_FPQ_LEAN || a.has_bn) bn_apply_packed<NP>(fin, bnp);
+      float o[2 * NP];
+#pragma unroll
+      for (int p = 0; p < NP; ++p) unpack2(fin[p], o[2 * p], o[2 * p + 1]);
+      if (QM == QM_MM_REDUCE) {
+#pragma unroll
+        for (int j = 0; j < W; ++j) {
+          lo = fminf(lo, o[j]);
+          hi = fmaxf(hi, o[j]);
+        }
+      } else {
+        plane_quant<QM, W>(o, a.q, mm);
+        if (active) plane_store_row<T, W>(rows + (k - (K - 1)) * PW, o);
+      }
+    }
+#pragma unroll
+    for (int m = K - 2; m >= 1; --m) {  // rows in the middle of their accumulation
+      if (k - m >= 0 && k - m < R && !zero_row)
+        taps(acc[ROTATE ? K - 1 - m : (u - m + NSET * 2) % NSET], m, false);
+    }
+    if (ROTATE) {  // row j moves from set s+1 to set s; the new row takes the last set
+#pragma unroll
+      for (int sft = 0; sft + 1 < NSET; ++sft) {
+#pragma unroll
+        for (int p = 0; p < NP; ++p) acc[sft][p] = acc[sft + 1][p];
+      }
+    }
+    if (k < R) {  // start output row k
+      f32x2 *st = acc[ROTATE ? NSET - 1 : u];
+      if (zero_row) {
+#pragma unroll
+        for (int p = 0; p < NP; ++p) st[p] = bias2;
+      } else {
+        taps(st, 0, true);
+      }
+    }
+  };
+
+  if (ROTATE) {
+#pragma unroll 1
+    for (int k = 0; k < NSTEP; ++k) step(k, IntC<0>{});
+  } else {
+#pragma unroll 1
+    for (int k0 = 0; k0 < NSTEP; k0 += NSET) {
+      static_loop<NSET>([&](auto uc) {
+        constexpr int u = decltype(uc)::value;
+        if (k0 + u < NSTEP) step(k0 + u, uc);
+      });
+    }
+  }
+
+  // ---- planes that need tap-skipping semantics: exact re-evaluation from global memory ----
+  if (exact && active)
+    plane_exact_block<T, QM>(a, plane, ch, r0 + rb * R, cb * W, R, W, rows, PW, mm, &lo, &hi);
+
+  if (QM == QM_MM_REDUCE) {
+    plane_reduce_minmax<TPP>(a.q, ch, lo, hi, active, lane);
+    return;
+  }
+
+  // ---- the finished tile leaves in one piece ------------------------------------------------
+  T *dst = y + (long long)plane0 * PE + (long long)r0 * PW;
+  const T *out_src = tile + HALO * PW;
+  if (async_tile) {
+    fence_proxy_async_smem();  // this thread's shared-memory writes, for the copy engine
+    __syncwarp();
+    if (lane == 0) bulk_store_1d_and_wait(dst, out_src, obytes);
+  } else {
+    __syncwarp();
+    const int n = (NBND > 1 ? TB : pv * H) * PW;
+    for (int i = lane; i < n; i += 32) dst[i] = out_src[i];
+  }
+}
+
 // ---- stride 2 ---------------------------------------------------------------------------
 // Thread block of 14 x 14 inputs = 7 x 7 outputs; a tile is NRB x NCB blocks: whole planes
 // (NBND == 1) or one band of 14 * NRB full-width input rows plus the row above it
@@ -579,24 +877,25 @@ __global__ void __launch_bounds__(32, 7)
 }
 
 // Host-side entry (fused_plane.cu).
-cudaError_t launch_plane(int dtype, int hw, int stride, int qm, const FusedArgs &a, const PlaneCfg &c,
-                         cudaStream_t stream);
-// Geometry of the instantiation for a square hw x hw plane and stride; tpp == 0 if none.
+cudaError_t launch_plane(int dtype, int k, int hw, int stride, int qm, const FusedArgs &a,
+                         const PlaneCfg &c, cudaStream_t stream);
+// Geometry of the instantiation for a square hw x hw plane, kernel size and stride; tpp == 0
+// if there is none.
 struct PlaneGeom {
-  int tpp;    // threads per plane (stride 1, banded: per band)
+  int tpp;    // threads per plane (banded: per band)
   int bands;  // bands per plane (1 = whole planes)
   int w, nrb, ncb;
 };
-__host__ inline PlaneGeom plane_geom(int h, int w, int stride) {
+__host__ inline PlaneGeom plane_geom(int k, int h, int w, int stride) {
   PlaneGeom g = {0, 1, 0, 0, 0};
   if (h != w) return g;
-  if (stride == 1) {
-    if (w == 7) g = {1, 1, 7, 1, 1};
+  if (stride == 1 && (k == 3 || k == 5)) {
+    if (w == 7 && k == 3) g = {1, 1, 7, 1, 1};
     else if (w == 14) g = {2, 1, 14, 2, 1};
     else if (w == 28) g = {8, 1, 14, 4, 2};
     else if (w == 56) g = {32, 1, 14, 8, 4};
     else if (w == 112) g = {32, 4, 14, 4, 8};
-  } else if (stride == 2) {
+  } else if (stride == 2 && k == 3) {
     if (w == 14) g = {1, 1, 14, 1, 1};
     else if (w == 28) g = {4, 1, 14, 2, 2};
     else if (w == 56) g = {16, 1, 14, 4, 4};
@@ -604,9 +903,9 @@ __host__ inline PlaneGeom plane_geom(int h, int w, int stride) {
   }
   return g;
 }
-__host__ inline size_t plane_launch_smem(int hw, int stride, int elem_size) {
-  const PlaneGeom g = plane_geom(hw, hw, stride);
-  if (stride == 1) return plane_smem_bytes(g.w, g.nrb, g.ncb, g.bands, elem_size);
+__host__ inline size_t plane_launch_smem(int k, int hw, int stride, int elem_size) {
+  const PlaneGeom g = plane_geom(k, hw, hw, stride);
+  if (stride == 1) return plane_smem_bytes(k, g.w, g.nrb, g.ncb, g.bands, elem_size);
   return plane_s2_smem_bytes(g.nrb, g.ncb, g.bands, elem_size);
 }
 

@@ -155,7 +155,7 @@ int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan
   if (n_planes > 0x7fffffffLL) return DWBNQ_OK;
 
   // ---- small planes (7x7, 14x14, 28x28): one warp per CTA, whole planes -------------------
-  const PlaneGeom pg = K == 3 ? plane_geom(d.h, d.w, s) : PlaneGeom{0, 1, 0, 0, 0};
+  const PlaneGeom pg = plane_geom(K, d.h, d.w, s);
   if (pg.tpp > 0 && (forced == PATH_AUTO || forced == PATH_PLANE)) {
     TileCfg &c = plan->cfg;
     c.P = 32 / pg.tpp;
@@ -175,7 +175,7 @@ int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan
     c.n_tiles = (int)nt;
     plan->path = PATH_PLANE;
     plan->threads = 32;
-    plan->smem = plane_launch_smem(d.w, s, d.dtype == DWBNQ_F32 ? 4 : 2);
+    plan->smem = plane_launch_smem(K, d.w, s, d.dtype == DWBNQ_F32 ? 4 : 2);
     plan->ctas = c.n_tiles;
     return DWBNQ_OK;
   }
@@ -321,7 +321,7 @@ int launch_fused(const dwbnq_conv_desc &d, FusedArgs &a, int qm, int device, cud
     pc.P = plan.cfg.P;
     pc.n_tiles = plan.cfg.n_tiles;
     pc.bulk = plan.cfg.vec_fill;
-    e = launch_plane(d.dtype, d.w, d.stride_h, qm, a, pc, stream);
+    e = launch_plane(d.dtype, d.kh, d.w, d.stride_h, qm, a, pc, stream);
     if (e != cudaSuccess) return fail_cuda(e, "fused_plane_kernel launch");
     return DWBNQ_OK;
   }

@@ -20,6 +20,19 @@ PlaneKernel pick_s1(int qm) {
   return nullptr;
 }
 
+template <typename T, int K, int W, int NRB, int NCB, int NBND>
+PlaneKernel pick_kxk(int qm) {
+  switch (qm) {
+    case QM_NONE: return fused_plane_kxk_kernel<T, K, W, NRB, NCB, NBND, QM_NONE>;
+    case QM_FPQ: return fused_plane_kxk_kernel<T, K, W, NRB, NCB, NBND, QM_FPQ>;
+    case QM_POW2: return fused_plane_kxk_kernel<T, K, W, NRB, NCB, NBND, QM_POW2>;
+    case QM_MM_APPLY: return fused_plane_kxk_kernel<T, K, W, NRB, NCB, NBND, QM_MM_APPLY>;
+    case QM_MM_REDUCE: return fused_plane_kxk_kernel<T, K, W, NRB, NCB, NBND, QM_MM_REDUCE>;
+    case QM_FPQ_LEAN: return fused_plane_kxk_kernel<T, K, W, NRB, NCB, NBND, QM_FPQ_LEAN>;
+  }
+  return nullptr;
+}
+
 template <typename T, int NRB, int NCB, int NBND>
 PlaneKernel pick_s2(int qm) {
   switch (qm) {
@@ -34,22 +47,28 @@ PlaneKernel pick_s2(int qm) {
 }
 
 template <typename T>
-cudaError_t launch_t(int hw, int stride, int qm, const FusedArgs &a, const PlaneCfg &c, cudaStream_t stream) {
+cudaError_t launch_t(int k, int hw, int stride, int qm, const FusedArgs &a, const PlaneCfg &c,
+                     cudaStream_t stream) {
   PlaneKernel kern = nullptr;
-  if (stride == 1) {
+  if (stride == 1 && k == 3) {
     if (hw == 7) kern = pick_s1<T, 7, 1, 1, 1>(qm);
     else if (hw == 14) kern = pick_s1<T, 14, 2, 1, 1>(qm);
     else if (hw == 28) kern = pick_s1<T, 14, 4, 2, 1>(qm);
     else if (hw == 56) kern = pick_s1<T, 14, 8, 4, 1>(qm);
     else if (hw == 112) kern = pick_s1<T, 14, 4, 8, 4>(qm);
-  } else if (stride == 2) {
+  } else if (stride == 1 && k == 5) {
+    if (hw == 14) kern = pick_kxk<T, 5, 14, 2, 1, 1>(qm);
+    else if (hw == 28) kern = pick_kxk<T, 5, 14, 4, 2, 1>(qm);
+    else if (hw == 56) kern = pick_kxk<T, 5, 14, 8, 4, 1>(qm);
+    else if (hw == 112) kern = pick_kxk<T, 5, 14, 4, 8, 4>(qm);
+  } else if (stride == 2 && k == 3) {
     if (hw == 14) kern = pick_s2<T, 1, 1, 1>(qm);
     else if (hw == 28) kern = pick_s2<T, 2, 2, 1>(qm);
     else if (hw == 56) kern = pick_s2<T, 4, 4, 1>(qm);
     else if (hw == 112) kern = pick_s2<T, 4, 8, 2>(qm);
   }
   if (!kern) return cudaErrorInvalidValue;
-  const size_t smem = plane_launch_smem(hw, stride, sizeof(T));
+  const size_t smem = plane_launch_smem(k, hw, stride, sizeof(T));
   // all of the unified L1 / shared memory as shared memory: the tiles are the working set
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
                                        cudaSharedmemCarveoutMaxShared);
@@ -60,10 +79,10 @@ cudaError_t launch_t(int hw, int stride, int qm, const FusedArgs &a, const Plane
 
 }  // namespace
 
-cudaError_t launch_plane(int dtype, int hw, int stride, int qm, const FusedArgs &a, const PlaneCfg &c,
-                         cudaStream_t stream) {
-  return dtype == DWBNQ_F32 ? launch_t<float>(hw, stride, qm, a, c, stream)
-                            : launch_t<__half>(hw, stride, qm, a, c, stream);
+cudaError_t launch_plane(int dtype, int k, int hw, int stride, int qm, const FusedArgs &a,
+                         const PlaneCfg &c, cudaStream_t stream) {
+  return dtype == DWBNQ_F32 ? launch_t<float>(k, hw, stride, qm, a, c, stream)
+                            : launch_t<__half>(k, hw, stride, qm, a, c, stream);
 }
 
 }  // namespace dwbnq

@@ -102,6 +102,7 @@ int fill_pow2(QuantArgs *q, int sign, int with_zero, int n, int m, int device) {
   q->p_sign = sign ? 1 : 0;
   q->p_with_zero = with_zero ? 1 : 0;
   q->p_window = pow2_table_window();
+  q->p_fast = q->p_min >= 2.350988701644575e-38f ? 1 : 0;  // 2^-125
   return pow2_table_device(device, &q->p_table);
 }
 

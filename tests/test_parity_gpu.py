@@ -361,6 +361,30 @@ def test_small_plane_kernel(oracle, cuda_device, dtype, hw, stride, quant):
             assert_same_bits(t["qr_max"].cpu().numpy(), extra[1], "qr_max")
 
 
+@pytest.mark.parametrize("quant", [SMALL_QUANTS[1], SMALL_QUANTS[4], SMALL_QUANTS[5]], ids=["fpq_lean", "pow2", "minmax"])
+@pytest.mark.parametrize("hw", [14, 28, 56, 112])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16], ids=["f32", "f16"])
+def test_plane_kernel_5x5(oracle, cuda_device, dtype, hw, quant):
+    """5x5 stride 1 pad 2 on the plane family: two halo rows / columns, four live accumulator
+    rows, weight pairs in shared memory; includes a plane with bias == -0.0 (exact path)."""
+    rng = np.random.default_rng(500 + hw)
+    for n, c in (((3, 40) if hw <= 28 else (2, 10)), (1, 5)):
+        spec = workloads.LayerSpec("p5", n, c, hw, hw, 5, 1, 2, None)
+        d = _rand_layer(rng, n, c, hw, hw, 5)
+        d["b"][1] = -0.0
+        if quant["kind"] == "minmax":
+            d.update(qr_min=np.zeros(c, np.float32), qr_max=np.ones(c, np.float32), ql_min=np.zeros(c, np.float32),
+                     ql_max=np.full(c, 255, np.float32))
+        h16, up = f16_inputs(d) if dtype == torch.float16 else (d, d)
+        plan = ops.fused_plan(dev(h16["x"], cuda_device), dev(h16["w"], cuda_device), pad=(2, 2), stride=(1, 1))
+        assert plan["path"] == L.PATH_PLANE, plan
+        want, _, _ = oracle_fused(oracle, up, spec, quant)
+        got, _ = run_fused(h16, spec, cuda_device, quant, dtype=dtype)
+        if dtype == torch.float16:
+            want = oracle.to_f16_result(want)
+        assert_same_bits(got, want, "5x5 %dx%d n=%d c=%d" % (hw, hw, n, c))
+
+
 @pytest.mark.parametrize("hw,stride", SMALL_SHAPES, ids=SMALL_SHAPE_IDS)
 def test_small_plane_kernel_unaligned_and_optional(oracle, cuda_device, hw, stride):
     rng = np.random.default_rng(200 + hw + stride)
