@@ -32,7 +32,20 @@ __global__ void __launch_bounds__(kThreads) quant_flat_kernel(const T *x, T *y,
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long step = (long long)gridDim.x * blockDim.x;
   const long long n_vec = vec_ok ? size / S : 0;
-  for (long long v = tid; v < n_vec; v += step) {
+  constexpr int U = 4;  // vectors per thread whose loads are in flight together
+  long long v = tid;
+  for (; v + (U - 1) * step < n_vec; v += U * step) {
+    float e[U][S];
+#pragma unroll
+    for (int u = 0; u < U; ++u) Vec16<T>::load_stream(x + (v + u * step) * S, e[u]);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+#pragma unroll
+      for (int j = 0; j < S; ++j) e[u][j] = quant_apply<QM>(e[u][j], q, none);
+      Vec16<T>::store_stream(y + (v + u * step) * S, e[u]);
+    }
+  }
+  for (; v < n_vec; v += step) {
     float e[S];
     Vec16<T>::load_stream(x + v * S, e);
 #pragma unroll
@@ -62,15 +75,8 @@ int launch_quant_flat(int dtype, long long size, const QuantArgs &q, const void 
 }
 
 // ---- per-channel element-wise ops on x viewed as [size0, C, size2] ------------------------
-// A thread walks 16-byte vectors of the flat array with a fixed stride and tracks
-// (channel, offset inside the plane) incrementally, so no division runs per vector. A
-// vector may straddle one plane boundary (size2 >= VEC is required by the vector path).
-
-struct ChanWalk {
-  long long step_planes;  // (step * VEC) / size2
-  int step_off;           // (step * VEC) % size2
-  int step_ch;            // step_planes % C
-};
+// 16-byte vectors of the flat array; (channel, offset inside the plane) is tracked
+// incrementally per warp, so no division runs per vector in the common case.
 
 enum ChanOp : int { OP_BN = 0, OP_MM_APPLY = 1 };
 
@@ -92,6 +98,7 @@ template <typename T> struct ChanCoef<T, OP_BN> {
     c.beta = a.beta ? Elem<T>::to_f32(static_cast<const T *>(a.beta)[ch]) : 0.0f;
   }
   __device__ __forceinline__ float apply(float v) const { return bn_apply(v, c); }
+  __device__ __forceinline__ BnCoef coef() const { return c; }
 };
 template <typename T> struct ChanCoef<T, OP_MM_APPLY> {
   MmCoef c;
@@ -101,52 +108,128 @@ template <typename T> struct ChanCoef<T, OP_MM_APPLY> {
     c.hi = a.mm_hi[ch];
   }
   __device__ __forceinline__ float apply(float v) const { return mm_apply(v, c); }
+  __device__ __forceinline__ BnCoef coef() const { return BnCoef{0.0f, 1.0f, 1.0f, 0.0f}; }
 };
+
+// Vector path. A CTA owns a contiguous chunk of kChanChunkVecs vectors and each warp a
+// contiguous run of it, 32 vectors per iteration: while the warp's span lies inside one plane
+// (the common case) the per-channel operands are derived once per plane - for BN the packed
+// form with the reciprocal of sqrt(var + eps) - and the arithmetic runs on f32x2 pairs.
+// Spans that straddle a plane boundary fall back to per-element operands.
+constexpr int kChanChunkVecs = kThreads * 8;
+
+template <typename T, int OP>
+__device__ __forceinline__ void chan_apply_whole(float *e, const ChanCoef<T, OP> &c, const BnPacked &bp) {
+  constexpr int S = Elem<T>::VEC;
+  if (OP == OP_BN) {
+    f32x2 v[S / 2];
+#pragma unroll
+    for (int j = 0; j < S / 2; ++j) v[j] = pack2(e[2 * j], e[2 * j + 1]);
+    bn_apply_packed<S / 2>(v, bp);
+#pragma unroll
+    for (int j = 0; j < S / 2; ++j) unpack2(v[j], e[2 * j], e[2 * j + 1]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < S; ++j) e[j] = c.apply(e[j]);
+  }
+}
 
 template <typename T, int OP>
 __global__ void __launch_bounds__(kThreads)
-    chan_vec_kernel(const T *x, T *y, const long long total, const int C,
-                    const int size2, const ChanWalk w, const ChanArgs a) {
+    chan_vec_kernel(const T *__restrict__ x, T *__restrict__ y, const long long total, const int C,
+                    const long long size2, const ChanArgs a) {
   constexpr int S = Elem<T>::VEC;
-  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long step = (long long)gridDim.x * blockDim.x;
   const long long n_vec = total / S;
-  if (tid < n_vec) {
-    const long long e0 = tid * S;
-    const long long plane = e0 / size2;
-    int off = (int)(e0 - plane * size2);
+  const long long v_begin = (long long)blockIdx.x * kChanChunkVecs;
+  const long long v_end = min(n_vec, v_begin + kChanChunkVecs);
+  const long long e_begin = v_begin * S, e_end = v_end * S;
+  const int lane = threadIdx.x & 31;
+  const int iters = kChanChunkVecs / kThreads;
+  const long long warp_first = e_begin + (long long)(threadIdx.x >> 5) * iters * 32 * S;
+  if (warp_first < e_end) {
+    long long plane = warp_first / size2;
+    long long off = warp_first - plane * size2;  // offset of the warp's span inside its plane
     int ch = (int)(plane % C);
-    for (long long v = tid; v < n_vec; v += step) {
-      float e[S];
-      Vec16<T>::load_stream(x + v * S, e);
-      ChanCoef<T, OP> c0;
-      c0.load(a, ch);
-      if (off + S <= size2) {
-#pragma unroll
-        for (int j = 0; j < S; ++j) e[j] = c0.apply(e[j]);
-      } else {
-        ChanCoef<T, OP> c1;
-        c1.load(a, ch + 1 == C ? 0 : ch + 1);
-#pragma unroll
-        for (int j = 0; j < S; ++j) e[j] = (off + j < size2) ? c0.apply(e[j]) : c1.apply(e[j]);
-      }
-      Vec16<T>::store_stream(y + v * S, e);
-      off += w.step_off;
-      int carry = 0;
-      if (off >= size2) {
+    bool have = false;
+    ChanCoef<T, OP> c;
+    BnPacked bp;
+    const f32x2 nz = negzero2();
+    auto advance = [&](int elems) {
+      off += elems;
+      while (off >= size2) {
         off -= size2;
-        carry = 1;
+        ch = ch + 1 == C ? 0 : ch + 1;
+        have = false;
       }
-      ch += w.step_ch + carry;
-      if (ch >= C) ch -= C;
+    };
+    auto ensure = [&]() {
+      if (!have) {
+        c.load(a, ch);
+        if (OP == OP_BN) bp = make_bn_packed(c.coef(), nz);
+        have = true;
+      }
+    };
+    constexpr int U = 4;  // vectors per lane whose loads are in flight together
+    static_assert((kChanChunkVecs / kThreads) % U == 0, "iterations come in groups of U");
+    for (int it = 0; it < iters; it += U) {
+      const long long span0 = warp_first + (long long)it * 32 * S;
+      if (span0 >= e_end) break;  // uniform
+      if (span0 + U * 32 * S <= e_end && off + U * 32 * S <= size2) {  // uniform: U spans, one plane
+        ensure();
+        const long long e0 = span0 + (long long)lane * S;
+        float e[U][S];
+#pragma unroll
+        for (int u = 0; u < U; ++u) Vec16<T>::load_stream(x + e0 + u * 32 * S, e[u]);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          chan_apply_whole<T, OP>(e[u], c, bp);
+          Vec16<T>::store_stream(y + e0 + u * 32 * S, e[u]);
+        }
+        advance(U * 32 * S);
+        continue;
+      }
+#pragma unroll 1
+      for (int u = 0; u < U; ++u) {
+        const long long sp = span0 + (long long)u * 32 * S;
+        if (sp >= e_end) break;  // uniform
+        const long long e0 = sp + (long long)lane * S;
+        if (sp + 32 * S <= e_end && off + 32 * S <= size2) {  // uniform: the span lies in one plane
+          ensure();
+          float e[S];
+          Vec16<T>::load_stream(x + e0, e);
+          chan_apply_whole<T, OP>(e, c, bp);
+          Vec16<T>::store_stream(y + e0, e);
+        } else if (e0 + S <= e_end) {
+          float e[S];
+          Vec16<T>::load_stream(x + e0, e);
+          const long long p0 = e0 / size2;
+          const long long loff = e0 - p0 * size2;
+          if (loff + S <= size2) {
+            ChanCoef<T, OP> c0;
+            c0.load(a, (int)(p0 % C));
+#pragma unroll
+            for (int j = 0; j < S; ++j) e[j] = c0.apply(e[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < S; ++j) {
+              ChanCoef<T, OP> cj;
+              cj.load(a, (int)(((e0 + j) / size2) % C));
+              e[j] = cj.apply(e[j]);
+            }
+          }
+          Vec16<T>::store_stream(y + e0, e);
+        }
+        advance(32 * S);
+      }
     }
   }
-  // scalar tail (total % VEC elements)
-  for (long long i = n_vec * S + tid; i < total; i += step) {
-    const int ch = (int)((i / size2) % C);
-    ChanCoef<T, OP> c;
-    c.load(a, ch);
-    y[i] = Elem<T>::from_f32(c.apply(Elem<T>::to_f32(x[i])));
+  // scalar tail (total % VEC elements), by the last CTA
+  if (blockIdx.x == gridDim.x - 1) {
+    for (long long i = n_vec * S + threadIdx.x; i < total; i += blockDim.x) {
+      ChanCoef<T, OP> ct;
+      ct.load(a, (int)((i / size2) % C));
+      y[i] = Elem<T>::from_f32(ct.apply(Elem<T>::to_f32(x[i])));
+    }
   }
 }
 
@@ -170,14 +253,9 @@ int launch_chan_t(long long size0, long long C, long long size2, const T *x, T *
   const long long total = size0 * C * size2;
   if (total == 0) return DWBNQ_OK;
   const bool vec = aligned16(x) && aligned16(y) && size2 >= S && size2 <= 0x7fffffffLL && C <= 0x7fffffffLL;
-  if (vec) {
-    const unsigned int grid = grid_for((total + S - 1) / S, 16);
-    const long long step_elems = (long long)grid * kThreads * S;
-    ChanWalk w;
-    w.step_planes = step_elems / size2;
-    w.step_off = (int)(step_elems % size2);
-    w.step_ch = (int)(w.step_planes % C);
-    chan_vec_kernel<T, OP><<<grid, kThreads, 0, stream>>>(x, y, total, (int)C, (int)size2, w, a);
+  const long long chunks = (total / S + kChanChunkVecs - 1) / kChanChunkVecs;
+  if (vec && chunks >= 1 && chunks <= 0x7fffffffLL) {
+    chan_vec_kernel<T, OP><<<(unsigned int)chunks, kThreads, 0, stream>>>(x, y, total, (int)C, size2, a);
   } else {
     chan_scalar_kernel<T, OP><<<grid_for(total, 16), kThreads, 0, stream>>>(x, y, total, (int)C, size2, a);
   }
@@ -218,44 +296,124 @@ __global__ void __launch_bounds__(kThreads)
   const long long plane_first = e_begin / size2;
   const float pinf = __uint_as_float(0x7f800000u), ninf = __uint_as_float(0xff800000u);
   if (vec_ok) {
-    for (long long e0 = e_begin + (long long)threadIdx.x * S; e0 < e_end; e0 += (long long)blockDim.x * S) {
-      if (e0 + S <= e_end) {
-        float e[S];
-        Vec16<T>::load_stream(x + e0, e);
-        const long long plane = e0 / size2;
-        const long long off = e0 - plane * size2;
-        const int slot = (int)(plane - plane_first);
-        if (off + S <= size2) {
-          float lo = pinf, hi = ninf;
+    // A warp walks a contiguous run of the chunk, 32 vectors per iteration. While the warp's
+    // span lies inside one plane (the common case for planes of a few hundred elements or
+    // more) every lane accumulates in registers; the partial result goes to the plane's
+    // shared-memory slot through one shuffle reduction when the plane changes. Spans that
+    // straddle a plane boundary take the per-lane path.
+    const int lane = threadIdx.x & 31;
+    const int n_warps = blockDim.x >> 5;
+    const int iters = kChunkVecs / kThreads;  // iterations per warp
+    const long long warp_first = e_begin + (long long)(threadIdx.x >> 5) * iters * 32 * S;
+    const long long rel0 = warp_first - plane_first * size2;  // < chunk + size2
+    int slot = (int)(rel0 / size2);
+    long long off = rel0 - (long long)slot * size2;  // offset of the warp's span inside its plane
+    (void)n_warps;
+    int cur = -1;
+    float lo = pinf, hi = ninf;
+    auto flush = [&]() {
+      if (cur < 0) return;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o));
+        hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+      }
+      if (lane == 0) {
+        if (lo != pinf) atomicMin(&s_red[2 * cur], enc_ordered(lo));
+        if (hi != ninf) atomicMax(&s_red[2 * cur + 1], enc_ordered(hi));
+      }
+      lo = pinf;
+      hi = ninf;
+    };
+    auto advance = [&](int elems) {
+      off += elems;
+      while (off >= size2) {
+        off -= size2;
+        ++slot;
+      }
+    };
+    constexpr int U = 4;  // vectors per lane whose loads are in flight together
+    static_assert((kChunkVecs / kThreads) % U == 0, "iterations come in groups of U");
+    for (int it = 0; it < iters; it += U) {
+      const long long span0 = warp_first + (long long)it * 32 * S;
+      if (span0 >= e_end) break;  // uniform
+      if (span0 + U * 32 * S <= e_end && off + U * 32 * S <= size2) {  // uniform: U spans, one plane
+        if (slot != cur) {
+          flush();
+          cur = slot;
+        }
+        const long long e0 = span0 + (long long)lane * S;
+        float e[U][S];
+#pragma unroll
+        for (int u = 0; u < U; ++u) Vec16<T>::load_stream(x + e0 + u * 32 * S, e[u]);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+#pragma unroll
+          for (int j = 0; j < S; ++j) {
+            lo = fminf(lo, e[u][j]);
+            hi = fmaxf(hi, e[u][j]);
+          }
+        }
+        advance(U * 32 * S);
+        continue;
+      }
+#pragma unroll 1
+      for (int u = 0; u < U; ++u) {
+        const long long sp = span0 + (long long)u * 32 * S;
+        if (sp >= e_end) break;  // uniform
+        const long long e0 = sp + (long long)lane * S;
+        if (sp + 32 * S <= e_end && off + 32 * S <= size2) {  // uniform: the span lies in one plane
+          if (slot != cur) {
+            flush();
+            cur = slot;
+          }
+          float e[S];
+          Vec16<T>::load_stream(x + e0, e);
 #pragma unroll
           for (int j = 0; j < S; ++j) {
             lo = fminf(lo, e[j]);
             hi = fmaxf(hi, e[j]);
           }
-          atomicMin(&s_red[2 * slot], enc_ordered(lo));
-          atomicMax(&s_red[2 * slot + 1], enc_ordered(hi));
-        } else {
-          // the vector straddles plane boundaries (possibly several when size2 < VEC)
+        } else if (e0 + S <= e_end) {
+          float e[S];
+          Vec16<T>::load_stream(x + e0, e);
+          const long long plane = e0 / size2;
+          const long long loff = e0 - plane * size2;
+          const int sl = (int)(plane - plane_first);
+          if (loff + S <= size2) {
+            float l2 = pinf, h2 = ninf;
 #pragma unroll
-          for (int j = 0; j < S; ++j) {
-            const int sl = (int)((e0 + j) / size2 - plane_first);
-            if (e[j] == e[j]) {
-              atomicMin(&s_red[2 * sl], enc_ordered(e[j]));
-              atomicMax(&s_red[2 * sl + 1], enc_ordered(e[j]));
+            for (int j = 0; j < S; ++j) {
+              l2 = fminf(l2, e[j]);
+              h2 = fmaxf(h2, e[j]);
+            }
+            if (l2 != pinf) atomicMin(&s_red[2 * sl], enc_ordered(l2));
+            if (h2 != ninf) atomicMax(&s_red[2 * sl + 1], enc_ordered(h2));
+          } else {
+            // the vector straddles plane boundaries (possibly several when size2 < VEC)
+#pragma unroll
+            for (int j = 0; j < S; ++j) {
+              const int s2 = (int)((e0 + j) / size2 - plane_first);
+              if (e[j] == e[j]) {
+                atomicMin(&s_red[2 * s2], enc_ordered(e[j]));
+                atomicMax(&s_red[2 * s2 + 1], enc_ordered(e[j]));
+              }
+            }
+          }
+        } else {
+          for (long long i = e0; i < e_end; ++i) {
+            const float v = Elem<T>::to_f32(x[i]);
+            const int s2 = (int)(i / size2 - plane_first);
+            if (v == v) {
+              atomicMin(&s_red[2 * s2], enc_ordered(v));
+              atomicMax(&s_red[2 * s2 + 1], enc_ordered(v));
             }
           }
         }
-      } else {
-        for (long long i = e0; i < e_end; ++i) {
-          const float v = Elem<T>::to_f32(x[i]);
-          const int sl = (int)(i / size2 - plane_first);
-          if (v == v) {
-            atomicMin(&s_red[2 * sl], enc_ordered(v));
-            atomicMax(&s_red[2 * sl + 1], enc_ordered(v));
-          }
-        }
+        advance(32 * S);
       }
     }
+    flush();
   } else {
     for (long long i = e_begin + threadIdx.x; i < e_end; i += blockDim.x) {
       const float v = Elem<T>::to_f32(x[i]);
