@@ -270,8 +270,20 @@ int dwbnq_fused_fwd(const dwbnq_conv_desc *desc, float bn_eps, const dwbnq_quant
   if (q->x_min_max) {
     st = launch_mm_init(ws, channels, s);
     if (st != DWBNQ_OK) return st;
-    st = launch_fused(*desc, a, QM_MM_REDUCE, dev, s);
+    // fp32 on the plane family: the first pass also stores the activation in y (exact in
+    // fp32) and the second pass quantizes y in place, 1.3x less traffic than recomputing.
+    // fp16 must recompute: its contract is one rounding, of the quantized value.
+    Plan plan;
+    st = make_plan(*desc, a.x, a.y, &plan);
     if (st != DWBNQ_OK) return st;
+    const bool store_first = desc->dtype == DWBNQ_F32 && plan.path == PATH_PLANE;
+    st = launch_fused(*desc, a, store_first ? QM_MM_REDUCE_STORE : QM_MM_REDUCE, dev, s);
+    if (st != DWBNQ_OK) return st;
+    if (store_first) {
+      st = mm_finish_ranges(desc->dtype, channels, *q, *mm, ws, comm, s);
+      if (st != DWBNQ_OK) return st;
+      return launch_mm_apply(desc->dtype, desc->n, channels, (long long)ho * wo, y, y, ws, s);
+    }
   }
   st = mm_finish_ranges(desc->dtype, channels, *q, *mm, ws, comm, s);
   if (st != DWBNQ_OK) return st;

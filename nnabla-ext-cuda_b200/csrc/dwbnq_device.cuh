@@ -16,8 +16,12 @@ enum QMode : int {
   QM_POW2 = 2,      // Pow2Quantize
   QM_MM_APPLY = 3,  // MinMaxQuantize, second pass: quantize with per-channel ranges
   QM_MM_REDUCE = 4, // MinMaxQuantize, first pass: per-channel min/max only, no store
-  QM_FPQ_LEAN = 5   // FixedPointQuantize, the common case compiled without per-row tests (tiled family)
+  QM_FPQ_LEAN = 5,  // FixedPointQuantize, the common case compiled without per-row tests (tiled family)
+  QM_MM_REDUCE_STORE = 6  // MinMaxQuantize, first pass that also stores the fp32 activation (plane family)
 };
+// Whether a mode reduces to per-channel min / max, and whether it writes y.
+__host__ __device__ constexpr bool qm_reduces(int qm) { return qm == QM_MM_REDUCE || qm == QM_MM_REDUCE_STORE; }
+__host__ __device__ constexpr bool qm_stores(int qm) { return qm != QM_MM_REDUCE; }
 
 // Kernel-argument block of the quantizers (passed by value; uniform -> constant bank).
 struct QuantArgs {

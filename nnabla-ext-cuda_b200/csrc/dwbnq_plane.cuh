@@ -129,12 +129,11 @@ __device__ __noinline__ void plane_exact_block(const FusedArgs &a, int plane, in
 #pragma unroll 1
     for (int j = 0; j < ncols; ++j) {
       const float v = prequant_point<T>(a, n, ch, oy0 + r, ox0 + j);
-      if (QM == QM_MM_REDUCE) {
+      if (qm_reduces(QM)) {
         lo = fminf(lo, v);
         hi = fmaxf(hi, v);
-      } else {
-        dst[r * pitch + j] = Elem<T>::from_f32(quant_apply<QM>(v, a.q, mm));
       }
+      if (qm_stores(QM)) dst[r * pitch + j] = Elem<T>::from_f32(quant_apply<QM>(v, a.q, mm));
     }
   }
   *lo_out = lo;
@@ -353,13 +352,14 @@ __global__ void __launch_bounds__(32, 16)
       float o[2 * NP];
 #pragma unroll
       for (int p = 0; p < NP; ++p) unpack2(fin[p], o[2 * p], o[2 * p + 1]);
-      if (QM == QM_MM_REDUCE) {
+      if (qm_reduces(QM)) {
 #pragma unroll
         for (int j = 0; j < W; ++j) {
           lo = fminf(lo, o[j]);
           hi = fmaxf(hi, o[j]);
         }
-      } else {
+      }
+      if (qm_stores(QM)) {
         plane_quant<QM, W>(o, a.q, mm);
         if (active) plane_store_row<T, W>(rows + (k - 2) * PW, o);
       }
@@ -385,10 +385,8 @@ __global__ void __launch_bounds__(32, 16)
   if (exact && active)
     plane_exact_block<T, QM>(a, plane, ch, r0 + rb * R, cb * W, R, W, rows, PW, mm, &lo, &hi);
 
-  if (QM == QM_MM_REDUCE) {
-    plane_reduce_minmax<TPP>(a.q, ch, lo, hi, active, lane);
-    return;
-  }
+  if (qm_reduces(QM)) plane_reduce_minmax<TPP>(a.q, ch, lo, hi, active, lane);
+  if (!qm_stores(QM)) return;
 
   // ---- the finished tile leaves in one piece ------------------------------------------------
   T *dst = y + (long long)plane0 * PE + (long long)r0 * PW;
@@ -630,13 +628,14 @@ __global__ void __launch_bounds__(32, 16)
       float o[2 * NP];
 #pragma unroll
       for (int p = 0; p < NP; ++p) unpack2(fin[p], o[2 * p], o[2 * p + 1]);
-      if (QM == QM_MM_REDUCE) {
+      if (qm_reduces(QM)) {
 #pragma unroll
         for (int j = 0; j < W; ++j) {
           lo = fminf(lo, o[j]);
           hi = fmaxf(hi, o[j]);
         }
-      } else {
+      }
+      if (qm_stores(QM)) {
         plane_quant<QM, W>(o, a.q, mm);
         if (active) plane_store_row<T, W>(rows + (k - (K - 1)) * PW, o);
       }
@@ -681,10 +680,8 @@ __global__ void __launch_bounds__(32, 16)
   if (exact && active)
     plane_exact_block<T, QM>(a, plane, ch, r0 + rb * R, cb * W, R, W, rows, PW, mm, &lo, &hi);
 
-  if (QM == QM_MM_REDUCE) {
-    plane_reduce_minmax<TPP>(a.q, ch, lo, hi, active, lane);
-    return;
-  }
+  if (qm_reduces(QM)) plane_reduce_minmax<TPP>(a.q, ch, lo, hi, active, lane);
+  if (!qm_stores(QM)) return;
 
   // ---- the finished tile leaves in one piece ------------------------------------------------
   T *dst = y + (long long)plane0 * PE + (long long)r0 * PW;
@@ -843,13 +840,14 @@ __global__ void __launch_bounds__(32, 7)
     float o[2 * NPO];
 #pragma unroll
     for (int p = 0; p < NPO; ++p) unpack2(pr[p], o[2 * p], o[2 * p + 1]);
-    if (QM == QM_MM_REDUCE) {
+    if (qm_reduces(QM)) {
 #pragma unroll
       for (int j = 0; j < OB; ++j) {
         lo = fminf(lo, o[j]);
         hi = fmaxf(hi, o[j]);
       }
-    } else {
+    }
+    if (qm_stores(QM)) {
       plane_quant<QM, OB>(o, a.q, mm);
 #pragma unroll
       for (int j = 0; j < OB; ++j) orows[t * OW + j] = Elem<T>::from_f32(o[j]);
@@ -860,10 +858,8 @@ __global__ void __launch_bounds__(32, 7)
   if (exact && active)
     plane_exact_block<T, QM>(a, plane, ch, band * TBO + rb * OB, cb * OB, OB, OB, orows, OW, mm, &lo, &hi);
 
-  if (QM == QM_MM_REDUCE) {
-    plane_reduce_minmax<TPP>(a.q, ch, lo, hi, active, lane);
-    return;
-  }
+  if (qm_reduces(QM)) plane_reduce_minmax<TPP>(a.q, ch, lo, hi, active, lane);
+  if (!qm_stores(QM)) return;
 
   T *dst = y + (long long)plane0 * OE + (long long)band * OTE;
   if (async_tile) {

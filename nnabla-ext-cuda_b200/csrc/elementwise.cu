@@ -116,6 +116,7 @@ template <typename T> struct ChanCoef<T, OP_MM_APPLY> {
 // (the common case) the per-channel operands are derived once per plane - for BN the packed
 // form with the reciprocal of sqrt(var + eps) - and the arithmetic runs on f32x2 pairs.
 // Spans that straddle a plane boundary fall back to per-element operands.
+// x and y may be the same buffer (every vector is read before it is written, by one thread).
 constexpr int kChanChunkVecs = kThreads * 8;
 
 template <typename T, int OP>
@@ -136,7 +137,7 @@ __device__ __forceinline__ void chan_apply_whole(float *e, const ChanCoef<T, OP>
 
 template <typename T, int OP>
 __global__ void __launch_bounds__(kThreads)
-    chan_vec_kernel(const T *__restrict__ x, T *__restrict__ y, const long long total, const int C,
+    chan_vec_kernel(const T *x, T *y, const long long total, const int C,
                     const long long size2, const ChanArgs a) {
   constexpr int S = Elem<T>::VEC;
   const long long n_vec = total / S;

@@ -16,6 +16,7 @@ PlaneKernel pick_s1(int qm) {
     case QM_MM_APPLY: return fused_plane_kernel<T, W, NRB, NCB, NBND, QM_MM_APPLY>;
     case QM_MM_REDUCE: return fused_plane_kernel<T, W, NRB, NCB, NBND, QM_MM_REDUCE>;
     case QM_FPQ_LEAN: return fused_plane_kernel<T, W, NRB, NCB, NBND, QM_FPQ_LEAN>;
+    case QM_MM_REDUCE_STORE: return fused_plane_kernel<T, W, NRB, NCB, NBND, QM_MM_REDUCE_STORE>;
   }
   return nullptr;
 }
@@ -29,6 +30,7 @@ PlaneKernel pick_kxk(int qm) {
     case QM_MM_APPLY: return fused_plane_kxk_kernel<T, K, W, NRB, NCB, NBND, QM_MM_APPLY>;
     case QM_MM_REDUCE: return fused_plane_kxk_kernel<T, K, W, NRB, NCB, NBND, QM_MM_REDUCE>;
     case QM_FPQ_LEAN: return fused_plane_kxk_kernel<T, K, W, NRB, NCB, NBND, QM_FPQ_LEAN>;
+    case QM_MM_REDUCE_STORE: return fused_plane_kxk_kernel<T, K, W, NRB, NCB, NBND, QM_MM_REDUCE_STORE>;
   }
   return nullptr;
 }
@@ -42,6 +44,7 @@ PlaneKernel pick_s2(int qm) {
     case QM_MM_APPLY: return fused_plane_s2_kernel<T, NRB, NCB, NBND, QM_MM_APPLY>;
     case QM_MM_REDUCE: return fused_plane_s2_kernel<T, NRB, NCB, NBND, QM_MM_REDUCE>;
     case QM_FPQ_LEAN: return fused_plane_s2_kernel<T, NRB, NCB, NBND, QM_FPQ_LEAN>;
+    case QM_MM_REDUCE_STORE: return fused_plane_s2_kernel<T, NRB, NCB, NBND, QM_MM_REDUCE_STORE>;
   }
   return nullptr;
 }
