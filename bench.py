@@ -11,7 +11,8 @@ The batch is sharded by image: with N GPUs every rank runs its own 256 images (w
 scaling), no data-path collective except cfg3's per-channel min/max all-reduce.
 
 One JSON line is printed by rank 0:
-  value      whole-job images/s with inputs resident in HBM (CUDA events, max over ranks)
+  value      whole-job images/s with inputs resident in HBM (CUDA events, max over ranks); the
+             17 launches of a step are replayed from a CUDA graph (config.launch)
   e2e        the same through the public call with HOST buffers: pinned-host -> device copy
              of every layer input and device -> host copy of every layer output inside the
              timed region
@@ -316,9 +317,20 @@ def run_own(args):
                               s.bn_eps, pad=(s.pad, s.pad), stride=(s.stride, s.stride), quant=q, comm=comm, ws=ws,
                               out=y)
 
-    def step():
+    def step_eager():
         for layer in layers:
             launch(layer)
+
+    # The launches of one step are captured once into a CUDA graph and replayed (--no-graph:
+    # launched one by one from the host). The library's entry points only set attributes and
+    # launch, so they can be captured once their first-call set-up has run in the warm-up.
+    graph = None
+
+    def step():
+        if graph is not None:
+            graph.replay()
+        else:
+            step_eager()
 
     def barrier():
         if world > 1:
@@ -336,6 +348,19 @@ def run_own(args):
     for _ in range(args.warmup):
         step()
     barrier()
+    if args.graph and comm is None:
+        cap = torch.cuda.Stream(device)
+        cap.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(cap):
+            step_eager()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=cap):
+                step_eager()
+        torch.cuda.current_stream(device).wait_stream(cap)
+        graph = g
+        for _ in range(3):
+            step()
+        barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -448,7 +473,7 @@ def run_own(args):
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16" if half else "f32", "data": "synthetic",
             "config": {"workload": workload_name(args), "batch_per_gpu": batch, "global_batch": batch * world,
-                       "layers": len(specs), "parallelism": "batch-sharded x%d" % world,
+                       "layers": len(specs), "parallelism": "batch-sharded x%d" % world, "launch": "cuda graph" if graph is not None else "stream",
                        "l2": "per-step working set %.1f GB >> 126 MB L2; every layer has its own buffers"
                              % (bytes_per_step / 1e9)},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -505,6 +530,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-layer-pass", action="store_true")
     ap.add_argument("--ablate", default="", help="profiling only: 'bn', 'quant' or 'bn,quant' are left out")
+    ap.add_argument("--no-graph", dest="graph", action="store_false",
+                    help="launch every kernel from the host instead of replaying the step from a CUDA graph")
     ap.add_argument("--force-path", type=int, default=None, help="profiling only: kernel family 0..4")
     ap.add_argument("--tune", default="", help="profiling only: planner override P,row_blocks,threads,rows_per_patch")
     args = ap.parse_args()
