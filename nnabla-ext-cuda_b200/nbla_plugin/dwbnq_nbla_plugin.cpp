@@ -123,10 +123,16 @@ protected:
     NBLA_CHECK(!this->batch_stat_, error_code::not_implemented,
                "BatchNormalizationCuda (dwbnq) implements batch_stat=False only");
     const Tc *x = inputs[0]->get_data_pointer<Tc>(this->ctx_);
-    const Tc *beta = this->no_bias_ ? nullptr : inputs[this->b_idx_]->get_data_pointer<Tc>(this->ctx_);
-    const Tc *gamma = this->no_scale_ ? nullptr : inputs[this->g_idx_]->get_data_pointer<Tc>(this->ctx_);
-    const Tc *rm = inputs[this->m_idx_]->get_data_pointer<Tc>(this->ctx_);
-    const Tc *rv = inputs[this->v_idx_]->get_data_pointer<Tc>(this->ctx_);
+    // (named Variable pointers: a call through inputs[<member of the dependent base>] would
+    // need the `template` disambiguator)
+    Variable *vb = this->no_bias_ ? nullptr : inputs[this->b_idx_];
+    Variable *vg = this->no_scale_ ? nullptr : inputs[this->g_idx_];
+    Variable *vm = inputs[this->m_idx_];
+    Variable *vv = inputs[this->v_idx_];
+    const Tc *beta = vb ? vb->get_data_pointer<Tc>(this->ctx_) : nullptr;
+    const Tc *gamma = vg ? vg->get_data_pointer<Tc>(this->ctx_) : nullptr;
+    const Tc *rm = vm->get_data_pointer<Tc>(this->ctx_);
+    const Tc *rv = vv->get_data_pointer<Tc>(this->ctx_);
     Tc *y = outputs[0]->cast_data_and_get_pointer<Tc>(this->ctx_, true);
     check(dwbnq_bn_infer_fwd(DType<T>::value, this->size0_, this->size1_, this->size2_, this->eps_, x, beta,
                              gamma, rm, rv, y, device_, nullptr),

@@ -1,0 +1,133 @@
+// TEST INFRASTRUCTURE: drives the dwbnq registry plugin through the stand-in nnabla interface
+// of nbla/stub_core.hpp. Built by tests/test_nbla_plugin.py together with the plugin source;
+// the functions are created through the (stub) registry under the reference's class names and
+// run on caller-provided device buffers.
+#include <cstring>
+#include <nbla/stub_core.hpp>
+
+extern "C" void dwbnq_register_nbla(void);
+
+namespace {
+thread_local std::string g_err;
+nbla::Context ctx_for(int device, int half) {
+  nbla::Context c;
+  c.backend = {half ? "cuda:half" : "cuda:float"};
+  c.array_class = "CudaCachedArray";
+  c.device_id = std::to_string(device);
+  return c;
+}
+template <typename F> int guarded(F &&f) {
+  try {
+    f();
+    return 0;
+  } catch (const nbla::Exception &e) {
+    g_err = e.what();
+    return 100 + (int)e.code;
+  } catch (const std::exception &e) {
+    g_err = e.what();
+    return 1;
+  }
+}
+nbla::Shape_t shp(const int64_t *s, int n) { return nbla::Shape_t(s, s + n); }
+}  // namespace
+
+extern "C" {
+const char *stub_last_error(void) { return g_err.c_str(); }
+// scratch for Variables the functions allocate themselves (MinMaxQuantize's workspace)
+void stub_set_scratch(void *p) {
+  nbla::Variable::default_alloc() = [p](size_t) { return p; };
+}
+int stub_registered(const char *base, const char *backend) {
+  dwbnq_register_nbla();
+  return nbla::StubRegistry::table().count(std::string(base) + "/" + backend) ? 1 : 0;
+}
+int stub_name(const char *backend, int device, char *out, int cap) {
+  return guarded([&] {
+    dwbnq_register_nbla();
+    std::unique_ptr<nbla::Function> f(nbla::stub_create<bool, int, float, bool>(
+        "FixedPointQuantize", backend, ctx_for(device, 0), true, 8, 0.0625f, true));
+    std::strncpy(out, f->name().c_str(), cap - 1);
+    out[cap - 1] = 0;
+  });
+}
+int stub_dwconv(int half, int device, const int64_t *xs, const int64_t *ws, int nd, void *x, void *w, void *b, void *y,
+                int pad, int stride, int dil, int mult) {
+  return guarded([&] {
+    dwbnq_register_nbla();
+    const std::vector<int> p(nd - 2, pad), s(nd - 2, stride), d(nd - 2, dil);
+    std::unique_ptr<nbla::Function> f(
+        nbla::stub_create<int, const std::vector<int> &, const std::vector<int> &, const std::vector<int> &, int>(
+            "DepthwiseConvolution", half ? "cuda:half" : "cuda:float", ctx_for(device, half), 1, p, s, d, mult));
+    nbla::Variable vx(shp(xs, nd), x), vw(shp(ws, nd - 1), w), vb(nbla::Shape_t{ws[0]}, b), vy(nbla::Shape_t{}, y);
+    nbla::Variables in{&vx, &vw};
+    if (b) in.push_back(&vb);
+    nbla::Variables out{&vy};
+    f->setup(in, out);
+    f->forward(in, out);
+  });
+}
+int stub_bn(int half, int device, const int64_t *xs, int nd, void *x, void *beta, void *gamma, void *mean, void *var,
+            void *y, float eps, int batch_stat) {
+  return guarded([&] {
+    dwbnq_register_nbla();
+    std::unique_ptr<nbla::Function> f(nbla::stub_create<const std::vector<int> &, float, float, bool, bool, bool>(
+        "BatchNormalization", half ? "cuda:half" : "cuda:float", ctx_for(device, half), std::vector<int>{1}, 0.9f, eps,
+        batch_stat != 0, gamma == nullptr, beta == nullptr));
+    nbla::Shape_t ps(nd, 1);
+    ps[1] = xs[1];
+    nbla::Variable vx(shp(xs, nd), x), vb(ps, beta), vg(ps, gamma), vm(ps, mean), vv(ps, var), vy(shp(xs, nd), y);
+    nbla::Variables in{&vx};
+    if (beta) in.push_back(&vb);
+    if (gamma) in.push_back(&vg);
+    in.push_back(&vm);
+    in.push_back(&vv);
+    nbla::Variables out{&vy};
+    f->setup(in, out);
+    f->forward(in, out);
+  });
+}
+int stub_fpq(int half, int device, int64_t size, void *x, void *y, int sign, int n, float delta) {
+  return guarded([&] {
+    dwbnq_register_nbla();
+    std::unique_ptr<nbla::Function> f(nbla::stub_create<bool, int, float, bool>(
+        "FixedPointQuantize", half ? "cuda:half" : "cuda:float", ctx_for(device, half), sign != 0, n, delta, true));
+    nbla::Variable vx(nbla::Shape_t{size}, x), vy(nbla::Shape_t{size}, y);
+    nbla::Variables in{&vx}, out{&vy};
+    f->setup(in, out);
+    f->forward(in, out);
+  });
+}
+int stub_pow2(int half, int device, int64_t size, void *x, void *y, int sign, int with_zero, int n, int m) {
+  return guarded([&] {
+    dwbnq_register_nbla();
+    std::unique_ptr<nbla::Function> f(nbla::stub_create<bool, bool, int, int, bool>(
+        "Pow2Quantize", half ? "cuda:half" : "cuda:float", ctx_for(device, half), sign != 0, with_zero != 0, n, m, true));
+    nbla::Variable vx(nbla::Shape_t{size}, x), vy(nbla::Shape_t{size}, y);
+    nbla::Variables in{&vx}, out{&vy};
+    f->setup(in, out);
+    f->forward(in, out);
+  });
+}
+int stub_minmax(int half, int device, const int64_t *xs, int nd, void *x, void *qr_min, void *qr_max, void *ql_min,
+                void *ql_max, void *y, float decay, int x_min_max, int ema, float eps) {
+  return guarded([&] {
+    dwbnq_register_nbla();
+    std::unique_ptr<nbla::Function> f(nbla::stub_create<float, bool, bool, bool, float>(
+        "MinMaxQuantize", half ? "cuda:half" : "cuda:float", ctx_for(device, half), decay, x_min_max != 0, ema != 0, true, eps));
+    nbla::Shape_t ps(nd, 1);
+    ps[1] = xs[1];
+    nbla::Variable vx(shp(xs, nd), x), a(ps, qr_min), b(ps, qr_max), c(ps, ql_min), d(ps, ql_max), vy(shp(xs, nd), y);
+    nbla::Variables in{&vx, &a, &b, &c, &d}, out{&vy};
+    f->setup(in, out);
+    f->forward(in, out);
+  });
+}
+int stub_backward_is_refused(int device) {
+  return guarded([&] {
+    dwbnq_register_nbla();
+    std::unique_ptr<nbla::Function> f(nbla::stub_create<bool, int, float, bool>(
+        "FixedPointQuantize", "cuda:float", ctx_for(device, 0), true, 8, 0.0625f, true));
+    f->backward({}, {}, {}, {});
+  });
+}
+}

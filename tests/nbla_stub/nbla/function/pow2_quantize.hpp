@@ -1,0 +1,1 @@
+#include <nbla/stub_core.hpp>

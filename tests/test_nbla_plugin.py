@@ -1,0 +1,136 @@
+"""The nbla registry plugin (nnabla-ext-cuda_b200/nbla_plugin) compiled against a stand-in
+for nnabla core's C++ interface (tests/nbla_stub: nnabla itself cannot be installed here) and
+driven end to end: registration under the reference's (function, backend) keys, class names,
+the forward of each of the five functions on device buffers against the CPU oracle, and the
+refusal of backward. What this cannot show - link compatibility with a real libnnabla - stays
+open until the plugin is built in an nnabla tree."""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.abspath(os.path.join(HERE, ".."))
+PKG = os.path.join(ROOT, "nnabla-ext-cuda_b200")
+STUB = os.path.join(HERE, "nbla_stub")
+FUNCTIONS = ["DepthwiseConvolution", "BatchNormalization", "FixedPointQuantize", "Pow2Quantize", "MinMaxQuantize"]
+
+
+@pytest.fixture(scope="module")
+def harness(dwlib):
+    out_dir = os.path.join(STUB, "_build")
+    os.makedirs(out_dir, exist_ok=True)
+    so = os.path.join(out_dir, "libdwbnq_nbla_stub.so")
+    srcs = [os.path.join(PKG, "nbla_plugin", "dwbnq_nbla_plugin.cpp"), os.path.join(STUB, "harness.cpp")]
+    deps = srcs + [os.path.join(STUB, "nbla", "stub_core.hpp"), os.path.join(ROOT, "include", "dwbnq.h")]
+    if not os.path.exists(so) or any(os.path.getmtime(d) > os.path.getmtime(so) for d in deps):
+        cmd = ["g++", "-std=c++17", "-O1", "-shared", "-fPIC", "-I" + STUB, "-I" + os.path.join(ROOT, "include")] + srcs + \
+              ["-L" + PKG, "-ldwbnq", "-Wl,-rpath," + PKG, "-o", so]
+        subprocess.run(cmd, check=True, capture_output=True, text=True)
+    lib = ctypes.CDLL(so)
+    lib.stub_last_error.restype = ctypes.c_char_p
+    return lib
+
+
+def test_registration_and_names(harness):
+    for f in FUNCTIONS:
+        for backend in (b"cuda:float", b"cuda:half"):
+            assert harness.stub_registered(f.encode(), backend) == 1, (f, backend)
+    assert harness.stub_registered(b"Convolution", b"cuda:float") == 0
+    buf = ctypes.create_string_buffer(64)
+    assert harness.stub_name(b"cuda:float", 0, buf, 64) == 0
+    assert buf.value == b"FixedPointQuantizeCuda"
+
+
+def test_backward_raises_not_implemented(harness):
+    rc = harness.stub_backward_is_refused(0)
+    assert rc == 100 + 1, rc  # error_code::not_implemented
+    assert b"forward pass only" in harness.stub_last_error()
+
+
+def _p(t):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _shape(a):
+    return (ctypes.c_int64 * a.dim())(*a.shape)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("half", [0, 1], ids=["float", "half"])
+def test_forward_of_the_five_functions(harness, oracle, cuda_device, half):
+    import torch
+    rng = np.random.default_rng(7)
+    dt = torch.float16 if half else torch.float32
+    n, c, hw = 3, 24, 14
+
+    def dev(a):
+        return torch.from_numpy(np.ascontiguousarray(a)).to(cuda_device).to(dt)
+
+    def host(t):
+        return t.float().cpu().numpy() if half else t.cpu().numpy()
+
+    def want16(a):
+        return oracle.to_f16_result(a).astype(np.float32) if half else a
+
+    x = rng.standard_normal((n, c, hw, hw)).astype(np.float32)
+    w = (rng.standard_normal((c, 3, 3)) / 3).astype(np.float32)
+    vec = {k: (rng.random(c) + 0.5).astype(np.float32) for k in ("b", "beta", "gamma", "mean", "var")}
+    if half:  # the oracle computes on the fp16-rounded inputs
+        x, w = x.astype(np.float16).astype(np.float32), w.astype(np.float16).astype(np.float32)
+        vec = {k: v.astype(np.float16).astype(np.float32) for k, v in vec.items()}
+    tx, tw = dev(x), dev(w)
+    tv = {k: dev(v) for k, v in vec.items()}
+    dev_index = cuda_device.index or 0
+
+    # DepthwiseConvolution, stride 2 pad 1
+    y = torch.empty((n, c, 7, 7), device=cuda_device, dtype=dt)
+    rc = harness.stub_dwconv(half, dev_index, _shape(tx), _shape(tw), 4, _p(tx), _p(tw), _p(tv["b"]), _p(y), 1, 2, 1, 1)
+    assert rc == 0, harness.stub_last_error()
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(host(y), want16(oracle.dwconv(x, w, vec["b"], (2, 2), (1, 1))))
+
+    # BatchNormalization, batch_stat=False, with and without gamma / beta
+    for use_beta, use_gamma in ((True, True), (False, True), (True, False)):
+        y = torch.empty_like(tx)
+        rc = harness.stub_bn(half, dev_index, _shape(tx), 4, _p(tx), _p(tv["beta"] if use_beta else None),
+                             _p(tv["gamma"] if use_gamma else None), _p(tv["mean"]), _p(tv["var"]), _p(y),
+                             ctypes.c_float(1e-5), 0)
+        assert rc == 0, harness.stub_last_error()
+        torch.cuda.synchronize()
+        want = oracle.bn_infer(x, vec["beta"] if use_beta else None, vec["gamma"] if use_gamma else None, vec["mean"],
+                               vec["var"], 1e-5)
+        np.testing.assert_array_equal(host(y), want16(want))
+    # batch_stat=True is refused with not_implemented
+    rc = harness.stub_bn(half, dev_index, _shape(tx), 4, _p(tx), _p(tv["beta"]), _p(tv["gamma"]), _p(tv["mean"]),
+                         _p(tv["var"]), _p(y), ctypes.c_float(1e-5), 1)
+    assert rc == 100 + 1
+
+    # FixedPointQuantize / Pow2Quantize
+    y = torch.empty_like(tx)
+    rc = harness.stub_fpq(half, dev_index, tx.numel(), _p(tx), _p(y), 1, 8, ctypes.c_float(2.0 ** -4))
+    assert rc == 0, harness.stub_last_error()
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(host(y), want16(oracle.fpq(x, True, 8, 2.0 ** -4)))
+    rc = harness.stub_pow2(half, dev_index, tx.numel(), _p(tx), _p(y), 1, 1, 8, 1)
+    assert rc == 0, harness.stub_last_error()
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(host(y), want16(oracle.pow2q(x, True, True, 8, 1)))
+
+    # MinMaxQuantize, per-channel ranges [1, C, 1, 1], updated in place
+    qr_min, qr_max = dev(np.zeros(c, np.float32)), dev(np.ones(c, np.float32))
+    ql_min, ql_max = dev(np.zeros(c, np.float32)), dev(np.full(c, 255, np.float32))
+    scratch = torch.empty(64 * c + 1024, device=cuda_device, dtype=torch.float32)
+    harness.stub_set_scratch(_p(scratch))
+    rc = harness.stub_minmax(half, dev_index, _shape(tx), 4, _p(tx), _p(qr_min), _p(qr_max), _p(ql_min), _p(ql_max), _p(y),
+                             ctypes.c_float(0.999), 1, 0, ctypes.c_float(0.01))
+    assert rc == 0, harness.stub_last_error()
+    torch.cuda.synchronize()
+    want, wmin, wmax = oracle.minmaxq(x, np.zeros(c, np.float32), np.ones(c, np.float32), np.zeros(c, np.float32),
+                                      np.full(c, 255, np.float32), 0.999, True, False, 0.01)
+    np.testing.assert_array_equal(host(y), want16(want))
+    if not half:
+        np.testing.assert_array_equal(qr_min.cpu().numpy(), wmin)
+        np.testing.assert_array_equal(qr_max.cpu().numpy(), wmax)
