@@ -465,7 +465,9 @@ def run_own(args):
         from oracle import oracle
         oracle.build()
         nthreads = host_threads()
-        cpu_ips, cpu_dt, cpu_passes = (0.0, 0.0, 0) if args.no_cpu else cpu_stack_images_per_s(
+        # the CPU baseline is timed at N = 1 only (at N > 1 the other ranks would sit idle for it)
+        skip_cpu = args.no_cpu or world > 1
+        cpu_ips, cpu_dt, cpu_passes = (None, 0.0, 0) if skip_cpu else cpu_stack_images_per_s(
             specs, args.cpu_sample, nthreads, args.cpu_seconds)
         bytes_per_image = sum(s.algorithmic_bytes(4, 1) for s in specs)
         line = {
@@ -483,9 +485,10 @@ def run_own(args):
                                    % launches_per_step,
                          "algorithmic_bytes_per_step": bytes_per_step},
             "cpu_baseline": {"value": cpu_ips, "unit": "images/s", "cores": nthreads, "kind": "port",
-                             "sample": "%d images of the layer stack, unfused 3-function chain, %d passes of %.2f s"
-                                       % (args.cpu_sample, cpu_passes, cpu_dt),
-                             "effective_gbs": cpu_ips * bytes_per_image / 1e9},
+                             "sample": ("not timed: measured at N = 1 only" if world > 1 else
+                                        "%d images of the layer stack, unfused 3-function chain, %d passes of %.2f s"
+                                        % (args.cpu_sample, cpu_passes, cpu_dt)),
+                             "effective_gbs": None if cpu_ips is None else cpu_ips * bytes_per_image / 1e9},
             "e2e": {"value": None if args.no_e2e else batch * world * e2e_steps / (e2e_ms / 1e3), "unit": "images/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "wall_ms_per_step": e2e_wall_ms / e2e_steps},

@@ -396,6 +396,40 @@ __device__ __forceinline__ float fpq_apply_fast(float x, const QuantArgs &q) {
   return (SIGNED && xc < 0.0f) ? -v : v;
 }
 
+// The same on a pair: the two directed-rounding steps and the final fma run packed (the
+// packed instructions take every rounding mode), the NaN-keeping clamp stays scalar.
+__device__ __forceinline__ f32x2 fma2_rm(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 r;
+  asm("fma.rm.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ f32x2 add2_rm(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("add.rm.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+struct FpqPacked {
+  f32x2 inv, half, magic, delta, nmagic;
+};
+__device__ __forceinline__ FpqPacked make_fpq_packed(const QuantArgs &q) {
+  FpqPacked f;
+  f.inv = splat2(q.fpq_inv_delta);
+  f.half = splat2(0.5f);
+  f.magic = splat2(8388608.0f);
+  f.delta = splat2(q.fpq_delta);
+  f.nmagic = splat2(q.fpq_nmagic_delta);
+  return f;
+}
+// Unsigned fast form on two values (x0, x1) -> pair.
+__device__ __forceinline__ f32x2 fpq_apply_fast_unsigned2(float x0, float x1, const QuantArgs &q,
+                                                          const FpqPacked &f) {
+  const float c0 = max_nan(min_nan(x0, q.fpq_max), q.fpq_min);
+  const float c1 = max_nan(min_nan(x1, q.fpq_max), q.fpq_min);
+  const f32x2 u = fma2_rm(pack2(c0, c1), f.inv, f.half);
+  const f32x2 kp = add2_rm(u, f.magic);
+  return fma2(kp, f.delta, f.nmagic);
+}
+
 // One epilogue for all modes (QM_MM_REDUCE does not come here).
 template <int QM>
 __device__ __forceinline__ float quant_apply(float v, const QuantArgs &q, const MmCoef &mm) {

@@ -144,8 +144,11 @@ __device__ __noinline__ void plane_exact_block(const FusedArgs &a, int plane, in
 template <int QM, int N>
 __device__ __forceinline__ void plane_quant(float *o, const QuantArgs &q, const MmCoef &mm) {
   if (QM == QM_FPQ_LEAN) {
+    const FpqPacked f = make_fpq_packed(q);
 #pragma unroll
-    for (int j = 0; j < N; ++j) o[j] = fpq_apply_fast<false>(o[j], q);
+    for (int p = 0; p < N / 2; ++p)
+      unpack2(fpq_apply_fast_unsigned2(o[2 * p], o[2 * p + 1], q, f), o[2 * p], o[2 * p + 1]);
+    if (N % 2) o[N - 1] = fpq_apply_fast<false>(o[N - 1], q);
   } else if (QM == QM_FPQ && q.fpq_fast) {
     if (q.fpq_min < 0.0f) {
 #pragma unroll
