@@ -438,6 +438,62 @@ def test_small_plane_kernel_exact_evaluation_planes(oracle, cuda_device, hw, str
         assert_same_bits(got_q, want_q, "pathological parameters, %s" % q["kind"])
 
 
+def test_random_geometries_against_the_oracle(oracle, cuda_device):
+    """A seeded sweep over shapes, kernel sizes, strides, paddings, dilations, multipliers,
+    dtypes and quantizers: whichever kernel family the planner picks must reproduce the
+    oracle bit for bit."""
+    rng = np.random.default_rng(2024)
+    quants = [None, {"kind": "fpq", "sign": False, "n": 8, "delta": 2.0 ** -3},
+              {"kind": "fpq", "sign": True, "n": 5, "delta": 0.17},
+              {"kind": "pow2", "sign": True, "with_zero": True, "n": 6, "m": 1},
+              {"kind": "pow2", "sign": False, "with_zero": False, "n": 4, "m": 0}]
+    sizes = [3, 5, 6, 7, 8, 12, 13, 14, 15, 16, 20, 24, 27, 28, 30, 40, 48, 56, 57, 64, 96, 112]
+    paths_seen = set()
+    for case in range(120):
+        k = int(rng.choice([1, 2, 3, 3, 3, 5, 5, 7]))
+        h, w = int(rng.choice(sizes)), int(rng.choice(sizes))
+        if rng.random() < 0.6:
+            w = h
+        stride = int(rng.choice([1, 1, 2, 3]))
+        dil = int(rng.choice([1, 1, 1, 2]))
+        pad = int(rng.choice([0, k // 2, k // 2, k // 2, k - 1]))
+        mult = int(rng.choice([1, 1, 1, 2]))
+        if h + 2 * pad < dil * (k - 1) + 1 or w + 2 * pad < dil * (k - 1) + 1:
+            continue
+        c = int(rng.choice([1, 3, 8, 17, 32]))
+        n = int(rng.choice([1, 2, 5]))
+        half = rng.random() < 0.3
+        quant = quants[int(rng.integers(len(quants)))]
+        has_bn = rng.random() < 0.8
+        oc = c * mult
+        d = {"x": rng.standard_normal((n, c, h, w)).astype(np.float32),
+             "w": (rng.standard_normal((oc, k, k)) / k).astype(np.float32),
+             "b": rng.standard_normal(oc).astype(np.float32),
+             "mean": rng.standard_normal(oc).astype(np.float32) * 0.3, "var": (rng.random(oc) + 0.5).astype(np.float32),
+             "gamma": (rng.random(oc) * 0.4 + 0.8).astype(np.float32), "beta": rng.standard_normal(oc).astype(np.float32) * 0.3}
+        h16, up = f16_inputs(d) if half else (d, d)
+        y = oracle.dwconv(up["x"], up["w"], up["b"], (stride, stride), (pad, pad), (dil, dil), mult)
+        if has_bn:
+            y = oracle.bn_infer(y, up["beta"], up["gamma"], up["mean"], up["var"], 1e-5)
+        if quant and quant["kind"] == "fpq":
+            y = oracle.fpq(y, quant["sign"], quant["n"], quant["delta"])
+        elif quant:
+            y = oracle.pow2q(y, quant["sign"], quant["with_zero"], quant["n"], quant["m"])
+        want = oracle.to_f16_result(y) if half else y
+        dt = torch.float16 if half else torch.float32
+        t = {k_: dev(v, cuda_device).to(dt) for k_, v in h16.items()}
+        paths_seen.add(ops.fused_plan(t["x"], t["w"], pad=(pad, pad), stride=(stride, stride), dilation=(dil, dil),
+                                      multiplier=mult)["path"])
+        got = ops.fused_dw_bn_quant(t["x"], t["w"], t["b"], t["beta"] if has_bn else None, t["gamma"] if has_bn else None,
+                                    t["mean"] if has_bn else None, t["var"] if has_bn else None, 1e-5, pad=(pad, pad),
+                                    stride=(stride, stride), dilation=(dil, dil), multiplier=mult, quant=quant)
+        torch.cuda.synchronize()
+        ops.check_device_flag()
+        assert_same_bits(got.cpu().numpy(), want, "case %d: n=%d c=%d %dx%d k=%d s=%d p=%d d=%d m=%d half=%s bn=%s q=%s"
+                         % (case, n, c, h, w, k, stride, pad, dil, mult, half, has_bn, quant and quant["kind"]))
+    assert {L.PATH_GENERIC, L.PATH_PLANE}.issubset(paths_seen), paths_seen
+
+
 # ---- the five standalone operators -----------------------------------------------------
 
 def test_standalone_batch_normalization(oracle, cuda_device):
