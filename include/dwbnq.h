@@ -216,12 +216,13 @@ int dwbnq_fused_fwd(const dwbnq_conv_desc *desc, float bn_eps, const dwbnq_quant
  * by cooperative loads, 2 = zero-padded tile filled by TMA tiled loads, 3 = whole planes
  * copied by the bulk copy engine (planes whose row pitch is not a multiple of 16 bytes),
  * 4 = small planes (7x7, 14x14; 3x3 stride 1): one warp per tile of whole planes, bulk copy
- * in, full-width rows per thread, bulk store out.
+ * in, full-width rows per thread, bulk store out, 5 = the same scheme with the geometry as
+ * a run-time argument (3x3 stride 1 on any other plane of even width).
  * *ctas is the number of tiles = CTAs of the launch. Diagnostic only. */
 int dwbnq_fused_plan(const dwbnq_conv_desc *desc, const void *x, const void *y,
                      int *path_out, int *planes_per_cta, int *rows_per_tile,
                      int *threads, int64_t *ctas, int *smem_bytes);
-/* Environment switch DWBNQ_FORCE_PATH=generic|coop|tma|raw|plane (read at each call) and this
+/* Environment switch DWBNQ_FORCE_PATH=generic|coop|tma|raw|plane|planegen (read at each call) and this
  * setter (-1 = automatic) restrict that choice; used by the tests to cover every path. */
 int dwbnq_set_forced_path(int path);
 /* Planner overrides for tuning runs (0 = automatic): planes per tile, 7-row patch blocks

@@ -195,7 +195,7 @@ size_t dwbnq_workspace_bytes(int32_t channels) {
 
 int dwbnq_set_forced_path(int path) {
   clear_error();
-  if (path < PATH_AUTO || path > PATH_PLANE) return fail(DWBNQ_ERR_INVALID_ARG, "path %d is not -1..4", path);
+  if (path < PATH_AUTO || path > PATH_PLANE_GEN) return fail(DWBNQ_ERR_INVALID_ARG, "path %d is not -1..5", path);
   set_forced_path(path);
   return DWBNQ_OK;
 }
@@ -276,7 +276,7 @@ int dwbnq_fused_fwd(const dwbnq_conv_desc *desc, float bn_eps, const dwbnq_quant
     Plan plan;
     st = make_plan(*desc, a.x, a.y, &plan);
     if (st != DWBNQ_OK) return st;
-    const bool store_first = desc->dtype == DWBNQ_F32 && plan.path == PATH_PLANE;
+    const bool store_first = desc->dtype == DWBNQ_F32 && (plan.path == PATH_PLANE || plan.path == PATH_PLANE_GEN);
     st = launch_fused(*desc, a, store_first ? QM_MM_REDUCE_STORE : QM_MM_REDUCE, dev, s);
     if (st != DWBNQ_OK) return st;
     if (store_first) {

@@ -7,6 +7,7 @@
 #include "../../include/dwbnq.h"
 #include "dwbnq_fused.cuh"
 #include "dwbnq_plane.cuh"
+#include "dwbnq_plane_gen.cuh"
 
 namespace dwbnq {
 
@@ -19,11 +20,12 @@ void clear_error();
 int enter_device(int device, int *out);
 
 // ---- fused / dw-conv family (fused.cu) --------------------------------------------------
-enum FusedPath : int { PATH_AUTO = -1, PATH_GENERIC = 0, PATH_COOP = 1, PATH_TMA = 2, PATH_RAW = 3, PATH_PLANE = 4 };
+enum FusedPath : int { PATH_AUTO = -1, PATH_GENERIC = 0, PATH_COOP = 1, PATH_TMA = 2, PATH_RAW = 3, PATH_PLANE = 4, PATH_PLANE_GEN = 5 };
 
 struct Plan {
   int path;
   TileCfg cfg;
+  PlaneGenCfg gen;  // PATH_PLANE_GEN
   long long ctas;
   int threads;
   size_t smem;

@@ -71,6 +71,7 @@ int forced_path() {
     if (!std::strcmp(e, "tma")) return PATH_TMA;
     if (!std::strcmp(e, "raw")) return PATH_RAW;
     if (!std::strcmp(e, "plane")) return PATH_PLANE;
+    if (!std::strcmp(e, "planegen")) return PATH_PLANE_GEN;
   }
   return g_forced_path.load();
 }
@@ -180,6 +181,40 @@ int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan
     return DWBNQ_OK;
   }
   if (forced == PATH_PLANE) return DWBNQ_OK;  // no instantiation for this shape: generic kernel
+
+  // ---- any other plane of even width, 3x3 stride 1: the general-geometry plane kernel -------
+  if (K == 3 && s == 1 && (forced == PATH_AUTO || forced == PATH_PLANE_GEN)) {
+    const bool al = (reinterpret_cast<uintptr_t>(x) % 16) == 0 && (reinterpret_cast<uintptr_t>(y) % 16) == 0;
+    float util = 0.0f;
+    const PlaneGenCfg g = plane_gen_geometry(d.h, d.w, n_planes, d.dtype == DWBNQ_F32 ? 4 : 2, al, &util);
+    // Measured on B200 against the tiled family: the plane scheme wins when its blocks tile
+    // the plane well (at least 80 % of the lane-work lands on real outputs), on small planes,
+    // and whenever the row pitch rules out the TMA tile; otherwise the TMA tile is faster.
+    const bool tma_possible = (reinterpret_cast<uintptr_t>(x) % 16) == 0 &&
+                              ((long long)d.w * (d.dtype == DWBNQ_F32 ? 4 : 2)) % 16 == 0 && encode_tiled_fn() != nullptr;
+    const bool take = forced == PATH_PLANE_GEN || util >= 0.8f || !tma_possible || (long long)d.h * d.w < 256;
+    if (g.n_tiles > 0 && take) {
+      TileCfg &c = plan->cfg;
+      c.P = g.P;
+      c.R = g.r;
+      c.n_rb = g.brb;
+      c.n_strips = g.ncb;
+      c.n_row_tiles = g.bands;
+      c.TH = g.brb * g.r;
+      c.TR = d.h;
+      c.WS = d.w;
+      c.tile_elems = d.h * d.w;
+      c.vec_fill = c.vec_store = al ? 1 : 0;
+      c.n_tiles = g.n_tiles;
+      plan->gen = g;
+      plan->path = PATH_PLANE_GEN;
+      plan->threads = 32;
+      plan->smem = plane_gen_smem_bytes(g, d.dtype == DWBNQ_F32 ? 4 : 2);
+      plan->ctas = g.n_tiles;
+      return DWBNQ_OK;
+    }
+  }
+  if (forced == PATH_PLANE_GEN) return DWBNQ_OK;
   const int n_strips = ceil_div(Wo, S);
   const int n_rb_total = ceil_div(Ho, R);
   // One tile per CTA and several CTAs per SM: the budget keeps four tiles (plus records)
@@ -312,6 +347,12 @@ int launch_fused(const dwbnq_conv_desc &d, FusedArgs &a, int qm, int device, cud
     e = d.dtype == DWBNQ_F32 ? launch_generic_t<float>(qm, a, total, stream)
                              : launch_generic_t<__half>(qm, a, total, stream);
     if (e != cudaSuccess) return fail_cuda(e, "fused_generic_kernel launch");
+    return DWBNQ_OK;
+  }
+  if (plan.path == PATH_PLANE_GEN) {
+    if (qm == QM_FPQ && a.has_bn && a.q.fpq_fast && !(a.q.fpq_min < 0.0f)) qm = QM_FPQ_LEAN;
+    e = launch_plane_gen(d.dtype, qm, a, plan.gen, stream);
+    if (e != cudaSuccess) return fail_cuda(e, "fused_plane_gen_kernel launch");
     return DWBNQ_OK;
   }
   if (plan.path == PATH_PLANE) {

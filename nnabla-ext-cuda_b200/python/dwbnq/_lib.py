@@ -12,7 +12,7 @@ LIB_PATH = os.path.join(_PKG_ROOT, "libdwbnq.so")
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_DEVICE_FLAG = range(7)
 F32, F16 = 0, 1
 Q_NONE, Q_FPQ, Q_POW2, Q_MINMAX = 0, 1, 2, 3
-PATH_AUTO, PATH_GENERIC, PATH_COOP, PATH_TMA, PATH_RAW, PATH_PLANE = -1, 0, 1, 2, 3, 4
+PATH_AUTO, PATH_GENERIC, PATH_COOP, PATH_TMA, PATH_RAW, PATH_PLANE, PATH_PLANE_GEN = -1, 0, 1, 2, 3, 4, 5
 UNIQUE_ID_BYTES = 128
 STATIC_MAX_CHANNELS = 4096
 

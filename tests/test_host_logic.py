@@ -132,7 +132,7 @@ def test_plan_selects_kernel_family(dwlib):
         assert plan(**kw) == dwlib.PATH_GENERIC
     for c, hw, s in ((32, 112, 1), (96, 112, 2), (144, 56, 1), (192, 28, 2), (384, 14, 1), (576, 14, 2), (960, 7, 1)):
         for dt in (dwlib.F32, dwlib.F16):
-            assert plan(dtype=dt, n=4, c=c, h=hw, w=hw, stride_h=s, stride_w=s) in (dwlib.PATH_COOP, dwlib.PATH_TMA, dwlib.PATH_RAW, dwlib.PATH_PLANE)
+            assert plan(dtype=dt, n=4, c=c, h=hw, w=hw, stride_h=s, stride_w=s) in (dwlib.PATH_COOP, dwlib.PATH_TMA, dwlib.PATH_RAW, dwlib.PATH_PLANE, dwlib.PATH_PLANE_GEN)
             assert 1 <= thr.value <= 256  # one patch per thread
             assert smem.value <= 200 * 1024 and p.value >= 1 and th.value >= 1
             planes = 4 * c

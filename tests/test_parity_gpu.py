@@ -438,6 +438,56 @@ def test_small_plane_kernel_exact_evaluation_planes(oracle, cuda_device, hw, str
         assert_same_bits(got_q, want_q, "pathological parameters, %s" % q["kind"])
 
 
+GEN_SHAPES = [(6, 6), (8, 8), (10, 10), (12, 12), (16, 16), (20, 20), (24, 24), (30, 30), (40, 40), (48, 48), (64, 64),
+              (96, 96), (20, 34), (15, 16), (100, 14), (9, 448), (1, 2), (57, 130)]
+
+
+@pytest.mark.parametrize("quant", [SMALL_QUANTS[1], SMALL_QUANTS[3], SMALL_QUANTS[4], SMALL_QUANTS[5]],
+                         ids=["fpq_lean", "fpq_0.3", "pow2", "minmax"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16], ids=["f32", "f16"])
+def test_general_geometry_plane_kernel(oracle, cuda_device, dtype, quant):
+    """3x3 stride 1 on planes of any even width: partly filled last column / row blocks, idle
+    lanes, bands with halo rows, tiles the copy engine cannot take (sizes that are not
+    multiples of 16 bytes), a plane with bias == -0.0, ragged plane counts."""
+    rng = np.random.default_rng(900)
+    for h, w in GEN_SHAPES:
+        for n, c in ((2, 9), (1, 1)):
+            spec = workloads.LayerSpec("gen", n, c, h, w, 3, 1, 1, None)
+            d = _rand_layer(rng, n, c, h, w, 3)
+            if c > 4:
+                d["b"][4] = -0.0
+            if quant["kind"] == "minmax":
+                d.update(qr_min=np.zeros(c, np.float32), qr_max=np.ones(c, np.float32), ql_min=np.zeros(c, np.float32),
+                         ql_max=np.full(c, 255, np.float32))
+            h16, up = f16_inputs(d) if dtype == torch.float16 else (d, d)
+            want, _, extra = oracle_fused(oracle, up, spec, quant)
+            got, t = run_fused(h16, spec, cuda_device, quant, dtype=dtype, path=L.PATH_PLANE_GEN)
+            plan = ops.fused_plan(dev(h16["x"], cuda_device), dev(h16["w"], cuda_device), pad=(1, 1), stride=(1, 1))
+            assert plan["path"] == L.PATH_PLANE_GEN, (h, w, plan)
+            if dtype == torch.float16:
+                want = oracle.to_f16_result(want)
+            assert_same_bits(got, want, "%dx%d n=%d c=%d" % (h, w, n, c))
+            if extra is not None and dtype == torch.float32:
+                assert_same_bits(t["qr_min"].cpu().numpy(), extra[0], "qr_min")
+                assert_same_bits(t["qr_max"].cpu().numpy(), extra[1], "qr_max")
+    # unaligned x / y
+    h, w, n, c = 24, 24, 2, 5
+    spec = workloads.LayerSpec("gen_unaligned", n, c, h, w, 3, 1, 1, None)
+    d = _rand_layer(rng, n, c, h, w, 3)
+    q = SMALL_QUANTS[1]
+    want, _, _ = oracle_fused(oracle, d, spec, q)
+    xbuf = torch.empty(d["x"].size + 1, device=cuda_device)
+    xbuf[1:] = dev(d["x"].ravel(), cuda_device)
+    ybuf = torch.empty(want.size + 1, device=cuda_device)
+    y = ybuf[1:].view(want.shape)
+    t = {k: dev(v, cuda_device) for k, v in d.items()}
+    ops.set_forced_path(L.PATH_PLANE_GEN)
+    ops.fused_dw_bn_quant(xbuf[1:].view(n, c, h, w), t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], 1e-5,
+                          (1, 1), (1, 1), quant=q, out=y)
+    if dtype == torch.float32:
+        assert_same_bits(y.cpu().numpy(), want, "unaligned x / y")
+
+
 def test_random_geometries_against_the_oracle(oracle, cuda_device):
     """A seeded sweep over shapes, kernel sizes, strides, paddings, dilations, multipliers,
     dtypes and quantizers: whichever kernel family the planner picks must reproduce the
@@ -491,7 +541,7 @@ def test_random_geometries_against_the_oracle(oracle, cuda_device):
         ops.check_device_flag()
         assert_same_bits(got.cpu().numpy(), want, "case %d: n=%d c=%d %dx%d k=%d s=%d p=%d d=%d m=%d half=%s bn=%s q=%s"
                          % (case, n, c, h, w, k, stride, pad, dil, mult, half, has_bn, quant and quant["kind"]))
-    assert {L.PATH_GENERIC, L.PATH_PLANE}.issubset(paths_seen), paths_seen
+    assert {L.PATH_GENERIC, L.PATH_PLANE, L.PATH_PLANE_GEN}.issubset(paths_seen), paths_seen
 
 
 # ---- the five standalone operators -----------------------------------------------------
