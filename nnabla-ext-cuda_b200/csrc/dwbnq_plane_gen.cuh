@@ -25,7 +25,9 @@ struct PlaneGenCfg {
   int ncb;      // column blocks per plane: ceil(W / wb)
   int brb;      // row blocks per tile (band): brb * ncb <= 32
   int bands;    // tiles per plane along rows; 1 = whole planes
-  int P;        // planes per tile (1 when bands > 1)
+  int gmode;    // H % r == 0: a tile is brb consecutive row blocks of the whole [planes * H, W]
+                // image, across plane boundaries (planes are adjacent in memory), so no lane idles
+  int P;        // planes per tile (1 when bands > 1 or gmode)
   int n_tiles;  // CTAs
   int bulk;     // x and y 16-byte aligned
 };
@@ -34,7 +36,7 @@ constexpr int kGenMaxW = 16;  // widest block of any instantiation (stash sizing
 
 // tile (P planes x (brb * 7 + 2 halo rows when banded) rows x W) | stash | mbarrier
 __host__ __device__ inline size_t plane_gen_smem_bytes(const PlaneGenCfg &g, int elem_size) {
-  const int rows = g.bands > 1 ? g.brb * g.r + 2 : g.H;
+  const int rows = (g.bands > 1 || g.gmode) ? g.brb * g.r + 2 : g.H;
   size_t s = (size_t)g.P * rows * g.W * elem_size;
   s = (s + 15) / 16 * 16;
   s += (size_t)32 * plane_stash_elems(g.wb) * elem_size;
@@ -76,7 +78,7 @@ __global__ void __launch_bounds__(32, 16)
   constexpr int SW = plane_stash_elems(W);
   const int PW = g.W, H = g.H;
   const int PE = H * PW;
-  const bool banded = g.bands > 1;
+  const bool banded = g.bands > 1 || g.gmode != 0;  // tile = a band of rows with a halo row each side
   const int TB = g.brb * R;                       // rows per band
   const int halo = banded ? 1 : 0;
   const int TE = (banded ? TB + 2 : H) * PW;      // shared-memory elements per plane of the tile
@@ -91,16 +93,22 @@ __global__ void __launch_bounds__(32, 16)
 
   const int lane = threadIdx.x;
   const int n_planes = (int)(a.n * a.OC);
-  const int plane0 = (banded ? blockIdx.x / g.bands : blockIdx.x) * g.P;
-  const int r0 = banded ? (blockIdx.x % g.bands) * TB : 0;  // first plane row of the tile
-  const int pv = min(g.P, n_planes - plane0);
+  const int nrb = H / R;  // gmode: row blocks per plane
+  // first / one-past-last row of the tile, of what is loaded, and of what is stored, as row
+  // indices of the whole [n_planes * H, W] image
+  const int plane0 = g.gmode ? 0 : (g.bands > 1 ? blockIdx.x / g.bands : blockIdx.x) * g.P;
+  const int r0 = g.gmode ? 0 : (g.bands > 1 ? (blockIdx.x % g.bands) * TB : 0);  // first plane row (not gmode)
+  const int pv = g.gmode ? 1 : min(g.P, n_planes - plane0);
+  const long long grow0 = g.gmode ? (long long)blockIdx.x * TB : (long long)plane0 * H + r0;
+  const long long glimit = g.gmode ? (long long)n_planes * H : (long long)plane0 * H + (banded ? H : pv * H);
+  const long long gfloor = g.gmode ? 0 : (long long)plane0 * H;
+  const long long in_first = banded ? max(grow0 - 1, gfloor) : grow0;
+  const int in_rows = (int)((banded ? min(grow0 + TB + 1, glimit) : glimit) - in_first);
+  const int out_rows = (int)(banded ? min((long long)TB, glimit - grow0) : glimit - grow0);
   T *y = static_cast<T *>(a.y);
-  const int in_first = banded ? max(r0 - 1, 0) : 0;
-  const int in_rows = banded ? min(r0 + TB + 1, H) - in_first : pv * H;
-  const int out_rows = banded ? min(TB, H - r0) : pv * H;
-  const T *in_src = static_cast<const T *>(a.x) + (long long)plane0 * PE + (long long)in_first * PW;
-  T *in_dst = tile + (banded ? (in_first - (r0 - 1)) * PW : 0);
-  T *dst = y + (long long)plane0 * PE + (long long)r0 * PW;
+  const T *in_src = static_cast<const T *>(a.x) + in_first * PW;
+  T *in_dst = tile + (banded ? (int)(in_first - (grow0 - 1)) * PW : 0);
+  T *dst = y + grow0 * PW;
   const unsigned int bytes = (unsigned int)((size_t)in_rows * PW * sizeof(T));
   const unsigned int obytes = (unsigned int)((size_t)out_rows * PW * sizeof(T));
   // the copy engine needs 16-byte aligned addresses and sizes on both sides
@@ -125,9 +133,12 @@ __global__ void __launch_bounds__(32, 16)
   const int rem = slot - pl * tpp;
   const int rb = rem / g.ncb;
   const int cb = rem - rb * g.ncb;
-  const int row_first = r0 + rb * R;             // first plane row of the block
-  const bool active = lane < g.P * tpp && pl < pv && row_first < H;
-  const int plane = (lane < g.P * tpp && pl < pv) ? plane0 + pl : n_planes - 1;
+  // the block's plane and its first row inside that plane
+  const long long gb = (long long)blockIdx.x * g.brb + rb;  // gmode: row block of the whole image
+  const bool in_range = lane < g.P * tpp && (g.gmode ? gb < (long long)n_planes * nrb : pl < pv);
+  const int plane = !in_range ? n_planes - 1 : g.gmode ? (int)(gb / nrb) : plane0 + pl;
+  const int row_first = g.gmode ? (int)(gb % nrb) * R : r0 + rb * R;
+  const bool active = in_range && row_first < H;
   const int ch = plane % a.OC;
   const int vw = min(W, PW - cb * W);            // valid columns of the block (even)
   const int vp = vw / 2;                         // valid pairs

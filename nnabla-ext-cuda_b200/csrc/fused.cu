@@ -187,12 +187,14 @@ int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan
     const bool al = (reinterpret_cast<uintptr_t>(x) % 16) == 0 && (reinterpret_cast<uintptr_t>(y) % 16) == 0;
     float util = 0.0f;
     const PlaneGenCfg g = plane_gen_geometry(d.h, d.w, n_planes, d.dtype == DWBNQ_F32 ? 4 : 2, al, &util);
-    // Measured on B200 against the tiled family: the plane scheme wins when its blocks tile
-    // the plane well (at least 80 % of the lane-work lands on real outputs), on small planes,
-    // and whenever the row pitch rules out the TMA tile; otherwise the TMA tile is faster.
+    // Measured on B200 against the TMA tile family (planes 6..96 wide): the plane scheme wins on
+    // small planes (up to 32 x 32), whenever the row pitch rules out the TMA tile, and with the
+    // 7 x 14 blocks when they tile the plane well; on mid-size planes that only the 8 x 8
+    // blocks tile, the TMA tile is 10-20 % faster.
     const bool tma_possible = (reinterpret_cast<uintptr_t>(x) % 16) == 0 &&
                               ((long long)d.w * (d.dtype == DWBNQ_F32 ? 4 : 2)) % 16 == 0 && encode_tiled_fn() != nullptr;
-    const bool take = forced == PATH_PLANE_GEN || util >= 0.8f || !tma_possible || (long long)d.h * d.w < 256;
+    const bool take = forced == PATH_PLANE_GEN || !tma_possible || (long long)d.h * d.w <= 1024 ||
+                      (util >= 0.8f && g.wb == 14);
     if (g.n_tiles > 0 && take) {
       TileCfg &c = plan->cfg;
       c.P = g.P;

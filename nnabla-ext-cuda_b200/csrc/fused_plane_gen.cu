@@ -13,12 +13,25 @@ PlaneGenCfg geometry_for(int wb, int r, int h, int w, long long n_planes, bool a
   g.W = w;
   g.wb = wb;
   g.r = r;
-  g.ncb = g.brb = g.bands = g.P = g.n_tiles = g.bulk = 0;
+  g.ncb = g.brb = g.bands = g.gmode = g.P = g.n_tiles = g.bulk = 0;
   *util = 0.0f;
   if (h < 1 || w < 2 || (w % 2) != 0 || w > wb * 32 || n_planes < 1) return g;
   g.ncb = (w + wb - 1) / wb;
   const int nrb_total = (h + r - 1) / r;
   int brb = 32 / g.ncb;
+  if (h % r == 0 && n_planes * (long long)nrb_total < 0x7fffffffLL) {
+    // row blocks line up across planes: bands of the whole image, every tile full
+    const long long blocks = n_planes * (long long)nrb_total;
+    if (brb > blocks) brb = (int)blocks;
+    g.gmode = 1;
+    g.brb = brb;
+    g.bands = 1;
+    g.P = 1;
+    g.n_tiles = (int)((blocks + brb - 1) / brb);
+    g.bulk = aligned ? 1 : 0;
+    *util = (float)((double)w / ((double)g.ncb * wb) * (double)(g.brb * g.ncb) / 32.0);
+    return g;
+  }
   if (brb > nrb_total) brb = nrb_total;
   g.bands = (nrb_total + brb - 1) / brb;
   g.brb = (nrb_total + g.bands - 1) / g.bands;  // even out the bands
