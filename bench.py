@@ -481,7 +481,7 @@ def run_own(args):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": measured_traffic(args, batch), "peak_kind": peak_kind,
                          "frac_of_nominal_8000": achieved / 8000.0,
-                         "kernel": "fused_tiled_kernel + fused_plane_kernel (all %d launches of a step)"
+                         "kernel": "fused_plane_kernel + fused_plane_s2_kernel (all %d launches of a step, per GPU)"
                                    % launches_per_step,
                          "algorithmic_bytes_per_step": bytes_per_step},
             "cpu_baseline": {"value": cpu_ips, "unit": "images/s", "cores": nthreads, "kind": "port",
