@@ -139,6 +139,18 @@ def test_plan_selects_kernel_family(dwlib):
             ho = (hw + 2 - 3) // s + 1
             assert ctas.value % (-(-planes // p.value)) == 0          # tiles = plane groups x row tiles
             assert (ctas.value // (-(-planes // p.value))) * th.value >= ho
+    # which family serves which shape (3x3 / 5x5, pad k/2, aligned pointers)
+    for hw, s, k in ((7, 1, 3), (14, 1, 3), (28, 1, 3), (56, 1, 3), (112, 1, 3), (14, 2, 3), (28, 2, 3), (56, 2, 3),
+                     (112, 2, 3), (14, 1, 5), (56, 1, 5), (112, 1, 5)):
+        assert plan(n=4, c=8, h=hw, w=hw, stride_h=s, stride_w=s, kh=k, kw=k, pad_h=k // 2, pad_w=k // 2) == dwlib.PATH_PLANE
+        assert thr.value == 32 and smem.value <= 32 * 1024
+    for hw in (6, 8, 10, 12, 16, 24, 30, 32):  # small planes, or a row pitch the TMA tile cannot take
+        assert plan(n=4, c=8, h=hw, w=hw) == dwlib.PATH_PLANE_GEN, hw
+    for hw in (40, 48, 80, 96):  # mid-size planes only the 8 x 8 blocks tile: the TMA tile where a driver offers it
+        assert plan(n=4, c=8, h=hw, w=hw) in (dwlib.PATH_TMA, dwlib.PATH_PLANE_GEN), hw
+    assert plan(n=4, c=8, h=42, w=42) == dwlib.PATH_PLANE_GEN   # 7 x 14 blocks tile it exactly
+    assert plan(n=4, c=8, h=15, w=15) in (dwlib.PATH_RAW, dwlib.PATH_COOP)  # odd width
+    assert plan(n=4, c=8, h=7, w=7, kh=5, kw=5, pad_h=2, pad_w=2) in (dwlib.PATH_RAW, dwlib.PATH_COOP)
     assert lib.dwbnq_set_forced_path(dwlib.PATH_GENERIC) == dwlib.OK
     assert plan(n=4, c=32, h=112, w=112) == dwlib.PATH_GENERIC
     assert lib.dwbnq_set_forced_path(dwlib.PATH_AUTO) == dwlib.OK
