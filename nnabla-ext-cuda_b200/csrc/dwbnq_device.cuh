@@ -203,20 +203,9 @@ static __device__ __noinline__ float pow2_round_exact(unsigned int a, const uint
   return pow2_of_int(e + (up ? 1 : 0));
 }
 
-__device__ __forceinline__ float pow2_apply(float x, const QuantArgs &p) {
-  const unsigned int a = __float_as_uint(x) & 0x7fffffffu;
-  const float ax = __uint_as_float(a);
+// Clamp / prune / sign rules of the quantizer on q = 2^round(log2f(|x|)).
+__device__ __forceinline__ float pow2_finish(float q, float x, float ax, const QuantArgs &p) {
   const bool neg = x < 0.0f;
-  // Common case, branch-free: away from the threshold the rounded exponent is e + 1 exactly
-  // when the mantissa is above sqrt(2)'s, i.e. adding (2^23 - 0x3504f3) carries into the
-  // exponent field. With p_min a normal number (p_fast) zeros and subnormals need no care
-  // either: whatever tiny power of two comes out is below p_min and the rules below decide
-  // on |x| alone. Infinity carries to infinity. Only NaN and the threshold window are left.
-  const int d = (int)(a & 0x007fffffu) - 0x3504f3;
-  const bool rare = (unsigned int)(d + p.p_window) <= 2u * (unsigned int)p.p_window || a > 0x7f800000u ||
-                    !p.p_fast;
-  float q = __uint_as_float((a + 0x004afb0du) & 0x7f800000u);
-  if (rare) q = pow2_round_exact(a, p.p_table, p.p_window);
   if (q > p.p_max) {
     q = p.p_max;
   } else if (q < p.p_min && p.p_with_zero) {
@@ -232,6 +221,48 @@ __device__ __forceinline__ float pow2_apply(float x, const QuantArgs &p) {
     q = neg ? p.p_min : q;
   }
   return q;
+}
+// Common case, branch-free: away from the threshold the rounded exponent is e + 1 exactly
+// when the mantissa is above sqrt(2)'s, i.e. adding (2^23 - 0x3504f3) carries into the
+// exponent field. With p_min a normal number (p_fast) zeros and subnormals need no care
+// either: whatever tiny power of two comes out is below p_min and the rules above decide on
+// |x| alone. Infinity carries to infinity. Only NaN and the threshold window are `rare`.
+__device__ __forceinline__ float pow2_round_fast(unsigned int a, const QuantArgs &p, bool *rare) {
+  const int d = (int)(a & 0x007fffffu) - 0x3504f3;
+  *rare = (unsigned int)(d + p.p_window) <= 2u * (unsigned int)p.p_window || a > 0x7f800000u || !p.p_fast;
+  return __uint_as_float((a + 0x004afb0du) & 0x7f800000u);
+}
+__device__ __forceinline__ float pow2_apply(float x, const QuantArgs &p) {
+  const unsigned int a = __float_as_uint(x) & 0x7fffffffu;
+  bool rare;
+  float q = pow2_round_fast(a, p, &rare);
+  if (rare) q = pow2_round_exact(a, p.p_table, p.p_window);
+  return pow2_finish(q, x, __uint_as_float(a), p);
+}
+// N values at once: the fast roundings of all N are independent straight-line code (the
+// scheduler interleaves them); the out-of-line exact rounding is reached through ONE branch
+// per group, taken when any of the N is a rare pattern.
+template <int N>
+__device__ __forceinline__ void pow2_apply_n(float *v, const QuantArgs &p) {
+  float q[N];
+  bool any = false;
+#pragma unroll
+  for (int j = 0; j < N; ++j) {
+    bool rare;
+    q[j] = pow2_round_fast(__float_as_uint(v[j]) & 0x7fffffffu, p, &rare);
+    any = any || rare;
+  }
+  if (any) {
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      const unsigned int a = __float_as_uint(v[j]) & 0x7fffffffu;
+      bool rare;
+      (void)pow2_round_fast(a, p, &rare);
+      if (rare) q[j] = pow2_round_exact(a, p.p_table, p.p_window);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < N; ++j) v[j] = pow2_finish(q[j], v[j], fabsf(v[j]), p);
 }
 
 // ---- MinMaxQuantize, quantize step ---------------------------------------------------

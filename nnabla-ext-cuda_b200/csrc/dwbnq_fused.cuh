@@ -699,8 +699,5 @@ constexpr int kRowsPerPatch = 7;
 template <typename T, int K>
 cudaError_t launch_tiled(int stride, int qm, int mode, const CUtensorMap &tmap, const FusedArgs &a,
                          const TileCfg &c, int ctas, int threads, size_t smem, cudaStream_t stream);
-// Resident CTAs per SM of that instantiation with `threads` threads and `smem` bytes.
-template <typename T, int K>
-cudaError_t tiled_occupancy(int stride, int qm, int mode, int threads, size_t smem, int *ctas_per_sm);
 
 }  // namespace dwbnq

@@ -55,17 +55,4 @@ cudaError_t launch_tiled<DWBNQ_INST_T, DWBNQ_INST_K>(int stride, int qm, int mod
   return cudaGetLastError();
 }
 
-template <>
-cudaError_t tiled_occupancy<DWBNQ_INST_T, DWBNQ_INST_K>(int stride, int qm, int mode, int threads,
-                                                        size_t smem, int *ctas_per_sm) {
-  TiledKernel kern = pick<DWBNQ_INST_T, DWBNQ_INST_K>(stride, qm, mode);
-  if (!kern) return cudaErrorInvalidValue;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return e;
-  // all of the unified L1 / shared memory as shared memory: the tiles are the working set
-  e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-  if (e != cudaSuccess) return e;
-  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(ctas_per_sm, kern, threads, smem);
-}
-
 }  // namespace dwbnq

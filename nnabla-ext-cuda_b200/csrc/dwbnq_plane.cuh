@@ -157,6 +157,8 @@ __device__ __forceinline__ void plane_quant(float *o, const QuantArgs &q, const 
 #pragma unroll
       for (int j = 0; j < N; ++j) o[j] = fpq_apply_fast<false>(o[j], q);
     }
+  } else if (QM == QM_POW2) {
+    pow2_apply_n<N>(o, q);
   } else {
 #pragma unroll
     for (int j = 0; j < N; ++j) o[j] = quant_apply<QM>(o[j], q, mm);

@@ -40,8 +40,12 @@ __global__ void __launch_bounds__(kThreads) quant_flat_kernel(const T *x, T *y,
     for (int u = 0; u < U; ++u) Vec16<T>::load_stream(x + (v + u * step) * S, e[u]);
 #pragma unroll
     for (int u = 0; u < U; ++u) {
+      if (QM == QM_POW2) {
+        pow2_apply_n<S>(e[u], q);
+      } else {
 #pragma unroll
-      for (int j = 0; j < S; ++j) e[u][j] = quant_apply<QM>(e[u][j], q, none);
+        for (int j = 0; j < S; ++j) e[u][j] = quant_apply<QM>(e[u][j], q, none);
+      }
       Vec16<T>::store_stream(y + (v + u * step) * S, e[u]);
     }
   }
