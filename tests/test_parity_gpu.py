@@ -544,6 +544,47 @@ def test_random_geometries_against_the_oracle(oracle, cuda_device):
     assert {L.PATH_GENERIC, L.PATH_PLANE, L.PATH_PLANE_GEN}.issubset(paths_seen), paths_seen
 
 
+def test_concurrent_host_threads_on_their_own_streams(oracle, cuda_device):
+    """The entry points are re-entrant: four host threads, each on its own stream, run
+    different layers at the same time (the reference allows concurrent function calls on one
+    device: test/test_multi_thread_training.cpp); every result must match the oracle."""
+    import threading
+    rng = np.random.default_rng(77)
+    jobs = []
+    for hw, k, stride, quant in ((14, 3, 1, SMALL_QUANTS[1]), (28, 3, 2, SMALL_QUANTS[4]), (24, 3, 1, SMALL_QUANTS[2]),
+                                 (15, 5, 1, SMALL_QUANTS[1])):
+        n, c = 4, 24
+        spec = workloads.LayerSpec("mt", n, c, hw, hw, k, stride, k // 2, None)
+        d = _rand_layer(rng, n, c, hw, hw, k)
+        want, _, _ = oracle_fused(oracle, d, spec, quant)
+        jobs.append((spec, {k_: dev(v, cuda_device) for k_, v in d.items()}, quant, want))
+    results, errors = [None] * len(jobs), []
+
+    def work(i):
+        try:
+            spec, t, quant, _ = jobs[i]
+            stream = torch.cuda.Stream(cuda_device)
+            with torch.cuda.stream(stream):
+                y = None
+                for _ in range(20):
+                    y = ops.fused_dw_bn_quant(t["x"], t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], spec.bn_eps,
+                                              pad=(spec.pad, spec.pad), stride=(spec.stride, spec.stride), quant=quant)
+                stream.synchronize()
+                results[i] = y.cpu().numpy()
+        except Exception as e:  # surfaced in the main thread
+            errors.append(e)
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(len(jobs))]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join()
+    assert not errors, errors
+    ops.check_device_flag()
+    for i, (_, _, _, want) in enumerate(jobs):
+        assert_same_bits(results[i], want, "thread %d" % i)
+
+
 # ---- the five standalone operators -----------------------------------------------------
 
 def test_standalone_batch_normalization(oracle, cuda_device):
