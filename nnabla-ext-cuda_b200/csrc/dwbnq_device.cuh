@@ -356,7 +356,7 @@ __device__ __forceinline__ float min3f(float a, float b, float c) {
 // 2^30; everything else (zeros, infinities, NaN, extreme magnitudes) takes __fdiv_rn.
 struct BnPacked {
   f32x2 nmean, scale, rcp, nstd, beta, nz;
-  float stdvar;  // for the out-of-range path
+  float stdvar, stdvar_hi;  // for the out-of-range path (low / high lane of a pair)
   float glo;     // lower guard on |a|: 2^-100, or +inf when stdvar itself is out of range
 };
 #define DWBNQ_DIV_GUARD_LO 7.888609052e-31f /* 2^-100 */
@@ -370,18 +370,36 @@ __device__ __forceinline__ BnPacked make_bn_packed(const BnCoef &c, f32x2 nz) {
   b.nstd = splat2(-c.stdvar);
   b.beta = splat2(c.beta);
   b.nz = nz;
-  b.stdvar = c.stdvar;
+  b.stdvar = b.stdvar_hi = c.stdvar;
   const bool safe = c.stdvar >= 9.31322574615478515625e-10f && c.stdvar <= 1073741824.0f;
   b.glo = safe ? DWBNQ_DIV_GUARD_LO : __uint_as_float(0x7f800000u);
+  return b;
+}
+// Two channels side by side: the low lane of every pair belongs to channel lo, the high lane
+// to channel hi.
+__device__ __forceinline__ BnPacked make_bn_packed2(const BnCoef &lo, const BnCoef &hi, f32x2 nz) {
+  BnPacked b;
+  b.nmean = pack2(-lo.mean, -hi.mean);
+  b.scale = pack2(lo.scale, hi.scale);
+  b.rcp = pack2(__frcp_rn(lo.stdvar), __frcp_rn(hi.stdvar));
+  b.nstd = pack2(-lo.stdvar, -hi.stdvar);
+  b.beta = pack2(lo.beta, hi.beta);
+  b.nz = nz;
+  b.stdvar = lo.stdvar;
+  b.stdvar_hi = hi.stdvar;
+  const bool safe = fminf(lo.stdvar, hi.stdvar) >= 9.31322574615478515625e-10f &&
+                    fmaxf(lo.stdvar, hi.stdvar) <= 1073741824.0f;  // (a NaN fails both)
+  b.glo = (safe && lo.stdvar == lo.stdvar && hi.stdvar == hi.stdvar) ? DWBNQ_DIV_GUARD_LO
+                                                                     : __uint_as_float(0x7f800000u);
   return b;
 }
 
 // The IEEE quotients of the out-of-range path, out of line: the path is cold and the inline
 // expansion of a correctly rounded division is several times the size of the whole BN step.
-static __device__ __noinline__ f32x2 bn_div_cold(f32x2 a, float stdvar) {
+static __device__ __noinline__ f32x2 bn_div_cold(f32x2 a, float stdvar_lo, float stdvar_hi) {
   float lo, hi;
   unpack2(a, lo, hi);
-  return pack2(__fdiv_rn(lo, stdvar), __fdiv_rn(hi, stdvar));
+  return pack2(__fdiv_rn(lo, stdvar_lo), __fdiv_rn(hi, stdvar_hi));
 }
 
 // In-place BN of NP pairs.
@@ -404,7 +422,7 @@ __device__ __forceinline__ void bn_apply_packed(f32x2 *v, const BnPacked &b) {
   }
   if (!(mn > b.glo && mx < DWBNQ_DIV_GUARD_HI)) {
 #pragma unroll
-    for (int p = 0; p < NP; ++p) v[p] = bn_div_cold(a[p], b.stdvar);
+    for (int p = 0; p < NP; ++p) v[p] = bn_div_cold(a[p], b.stdvar, b.stdvar_hi);
   }
 #pragma unroll
   for (int p = 0; p < NP; ++p) v[p] = add2(v[p], b.beta);

@@ -702,6 +702,178 @@ __global__ void __launch_bounds__(32, 16)
   }
 }
 
+// ---- 7x7 planes, 3x3 stride 1: two planes per thread --------------------------------------
+// A 7-wide row has an odd number of elements, so pairing neighbours along the row wastes a
+// lane and needs scalar loads. Here the two lanes of a pair are the SAME position of two
+// different planes (thread t owns planes t and t + 32 of a 64-plane tile): the weights and
+// BN operands of a pair are (channel of plane t, channel of plane t + 32), a shifted tap is
+// just another column, and - with whole planes per thread - every halo tap is skipped at
+// compile time (columns) or by a uniform test (rows), which is the contract's own rule: no
+// zero padding enters, so there is no exact-evaluation fall-back, no stash and no barrier
+// inside the loop. Input rows stream through the thread as in fused_plane_kernel.
+template <typename T, int QM>
+__global__ void __launch_bounds__(32, 16)
+    fused_plane_pair7_kernel(const __grid_constant__ FusedArgs a, const PlaneCfg c) {
+  constexpr int W = 7, H = 7, PE = 49, P = 64;
+
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  T *tile = reinterpret_cast<T *>(smem_raw);
+  constexpr size_t tile_bytes = ((size_t)P * PE * sizeof(T) + 15) / 16 * 16;
+  unsigned long long *bar = reinterpret_cast<unsigned long long *>(smem_raw + tile_bytes);
+
+  const int lane = threadIdx.x;
+  const int n_planes = (int)(a.n * a.OC);
+  const int plane0 = blockIdx.x * P;
+  const int pv = min(P, n_planes - plane0);
+  T *y = static_cast<T *>(a.y);
+  const T *in_src = static_cast<const T *>(a.x) + (long long)plane0 * PE;
+  T *dst = y + (long long)plane0 * PE;
+  const unsigned int bytes = (unsigned int)(pv * PE * sizeof(T));
+  const bool async_tile = c.bulk != 0 && (bytes % 16) == 0;
+
+  if (lane == 0) {
+    mbar_init(bar, 1);
+    mbar_fence_init();
+    if (async_tile) {
+      mbar_expect_tx(bar, bytes);
+      bulk_load_1d(tile, in_src, bytes, bar);
+    }
+  }
+
+  // planes (lane, lane + 32) -> the (low, high) lanes of every pair
+  const bool act0 = lane < pv, act1 = lane + 32 < pv;
+  const int ch0 = (act0 ? plane0 + lane : n_planes - 1) % a.OC;
+  const int ch1 = (act1 ? plane0 + lane + 32 : n_planes - 1) % a.OC;
+  const f32x2 nz = negzero2();
+  f32x2 w2[9];
+  {
+    const T *w0 = static_cast<const T *>(a.w) + (long long)ch0 * 9;
+    const T *w1 = static_cast<const T *>(a.w) + (long long)ch1 * 9;
+#pragma unroll
+    for (int i = 0; i < 9; ++i) {
+      w2[i] = pack2(Elem<T>::to_f32(w0[i]), Elem<T>::to_f32(w1[i]));
+      pin(w2[i]);
+    }
+  }
+  const T *bp = static_cast<const T *>(a.b);
+  f32x2 bias2 = pack2(bp ? Elem<T>::to_f32(bp[ch0]) : 0.0f, bp ? Elem<T>::to_f32(bp[ch1]) : 0.0f);
+  pin(bias2);
+  BnPacked bnp;
+  if (QM == QM_FPQ_LEAN || a.has_bn) bnp = make_bn_packed2(load_bn<T>(a, ch0), load_bn<T>(a, ch1), nz);
+  const MmCoef mm0 = load_mm<QM>(a, ch0), mm1 = load_mm<QM>(a, ch1);
+
+  if (!async_tile) {
+    const int n = pv * PE;
+    for (int i = lane; i < n; i += 32) tile[i] = in_src[i];
+  }
+  __syncwarp();
+  if (async_tile && !mbar_wait_bounded(bar, 0)) {
+    if (a.flag) atomicExch(a.flag, 1);
+    return;
+  }
+
+  T *p0 = tile + lane * PE;         // lane stride 49 words: conflict-free
+  T *p1 = tile + (lane + 32) * PE;
+  float lo0 = __uint_as_float(0x7f800000u), hi0 = __uint_as_float(0xff800000u), lo1 = lo0, hi1 = hi0;
+  f32x2 acc0[W], acc1[W];
+
+  // step k: input row k - 1 finishes output row k - 2 (ky = 2), continues row k - 1 (ky = 1)
+  // and starts row k (ky = 0); rows -1 and 7 do not exist and their taps are skipped
+  auto step = [&](int k, f32x2 *fin, f32x2 *mid) {
+    const bool have_row = k >= 1 && k <= H;
+    f32x2 X[W];
+    if (have_row) {
+#pragma unroll
+      for (int j = 0; j < W; ++j)
+        X[j] = pack2(Elem<T>::to_f32(p0[(k - 1) * W + j]), Elem<T>::to_f32(p1[(k - 1) * W + j]));
+    }
+    auto taps = [&](f32x2 *acc, int ky, bool init) {
+#pragma unroll
+      for (int j = 0; j < W; ++j) {
+        f32x2 v = init ? bias2 : acc[j];
+#pragma unroll
+        for (int kx = 0; kx < 3; ++kx) {
+          if (j + kx - 1 < 0 || j + kx - 1 >= W) continue;  // outside the plane: tap skipped
+          v = tap_add2<T>(v, w2[ky * 3 + kx], X[j + kx - 1], nz);
+        }
+        acc[j] = v;
+      }
+    };
+    if (k >= 2) {
+      if (have_row) taps(fin, 2, false);
+      if (QM == QM_FPQ_LEAN || a.has_bn) bn_apply_packed<W>(fin, bnp);
+      float o[2 * W];  // o[2j] = plane 0, o[2j + 1] = plane 1, column j
+#pragma unroll
+      for (int j = 0; j < W; ++j) unpack2(fin[j], o[2 * j], o[2 * j + 1]);
+      if (qm_reduces(QM)) {
+#pragma unroll
+        for (int j = 0; j < W; ++j) {
+          lo0 = fminf(lo0, o[2 * j]);
+          hi0 = fmaxf(hi0, o[2 * j]);
+          lo1 = fminf(lo1, o[2 * j + 1]);
+          hi1 = fmaxf(hi1, o[2 * j + 1]);
+        }
+      }
+      if (qm_stores(QM)) {
+        if (QM == QM_MM_APPLY) {
+#pragma unroll
+          for (int j = 0; j < W; ++j) {
+            o[2 * j] = mm_apply(o[2 * j], mm0);
+            o[2 * j + 1] = mm_apply(o[2 * j + 1], mm1);
+          }
+        } else {
+          plane_quant<QM, 2 * W>(o, a.q, mm0);
+        }
+#pragma unroll
+        for (int j = 0; j < W; ++j) {
+          if (act0) p0[(k - 2) * W + j] = Elem<T>::from_f32(o[2 * j]);
+          if (act1) p1[(k - 2) * W + j] = Elem<T>::from_f32(o[2 * j + 1]);
+        }
+      }
+    }
+    if (k >= 1 && k <= H && have_row) taps(mid, 1, false);
+    if (k <= H - 1) {
+      if (have_row) {
+        taps(fin, 0, true);
+      } else {
+#pragma unroll
+        for (int j = 0; j < W; ++j) fin[j] = bias2;
+      }
+    }
+  };
+
+#pragma unroll 1
+  for (int k = 0; k < H + 2; k += 2) {
+    step(k, acc0, acc1);
+    if (k + 1 < H + 2) step(k + 1, acc1, acc0);
+  }
+
+  if (qm_reduces(QM)) {
+    if (act0) {
+      atomicMin(a.q.mm_enc_min + ch0, enc_ordered(lo0));
+      atomicMax(a.q.mm_enc_max + ch0, enc_ordered(hi0));
+    }
+    if (act1) {
+      atomicMin(a.q.mm_enc_min + ch1, enc_ordered(lo1));
+      atomicMax(a.q.mm_enc_max + ch1, enc_ordered(hi1));
+    }
+  }
+  if (!qm_stores(QM)) return;
+
+  if (async_tile) {
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) bulk_store_1d_and_wait(dst, tile, bytes);
+  } else {
+    __syncwarp();
+    const int n = pv * PE;
+    for (int i = lane; i < n; i += 32) dst[i] = tile[i];
+  }
+}
+__host__ __device__ constexpr size_t plane_pair7_smem_bytes(int elem_size) {
+  return ((size_t)64 * 49 * elem_size + 15) / 16 * 16 + 16;
+}
+
 // ---- stride 2 ---------------------------------------------------------------------------
 // Thread block of 14 x 14 inputs = 7 x 7 outputs; a tile is NRB x NCB blocks: whole planes
 // (NBND == 1) or one band of 14 * NRB full-width input rows plus the row above it
@@ -906,6 +1078,7 @@ __host__ inline PlaneGeom plane_geom(int k, int h, int w, int stride) {
 }
 __host__ inline size_t plane_launch_smem(int k, int hw, int stride, int elem_size) {
   const PlaneGeom g = plane_geom(k, hw, hw, stride);
+  if (stride == 1 && k == 3 && hw == 7) return plane_pair7_smem_bytes(elem_size);
   if (stride == 1) return plane_smem_bytes(k, g.w, g.nrb, g.ncb, g.bands, elem_size);
   return plane_s2_smem_bytes(g.nrb, g.ncb, g.bands, elem_size);
 }

@@ -159,7 +159,7 @@ int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan
   const PlaneGeom pg = plane_geom(K, d.h, d.w, s);
   if (pg.tpp > 0 && (forced == PATH_AUTO || forced == PATH_PLANE)) {
     TileCfg &c = plan->cfg;
-    c.P = 32 / pg.tpp;
+    c.P = (K == 3 && s == 1 && d.w == 7) ? 64 : 32 / pg.tpp;  // 7x7: two planes per thread
     c.R = kPlaneRows;
     c.n_rb = pg.nrb;
     c.n_strips = pg.ncb;

@@ -35,6 +35,20 @@ PlaneKernel pick_kxk(int qm) {
   return nullptr;
 }
 
+template <typename T>
+PlaneKernel pick_pair7(int qm) {
+  switch (qm) {
+    case QM_NONE: return fused_plane_pair7_kernel<T, QM_NONE>;
+    case QM_FPQ: return fused_plane_pair7_kernel<T, QM_FPQ>;
+    case QM_POW2: return fused_plane_pair7_kernel<T, QM_POW2>;
+    case QM_MM_APPLY: return fused_plane_pair7_kernel<T, QM_MM_APPLY>;
+    case QM_MM_REDUCE: return fused_plane_pair7_kernel<T, QM_MM_REDUCE>;
+    case QM_FPQ_LEAN: return fused_plane_pair7_kernel<T, QM_FPQ_LEAN>;
+    case QM_MM_REDUCE_STORE: return fused_plane_pair7_kernel<T, QM_MM_REDUCE_STORE>;
+  }
+  return nullptr;
+}
+
 template <typename T, int NRB, int NCB, int NBND>
 PlaneKernel pick_s2(int qm) {
   switch (qm) {
@@ -54,7 +68,7 @@ cudaError_t launch_t(int k, int hw, int stride, int qm, const FusedArgs &a, cons
                      cudaStream_t stream) {
   PlaneKernel kern = nullptr;
   if (stride == 1 && k == 3) {
-    if (hw == 7) kern = pick_s1<T, 7, 1, 1, 1>(qm);
+    if (hw == 7) kern = pick_pair7<T>(qm);
     else if (hw == 14) kern = pick_s1<T, 14, 2, 1, 1>(qm);
     else if (hw == 28) kern = pick_s1<T, 14, 4, 2, 1>(qm);
     else if (hw == 56) kern = pick_s1<T, 14, 8, 4, 1>(qm);
