@@ -145,6 +145,32 @@ def execute(nodes, tensors, comm=None):
     return t
 
 
+class GraphRunner:
+    """A node list captured once into a CUDA graph and replayed: the host launches one graph
+    instead of one kernel per node (what matters at small batches, where the kernels are
+    shorter than their launches). The tensors dict passed in is the graph's memory: write new
+    inputs into its tensors in place (``copy_``), call ``replay()``, read the outputs from it.
+    Nodes that need a communicator are not captured (run them with ``execute``)."""
+
+    def __init__(self, nodes, tensors, warmup=2):
+        import torch
+        self.nodes, self.tensors = list(nodes), tensors
+        dev = next(t.device for t in tensors.values() if t is not None)
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(max(1, warmup)):  # first-call set-up (tables, symbol look-ups) and allocations
+                execute(self.nodes, self.tensors)
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=side):
+                execute(self.nodes, self.tensors)
+        torch.cuda.current_stream(dev).wait_stream(side)
+
+    def replay(self):
+        self.graph.replay()
+        return self.tensors
+
+
 def _bn_inputs(rest, args):
     """BatchNormalization inputs after x: [beta, gamma, mean, var] with beta / gamma absent
     when no_bias / no_scale (src/nbla/cuda/function/generic/batch_normalization.cu:120-123)."""

@@ -89,3 +89,28 @@ def test_fused_graph_equals_unfused_graph_and_oracle(oracle, cuda_device):
             np.testing.assert_array_equal(t_fused["qr_max"].cpu().numpy(), qmax)
         got = t_fused["y"].cpu().numpy()
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), spec.name
+
+
+@pytest.mark.gpu
+def test_graph_runner_replays_the_fused_layers(oracle, cuda_device):
+    """The fused node list captured into a CUDA graph: replays reproduce the eager result,
+    also after the input tensor has been overwritten in place."""
+    import torch
+    from dwbnq import workloads
+    spec = workloads.cfg1(n=2)[6]  # 28x28 stride 2
+    d = workloads.make_layer_data(spec)
+    nodes = graph.fuse_dw_bn_quant(_chain("FixedPointQuantize", {"sign": False, "n": 8, "delta": 2.0 ** -3}), ["y"])
+    nodes[0]["conv_args"].update(pad=(spec.pad,) * 2, stride=(spec.stride,) * 2)
+    names = ["x", "w", "b", "beta", "gamma", "mean", "var"]
+    t = {k: torch.from_numpy(d[k].copy()).to(cuda_device) for k in names}
+    runner = graph.GraphRunner(nodes, t)
+    q = {"kind": "fpq", "sign": False, "n": 8, "delta": 2.0 ** -3}
+    for scale in (1.0, -0.5):
+        x = (d["x"] * np.float32(scale)).astype(np.float32)
+        t["x"].copy_(torch.from_numpy(x))
+        out = runner.replay()
+        torch.cuda.synchronize()
+        want = oracle.fused_layer(x, d["w"], d["b"], d["beta"], d["gamma"], d["mean"], d["var"], 1e-5,
+                                  (spec.stride,) * 2, (spec.pad,) * 2, q, nthreads=oracle.max_threads())
+        got = out["y"].cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), scale
