@@ -73,6 +73,12 @@ __device__ __forceinline__ void bulk_store_1d_and_wait(void *dst, const void *sr
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
+// Programmatic dependent launch (no-ops when the launch does not carry the attribute): a grid
+// lets its successor in the stream become resident early, and itself touches global memory
+// only after its predecessor has completed and flushed.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_for_predecessor() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -243,9 +249,13 @@ __global__ void __launch_bounds__(32, 16)
   const unsigned int obytes = (unsigned int)((NBND > 1 ? TB : pv * H) * PW * sizeof(T));
   const bool async_tile = c.bulk != 0 && (bytes % 16) == 0 && (obytes % 16) == 0;
 
+  pdl_launch_dependents();
   if (lane == 0) {
     mbar_init(bar, 1);
     mbar_fence_init();
+  }
+  pdl_wait_for_predecessor();  // nothing global is read or written before this point
+  if (lane == 0) {
     if (async_tile) {
       mbar_expect_tx(bar, bytes);
       bulk_load_1d(in_dst, in_src, bytes, bar);
@@ -475,9 +485,13 @@ __global__ void __launch_bounds__(32, 16)
   const unsigned int obytes = (unsigned int)((NBND > 1 ? TB : pv * H) * PW * sizeof(T));
   const bool async_tile = c.bulk != 0 && (bytes % 16) == 0 && (obytes % 16) == 0;
 
+  pdl_launch_dependents();
   if (lane == 0) {
     mbar_init(bar, 1);
     mbar_fence_init();
+  }
+  pdl_wait_for_predecessor();  // nothing global is read or written before this point
+  if (lane == 0) {
     if (async_tile) {
       mbar_expect_tx(bar, bytes);
       bulk_load_1d(in_dst, in_src, bytes, bar);
@@ -731,9 +745,13 @@ __global__ void __launch_bounds__(32, 16)
   const unsigned int bytes = (unsigned int)(pv * PE * sizeof(T));
   const bool async_tile = c.bulk != 0 && (bytes % 16) == 0;
 
+  pdl_launch_dependents();
   if (lane == 0) {
     mbar_init(bar, 1);
     mbar_fence_init();
+  }
+  pdl_wait_for_predecessor();  // nothing global is read or written before this point
+  if (lane == 0) {
     if (async_tile) {
       mbar_expect_tx(bar, bytes);
       bulk_load_1d(tile, in_src, bytes, bar);
@@ -923,9 +941,13 @@ __global__ void __launch_bounds__(32, 7)
   const unsigned int obytes = (unsigned int)(out_elems * sizeof(T));
   const bool async_tile = c.bulk != 0 && (bytes % 16) == 0 && (obytes % 16) == 0;
 
+  pdl_launch_dependents();
   if (lane == 0) {
     mbar_init(bar, 1);
     mbar_fence_init();
+  }
+  pdl_wait_for_predecessor();  // nothing global is read or written before this point
+  if (lane == 0) {
     if (async_tile) {
       mbar_expect_tx(bar, bytes);
       bulk_load_1d(in_dst, in_src, bytes, bar);

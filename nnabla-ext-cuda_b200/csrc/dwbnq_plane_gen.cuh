@@ -118,9 +118,13 @@ __global__ void __launch_bounds__(32, 16)
                           (((size_t)(in_dst - tile) * sizeof(T)) % 16) == 0 &&
                           (((size_t)halo * PW * sizeof(T)) % 16) == 0;
 
+  pdl_launch_dependents();
   if (lane == 0) {
     mbar_init(bar, 1);
     mbar_fence_init();
+  }
+  pdl_wait_for_predecessor();  // nothing global is read or written before this point
+  if (lane == 0) {
     if (async_tile) {
       mbar_expect_tx(bar, bytes);
       bulk_load_1d(in_dst, in_src, bytes, bar);
