@@ -4,9 +4,20 @@
 #include <cstdio>
 #include <cstring>
 
+#include <cstdlib>
+
 #include "dwbnq_internal.h"
 
 namespace dwbnq {
+
+bool pdl_enabled() {
+  static const bool enabled = [] {
+    const char *e = std::getenv("DWBNQ_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return enabled;
+}
+
 
 namespace {
 thread_local char g_err[512] = "";

@@ -43,6 +43,12 @@ struct QuantArgs {
   unsigned int *mm_enc_min, *mm_enc_max;
 };
 
+// Programmatic dependent launch (no-ops when the launch does not carry the attribute): a grid
+// lets its successor in the stream become resident early, and itself touches global memory
+// only after its predecessor has completed and flushed.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_for_predecessor() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- element traits -----------------------------------------------------------------
 
 template <typename T> struct Elem;

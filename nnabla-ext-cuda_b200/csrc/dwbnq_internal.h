@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 #include "../../include/dwbnq.h"
 #include "dwbnq_fused.cuh"
 #include "dwbnq_plane.cuh"
@@ -18,6 +20,27 @@ void clear_error();
 
 // Makes `device` current (-1 keeps the current one) and returns its ordinal in *out.
 int enter_device(int device, int *out);
+
+// Launch with programmatic stream serialization: the grid may become resident while its
+// predecessor in the stream drains; the kernels of this library wait for the predecessor's
+// completion (griddepcontrol.wait) before their first global access, so stream order holds.
+// DWBNQ_PDL=0 in the environment launches plainly.
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                       Args &&... args) {
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = grid;
+  lc.blockDim = block;
+  lc.dynamicSmemBytes = smem;
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = attr;
+  lc.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&lc, kern, std::forward<Args>(args)...);
+}
 
 // ---- fused / dw-conv family (fused.cu) --------------------------------------------------
 enum FusedPath : int { PATH_AUTO = -1, PATH_GENERIC = 0, PATH_COOP = 1, PATH_TMA = 2, PATH_RAW = 3, PATH_PLANE = 4, PATH_PLANE_GEN = 5 };

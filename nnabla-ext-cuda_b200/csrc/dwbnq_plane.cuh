@@ -73,12 +73,6 @@ __device__ __forceinline__ void bulk_store_1d_and_wait(void *dst, const void *sr
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
-// Programmatic dependent launch (no-ops when the launch does not carry the attribute): a grid
-// lets its successor in the stream become resident early, and itself touches global memory
-// only after its predecessor has completed and flushed.
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait_for_predecessor() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

@@ -28,6 +28,8 @@ __global__ void __launch_bounds__(kThreads) quant_flat_kernel(const T *x, T *y,
                                                               const long long size, const int vec_ok,
                                                               const QuantArgs q) {
   constexpr int S = Elem<T>::VEC;
+  pdl_launch_dependents();
+  pdl_wait_for_predecessor();
   const MmCoef none{1.0f, 0.0f, 0.0f};
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long step = (long long)gridDim.x * blockDim.x;
@@ -66,14 +68,14 @@ int launch_quant_flat(int dtype, long long size, const QuantArgs &q, const void 
                       cudaStream_t stream) {
   if (size == 0) return DWBNQ_OK;
   const int vec_ok = aligned16(x) && aligned16(y);
+  cudaError_t e;
   if (dtype == DWBNQ_F32) {
-    quant_flat_kernel<float, QM><<<grid_for((size + 3) / 4, 16), kThreads, 0, stream>>>(
-        static_cast<const float *>(x), static_cast<float *>(y), size, vec_ok, q);
+    e = launch_pdl(quant_flat_kernel<float, QM>, dim3(grid_for((size + 3) / 4, 16)), dim3(kThreads), 0, stream,
+                   static_cast<const float *>(x), static_cast<float *>(y), size, vec_ok, q);
   } else {
-    quant_flat_kernel<__half, QM><<<grid_for((size + 7) / 8, 16), kThreads, 0, stream>>>(
-        static_cast<const __half *>(x), static_cast<__half *>(y), size, vec_ok, q);
+    e = launch_pdl(quant_flat_kernel<__half, QM>, dim3(grid_for((size + 7) / 8, 16)), dim3(kThreads), 0, stream,
+                   static_cast<const __half *>(x), static_cast<__half *>(y), size, vec_ok, q);
   }
-  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail_cuda(e, "quant_flat_kernel launch");
   return DWBNQ_OK;
 }
@@ -144,6 +146,8 @@ __global__ void __launch_bounds__(kThreads)
     chan_vec_kernel(const T *x, T *y, const long long total, const int C,
                     const long long size2, const ChanArgs a) {
   constexpr int S = Elem<T>::VEC;
+  pdl_launch_dependents();
+  pdl_wait_for_predecessor();
   const long long n_vec = total / S;
   const long long v_begin = (long long)blockIdx.x * kChanChunkVecs;
   const long long v_end = min(n_vec, v_begin + kChanChunkVecs);
@@ -260,7 +264,9 @@ int launch_chan_t(long long size0, long long C, long long size2, const T *x, T *
   const bool vec = aligned16(x) && aligned16(y) && size2 >= S && size2 <= 0x7fffffffLL && C <= 0x7fffffffLL;
   const long long chunks = (total / S + kChanChunkVecs - 1) / kChanChunkVecs;
   if (vec && chunks >= 1 && chunks <= 0x7fffffffLL) {
-    chan_vec_kernel<T, OP><<<(unsigned int)chunks, kThreads, 0, stream>>>(x, y, total, (int)C, size2, a);
+    const cudaError_t le = launch_pdl(chan_vec_kernel<T, OP>, dim3((unsigned int)chunks), dim3(kThreads), 0, stream, x, y,
+                                      total, (int)C, size2, a);
+    if (le != cudaSuccess) return fail_cuda(le, "per-channel element-wise kernel launch");
   } else {
     chan_scalar_kernel<T, OP><<<grid_for(total, 16), kThreads, 0, stream>>>(x, y, total, (int)C, size2, a);
   }

@@ -7,29 +7,6 @@ namespace dwbnq {
 
 namespace {
 
-// One-warp CTAs, launched so that the grid may become resident while its predecessor in the
-// stream drains (programmatic stream serialization; the kernels wait for the predecessor's
-// completion before their first global access). DWBNQ_PDL=0 in the environment turns it off.
-template <typename Kern, typename Cfg>
-cudaError_t launch_pdl(Kern kern, unsigned int grid, size_t smem, cudaStream_t stream, const FusedArgs &a,
-                       const Cfg &cfg) {
-  static const bool enabled = [] {
-    const char *e = std::getenv("DWBNQ_PDL");
-    return !(e && e[0] == '0');
-  }();
-  cudaLaunchConfig_t lc = {};
-  lc.gridDim = dim3(grid, 1, 1);
-  lc.blockDim = dim3(32, 1, 1);
-  lc.dynamicSmemBytes = smem;
-  lc.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  lc.attrs = attr;
-  lc.numAttrs = enabled ? 1 : 0;
-  return cudaLaunchKernelEx(&lc, kern, a, cfg);
-}
-
 typedef void (*PlaneKernel)(const FusedArgs, const PlaneCfg);
 
 template <typename T, int W, int NRB, int NCB, int NBND>
@@ -115,7 +92,7 @@ cudaError_t launch_t(int k, int hw, int stride, int qm, const FusedArgs &a, cons
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
                                        cudaSharedmemCarveoutMaxShared);
   if (e != cudaSuccess) return e;
-  return launch_pdl(kern, (unsigned int)c.n_tiles, smem, stream, a, c);
+  return launch_pdl(kern, dim3((unsigned int)c.n_tiles), dim3(32), smem, stream, a, c);
 }
 
 }  // namespace

@@ -62,29 +62,6 @@ PlaneGenCfg plane_gen_geometry(int h, int w, long long n_planes, int elem_size, 
 
 namespace {
 
-// One-warp CTAs, launched so that the grid may become resident while its predecessor in the
-// stream drains (programmatic stream serialization; the kernels wait for the predecessor's
-// completion before their first global access). DWBNQ_PDL=0 in the environment turns it off.
-template <typename Kern, typename Cfg>
-cudaError_t launch_pdl(Kern kern, unsigned int grid, size_t smem, cudaStream_t stream, const FusedArgs &a,
-                       const Cfg &cfg) {
-  static const bool enabled = [] {
-    const char *e = std::getenv("DWBNQ_PDL");
-    return !(e && e[0] == '0');
-  }();
-  cudaLaunchConfig_t lc = {};
-  lc.gridDim = dim3(grid, 1, 1);
-  lc.blockDim = dim3(32, 1, 1);
-  lc.dynamicSmemBytes = smem;
-  lc.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  lc.attrs = attr;
-  lc.numAttrs = enabled ? 1 : 0;
-  return cudaLaunchKernelEx(&lc, kern, a, cfg);
-}
-
 typedef void (*GenKernel)(const FusedArgs, const PlaneGenCfg);
 
 template <typename T, int WB, int R>
@@ -116,7 +93,7 @@ cudaError_t launch_plane_gen(int dtype, int qm, const FusedArgs &a, const PlaneG
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
                                        cudaSharedmemCarveoutMaxShared);
   if (e != cudaSuccess) return e;
-  return launch_pdl(kern, (unsigned int)g.n_tiles, smem, stream, a, g);
+  return launch_pdl(kern, dim3((unsigned int)g.n_tiles), dim3(32), smem, stream, a, g);
 }
 
 }  // namespace dwbnq
