@@ -469,6 +469,8 @@ def run_own(args):
         skip_cpu = args.no_cpu or world > 1
         cpu_ips, cpu_dt, cpu_passes = (None, 0.0, 0) if skip_cpu else cpu_stack_images_per_s(
             specs, args.cpu_sample, nthreads, args.cpu_seconds)
+        # the same chain on one core (nnabla's CPU functions are plain loops), 8 images
+        cpu_1core = None if skip_cpu else cpu_stack_images_per_s(specs, 8, 1, 2.0)[0]
         bytes_per_image = sum(s.algorithmic_bytes(4, 1) for s in specs)
         line = {
             "metric": "images_per_s", "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
@@ -488,7 +490,8 @@ def run_own(args):
                              "sample": ("not timed: measured at N = 1 only" if world > 1 else
                                         "%d images of the layer stack, unfused 3-function chain, %d passes of %.2f s"
                                         % (args.cpu_sample, cpu_passes, cpu_dt)),
-                             "effective_gbs": None if cpu_ips is None else cpu_ips * bytes_per_image / 1e9},
+                             "effective_gbs": None if cpu_ips is None else cpu_ips * bytes_per_image / 1e9,
+                             "value_one_core": cpu_1core},
             "e2e": {"value": None if args.no_e2e else batch * world * e2e_steps / (e2e_ms / 1e3), "unit": "images/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "wall_ms_per_step": e2e_wall_ms / e2e_steps},
