@@ -4,6 +4,8 @@
 // entry point works) where NCCL is absent.
 #include <dlfcn.h>
 
+#include <cstdlib>
+
 #include <chrono>
 #include <cstring>
 #include <mutex>
@@ -40,7 +42,11 @@ NcclApi g_nccl;
 std::once_flag g_nccl_once;
 
 void load_nccl() {
-  const char *names[] = {"libnccl.so.2", "libnccl.so"};
+  // DWBNQ_NCCL_LIB names the library to load instead of the default sonames (a site build
+  // of NCCL, or the stand-in the tests use to exercise the error and deadline paths).
+  const char *override_path = std::getenv("DWBNQ_NCCL_LIB");
+  const char *names[] = {override_path && *override_path ? override_path : "libnccl.so.2", "libnccl.so.2",
+                         "libnccl.so"};
   for (const char *n : names) {
     g_nccl.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
     if (g_nccl.handle) break;
