@@ -1,6 +1,8 @@
 // Fused DepthwiseConvolution -> BatchNormalization(inference) -> quantizer kernels.
 //
-// Two kernel families share one arithmetic core:
+// The kernel families of the library share one arithmetic core. The plane kernels of
+// dwbnq_plane.cuh / dwbnq_plane_gen.cuh serve 3x3 (stride 1 and 2) and 5x5 (stride 1) on the
+// plane sizes they tile; this header holds the two families behind them:
 //  * fused_generic_kernel: one thread per output element, taps read straight from global
 //    memory, out-of-bounds taps skipped. Handles every geometry the reference accepts
 //    (any kernel size, stride, pad, dilation, multiplier, 1-D) and is also the in-kernel
@@ -9,16 +11,17 @@
 //  * fused_tiled_kernel: a CTA owns one tile of `P` (n, c) planes x a band of output rows.
 //    The input of the tile is staged in shared memory by the copy engines - one TMA tiled
 //    box load per plane (halo rows / columns arrive as zeros), or, where the row pitch is
-//    not a multiple of 16 bytes (14x14, 7x7 planes), one bulk async copy of the contiguous
+//    not a multiple of 16 bytes (odd widths), one bulk async copy of the contiguous
 //    planes with the halo masked when the window is read - while the threads build the
 //    per-plane parameter records; several resident CTAs per SM overlap one tile's
 //    arithmetic with the next tile's copy. Each thread computes R x VEC output patches
 //    from a rolling register window on packed f32x2 pairs, applies BN and the quantizer in
 //    registers and stores 16-byte vectors.
 //
-// Arithmetic contract (identical in both families): accumulator starts at the bias,
-// taps in ky-major / kx-minor order, product and sum rounded separately (no FMA),
-// then the BN and quantizer steps of dwbnq_device.cuh.
+// Arithmetic contract (identical in every family): accumulator starts at the bias, taps in
+// ky-major / kx-minor order, product and sum rounded separately (never contracted; for
+// binary16 inputs the product is exact in fp32, so a fused multiply-add is the same
+// operation), then the BN and quantizer steps of dwbnq_device.cuh.
 #pragma once
 
 #include <cuda.h>
