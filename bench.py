@@ -266,6 +266,31 @@ def run_standalone_ops(args):
     print(json.dumps(line), flush=True)
 
 
+def bind_to_gpu_numa_node(torch, index):
+    """Restricts this process to the CPUs of the NUMA node its GPU hangs off, so that the
+    pinned host buffers of the end-to-end pass (allocated afterwards, first touched here) are
+    local to the GPU's PCIe root. Returns the node, or None when the topology is not exposed."""
+    try:
+        p = torch.cuda.get_device_properties(index)
+        bdf = "%04x:%02x:%02x.0" % (p.pci_domain_id, p.pci_bus_id, p.pci_device_id)
+        with open("/sys/bus/pci/devices/%s/numa_node" % bdf) as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open("/sys/devices/system/node/node%d/cpulist" % node) as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if len(allowed) >= 2:
+            os.sched_setaffinity(0, allowed)
+            return node
+    except Exception:
+        pass
+    return None
+
+
 def run_own(args):
     import torch
     import torch.distributed as dist
@@ -279,6 +304,7 @@ def run_own(args):
         raise SystemExit("bench.py needs a CUDA device: the dwbnq path has no CPU fallback")
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
+    numa = bind_to_gpu_numa_node(torch, local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     half = args.workload == "cfg4" or args.dtype == "f16"
@@ -477,7 +503,7 @@ def run_own(args):
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16" if half else "f32", "data": "synthetic",
             "config": {"workload": workload_name(args), "batch_per_gpu": batch, "global_batch": batch * world,
-                       "layers": len(specs), "parallelism": "batch-sharded x%d" % world, "launch": "cuda graph" if graph is not None else "stream",
+                       "layers": len(specs), "parallelism": "batch-sharded x%d" % world, "numa_node": numa, "launch": "cuda graph" if graph is not None else "stream",
                        "l2": "per-step working set %.1f GB >> 126 MB L2; every layer has its own buffers"
                              % (bytes_per_step / 1e9)},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
