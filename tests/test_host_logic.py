@@ -199,3 +199,53 @@ def test_no_cpu_fallback_without_a_gpu(dwlib):
     from dwbnq import ops
     with pytest.raises(ValueError):
         ops.fixed_point_quantize(torch.zeros(4))
+
+
+def test_planner_invariants_over_random_descriptors(dwlib):
+    """Whatever the geometry, the planner answers OK with a launchable plan (or the reference's
+    own limit error): shared memory below the 48 KB a launch gets without opting in for the
+    one-warp families, one warp per CTA there, enough tiles to cover every plane and row."""
+    lib = dwlib.lib()
+    rng = np.random.default_rng(99)
+    path, p, th, thr, smem = (ctypes.c_int() for _ in range(5))
+    ctas = ctypes.c_int64()
+    seen = set()
+    for _ in range(3000):
+        k = int(rng.choice([1, 3, 3, 3, 5, 7]))
+        h, w = int(rng.integers(1, 130)), int(rng.integers(1, 130))
+        if rng.random() < 0.5:
+            w = h
+        s = int(rng.choice([1, 1, 2, 3]))
+        pad = int(rng.choice([0, k // 2, k // 2, k - 1]))
+        dil = int(rng.choice([1, 1, 2]))
+        mult = int(rng.choice([1, 1, 2]))
+        n, c = int(rng.integers(1, 300)), int(rng.integers(1, 700))
+        dt = int(rng.choice([dwlib.F32, dwlib.F16]))
+        d = _desc(dwlib, dtype=dt, n=n, c=c, h=h, w=w, kh=k, kw=k, stride_h=s, stride_w=s, pad_h=pad, pad_w=pad,
+                  dil_h=dil, dil_w=dil, multiplier=mult)
+        al = int(rng.choice([0, 4]))  # aligned or 4 bytes off
+        st = lib.dwbnq_fused_plan(ctypes.byref(d), ctypes.c_void_p(4096 + al), ctypes.c_void_p(8192 + al),
+                                  ctypes.byref(path), ctypes.byref(p), ctypes.byref(th), ctypes.byref(thr),
+                                  ctypes.byref(ctas), ctypes.byref(smem))
+        fits = h + 2 * pad >= dil * (k - 1) + 1 and w + 2 * pad >= dil * (k - 1) + 1
+        if not fits:
+            assert st == dwlib.ERR_INVALID_ARG
+            continue
+        if c * mult * k * k > 65536:
+            assert st == dwlib.ERR_UNSUPPORTED
+            continue
+        assert st == dwlib.OK, lib.dwbnq_last_error_string()
+        seen.add(path.value)
+        if path.value == dwlib.PATH_GENERIC:
+            continue
+        ho = (h + 2 * pad - dil * (k - 1) - 1) // s + 1
+        assert p.value >= 1 and th.value >= 1 and ctas.value >= 1
+        if path.value in (dwlib.PATH_PLANE, dwlib.PATH_PLANE_GEN):
+            assert thr.value == 32 and smem.value <= 48 * 1024, (h, w, k, s, smem.value)
+        else:
+            assert 1 <= thr.value <= 256 and smem.value <= 200 * 1024
+        assert k in (3, 5) and s in (1, 2) and pad == k // 2 and dil == 1 and mult == 1
+        if path.value != dwlib.PATH_PLANE_GEN:  # (its bands run across plane boundaries)
+            groups = -(-n * c // p.value)
+            assert ctas.value % groups == 0 and (ctas.value // groups) * th.value >= ho, (h, w, k, s, path.value)
+    assert {dwlib.PATH_GENERIC, dwlib.PATH_PLANE, dwlib.PATH_PLANE_GEN}.issubset(seen), seen
