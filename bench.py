@@ -401,6 +401,13 @@ def run_own(args):
     barrier()
     t_end = time.time()
     elapsed_ms = ev0.elapsed_time(ev1)
+    # A short timed region sees too few of the 50 ms clock samples: keep the same load running,
+    # untimed, until 0.4 s of it have been sampled.
+    while time.time() - t_begin < 0.4:
+        step()
+        torch.cuda.synchronize()
+        t_end = time.time()
+    barrier()
     clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
     ops.check_device_flag()
 
