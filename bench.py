@@ -403,7 +403,7 @@ def run_own(args):
     elapsed_ms = ev0.elapsed_time(ev1)
     # A short timed region sees too few of the 50 ms clock samples: keep the same load running,
     # untimed, until 0.4 s of it have been sampled.
-    while time.time() - t_begin < 0.4:
+    while comm is None and time.time() - t_begin < 0.4:  # (steps with a collective must stay in lock step)
         step()
         torch.cuda.synchronize()
         t_end = time.time()
