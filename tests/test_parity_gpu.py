@@ -585,6 +585,38 @@ def test_concurrent_host_threads_on_their_own_streams(oracle, cuda_device):
         assert_same_bits(results[i], want, "thread %d" % i)
 
 
+def test_in_place_tiles_give_the_same_bits_every_time(oracle, cuda_device):
+    """The plane kernels overwrite their tile in place; the rows and columns one thread reads
+    and another writes are ordered by warp barriers. A missing ordering would show up as a
+    timing-dependent result: every shape is run 60 times, with a second stream keeping the
+    GPU busy to perturb the timing, and every run must reproduce the oracle's bits."""
+    rng = np.random.default_rng(4242)
+    noise = torch.empty(64 << 20, dtype=torch.float32, device=cuda_device)
+    side = torch.cuda.Stream(cuda_device)
+    cases = [(14, 3, 1), (28, 3, 1), (56, 3, 1), (112, 3, 1), (28, 5, 1), (56, 5, 1), (28, 3, 2), (112, 3, 2), (24, 3, 1),
+             (40, 3, 1), (30, 3, 1)]
+    for hw, k, stride in cases:
+        n, c = 4, 24
+        spec = workloads.LayerSpec("rep", n, c, hw, hw, k, stride, k // 2, None)
+        d = _rand_layer(rng, n, c, hw, hw, k)
+        q = SMALL_QUANTS[1]
+        want, _, _ = oracle_fused(oracle, d, spec, q)
+        t = {k_: dev(v, cuda_device) for k_, v in d.items()}
+        ops.set_forced_path(L.PATH_PLANE_GEN if hw in (24, 40, 30) else L.PATH_AUTO)
+        wb = torch.from_numpy(want).to(cuda_device)
+        bad = 0
+        for i in range(60):
+            if i % 3 == 0:
+                with torch.cuda.stream(side):
+                    noise.mul_(1.0001)
+            y = ops.fused_dw_bn_quant(t["x"], t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], 1e-5,
+                                      pad=(k // 2,) * 2, stride=(stride,) * 2, quant=q)
+            bad += int((y.view(torch.int32) != wb.view(torch.int32)).sum().item())
+        torch.cuda.synchronize()
+        ops.check_device_flag()
+        assert bad == 0, (hw, k, stride, bad)
+
+
 # ---- the five standalone operators -----------------------------------------------------
 
 def test_standalone_batch_normalization(oracle, cuda_device):
