@@ -218,18 +218,11 @@ int dwbnq_fused_fwd(const dwbnq_conv_desc *desc, float bn_eps, const dwbnq_quant
  * 4 = small planes (7x7, 14x14; 3x3 stride 1): one warp per tile of whole planes, bulk copy
  * in, full-width rows per thread, bulk store out, 5 = the same scheme with the geometry as
  * a run-time argument (3x3 stride 1 on any other plane of even width).
- * *ctas is the number of tiles = CTAs of the launch. Diagnostic only. */
+ * *ctas is the number of tiles = CTAs of the launch. Diagnostic only. (The switches that
+ * restrict this choice for tests and tuning runs are declared in dwbnq_debug.h.) */
 int dwbnq_fused_plan(const dwbnq_conv_desc *desc, const void *x, const void *y,
                      int *path_out, int *planes_per_cta, int *rows_per_tile,
                      int *threads, int64_t *ctas, int *smem_bytes);
-/* Environment switch DWBNQ_FORCE_PATH=generic|coop|tma|raw|plane|planegen (read at each call) and this
- * setter (-1 = automatic) restrict that choice; used by the tests to cover every path. */
-int dwbnq_set_forced_path(int path);
-/* Planner overrides for tuning runs (0 = automatic): planes per tile, 7-row patch blocks
- * per tile, threads per CTA; the fourth value is reserved (pass 0). Values that do not fit
- * the shared-memory budget fall back to the generic kernel. */
-int dwbnq_set_tuning(int planes_per_cta, int row_blocks_per_tile, int threads, int rows_per_patch);
-
 /* ---- communicator: the one exchange the path needs (per-channel min/max) ----------- */
 
 /* NCCL is loaded with dlopen at first use, like the reference does
@@ -240,6 +233,17 @@ int dwbnq_set_tuning(int planes_per_cta, int row_blocks_per_tile, int threads, i
 int dwbnq_comm_get_unique_id(void *id128);
 int dwbnq_comm_create(const void *id128, int nranks, int rank, int device, void **comm);
 int dwbnq_comm_destroy(void *comm);
+/* Deadline of the all-reduce the MINMAX entry points issue themselves (dwbnq_minmaxq_fwd,
+ * dwbnq_fused_fwd with a `comm`). 0 (the default; the environment variable
+ * DWBNQ_COMM_DEADLINE_MS sets another default at dwbnq_comm_create) only enqueues the
+ * collective. A positive value makes those calls wait on the host until the collective has
+ * completed: after `ms` milliseconds, or on an asynchronous NCCL error, the communicator
+ * is aborted and the call returns DWBNQ_ERR_TIMEOUT / DWBNQ_ERR_NCCL - the role of the
+ * reference's watch dog (src/nbla/cuda/communicator/watch_dog.cpp:59-108, armed around
+ * each collective at multi_process_data_parallel_communicator.cu:718-720). Because the
+ * call then synchronises with the host, do not set a deadline on a communicator that is
+ * used while a stream capture is in progress. */
+int dwbnq_comm_set_deadline_ms(void *comm, int ms);
 /* All-reduce(max) of `count` fp32 values in place; waits at most timeout_ms for
  * completion when timeout_ms > 0 (then aborts the communicator and returns
  * DWBNQ_ERR_TIMEOUT), otherwise only enqueues. */

@@ -73,7 +73,10 @@ int check_mm(const dwbnq_quant_desc *q, const dwbnq_minmax_ptrs *mm, const void 
 }
 
 // The range part of MinMaxQuantize once the encoded per-channel min/max are in the
-// workspace: optional all-reduce across shards, then the range derivation.
+// workspace: optional all-reduce across shards, then the range derivation. The collective
+// runs under the deadline the communicator carries (dwbnq_comm_set_deadline_ms): with one
+// set, a peer that never joins ends this call with DWBNQ_ERR_TIMEOUT and an aborted
+// communicator instead of a stream that never drains.
 int mm_finish_ranges(int dtype, int channels, const dwbnq_quant_desc &q, const dwbnq_minmax_ptrs &mm,
                      const MmWorkspace &w, void *comm, cudaStream_t stream) {
   int st;
@@ -81,7 +84,7 @@ int mm_finish_ranges(int dtype, int channels, const dwbnq_quant_desc &q, const d
   if (q.x_min_max && comm) {
     st = launch_mm_pack(w, channels, stream);
     if (st != DWBNQ_OK) return st;
-    st = comm_allreduce_max(comm, w.packed, 2LL * channels, stream, 0);
+    st = comm_allreduce_max(comm, w.packed, 2LL * channels, stream, comm_deadline_ms(comm));
     if (st != DWBNQ_OK) return st;
     from_packed = 1;
   }
@@ -237,13 +240,19 @@ int dwbnq_fused_fwd(const dwbnq_conv_desc *desc, float bn_eps, const dwbnq_quant
   int ho, wo;
   int st = validate_conv(desc, &ho, &wo);
   if (st != DWBNQ_OK) return st;
-  if (desc->n == 0) return DWBNQ_OK;  // empty batch: nothing to read or write
-  if (!x || !w || !y) return fail(DWBNQ_ERR_INVALID_ARG, "x, w and y must not be null");
-  if ((bn_mean == nullptr) != (bn_var == nullptr))
-    return fail(DWBNQ_ERR_INVALID_ARG, "bn_mean and bn_var must be given together");
   const int kind = q ? q->kind : DWBNQ_Q_NONE;
   if (kind < DWBNQ_Q_NONE || kind > DWBNQ_Q_MINMAX)
     return fail(DWBNQ_ERR_INVALID_ARG, "quantizer kind %d unknown", kind);
+  // An empty batch has nothing to read or write - unless this rank's (empty) shard belongs
+  // to a batch whose per-channel min/max are all-reduced: then the rank must still take
+  // part in the collective (its identities +inf / -inf are neutral under max), or its peers
+  // would wait for it forever, and it must derive the same ranges as they do.
+  const bool empty = desc->n == 0;
+  const bool empty_joins = empty && kind == DWBNQ_Q_MINMAX && q->x_min_max && comm != nullptr;
+  if (empty && !empty_joins) return DWBNQ_OK;
+  if (!empty && (!x || !w || !y)) return fail(DWBNQ_ERR_INVALID_ARG, "x, w and y must not be null");
+  if ((bn_mean == nullptr) != (bn_var == nullptr))
+    return fail(DWBNQ_ERR_INVALID_ARG, "bn_mean and bn_var must be given together");
   if (kind == DWBNQ_Q_MINMAX) {
     st = check_mm(q, mm, workspace);
     if (st != DWBNQ_OK) return st;
@@ -269,8 +278,9 @@ int dwbnq_fused_fwd(const dwbnq_conv_desc *desc, float bn_eps, const dwbnq_quant
     default:
       break;
   }
-  // MinMaxQuantize: first pass reduces the (never stored) activation to per-channel
-  // min / max, second pass recomputes it and quantizes with the derived ranges.
+  // MinMaxQuantize: a first pass reduces the activation to per-channel min / max (encoded
+  // slots of the workspace), the ranges are derived (after the all-reduce, for a sharded
+  // batch), and a second pass quantizes. Which form the two passes take is chosen below.
   const int channels = a.OC;
   const MmWorkspace ws = mm_workspace(workspace, channels);
   a.q.mm_enc_min = ws.enc_min;
@@ -278,6 +288,11 @@ int dwbnq_fused_fwd(const dwbnq_conv_desc *desc, float bn_eps, const dwbnq_quant
   a.q.mm_scale = ws.scale;
   a.q.mm_lo = ws.lo;
   a.q.mm_hi = ws.hi;
+  if (empty_joins) {
+    st = launch_mm_init(ws, channels, s);
+    if (st != DWBNQ_OK) return st;
+    return mm_finish_ranges(desc->dtype, channels, *q, *mm, ws, comm, s);
+  }
   if (q->x_min_max) {
     st = launch_mm_init(ws, channels, s);
     if (st != DWBNQ_OK) return st;

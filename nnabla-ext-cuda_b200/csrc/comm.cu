@@ -78,10 +78,20 @@ int fail_nccl(int r, const char *what) {
 struct Comm {
   ncclComm_t nccl = nullptr;
   int nranks = 0, rank = 0, device = 0;
+  int deadline_ms = 0;  // for the collectives the MINMAX entry points issue (0 = enqueue only)
   bool aborted = false;
 };
 
+int env_deadline_ms() {
+  const char *e = std::getenv("DWBNQ_COMM_DEADLINE_MS");
+  if (!e || !*e) return 0;
+  const long v = std::strtol(e, nullptr, 10);
+  return v > 0 && v < 0x7fffffffL ? (int)v : 0;
+}
+
 }  // namespace
+
+int comm_deadline_ms(void *comm) { return comm ? static_cast<Comm *>(comm)->deadline_ms : 0; }
 
 int comm_allreduce_max(void *comm, float *buf, long long count, cudaStream_t stream, int timeout_ms) {
   if (!comm) return fail(DWBNQ_ERR_INVALID_ARG, "communicator is null");
@@ -163,12 +173,21 @@ extern "C" int dwbnq_comm_create(const void *id128, int nranks, int rank, int de
   c->nranks = nranks;
   c->rank = rank;
   c->device = dev;
+  c->deadline_ms = env_deadline_ms();
   int r = g_nccl.CommInitRank(&c->nccl, nranks, id, rank);
   if (r != kNcclSuccess) {
     delete c;
     return fail_nccl(r, "ncclCommInitRank");
   }
   *comm = c;
+  return DWBNQ_OK;
+}
+
+extern "C" int dwbnq_comm_set_deadline_ms(void *comm, int ms) {
+  clear_error();
+  if (!comm) return fail(DWBNQ_ERR_INVALID_ARG, "communicator is null");
+  if (ms < 0) return fail(DWBNQ_ERR_INVALID_ARG, "deadline %d ms is negative", ms);
+  static_cast<Comm *>(comm)->deadline_ms = ms;
   return DWBNQ_OK;
 }
 

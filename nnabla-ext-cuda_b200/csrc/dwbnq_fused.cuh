@@ -209,14 +209,48 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long *bar, unsigned 
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after 2^16 polls (a few seconds at most), so a transfer that never
-// lands cannot hang the GPU.
-__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long *bar, unsigned int parity) {
+// Bounded wait. The limit is a TIME (2 s of the global nanosecond timer by default): a poll
+// count alone would depend on how long the hardware parks a poll, and a healthy copy on a
+// busy GPU must not be mistaken for a lost one. A poll cap (2^24, far beyond the time limit)
+// backs the timer up. When the limit passes the caller records it in the device flag and
+// returns, so a transfer that never lands cannot hang the GPU.
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool mbar_wait_bounded_lane(unsigned long long *bar, unsigned int parity,
+                                                       unsigned long long limit_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
 #pragma unroll 1
-  for (unsigned int i = 0; i < (1u << 16); ++i) {
+  for (unsigned int i = 0; i < (1u << 24); ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() - t0 > limit_ns) break;
   }
   return false;
+}
+// Warp-uniform form (all 32 lanes call it): either every lane has observed the phase, or
+// every lane gives up. A lane that ran out of time while another saw the phase complete
+// polls once more (the phase stays complete), which also gives it the acquire it needs.
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long *bar, unsigned int parity,
+                                                  unsigned long long limit_ns = kWaitLimitNs) {
+  bool ok = mbar_wait_bounded_lane(bar, parity, limit_ns);
+  if (!__all_sync(0xffffffffu, ok)) {
+    if (__any_sync(0xffffffffu, ok) && !ok) ok = mbar_try_wait(bar, parity);
+    ok = __all_sync(0xffffffffu, ok);
+  }
+  return ok;
+}
+// CTA-uniform form (every thread of the block calls it): a block whose threads meet at
+// barriers afterwards must leave as a whole.
+__device__ __forceinline__ bool mbar_wait_bounded_cta(unsigned long long *bar, unsigned int parity,
+                                                      unsigned long long limit_ns = kWaitLimitNs) {
+  bool ok = mbar_wait_bounded_lane(bar, parity, limit_ns);
+  if (__syncthreads_and(ok)) return true;
+  if (!ok) ok = mbar_try_wait(bar, parity);  // completed meanwhile for a slower thread
+  return __syncthreads_and(ok) != 0;
 }
 // One tiled 3-D box load {x, y, z} -> shared memory, completion counted on `bar`.
 __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *tm, int x, int y, int z,
@@ -467,7 +501,7 @@ __global__ void __launch_bounds__(256, tiled_min_blocks(sizeof(T), K, MODE))
 
   // Every lane waits itself with the hardware parking it (a one-lane poll would leave its
   // warp split in two for the rest of the kernel).
-  if (ASYNC && async_tile && !mbar_wait_bounded(bar, 0)) {
+  if (ASYNC && async_tile && !mbar_wait_bounded_cta(bar, 0)) {  // async_tile is CTA-uniform
     if (a.flag) atomicExch(a.flag, 1);
     return;
   }

@@ -7,6 +7,7 @@
 #include <utility>
 
 #include "../../include/dwbnq.h"
+#include "../../include/dwbnq_debug.h"
 #include "dwbnq_fused.cuh"
 #include "dwbnq_plane.cuh"
 #include "dwbnq_plane_gen.cuh"
@@ -65,6 +66,8 @@ void set_forced_path(int p);
 int device_flag_ptr(int device, int **ptr);
 
 int validate_conv(const dwbnq_conv_desc *d, int *ho, int *wo);
+// Streaming multiprocessors of `device` (-1 = the current device), cached per device.
+int sm_count(int device);
 
 // ---- element-wise family (elementwise.cu) -----------------------------------------------
 int launch_bn_infer(int dtype, long long size0, long long size1, long long size2, float eps,
@@ -111,5 +114,8 @@ int pow2_table_device(int device, const uint32_t **ptr);
 // ---- communicator (comm.cpp) --------------------------------------------------------------
 int comm_allreduce_max(void *comm, float *buf, long long count, cudaStream_t stream,
                        int timeout_ms);
+// Deadline (ms, 0 = none) the communicator carries for the collectives the MINMAX entry
+// points issue on the caller's behalf.
+int comm_deadline_ms(void *comm);
 
 }  // namespace dwbnq

@@ -9,11 +9,12 @@ namespace dwbnq {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kSMs = 148;
 
+// Grid of at most `per_sm` CTAs per SM of the current device (the entry points have made
+// the call's device current before they come here).
 inline unsigned int grid_for(long long work_items, int per_sm) {
   long long blocks = (work_items + kThreads - 1) / kThreads;
-  const long long cap = (long long)kSMs * per_sm;
+  const long long cap = (long long)sm_count(-1) * per_sm;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   return (unsigned int)blocks;

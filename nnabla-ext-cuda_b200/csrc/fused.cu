@@ -13,9 +13,12 @@ __device__ int g_device_flag = 0;
 
 namespace {
 
-std::atomic<int> g_forced_path{PATH_AUTO};
-// Planner overrides for tuning runs: planes per CTA, row blocks per tile, threads (0 = auto).
-std::atomic<int> g_tune_p{0}, g_tune_rb{0}, g_tune_threads{0}, g_tune_r{0};
+// Test / tuning switches (include/dwbnq_debug.h) belong to the calling host thread: a thread
+// that forces a family or overrides the planner never changes another thread's kernels.
+constexpr int kPathUnset = -2;
+thread_local int t_forced_path = kPathUnset;
+// Planner overrides for tuning runs: planes per CTA, row blocks per tile (0 = auto).
+thread_local int t_tune_p = 0, t_tune_rb = 0;
 
 constexpr int kMaxDevices = 64;
 int *g_flag_ptr[kMaxDevices] = {nullptr};
@@ -44,10 +47,10 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 inline int round_up(int a, int b) { return ceil_div(a, b) * b; }
 
 template <typename T>
-cudaError_t launch_generic_t(int qm, const FusedArgs &a, long long total, cudaStream_t stream) {
+cudaError_t launch_generic_t(int qm, const FusedArgs &a, long long total, int sms, cudaStream_t stream) {
   const int threads = 256;
   long long blocks = (total + threads - 1) / threads;
-  const long long cap = 148LL * 64;  // grid-stride beyond 64 CTAs per SM
+  const long long cap = (long long)sms * 64;  // grid-stride beyond 64 CTAs per SM
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   switch (qm) {
@@ -64,18 +67,22 @@ cudaError_t launch_generic_t(int qm, const FusedArgs &a, long long total, cudaSt
 }  // namespace
 
 int forced_path() {
-  const char *e = std::getenv("DWBNQ_FORCE_PATH");
-  if (e && *e) {
-    if (!std::strcmp(e, "generic")) return PATH_GENERIC;
-    if (!std::strcmp(e, "coop")) return PATH_COOP;
-    if (!std::strcmp(e, "tma")) return PATH_TMA;
-    if (!std::strcmp(e, "raw")) return PATH_RAW;
-    if (!std::strcmp(e, "plane")) return PATH_PLANE;
-    if (!std::strcmp(e, "planegen")) return PATH_PLANE_GEN;
-  }
-  return g_forced_path.load();
+  // the environment's default is read once (init-once state); a thread's own setting wins
+  static const int env_default = [] {
+    const char *e = std::getenv("DWBNQ_FORCE_PATH");
+    if (e && *e) {
+      if (!std::strcmp(e, "generic")) return (int)PATH_GENERIC;
+      if (!std::strcmp(e, "coop")) return (int)PATH_COOP;
+      if (!std::strcmp(e, "tma")) return (int)PATH_TMA;
+      if (!std::strcmp(e, "raw")) return (int)PATH_RAW;
+      if (!std::strcmp(e, "plane")) return (int)PATH_PLANE;
+      if (!std::strcmp(e, "planegen")) return (int)PATH_PLANE_GEN;
+    }
+    return (int)PATH_AUTO;
+  }();
+  return t_forced_path == kPathUnset ? env_default : t_forced_path;
 }
-void set_forced_path(int p) { g_forced_path.store(p); }
+void set_forced_path(int p) { t_forced_path = p; }
 
 int device_flag_ptr(int device, int **ptr) {
   if (device < 0 || device >= kMaxDevices) return fail(DWBNQ_ERR_INVALID_ARG, "device %d out of range", device);
@@ -114,21 +121,27 @@ int validate_conv(const dwbnq_conv_desc *d, int *ho, int *wo) {
   return DWBNQ_OK;
 }
 
-namespace {
-
+// Streaming multiprocessors of `device` (-1: the current device), asked of the driver once
+// per device; grids that are capped "per SM" are sized from this, not from a literal.
 int sm_count(int device) {
-  static int cached[kMaxDevices] = {0};
-  if (device < 0 || device >= kMaxDevices) return 148;
-  if (!cached[device]) {
-    int n = 0;
+  static std::atomic<int> cached[kMaxDevices];
+  if (device < 0 && cudaGetDevice(&device) != cudaSuccess) {
+    (void)cudaGetLastError();
+    device = 0;
+  }
+  const bool slot = device >= 0 && device < kMaxDevices;
+  int n = slot ? cached[device].load(std::memory_order_relaxed) : 0;
+  if (n <= 0) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) {
       (void)cudaGetLastError();
-      n = 148;
+      return 148;  // no usable device: the launch that follows reports the real error
     }
-    cached[device] = n;
+    if (slot) cached[device].store(n, std::memory_order_relaxed);
   }
-  return cached[device];
+  return n;
 }
+
+namespace {
 
 long long gcd_ll(long long a, long long b) { return b ? gcd_ll(b, a % b) : a; }
 
@@ -252,7 +265,7 @@ int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan
     // small planes: many small CTAs hide the per-CTA copy / record latency better than few
     // large ones (measured on B200): about 64 threads each
     long long want = std::max(1, (ipp <= 64 ? 64 : max_threads) / ipp);
-    if (g_tune_p.load() > 0) want = g_tune_p.load();
+    if (t_tune_p > 0) want = t_tune_p;
     want = std::min(want, fit);
     long long Pl = want / pal * pal;
     if (Pl < pal) Pl = pal <= fit ? pal : want;  // cannot align: the copies fall back to threads
@@ -276,7 +289,7 @@ int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan
     // Row blocks per tile: aim at one patch per thread, split the plane evenly, and keep one
     // plane's tile inside the budget.
     int rb_per_tile = std::max(1, std::min(n_rb_total, max_threads / n_strips));
-    if (g_tune_rb.load() > 0) rb_per_tile = std::min(g_tune_rb.load(), n_rb_total);
+    if (t_tune_rb > 0) rb_per_tile = std::min(t_tune_rb, n_rb_total);
     int n_row_tiles, TH, TR, n_boxes, box_rows, tile_elems;
     for (;;) {
       n_row_tiles = ceil_div(n_rb_total, rb_per_tile);
@@ -297,7 +310,7 @@ int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan
     // whole small planes: about 64 threads per CTA (see above); otherwise fill the CTA
     P = std::max(1, ((n_row_tiles == 1 && ipp <= 64) ? 64 : max_threads) / ipp);
     while (P > 1 && (long long)P * tile_bytes > stage_budget) --P;
-    if (g_tune_p.load() > 0) P = g_tune_p.load();
+    if (t_tune_p > 0) P = t_tune_p;
     if (P > n_planes) P = (int)n_planes;
     c.n_row_tiles = n_row_tiles;
     c.n_rb = rb_per_tile;
@@ -346,8 +359,9 @@ int launch_fused(const dwbnq_conv_desc &d, FusedArgs &a, int qm, int device, cud
   const long long total = d.n * (long long)a.OC * a.Ho * a.Wo;
   cudaError_t e;
   if (plan.path == PATH_GENERIC) {
-    e = d.dtype == DWBNQ_F32 ? launch_generic_t<float>(qm, a, total, stream)
-                             : launch_generic_t<__half>(qm, a, total, stream);
+    const int sms = sm_count(device);
+    e = d.dtype == DWBNQ_F32 ? launch_generic_t<float>(qm, a, total, sms, stream)
+                             : launch_generic_t<__half>(qm, a, total, sms, stream);
     if (e != cudaSuccess) return fail_cuda(e, "fused_generic_kernel launch");
     return DWBNQ_OK;
   }
@@ -401,10 +415,42 @@ int launch_fused(const dwbnq_conv_desc &d, FusedArgs &a, int qm, int device, cud
 
 }  // namespace dwbnq
 
+// One warp, one barrier nobody completes: the bounded wait runs out after `limit_ns` and the
+// kernel records it, exactly like a copy-engine kernel whose transfer never landed.
+namespace dwbnq {
+__global__ void expire_wait_kernel(int *flag, unsigned long long limit_ns) {
+  __shared__ __align__(8) unsigned long long bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  if (!mbar_wait_bounded(&bar, 0, limit_ns)) {
+    if (flag) atomicExch(flag, 1);
+    return;
+  }
+}
+}  // namespace dwbnq
+
 extern "C" int dwbnq_set_tuning(int planes_per_cta, int row_blocks_per_tile, int threads, int rows_per_patch) {
-  dwbnq::g_tune_p.store(planes_per_cta);
-  dwbnq::g_tune_rb.store(row_blocks_per_tile);
-  dwbnq::g_tune_threads.store(threads);
-  dwbnq::g_tune_r.store(rows_per_patch);
+  (void)threads;
+  (void)rows_per_patch;
+  dwbnq::t_tune_p = planes_per_cta;
+  dwbnq::t_tune_rb = row_blocks_per_tile;
+  return DWBNQ_OK;
+}
+
+extern "C" int dwbnq_debug_expire_wait(unsigned int limit_us, int device, void *stream) {
+  using namespace dwbnq;
+  clear_error();
+  int dev;
+  int st = enter_device(device, &dev);
+  if (st != DWBNQ_OK) return st;
+  int *flag = nullptr;
+  st = device_flag_ptr(dev, &flag);
+  if (st != DWBNQ_OK) return st;
+  expire_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flag, 1000ull * limit_us);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail_cuda(e, "expire_wait_kernel launch");
   return DWBNQ_OK;
 }

@@ -17,6 +17,10 @@
 // the legacy default stream, return without synchronising. A non-zero dwbnq status becomes an
 // nbla::Exception through NBLA_ERROR. Backward is left to the base classes' contract:
 // it raises not_implemented (this library is the inference path).
+//
+// Besides the five registered classes the plugin holds FusedDwBnQuantCuda, the single
+// function object a graph converter substitutes for a whole dw-conv -> BN -> quantizer
+// chain, and its factory dwbnq_nbla_create_fused().
 #include <dwbnq.h>
 
 #include <nbla/cuda/common.hpp>
@@ -257,7 +261,179 @@ protected:
   DWBNQ_NO_BACKWARD("MinMaxQuantizeCuda")
 };
 
+// ---- the fused layer: DepthwiseConvolution -> BatchNormalization(batch_stat=false) -> quantizer --
+// One function object for the three-function chain, which is what a graph converter puts in
+// the chain's place (the way nnabla's BatchNormalizationFolding replaces conv -> BN by one
+// convolution): its constructor takes the constructor arguments of the three functions it
+// replaces, its inputs are theirs in order,
+//   [x, w, (b), (beta), (gamma), mean, var, (qr_min, qr_max, ql_min, ql_max)]
+// (b when with_bias; beta / gamma unless no_bias / no_scale; the four range tensors for
+// MinMaxQuantize), and its one output is the quantizer's. forward_impl is one call of
+// dwbnq_fused_fwd: x is read once and the quantized y written once, instead of three
+// kernels with two intermediate tensors. It derives from core's BaseFunction like every
+// generated function class (include/nbla/cuda/function/function_impl.hpp.tmpl:29-58 shows
+// the shape of a derived CUDA class); there is no core base class for it, so the members a
+// generated base would supply (copy, in/out types, min inputs/outputs, output shape) are here.
+template <typename T>
+class FusedDwBnQuantCuda
+    : public BaseFunction<int, const vector<int> &, const vector<int> &, const vector<int> &, int, bool,
+                          float, bool, bool, int, bool, bool, int, int, float, float, bool, bool, float> {
+public:
+  typedef typename CudaType<T>::type Tc;
+  typedef BaseFunction<int, const vector<int> &, const vector<int> &, const vector<int> &, int, bool, float,
+                       bool, bool, int, bool, bool, int, int, float, float, bool, bool, float>
+      Base;
+  // conv: base_axis, pad, stride, dilation, multiplier (+ whether a bias input is present);
+  // BN: eps, no_scale, no_bias (axes = [base_axis], batch_stat = false by construction);
+  // quantizer: kind (dwbnq_quant_kind) and the union of the three quantizers' arguments.
+  FusedDwBnQuantCuda(const Context &ctx, int base_axis, const vector<int> &pad, const vector<int> &stride,
+                     const vector<int> &dilation, int multiplier, bool with_bias, float bn_eps, bool no_scale,
+                     bool no_bias, int quant_kind, bool sign, bool with_zero, int n, int m, float delta,
+                     float decay, bool x_min_max, bool ema, float mm_eps)
+      : Base(ctx, base_axis, pad, stride, dilation, multiplier, with_bias, bn_eps, no_scale, no_bias, quant_kind,
+             sign, with_zero, n, m, delta, decay, x_min_max, ema, mm_eps),
+        base_axis_(base_axis), pad_(pad), stride_(stride), dilation_(dilation), multiplier_(multiplier),
+        with_bias_(with_bias), bn_eps_(bn_eps), no_scale_(no_scale), no_bias_(no_bias),
+        device_(std::stoi(ctx.device_id)) {
+    q_ = dwbnq_quant_desc();
+    q_.kind = quant_kind;
+    q_.sign = sign;
+    q_.with_zero = with_zero;
+    q_.n = n;
+    q_.m = m;
+    q_.delta = delta;
+    q_.decay = decay;
+    q_.x_min_max = x_min_max;
+    q_.ema = ema;
+    q_.eps = mm_eps;
+  }
+  virtual ~FusedDwBnQuantCuda() {}
+  virtual shared_ptr<Function> copy() const {
+    return shared_ptr<Function>(new FusedDwBnQuantCuda<T>(
+        this->ctx_, base_axis_, pad_, stride_, dilation_, multiplier_, with_bias_, bn_eps_, no_scale_, no_bias_,
+        q_.kind, q_.sign != 0, q_.with_zero != 0, q_.n, q_.m, q_.delta, q_.decay, q_.x_min_max != 0, q_.ema != 0,
+        q_.eps));
+  }
+  virtual vector<dtypes> in_types() { return vector<dtypes>(n_inputs(), get_dtype<T>()); }
+  virtual vector<dtypes> out_types() { return vector<dtypes>{get_dtype<T>()}; }
+  virtual int min_inputs() { return n_inputs(); }
+  virtual int min_outputs() { return 1; }
+  virtual string name() { return "FusedDwBnQuantCuda"; }
+  virtual vector<string> allowed_array_classes() {
+    return SingletonManager::get<Cuda>()->array_classes();
+  }
+
+protected:
+  int base_axis_;
+  vector<int> pad_, stride_, dilation_;
+  int multiplier_;
+  bool with_bias_;
+  float bn_eps_;
+  bool no_scale_, no_bias_;
+  int device_;
+  dwbnq_quant_desc q_;
+  dwbnq_conv_desc desc_;
+  Variable workspace_;
+  int n_inputs() const {
+    return 2 + (with_bias_ ? 1 : 0) + (no_bias_ ? 0 : 1) + (no_scale_ ? 0 : 1) + 2 +
+           (q_.kind == DWBNQ_Q_MINMAX ? 4 : 0);
+  }
+  virtual void setup_impl(const Variables &inputs, const Variables &outputs) {
+    NBLA_CHECK((int)inputs.size() == n_inputs(), error_code::value,
+               "FusedDwBnQuantCuda expects %d inputs, got %d", n_inputs(), (int)inputs.size());
+    const Shape_t xs = inputs[0]->shape(), ws = inputs[1]->shape();
+    const int sdims = (int)xs.size() - base_axis_ - 1;
+    NBLA_CHECK(sdims == 1 || sdims == 2, error_code::value, "1-D or 2-D depthwise convolution expected");
+    NBLA_CHECK((int)ws.size() == sdims + 1 && (int)pad_.size() == sdims && (int)stride_.size() == sdims &&
+                   (int)dilation_.size() == sdims,
+               error_code::value, "weight rank / pad / stride / dilation do not match %d spatial dims", sdims);
+    const bool two_d = sdims == 2;
+    desc_ = dwbnq_conv_desc();
+    desc_.dtype = DType<T>::value;
+    desc_.c = (int)xs[base_axis_];
+    desc_.n = 1;
+    for (int i = 0; i < base_axis_; ++i) desc_.n *= xs[i];
+    desc_.h = two_d ? (int)xs[base_axis_ + 1] : 1;
+    desc_.w = (int)xs[base_axis_ + (two_d ? 2 : 1)];
+    desc_.kh = two_d ? (int)ws[1] : 1;
+    desc_.kw = (int)ws[two_d ? 2 : 1];
+    desc_.stride_h = two_d ? stride_[0] : 1;
+    desc_.stride_w = stride_[two_d ? 1 : 0];
+    desc_.pad_h = two_d ? pad_[0] : 0;
+    desc_.pad_w = pad_[two_d ? 1 : 0];
+    desc_.dil_h = two_d ? dilation_[0] : 1;
+    desc_.dil_w = dilation_[two_d ? 1 : 0];
+    desc_.multiplier = multiplier_;
+    NBLA_CHECK(ws[0] == (Size_t)desc_.c * multiplier_, error_code::value,
+               "weight has %d output maps, expected channels x multiplier = %d", (int)ws[0], desc_.c * multiplier_);
+    int32_t ho = 0, wo = 0;
+    check(dwbnq_conv_out_shape(&desc_, &ho, &wo), "FusedDwBnQuantCuda::setup");
+    Shape_t ys(xs.begin(), xs.begin() + base_axis_);
+    ys.push_back(ws[0]);
+    if (two_d) ys.push_back(ho);
+    ys.push_back(wo);
+    outputs[0]->reshape(ys, true);
+    if (q_.kind == DWBNQ_Q_MINMAX)
+      workspace_.reshape(Shape_t{(Size_t)(dwbnq_workspace_bytes((int)ws[0]) / sizeof(float))}, true);
+  }
+  virtual void forward_impl(const Variables &inputs, const Variables &outputs) {
+    int i = 0;
+    const Tc *x = inputs[i++]->get_data_pointer<Tc>(this->ctx_);
+    const Tc *w = inputs[i++]->get_data_pointer<Tc>(this->ctx_);
+    const Tc *b = with_bias_ ? inputs[i++]->get_data_pointer<Tc>(this->ctx_) : nullptr;
+    const Tc *beta = no_bias_ ? nullptr : inputs[i++]->get_data_pointer<Tc>(this->ctx_);
+    const Tc *gamma = no_scale_ ? nullptr : inputs[i++]->get_data_pointer<Tc>(this->ctx_);
+    const Tc *rm = inputs[i++]->get_data_pointer<Tc>(this->ctx_);
+    const Tc *rv = inputs[i++]->get_data_pointer<Tc>(this->ctx_);
+    dwbnq_minmax_ptrs mm = dwbnq_minmax_ptrs();
+    float *ws = nullptr;
+    if (q_.kind == DWBNQ_Q_MINMAX) {
+      mm.qr_min = inputs[i++]->cast_data_and_get_pointer<Tc>(this->ctx_);
+      mm.qr_max = inputs[i++]->cast_data_and_get_pointer<Tc>(this->ctx_);
+      mm.ql_min = inputs[i++]->get_data_pointer<Tc>(this->ctx_);
+      mm.ql_max = inputs[i++]->get_data_pointer<Tc>(this->ctx_);
+      ws = workspace_.cast_data_and_get_pointer<float>(this->ctx_, true);
+    }
+    Tc *y = outputs[0]->cast_data_and_get_pointer<Tc>(this->ctx_, true);
+    check(dwbnq_fused_fwd(&desc_, bn_eps_, &q_, x, w, b, beta, gamma, rm, rv,
+                          q_.kind == DWBNQ_Q_MINMAX ? &mm : nullptr, y, ws, nullptr, device_, nullptr),
+          "FusedDwBnQuantCuda::forward");
+  }
+  DWBNQ_NO_BACKWARD("FusedDwBnQuantCuda")
+};
+
 }  // namespace dwbnq_nbla
+
+// Factory of the fused function object, for the graph converter that replaces a matched
+// DepthwiseConvolution -> BatchNormalization -> quantizer chain (INTEGRATION.md shows the
+// converter). Arguments are plain C values: the constructor arguments of the three
+// functions; pad / stride / dilation point to `spatial_dims` ints each. `half` selects the
+// "cuda:half" class. Returns a new nbla::Function* (the caller wraps it in a FunctionPtr /
+// CgFunction, which then owns it), or NULL with the reason in dwbnq_last_error_string()
+// when an argument is out of range.
+extern "C" void *dwbnq_nbla_create_fused(int half, int device, int base_axis, int spatial_dims, const int *pad,
+                                         const int *stride, const int *dilation, int multiplier, int with_bias,
+                                         float bn_eps, int no_scale, int no_bias, int quant_kind, int sign,
+                                         int with_zero, int n, int m, float delta, float decay, int x_min_max,
+                                         int ema, float mm_eps) {
+  using namespace nbla;
+  using namespace dwbnq_nbla;
+  if (spatial_dims < 1 || spatial_dims > 2 || !pad || !stride || !dilation || quant_kind < DWBNQ_Q_NONE ||
+      quant_kind > DWBNQ_Q_MINMAX || base_axis < 0 || device < 0)
+    return nullptr;
+  Context ctx;
+  ctx.backend = {half ? "cuda:half" : "cuda:float"};
+  ctx.array_class = "CudaCachedArray";
+  ctx.device_id = std::to_string(device);
+  const vector<int> p(pad, pad + spatial_dims), s(stride, stride + spatial_dims), d(dilation, dilation + spatial_dims);
+  if (half)
+    return static_cast<Function *>(new FusedDwBnQuantCuda<Half>(
+        ctx, base_axis, p, s, d, multiplier, with_bias != 0, bn_eps, no_scale != 0, no_bias != 0, quant_kind,
+        sign != 0, with_zero != 0, n, m, delta, decay, x_min_max != 0, ema != 0, mm_eps));
+  return static_cast<Function *>(new FusedDwBnQuantCuda<float>(
+      ctx, base_axis, p, s, d, multiplier, with_bias != 0, bn_eps, no_scale != 0, no_bias != 0, quant_kind,
+      sign != 0, with_zero != 0, n, m, delta, decay, x_min_max != 0, ema != 0, mm_eps));
+}
 
 // Replaces the five registry entries for "cuda:float" and "cuda:half". Call once, after
 // nnabla_ext.cuda (init_cuda) has registered the stock classes.

@@ -46,7 +46,7 @@ class DwbnqError(RuntimeError):
 _vp, _int, _i64, _flt = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
 _P = ctypes.POINTER
 
-# name -> (restype, argtypes); every symbol include/dwbnq.h declares
+# name -> (restype, argtypes); every symbol include/dwbnq.h and include/dwbnq_debug.h declare
 SIGNATURES = {
     "dwbnq_version": (_int, []),
     "dwbnq_last_error_string": (ctypes.c_char_p, []),
@@ -74,6 +74,8 @@ SIGNATURES = {
     "dwbnq_comm_get_unique_id": (_int, [_vp]),
     "dwbnq_comm_create": (_int, [_vp, _int, _int, _int, _P(_vp)]),
     "dwbnq_comm_destroy": (_int, [_vp]),
+    "dwbnq_comm_set_deadline_ms": (_int, [_vp, _int]),
+    "dwbnq_debug_expire_wait": (_int, [ctypes.c_uint, _int, _vp]),
     "dwbnq_comm_allreduce_max_f32": (_int, [_vp, _vp, _i64, _vp, _int]),
 }
 

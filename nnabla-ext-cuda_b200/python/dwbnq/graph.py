@@ -34,10 +34,15 @@ def _bn_is_fusable(bn, channel_axis):
     return (not a.get("batch_stat", True)) and axes == [channel_axis] and len(bn["outputs"]) == 1
 
 
-def fuse_dw_bn_quant(nodes, graph_outputs=()):
+def fuse_dw_bn_quant(nodes, graph_outputs=(), shapes=None):
     """Returns a new node list where every dw-conv -> BN(inference) -> quantizer chain whose
     intermediates have no other consumer (and are not graph outputs) is one FusedDwBnQuant
-    node. A dw-conv -> BN chain without a quantizer is fused too (quantizer "none")."""
+    node. A dw-conv -> BN chain without a quantizer is fused too (quantizer "none").
+
+    ``shapes`` maps variable names to shapes (``from_nnabla`` returns it). A MinMaxQuantize
+    is absorbed only when its range tensors are known to be per-channel along the
+    convolution's channel axis ([1, C*multiplier, 1, 1]); with per-tensor ranges, or without
+    shape information, it stays a node of its own behind the fused conv + BN."""
     nodes = list(nodes)
     uses = _consumers(nodes)
     keep = set(graph_outputs)
@@ -77,7 +82,7 @@ def fuse_dw_bn_quant(nodes, graph_outputs=()):
         k = sole_consumer(bn["outputs"][0])
         if k is not None and nodes[k]["op"] in QUANTIZERS and nodes[k]["inputs"][0] == bn["outputs"][0]:
             qn = nodes[k]
-            if qn["op"] != "MinMaxQuantize" or _minmax_is_per_channel(qn):
+            if qn["op"] != "MinMaxQuantize" or _minmax_is_per_channel(qn, conv, shapes):
                 fused["quant"] = {"op": qn["op"], "args": dict(qn["args"])}
                 fused["inputs"] += list(qn["inputs"][1:])
                 fused["outputs"] = list(qn["outputs"])
@@ -88,13 +93,35 @@ def fuse_dw_bn_quant(nodes, graph_outputs=()):
     return out
 
 
-def _minmax_is_per_channel(qn):
-    return qn["args"].get("per_channel_axis", 1) == 1
+def _minmax_is_per_channel(qn, conv, shapes):
+    """MinMaxQuantize has no axis argument (decay, x_min_max, ema, ste_fine_grained, eps):
+    whether it is per-channel or per-tensor is decided by the shape of its range inputs."""
+    if not shapes or len(qn["inputs"]) < 5 or len(conv["inputs"]) < 2:
+        return False
+    w_shape = shapes.get(conv["inputs"][1])
+    if not w_shape:
+        return False
+    oc = int(w_shape[0])
+    axis = conv["args"].get("base_axis", 1)
+    for name in qn["inputs"][1:5]:
+        shp = shapes.get(name)
+        if shp is None:
+            return False
+        shp = tuple(int(v) for v in shp)
+        if len(shp) == 1:  # a bare [C] vector is accepted as per-channel too
+            if shp[0] != oc:
+                return False
+            continue
+        if axis >= len(shp) or shp[axis] != oc or any(v != 1 for i, v in enumerate(shp) if i != axis):
+            return False
+    return True
 
 
-def execute(nodes, tensors, comm=None):
+def execute(nodes, tensors, comm=None, check=False):
     """Runs the node list on torch CUDA tensors (dict name -> tensor, updated in place with
-    every produced variable). Only the operators of this library are known."""
+    every produced variable). Only the operators of this library are known. ``check=True``
+    synchronises at the end and raises if a kernel gave up one of its bounded waits (its
+    output tile would then be stale)."""
     from . import ops
 
     t = tensors
@@ -142,6 +169,8 @@ def execute(nodes, tensors, comm=None):
         else:
             raise NotImplementedError("operator %r is outside the dwbnq path" % (n["op"],))
         t[n["outputs"][0]] = y
+    if check:
+        ops.check_device_flag()
     return t
 
 
@@ -170,6 +199,13 @@ class GraphRunner:
         self.graph.replay()
         return self.tensors
 
+    def synchronize(self):
+        """Waits for the replays issued so far and raises if a kernel gave up one of its
+        bounded waits: call it where the outputs are read."""
+        from . import ops
+        ops.check_device_flag()
+        return self.tensors
+
 
 def _bn_inputs(rest, args):
     """BatchNormalization inputs after x: [beta, gamma, mean, var] with beta / gamma absent
@@ -181,19 +217,26 @@ def _bn_inputs(rest, args):
 
 
 def from_nnabla(output_variable):
-    """Builds the node list from an nnabla graph (needs nnabla; import guarded)."""
+    """Builds the node list from an nnabla graph (needs nnabla; import guarded).
+
+    Returns (nodes, names, shapes): the node list in forward order, the Variable -> name map
+    and the name -> shape map ``fuse_dw_bn_quant`` uses to tell a per-channel MinMaxQuantize
+    from a per-tensor one. Walks the graph with ``Variable.visit``, reading each function's
+    ``info.type_name`` / ``info.args`` and its ``inputs`` / ``outputs``."""
     try:
         import nnabla  # noqa: F401
-    except ImportError as e:  # pragma: no cover - nnabla is not installed in this environment
+    except ImportError as e:
         raise ImportError("from_nnabla needs the nnabla package") from e
-    nodes, names = [], {}
+    nodes, names, shapes = [], {}, {}
 
     def name(v):
-        return names.setdefault(v, "v%d" % len(names))
+        n = names.setdefault(v, "v%d" % len(names))
+        shapes.setdefault(n, tuple(int(d) for d in v.shape))
+        return n
 
     def visit(f):
         nodes.append({"op": f.info.type_name, "args": dict(f.info.args), "inputs": [name(v) for v in f.inputs],
                       "outputs": [name(v) for v in f.outputs]})
 
     output_variable.visit(visit)
-    return nodes, names
+    return nodes, names, shapes

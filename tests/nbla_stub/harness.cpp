@@ -6,6 +6,11 @@
 #include <nbla/stub_core.hpp>
 
 extern "C" void dwbnq_register_nbla(void);
+extern "C" void *dwbnq_nbla_create_fused(int half, int device, int base_axis, int spatial_dims, const int *pad,
+                                         const int *stride, const int *dilation, int multiplier, int with_bias,
+                                         float bn_eps, int no_scale, int no_bias, int quant_kind, int sign,
+                                         int with_zero, int n, int m, float delta, float decay, int x_min_max,
+                                         int ema, float mm_eps);
 
 namespace {
 thread_local std::string g_err;
@@ -120,6 +125,58 @@ int stub_minmax(int half, int device, const int64_t *xs, int nd, void *x, void *
     nbla::Variables in{&vx, &a, &b, &c, &d}, out{&vy};
     f->setup(in, out);
     f->forward(in, out);
+  });
+}
+// The fused function object through its factory: inputs in the order of the three functions
+// it replaces; ptrs = {x, w, b, beta, gamma, mean, var, qr_min, qr_max, ql_min, ql_max} with
+// null for an absent optional input. The output Variable starts without a shape: setup
+// must derive it (out_shape receives it).
+int stub_fused(int half, int device, const int64_t *xs, const int64_t *ws, int nd, void *const *ptrs, void *y,
+               int pad, int stride, float bn_eps, int quant_kind, int sign, int with_zero, int n, int m, float delta,
+               float decay, int x_min_max, int ema, float mm_eps, int64_t *out_shape, int *n_inputs, int *copies_ok) {
+  return guarded([&] {
+    const int p[2] = {pad, pad}, s[2] = {stride, stride}, d[2] = {1, 1};
+    nbla::Function *raw = static_cast<nbla::Function *>(dwbnq_nbla_create_fused(
+        half, device, 1, nd - 2, p, s, d, 1, ptrs[2] != nullptr, bn_eps, ptrs[4] == nullptr, ptrs[3] == nullptr,
+        quant_kind, sign, with_zero, n, m, delta, decay, x_min_max, ema, mm_eps));
+    if (!raw) throw std::runtime_error("factory returned null");
+    std::unique_ptr<nbla::Function> f(raw);
+    nbla::Shape_t ps(nd, 1);
+    ps[1] = ws[0];
+    nbla::Variable vx(shp(xs, nd), ptrs[0]), vw(shp(ws, nd - 1), ptrs[1]), vb(nbla::Shape_t{ws[0]}, ptrs[2]);
+    nbla::Variable vbeta(ps, ptrs[3]), vgamma(ps, ptrs[4]), vmean(ps, ptrs[5]), vvar(ps, ptrs[6]);
+    nbla::Variable r0(ps, ptrs[7]), r1(ps, ptrs[8]), r2(ps, ptrs[9]), r3(ps, ptrs[10]);
+    nbla::Variable vy(nbla::Shape_t{}, y);
+    nbla::Variables in{&vx, &vw};
+    if (ptrs[2]) in.push_back(&vb);
+    if (ptrs[3]) in.push_back(&vbeta);
+    if (ptrs[4]) in.push_back(&vgamma);
+    in.push_back(&vmean);
+    in.push_back(&vvar);
+    if (quant_kind == 3) {
+      in.push_back(&r0);
+      in.push_back(&r1);
+      in.push_back(&r2);
+      in.push_back(&r3);
+    }
+    *n_inputs = f->min_inputs();
+    nbla::Variables out{&vy};
+    // a copy (what nnabla makes when a graph is cloned) must behave like the original
+    std::shared_ptr<nbla::Function> g = f->copy();
+    *copies_ok = g && g->name() == f->name() && g->min_inputs() == f->min_inputs() &&
+                 g->in_types().size() == (size_t)f->min_inputs() && g->out_types().size() == 1;
+    g->setup(in, out);
+    g->forward(in, out);
+    const nbla::Shape_t ys = vy.shape();
+    for (int i = 0; i < nd; ++i) out_shape[i] = i < (int)ys.size() ? ys[i] : -1;
+  });
+}
+int stub_fused_backward_is_refused(int device) {
+  return guarded([&] {
+    const int p[2] = {1, 1}, s[2] = {1, 1}, d[2] = {1, 1};
+    std::unique_ptr<nbla::Function> f(static_cast<nbla::Function *>(dwbnq_nbla_create_fused(
+        0, device, 1, 2, p, s, d, 1, 1, 1e-5f, 0, 0, 1, 1, 0, 8, 0, 0.0625f, 0.f, 0, 0, 0.f)));
+    f->backward({}, {}, {}, {});
   });
 }
 int stub_backward_is_refused(int device) {

@@ -15,9 +15,12 @@
 #include <memory>
 #include <stdexcept>
 #include <string>
+#include <tuple>
+#include <type_traits>
 #include <vector>
 
 namespace nbla {
+using std::shared_ptr;
 using std::string;
 using std::vector;
 typedef int64_t Size_t;
@@ -70,9 +73,10 @@ public:
     for (size_t i = axis < 0 ? 0 : (size_t)axis; i < shape_.size(); ++i) n *= shape_[i];
     return n;
   }
+  // a Variable that wraps a caller's buffer keeps it; one a function owns gets scratch
   void reshape(const Shape_t &s, bool) {
     shape_ = s;
-    ptr_ = default_alloc()((size_t)size() * sizeof(float));
+    if (!ptr_) ptr_ = default_alloc()((size_t)size() * sizeof(float));
   }
   template <typename T> const T *get_data_pointer(const Context &) { return static_cast<const T *>(ptr_); }
   template <typename T> T *cast_data_and_get_pointer(const Context &, bool = false) { return static_cast<T *>(ptr_); }
@@ -90,6 +94,9 @@ struct SingletonManager {
   }
 };
 
+enum class dtypes { FLOAT, HALF };
+template <typename T> dtypes get_dtype() { return std::is_same<T, Half>::value ? dtypes::HALF : dtypes::FLOAT; }
+
 class Function {
 protected:
   Context ctx_;
@@ -99,6 +106,13 @@ public:
   virtual ~Function() {}
   virtual string name() = 0;
   virtual vector<string> allowed_array_classes() = 0;
+  // supplied by the generated base class of a core function; a function without one (the
+  // plugin's fused layer) defines them itself
+  virtual shared_ptr<Function> copy() const { return nullptr; }
+  virtual vector<dtypes> in_types() { return {}; }
+  virtual vector<dtypes> out_types() { return {}; }
+  virtual int min_inputs() { return 0; }
+  virtual int min_outputs() { return 0; }
   void setup(const Variables &i, const Variables &o) { setup_impl(i, o); }
   void forward(const Variables &i, const Variables &o) { forward_impl(i, o); }
   void backward(const Variables &i, const Variables &o, const vector<bool> &p, const vector<bool> &a) {
@@ -109,6 +123,16 @@ protected:
   virtual void setup_impl(const Variables &, const Variables &) = 0;
   virtual void forward_impl(const Variables &, const Variables &) = 0;
   virtual void backward_impl(const Variables &, const Variables &, const vector<bool> &, const vector<bool> &) = 0;
+};
+
+// Base of every function class: keeps the constructor arguments (core: nbla/function.hpp).
+template <typename... Args> class BaseFunction : public Function {
+protected:
+  std::tuple<typename std::remove_cv<typename std::remove_reference<Args>::type>::type...> args_;
+
+public:
+  BaseFunction(const Context &ctx, Args... args) : Function(ctx), args_(args...) {}
+  int num_args() const { return (int)sizeof...(Args); }
 };
 
 // ---- the five base functions: constructor arguments and the members the CUDA classes read --

@@ -23,9 +23,14 @@ def _chain(quant_op="FixedPointQuantize", quant_args=None, bn_args=None, extra_c
     return nodes
 
 
+def _mm_shapes(c=8, per_channel=True):
+    r = (1, c, 1, 1) if per_channel else (1, 1, 1, 1)
+    return {"x": (2, c, 14, 14), "w": (c, 3, 3), "qr_min": r, "qr_max": r, "ql_min": r, "ql_max": r}
+
+
 def test_chain_is_fused_into_one_node():
     for op in ("FixedPointQuantize", "Pow2Quantize", "MinMaxQuantize"):
-        fused = graph.fuse_dw_bn_quant(_chain(op), graph_outputs=["y"])
+        fused = graph.fuse_dw_bn_quant(_chain(op), graph_outputs=["y"], shapes=_mm_shapes())
         assert [n["op"] for n in fused] == [graph.FUSED]
         f = fused[0]
         assert f["outputs"] == ["y"] and f["quant"]["op"] == op
@@ -52,10 +57,89 @@ def test_patterns_that_must_not_fuse():
     # the BN output is a graph output: the quantizer is not absorbed
     g = graph.fuse_dw_bn_quant(_chain(), ["y", "n"])
     assert [n["op"] for n in g] == [graph.FUSED, "FixedPointQuantize"]
+    # MinMaxQuantize with per-tensor ranges ([1,1,1,1]) or with unknown range shapes: the fused
+    # kernel is per-channel, so the quantizer stays its own node behind the fused conv + BN
+    for shapes in (_mm_shapes(per_channel=False), None, {"w": (8, 3, 3)}):
+        g = graph.fuse_dw_bn_quant(_chain("MinMaxQuantize"), ["y"], shapes=shapes)
+        assert [n["op"] for n in g] == [graph.FUSED, "MinMaxQuantize"], shapes
+        assert g[0]["quant"] is None and g[0]["outputs"] == ["n"] and g[1]["inputs"][0] == "n"
+    # a bare [C] range vector counts as per-channel
+    v = dict(_mm_shapes(), qr_min=(8,), qr_max=(8,), ql_min=(8,), ql_max=(8,))
+    assert [n["op"] for n in graph.fuse_dw_bn_quant(_chain("MinMaxQuantize"), ["y"], shapes=v)] == [graph.FUSED]
     # unrelated nodes pass through untouched and in order
     other = {"op": "ReLU6", "inputs": ["y"], "outputs": ["r"], "args": {}}
     g = graph.fuse_dw_bn_quant(_chain() + [other], ["r"])
     assert [n["op"] for n in g] == [graph.FUSED, "ReLU6"]
+
+
+class _FakeNnabla:
+    """The surface of nnabla that from_nnabla touches: Variable.visit(callback) walks the
+    functions in forward order; a function has info.type_name, info.args, inputs, outputs;
+    a variable has shape."""
+
+    class Variable:
+        def __init__(self, shape, parent=None):
+            self.shape, self.parent = tuple(shape), parent
+
+        def visit(self, f):
+            seen, order = set(), []
+
+            def walk(v):
+                fn = v.parent
+                if fn is None or id(fn) in seen:
+                    return
+                seen.add(id(fn))
+                for i in fn.inputs:
+                    walk(i)
+                order.append(fn)
+
+            walk(self)
+            for fn in order:
+                f(fn)
+
+    class Function:
+        def __init__(self, type_name, args, inputs, out_shape):
+            import types
+            self.info = types.SimpleNamespace(type_name=type_name, args=args)
+            self.inputs = list(inputs)
+            self.outputs = [_FakeNnabla.Variable(out_shape, parent=self)]
+
+
+def test_from_nnabla_walks_a_graph_and_the_result_fuses(monkeypatch):
+    import sys
+    import types
+    monkeypatch.setitem(sys.modules, "nnabla", types.ModuleType("nnabla"))
+    V, F = _FakeNnabla.Variable, _FakeNnabla.Function
+    c = 8
+    for per_channel in (True, False):
+        r = (1, c, 1, 1) if per_channel else (1, 1, 1, 1)
+        x, w, b = V((2, c, 14, 14)), V((c, 3, 3)), V((c,))
+        beta, gamma, mean, var = (V((1, c, 1, 1)) for _ in range(4))
+        qr_min, qr_max, ql_min, ql_max = (V(r) for _ in range(4))
+        conv = F("DepthwiseConvolution", {"base_axis": 1, "pad": [1, 1], "stride": [1, 1], "dilation": [1, 1],
+                                          "multiplier": 1}, [x, w, b], (2, c, 14, 14))
+        bn = F("BatchNormalization", {"axes": [1], "decay_rate": 0.9, "eps": 1e-5, "batch_stat": False,
+                                      "no_scale": False, "no_bias": False},
+               [conv.outputs[0], beta, gamma, mean, var], (2, c, 14, 14))
+        q = F("MinMaxQuantize", {"decay": 0.999, "x_min_max": True, "ema": False, "ste_fine_grained": True,
+                                 "eps": 0.01}, [bn.outputs[0], qr_min, qr_max, ql_min, ql_max], (2, c, 14, 14))
+        relu = F("ReLU6", {}, [q.outputs[0]], (2, c, 14, 14))
+        nodes, names, shapes = graph.from_nnabla(relu.outputs[0])
+        assert [n["op"] for n in nodes] == ["DepthwiseConvolution", "BatchNormalization", "MinMaxQuantize", "ReLU6"]
+        assert nodes[0]["inputs"] == [names[x], names[w], names[b]] and nodes[2]["args"]["x_min_max"] is True
+        assert shapes[names[w]] == (c, 3, 3) and shapes[names[qr_min]] == r
+        fused = graph.fuse_dw_bn_quant(nodes, [names[relu.outputs[0]]], shapes=shapes)
+        if per_channel:
+            assert [n["op"] for n in fused] == [graph.FUSED, "ReLU6"]
+            assert fused[0]["inputs"][-4:] == [names[v] for v in (qr_min, qr_max, ql_min, ql_max)]
+            assert fused[0]["outputs"] == nodes[2]["outputs"]
+        else:
+            assert [n["op"] for n in fused] == [graph.FUSED, "MinMaxQuantize", "ReLU6"]
+
+
+def test_from_nnabla_needs_nnabla():
+    with pytest.raises(ImportError):
+        graph.from_nnabla(object())
 
 
 @pytest.mark.gpu
@@ -76,7 +160,7 @@ def test_fused_graph_equals_unfused_graph_and_oracle(oracle, cuda_device):
             return {k: torch.from_numpy(d[k].copy()).to(cuda_device) for k in names}
 
         t_unfused = graph.execute(nodes, fresh())
-        fused = graph.fuse_dw_bn_quant(nodes, ["y"])
+        fused = graph.fuse_dw_bn_quant(nodes, ["y"], shapes={k: tuple(d[k].shape) for k in names})
         assert len(fused) == 1
         t_fused = graph.execute(fused, fresh())
         assert torch.equal(t_unfused["y"].view(torch.int32), t_fused["y"].view(torch.int32)), spec.name

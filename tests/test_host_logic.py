@@ -19,13 +19,14 @@ def _desc(L, **kw):
 
 
 def test_header_symbols_are_exported_and_bound(dwlib):
-    text = open(os.path.join(ROOT, "include", "dwbnq.h")).read()
+    text = "".join(open(os.path.join(ROOT, "include", h)).read()
+                   for h in sorted(os.listdir(os.path.join(ROOT, "include"))) if h.endswith(".h"))
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     declared = set(re.findall(r"\b(dwbnq_[a-z0-9_]+)\s*\(", text))
     assert len(declared) >= 20
     lib = dwlib.lib()
     for name in declared:
-        assert hasattr(lib, name), "%s declared in dwbnq.h but not exported" % name
+        assert hasattr(lib, name), "%s declared in include/*.h but not exported" % name
         assert name in dwlib.SIGNATURES, "%s has no ctypes signature" % name
     assert set(dwlib.SIGNATURES) == declared
     assert lib.dwbnq_version() == 1

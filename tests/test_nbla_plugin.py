@@ -1,8 +1,9 @@
 """The nbla registry plugin (nnabla-ext-cuda_b200/nbla_plugin) compiled against a stand-in
 for nnabla core's C++ interface (tests/nbla_stub: nnabla itself cannot be installed here) and
 driven end to end: registration under the reference's (function, backend) keys, class names,
-the forward of each of the five functions on device buffers against the CPU oracle, and the
-refusal of backward. What this cannot show - link compatibility with a real libnnabla - stays
+the forward of each of the five functions on device buffers against the CPU oracle, the fused
+function object a graph converter substitutes for a dw-conv -> BN -> quantizer chain (through
+its extern "C" factory, float and half, every quantizer), and the refusal of backward. What this cannot show - link compatibility with a real libnnabla - stays
 open until the plugin is built in an nnabla tree."""
 import ctypes
 import os
@@ -48,6 +49,12 @@ def test_backward_raises_not_implemented(harness):
     rc = harness.stub_backward_is_refused(0)
     assert rc == 100 + 1, rc  # error_code::not_implemented
     assert b"forward pass only" in harness.stub_last_error()
+
+
+def test_fused_function_backward_raises_not_implemented(harness):
+    rc = harness.stub_fused_backward_is_refused(0)
+    assert rc == 100 + 1, rc
+    assert b"FusedDwBnQuantCuda" in harness.stub_last_error()
 
 
 def _p(t):
@@ -134,3 +141,74 @@ def test_forward_of_the_five_functions(harness, oracle, cuda_device, half):
     if not half:
         np.testing.assert_array_equal(qr_min.cpu().numpy(), wmin)
         np.testing.assert_array_equal(qr_max.cpu().numpy(), wmax)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("half", [0, 1], ids=["float", "half"])
+def test_fused_function_object(harness, oracle, cuda_device, half):
+    """FusedDwBnQuantCuda through dwbnq_nbla_create_fused: inputs in the order of the three
+    functions it replaces, output shape derived in setup, a copy() of the object run instead of
+    the original; result against the CPU oracle's three-function chain, bit for bit."""
+    import torch
+    rng = np.random.default_rng(11)
+    dt = torch.float16 if half else torch.float32
+    n, c, hw = 3, 24, 14
+    dev_index = cuda_device.index or 0
+
+    def rnd16(a):
+        return a.astype(np.float16).astype(np.float32) if half else a
+
+    x = rnd16(rng.standard_normal((n, c, hw, hw)).astype(np.float32))
+    w = rnd16((rng.standard_normal((c, 3, 3)) / 3).astype(np.float32))
+    vec = {k: rnd16((rng.random(c) + 0.5).astype(np.float32)) for k in ("b", "beta", "gamma", "mean", "var")}
+    to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(cuda_device).to(dt)
+    tx, tw = to(x), to(w)
+    tv = {k: to(v) for k, v in vec.items()}
+    scratch = torch.empty(64 * c + 1024, device=cuda_device, dtype=torch.float32)
+    harness.stub_set_scratch(_p(scratch))
+    cases = [
+        # (stride, quant dict for the oracle, kind, with b/beta/gamma)
+        (1, {"kind": "fpq", "sign": False, "n": 8, "delta": 2.0 ** -3}, 1, (True, True, True)),
+        (2, {"kind": "pow2", "sign": True, "with_zero": True, "n": 8, "m": 1}, 2, (True, True, True)),
+        (1, {"kind": "fpq", "sign": True, "n": 8, "delta": 2.0 ** -4}, 1, (False, False, True)),
+        (2, {"kind": "minmax", "x_min_max": True, "ema": False, "decay": 0.999, "eps": 0.01}, 3, (True, True, False)),
+        (1, None, 0, (True, True, True)),
+    ]
+    for stride, q, kind, (use_b, use_beta, use_gamma) in cases:
+        ho = (hw + 2 - 3) // stride + 1
+        y = torch.full((n, c, ho, ho), float("nan"), device=cuda_device, dtype=dt)
+        ranges = None
+        if kind == 3:
+            ranges = [to(np.zeros(c, np.float32)), to(np.ones(c, np.float32)), to(np.zeros(c, np.float32)),
+                      to(np.full(c, 255, np.float32))]
+            q = dict(q, qr_min=np.zeros(c, np.float32), qr_max=np.ones(c, np.float32),
+                     ql_min=np.zeros(c, np.float32), ql_max=np.full(c, 255, np.float32))
+        ptrs = [tx, tw, tv["b"] if use_b else None, tv["beta"] if use_beta else None,
+                tv["gamma"] if use_gamma else None, tv["mean"], tv["var"]] + (ranges or [None] * 4)
+        arr = (ctypes.c_void_p * 11)(*[_p(t) for t in ptrs])
+        out_shape = (ctypes.c_int64 * 4)()
+        n_inputs, copies_ok = ctypes.c_int(), ctypes.c_int()
+        qa = q or {}
+        rc = harness.stub_fused(half, dev_index, _shape(tx), _shape(tw), 4, arr, _p(y), 1, stride,
+                                ctypes.c_float(1e-5), kind, int(qa.get("sign", 0)), int(qa.get("with_zero", 0)),
+                                int(qa.get("n", 8)), int(qa.get("m", 0)), ctypes.c_float(qa.get("delta", 0.0)),
+                                ctypes.c_float(qa.get("decay", 0.0)), int(qa.get("x_min_max", 0)), int(qa.get("ema", 0)),
+                                ctypes.c_float(qa.get("eps", 0.0)), out_shape, ctypes.byref(n_inputs),
+                                ctypes.byref(copies_ok))
+        assert rc == 0, harness.stub_last_error()
+        torch.cuda.synchronize()
+        assert list(out_shape) == [n, c, ho, ho]
+        assert n_inputs.value == 4 + use_b + use_beta + use_gamma + (4 if kind == 3 else 0)
+        assert copies_ok.value == 1
+        want = oracle.fused_layer(x, w, vec["b"] if use_b else None, vec["beta"] if use_beta else None,
+                                  vec["gamma"] if use_gamma else None, vec["mean"], vec["var"], 1e-5,
+                                  (stride, stride), (1, 1), q or {"kind": "none"}, nthreads=oracle.max_threads())
+        if kind == 3:
+            want, wmin, wmax = want
+            if not half:
+                np.testing.assert_array_equal(ranges[0].cpu().numpy(), wmin)
+                np.testing.assert_array_equal(ranges[1].cpu().numpy(), wmax)
+        if half:  # binary16 storage, fp32 arithmetic, one rounding at the store
+            want = oracle.to_f16_result(want).astype(np.float32)
+        got = y.float().cpu().numpy() if half else y.cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (stride, kind, half)
