@@ -2,7 +2,7 @@
 """Benchmark of the fused dw-conv + BN-inference + quantize path.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl own|reference]
-                  [--workload cfg1|cfg0|cfg2|cfg3|cfg4] [--batch B]
+                  [--workload cfg1|cfg0|cfg2|cfg3|cfg4|ops] [--batch B] [--scaling weak|strong]
 
 A "step" is one pass of the workload's layer stack over one batch of seeded synthetic
 input (cfg1: the 17 depthwise layers of MobileNetV2 at 224x224, batch 256 per GPU, fp32,
@@ -20,6 +20,8 @@ One JSON line is printed by rank 0:
              against the measured HBM copy bandwidth (MEASURED_PEAKS.json)
   cpu_baseline  the CPU oracle (a port of the reference's CPU algorithm; nnabla core is not
              installable here) on a bounded sample, all host cores
+  other_workloads (N = 1, cfg1 only)  short device-timed passes of cfg0, cfg2, cfg3, cfg4 and the
+             five standalone operators, each with its algorithmic GB/s and roofline fraction
 --impl reference times that CPU path alone, on the same workload definition.
 """
 import argparse
@@ -50,17 +52,19 @@ def measured_peak():
 
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum, one ncu pass per launch) of the 17
-# launches of one cfg1 fp32 step at the bench batch of 256 images: 3832.2 MB read (1.000x the
-# algorithmic input bytes) + 1566.6 MB written before the kernels ended (the remaining
-# output lines are still in the 126 MB L2 then and are written back later). Traffic is
-# proportional to the batch.
-CFG1_F32_TRAFFIC_BATCH256 = 3832201984 + 1566551552
+# launches of one cfg1 fp32 step, captured at batch 64 (profiles/cfg1_step_dram_traffic_batch64.md):
+# 958.7 MB read (1.001x the algorithmic input bytes) + 171.6 MB written before the kernels
+# ended (the remaining output lines are still in the 126 MB L2 then and are written back
+# later). The read traffic is proportional to the batch, so the figure is scaled by
+# batch / 64; the write share seen before a kernel ends grows with the batch, so the scaled
+# figure is a lower bound of the writes (which cannot exceed the output bytes: no re-writes).
+CFG1_F32_TRAFFIC_BATCH64 = 958.7e6 + 171.6e6
 
 
 def measured_traffic(args, batch):
     if args.workload != "cfg1" or args.dtype != "f32" or args.only_layers or args.force_path is not None:
         return None
-    return CFG1_F32_TRAFFIC_BATCH256 * batch / 256.0
+    return CFG1_F32_TRAFFIC_BATCH64 * batch / 64.0
 
 
 class ClockSampler:
@@ -204,20 +208,14 @@ def workload_name(args):
     return names[args.workload]
 
 
-def run_standalone_ops(args):
-    """The five standalone operators on one [B, 96, 56, 56] activation (308 MB at the default
-    B = 256, fp32): per-operator time and algorithmic GB/s (2 * B bytes per element: read
-    once, write once). One JSON line in the bench format; `layers` holds the operators."""
-    import torch
-    from dwbnq import ops
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the dwbnq path has no CPU fallback")
-    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
-    torch.cuda.set_device(device)
-    half = args.dtype == "f16"
+def standalone_op_rows(torch, ops, device, n, half, warmup, reps):
+    """Times the five standalone operators on one [n, 96, 56, 56] activation, L2 flushed
+    before every timed launch. Rows of {layer, ms, gbs, bytes}; the algorithmic bytes are
+    2 * itemsize per element (read once, write once), and 3 * itemsize for MinMaxQuantize (a
+    read for the per-channel min / max, then a read and a write for the quantize step)."""
     tdtype = torch.float16 if half else torch.float32
     itemsize = 2 if half else 4
-    n, c, hw = args.batch, 96, 56
+    c, hw = 96, 56
     g = torch.Generator(device="cpu").manual_seed(0)
     x = torch.randn((n, c, hw, hw), generator=g, dtype=torch.float32).to(device).to(tdtype)
     w = (torch.randn((c, 3, 3), generator=g) / 3).to(device).to(tdtype)
@@ -235,15 +233,13 @@ def run_standalone_ops(args):
         ("MinMaxQuantize(per-channel, x_min_max)", lambda: ops.min_max_quantize(
             x, qr_min, qr_max, ql_min, ql_max, x_min_max=True, ws=ws, out=y)),
     ]
-    peak, peak_kind = measured_peak()
     rows = []
-    total_ms = 0.0
     for name, fn in calls:
-        for _ in range(args.warmup):
+        for _ in range(warmup):
             fn()
         ts = []
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        for _ in range(max(3, min(args.steps, 20))):
+        for _ in range(reps):
             flush_l2(torch, device)
             e0.record()
             fn()
@@ -251,10 +247,29 @@ def run_standalone_ops(args):
             torch.cuda.synchronize()
             ts.append(e0.elapsed_time(e1))
         ms = float(np.median(ts))
-        total_ms += ms
-        rows.append({"layer": name, "ms": ms, "gbs": 2 * x.numel() * itemsize / ms / 1e6})
+        nbytes = (3 if name.startswith("MinMax") else 2) * x.numel() * itemsize
+        rows.append({"layer": name, "ms": ms, "gbs": nbytes / ms / 1e6, "elements": x.numel(), "bytes": nbytes})
     ops.check_device_flag()
-    bytes_all = 2 * x.numel() * itemsize * len(calls)
+    return rows
+
+
+def run_standalone_ops(args):
+    """The five standalone operators on one [B, 96, 56, 56] activation (308 MB at the default
+    B = 256, fp32): per-operator time and algorithmic GB/s (2 * B bytes per element: read
+    once, write once). One JSON line in the bench format; `layers` holds the operators."""
+    import torch
+    from dwbnq import ops
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the dwbnq path has no CPU fallback")
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    half = args.dtype == "f16"
+    itemsize = 2 if half else 4
+    n, c, hw = args.batch, 96, 56
+    peak, peak_kind = measured_peak()
+    rows = standalone_op_rows(torch, ops, device, n, half, args.warmup, max(3, min(args.steps, 20)))
+    total_ms = sum(r["ms"] for r in rows)
+    bytes_all = sum(r["bytes"] for r in rows)
     achieved = bytes_all / total_ms / 1e6
     line = {"metric": "images_per_s", "value": n / (total_ms / 1e3), "unit": "images/s", "n_gpus": 1,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms, "higher_is_better": True,
@@ -291,6 +306,107 @@ def bind_to_gpu_numa_node(torch, index):
     return None
 
 
+FAMILY = {0: "fused_generic_kernel", 1: "fused_tiled_kernel (cooperative fill)", 2: "fused_tiled_kernel (TMA)",
+          3: "fused_tiled_kernel (bulk copy)", 4: "fused_plane_* kernels", 5: "fused_plane_gen_kernel"}
+
+
+def other_workloads(torch, ops, workloads, device, cfg1_layers, args):
+    """Short device-timed passes of the configurations that are not the headline workload
+    (cfg0, cfg2, cfg3, cfg4) and of the five standalone operators, each with its algorithmic
+    bytes against the measured copy bandwidth. Inputs are resident in HBM; cfg0's 51 MB
+    working set would stay in L2, so L2 is flushed before each of its timed launches; the
+    others move more than L2 holds per step and are replayed from a CUDA graph."""
+    peak, _ = measured_peak()
+    out = []
+
+    def timed(name, dtype_name, batch, specs, tensors, flush, extra=None):
+        tdtype = torch.float16 if dtype_name == "f16" else torch.float32
+        itemsize = 2 if dtype_name == "f16" else 4
+        lay = []
+        for s, t in zip(specs, tensors):
+            y = torch.empty((batch, s.c, s.ho, s.wo), dtype=tdtype, device=device)
+            q = workloads.quant_for_ops(s, t)
+            ws = ops.workspace(s.c, device) if s.quant["kind"] == "minmax" else None
+            lay.append((s, t, y, q, ws))
+
+        def step():
+            for s, t, y, q, ws in lay:
+                ops.fused_dw_bn_quant(t["x"], t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], s.bn_eps,
+                                      pad=(s.pad, s.pad), stride=(s.stride, s.stride), quant=q, ws=ws, out=y)
+
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if flush:
+            ts = []
+            for _ in range(10):
+                flush_l2(torch, device)
+                e0.record()
+                step()
+                e1.record()
+                torch.cuda.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            ms, how = float(np.median(ts)), "median of 10 launches, L2 flushed before each"
+        else:
+            g = torch.cuda.CUDAGraph()
+            cap = torch.cuda.Stream(device)
+            cap.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(cap):
+                step()
+                with torch.cuda.graph(g, stream=cap):
+                    step()
+            torch.cuda.current_stream(device).wait_stream(cap)
+            for _ in range(3):
+                g.replay()
+            torch.cuda.synchronize()
+            reps = 50
+            e0.record()
+            for _ in range(reps):
+                g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ms, how = e0.elapsed_time(e1) / reps, "mean of %d CUDA-graph replays" % reps
+        ops.check_device_flag()
+        nbytes = sum(s.algorithmic_bytes(itemsize, batch) for s in specs)
+        s0 = specs[0]
+        plan = ops.fused_plan(tensors[0]["x"], tensors[0]["w"], lay[0][2], pad=(s0.pad, s0.pad),
+                              stride=(s0.stride, s0.stride))
+        row = {"workload": name, "dtype": dtype_name, "batch": batch, "ms": ms, "images_per_s": batch / (ms / 1e3),
+               "gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak, "algorithmic_bytes": nbytes,
+               "kernel": FAMILY.get(plan["path"], "?") if len(specs) == 1 else "fused_plane_* kernels (17 launches)",
+               "timing": how}
+        if extra:
+            row.update(extra)
+        out.append(row)
+
+    def on_device(spec, n, tdtype):
+        d = workloads.make_layer_data(spec, n=n)
+        return {k: torch.from_numpy(v).to(device).to(tdtype) for k, v in d.items()}
+
+    s = workloads.cfg0()
+    timed("cfg0", "f32", 32, s, [on_device(s[0], 32, torch.float32)], flush=True)
+    s = workloads.cfg2()
+    timed("cfg2", "f32", 128, s, [on_device(s[0], 128, torch.float32)], flush=False)
+    s = workloads.cfg3()
+    timed("cfg3", "f32", 512, s, [on_device(s[0], 512, torch.float32)], flush=False,
+          extra={"note": "one GPU, no collective; two passes (reduce + store fp32, quantize in place): "
+                         "executed bytes 4*(E_in + 3*E_out), gbs counts the compulsory 4*(E_in + E_out)"})
+    if args.dtype == "f32" and cfg1_layers and cfg1_layers[0][0].n == 256:
+        # cfg4 = the cfg1 tensors cast to fp16
+        specs = [l[0] for l in cfg1_layers]
+        tens = [{k: v.half() for k, v in l[2].items()} for l in cfg1_layers]
+        timed("cfg4", "f16", 256, specs, tens, flush=False)
+        del tens
+    for r in standalone_op_rows(torch, ops, device, 256, False, 3, 10):
+        out.append({"workload": "op: " + r["layer"], "dtype": "f32", "batch": 256, "ms": r["ms"],
+                    "images_per_s": 256 / (r["ms"] / 1e3), "gbs": r["gbs"], "frac": r["gbs"] / peak,
+                    "algorithmic_bytes": r["bytes"], "kernel": "standalone operator on [256,96,56,56]",
+                    "timing": "median of 10 launches, L2 flushed before each"})
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_own(args):
     import torch
     import torch.distributed as dist
@@ -310,7 +426,14 @@ def run_own(args):
     half = args.workload == "cfg4" or args.dtype == "f16"
     tdtype = torch.float16 if half else torch.float32
     itemsize = 2 if half else 4
-    batch = args.batch
+    # weak scaling (default): --batch images on every GPU. strong: --batch is the GLOBAL batch,
+    # split evenly, so the total work stays fixed as GPUs are added.
+    if args.scaling == "strong":
+        if args.batch % world:
+            raise SystemExit("--scaling strong needs a global batch divisible by the GPU count")
+        batch = args.batch // world
+    else:
+        batch = args.batch
     specs = workloads.workload(args.workload, batch)
     if args.only_layers:
         specs = [specs[int(i)] for i in args.only_layers.split(",")]
@@ -330,7 +453,7 @@ def run_own(args):
         layers.append((s, host, devt, y, y_host, q, ws))
     torch.cuda.synchronize()
 
-    def launch(layer, x=None):
+    def launch(layer, x=None, use_comm=True):
         s, _, t, y, _, q, ws = layer
         if args.ablate:  # profiling only: drop BN and / or the quantizer to attribute instruction counts
             bn = None if "bn" in args.ablate else t
@@ -340,8 +463,8 @@ def run_own(args):
                                   quant=qq, out=y)
             return
         ops.fused_dw_bn_quant(t["x"] if x is None else x, t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"],
-                              s.bn_eps, pad=(s.pad, s.pad), stride=(s.stride, s.stride), quant=q, comm=comm, ws=ws,
-                              out=y)
+                              s.bn_eps, pad=(s.pad, s.pad), stride=(s.stride, s.stride), quant=q,
+                              comm=comm if use_comm else None, ws=ws, out=y)
 
     def step_eager():
         for layer in layers:
@@ -392,15 +515,22 @@ def run_own(args):
         sampler.start()
         time.sleep(0.3)
     barrier()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # events every `chunk` steps inside the one timed region: the value is total / steps (mean);
+    # the chunks give the median and the best step beside it
+    chunk = 5 if args.steps >= 10 else 1
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps // chunk + 2)]
     t_begin = time.time()
-    ev0.record()
-    for _ in range(args.steps):
+    marks[0].record()
+    n_marks = 1
+    for i in range(args.steps):
         step()
-    ev1.record()
+        if (i + 1) % chunk == 0 or i + 1 == args.steps:
+            marks[n_marks].record()
+            n_marks += 1
     barrier()
     t_end = time.time()
-    elapsed_ms = ev0.elapsed_time(ev1)
+    elapsed_ms = marks[0].elapsed_time(marks[n_marks - 1])
+    chunk_ms = [marks[j].elapsed_time(marks[j + 1]) / chunk for j in range(args.steps // chunk)]
     # A short timed region sees too few of the 50 ms clock samples: keep the same load running,
     # untimed, until 0.4 s of it have been sampled.
     while comm is None and time.time() - t_begin < 0.4:  # (steps with a collective must stay in lock step)
@@ -410,6 +540,28 @@ def run_own(args):
     barrier()
     clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
     ops.check_device_flag()
+
+    # ---- MinMax with a collective: where the step's time goes ------------------------------
+    # (a) the two passes alone (every rank reduces and quantizes with its own shard's ranges),
+    # (b) the bare all-reduce(max) of the 2*C packed floats, back to back on the stream; the
+    # step itself, timed above, is (a) + pack kernel + all-reduce in between.
+    phase_ms = [0.0, 0.0]
+    if comm is not None:
+        def loop_ms(fn, reps=50):
+            for _ in range(3):
+                fn()
+            barrier()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            for _ in range(reps):
+                fn()
+            a1.record()
+            barrier()
+            return a0.elapsed_time(a1) / reps
+
+        phase_ms[0] = loop_ms(lambda: [launch(layer, use_comm=False) for layer in layers])
+        buf = torch.zeros(2 * max(s.c for s in specs), device=device, dtype=torch.float32)
+        phase_ms[1] = loop_ms(lambda: comm.allreduce_max_(buf))
 
     # ---- per-layer durations (separate pass, same launches; for the roofline breakdown) ----
     per_layer = []
@@ -442,7 +594,7 @@ def run_own(args):
     ev_out = [torch.cuda.Event() for _ in layers]
     first = [True]
 
-    def e2e_step():
+    def e2e_step(kernels=True):
         for i, layer in enumerate(layers):
             s, host, t, y, y_host, q, ws = layer
             with torch.cuda.stream(up):
@@ -453,7 +605,8 @@ def run_own(args):
             compute.wait_event(ev_in[i])
             if not first[0]:
                 compute.wait_event(ev_out[i])  # last step's result has left the output buffer
-            launch(layer)
+            if kernels:
+                launch(layer)
             ev_done[i].record(compute)
             with torch.cuda.stream(down):
                 down.wait_event(ev_done[i])
@@ -479,14 +632,32 @@ def run_own(args):
     barrier()
     e2e_ms = max(e0.elapsed_time(e1), 0.0)
     e2e_wall_ms = 1e3 * (time.perf_counter() - t0)
+    # The same copies on the same three streams with the same event chain and NO kernel: how
+    # fast the box moves these bytes at this N. e2e close to it = bound by the copies.
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    for _ in range(0 if args.no_e2e else e2e_steps):
+        e2e_step(kernels=False)
+    e2e_join()
+    c1.record()
+    barrier()
+    copy_ms = max(c0.elapsed_time(c1), 0.0)
     h2d = sum(l[1]["x"].numel() * itemsize for l in layers)
     d2h = sum(l[3].numel() * itemsize for l in layers)
 
+    # ---- the other configurations and the standalone operators (N = 1, cfg1 runs only) --------
+    other = None
+    if world == 1 and args.workload == "cfg1" and not args.no_other and not args.only_layers and \
+            args.force_path is None and not args.ablate:
+        other = other_workloads(torch, ops, workloads, device, layers, args)
+
     # ---- max over ranks ---------------------------------------------------------------------
     if world > 1:
-        tt = torch.tensor([elapsed_ms, e2e_ms], device=device, dtype=torch.float64)
+        tt = torch.tensor([elapsed_ms, e2e_ms, copy_ms] + phase_ms + chunk_ms, device=device, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        elapsed_ms, e2e_ms = float(tt[0]), float(tt[1])
+        elapsed_ms, e2e_ms, copy_ms = float(tt[0]), float(tt[1]), float(tt[2])
+        phase_ms = [float(tt[3]), float(tt[4])]
+        chunk_ms = [float(v) for v in tt[5:]]
 
     if rank == 0:
         images = batch * world * args.steps
@@ -507,7 +678,10 @@ def run_own(args):
         bytes_per_image = sum(s.algorithmic_bytes(4, 1) for s in specs)
         line = {
             "metric": "images_per_s", "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "ms_per_step_median": float(np.median(chunk_ms)) if chunk_ms else ms_per_step,
+            "ms_per_step_best": float(min(chunk_ms)) if chunk_ms else ms_per_step,
+            "higher_is_better": True, "scaling": args.scaling,
             "vs_baseline": None, "dtype": "f16" if half else "f32", "data": "synthetic",
             "config": {"workload": workload_name(args), "batch_per_gpu": batch, "global_batch": batch * world,
                        "layers": len(specs), "parallelism": "batch-sharded x%d" % world, "numa_node": numa, "launch": "cuda graph" if graph is not None else "stream",
@@ -527,11 +701,23 @@ def run_own(args):
                              "value_one_core": cpu_1core},
             "e2e": {"value": None if args.no_e2e else batch * world * e2e_steps / (e2e_ms / 1e3), "unit": "images/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-                    "wall_ms_per_step": e2e_wall_ms / e2e_steps},
+                    "wall_ms_per_step": e2e_wall_ms / e2e_steps,
+                    "copy_only": None if args.no_e2e else {
+                        "value": batch * world * e2e_steps / (copy_ms / 1e3), "unit": "images/s",
+                        "gbs_per_gpu": (h2d + d2h) * e2e_steps / (copy_ms / 1e3) / 1e9,
+                        "what": "the same host<->device copies, streams and events without the kernels"}},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
             "layers": per_layer,
         }
+        if other is not None:
+            line["other_workloads"] = other
+        if comm is not None:
+            line["phases"] = {"step_ms": ms_per_step, "two_passes_without_collective_ms": phase_ms[0],
+                              "allreduce_max_alone_ms": phase_ms[1],
+                              "collective_share_of_step": max(0.0, 1.0 - phase_ms[0] / ms_per_step),
+                              "what": "max over ranks; the collective is one ncclAllReduce(max) of 2*C floats "
+                                      "between the reduce pass and the quantize pass"}
         print(json.dumps(line), flush=True)
     if comm is not None:
         comm.destroy()
@@ -568,6 +754,9 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-layer-pass", action="store_true")
+    ap.add_argument("--no-other", action="store_true", help="skip the short passes of the other configurations")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: --batch images per GPU; strong: --batch is the global batch, split over the GPUs")
     ap.add_argument("--ablate", default="", help="profiling only: 'bn', 'quant' or 'bn,quant' are left out")
     ap.add_argument("--no-graph", dest="graph", action="store_false",
                     help="launch every kernel from the host instead of replaying the step from a CUDA graph")

@@ -37,6 +37,14 @@ struct QuantArgs {
   int p_window;               // |mantissa - sqrt2 mantissa| beyond which no table look-up is needed
   int p_fast;                 // p_min >= 2^-125: zeros and subnormals need no exact exponent
   const uint32_t *p_table;    // 277 thresholds, device memory
+  // Pow2Quantize as a function of the magnitude bit pattern a = bits(|x|) alone (host-derived
+  // from the same libm thresholds): a is clamped to [p_lo_bits, p_hi_bits] = bits(p_min),
+  // bits(p_max) before the rounding (every pattern outside rounds to the same result as the
+  // bound), a < p_prune_bits gives zero (with_zero: min(bits(pruning_threshold), first
+  // pattern that rounds to p_min); otherwise 0 = never), and a negative input turns the
+  // result q into (q & p_neg_keep) ^ p_neg_xor: -q (sign), +0.0 (unsigned, with_zero) or
+  // p_min (unsigned, without zero).
+  unsigned int p_lo_bits, p_hi_bits, p_prune_bits, p_neg_keep, p_neg_xor;
   // MinMaxQuantize second pass: per-channel fp32 arrays in the workspace.
   const float *mm_scale, *mm_lo, *mm_hi;
   // MinMaxQuantize first pass: per-channel order-encoded min / max in the workspace.
@@ -245,30 +253,39 @@ __device__ __forceinline__ float pow2_apply(float x, const QuantArgs &p) {
   if (rare) q = pow2_round_exact(a, p.p_table, p.p_window);
   return pow2_finish(q, x, __uint_as_float(a), p);
 }
-// N values at once: the fast roundings of all N are independent straight-line code (the
-// scheduler interleaves them); the out-of-line exact rounding is reached through ONE branch
-// per group, taken when any of the N is a rare pattern.
+// N values at once, branch-free in the common case. With the magnitude pattern clamped to
+// [bits(p_min), bits(p_max)] first, the clamp rules of the quantizer need no test of their own
+// (a pattern below bits(p_min) gives p_min unless it is pruned, one above bits(p_max) gives
+// p_max, and the clamped bounds have a zero mantissa: never near a rounding threshold), the
+// pruning rule is one compare on the pattern, and the sign rule one select. What does not fit
+// this scheme - a NaN, a mantissa within the window around the rounding threshold, a p_min
+// that is not a normal number - is detected for the whole group with a running minimum /
+// maximum and re-evaluated value by value through pow2_apply (ONE branch per group).
 template <int N>
 __device__ __forceinline__ void pow2_apply_n(float *v, const QuantArgs &p) {
-  float q[N];
-  bool any = false;
+  unsigned int q[N];
+  unsigned int near = 0xffffffffu, amax = 0u;
+  const unsigned int w = (unsigned int)p.p_window;
 #pragma unroll
   for (int j = 0; j < N; ++j) {
-    bool rare;
-    q[j] = pow2_round_fast(__float_as_uint(v[j]) & 0x7fffffffu, p, &rare);
-    any = any || rare;
+    const unsigned int a = __float_as_uint(v[j]) & 0x7fffffffu;
+    const unsigned int ac = min(max(a, p.p_lo_bits), p.p_hi_bits);
+    const unsigned int t = ac + 0x004afb0du;  // carries into the exponent above sqrt(2)'s mantissa
+    near = min(near, (t + w) & 0x007fffffu);  // <= 2w: within the window of the threshold
+    amax = max(amax, a);
+    q[j] = a < p.p_prune_bits ? 0u : (t & 0x7f800000u);
   }
-  if (any) {
+  const bool any_rare = near <= 2u * w || amax > 0x7f800000u || !p.p_fast;
+  if (any_rare) {
 #pragma unroll
-    for (int j = 0; j < N; ++j) {
-      const unsigned int a = __float_as_uint(v[j]) & 0x7fffffffu;
-      bool rare;
-      (void)pow2_round_fast(a, p, &rare);
-      if (rare) q[j] = pow2_round_exact(a, p.p_table, p.p_window);
-    }
+    for (int j = 0; j < N; ++j) v[j] = pow2_apply(v[j], p);
+    return;
   }
 #pragma unroll
-  for (int j = 0; j < N; ++j) v[j] = pow2_finish(q[j], v[j], fabsf(v[j]), p);
+  for (int j = 0; j < N; ++j) {
+    const unsigned int alt = (q[j] & p.p_neg_keep) ^ p.p_neg_xor;
+    v[j] = __uint_as_float(v[j] < 0.0f ? alt : q[j]);
+  }
 }
 
 // ---- MinMaxQuantize, quantize step ---------------------------------------------------

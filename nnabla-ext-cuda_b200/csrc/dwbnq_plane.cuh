@@ -43,14 +43,14 @@ constexpr int kPlaneRows = 7;  // rows per thread
 
 // Stash row of a thread: [2 unused | left halo | W elements | right halo | pad], even size.
 __host__ __device__ constexpr int plane_stash_elems(int W) { return (W + 4 + 1) / 2 * 2; }
-// stride 1: tile | stash (NRB > 1) | weight pairs (5x5) | mbarrier
+// stride 1: tile | stash (NRB > 1) | weight pairs, row of zeros (5x5) | mbarrier
 __host__ __device__ constexpr size_t plane_smem_bytes(int K, int W, int NRB, int NCB, int NBND, int elem_size) {
   const int P = 32 / (NRB * NCB);
   size_t s = (size_t)P * (kPlaneRows * NRB + (NBND > 1 ? 2 * (K / 2) : 0)) * (W * NCB) * elem_size;
   s = (s + 15) / 16 * 16;
   if (NRB > 1) s += (size_t)32 * (K / 2) * plane_stash_elems(W) * elem_size;
   s = (s + 15) / 16 * 16;
-  if (K == 5) s += (size_t)P * 25 * 8;  // weight pairs
+  if (K == 5) s += (size_t)P * 25 * 8 + 128;  // weight pairs, row of zeros
   return s + 16;
 }
 // stride 2: input tile (with the row above a band) | output tile | mbarrier
@@ -426,8 +426,11 @@ __global__ void __launch_bounds__(32, 16)
 // row finished in a step hands its registers to the row started in the same step, so K-1
 // sets are live and the loop is unrolled K-1 steps per trip to keep the set indices static.
 // Compiled for 16 one-warp CTAs per SM (128 registers).
+// Compiled for 12 one-warp CTAs per SM: the tile, stash and weight pairs of a 56 x 56 fp32
+// plane (17.5 KB) leave room for no more, and the registers this frees (140 instead of 128)
+// save moves.
 template <typename T, int K, int W, int NRB, int NCB, int NBND, int QM>
-__global__ void __launch_bounds__(32, 16)
+__global__ void __launch_bounds__(32, K == 5 ? 12 : 16)
     fused_plane_kxk_kernel(const __grid_constant__ FusedArgs a, const PlaneCfg c) {
   static_assert(K == 3 || K == 5, "3x3 or 5x5");
   static_assert(NCB == 1 || W % 2 == 0, "column blocks need an even block width");
@@ -461,10 +464,14 @@ __global__ void __launch_bounds__(32, 16)
   constexpr size_t stash_bytes = NRB > 1 ? ((size_t)32 * PAD * SW * sizeof(T) + 15) / 16 * 16 : 0;
   f32x2 *wsm = reinterpret_cast<f32x2 *>(smem_raw + tile_bytes + stash_bytes);
   constexpr size_t wsm_bytes = W_SMEM ? (size_t)P * KK * sizeof(f32x2) : 0;
+  // 5x5: 128 bytes of zeros that stand in for a row (or a neighbour's columns) outside the plane
+  constexpr size_t zrow_bytes = K == 5 ? 128 : 0;
+  T *zrow = reinterpret_cast<T *>(smem_raw + tile_bytes + stash_bytes + wsm_bytes);
   unsigned long long *bar =
-      reinterpret_cast<unsigned long long *>(smem_raw + tile_bytes + stash_bytes + wsm_bytes);
+      reinterpret_cast<unsigned long long *>(smem_raw + tile_bytes + stash_bytes + wsm_bytes + zrow_bytes);
 
   const int lane = threadIdx.x;
+  if (K == 5) reinterpret_cast<float *>(zrow)[lane] = 0.0f;
   const int n_planes = (int)(a.n * a.OC);
   const int plane0 = (NBND > 1 ? blockIdx.x / NBND : blockIdx.x) * P;
   const int r0 = NBND > 1 ? (blockIdx.x % NBND) * TB : 0;  // first plane row of the tile
@@ -579,17 +586,38 @@ __global__ void __launch_bounds__(32, 16)
                                                               : rows + (k - PAD) * PW;
     // xs[PAD + j] = element j of the row, j = -PAD .. W + PAD - 1 (zeros outside the plane)
     float xs[2 * NP + 2 * PAD + 1];
-    plane_load_row<T, W>(src, valid, xs + PAD);
+    f32x2 Lm[NP + 1];  // 5x5: the odd-offset pairs (x[2j-1], x[2j]), loaded as such
+    if (K == 5 && W % 2 == 0) {
+      // Unconditional loads: a row (or a neighbour's columns) outside the plane is read from
+      // the row of zeros instead, chosen by pointer, so the step has no per-load predicate
+      // (the compiler turned each predicated load into a branch); the odd-offset pairs are
+      // loaded straight into register pairs instead of being assembled with moves.
+      const T *zc = zrow + 8;
+      const T *rp = valid ? src : zc;
+      const T *lp = (NCB > 1 && valid && has_left) ? src : zc;
+      const T *rq = (NCB > 1 && valid && has_right) ? src : zc;
+      plane_load_row<T, 2>(lp - 2, true, xs);
+      plane_load_row<T, W>(rp, true, xs + PAD);
+      plane_load_row<T, 2>(rq + W, true, xs + PAD + W);
 #pragma unroll
-    for (int e = 1; e <= PAD; ++e) {
-      xs[PAD - e] = 0.0f;
-      if (W % 2 == 0) xs[PAD + W - 1 + e] = 0.0f;
-      if (NCB > 1) {
-        if (valid && has_left) xs[PAD - e] = Elem<T>::to_f32(src[-e]);
-        if (valid && has_right) xs[PAD + W - 1 + e] = Elem<T>::to_f32(src[W - 1 + e]);
+      for (int j = 0; j <= NP; ++j) {
+        const float a0 = Elem<T>::to_f32(j == 0 ? lp[-1] : rp[2 * j - 1]);
+        const float a1 = Elem<T>::to_f32(j == NP ? rq[W] : rp[2 * j]);
+        Lm[j] = pack2(a0, a1);
       }
+    } else {
+      plane_load_row<T, W>(src, valid, xs + PAD);
+#pragma unroll
+      for (int e = 1; e <= PAD; ++e) {
+        xs[PAD - e] = 0.0f;
+        if (W % 2 == 0) xs[PAD + W - 1 + e] = 0.0f;
+        if (NCB > 1) {
+          if (valid && has_left) xs[PAD - e] = Elem<T>::to_f32(src[-e]);
+          if (valid && has_right) xs[PAD + W - 1 + e] = Elem<T>::to_f32(src[W - 1 + e]);
+        }
+      }
+      if (W % 2 != 0) xs[PAD + W + 1] = 0.0f;
     }
-    if (W % 2 != 0) xs[PAD + W + 1] = 0.0f;
     // Reads of this step come before any write of this step: rows above the block are the
     // upper neighbour's last rows (written in its last steps), and a neighbour's edge columns
     // of this row are overwritten by their owner K-1 steps later.
@@ -601,7 +629,8 @@ __global__ void __launch_bounds__(32, 16)
 #pragma unroll
     for (int j = -EH; j < NP + EH; ++j) E[EH + j] = pack2(xs[PAD + 2 * j], xs[PAD + 2 * j + 1]);
 #pragma unroll
-    for (int j = 0; j <= NP; ++j) L[j] = pack2(xs[PAD + 2 * j - 1], xs[PAD + 2 * j]);
+    for (int j = 0; j <= NP; ++j)
+      L[j] = (K == 5 && W % 2 == 0) ? Lm[j] : pack2(xs[PAD + 2 * j - 1], xs[PAD + 2 * j]);
     constexpr bool LAST_L_ZERO = (W % 2) != 0;  // odd W (3x3 only): L[NP] = (0, 0)
 
     // ky = m taps of this input row onto the accumulator row that started m steps ago
@@ -650,7 +679,8 @@ __global__ void __launch_bounds__(32, 16)
       }
       if (qm_stores(QM)) {
         plane_quant<QM, W>(o, a.q, mm);
-        if (active) plane_store_row<T, W>(rows + (k - (K - 1)) * PW, o);
+        // (a lane without a plane writes into its own, never copied-out part of the tile)
+        if (K == 5 || active) plane_store_row<T, W>(rows + (k - (K - 1)) * PW, o);
       }
     }
 #pragma unroll

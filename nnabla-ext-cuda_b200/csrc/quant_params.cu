@@ -103,6 +103,40 @@ int fill_pow2(QuantArgs *q, int sign, int with_zero, int n, int m, int device) {
   q->p_with_zero = with_zero ? 1 : 0;
   q->p_window = pow2_table_window();
   q->p_fast = q->p_min >= 2.350988701644575e-38f ? 1 : 0;  // 2^-125
+  // The quantizer as a function of the magnitude pattern (see QuantArgs). first_reaching(v):
+  // the smallest pattern a with 2^round(log2f(a)) >= v, by bisection with the host libm (the
+  // rounded exponent is monotone in a).
+  auto float_bits = [](float f) {
+    uint32_t b;
+    std::memcpy(&b, &f, 4);
+    return b;
+  };
+  auto first_reaching = [&](float v) {
+    uint32_t lo = 1u, hi = 0x7f800000u;  // q(hi) = inf >= v
+    while (lo < hi) {
+      const uint32_t mid = lo + (hi - lo) / 2;
+      if (powf(2.0f, roundf(log2f(bits_to_float(mid)))) >= v) hi = mid;
+      else lo = mid + 1;
+    }
+    return lo;
+  };
+  q->p_lo_bits = float_bits(q->p_min);
+  q->p_hi_bits = float_bits(q->p_max);
+  q->p_prune_bits = 0u;
+  if (with_zero && q->p_min > 0.0f) {
+    const uint32_t a_min = first_reaching(q->p_min);  // patterns below it round below p_min
+    const uint32_t thr = float_bits(q->prune_thr);
+    q->p_prune_bits = a_min < thr ? a_min : thr;
+  }
+  if (sign) {
+    q->p_neg_keep = 0xffffffffu;
+    q->p_neg_xor = 0x80000000u;
+  } else {
+    q->p_neg_keep = 0u;
+    q->p_neg_xor = with_zero ? 0u : float_bits(q->p_min);
+  }
+  // the pattern form needs p_min and p_max to be normal numbers with p_min <= p_max
+  if (!(q->p_max < INFINITY) || !(q->p_min <= q->p_max)) q->p_fast = 0;
   return pow2_table_device(device, &q->p_table);
 }
 

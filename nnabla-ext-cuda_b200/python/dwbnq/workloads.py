@@ -1,9 +1,13 @@
 """The benchmark / parity workloads and their seeded synthetic inputs.
 
 No dataset is involved: activations, weights and BN statistics are drawn from the
-distributions the workload definitions state, with ``numpy.random.default_rng(seed)``
-and a fixed draw order per layer (x, W, b, mean, var, gamma, beta, then MinMax outliers),
-all in float32. ``N(mu, v)`` below means variance ``v``.
+distributions the workload definitions state, all in float32, with
+``numpy.random.default_rng``: the parameters of a layer come first from the layer's
+generator (seed), in the order W, b, mean, var, gamma, beta; every image then comes from a
+generator of its own (seed, image index), which draws x and, for cfg3, the outlier mask and
+values. An image is therefore the same whichever batch shard it is drawn in, which is what
+lets the ranks of a sharded job and the single-device oracle see identical data.
+``N(mu, v)`` below means variance ``v``.
 
 Workloads (ids follow the benchmark's config list):
   cfg0  single layer  x[32,64,56,56]~N(0,1), 3x3 s1 p1, BN, FixedPointQuantize(sign, n=8, delta=2^-4)

@@ -758,6 +758,56 @@ def test_full_size_largest_layer_sampled_images(oracle, cuda_device):
     ops.check_device_flag()
 
 
+def test_full_size_cfg2_batch128(oracle, cuda_device):
+    """cfg2 at its full batch of 128 (5x5 + BN + Pow2Quantize on [128,144,56,56]): the GPU runs
+    the whole seeded batch, the oracle checks whole images from its start, middle and end; all
+    outputs are checked through the quantizer's value set (0 or +-2^k, 2^-62 <= |y| <= 2)."""
+    spec = workloads.cfg2()[0]
+    assert (spec.n, spec.c, spec.h, spec.k) == (128, 144, 56, 5)
+    d = workloads.make_layer_data(spec)
+    q = workloads.quant_for_ops(spec)
+    got, _ = run_fused(d, spec, cuda_device, q)
+    for first in (0, 62, 126):
+        sub = dict(d, x=d["x"][first:first + 2])
+        want, _, _ = oracle_fused(oracle, sub, spec, q)
+        assert_same_bits(got[first:first + 2], want, "cfg2 images %d, %d of 128" % (first, first + 1))
+    a = np.abs(got)
+    nz = a[a != 0]
+    mant, expo = np.frexp(nz)
+    assert np.all(mant == 0.5) and expo.min() - 1 >= -62 and expo.max() - 1 <= 1
+
+
+def test_full_size_cfg3_batch512_every_image(oracle, cuda_device):
+    """cfg3 at its full batch of 512 (3x3 stride 2 + BN + per-channel MinMaxQuantize whose
+    min / max run over the whole batch): the oracle computes all 512 images on all host cores
+    and every output and both range vectors are compared."""
+    spec = workloads.cfg3()[0]
+    assert (spec.n, spec.c, spec.h, spec.stride) == (512, 192, 28, 2)
+    d = workloads.make_layer_data(spec)
+    q = workloads.quant_for_ops(spec, d)
+    want, _, (qmin, qmax) = oracle_fused(oracle, d, spec, q)
+    got, t = run_fused(d, spec, cuda_device, q)
+    assert_same_bits(got, want, "cfg3, all 512 images")
+    np.testing.assert_array_equal(t["qr_min"].cpu().numpy(), qmin)
+    np.testing.assert_array_equal(t["qr_max"].cpu().numpy(), qmax)
+    # at most 256 levels per channel
+    assert max(len(np.unique(got[:, c])) for c in (0, 95, 191)) <= 256
+
+
+@pytest.mark.parametrize("layer", [4, 14], ids=["28x28x192_s1", "7x7x960_s1"])
+def test_full_size_cfg4_fp16_batch256(oracle, cuda_device, layer):
+    """Two cfg4 layers (fp16 storage, fp32 arithmetic) at the bench batch of 256, every output
+    against the oracle's fp16 convention: a stride-1 28x28 layer and a 7x7 layer."""
+    spec = workloads.cfg1()[layer]
+    assert spec.n == 256 and spec.stride == 1
+    d = workloads.make_layer_data(spec)
+    h, up = f16_inputs(d)
+    q = workloads.quant_for_ops(spec)
+    want32, _, _ = oracle_fused(oracle, up, spec, q)
+    got, _ = run_fused(h, spec, cuda_device, q, dtype=torch.float16)
+    assert_same_bits(got, oracle.to_f16_result(want32), "cfg4 layer %d at batch 256" % layer)
+
+
 def test_more_than_2_pow_31_elements(oracle, cuda_device):
     """Offsets beyond 2^31 elements (the reference indexes with int): a [1800, 96, 112, 112]
     input has 2.17e9 elements; the last images are checked against the oracle."""

@@ -4,9 +4,9 @@ Such callers exist: a function object that a framework invokes with nothing but 
 pointers after the framework's pool has taken the whole device, or a serving loop that may
 not enter the allocator once it runs. For them the library keeps the per-channel scratch in
 a fixed device array of its own. This file checks, through the C ABI, that the entry point
-produces exactly what dwbnq_minmaxq_fwd produces with a caller-provided workspace - on two
-consecutive calls, because the array keeps the previous call's contents - and that it refuses
-more channels than the array holds. It is named to be collected last, so a run that stops at
+produces exactly what dwbnq_minmaxq_fwd produces with a caller-provided workspace, and (in
+fp32) what the CPU oracle computes - on two consecutive calls, because the array keeps the
+previous call's contents - and that it refuses more channels than the array holds. It is named to be collected last, so a run that stops at
 the first failure has already executed every other test.
 """
 import ctypes
@@ -33,7 +33,7 @@ def _static_call(x, qr_min, qr_max, ql_min, ql_max, q, y):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16], ids=["f32", "f16"])
-def test_static_workspace_matches_caller_workspace_twice(cuda_device, dtype):
+def test_static_workspace_matches_caller_workspace_twice(cuda_device, oracle, dtype):
     g = torch.Generator(device="cpu").manual_seed(5)
     # two different problems back to back: the second one finds the first one's leftovers
     for shape in ((6, 192, 14, 14), (3, 37, 9, 5)):
@@ -57,6 +57,12 @@ def test_static_workspace_matches_caller_workspace_twice(cuda_device, dtype):
             assert torch.equal(got.view(bits), want.view(bits)), (shape, x_min_max, ema)
             assert torch.equal(got_min.view(bits), want_min.view(bits))
             assert torch.equal(got_max.view(bits), want_max.view(bits))
+            if dtype == torch.float32:  # and against the CPU oracle itself, not only CUDA against CUDA
+                oy, omin, omax = oracle.minmaxq(x.cpu().numpy(), qr0.numpy(), qr1.numpy(), ql_min.cpu().numpy(),
+                                                ql_max.cpu().numpy(), 0.9, x_min_max, ema, 0.01)
+                assert np.array_equal(got.cpu().numpy().view(np.uint32), oy.view(np.uint32)), (shape, x_min_max, ema)
+                np.testing.assert_array_equal(got_min.cpu().numpy(), omin)
+                np.testing.assert_array_equal(got_max.cpu().numpy(), omax)
     ops.check_device_flag()
 
 
