@@ -2,7 +2,7 @@
 """Benchmark of the fused dw-conv + BN-inference + quantize path.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl own|reference]
-                  [--workload cfg1|cfg0|cfg2|cfg3|cfg4|ops] [--batch B] [--scaling weak|strong]
+                  [--workload cfg1|cfg0|cfg2|cfg3|cfg4|cfg1q8|ops] [--batch B] [--scaling weak|strong]
 
 A "step" is one pass of the workload's layer stack over one batch of seeded synthetic
 input (cfg1: the 17 depthwise layers of MobileNetV2 at 224x224, batch 256 per GPU, fp32,
@@ -204,7 +204,9 @@ def workload_name(args):
              "cfg1": "cfg1 MobileNetV2 17 depthwise 3x3 layers @224 + BN + FixedPointQuantize(unsigned,n=8,2^-3)",
              "cfg2": "cfg2 [B,144,56,56] 5x5 s1 + BN + Pow2Quantize(sign,with_zero,n=8,m=1)",
              "cfg3": "cfg3 [B,192,28,28] 3x3 s2 + BN + MinMaxQuantize(per-channel, batch-inclusive)",
-             "cfg4": "cfg4 = cfg1 in fp16"}
+             "cfg4": "cfg4 = cfg1 in fp16",
+             "cfg1q8": "cfg1 with 8-bit storage: inputs are uint8 codes of FixedPointQuantize(unsigned,n=8,2^-5) of the "
+                       "cfg1 activations, outputs the uint8 codes of the layer's FixedPointQuantize(unsigned,n=8,2^-3)"}
     return names[args.workload]
 
 
@@ -424,8 +426,10 @@ def run_own(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     half = args.workload == "cfg4" or args.dtype == "f16"
+    code8 = args.workload == "cfg1q8"  # activations travel as one-byte codes, parameters stay fp32
     tdtype = torch.float16 if half else torch.float32
-    itemsize = 2 if half else 4
+    itemsize = 1 if code8 else (2 if half else 4)
+    in_delta = 2.0 ** -5
     # weak scaling (default): --batch images on every GPU. strong: --batch is the GLOBAL batch,
     # split evenly, so the total work stays fixed as GPUs are added.
     if args.scaling == "strong":
@@ -445,9 +449,13 @@ def run_own(args):
     for s in specs:
         d = workloads.make_layer_data(s, n=batch, first_image=rank * batch)
         host = {k: torch.from_numpy(v).to(tdtype).pin_memory() for k, v in d.items()}
+        if code8:  # the layer input as the previous layer would have left it: FixedPointQuantize codes
+            xq = np.clip(np.floor(d["x"] / np.float32(in_delta) + np.float32(0.5)), 0, 255).astype(np.uint8)
+            host["x"] = torch.from_numpy(xq).pin_memory()
         devt = {k: v.to(device, non_blocking=True) for k, v in host.items()}
-        y = torch.empty((batch, s.c, s.ho, s.wo), dtype=tdtype, device=device)
-        y_host = torch.empty(y.shape, dtype=tdtype).pin_memory()
+        ydt = torch.uint8 if code8 else tdtype
+        y = torch.empty((batch, s.c, s.ho, s.wo), dtype=ydt, device=device)
+        y_host = torch.empty(y.shape, dtype=ydt).pin_memory()
         q = workloads.quant_for_ops(s, devt)
         ws = ops.workspace(s.c, device) if s.quant["kind"] == "minmax" else None
         layers.append((s, host, devt, y, y_host, q, ws))
@@ -461,6 +469,10 @@ def run_own(args):
             ops.fused_dw_bn_quant(t["x"], t["w"], t["b"], bn and bn["beta"], bn and bn["gamma"], bn and bn["mean"],
                                   bn and bn["var"], s.bn_eps, pad=(s.pad, s.pad), stride=(s.stride, s.stride),
                                   quant=qq, out=y)
+            return
+        if code8:
+            ops.fused_dw_bn_quant_code8(t["x"], in_delta, t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"],
+                                        s.bn_eps, pad=(s.pad, s.pad), stride=(s.stride, s.stride), quant=q, out=y)
             return
         ops.fused_dw_bn_quant(t["x"] if x is None else x, t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"],
                               s.bn_eps, pad=(s.pad, s.pad), stride=(s.stride, s.stride), quant=q,
@@ -683,6 +695,7 @@ def run_own(args):
             "ms_per_step_best": float(min(chunk_ms)) if chunk_ms else ms_per_step,
             "higher_is_better": True, "scaling": args.scaling,
             "vs_baseline": None, "dtype": "f16" if half else "f32", "data": "synthetic",
+            "storage": "uint8 codes" if code8 else ("f16" if half else "f32"),
             "config": {"workload": workload_name(args), "batch_per_gpu": batch, "global_batch": batch * world,
                        "layers": len(specs), "parallelism": "batch-sharded x%d" % world, "numa_node": numa, "launch": "cuda graph" if graph is not None else "stream",
                        "l2": "per-step working set %.1f GB >> 126 MB L2; every layer has its own buffers"
@@ -743,7 +756,7 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
-    ap.add_argument("--workload", default="cfg1", choices=["cfg0", "cfg1", "cfg2", "cfg3", "cfg4", "ops"])
+    ap.add_argument("--workload", default="cfg1", choices=["cfg0", "cfg1", "cfg2", "cfg3", "cfg4", "cfg1q8", "ops"])
     ap.add_argument("--batch", type=int, default=None, help="images per GPU (default: the workload's batch)")
     ap.add_argument("--dtype", default="f32", choices=["f32", "f16"])
     ap.add_argument("--cpu-sample", type=int, default=None, help="images per CPU-baseline pass")
@@ -763,13 +776,14 @@ def main():
     ap.add_argument("--force-path", type=int, default=None, help="profiling only: kernel family 0..4")
     ap.add_argument("--tune", default="", help="profiling only: planner override P,row_blocks,threads,rows_per_patch")
     args = ap.parse_args()
-    defaults = {"cfg0": 32, "cfg1": 256, "cfg2": 128, "cfg3": 512, "cfg4": 256, "ops": 256}
+    defaults = {"cfg0": 32, "cfg1": 256, "cfg2": 128, "cfg3": 512, "cfg4": 256, "cfg1q8": 256, "ops": 256}
     if args.batch is None:
         args.batch = defaults[args.workload]
     if args.warmup < 3:
         args.warmup = 3
     if args.cpu_sample is None:
-        args.cpu_sample = {"cfg0": 32, "cfg1": 64, "cfg2": 32, "cfg3": 128, "cfg4": 64, "ops": 0}[args.workload]
+        args.cpu_sample = {"cfg0": 32, "cfg1": 64, "cfg2": 32, "cfg3": 128, "cfg4": 64, "cfg1q8": 64,
+                           "ops": 0}[args.workload]
     if args.workload == "ops":
         run_standalone_ops(args)
     elif args.impl == "reference":

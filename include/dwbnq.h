@@ -211,6 +211,57 @@ int dwbnq_fused_fwd(const dwbnq_conv_desc *desc, float bn_eps, const dwbnq_quant
                     const dwbnq_minmax_ptrs *mm, void *y, void *workspace, void *comm,
                     int device, void *stream);
 
+/* ---- 8-bit storage of quantized activations -------------------------------------------- */
+
+/* The outputs of a FixedPointQuantize layer with n <= 8 take 2^n values k * delta: as T
+ * values they spend 4 (or 2) bytes on 8 bits of information, on HBM and on every bus the
+ * tensor crosses. These entry points keep the activation as its integer code k, one byte per
+ * element. The boundary is the reference's QuantizeLinear / DequantizeLinear pair
+ * (src/nbla/cuda/function/generic/quantize_linear.cu:22-74: saturate, round half away from
+ * zero or half to even; dequantize_linear.cu:22-27): a code tensor is what
+ * QuantizeLinear(x, scale = delta, zero_point = 0) yields, stored as int8 / uint8 instead of
+ * a float tensor of integers, and FixedPointQuantize(x) == DequantizeLinear(codes). */
+
+typedef enum dwbnq_round_mode {
+  DWBNQ_ROUND_HALF_AWAY_FROM_ZERO = 0, /* round(), quantize_linear.cu:33-35            */
+  DWBNQ_ROUND_HALF_TO_EVEN = 1         /* quantize_linear.cu:37-47                     */
+} dwbnq_round_mode;
+
+/* QuantizeLinear forward with scalar scale and zero point, result stored as 8-bit codes:
+ * code = saturate(round(x / scale + zero_point), min_range, max_range), the steps and their
+ * order being the reference composite's (division, addition, rounding, saturation). Codes
+ * are written as int8 when min_range < 0, else uint8; the range must fit that type.
+ * x: `size` elements of `dtype`. */
+int dwbnq_quantize_linear_code8_fwd(int dtype, int64_t size, float scale, int zero_point,
+                                    int round_mode, int min_range, int max_range, const void *x,
+                                    void *codes, int device, void *stream);
+/* DequantizeLinear forward from 8-bit codes: y = (code - zero_point) * scale, y of `dtype`. */
+int dwbnq_dequantize_linear_code8_fwd(int dtype, int64_t size, float scale, int zero_point,
+                                      int codes_signed, const void *codes, void *y, int device,
+                                      void *stream);
+
+/* How the fused layer's input codes are to be read: x = code * in_delta (the previous
+ * layer's FixedPointQuantize step), codes int8 when in_signed, else uint8. */
+typedef struct dwbnq_code8_desc {
+  int32_t in_signed;
+  float in_delta;
+} dwbnq_code8_desc;
+
+/* dwbnq_fused_fwd with x and y as 8-bit codes: y_code = FixedPointQuantize(BN(conv(x_code *
+ * in_delta))) / delta. The arithmetic is that of dwbnq_fused_fwd on the dequantized input -
+ * same operations, same order, same roundings - so y_code * delta equals its fp32 output
+ * value for value (a -0.0 of the signed quantizer is stored as code 0). `q` must be a
+ * FixedPointQuantize with n <= 8 and delta a power of two (the code is then exact); codes are
+ * int8 when q->sign, else uint8. desc->dtype names the type of w, b and the BN vectors
+ * (DWBNQ_F32). Every geometry is accepted; 3x3 convolutions on 7, 14, 28, 56 and 112 wide
+ * square planes run on the plane kernels with the code tiles expanded in shared memory, the
+ * rest on the generic kernel. A NaN activation has no code and is stored as 0. */
+int dwbnq_fused_fwd_code8(const dwbnq_conv_desc *desc, float bn_eps, const dwbnq_quant_desc *q,
+                          const dwbnq_code8_desc *io, const void *x_codes, const void *w,
+                          const void *b, const void *bn_beta, const void *bn_gamma,
+                          const void *bn_mean, const void *bn_var, void *y_codes, int device,
+                          void *stream);
+
 /* Which kernel family the fused / dw-conv entry points would use for `desc` given the
  * pointer alignment: 0 = generic direct kernel, 1 = zero-padded shared-memory tile filled
  * by cooperative loads, 2 = zero-padded tile filled by TMA tiled loads, 3 = whole planes

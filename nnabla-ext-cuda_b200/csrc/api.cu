@@ -316,6 +316,79 @@ int dwbnq_fused_fwd(const dwbnq_conv_desc *desc, float bn_eps, const dwbnq_quant
   return launch_fused(*desc, a, QM_MM_APPLY, dev, s);
 }
 
+int dwbnq_fused_fwd_code8(const dwbnq_conv_desc *desc, float bn_eps, const dwbnq_quant_desc *q,
+                          const dwbnq_code8_desc *io, const void *x_codes, const void *w, const void *b,
+                          const void *bn_beta, const void *bn_gamma, const void *bn_mean, const void *bn_var,
+                          void *y_codes, int device, void *stream) {
+  clear_error();
+  int ho, wo;
+  int st = validate_conv(desc, &ho, &wo);
+  if (st != DWBNQ_OK) return st;
+  if (desc->dtype != DWBNQ_F32)
+    return fail(DWBNQ_ERR_UNSUPPORTED, "8-bit storage: weights and BN vectors must be DWBNQ_F32");
+  if (!q || q->kind != DWBNQ_Q_FPQ)
+    return fail(DWBNQ_ERR_INVALID_ARG, "8-bit storage needs a FixedPointQuantize quantizer (its codes are what is stored)");
+  if (!io) return fail(DWBNQ_ERR_INVALID_ARG, "code8 desc is null");
+  if (!(io->in_delta > 0.0f) || io->in_delta > 3.0e38f)
+    return fail(DWBNQ_ERR_INVALID_ARG, "in_delta must be positive and finite");
+  if (desc->n == 0) return DWBNQ_OK;
+  if (!x_codes || !w || !y_codes) return fail(DWBNQ_ERR_INVALID_ARG, "x, w and y must not be null");
+  if ((bn_mean == nullptr) != (bn_var == nullptr))
+    return fail(DWBNQ_ERR_INVALID_ARG, "bn_mean and bn_var must be given together");
+  FusedArgs a;
+  fill_args(&a, *desc, ho, wo, bn_eps, x_codes, w, b, bn_beta, bn_gamma, bn_mean, bn_var, y_codes);
+  st = fill_fpq(&a.q, q->sign, q->n, q->delta);
+  if (st != DWBNQ_OK) return st;
+  if (q->n > 8) return fail(DWBNQ_ERR_UNSUPPORTED, "8-bit storage: FixedPointQuantize with n = %d does not fit a byte", q->n);
+  if (!a.q.fpq_fast)
+    return fail(DWBNQ_ERR_UNSUPPORTED, "8-bit storage needs delta to be a power of two (the code y / delta is then exact)");
+  a.code8 = 1;
+  a.code_in_signed = io->in_signed ? 1 : 0;
+  a.code_in_delta = io->in_delta;
+  int dev;
+  st = enter_device(device, &dev);
+  if (st != DWBNQ_OK) return st;
+  return launch_fused(*desc, a, QM_FPQ, dev, static_cast<cudaStream_t>(stream));
+}
+
+int dwbnq_quantize_linear_code8_fwd(int dtype, int64_t size, float scale, int zero_point, int round_mode,
+                                    int min_range, int max_range, const void *x, void *codes, int device,
+                                    void *stream) {
+  clear_error();
+  int st = check_dtype(dtype);
+  if (st != DWBNQ_OK) return st;
+  if (size < 0) return fail(DWBNQ_ERR_INVALID_ARG, "negative size");
+  if (!(scale > 0.0f) || scale > 3.0e38f) return fail(DWBNQ_ERR_INVALID_ARG, "scale must be positive and finite");
+  if (round_mode != DWBNQ_ROUND_HALF_AWAY_FROM_ZERO && round_mode != DWBNQ_ROUND_HALF_TO_EVEN)
+    return fail(DWBNQ_ERR_INVALID_ARG, "round mode %d unknown", round_mode);
+  if (min_range > max_range) return fail(DWBNQ_ERR_INVALID_ARG, "min_range %d > max_range %d", min_range, max_range);
+  if (min_range < 0 ? (min_range < -128 || max_range > 127) : max_range > 255)
+    return fail(DWBNQ_ERR_UNSUPPORTED, "range [%d, %d] does not fit %s", min_range, max_range,
+                min_range < 0 ? "int8" : "uint8");
+  if (size > 0 && (!x || !codes)) return fail(DWBNQ_ERR_INVALID_ARG, "x and codes must not be null");
+  int dev;
+  st = enter_device(device, &dev);
+  if (st != DWBNQ_OK) return st;
+  if (size == 0) return DWBNQ_OK;
+  return launch_quantize_linear_code8(dtype, size, scale, zero_point, round_mode, min_range, max_range, x, codes,
+                                      static_cast<cudaStream_t>(stream));
+}
+
+int dwbnq_dequantize_linear_code8_fwd(int dtype, int64_t size, float scale, int zero_point, int codes_signed,
+                                      const void *codes, void *y, int device, void *stream) {
+  clear_error();
+  int st = check_dtype(dtype);
+  if (st != DWBNQ_OK) return st;
+  if (size < 0) return fail(DWBNQ_ERR_INVALID_ARG, "negative size");
+  if (size > 0 && (!codes || !y)) return fail(DWBNQ_ERR_INVALID_ARG, "codes and y must not be null");
+  int dev;
+  st = enter_device(device, &dev);
+  if (st != DWBNQ_OK) return st;
+  if (size == 0) return DWBNQ_OK;
+  return launch_dequantize_linear_code8(dtype, size, scale, zero_point, codes_signed, codes, y,
+                                        static_cast<cudaStream_t>(stream));
+}
+
 int dwbnq_dwconv_fwd(const dwbnq_conv_desc *desc, const void *x, const void *w, const void *b,
                      void *y, int device, void *stream) {
   return dwbnq_fused_fwd(desc, 0.0f, nullptr, x, w, b, nullptr, nullptr, nullptr, nullptr, nullptr, y,

@@ -41,7 +41,29 @@ struct FusedArgs {
   int kh, kw, sh, sw, ph, pw, dh, dw, mult;
   QuantArgs q;
   int *flag;  // device word set when a bounded wait runs out
+  // 8-bit storage (dwbnq_fused_fwd_code8): x and y hold FixedPointQuantize codes, one byte
+  // per element, instead of T values. x = code * code_in_delta (int8 codes when
+  // code_in_signed); y's code is the quantized value / q.fpq_delta (int8 when q.fpq_min < 0).
+  // Weights, bias and the BN vectors stay T. 0 = off.
+  int code8;
+  int code_in_signed;
+  float code_in_delta;
 };
+
+// One input element as fp32: a T value, or (8-bit storage) a code times its step.
+template <typename T>
+__device__ __forceinline__ float load_x(const FusedArgs &a, const void *base, long long idx) {
+  if (a.code8) {
+    const int c = a.code_in_signed ? (int)static_cast<const signed char *>(base)[idx]
+                                   : (int)static_cast<const unsigned char *>(base)[idx];
+    return __fmul_rn((float)c, a.code_in_delta);  // exact: a code has 8 bits
+  }
+  return Elem<T>::to_f32(static_cast<const T *>(base)[idx]);
+}
+// The code of a FixedPointQuantize output v = k * delta (delta a power of two: exact).
+__device__ __forceinline__ int fpq_code(float v, const QuantArgs &q) {
+  return __float2int_rn(__fmul_rn(v, q.fpq_inv_delta));
+}
 
 // Where the input tile of the tiled family comes from and how it is laid out.
 enum TileMode : int {
@@ -75,11 +97,10 @@ struct TileCfg {
 template <typename T>
 __device__ __forceinline__ float conv_point(const FusedArgs &a, long long n, int oc, int oy,
                                             int ox) {
-  const T *x = static_cast<const T *>(a.x);
   const T *w = static_cast<const T *>(a.w);
   const T *b = static_cast<const T *>(a.b);
   const int ic = oc / a.mult;
-  const T *xp = x + (n * a.C + ic) * (long long)a.H * a.W;
+  const long long xbase = (n * a.C + ic) * (long long)a.H * a.W;
   const T *wp = w + (long long)oc * a.kh * a.kw;
   float acc = b ? Elem<T>::to_f32(b[oc]) : 0.0f;
   for (int ky = 0; ky < a.kh; ++ky) {
@@ -87,7 +108,7 @@ __device__ __forceinline__ float conv_point(const FusedArgs &a, long long n, int
     for (int kx = 0; kx < a.kw; ++kx) {
       const int ix = ox * a.sw + kx * a.dw - a.pw;
       if (iy >= 0 && iy < a.H && ix >= 0 && ix < a.W) {
-        const float xv = Elem<T>::to_f32(xp[(long long)iy * a.W + ix]);
+        const float xv = load_x<T>(a, a.x, xbase + (long long)iy * a.W + ix);
         const float wv = Elem<T>::to_f32(wp[ky * a.kw + kx]);
         acc = __fadd_rn(acc, __fmul_rn(wv, xv));
       }
@@ -172,7 +193,9 @@ __global__ void __launch_bounds__(256) fused_generic_kernel(const FusedArgs a,
     if (QM == QM_MM_REDUCE) {
       reduce_minmax_to_global(a.q, oc, v, valid);
     } else if (valid) {
-      y[o] = Elem<T>::from_f32(quant_apply<QM>(v, a.q, load_mm<QM>(a, oc)));
+      const float r = quant_apply<QM>(v, a.q, load_mm<QM>(a, oc));
+      if ((QM == QM_FPQ || QM == QM_FPQ_LEAN) && a.code8) static_cast<signed char *>(a.y)[o] = (signed char)fpq_code(r, a.q);
+      else y[o] = Elem<T>::from_f32(r);
     }
   }
 }

@@ -78,6 +78,12 @@ int launch_fpq(int dtype, long long size, const QuantArgs &q, const void *x, voi
 int launch_pow2q(int dtype, long long size, const QuantArgs &q, const void *x, void *y,
                  cudaStream_t stream);
 
+// QuantizeLinear / DequantizeLinear with 8-bit codes (scalar scale and zero point).
+int launch_quantize_linear_code8(int dtype, long long size, float scale, int zero_point, int round_mode,
+                                 int min_range, int max_range, const void *x, void *codes, cudaStream_t stream);
+int launch_dequantize_linear_code8(int dtype, long long size, float scale, int zero_point, int codes_signed,
+                                   const void *codes, void *y, cudaStream_t stream);
+
 // MinMaxQuantize pieces. Workspace layout (4-byte words, C = channels):
 //   [0,C) encoded min | [C,2C) encoded max | [2C,3C) scale | [3C,4C) m' | [4C,5C) M' |
 //   [5C,7C) packed [max..., -min...] for the all-reduce.

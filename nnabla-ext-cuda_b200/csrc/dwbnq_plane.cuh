@@ -43,24 +43,86 @@ constexpr int kPlaneRows = 7;  // rows per thread
 
 // Stash row of a thread: [2 unused | left halo | W elements | right halo | pad], even size.
 __host__ __device__ constexpr int plane_stash_elems(int W) { return (W + 4 + 1) / 2 * 2; }
-// stride 1: tile | stash (NRB > 1) | weight pairs, row of zeros (5x5) | mbarrier
-__host__ __device__ constexpr size_t plane_smem_bytes(int K, int W, int NRB, int NCB, int NBND, int elem_size) {
+// stride 1: tile | stash (NRB > 1) | weight pairs, row of zeros (5x5) | 8-bit codes of the
+// tile (8-bit storage) | mbarrier
+__host__ __device__ constexpr size_t plane_smem_bytes(int K, int W, int NRB, int NCB, int NBND, int elem_size,
+                                                      bool code8 = false) {
   const int P = 32 / (NRB * NCB);
-  size_t s = (size_t)P * (kPlaneRows * NRB + (NBND > 1 ? 2 * (K / 2) : 0)) * (W * NCB) * elem_size;
+  const size_t tile_elems = (size_t)P * (kPlaneRows * NRB + (NBND > 1 ? 2 * (K / 2) : 0)) * (W * NCB);
+  size_t s = tile_elems * elem_size;
   s = (s + 15) / 16 * 16;
   if (NRB > 1) s += (size_t)32 * (K / 2) * plane_stash_elems(W) * elem_size;
   s = (s + 15) / 16 * 16;
   if (K == 5) s += (size_t)P * 25 * 8 + 128;  // weight pairs, row of zeros
+  if (code8) s += (tile_elems + 15) / 16 * 16;
   return s + 16;
 }
-// stride 2: input tile (with the row above a band) | output tile | mbarrier
-__host__ __device__ constexpr size_t plane_s2_smem_bytes(int NRB, int NCB, int NBND, int elem_size) {
+// stride 2: input tile (with the row above a band) | output tile | codes (8-bit storage) | mbarrier
+__host__ __device__ constexpr size_t plane_s2_smem_bytes(int NRB, int NCB, int NBND, int elem_size,
+                                                         bool code8 = false) {
   const int P = 32 / (NRB * NCB);
-  size_t s = (size_t)P * (14 * NRB + (NBND > 1 ? 1 : 0)) * (14 * NCB) * elem_size;
+  const size_t tile_elems = (size_t)P * (14 * NRB + (NBND > 1 ? 1 : 0)) * (14 * NCB);
+  size_t s = tile_elems * elem_size;
   s = (s + 15) / 16 * 16;
   s += (size_t)P * (7 * NRB) * (7 * NCB) * elem_size;
   s = (s + 15) / 16 * 16;
+  if (code8) s += (tile_elems + 15) / 16 * 16;
   return s + 16;
+}
+
+// ---- 8-bit storage: the tile travels as one byte per element ------------------------------
+// The copy engine moves the codes; the warp expands them to fp32 in shared memory before the
+// (unchanged) computation and packs the quantized results back to codes after it.
+// n codes at src -> n floats at dst, value = code * delta. src 4-byte, dst 16-byte aligned.
+// A byte b placed in the low mantissa bits of 2^23 is the float 2^23 + b, so
+// fma(2^23 + b, delta, -2^23 * delta) = RN(b * delta): the conversion and the scaling are one
+// instruction, bit-identical to (float)b * delta. Signed codes enter as b ^ 0x80 = code + 128.
+__device__ __forceinline__ void plane_expand_codes(const unsigned char *src, float *dst, int n, float delta,
+                                                   bool is_signed, int lane) {
+  // (2^23 + 128) * delta is exact only for a power-of-two delta: other signed steps go one by one
+  if (is_signed && (__float_as_uint(delta) & 0x007fffffu) != 0u) {
+    for (int i = lane; i < n; i += 32) dst[i] = __fmul_rn((float)(signed char)src[i], delta);
+    return;
+  }
+  const int nv = n >> 2;
+  const unsigned int *s4 = reinterpret_cast<const unsigned int *>(src);
+  float4 *d4 = reinterpret_cast<float4 *>(dst);
+  const unsigned int flip = is_signed ? 0x80808080u : 0u;
+  const float off = __fmul_rn(is_signed ? -8388736.0f : -8388608.0f, delta);  // -(2^23 [+ 128]) * delta
+  for (int i = lane; i < nv; i += 32) {
+    const unsigned int u = s4[i] ^ flip;
+    float4 f;
+    f.x = __fmaf_rn(__uint_as_float(__byte_perm(u, 0x4b000000u, 0x7440)), delta, off);
+    f.y = __fmaf_rn(__uint_as_float(__byte_perm(u, 0x4b000000u, 0x7441)), delta, off);
+    f.z = __fmaf_rn(__uint_as_float(__byte_perm(u, 0x4b000000u, 0x7442)), delta, off);
+    f.w = __fmaf_rn(__uint_as_float(__byte_perm(u, 0x4b000000u, 0x7443)), delta, off);
+    d4[i] = f;
+  }
+  for (int i = (nv << 2) + lane; i < n; i += 32) {
+    const unsigned int b = (unsigned int)src[i] ^ (flip & 0xffu);
+    dst[i] = __fmaf_rn(__uint_as_float(0x4b000000u | b), delta, off);
+  }
+}
+// n quantized values k * delta at src -> their codes k (low 8 bits of the integer: int8 and
+// uint8 alike) at dst. src 16-byte, dst 4-byte aligned. k = v * inv_delta is exact and
+// |k| < 2^8, so fma(v, inv_delta, 1.5 * 2^23) holds k in its low mantissa byte (two's
+// complement); a NaN has no code and is stored as 0.
+__device__ __forceinline__ unsigned int plane_code_bits(float v, float inv_delta) {
+  const float t = __fmaf_rn(v, inv_delta, 12582912.0f);
+  return __float_as_uint(v == v ? t : 12582912.0f);
+}
+__device__ __forceinline__ void plane_pack_codes(const float *src, unsigned char *dst, int n, float inv_delta,
+                                                 int lane) {
+  const int nv = n >> 2;
+  const float4 *s4 = reinterpret_cast<const float4 *>(src);
+  unsigned int *d4 = reinterpret_cast<unsigned int *>(dst);
+  for (int i = lane; i < nv; i += 32) {
+    const float4 f = s4[i];
+    const unsigned int lo = __byte_perm(plane_code_bits(f.x, inv_delta), plane_code_bits(f.y, inv_delta), 0x0040);
+    const unsigned int hi = __byte_perm(plane_code_bits(f.z, inv_delta), plane_code_bits(f.w, inv_delta), 0x0040);
+    d4[i] = __byte_perm(lo, hi, 0x5410);
+  }
+  for (int i = (nv << 2) + lane; i < n; i += 32) dst[i] = (unsigned char)(plane_code_bits(src[i], inv_delta) & 0xffu);
 }
 
 // Bulk async store shared -> global of `bytes` (multiple of 16, both sides 16-byte
@@ -204,11 +266,13 @@ __device__ __forceinline__ f32x2 tap_add2(f32x2 acc, f32x2 w, f32x2 x, f32x2 nz)
 // NBND > 1 a plane is cut into NBND bands of full-width rows, one band per CTA, and the
 // copy brings the row above and the row below the band along (they are contiguous with it).
 // Compiled for 16 one-warp CTAs per SM (128 registers).
-template <typename T, int W, int NRB, int NCB, int NBND, int QM>
+template <typename T, int W, int NRB, int NCB, int NBND, int QM, bool IO8 = false>
 __global__ void __launch_bounds__(32, 16)
     fused_plane_kernel(const __grid_constant__ FusedArgs a, const PlaneCfg c) {
   static_assert(NCB == 1 || W % 2 == 0, "column blocks need an even block width");
   static_assert(NBND == 1 || NRB * NCB == 32, "a band is one warp's worth of blocks");
+  static_assert(!IO8 || (sizeof(T) == 4 && (QM == QM_FPQ || QM == QM_FPQ_LEAN)),
+                "8-bit storage: fp32 arithmetic, FixedPointQuantize codes");
   constexpr int R = kPlaneRows;
   constexpr int TB = R * NRB;        // rows per tile
   constexpr int H = TB * NBND;       // plane height
@@ -226,21 +290,28 @@ __global__ void __launch_bounds__(32, 16)
   constexpr size_t tile_bytes = ((size_t)P * TE * sizeof(T) + 15) / 16 * 16;
   T *stash = reinterpret_cast<T *>(smem_raw + tile_bytes);
   constexpr size_t stash_bytes = NRB > 1 ? ((size_t)32 * SW * sizeof(T) + 15) / 16 * 16 : 0;
-  unsigned long long *bar = reinterpret_cast<unsigned long long *>(smem_raw + tile_bytes + stash_bytes);
+  // 8-bit storage: the codes of the tile, same element layout as the tile, one byte each
+  unsigned char *codes = smem_raw + tile_bytes + stash_bytes;
+  constexpr size_t codes_bytes = IO8 ? ((size_t)P * TE + 15) / 16 * 16 : 0;
+  unsigned long long *bar =
+      reinterpret_cast<unsigned long long *>(smem_raw + tile_bytes + stash_bytes + codes_bytes);
+  constexpr int ESZ = IO8 ? 1 : (int)sizeof(T);  // bytes per element in global memory
 
   const int lane = threadIdx.x;
   const int n_planes = (int)(a.n * a.OC);
   const int plane0 = (NBND > 1 ? blockIdx.x / NBND : blockIdx.x) * P;
   const int r0 = NBND > 1 ? (blockIdx.x % NBND) * TB : 0;  // first plane row of the tile
   const int pv = min(P, n_planes - plane0);
-  T *y = static_cast<T *>(a.y);
   // what comes in (band: with the rows above / below it that exist) and what goes out
   const int in_first = NBND > 1 ? max(r0 - 1, 0) : 0;
   const int in_rows = NBND > 1 ? min(r0 + TB + 1, H) - in_first : pv * H;
-  const T *in_src = static_cast<const T *>(a.x) + (long long)plane0 * PE + (long long)in_first * PW;
-  T *in_dst = tile + (NBND > 1 ? (in_first - (r0 - 1)) * PW : 0);
-  const unsigned int bytes = (unsigned int)(in_rows * PW * sizeof(T));
-  const unsigned int obytes = (unsigned int)((NBND > 1 ? TB : pv * H) * PW * sizeof(T));
+  const unsigned char *in_src = static_cast<const unsigned char *>(a.x) +
+                                ((long long)plane0 * PE + (long long)in_first * PW) * ESZ;
+  const int in_off = NBND > 1 ? (in_first - (r0 - 1)) * PW : 0;  // tile element the copy starts at
+  T *in_dst = tile + in_off;
+  const int n_in = in_rows * PW, n_out = (NBND > 1 ? TB : pv * H) * PW;
+  const unsigned int bytes = (unsigned int)(n_in * ESZ);
+  const unsigned int obytes = (unsigned int)(n_out * ESZ);
   const bool async_tile = c.bulk != 0 && (bytes % 16) == 0 && (obytes % 16) == 0;
 
   pdl_launch_dependents();
@@ -252,7 +323,8 @@ __global__ void __launch_bounds__(32, 16)
   if (lane == 0) {
     if (async_tile) {
       mbar_expect_tx(bar, bytes);
-      bulk_load_1d(in_dst, in_src, bytes, bar);
+      if (IO8) bulk_load_1d(codes + in_off, in_src, bytes, bar);
+      else bulk_load_1d(in_dst, in_src, bytes, bar);
     }
   }
 
@@ -287,13 +359,22 @@ __global__ void __launch_bounds__(32, 16)
   const MmCoef mm = load_mm<QM>(a, ch);
 
   if (!async_tile) {
-    const int n = in_rows * PW;
-    for (int i = lane; i < n; i += 32) in_dst[i] = in_src[i];
+    if (IO8) {
+      for (int i = lane; i < n_in; i += 32) codes[in_off + i] = in_src[i];
+    } else {
+      const T *src_t = reinterpret_cast<const T *>(in_src);
+      for (int i = lane; i < n_in; i += 32) in_dst[i] = src_t[i];
+    }
   }
   __syncwarp();  // barrier initialisation and thread-copied data are visible
   if (async_tile && !mbar_wait_bounded(bar, 0)) {
     if (a.flag) atomicExch(a.flag, 1);
     return;
+  }
+  if (IO8) {  // codes -> fp32 values, in the tile's own layout
+    plane_expand_codes(codes + in_off, reinterpret_cast<float *>(in_dst), n_in, a.code_in_delta,
+                       a.code_in_signed != 0, lane);
+    __syncwarp();
   }
 
   // this thread's R x W block, overwritten in place (row pitch PW)
@@ -398,16 +479,25 @@ __global__ void __launch_bounds__(32, 16)
   if (!qm_stores(QM)) return;
 
   // ---- the finished tile leaves in one piece ------------------------------------------------
-  T *dst = y + (long long)plane0 * PE + (long long)r0 * PW;
+  unsigned char *dst = static_cast<unsigned char *>(a.y) + ((long long)plane0 * PE + (long long)r0 * PW) * ESZ;
   const T *out_src = tile + HALO * PW;
+  if (IO8) {  // quantized values -> codes (the input codes are spent: their buffer is reused)
+    __syncwarp();
+    plane_pack_codes(reinterpret_cast<const float *>(out_src), codes, n_out, a.q.fpq_inv_delta, lane);
+  }
+  const void *out_bytes = IO8 ? static_cast<const void *>(codes) : static_cast<const void *>(out_src);
   if (async_tile) {
     fence_proxy_async_smem();  // this thread's shared-memory writes, for the copy engine
     __syncwarp();
-    if (lane == 0) bulk_store_1d_and_wait(dst, out_src, obytes);
+    if (lane == 0) bulk_store_1d_and_wait(dst, out_bytes, obytes);
   } else {
     __syncwarp();
-    const int n = (NBND > 1 ? TB : pv * H) * PW;
-    for (int i = lane; i < n; i += 32) dst[i] = out_src[i];
+    if (IO8) {
+      for (int i = lane; i < n_out; i += 32) dst[i] = codes[i];
+    } else {
+      T *dst_t = reinterpret_cast<T *>(dst);
+      for (int i = lane; i < n_out; i += 32) dst_t[i] = out_src[i];
+    }
   }
 }
 
@@ -749,24 +839,28 @@ __global__ void __launch_bounds__(32, K == 5 ? 12 : 16)
 // compile time (columns) or by a uniform test (rows), which is the contract's own rule: no
 // zero padding enters, so there is no exact-evaluation fall-back, no stash and no barrier
 // inside the loop. Input rows stream through the thread as in fused_plane_kernel.
-template <typename T, int QM>
+template <typename T, int QM, bool IO8 = false>
 __global__ void __launch_bounds__(32, 16)
     fused_plane_pair7_kernel(const __grid_constant__ FusedArgs a, const PlaneCfg c) {
   constexpr int W = 7, H = 7, PE = 49, P = 64;
+  static_assert(!IO8 || (sizeof(T) == 4 && (QM == QM_FPQ || QM == QM_FPQ_LEAN)),
+                "8-bit storage: fp32 arithmetic, FixedPointQuantize codes");
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
   T *tile = reinterpret_cast<T *>(smem_raw);
   constexpr size_t tile_bytes = ((size_t)P * PE * sizeof(T) + 15) / 16 * 16;
-  unsigned long long *bar = reinterpret_cast<unsigned long long *>(smem_raw + tile_bytes);
+  unsigned char *codes = smem_raw + tile_bytes;  // 8-bit storage: the tile's codes
+  constexpr size_t codes_bytes = IO8 ? ((size_t)P * PE + 15) / 16 * 16 : 0;
+  unsigned long long *bar = reinterpret_cast<unsigned long long *>(smem_raw + tile_bytes + codes_bytes);
+  constexpr int ESZ = IO8 ? 1 : (int)sizeof(T);
 
   const int lane = threadIdx.x;
   const int n_planes = (int)(a.n * a.OC);
   const int plane0 = blockIdx.x * P;
   const int pv = min(P, n_planes - plane0);
-  T *y = static_cast<T *>(a.y);
-  const T *in_src = static_cast<const T *>(a.x) + (long long)plane0 * PE;
-  T *dst = y + (long long)plane0 * PE;
-  const unsigned int bytes = (unsigned int)(pv * PE * sizeof(T));
+  const unsigned char *in_src = static_cast<const unsigned char *>(a.x) + (long long)plane0 * PE * ESZ;
+  unsigned char *dst = static_cast<unsigned char *>(a.y) + (long long)plane0 * PE * ESZ;
+  const unsigned int bytes = (unsigned int)(pv * PE * ESZ);
   const bool async_tile = c.bulk != 0 && (bytes % 16) == 0;
 
   pdl_launch_dependents();
@@ -778,7 +872,7 @@ __global__ void __launch_bounds__(32, 16)
   if (lane == 0) {
     if (async_tile) {
       mbar_expect_tx(bar, bytes);
-      bulk_load_1d(tile, in_src, bytes, bar);
+      bulk_load_1d(IO8 ? static_cast<void *>(codes) : static_cast<void *>(tile), in_src, bytes, bar);
     }
   }
 
@@ -806,12 +900,21 @@ __global__ void __launch_bounds__(32, 16)
 
   if (!async_tile) {
     const int n = pv * PE;
-    for (int i = lane; i < n; i += 32) tile[i] = in_src[i];
+    if (IO8) {
+      for (int i = lane; i < n; i += 32) codes[i] = in_src[i];
+    } else {
+      const T *src_t = reinterpret_cast<const T *>(in_src);
+      for (int i = lane; i < n; i += 32) tile[i] = src_t[i];
+    }
   }
   __syncwarp();
   if (async_tile && !mbar_wait_bounded(bar, 0)) {
     if (a.flag) atomicExch(a.flag, 1);
     return;
+  }
+  if (IO8) {
+    plane_expand_codes(codes, reinterpret_cast<float *>(tile), pv * PE, a.code_in_delta, a.code_in_signed != 0, lane);
+    __syncwarp();
   }
 
   T *p0 = tile + lane * PE;         // lane stride 49 words: conflict-free
@@ -902,18 +1005,28 @@ __global__ void __launch_bounds__(32, 16)
   }
   if (!qm_stores(QM)) return;
 
+  if (IO8) {
+    __syncwarp();
+    plane_pack_codes(reinterpret_cast<const float *>(tile), codes, pv * PE, a.q.fpq_inv_delta, lane);
+  }
+  const void *out_bytes = IO8 ? static_cast<const void *>(codes) : static_cast<const void *>(tile);
   if (async_tile) {
     fence_proxy_async_smem();
     __syncwarp();
-    if (lane == 0) bulk_store_1d_and_wait(dst, tile, bytes);
+    if (lane == 0) bulk_store_1d_and_wait(dst, out_bytes, bytes);
   } else {
     __syncwarp();
     const int n = pv * PE;
-    for (int i = lane; i < n; i += 32) dst[i] = tile[i];
+    if (IO8) {
+      for (int i = lane; i < n; i += 32) dst[i] = codes[i];
+    } else {
+      T *dst_t = reinterpret_cast<T *>(dst);
+      for (int i = lane; i < n; i += 32) dst_t[i] = tile[i];
+    }
   }
 }
-__host__ __device__ constexpr size_t plane_pair7_smem_bytes(int elem_size) {
-  return ((size_t)64 * 49 * elem_size + 15) / 16 * 16 + 16;
+__host__ __device__ constexpr size_t plane_pair7_smem_bytes(int elem_size, bool code8 = false) {
+  return ((size_t)64 * 49 * elem_size + 15) / 16 * 16 + (code8 ? ((size_t)64 * 49 + 15) / 16 * 16 : 0) + 16;
 }
 
 // ---- stride 2 ---------------------------------------------------------------------------
@@ -922,10 +1035,12 @@ __host__ __device__ constexpr size_t plane_pair7_smem_bytes(int elem_size) {
 // (NBND > 1). Taps are scalar (the two outputs of a packed pair would need operands two
 // elements apart, which costs more moves than it saves), BN is packed. The traffic per
 // output is 2.5 times that of stride 1, so the arithmetic has issue slots to spare.
-template <typename T, int NRB, int NCB, int NBND, int QM>
+template <typename T, int NRB, int NCB, int NBND, int QM, bool IO8 = false>
 __global__ void __launch_bounds__(32, 7)
     fused_plane_s2_kernel(const __grid_constant__ FusedArgs a, const PlaneCfg c) {
   static_assert(NBND == 1 || NRB * NCB == 32, "a band is one warp's worth of blocks");
+  static_assert(!IO8 || (sizeof(T) == 4 && (QM == QM_FPQ || QM == QM_FPQ_LEAN)),
+                "8-bit storage: fp32 arithmetic, FixedPointQuantize codes");
   constexpr int BW = 14;             // input block edge
   constexpr int OB = 7;              // output block edge
   constexpr int PW = BW * NCB;       // input plane width
@@ -947,7 +1062,12 @@ __global__ void __launch_bounds__(32, 7)
   constexpr size_t tile_bytes = ((size_t)P * TE * sizeof(T) + 15) / 16 * 16;
   T *otile = reinterpret_cast<T *>(smem_raw + tile_bytes);
   constexpr size_t otile_bytes = ((size_t)P * OTE * sizeof(T) + 15) / 16 * 16;
-  unsigned long long *bar = reinterpret_cast<unsigned long long *>(smem_raw + tile_bytes + otile_bytes);
+  // 8-bit storage: the input tile's codes; the (smaller) output tile's codes reuse the buffer
+  unsigned char *codes = smem_raw + tile_bytes + otile_bytes;
+  constexpr size_t codes_bytes = IO8 ? ((size_t)P * TE + 15) / 16 * 16 : 0;
+  unsigned long long *bar =
+      reinterpret_cast<unsigned long long *>(smem_raw + tile_bytes + otile_bytes + codes_bytes);
+  constexpr int ESZ = IO8 ? 1 : (int)sizeof(T);
 
   const int lane = threadIdx.x;
   const int n_planes = (int)(a.n * a.OC);
@@ -955,14 +1075,16 @@ __global__ void __launch_bounds__(32, 7)
   const int band = NBND > 1 ? blockIdx.x % NBND : 0;
   const int r0 = band * TBI;  // first input row of the tile
   const int pv = min(P, n_planes - plane0);
-  T *y = static_cast<T *>(a.y);
   const int in_first = NBND > 1 ? max(r0 - 1, 0) : 0;
   const int in_rows = NBND > 1 ? r0 + TBI - in_first : pv * H;
-  const T *in_src = static_cast<const T *>(a.x) + (long long)plane0 * PE + (long long)in_first * PW;
-  T *in_dst = tile + (NBND > 1 ? (in_first - (r0 - 1)) * PW : 0);
-  const unsigned int bytes = (unsigned int)(in_rows * PW * sizeof(T));
+  const unsigned char *in_src = static_cast<const unsigned char *>(a.x) +
+                                ((long long)plane0 * PE + (long long)in_first * PW) * ESZ;
+  const int in_off = NBND > 1 ? (in_first - (r0 - 1)) * PW : 0;
+  T *in_dst = tile + in_off;
+  const int n_in = in_rows * PW;
+  const unsigned int bytes = (unsigned int)(n_in * ESZ);
   const int out_elems = (NBND > 1 ? 1 : pv) * OTE;
-  const unsigned int obytes = (unsigned int)(out_elems * sizeof(T));
+  const unsigned int obytes = (unsigned int)(out_elems * ESZ);
   const bool async_tile = c.bulk != 0 && (bytes % 16) == 0 && (obytes % 16) == 0;
 
   pdl_launch_dependents();
@@ -974,7 +1096,8 @@ __global__ void __launch_bounds__(32, 7)
   if (lane == 0) {
     if (async_tile) {
       mbar_expect_tx(bar, bytes);
-      bulk_load_1d(in_dst, in_src, bytes, bar);
+      if (IO8) bulk_load_1d(codes + in_off, in_src, bytes, bar);
+      else bulk_load_1d(in_dst, in_src, bytes, bar);
     }
   }
 
@@ -1005,13 +1128,22 @@ __global__ void __launch_bounds__(32, 7)
   const MmCoef mm = load_mm<QM>(a, ch);
 
   if (!async_tile) {
-    const int n = in_rows * PW;
-    for (int i = lane; i < n; i += 32) in_dst[i] = in_src[i];
+    if (IO8) {
+      for (int i = lane; i < n_in; i += 32) codes[in_off + i] = in_src[i];
+    } else {
+      const T *src_t = reinterpret_cast<const T *>(in_src);
+      for (int i = lane; i < n_in; i += 32) in_dst[i] = src_t[i];
+    }
   }
   __syncwarp();
   if (async_tile && !mbar_wait_bounded(bar, 0)) {
     if (a.flag) atomicExch(a.flag, 1);
     return;
+  }
+  if (IO8) {
+    plane_expand_codes(codes + in_off, reinterpret_cast<float *>(in_dst), n_in, a.code_in_delta,
+                       a.code_in_signed != 0, lane);
+    __syncwarp();
   }
 
   const T *rows = tile + pl * TE + (HALO + rb * BW) * PW + cb * BW;  // this thread's 14 x 14 inputs
@@ -1084,20 +1216,32 @@ __global__ void __launch_bounds__(32, 7)
   if (qm_reduces(QM)) plane_reduce_minmax<TPP>(a.q, ch, lo, hi, active, lane);
   if (!qm_stores(QM)) return;
 
-  T *dst = y + (long long)plane0 * OE + (long long)band * OTE;
+  unsigned char *dst = static_cast<unsigned char *>(a.y) + ((long long)plane0 * OE + (long long)band * OTE) * ESZ;
+  if (IO8) {
+    __syncwarp();
+    plane_pack_codes(reinterpret_cast<const float *>(otile), codes, out_elems, a.q.fpq_inv_delta, lane);
+  }
+  const void *out_bytes = IO8 ? static_cast<const void *>(codes) : static_cast<const void *>(otile);
   if (async_tile) {
     fence_proxy_async_smem();
     __syncwarp();
-    if (lane == 0) bulk_store_1d_and_wait(dst, otile, obytes);
+    if (lane == 0) bulk_store_1d_and_wait(dst, out_bytes, obytes);
   } else {
     __syncwarp();
-    for (int i = lane; i < out_elems; i += 32) dst[i] = otile[i];
+    if (IO8) {
+      for (int i = lane; i < out_elems; i += 32) dst[i] = codes[i];
+    } else {
+      T *dst_t = reinterpret_cast<T *>(dst);
+      for (int i = lane; i < out_elems; i += 32) dst_t[i] = otile[i];
+    }
   }
 }
 
 // Host-side entry (fused_plane.cu).
 cudaError_t launch_plane(int dtype, int k, int hw, int stride, int qm, const FusedArgs &a,
                          const PlaneCfg &c, cudaStream_t stream);
+// Whether 8-bit storage has a plane-kernel instantiation for this shape and mode.
+bool plane_has_code8(int dtype, int k, int hw, int stride, int qm);
 // Geometry of the instantiation for a square hw x hw plane, kernel size and stride; tpp == 0
 // if there is none.
 struct PlaneGeom {
@@ -1122,11 +1266,11 @@ __host__ inline PlaneGeom plane_geom(int k, int h, int w, int stride) {
   }
   return g;
 }
-__host__ inline size_t plane_launch_smem(int k, int hw, int stride, int elem_size) {
+__host__ inline size_t plane_launch_smem(int k, int hw, int stride, int elem_size, bool code8 = false) {
   const PlaneGeom g = plane_geom(k, hw, hw, stride);
-  if (stride == 1 && k == 3 && hw == 7) return plane_pair7_smem_bytes(elem_size);
-  if (stride == 1) return plane_smem_bytes(k, g.w, g.nrb, g.ncb, g.bands, elem_size);
-  return plane_s2_smem_bytes(g.nrb, g.ncb, g.bands, elem_size);
+  if (stride == 1 && k == 3 && hw == 7) return plane_pair7_smem_bytes(elem_size, code8);
+  if (stride == 1) return plane_smem_bytes(k, g.w, g.nrb, g.ncb, g.bands, elem_size, code8);
+  return plane_s2_smem_bytes(g.nrb, g.ncb, g.bands, elem_size, code8);
 }
 
 }  // namespace dwbnq

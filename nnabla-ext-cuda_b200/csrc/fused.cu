@@ -358,6 +358,12 @@ int launch_fused(const dwbnq_conv_desc &d, FusedArgs &a, int qm, int device, cud
   if (st != DWBNQ_OK) return st;
   const long long total = d.n * (long long)a.OC * a.Ho * a.Wo;
   cudaError_t e;
+  if (a.code8) {
+    // 8-bit storage: the plane kernels that carry a code path, else the generic kernel
+    int pq = qm;
+    if (pq == QM_FPQ && a.has_bn && a.q.fpq_fast && !(a.q.fpq_min < 0.0f)) pq = QM_FPQ_LEAN;
+    if (!(plan.path == PATH_PLANE && plane_has_code8(d.dtype, d.kh, d.w, d.stride_h, pq))) plan.path = PATH_GENERIC;
+  }
   if (plan.path == PATH_GENERIC) {
     const int sms = sm_count(device);
     e = d.dtype == DWBNQ_F32 ? launch_generic_t<float>(qm, a, total, sms, stream)

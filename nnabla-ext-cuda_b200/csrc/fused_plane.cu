@@ -23,6 +23,40 @@ PlaneKernel pick_s1(int qm) {
   return nullptr;
 }
 
+// 8-bit storage: FixedPointQuantize modes, fp32 arithmetic
+template <int W, int NRB, int NCB, int NBND>
+PlaneKernel pick_s1_code8(int qm) {
+  if (qm == QM_FPQ) return fused_plane_kernel<float, W, NRB, NCB, NBND, QM_FPQ, true>;
+  if (qm == QM_FPQ_LEAN) return fused_plane_kernel<float, W, NRB, NCB, NBND, QM_FPQ_LEAN, true>;
+  return nullptr;
+}
+template <int NRB, int NCB, int NBND>
+PlaneKernel pick_s2_code8(int qm) {
+  if (qm == QM_FPQ) return fused_plane_s2_kernel<float, NRB, NCB, NBND, QM_FPQ, true>;
+  if (qm == QM_FPQ_LEAN) return fused_plane_s2_kernel<float, NRB, NCB, NBND, QM_FPQ_LEAN, true>;
+  return nullptr;
+}
+PlaneKernel pick_pair7_code8(int qm) {
+  if (qm == QM_FPQ) return fused_plane_pair7_kernel<float, QM_FPQ, true>;
+  if (qm == QM_FPQ_LEAN) return fused_plane_pair7_kernel<float, QM_FPQ_LEAN, true>;
+  return nullptr;
+}
+PlaneKernel pick_code8(int k, int hw, int stride, int qm) {
+  if (stride == 1 && k == 3) {
+    if (hw == 7) return pick_pair7_code8(qm);
+    if (hw == 14) return pick_s1_code8<14, 2, 1, 1>(qm);
+    if (hw == 28) return pick_s1_code8<14, 4, 2, 1>(qm);
+    if (hw == 56) return pick_s1_code8<14, 8, 4, 1>(qm);
+    if (hw == 112) return pick_s1_code8<14, 4, 8, 4>(qm);
+  } else if (stride == 2 && k == 3) {
+    if (hw == 14) return pick_s2_code8<1, 1, 1>(qm);
+    if (hw == 28) return pick_s2_code8<2, 2, 1>(qm);
+    if (hw == 56) return pick_s2_code8<4, 4, 1>(qm);
+    if (hw == 112) return pick_s2_code8<4, 8, 2>(qm);
+  }
+  return nullptr;
+}
+
 template <typename T, int K, int W, int NRB, int NCB, int NBND>
 PlaneKernel pick_kxk(int qm) {
   switch (qm) {
@@ -69,7 +103,9 @@ template <typename T>
 cudaError_t launch_t(int k, int hw, int stride, int qm, const FusedArgs &a, const PlaneCfg &c,
                      cudaStream_t stream) {
   PlaneKernel kern = nullptr;
-  if (stride == 1 && k == 3) {
+  if (a.code8) {
+    kern = sizeof(T) == 4 ? pick_code8(k, hw, stride, qm) : nullptr;
+  } else if (stride == 1 && k == 3) {
     if (hw == 7) kern = pick_pair7<T>(qm);
     else if (hw == 14) kern = pick_s1<T, 14, 2, 1, 1>(qm);
     else if (hw == 28) kern = pick_s1<T, 14, 4, 2, 1>(qm);
@@ -87,7 +123,7 @@ cudaError_t launch_t(int k, int hw, int stride, int qm, const FusedArgs &a, cons
     else if (hw == 112) kern = pick_s2<T, 4, 8, 2>(qm);
   }
   if (!kern) return cudaErrorInvalidValue;
-  const size_t smem = plane_launch_smem(k, hw, stride, sizeof(T));
+  const size_t smem = plane_launch_smem(k, hw, stride, sizeof(T), a.code8 != 0);
   // all of the unified L1 / shared memory as shared memory: the tiles are the working set
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
                                        cudaSharedmemCarveoutMaxShared);
@@ -96,6 +132,10 @@ cudaError_t launch_t(int k, int hw, int stride, int qm, const FusedArgs &a, cons
 }
 
 }  // namespace
+
+bool plane_has_code8(int dtype, int k, int hw, int stride, int qm) {
+  return dtype == DWBNQ_F32 && pick_code8(k, hw, stride, qm) != nullptr;
+}
 
 cudaError_t launch_plane(int dtype, int k, int hw, int stride, int qm, const FusedArgs &a,
                          const PlaneCfg &c, cudaStream_t stream) {

@@ -37,6 +37,13 @@ class MinMaxPtrs(ctypes.Structure):
                 ("ql_min", ctypes.c_void_p), ("ql_max", ctypes.c_void_p)]
 
 
+class Code8Desc(ctypes.Structure):
+    _fields_ = [("in_signed", ctypes.c_int32), ("in_delta", ctypes.c_float)]
+
+
+ROUND_HALF_AWAY_FROM_ZERO, ROUND_HALF_TO_EVEN = 0, 1
+
+
 class DwbnqError(RuntimeError):
     def __init__(self, status, message):
         super().__init__("dwbnq status %d: %s" % (status, message))
@@ -67,6 +74,10 @@ SIGNATURES = {
                                         _vp, _int, _vp]),
     "dwbnq_fused_fwd": (_int, [_P(ConvDesc), _flt, _P(QuantDesc), _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                _P(MinMaxPtrs), _vp, _vp, _vp, _int, _vp]),
+    "dwbnq_quantize_linear_code8_fwd": (_int, [_int, _i64, _flt, _int, _int, _int, _int, _vp, _vp, _int, _vp]),
+    "dwbnq_dequantize_linear_code8_fwd": (_int, [_int, _i64, _flt, _int, _int, _vp, _vp, _int, _vp]),
+    "dwbnq_fused_fwd_code8": (_int, [_P(ConvDesc), _flt, _P(QuantDesc), _P(Code8Desc), _vp, _vp, _vp, _vp, _vp,
+                                     _vp, _vp, _vp, _int, _vp]),
     "dwbnq_fused_plan": (_int, [_P(ConvDesc), _vp, _vp, _P(_int), _P(_int), _P(_int), _P(_int),
                                 _P(_i64), _P(_int)]),
     "dwbnq_set_forced_path": (_int, [_int]),

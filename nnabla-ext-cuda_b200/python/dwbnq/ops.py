@@ -53,6 +53,16 @@ def _pair(v, ndim=2):
     return v
 
 
+class _ShapeOf:
+    """What conv_desc reads of a tensor: its shape and element type."""
+
+    def __init__(self, shape, dtype):
+        self.shape, self.dtype = tuple(shape), dtype
+
+    def dim(self):
+        return len(self.shape)
+
+
 def conv_desc(x, w, base_axis=1, pad=None, stride=None, dilation=None, multiplier=1):
     """dwbnq_conv_desc for x [..., C, (H,) W] and w [C*mult, (kh,) kw]."""
     sdims = x.dim() - base_axis - 1
@@ -206,6 +216,60 @@ def fused_dw_bn_quant(x, w, b, beta, gamma, mean, variance, eps=1e-5, pad=None, 
                                     _ptr(beta), _ptr(gamma), _ptr(mean), _ptr(variance), mm, _ptr(y),
                                     _ptr(ws) if mmt else None, None if comm is None else comm.handle,
                                     dev.index, _stream(dev)))
+    return y
+
+
+# ---- 8-bit storage of quantized activations -------------------------------------------------
+
+def quantize_linear_code8(x, scale, zero_point=0, round_mode="HALF_AWAY_FROM_ZERO", signed=False,
+                          min_range=None, max_range=None, out=None):
+    """QuantizeLinear (scalar scale / zero point) with the result stored as int8 / uint8 codes:
+    saturate(round(x / scale + zero_point)). The argument names are nnabla's
+    ``F.quantize_linear``; ``signed`` picks the narrow type, the range defaults to all of it."""
+    dev = _chk_cuda(x, out)
+    lo = (-128 if signed else 0) if min_range is None else int(min_range)
+    hi = (127 if signed else 255) if max_range is None else int(max_range)
+    mode = {"HALF_AWAY_FROM_ZERO": L.ROUND_HALF_AWAY_FROM_ZERO, "HALF_TO_EVEN": L.ROUND_HALF_TO_EVEN}[round_mode]
+    y = out if out is not None else torch.empty(x.shape, dtype=torch.int8 if lo < 0 else torch.uint8, device=dev)
+    L.check(L.lib().dwbnq_quantize_linear_code8_fwd(_dtype_code(x), x.numel(), float(scale), int(zero_point), mode,
+                                                    lo, hi, _ptr(x), _ptr(y), dev.index, _stream(dev)))
+    return y
+
+
+def dequantize_linear_code8(codes, scale, zero_point=0, dtype=torch.float32, out=None):
+    """DequantizeLinear from int8 / uint8 codes: (code - zero_point) * scale."""
+    dev = _chk_cuda(codes, out)
+    if codes.dtype not in (torch.int8, torch.uint8):
+        raise TypeError("codes must be int8 or uint8")
+    y = out if out is not None else torch.empty(codes.shape, dtype=dtype, device=dev)
+    L.check(L.lib().dwbnq_dequantize_linear_code8_fwd(_dtype_code(y), codes.numel(), float(scale), int(zero_point),
+                                                      int(codes.dtype == torch.int8), _ptr(codes), _ptr(y), dev.index,
+                                                      _stream(dev)))
+    return y
+
+
+def fused_dw_bn_quant_code8(x_codes, in_delta, w, b, beta, gamma, mean, variance, eps=1e-5, pad=None, stride=None,
+                            dilation=None, multiplier=1, quant=None, base_axis=1, out=None):
+    """The fused layer on 8-bit codes: x_codes (int8 / uint8) stands for x = code * in_delta,
+    the result is the code of FixedPointQuantize(BN(conv(x))), int8 when the quantizer is
+    signed, else uint8. ``quant`` is a FixedPointQuantize dict with n <= 8 and a power-of-two
+    delta; w, b and the BN vectors are float32."""
+    if x_codes.dtype not in (torch.int8, torch.uint8):
+        raise TypeError("x_codes must be int8 or uint8")
+    if not quant or quant["kind"] != "fpq":
+        raise ValueError("8-bit storage needs a FixedPointQuantize quantizer")
+    dev = _chk_cuda(x_codes, w, b, beta, gamma, mean, variance, out)
+    # geometry from the code tensor's shape, parameter dtype from w
+    d, oshape = conv_desc(_ShapeOf(x_codes.shape, w.dtype), w, base_axis, pad, stride, dilation, multiplier)
+    q = quant_desc(quant)
+    io = L.Code8Desc(in_signed=int(x_codes.dtype == torch.int8), in_delta=float(in_delta))
+    ydt = torch.int8 if quant["sign"] else torch.uint8
+    y = out if out is not None else torch.empty(oshape, dtype=ydt, device=dev)
+    if y.dtype != ydt:
+        raise TypeError("out must be %s for this quantizer" % ydt)
+    L.check(L.lib().dwbnq_fused_fwd_code8(ctypes.byref(d), float(eps), ctypes.byref(q), ctypes.byref(io), _ptr(x_codes),
+                                          _ptr(w), _ptr(b), _ptr(beta), _ptr(gamma), _ptr(mean), _ptr(variance),
+                                          _ptr(y), dev.index, _stream(dev)))
     return y
 
 

@@ -88,7 +88,7 @@ def cfg3(n=512):
 
 
 def workload(name, n=None):
-    table = {"cfg0": cfg0, "cfg1": cfg1, "cfg2": cfg2, "cfg3": cfg3, "cfg4": cfg1}
+    table = {"cfg0": cfg0, "cfg1": cfg1, "cfg2": cfg2, "cfg3": cfg3, "cfg4": cfg1, "cfg1q8": cfg1}
     return table[name]() if n is None else table[name](n)
 
 

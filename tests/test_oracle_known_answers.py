@@ -187,3 +187,23 @@ def test_threads_do_not_change_results(oracle):
     b = oracle.dwconv(x, w, None, (1, 1), (1, 1), nthreads=4)
     np.testing.assert_array_equal(a, b)
     np.testing.assert_array_equal(oracle.fpq(x, nthreads=1), oracle.fpq(x, nthreads=4))
+
+
+def test_quantize_linear_known_answers(oracle):
+    """Worked from src/nbla/cuda/function/generic/quantize_linear.cu: round() is half away from
+    zero (:33-35); half to even replaces exact .5 cases by round(x * 0.5) * 2 (:37-47); saturate
+    clamps to [min_range, max_range] (:22-31); the composite is x / scale + zero_point first."""
+    x = np.array([0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 0.49, 300.0, -300.0, 1.0], np.float32)
+    away = oracle.quantize_linear(x, 1.0, 0, "HALF_AWAY_FROM_ZERO", -128, 127)
+    np.testing.assert_array_equal(away, [1, 2, 3, -1, -2, -3, 0, 127, -128, 1])
+    even = oracle.quantize_linear(x, 1.0, 0, "HALF_TO_EVEN", -128, 127)
+    np.testing.assert_array_equal(even, [0, 2, 2, 0, -2, -2, 0, 127, -128, 1])
+    # scale and zero point: 0.3 / 0.125 + 3 = 5.4 -> 5; unsigned range clamps negatives to 0
+    np.testing.assert_array_equal(oracle.quantize_linear(np.array([0.3, -1.0], np.float32), 0.125, 3,
+                                                         "HALF_AWAY_FROM_ZERO", 0, 255), [5, 0])
+    np.testing.assert_array_equal(oracle.dequantize_linear(np.array([5, 0, 255]), 0.125, 3),
+                                  np.array([0.25, -0.375, 31.5], np.float32))
+    # FixedPointQuantize(unsigned, n = 8, delta) is the dequantized code
+    v = np.array([0.03, 0.0625, 0.19, 40.0, -1.0], np.float32)
+    codes = oracle.quantize_linear(v, 0.125, 0, "HALF_AWAY_FROM_ZERO", 0, 255)
+    np.testing.assert_array_equal(oracle.dequantize_linear(codes, 0.125, 0), oracle.fpq(v, False, 8, 0.125))
