@@ -448,14 +448,17 @@ def run_own(args):
     layers = []
     for s in specs:
         d = workloads.make_layer_data(s, n=batch, first_image=rank * batch)
-        host = {k: torch.from_numpy(v).to(tdtype).pin_memory() for k, v in d.items()}
+        pin = (lambda t: t) if args.no_e2e else (lambda t: t.pin_memory())  # pinned only when it is copied from
+        host = {k: pin(torch.from_numpy(v).to(tdtype)) for k, v in d.items()}
         if code8:  # the layer input as the previous layer would have left it: FixedPointQuantize codes
             xq = np.clip(np.floor(d["x"] / np.float32(in_delta) + np.float32(0.5)), 0, 255).astype(np.uint8)
-            host["x"] = torch.from_numpy(xq).pin_memory()
+            host["x"] = pin(torch.from_numpy(xq))
         devt = {k: v.to(device, non_blocking=True) for k, v in host.items()}
         ydt = torch.uint8 if code8 else tdtype
         y = torch.empty((batch, s.c, s.ho, s.wo), dtype=ydt, device=device)
-        y_host = torch.empty(y.shape, dtype=ydt).pin_memory()
+        y_host = None if args.no_e2e else torch.empty(y.shape, dtype=ydt).pin_memory()
+        if args.no_e2e:
+            host = {"x": host["x"][:0]}  # the device copies are all that is needed
         q = workloads.quant_for_ops(s, devt)
         ws = ops.workspace(s.c, device) if s.quant["kind"] == "minmax" else None
         layers.append((s, host, devt, y, y_host, q, ws))
