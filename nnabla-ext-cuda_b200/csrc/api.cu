@@ -6,9 +6,22 @@
 
 #include <cstdlib>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "dwbnq_internal.h"
 
 namespace dwbnq {
+
+// A named NVTX range around each operator call, so that a timeline shows which library call
+// a kernel belongs to (the reference wraps its own regions the same way,
+// src/nbla/cuda/nvtx.cpp:35-59). Header-only NVTX: without a profiler attached the push and
+// the pop are a pointer test each.
+struct NvtxRange {
+  explicit NvtxRange(const char *name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+  NvtxRange(const NvtxRange &) = delete;
+  NvtxRange &operator=(const NvtxRange &) = delete;
+};
 
 bool pdl_enabled() {
   static const bool enabled = [] {
@@ -237,6 +250,7 @@ int dwbnq_fused_fwd(const dwbnq_conv_desc *desc, float bn_eps, const dwbnq_quant
                     const dwbnq_minmax_ptrs *mm, void *y, void *workspace, void *comm, int device,
                     void *stream) {
   clear_error();
+  NvtxRange nvtx_range("dwbnq_fused_fwd");
   int ho, wo;
   int st = validate_conv(desc, &ho, &wo);
   if (st != DWBNQ_OK) return st;
@@ -321,6 +335,7 @@ int dwbnq_fused_fwd_code8(const dwbnq_conv_desc *desc, float bn_eps, const dwbnq
                           const void *bn_beta, const void *bn_gamma, const void *bn_mean, const void *bn_var,
                           void *y_codes, int device, void *stream) {
   clear_error();
+  NvtxRange nvtx_range("dwbnq_fused_fwd_code8");
   int ho, wo;
   int st = validate_conv(desc, &ho, &wo);
   if (st != DWBNQ_OK) return st;
@@ -355,6 +370,7 @@ int dwbnq_quantize_linear_code8_fwd(int dtype, int64_t size, float scale, int ze
                                     int min_range, int max_range, const void *x, void *codes, int device,
                                     void *stream) {
   clear_error();
+  NvtxRange nvtx_range("dwbnq_quantize_linear_code8_fwd");
   int st = check_dtype(dtype);
   if (st != DWBNQ_OK) return st;
   if (size < 0) return fail(DWBNQ_ERR_INVALID_ARG, "negative size");
@@ -377,6 +393,7 @@ int dwbnq_quantize_linear_code8_fwd(int dtype, int64_t size, float scale, int ze
 int dwbnq_dequantize_linear_code8_fwd(int dtype, int64_t size, float scale, int zero_point, int codes_signed,
                                       const void *codes, void *y, int device, void *stream) {
   clear_error();
+  NvtxRange nvtx_range("dwbnq_dequantize_linear_code8_fwd");
   int st = check_dtype(dtype);
   if (st != DWBNQ_OK) return st;
   if (size < 0) return fail(DWBNQ_ERR_INVALID_ARG, "negative size");
@@ -399,6 +416,7 @@ int dwbnq_bn_infer_fwd(int dtype, int64_t size0, int64_t size1, int64_t size2, f
                        const void *x, const void *beta, const void *gamma, const void *mean,
                        const void *var, void *y, int device, void *stream) {
   clear_error();
+  NvtxRange nvtx_range("dwbnq_bn_infer_fwd");
   int st = check_dtype(dtype);
   if (st != DWBNQ_OK) return st;
   if (size0 < 0 || size1 <= 0 || size2 < 0)
@@ -415,6 +433,7 @@ int dwbnq_bn_infer_fwd(int dtype, int64_t size0, int64_t size1, int64_t size2, f
 int dwbnq_fpq_fwd(int dtype, int64_t size, int sign, int n, float delta, const void *x, void *y,
                   int device, void *stream) {
   clear_error();
+  NvtxRange nvtx_range("dwbnq_fpq_fwd");
   int st = check_dtype(dtype);
   if (st != DWBNQ_OK) return st;
   if (size < 0) return fail(DWBNQ_ERR_INVALID_ARG, "negative size");
@@ -433,6 +452,7 @@ int dwbnq_fpq_fwd(int dtype, int64_t size, int sign, int n, float delta, const v
 int dwbnq_pow2q_fwd(int dtype, int64_t size, int sign, int with_zero, int n, int m, const void *x,
                     void *y, int device, void *stream) {
   clear_error();
+  NvtxRange nvtx_range("dwbnq_pow2q_fwd");
   int st = check_dtype(dtype);
   if (st != DWBNQ_OK) return st;
   if (size < 0) return fail(DWBNQ_ERR_INVALID_ARG, "negative size");
@@ -453,6 +473,7 @@ int dwbnq_minmaxq_fwd(int dtype, int64_t size0, int32_t channels, int64_t size2,
                       const dwbnq_quant_desc *q, const void *x, const dwbnq_minmax_ptrs *mm, void *y,
                       void *workspace, void *comm, int device, void *stream) {
   clear_error();
+  NvtxRange nvtx_range("dwbnq_minmaxq_fwd");
   int st = check_dtype(dtype);
   if (st != DWBNQ_OK) return st;
   if (size0 < 0 || channels <= 0 || size2 < 0)

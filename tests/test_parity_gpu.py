@@ -733,6 +733,34 @@ def test_standalone_chain_equals_fused(cuda_device):
     assert torch.equal(y.view(torch.int32), f.view(torch.int32))
 
 
+# ---- many tiles, every quantizer, planes that need the tap-by-tap path ------------------------
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16], ids=["f32", "f16"])
+@pytest.mark.parametrize("hw,n,c", [(14, 128, 320), (28, 32, 320), (56, 8, 400)])
+def test_plane_kernels_more_tiles_than_resident_ctas(oracle, cuda_device, dtype, hw, n, c):
+    """3x3 stride 1 on 14 / 28 / 56 wide planes with more tiles than the device holds CTAs
+    (several waves, the last one partial): every quantizer, one plane with a -0.0 bias and one
+    with an infinite weight (tap-by-tap re-evaluation)."""
+    for kind in ("fpq", "pow2", "minmax", None):
+        quant = {"fpq": dict(workloads.FPQ_CFG1), "pow2": dict(workloads.POW2_CFG2),
+                 "minmax": dict(workloads.MINMAX_CFG3), None: None}[kind]
+        spec = workloads.LayerSpec("waves", n, c, hw, hw, 3, 1, 1, quant or dict(workloads.FPQ_CFG1), seed=hw,
+                                   x_dist="normal2_outliers" if kind == "minmax" else "relu6")
+        d = workloads.make_layer_data(spec)
+        d["b"][5] = -0.0
+        d["w"][7, 1, 1] = np.inf
+        h16, up = f16_inputs(d) if dtype == torch.float16 else (d, d)
+        q = workloads.quant_for_ops(spec, up) if kind else None
+        want, _, extra = oracle_fused(oracle, up, spec, q)
+        got, t = run_fused(h16, spec, cuda_device, q, dtype=dtype)
+        if dtype == torch.float16:
+            want = oracle.to_f16_result(want)
+        assert_same_bits(got, want, "%dx%d %s %s" % (hw, hw, kind, dtype))
+        if kind == "minmax" and dtype == torch.float32:
+            np.testing.assert_array_equal(t["qr_min"].cpu().numpy(), extra[0])
+            np.testing.assert_array_equal(t["qr_max"].cpu().numpy(), extra[1])
+
+
 # ---- full benchmark sizes: sampled parity and size-independent properties ------------------
 
 def test_full_size_largest_layer_sampled_images(oracle, cuda_device):
