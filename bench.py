@@ -255,6 +255,47 @@ def standalone_op_rows(torch, ops, device, n, half, warmup, reps):
     return rows
 
 
+def backward_op_rows(torch, ops, device, n, warmup, reps):
+    """The training-side kernels on [n, 96, 56, 56] fp32, L2 flushed before every timed launch:
+    the straight-through backward of the two quantizers (x and dy read, dx written: 3 * 4 bytes
+    per element) and the convolution's gradients (input gradient: dy read, dx written; weight
+    and bias gradients: x and dy read)."""
+    c, hw = 96, 56
+    g = torch.Generator(device="cpu").manual_seed(1)
+    x = torch.randn((n, c, hw, hw), generator=g).to(device)
+    dy = torch.randn((n, c, hw, hw), generator=g).to(device)
+    w = (torch.randn((c, 3, 3), generator=g) / 3).to(device)
+    dx, dw, db = torch.empty_like(x), torch.empty_like(w), torch.empty(c, device=device)
+    e = x.numel() * 4
+    calls = [
+        ("FixedPointQuantize backward (fine-grained STE)", 3 * e,
+         lambda: ops.fixed_point_quantize_backward(dy, x, True, 8, 2.0 ** -4, True, dx=dx)),
+        ("Pow2Quantize backward (fine-grained STE)", 3 * e,
+         lambda: ops.pow2_quantize_backward(dy, x, True, True, 8, 1, True, dx=dx)),
+        ("DepthwiseConvolution 3x3 s1 backward: input gradient", 2 * e,
+         lambda: ops.depthwise_convolution_backward(x, w, dy, 1, (1, 1), (1, 1), dx=dx, need=(True, False, False))),
+        ("DepthwiseConvolution 3x3 s1 backward: weight and bias gradients", 2 * e,
+         lambda: ops.depthwise_convolution_backward(x, w, dy, 1, (1, 1), (1, 1), dw=dw, db=db, need=(False, True, True))),
+    ]
+    rows = []
+    for name, nbytes, fn in calls:
+        for _ in range(warmup):
+            fn()
+        ts = []
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(reps):
+            flush_l2(torch, device)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        ms = float(np.median(ts))
+        rows.append({"layer": name, "ms": ms, "gbs": nbytes / ms / 1e6, "bytes": nbytes})
+    ops.check_device_flag()
+    return rows
+
+
 def run_standalone_ops(args):
     """The five standalone operators on one [B, 96, 56, 56] activation (308 MB at the default
     B = 256, fp32): per-operator time and algorithmic GB/s (2 * B bytes per element: read
@@ -404,6 +445,11 @@ def other_workloads(torch, ops, workloads, device, cfg1_layers, args):
         out.append({"workload": "op: " + r["layer"], "dtype": "f32", "batch": 256, "ms": r["ms"],
                     "images_per_s": 256 / (r["ms"] / 1e3), "gbs": r["gbs"], "frac": r["gbs"] / peak,
                     "algorithmic_bytes": r["bytes"], "kernel": "standalone operator on [256,96,56,56]",
+                    "timing": "median of 10 launches, L2 flushed before each"})
+    for r in backward_op_rows(torch, ops, device, 256, 3, 10):
+        out.append({"workload": "bwd: " + r["layer"], "dtype": "f32", "batch": 256, "ms": r["ms"],
+                    "images_per_s": 256 / (r["ms"] / 1e3), "gbs": r["gbs"], "frac": r["gbs"] / peak,
+                    "algorithmic_bytes": r["bytes"], "kernel": "training-side kernel on [256,96,56,56]",
                     "timing": "median of 10 launches, L2 flushed before each"})
     torch.cuda.empty_cache()
     return out

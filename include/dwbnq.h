@@ -211,6 +211,31 @@ int dwbnq_fused_fwd(const dwbnq_conv_desc *desc, float bn_eps, const dwbnq_quant
                     const dwbnq_minmax_ptrs *mm, void *y, void *workspace, void *comm,
                     int device, void *stream);
 
+/* ---- training side: backward of the quantizers and of the convolution ------------------- */
+
+/* FixedPointQuantizeCuda<T>::backward_impl, the straight-through estimator
+ * (src/nbla/cuda/function/generic/fixed_point_quantize.cu:63-128): dx = dy, or with
+ * ste_fine_grained dx = dy where min <= x <= max and 0 elsewhere; `accum` adds to dx instead
+ * (clipped elements are then left untouched). x may be NULL without ste_fine_grained. */
+int dwbnq_fpq_bwd(int dtype, int64_t size, int sign, int n, float delta, int ste_fine_grained,
+                  int accum, const void *x, const void *dy, void *dx, int device, void *stream);
+/* Pow2QuantizeCuda<T>::backward_impl (src/nbla/cuda/function/generic/pow2_quantize.cu:79-160):
+ * dx (+)= c * dy with c = 0 where 2^round(log2f|x|) > p_max, and where x < 0 for the unsigned
+ * quantizer, else 1; plain pass-through without ste_fine_grained. */
+int dwbnq_pow2q_bwd(int dtype, int64_t size, int sign, int with_zero, int n, int m,
+                    int ste_fine_grained, int accum, const void *x, const void *dy, void *dx,
+                    int device, void *stream);
+/* DepthwiseConvolutionCuda<T>::backward_impl
+ * (src/nbla/cuda/function/generic/depthwise_convolution.cu:492-650; kernels :114-366).
+ * Any of dx [n,c,h,w], dw [c*mult,kh,kw], db [c*mult] may be NULL (propagate_down false).
+ * accum_mask bit 0 / 1 / 2: accumulate onto dx / dw / db instead of overwriting (the
+ * reference zeroes a gradient that is not accumulated, then adds). The input gradient sums in
+ * the reference's order and is bit-identical to the CPU loop; the weight and bias gradients
+ * are block reductions finished with atomic adds (order of the fp32 sum not fixed: compare
+ * within a tolerance). DWBNQ_F32 only. */
+int dwbnq_dwconv_bwd(const dwbnq_conv_desc *desc, const void *x, const void *w, const void *dy,
+                     void *dx, void *dw, void *db, int accum_mask, int device, void *stream);
+
 /* ---- 8-bit storage of quantized activations -------------------------------------------- */
 
 /* The outputs of a FixedPointQuantize layer with n <= 8 take 2^n values k * delta: as T

@@ -406,6 +406,69 @@ int dwbnq_dequantize_linear_code8_fwd(int dtype, int64_t size, float scale, int 
                                         static_cast<cudaStream_t>(stream));
 }
 
+int dwbnq_fpq_bwd(int dtype, int64_t size, int sign, int n, float delta, int ste_fine_grained, int accum,
+                  const void *x, const void *dy, void *dx, int device, void *stream) {
+  clear_error();
+  NvtxRange nvtx_range("dwbnq_fpq_bwd");
+  int st = check_dtype(dtype);
+  if (st != DWBNQ_OK) return st;
+  if (size < 0) return fail(DWBNQ_ERR_INVALID_ARG, "negative size");
+  QuantArgs q;
+  std::memset(&q, 0, sizeof(q));
+  st = fill_fpq(&q, sign, n, delta);
+  if (st != DWBNQ_OK) return st;
+  if (size > 0 && (!dy || !dx || (ste_fine_grained && !x)))
+    return fail(DWBNQ_ERR_INVALID_ARG, "dy and dx (and x for the fine-grained form) must not be null");
+  int dev;
+  st = enter_device(device, &dev);
+  if (st != DWBNQ_OK) return st;
+  if (size == 0) return DWBNQ_OK;
+  return launch_ste_backward(dtype, ste_fine_grained ? 1 : 0, accum, size, q.fpq_max, q.fpq_min, 0u, 0, x, dy, dx,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int dwbnq_pow2q_bwd(int dtype, int64_t size, int sign, int with_zero, int n, int m, int ste_fine_grained, int accum,
+                    const void *x, const void *dy, void *dx, int device, void *stream) {
+  clear_error();
+  NvtxRange nvtx_range("dwbnq_pow2q_bwd");
+  int st = check_dtype(dtype);
+  if (st != DWBNQ_OK) return st;
+  if (size < 0) return fail(DWBNQ_ERR_INVALID_ARG, "negative size");
+  if (n < 1 || n > 31) return fail(DWBNQ_ERR_INVALID_ARG, "Pow2Quantize: bit width n=%d out of range", n);
+  if (size > 0 && (!dy || !dx || (ste_fine_grained && !x)))
+    return fail(DWBNQ_ERR_INVALID_ARG, "dy and dx (and x for the fine-grained form) must not be null");
+  float p_max, p_min, thr;
+  pow2q_range(sign, with_zero, n, m, &p_max, &p_min, &thr);
+  // q > p_max for powers of two q: q >= 2 * p_max (an overflow to inf leaves only |x| = inf)
+  const uint32_t first_above = pow2_first_pattern_reaching(p_max * 2.0f);
+  int dev;
+  st = enter_device(device, &dev);
+  if (st != DWBNQ_OK) return st;
+  if (size == 0) return DWBNQ_OK;
+  return launch_ste_backward(dtype, ste_fine_grained ? 2 : 0, accum, size, 0.0f, 0.0f, first_above, sign ? 1 : 0, x, dy,
+                             dx, static_cast<cudaStream_t>(stream));
+}
+
+int dwbnq_dwconv_bwd(const dwbnq_conv_desc *desc, const void *x, const void *w, const void *dy, void *dx, void *dw,
+                     void *db, int accum_mask, int device, void *stream) {
+  clear_error();
+  NvtxRange nvtx_range("dwbnq_dwconv_bwd");
+  int ho, wo;
+  int st = validate_conv(desc, &ho, &wo);
+  if (st != DWBNQ_OK) return st;
+  if (desc->dtype != DWBNQ_F32)
+    return fail(DWBNQ_ERR_UNSUPPORTED, "DepthwiseConvolution backward is implemented for DWBNQ_F32");
+  if (!dx && !dw && !db) return DWBNQ_OK;  // nothing to propagate (the reference returns early too)
+  if (!dy) return fail(DWBNQ_ERR_INVALID_ARG, "dy must not be null");
+  if (dx && !w) return fail(DWBNQ_ERR_INVALID_ARG, "the input gradient needs w");
+  if (dw && !x) return fail(DWBNQ_ERR_INVALID_ARG, "the weight gradient needs x");
+  int dev;
+  st = enter_device(device, &dev);
+  if (st != DWBNQ_OK) return st;
+  if (desc->n == 0 && !dw && !db) return DWBNQ_OK;
+  return launch_dwconv_backward(*desc, ho, wo, x, w, dy, dx, dw, db, accum_mask, static_cast<cudaStream_t>(stream));
+}
+
 int dwbnq_dwconv_fwd(const dwbnq_conv_desc *desc, const void *x, const void *w, const void *b,
                      void *y, int device, void *stream) {
   return dwbnq_fused_fwd(desc, 0.0f, nullptr, x, w, b, nullptr, nullptr, nullptr, nullptr, nullptr, y,

@@ -1,0 +1,362 @@
+// Training side of the path: straight-through backward of FixedPointQuantize and
+// Pow2Quantize, and the three gradients of DepthwiseConvolution.
+//
+// What each kernel computes is the reference's backward
+// (src/nbla/cuda/function/generic/fixed_point_quantize.cu:63-128, pow2_quantize.cu:79-160,
+// depthwise_convolution.cu:114-366 and 492-650):
+//  * quantizers: dx (+)= c * dy with c = 1, except (fine-grained STE) c = 0 where the forward
+//    clipped: FixedPointQuantize x > max or x < min (then dx is left alone when accumulating,
+//    zeroed otherwise); Pow2Quantize 2^round(log2f|x|) > p_max, or x < 0 for the unsigned form.
+//    Element-wise, one rounded operation per element: bit-identical to the CPU loop.
+//  * dw-conv input gradient: dx[n,c,iy,ix] += sum over ky, kx (ascending), m of
+//    w[c*mult+m][ky][kx] * dy[n, c*mult+m, oy, ox] with oy*s = iy + p - ky*d (taps that do not
+//    land on an output are skipped); the sum starts at +0, runs in that order with product and
+//    sum rounded separately, and is added to the gradient (to +0 when not accumulating): the
+//    order of the reference loop, so the result is bit-identical to the CPU restatement.
+//  * dw-conv weight and bias gradients: dw[oc][ky][kx] += sum over n, oy, ox of
+//    x[n, oc/mult, oy*s + ky*d - p, ox*s + kx*d - p] * dy[n,oc,oy,ox]; db[oc] += sum of dy.
+//    The reference reduces with a block tree (blockReduceSum), this kernel with per-thread
+//    partial sums, a warp and block reduction and one atomic add per CTA: the association of
+//    the fp32 sum differs (from the reference's as from the CPU loop's), so these two
+//    gradients are compared within a tolerance, not bit for bit.
+// All kernels are bandwidth-shaped: 16-byte accesses where the layout allows, grids sized from
+// the SM count.
+#include "dwbnq_internal.h"
+
+namespace dwbnq {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+unsigned int grid_for(long long items, int per_sm) {
+  long long blocks = (items + kThreads - 1) / kThreads;
+  const long long cap = (long long)sm_count(-1) * per_sm;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (unsigned int)blocks;
+}
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) % 16) == 0; }
+
+// ---- straight-through backward of the quantizers ------------------------------------------
+// MODE 0: pass-through (ste_fine_grained = false); 1: FixedPointQuantize mask; 2: Pow2 mask.
+struct SteArgs {
+  float fpq_max, fpq_min;
+  unsigned int pow2_first_above;  // smallest |x| pattern whose rounded power of two exceeds p_max
+  int pow2_sign;
+};
+
+template <int MODE, bool ACCUM>
+__device__ __forceinline__ float ste_one(float x, float dy, float dx_old, const SteArgs &s) {
+  if (MODE == 0) return ACCUM ? __fadd_rn(dx_old, dy) : dy;
+  if (MODE == 1) {
+    if (x > s.fpq_max || x < s.fpq_min) return ACCUM ? dx_old : 0.0f;
+    return ACCUM ? __fadd_rn(dx_old, dy) : dy;
+  }
+  // Pow2: c = 1; q > p_max -> 0 (a NaN x compares false); unsigned and x < 0 -> 0; dx (+)= c * dy
+  const unsigned int a = __float_as_uint(x) & 0x7fffffffu;
+  float c = (a >= s.pow2_first_above && a <= 0x7f800000u) ? 0.0f : 1.0f;
+  if (!s.pow2_sign && x < 0.0f) c = 0.0f;
+  const float g = __fmul_rn(c, dy);
+  return ACCUM ? __fadd_rn(dx_old, g) : g;
+}
+
+template <typename T, int MODE, bool ACCUM>
+__global__ void __launch_bounds__(kThreads)
+    ste_backward_kernel(const T *__restrict__ x, const T *__restrict__ dy, T *dx, long long size, int vec_ok,
+                        SteArgs s) {
+  constexpr int S = Elem<T>::VEC;
+  pdl_launch_dependents();
+  pdl_wait_for_predecessor();
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long step = (long long)gridDim.x * blockDim.x;
+  const long long n_vec = vec_ok ? size / S : 0;
+  for (long long v = tid; v < n_vec; v += step) {
+    float ex[S], ey[S], eo[S];
+    if (MODE != 0) Vec16<T>::load_stream(x + v * S, ex);
+    Vec16<T>::load_stream(dy + v * S, ey);
+    if (ACCUM) Vec16<T>::load(dx + v * S, eo);
+#pragma unroll
+    for (int j = 0; j < S; ++j) eo[j] = ste_one<MODE, ACCUM>(MODE != 0 ? ex[j] : 0.0f, ey[j], ACCUM ? eo[j] : 0.0f, s);
+    Vec16<T>::store_stream(dx + v * S, eo);
+  }
+  for (long long i = n_vec * S + tid; i < size; i += step) {
+    const float xo = MODE != 0 ? Elem<T>::to_f32(x[i]) : 0.0f;
+    const float old = ACCUM ? Elem<T>::to_f32(dx[i]) : 0.0f;
+    dx[i] = Elem<T>::from_f32(ste_one<MODE, ACCUM>(xo, Elem<T>::to_f32(dy[i]), old, s));
+  }
+}
+
+template <typename T>
+cudaError_t launch_ste_t(int mode, int accum, const T *x, const T *dy, T *dx, long long size, const SteArgs &s,
+                         cudaStream_t stream) {
+  const int S = Elem<T>::VEC;
+  const int vec_ok = aligned16(dy) && aligned16(dx) && (mode == 0 || aligned16(x));
+  const dim3 grid(grid_for((size + S - 1) / S, 16)), block(kThreads);
+#define DWBNQ_STE(M, A) \
+  return launch_pdl(ste_backward_kernel<T, M, A>, grid, block, 0, stream, x, dy, dx, size, vec_ok, s)
+  if (mode == 0) {
+    if (accum) DWBNQ_STE(0, true);
+    DWBNQ_STE(0, false);
+  }
+  if (mode == 1) {
+    if (accum) DWBNQ_STE(1, true);
+    DWBNQ_STE(1, false);
+  }
+  if (accum) DWBNQ_STE(2, true);
+  DWBNQ_STE(2, false);
+#undef DWBNQ_STE
+}
+
+// ---- DepthwiseConvolution: input gradient ------------------------------------------------------
+struct BwdArgs {
+  const void *x, *w, *dy;
+  void *dx, *dw, *db;
+  long long n;
+  int C, H, W, OC, Ho, Wo;
+  int kh, kw, sh, sw, ph, pw, dh, dw_, mult;
+};
+
+template <typename T, bool ACCUM>
+__global__ void __launch_bounds__(kThreads)
+    dwconv_bwd_input_kernel(const BwdArgs a, const long long total) {
+  const T *w = static_cast<const T *>(a.w);
+  const T *dy = static_cast<const T *>(a.dy);
+  T *dx = static_cast<T *>(a.dx);
+  pdl_launch_dependents();
+  pdl_wait_for_predecessor();
+  const long long step = (long long)gridDim.x * blockDim.x;
+  const long long plane_out = (long long)a.Ho * a.Wo;
+  for (long long o = (long long)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += step) {
+    const int ix = (int)(o % a.W);
+    long long t = o / a.W;
+    const int iy = (int)(t % a.H);
+    t /= a.H;
+    const int c = (int)(t % a.C);
+    const long long n = t / a.C;
+    const int oc0 = c * a.mult;
+    const T *dyp = dy + (n * a.OC + oc0) * plane_out;
+    const T *wp = w + (long long)oc0 * a.kh * a.kw;
+    float value = 0.0f;
+    for (int ky = 0; ky < a.kh; ++ky) {
+      const int ty = iy + a.ph - ky * a.dh;
+      // C division truncates toward zero: the reference tests (t - (t / s) * s == 0) and then
+      // the range, so a negative multiple of the stride passes the first test and fails the second
+      const int oy = ty / a.sh;
+      const bool row_ok = (ty - oy * a.sh == 0) && oy >= 0 && oy < a.Ho;
+      for (int kx = 0; kx < a.kw; ++kx) {
+        const int tx = ix + a.pw - kx * a.dw_;
+        const int ox = tx / a.sw;
+        if (row_ok && (tx - ox * a.sw == 0) && ox >= 0 && ox < a.Wo) {
+          const long long off = (long long)oy * a.Wo + ox;
+          const int wi = ky * a.kw + kx;
+          for (int m = 0; m < a.mult; ++m)
+            value = __fadd_rn(value, __fmul_rn(Elem<T>::to_f32(wp[m * a.kh * a.kw + wi]),
+                                               Elem<T>::to_f32(dyp[m * plane_out + off])));
+        }
+      }
+    }
+    const float old = ACCUM ? Elem<T>::to_f32(dx[o]) : 0.0f;
+    dx[o] = Elem<T>::from_f32(__fadd_rn(old, value));
+  }
+}
+
+// ---- DepthwiseConvolution: weight and bias gradients ---------------------------------------------
+// CTA = one output channel x one slice of the batch. A thread walks over output positions of
+// its slice, keeps dy in a register and accumulates x * dy for each of the KK taps in
+// registers (x re-read through L1: neighbouring taps hit the same lines), plus dy for the
+// bias; warp shuffles and shared memory reduce the CTA's partial sums, which are then added to
+// the gradients with one atomic per value. The gradients must be zero (or hold the value to
+// accumulate onto) when the kernel starts.
+template <typename T, int KH, int KW>
+__global__ void __launch_bounds__(kThreads)
+    dwconv_bwd_weights_kernel(const BwdArgs a, const int slices) {
+  constexpr int KK = KH * KW;
+  __shared__ float red[kThreads / 32][KK + 1];
+  const T *x = static_cast<const T *>(a.x);
+  const T *dy = static_cast<const T *>(a.dy);
+  pdl_launch_dependents();
+  pdl_wait_for_predecessor();
+  const int oc = blockIdx.x / slices;
+  const int slice = blockIdx.x % slices;
+  const int ic = oc / a.mult;
+  const long long plane_out = (long long)a.Ho * a.Wo;
+  const long long plane_in = (long long)a.H * a.W;
+  // images [n0, n1) of this slice
+  const long long per = (a.n + slices - 1) / slices;
+  const long long n0 = (long long)slice * per;
+  const long long n1 = n0 + per < a.n ? n0 + per : a.n;
+  float acc[KK];
+#pragma unroll
+  for (int i = 0; i < KK; ++i) acc[i] = 0.0f;
+  float bsum = 0.0f;
+  const long long items = (n1 > n0 ? n1 - n0 : 0) * plane_out;
+  for (long long it = threadIdx.x; it < items; it += kThreads) {
+    const long long n = n0 + it / plane_out;
+    const int pos = (int)(it % plane_out);
+    const int oy = pos / a.Wo, ox = pos - oy * a.Wo;
+    const float g = Elem<T>::to_f32(dy[(n * a.OC + oc) * plane_out + pos]);
+    const T *xp = x + (n * a.C + ic) * plane_in;
+    bsum += g;
+#pragma unroll
+    for (int i = 0; i < KK; ++i) {
+      const int ky = i / KW, kx = i - ky * KW;
+      const int iy = oy * a.sh + ky * a.dh - a.ph;
+      const int ix = ox * a.sw + kx * a.dw_ - a.pw;
+      if (iy >= 0 && iy < a.H && ix >= 0 && ix < a.W) acc[i] += Elem<T>::to_f32(xp[(long long)iy * a.W + ix]) * g;
+    }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int i = 0; i <= KK; ++i) {
+    float v = i < KK ? acc[i < KK ? i : 0] : bsum;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) red[warp][i] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x <= KK) {
+    float v = 0.0f;
+#pragma unroll
+    for (int wv = 0; wv < kThreads / 32; ++wv) v += red[wv][threadIdx.x];
+    if (threadIdx.x < KK) {
+      if (a.dw) atomicAdd(static_cast<float *>(a.dw) + (long long)oc * KK + threadIdx.x, v);
+    } else if (a.db) {
+      atomicAdd(static_cast<float *>(a.db) + oc, v);
+    }
+  }
+}
+
+// Any kernel size: one CTA per weight value (and one more per channel for the bias), the
+// reference's own decomposition. Slow path for kernels other than 3x3 and 5x5.
+template <typename T>
+__global__ void __launch_bounds__(kThreads) dwconv_bwd_weights_any_kernel(const BwdArgs a) {
+  __shared__ float red[kThreads / 32];
+  const T *x = static_cast<const T *>(a.x);
+  const T *dy = static_cast<const T *>(a.dy);
+  const int kk = a.kh * a.kw;
+  const int oc = blockIdx.x / (kk + 1);
+  const int tap = blockIdx.x % (kk + 1);  // kk = the bias
+  if (tap == kk && !a.db) return;
+  if (tap < kk && !a.dw) return;
+  const int ic = oc / a.mult;
+  const int ky = tap < kk ? tap / a.kw : 0, kx = tap < kk ? tap % a.kw : 0;
+  const long long plane_out = (long long)a.Ho * a.Wo;
+  float v = 0.0f;
+  for (long long it = threadIdx.x; it < a.n * plane_out; it += kThreads) {
+    const long long n = it / plane_out;
+    const int pos = (int)(it % plane_out);
+    const int oy = pos / a.Wo, ox = pos - oy * a.Wo;
+    const float g = Elem<T>::to_f32(dy[(n * a.OC + oc) * plane_out + pos]);
+    if (tap == kk) {
+      v += g;
+    } else {
+      const int iy = oy * a.sh + ky * a.dh - a.ph;
+      const int ix = ox * a.sw + kx * a.dw_ - a.pw;
+      if (iy >= 0 && iy < a.H && ix >= 0 && ix < a.W)
+        v += Elem<T>::to_f32(x[((n * a.C + ic) * a.H + iy) * (long long)a.W + ix]) * g;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float s = 0.0f;
+    for (int i = 0; i < kThreads / 32; ++i) s += red[i];
+    if (tap == kk) atomicAdd(static_cast<float *>(a.db) + oc, s);
+    else atomicAdd(static_cast<float *>(a.dw) + (long long)oc * kk + tap, s);
+  }
+}
+
+__global__ void zero_f32_kernel(float *p, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    p[i] = 0.0f;
+}
+
+}  // namespace
+
+int launch_ste_backward(int dtype, int mode, int accum, long long size, float fpq_max, float fpq_min,
+                        unsigned int pow2_first_above, int pow2_sign, const void *x, const void *dy, void *dx,
+                        cudaStream_t stream) {
+  SteArgs s;
+  s.fpq_max = fpq_max;
+  s.fpq_min = fpq_min;
+  s.pow2_first_above = pow2_first_above;
+  s.pow2_sign = pow2_sign;
+  const cudaError_t e =
+      dtype == DWBNQ_F32
+          ? launch_ste_t<float>(mode, accum, static_cast<const float *>(x), static_cast<const float *>(dy),
+                                static_cast<float *>(dx), size, s, stream)
+          : launch_ste_t<__half>(mode, accum, static_cast<const __half *>(x), static_cast<const __half *>(dy),
+                                 static_cast<__half *>(dx), size, s, stream);
+  if (e != cudaSuccess) return fail_cuda(e, "ste_backward_kernel launch");
+  return DWBNQ_OK;
+}
+
+int launch_dwconv_backward(const dwbnq_conv_desc &d, int ho, int wo, const void *x, const void *w, const void *dy,
+                           void *dx, void *dw, void *db, int accum_mask, cudaStream_t stream) {
+  BwdArgs a;
+  a.x = x;
+  a.w = w;
+  a.dy = dy;
+  a.dx = dx;
+  a.dw = dw;
+  a.db = db;
+  a.n = d.n;
+  a.C = d.c;
+  a.H = d.h;
+  a.W = d.w;
+  a.OC = d.c * d.multiplier;
+  a.Ho = ho;
+  a.Wo = wo;
+  a.kh = d.kh;
+  a.kw = d.kw;
+  a.sh = d.stride_h;
+  a.sw = d.stride_w;
+  a.ph = d.pad_h;
+  a.pw = d.pad_w;
+  a.dh = d.dil_h;
+  a.dw_ = d.dil_w;
+  a.mult = d.multiplier;
+  cudaError_t e = cudaSuccess;
+  if (dx) {
+    const long long total = d.n * (long long)d.c * d.h * d.w;
+    const dim3 grid(grid_for(total, 32)), block(kThreads);
+    const bool acc = (accum_mask & 1) != 0;
+    e = acc ? launch_pdl(dwconv_bwd_input_kernel<float, true>, grid, block, 0, stream, a, total)
+            : launch_pdl(dwconv_bwd_input_kernel<float, false>, grid, block, 0, stream, a, total);
+    if (e != cudaSuccess) return fail_cuda(e, "dwconv_bwd_input_kernel launch");
+  }
+  if (dw || db) {
+    const int kk = d.kh * d.kw;
+    // gradients that are not accumulated onto start from zero (the kernels add atomically)
+    if (dw && !(accum_mask & 2)) {
+      zero_f32_kernel<<<grid_for((long long)a.OC * kk, 4), kThreads, 0, stream>>>(static_cast<float *>(dw),
+                                                                                    (long long)a.OC * kk);
+      if ((e = cudaGetLastError()) != cudaSuccess) return fail_cuda(e, "zero_f32_kernel launch");
+    }
+    if (db && !(accum_mask & 4)) {
+      zero_f32_kernel<<<grid_for(a.OC, 4), kThreads, 0, stream>>>(static_cast<float *>(db), a.OC);
+      if ((e = cudaGetLastError()) != cudaSuccess) return fail_cuda(e, "zero_f32_kernel launch");
+    }
+    const bool k3 = d.kh == 3 && d.kw == 3, k5 = d.kh == 5 && d.kw == 5;
+    if (k3 || k5) {
+      // enough CTAs for eight per SM; a slice is at least one image
+      long long slices = ((long long)sm_count(-1) * 8 + a.OC - 1) / a.OC;
+      if (slices > d.n) slices = d.n;
+      if (slices < 1) slices = 1;
+      const dim3 grid((unsigned int)(a.OC * slices)), block(kThreads);
+      e = k3 ? launch_pdl(dwconv_bwd_weights_kernel<float, 3, 3>, grid, block, 0, stream, a, (int)slices)
+             : launch_pdl(dwconv_bwd_weights_kernel<float, 5, 5>, grid, block, 0, stream, a, (int)slices);
+    } else {
+      const dim3 grid((unsigned int)(a.OC * (kk + 1))), block(kThreads);
+      dwconv_bwd_weights_any_kernel<float><<<grid, block, 0, stream>>>(a);
+      e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) return fail_cuda(e, "dwconv_bwd_weights_kernel launch");
+  }
+  return DWBNQ_OK;
+}
+
+}  // namespace dwbnq

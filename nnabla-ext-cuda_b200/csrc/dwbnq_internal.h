@@ -117,6 +117,20 @@ int fill_pow2(QuantArgs *q, int sign, int with_zero, int n, int m, int device);
 // Device copy of the table (pow2_table_dev.cu).
 int pow2_table_device(int device, const uint32_t **ptr);
 
+// ---- training side (backward.cu) ---------------------------------------------------------------
+// Straight-through backward of a quantizer. mode 0 = pass-through, 1 = FixedPointQuantize mask
+// (fpq_max / fpq_min), 2 = Pow2Quantize mask (pow2_first_above: the smallest magnitude pattern
+// whose rounded power of two exceeds p_max; pow2_sign).
+int launch_ste_backward(int dtype, int mode, int accum, long long size, float fpq_max, float fpq_min,
+                        unsigned int pow2_first_above, int pow2_sign, const void *x, const void *dy, void *dx,
+                        cudaStream_t stream);
+// Gradients of DepthwiseConvolution (fp32); any of dx, dw, db may be null. accum_mask: bit 0
+// dx, bit 1 dw, bit 2 db are accumulated onto instead of overwritten.
+int launch_dwconv_backward(const dwbnq_conv_desc &d, int ho, int wo, const void *x, const void *w, const void *dy,
+                           void *dx, void *dw, void *db, int accum_mask, cudaStream_t stream);
+// Smallest float bit pattern a > 0 with 2^round(log2f(a)) >= v (host libm, bisection).
+uint32_t pow2_first_pattern_reaching(float v);
+
 // ---- communicator (comm.cpp) --------------------------------------------------------------
 int comm_allreduce_max(void *comm, float *buf, long long count, cudaStream_t stream,
                        int timeout_ms);

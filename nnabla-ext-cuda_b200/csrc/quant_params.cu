@@ -96,6 +96,16 @@ int pow2_table_window() {
   return g_window;
 }
 
+uint32_t pow2_first_pattern_reaching(float v) {
+  uint32_t lo = 1u, hi = 0x7f800000u;  // q(hi) = inf >= v
+  while (lo < hi) {
+    const uint32_t mid = lo + (hi - lo) / 2;
+    if (powf(2.0f, roundf(log2f(bits_to_float(mid)))) >= v) hi = mid;
+    else lo = mid + 1;
+  }
+  return lo;
+}
+
 int fill_pow2(QuantArgs *q, int sign, int with_zero, int n, int m, int device) {
   if (n < 1 || n > 31) return fail(DWBNQ_ERR_INVALID_ARG, "Pow2Quantize: bit width n=%d out of range", n);
   pow2q_range(sign, with_zero, n, m, &q->p_max, &q->p_min, &q->prune_thr);
@@ -111,15 +121,7 @@ int fill_pow2(QuantArgs *q, int sign, int with_zero, int n, int m, int device) {
     std::memcpy(&b, &f, 4);
     return b;
   };
-  auto first_reaching = [&](float v) {
-    uint32_t lo = 1u, hi = 0x7f800000u;  // q(hi) = inf >= v
-    while (lo < hi) {
-      const uint32_t mid = lo + (hi - lo) / 2;
-      if (powf(2.0f, roundf(log2f(bits_to_float(mid)))) >= v) hi = mid;
-      else lo = mid + 1;
-    }
-    return lo;
-  };
+  auto first_reaching = [&](float v) { return pow2_first_pattern_reaching(v); };
   q->p_lo_bits = float_bits(q->p_min);
   q->p_hi_bits = float_bits(q->p_max);
   q->p_prune_bits = 0u;

@@ -15,8 +15,10 @@
 // (e.g. src/nbla/cuda/function/generic/depthwise_convolution.cu:435-449): make the device
 // current, fetch device pointers with get_data_pointer / cast_data_and_get_pointer, launch on
 // the legacy default stream, return without synchronising. A non-zero dwbnq status becomes an
-// nbla::Exception through NBLA_ERROR. Backward is left to the base classes' contract:
-// it raises not_implemented (this library is the inference path).
+// nbla::Exception through NBLA_ERROR. Backward: DepthwiseConvolution (float), FixedPointQuantize
+// and Pow2Quantize call the library's backward entry points with the reference's
+// propagate_down / accum semantics; BatchNormalization, MinMaxQuantize and the fused function
+// object raise not_implemented (inference path).
 //
 // Besides the five registered classes the plugin holds FusedDwBnQuantCuda, the single
 // function object a graph converter substitutes for a whole dw-conv -> BN -> quantizer
@@ -104,7 +106,21 @@ protected:
     Tc *y = outputs[0]->cast_data_and_get_pointer<Tc>(this->ctx_, true);
     check(dwbnq_dwconv_fwd(&desc_, x, w, b, y, device_, nullptr), "DepthwiseConvolutionCuda::forward");
   }
-  DWBNQ_NO_BACKWARD("DepthwiseConvolutionCuda")
+  // The reference's backward_impl (depthwise_convolution.cu:492-650): a gradient is computed
+  // when its propagate_down flag is set and overwritten unless its accum flag is set.
+  virtual void backward_impl(const Variables &inputs, const Variables &outputs, const vector<bool> &propagate_down,
+                             const vector<bool> &accum) {
+    const bool has_bias = inputs.size() == 3;
+    if (!(propagate_down[0] || propagate_down[1] || (has_bias && propagate_down[2]))) return;
+    const Tc *x = inputs[0]->get_data_pointer<Tc>(this->ctx_);
+    const Tc *w = inputs[1]->get_data_pointer<Tc>(this->ctx_);
+    const Tc *dy = outputs[0]->get_grad_pointer<Tc>(this->ctx_);
+    Tc *dx = propagate_down[0] ? inputs[0]->cast_grad_and_get_pointer<Tc>(this->ctx_, !accum[0]) : nullptr;
+    Tc *dw = propagate_down[1] ? inputs[1]->cast_grad_and_get_pointer<Tc>(this->ctx_, !accum[1]) : nullptr;
+    Tc *db = (has_bias && propagate_down[2]) ? inputs[2]->cast_grad_and_get_pointer<Tc>(this->ctx_, !accum[2]) : nullptr;
+    const int mask = (accum[0] ? 1 : 0) | (accum[1] ? 2 : 0) | ((has_bias && accum[2]) ? 4 : 0);
+    check(dwbnq_dwconv_bwd(&desc_, x, w, dy, dx, dw, db, mask, device_, nullptr), "DepthwiseConvolutionCuda::backward");
+  }
 };
 
 // ---- BatchNormalization (batch_stat = false) ---------------------------------------------
@@ -166,7 +182,16 @@ protected:
                         nullptr),
           "FixedPointQuantizeCuda::forward");
   }
-  DWBNQ_NO_BACKWARD("FixedPointQuantizeCuda")
+  virtual void backward_impl(const Variables &inputs, const Variables &outputs, const vector<bool> &propagate_down,
+                             const vector<bool> &accum) {
+    if (!propagate_down[0]) return;
+    Tc *dx = inputs[0]->cast_grad_and_get_pointer<Tc>(this->ctx_, !accum[0]);
+    const Tc *dy = outputs[0]->get_grad_pointer<Tc>(this->ctx_);
+    const Tc *x = inputs[0]->get_data_pointer<Tc>(this->ctx_);
+    check(dwbnq_fpq_bwd(DType<T>::value, inputs[0]->size(), this->sign_, this->n_, this->delta_,
+                        this->ste_fine_grained_, accum[0], x, dy, dx, device_, nullptr),
+          "FixedPointQuantizeCuda::backward");
+  }
 };
 
 // ---- Pow2Quantize ------------------------------------------------------------------------------
@@ -190,7 +215,16 @@ protected:
                           x, y, device_, nullptr),
           "Pow2QuantizeCuda::forward");
   }
-  DWBNQ_NO_BACKWARD("Pow2QuantizeCuda")
+  virtual void backward_impl(const Variables &inputs, const Variables &outputs, const vector<bool> &propagate_down,
+                             const vector<bool> &accum) {
+    if (!propagate_down[0]) return;
+    const Tc *x = inputs[0]->get_data_pointer<Tc>(this->ctx_);
+    Tc *dx = inputs[0]->cast_grad_and_get_pointer<Tc>(this->ctx_, !accum[0]);
+    const Tc *dy = outputs[0]->get_grad_pointer<Tc>(this->ctx_);
+    check(dwbnq_pow2q_bwd(DType<T>::value, inputs[0]->size(), this->sign_, this->with_zero_, this->n_, this->m_,
+                          this->ste_fine_grained_, accum[0], x, dy, dx, device_, nullptr),
+          "Pow2QuantizeCuda::backward");
+  }
 };
 
 // ---- MinMaxQuantize (per-channel ranges [1, C, 1, 1]) --------------------------------------------

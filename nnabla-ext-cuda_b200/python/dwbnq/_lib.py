@@ -74,6 +74,9 @@ SIGNATURES = {
                                         _vp, _int, _vp]),
     "dwbnq_fused_fwd": (_int, [_P(ConvDesc), _flt, _P(QuantDesc), _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                _P(MinMaxPtrs), _vp, _vp, _vp, _int, _vp]),
+    "dwbnq_fpq_bwd": (_int, [_int, _i64, _int, _int, _flt, _int, _int, _vp, _vp, _vp, _int, _vp]),
+    "dwbnq_pow2q_bwd": (_int, [_int, _i64, _int, _int, _int, _int, _int, _int, _vp, _vp, _vp, _int, _vp]),
+    "dwbnq_dwconv_bwd": (_int, [_P(ConvDesc), _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _vp]),
     "dwbnq_quantize_linear_code8_fwd": (_int, [_int, _i64, _flt, _int, _int, _int, _int, _vp, _vp, _int, _vp]),
     "dwbnq_dequantize_linear_code8_fwd": (_int, [_int, _i64, _flt, _int, _int, _vp, _vp, _int, _vp]),
     "dwbnq_fused_fwd_code8": (_int, [_P(ConvDesc), _flt, _P(QuantDesc), _P(Code8Desc), _vp, _vp, _vp, _vp, _vp,

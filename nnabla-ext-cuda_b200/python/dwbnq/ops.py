@@ -219,6 +219,46 @@ def fused_dw_bn_quant(x, w, b, beta, gamma, mean, variance, eps=1e-5, pad=None, 
     return y
 
 
+# ---- training side -------------------------------------------------------------------------------
+
+def fixed_point_quantize_backward(dy, x=None, sign=True, n=8, delta=2.0 ** -4, ste_fine_grained=True, dx=None,
+                                  accum=False):
+    """STE backward of fixed_point_quantize: returns dx (``dx`` given and ``accum``: added onto)."""
+    dev = _chk_cuda(dy, x, dx)
+    out = dx if dx is not None else torch.empty_like(dy)
+    L.check(L.lib().dwbnq_fpq_bwd(_dtype_code(dy), dy.numel(), int(sign), int(n), float(delta), int(ste_fine_grained),
+                                  int(accum), _ptr(x), _ptr(dy), _ptr(out), dev.index, _stream(dev)))
+    return out
+
+
+def pow2_quantize_backward(dy, x=None, sign=True, with_zero=True, n=8, m=1, ste_fine_grained=True, dx=None,
+                           accum=False):
+    """STE backward of pow2_quantize."""
+    dev = _chk_cuda(dy, x, dx)
+    out = dx if dx is not None else torch.empty_like(dy)
+    L.check(L.lib().dwbnq_pow2q_bwd(_dtype_code(dy), dy.numel(), int(sign), int(with_zero), int(n), int(m),
+                                    int(ste_fine_grained), int(accum), _ptr(x), _ptr(dy), _ptr(out), dev.index,
+                                    _stream(dev)))
+    return out
+
+
+def depthwise_convolution_backward(x, w, dy, base_axis=1, pad=None, stride=None, dilation=None, multiplier=1,
+                                   dx=None, dw=None, db=None, need=(True, True, True), accum=(False, False, False)):
+    """Gradients of depthwise_convolution: returns (dx, dw, db), None where ``need`` is False
+    (propagate_down); ``accum[i]`` adds onto the given tensor instead of overwriting it."""
+    dev = _chk_cuda(x, w, dy, dx, dw, db)
+    d, oshape = conv_desc(x, w, base_axis, pad, stride, dilation, multiplier)
+    if tuple(dy.shape) != tuple(oshape):
+        raise ValueError("dy has shape %s, the convolution's output is %s" % (tuple(dy.shape), tuple(oshape)))
+    dx = (dx if dx is not None else torch.empty_like(x)) if need[0] else None
+    dw = (dw if dw is not None else torch.empty_like(w)) if need[1] else None
+    db = (db if db is not None else torch.empty(w.shape[0], dtype=w.dtype, device=dev)) if need[2] else None
+    mask = (1 if accum[0] else 0) | (2 if accum[1] else 0) | (4 if accum[2] else 0)
+    L.check(L.lib().dwbnq_dwconv_bwd(ctypes.byref(d), _ptr(x), _ptr(w), _ptr(dy), _ptr(dx), _ptr(dw), _ptr(db), mask,
+                                     dev.index, _stream(dev)))
+    return dx, dw, db
+
+
 # ---- 8-bit storage of quantized activations -------------------------------------------------
 
 def quantize_linear_code8(x, scale, zero_point=0, round_mode="HALF_AWAY_FROM_ZERO", signed=False,

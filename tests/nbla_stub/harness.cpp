@@ -182,9 +182,55 @@ int stub_fused_backward_is_refused(int device) {
 int stub_backward_is_refused(int device) {
   return guarded([&] {
     dwbnq_register_nbla();
-    std::unique_ptr<nbla::Function> f(nbla::stub_create<bool, int, float, bool>(
-        "FixedPointQuantize", "cuda:float", ctx_for(device, 0), true, 8, 0.0625f, true));
+    std::unique_ptr<nbla::Function> f(nbla::stub_create<float, bool, bool, bool, float>(
+        "MinMaxQuantize", "cuda:float", ctx_for(device, 0), 0.999f, true, false, true, 0.01f));
     f->backward({}, {}, {}, {});
+  });
+}
+// backward of the two quantizers through the registered classes: which = 0 FixedPointQuantize
+// (sign, n, delta), 1 Pow2Quantize (sign, with_zero = a, n, m = b)
+int stub_quant_bwd(int which, int half, int device, int64_t size, void *x, void *dy, void *dx, int sign, int n, float delta,
+                   int a, int b, int fine, int accum, int propagate) {
+  return guarded([&] {
+    dwbnq_register_nbla();
+    const char *be = half ? "cuda:half" : "cuda:float";
+    std::unique_ptr<nbla::Function> f(
+        which == 0 ? nbla::stub_create<bool, int, float, bool>("FixedPointQuantize", be, ctx_for(device, half), sign != 0, n,
+                                                               delta, fine != 0)
+                   : nbla::stub_create<bool, bool, int, int, bool>("Pow2Quantize", be, ctx_for(device, half), sign != 0,
+                                                                   a != 0, n, b, fine != 0));
+    nbla::Variable vx(nbla::Shape_t{size}, x), vy(nbla::Shape_t{size}, nullptr);
+    vx.set_grad(dx);
+    vy.set_grad(dy);
+    nbla::Variables in{&vx}, out{&vy};
+    f->setup(in, out);
+    f->backward(in, out, {propagate != 0}, {accum != 0});
+  });
+}
+int stub_dwconv_bwd(int half, int device, const int64_t *xs, const int64_t *ws, int nd, void *x, void *w, void *b, void *dy,
+                    void *dx, void *dw, void *db, int pad, int stride, int dil, int mult, int propagate_mask,
+                    int accum_mask) {
+  return guarded([&] {
+    dwbnq_register_nbla();
+    const std::vector<int> p(nd - 2, pad), s(nd - 2, stride), d(nd - 2, dil);
+    std::unique_ptr<nbla::Function> f(
+        nbla::stub_create<int, const std::vector<int> &, const std::vector<int> &, const std::vector<int> &, int>(
+            "DepthwiseConvolution", half ? "cuda:half" : "cuda:float", ctx_for(device, half), 1, p, s, d, mult));
+    nbla::Variable vx(shp(xs, nd), x), vw(shp(ws, nd - 1), w), vb(nbla::Shape_t{ws[0]}, b), vy(nbla::Shape_t{}, nullptr);
+    vx.set_grad(dx);
+    vw.set_grad(dw);
+    vb.set_grad(db);
+    vy.set_grad(dy);
+    nbla::Variables in{&vx, &vw};
+    if (b) in.push_back(&vb);
+    nbla::Variables out{&vy};
+    f->setup(in, out);
+    std::vector<bool> pd, ac;
+    for (size_t i = 0; i < in.size(); ++i) {
+      pd.push_back((propagate_mask >> i) & 1);
+      ac.push_back((accum_mask >> i) & 1);
+    }
+    f->backward(in, out, pd, ac);
   });
 }
 }

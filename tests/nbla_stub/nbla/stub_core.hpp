@@ -58,6 +58,7 @@ inline string format_string(const char *fmt, ...) {
 class Variable {
   Shape_t shape_;
   void *ptr_ = nullptr;
+  void *grad_ = nullptr;  // the gradient array of the variable (caller-provided, may be null)
   std::function<void *(size_t)> alloc_;  // used by reshape() of variables the functions own
 
 public:
@@ -78,6 +79,9 @@ public:
     shape_ = s;
     if (!ptr_) ptr_ = default_alloc()((size_t)size() * sizeof(float));
   }
+  void set_grad(void *g) { grad_ = g; }
+  template <typename T> const T *get_grad_pointer(const Context &) { return static_cast<const T *>(grad_); }
+  template <typename T> T *cast_grad_and_get_pointer(const Context &, bool = false) { return static_cast<T *>(grad_); }
   template <typename T> const T *get_data_pointer(const Context &) { return static_cast<const T *>(ptr_); }
   template <typename T> T *cast_data_and_get_pointer(const Context &, bool = false) { return static_cast<T *>(ptr_); }
 };

@@ -46,6 +46,7 @@ def test_registration_and_names(harness):
 
 
 def test_backward_raises_not_implemented(harness):
+    """MinMaxQuantize (like BatchNormalization and the fused object) has no backward here."""
     rc = harness.stub_backward_is_refused(0)
     assert rc == 100 + 1, rc  # error_code::not_implemented
     assert b"forward pass only" in harness.stub_last_error()
@@ -212,3 +213,64 @@ def test_fused_function_object(harness, oracle, cuda_device, half):
             want = oracle.to_f16_result(want).astype(np.float32)
         got = y.float().cpu().numpy() if half else y.cpu().numpy()
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (stride, kind, half)
+
+
+@pytest.mark.gpu
+def test_backward_of_the_registered_classes(harness, oracle, cuda_device):
+    """backward_impl of FixedPointQuantizeCuda, Pow2QuantizeCuda and DepthwiseConvolutionCuda with
+    the reference's propagate_down / accum flags, against the CPU oracle."""
+    import torch
+    rng = np.random.default_rng(13)
+    dev_index = cuda_device.index or 0
+    to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(cuda_device)
+    x = (rng.standard_normal(5000) * 5).astype(np.float32)
+    dy = rng.standard_normal(5000).astype(np.float32)
+    old = rng.standard_normal(5000).astype(np.float32)
+    tx, tdy = to(x), to(dy)
+    for accum in (0, 1):
+        dx = to(old)
+        rc = harness.stub_quant_bwd(0, 0, dev_index, x.size, _p(tx), _p(tdy), _p(dx), 1, 8, ctypes.c_float(2.0 ** -4), 0, 0,
+                                    1, accum, 1)
+        assert rc == 0, harness.stub_last_error()
+        torch.cuda.synchronize()
+        np.testing.assert_array_equal(dx.cpu().numpy(), oracle.fpq_bwd(x, dy, old if accum else None, True, 8, 2.0 ** -4, True))
+        dx = to(old)
+        rc = harness.stub_quant_bwd(1, 0, dev_index, x.size, _p(tx), _p(tdy), _p(dx), 1, 8, ctypes.c_float(0), 1, 1, 1,
+                                    accum, 1)
+        assert rc == 0, harness.stub_last_error()
+        torch.cuda.synchronize()
+        np.testing.assert_array_equal(dx.cpu().numpy(), oracle.pow2q_bwd(x, dy, old if accum else None, True, True, 8, 1, True))
+    # propagate_down false: the gradient is not touched
+    dx = to(old)
+    assert harness.stub_quant_bwd(0, 0, dev_index, x.size, _p(tx), _p(tdy), _p(dx), 1, 8, ctypes.c_float(2.0 ** -4), 0, 0, 1,
+                                  0, 0) == 0
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(dx.cpu().numpy(), old)
+
+    n, c, hw = 3, 12, 14
+    xc = rng.standard_normal((n, c, hw, hw)).astype(np.float32)
+    w = (rng.standard_normal((c, 3, 3)) / 3).astype(np.float32)
+    b = rng.standard_normal(c).astype(np.float32)
+    dyc = rng.standard_normal((n, c, 7, 7)).astype(np.float32)
+    wdx, wdw, wdb = oracle.dwconv_bwd(xc, w, dyc, (2, 2), (1, 1))
+    txc, tw, tb, tdyc = to(xc), to(w), to(b), to(dyc)
+    dx, dw, db = torch.full_like(txc, 9.0), torch.full_like(tw, 9.0), torch.full_like(tb, 9.0)
+    rc = harness.stub_dwconv_bwd(0, dev_index, _shape(txc), _shape(tw), 4, _p(txc), _p(tw), _p(tb), _p(tdyc), _p(dx), _p(dw),
+                                 _p(db), 1, 2, 1, 1, 0b111, 0)
+    assert rc == 0, harness.stub_last_error()
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(dx.cpu().numpy(), wdx)
+    np.testing.assert_allclose(dw.cpu().numpy(), wdw, rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(db.cpu().numpy(), wdb, rtol=1e-4, atol=1e-4)
+    # only the weights, accumulated
+    dx2, dw2 = torch.full_like(txc, 9.0), torch.ones_like(tw)
+    rc = harness.stub_dwconv_bwd(0, dev_index, _shape(txc), _shape(tw), 4, _p(txc), _p(tw), _p(tb), _p(tdyc), _p(dx2), _p(dw2),
+                                 _p(db), 1, 2, 1, 1, 0b010, 0b010)
+    assert rc == 0, harness.stub_last_error()
+    torch.cuda.synchronize()
+    assert float(dx2.min()) == 9.0 and float(dx2.max()) == 9.0
+    np.testing.assert_allclose(dw2.cpu().numpy(), wdw + 1.0, rtol=1e-4, atol=1e-4)
+    # half: the convolution's backward is not implemented and says so
+    rc = harness.stub_dwconv_bwd(1, dev_index, _shape(txc), _shape(tw), 4, _p(txc), _p(tw), _p(tb), _p(tdyc), _p(dx), _p(dw),
+                                 _p(db), 1, 2, 1, 1, 0b111, 0)
+    assert rc >= 100 and b"DWBNQ_F32" in harness.stub_last_error()

@@ -89,3 +89,35 @@ def test_minmax_against_its_definition(oracle):
         yc, xc = y[:, ch].astype(np.float64), x[:, ch].astype(np.float64)
         assert np.unique(y[:, ch]).size <= 256
         assert np.abs(yc - xc).max() <= scale[ch] * (1.0 + 1e-4)
+
+
+def test_backward_restatements_against_autograd(oracle):
+    """The oracle's DepthwiseConvolution gradients against PyTorch's autograd of the grouped
+    convolution in fp64, and the STE rules against their definitions."""
+    import torch
+    rng = np.random.default_rng(8)
+    for (n, c, h, w_, k, s, p, dil, mult) in ((2, 4, 9, 11, 3, 1, 1, 1, 1), (2, 3, 12, 12, 5, 2, 2, 1, 2),
+                                              (1, 2, 10, 10, 3, 2, 0, 2, 1)):
+        x = rng.standard_normal((n, c, h, w_)).astype(np.float32)
+        w = rng.standard_normal((c * mult, k, k)).astype(np.float32)
+        tx = torch.tensor(x, dtype=torch.float64, requires_grad=True)
+        tw = torch.tensor(w, dtype=torch.float64, requires_grad=True)
+        tb = torch.zeros(c * mult, dtype=torch.float64, requires_grad=True)
+        y = torch.nn.functional.conv2d(tx, tw[:, None], tb, stride=s, padding=p, dilation=dil, groups=c)
+        dy = rng.standard_normal(tuple(y.shape)).astype(np.float32)
+        y.backward(torch.tensor(dy, dtype=torch.float64))
+        dx, dw, db = oracle.dwconv_bwd(x, w, dy, (s, s), (p, p), (dil, dil), mult)
+        np.testing.assert_allclose(dx, tx.grad.numpy(), rtol=2e-5, atol=2e-5)
+        np.testing.assert_allclose(dw, tw.grad.numpy(), rtol=2e-5, atol=2e-5)
+        np.testing.assert_allclose(db, tb.grad.numpy(), rtol=2e-5, atol=2e-5)
+    x = np.array([0.0, 8.5, -8.5, 1.0, -1.0, 7.9375, np.nan], np.float32)
+    dy = np.arange(1, 8, dtype=np.float32)
+    # FixedPointQuantize(sign, n = 8, 2^-4): range [-7.9375, 7.9375]; clipped elements get 0
+    np.testing.assert_array_equal(oracle.fpq_bwd(x, dy, None, True, 8, 2.0 ** -4, True), [1, 0, 0, 4, 5, 6, 7])
+    np.testing.assert_array_equal(oracle.fpq_bwd(x, dy, None, True, 8, 2.0 ** -4, False), dy)
+    np.testing.assert_array_equal(oracle.fpq_bwd(x, dy, np.ones(7, np.float32), True, 8, 2.0 ** -4, True),
+                                  [2, 1, 1, 5, 6, 7, 8])
+    # Pow2Quantize(sign, with_zero, n = 8, m = 1): p_max = 2; 3.0 rounds to 4 > 2 -> 0; unsigned: negatives -> 0
+    xp = np.array([3.0, 2.5, -3.0, -0.3, 0.0], np.float32)
+    np.testing.assert_array_equal(oracle.pow2q_bwd(xp, dy[:5], None, True, True, 8, 1, True), [0, 2, 0, 4, 5])
+    np.testing.assert_array_equal(oracle.pow2q_bwd(xp, dy[:5], None, False, True, 8, 1, True), [0, 2, 0, 0, 5])
