@@ -21,6 +21,9 @@
 //    gradients are compared within a tolerance, not bit for bit.
 // All kernels are bandwidth-shaped: 16-byte accesses where the layout allows, grids sized from
 // the SM count.
+#include <cstdlib>
+#include <cstring>
+
 #include "dwbnq_internal.h"
 
 namespace dwbnq {
@@ -37,6 +40,16 @@ unsigned int grid_for(long long items, int per_sm) {
   return (unsigned int)blocks;
 }
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) % 16) == 0; }
+
+// DWBNQ_BWD_INPUT_DIRECT=1 keeps every input gradient on the direct kernel (the reference's
+// summation order, bit-identical to the CPU loop); read once.
+bool bwd_input_by_forward_enabled() {
+  static const bool on = [] {
+    const char *e = std::getenv("DWBNQ_BWD_INPUT_DIRECT");
+    return !(e && e[0] == '1');
+  }();
+  return on;
+}
 
 // ---- straight-through backward of the quantizers ------------------------------------------
 // MODE 0: pass-through (ste_fine_grained = false); 1: FixedPointQuantize mask; 2: Pow2 mask.
@@ -117,61 +130,93 @@ struct BwdArgs {
   int kh, kw, sh, sw, ph, pw, dh, dw_, mult;
 };
 
-template <typename T, bool ACCUM>
+// One thread per input-gradient element, in the reference's order (ky outer, kx inner,
+// multiplier innermost). K > 0: square K x K kernel, multiplier 1, no dilation, stride S (1 or
+// 2), everything about the taps known at compile time (no division: a tap lands on an output
+// when iy + p - ky is a non-negative multiple of S inside the output). K == 0: any geometry.
+// A CTA owns a run of consecutive elements; the plane and the position inside it come from one
+// 64-bit division per CTA and two 32-bit ones per element.
+template <typename T, int K, int S, bool ACCUM>
 __global__ void __launch_bounds__(kThreads)
-    dwconv_bwd_input_kernel(const BwdArgs a, const long long total) {
+    dwconv_bwd_input_kernel(const BwdArgs a, const long long total, const int per_cta) {
   const T *w = static_cast<const T *>(a.w);
   const T *dy = static_cast<const T *>(a.dy);
   T *dx = static_cast<T *>(a.dx);
   pdl_launch_dependents();
   pdl_wait_for_predecessor();
-  const long long step = (long long)gridDim.x * blockDim.x;
-  const long long plane_out = (long long)a.Ho * a.Wo;
-  for (long long o = (long long)blockIdx.x * blockDim.x + threadIdx.x; o < total; o += step) {
-    const int ix = (int)(o % a.W);
-    long long t = o / a.W;
-    const int iy = (int)(t % a.H);
-    t /= a.H;
-    const int c = (int)(t % a.C);
-    const long long n = t / a.C;
-    const int oc0 = c * a.mult;
-    const T *dyp = dy + (n * a.OC + oc0) * plane_out;
-    const T *wp = w + (long long)oc0 * a.kh * a.kw;
-    float value = 0.0f;
-    for (int ky = 0; ky < a.kh; ++ky) {
-      const int ty = iy + a.ph - ky * a.dh;
-      // C division truncates toward zero: the reference tests (t - (t / s) * s == 0) and then
-      // the range, so a negative multiple of the stride passes the first test and fails the second
-      const int oy = ty / a.sh;
-      const bool row_ok = (ty - oy * a.sh == 0) && oy >= 0 && oy < a.Ho;
-      for (int kx = 0; kx < a.kw; ++kx) {
-        const int tx = ix + a.pw - kx * a.dw_;
-        const int ox = tx / a.sw;
-        if (row_ok && (tx - ox * a.sw == 0) && ox >= 0 && ox < a.Wo) {
-          const long long off = (long long)oy * a.Wo + ox;
-          const int wi = ky * a.kw + kx;
-          for (int m = 0; m < a.mult; ++m)
-            value = __fadd_rn(value, __fmul_rn(Elem<T>::to_f32(wp[m * a.kh * a.kw + wi]),
-                                               Elem<T>::to_f32(dyp[m * plane_out + off])));
+  const int HW = a.H * a.W;
+  const int plane_out = a.Ho * a.Wo;
+  for (long long base = (long long)blockIdx.x * per_cta; base < total; base += (long long)gridDim.x * per_cta) {
+    const long long plane0 = base / HW;
+    const int rem0 = (int)(base - plane0 * HW);
+    const int n_here = (int)(total - base < per_cta ? total - base : per_cta);
+    for (int t = threadIdx.x; t < n_here; t += kThreads) {
+      const int idx = rem0 + t;
+      const int dp = idx / HW;
+      const int e = idx - dp * HW;
+      const int iy = e / a.W, ix = e - iy * a.W;
+      const long long plane = plane0 + dp;  // = n * C + c
+      const int c = (int)(plane % a.C);
+      float value = 0.0f;
+      if (K > 0) {
+        const T *dyp = dy + plane * plane_out;  // multiplier 1: output plane index = input plane index
+        const T *wp = w + (long long)c * K * K;
+#pragma unroll
+        for (int ky = 0; ky < K; ++ky) {
+          const int ty = iy + a.ph - ky;
+          const int oy = S == 1 ? ty : ty >> 1;
+          const bool row_ok = (S == 1 || (ty & 1) == 0) && (unsigned int)oy < (unsigned int)a.Ho;
+#pragma unroll
+          for (int kx = 0; kx < K; ++kx) {
+            const int tx = ix + a.pw - kx;
+            const int ox = S == 1 ? tx : tx >> 1;
+            if (row_ok && (S == 1 || (tx & 1) == 0) && (unsigned int)ox < (unsigned int)a.Wo)
+              value = __fadd_rn(value, __fmul_rn(Elem<T>::to_f32(wp[ky * K + kx]), Elem<T>::to_f32(dyp[oy * a.Wo + ox])));
+          }
+        }
+      } else {
+        const long long n = plane / a.C;
+        const int oc0 = c * a.mult;
+        const T *dyp = dy + (n * a.OC + oc0) * plane_out;
+        const T *wp = w + (long long)oc0 * a.kh * a.kw;
+        for (int ky = 0; ky < a.kh; ++ky) {
+          const int ty = iy + a.ph - ky * a.dh;
+          // C division truncates toward zero: the reference tests (t - (t / s) * s == 0) and then
+          // the range, so a negative multiple of the stride passes the first test and fails the second
+          const int oy = ty / a.sh;
+          const bool row_ok = (ty - oy * a.sh == 0) && oy >= 0 && oy < a.Ho;
+          for (int kx = 0; kx < a.kw; ++kx) {
+            const int tx = ix + a.pw - kx * a.dw_;
+            const int ox = tx / a.sw;
+            if (row_ok && (tx - ox * a.sw == 0) && ox >= 0 && ox < a.Wo) {
+              const int off = oy * a.Wo + ox;
+              const int wi = ky * a.kw + kx;
+              for (int m = 0; m < a.mult; ++m)
+                value = __fadd_rn(value, __fmul_rn(Elem<T>::to_f32(wp[m * a.kh * a.kw + wi]),
+                                                   Elem<T>::to_f32(dyp[(long long)m * plane_out + off])));
+            }
+          }
         }
       }
+      const long long o = base + t;
+      const float old = ACCUM ? Elem<T>::to_f32(dx[o]) : 0.0f;
+      dx[o] = Elem<T>::from_f32(__fadd_rn(old, value));
     }
-    const float old = ACCUM ? Elem<T>::to_f32(dx[o]) : 0.0f;
-    dx[o] = Elem<T>::from_f32(__fadd_rn(old, value));
   }
 }
 
 // ---- DepthwiseConvolution: weight and bias gradients ---------------------------------------------
-// CTA = one output channel x one slice of the batch. A thread walks over output positions of
-// its slice, keeps dy in a register and accumulates x * dy for each of the KK taps in
-// registers (x re-read through L1: neighbouring taps hit the same lines), plus dy for the
-// bias; warp shuffles and shared memory reduce the CTA's partial sums, which are then added to
-// the gradients with one atomic per value. The gradients must be zero (or hold the value to
+// CTA = one output channel x one slice of the batch; a warp takes one image of the slice at a
+// time and its lanes walk over the output positions of that plane 32 at a time, so dy and the
+// K x K input values under each position are read as coalesced rows (the nine or twenty-five
+// shifted reads of a row hit L1). Each lane accumulates x * dy for every tap in registers, plus
+// dy for the bias. Warp shuffles and shared memory reduce the CTA's partial sums, which are added to the
+// gradients with one atomic per value: the gradients must be zero (or hold the value to
 // accumulate onto) when the kernel starts.
-template <typename T, int KH, int KW>
-__global__ void __launch_bounds__(kThreads)
+template <typename T, int K, int S>
+__global__ void __launch_bounds__(kThreads, K == 3 ? 4 : 2)
     dwconv_bwd_weights_kernel(const BwdArgs a, const int slices) {
-  constexpr int KK = KH * KW;
+  constexpr int KK = K * K;
   __shared__ float red[kThreads / 32][KK + 1];
   const T *x = static_cast<const T *>(a.x);
   const T *dy = static_cast<const T *>(a.dy);
@@ -180,8 +225,9 @@ __global__ void __launch_bounds__(kThreads)
   const int oc = blockIdx.x / slices;
   const int slice = blockIdx.x % slices;
   const int ic = oc / a.mult;
-  const long long plane_out = (long long)a.Ho * a.Wo;
-  const long long plane_in = (long long)a.H * a.W;
+  const int plane_out = a.Ho * a.Wo;
+  const int plane_in = a.H * a.W;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // images [n0, n1) of this slice
   const long long per = (a.n + slices - 1) / slices;
   const long long n0 = (long long)slice * per;
@@ -190,23 +236,43 @@ __global__ void __launch_bounds__(kThreads)
 #pragma unroll
   for (int i = 0; i < KK; ++i) acc[i] = 0.0f;
   float bsum = 0.0f;
-  const long long items = (n1 > n0 ? n1 - n0 : 0) * plane_out;
-  for (long long it = threadIdx.x; it < items; it += kThreads) {
-    const long long n = n0 + it / plane_out;
-    const int pos = (int)(it % plane_out);
-    const int oy = pos / a.Wo, ox = pos - oy * a.Wo;
-    const float g = Elem<T>::to_f32(dy[(n * a.OC + oc) * plane_out + pos]);
+  for (long long n = n0 + warp; n < n1; n += kThreads / 32) {
+    const T *dyp = dy + (n * a.OC + oc) * plane_out;
     const T *xp = x + (n * a.C + ic) * plane_in;
-    bsum += g;
+    // Two positions per trip, every load unconditional (row and column clamped into the image,
+    // the value replaced by zero where the tap lies outside): no branch stands between the
+    // loads of a trip, so they are all in flight together.
+    for (int pos = lane; pos < plane_out; pos += 64) {
+      float g[2], xv[2][KK];
 #pragma unroll
-    for (int i = 0; i < KK; ++i) {
-      const int ky = i / KW, kx = i - ky * KW;
-      const int iy = oy * a.sh + ky * a.dh - a.ph;
-      const int ix = ox * a.sw + kx * a.dw_ - a.pw;
-      if (iy >= 0 && iy < a.H && ix >= 0 && ix < a.W) acc[i] += Elem<T>::to_f32(xp[(long long)iy * a.W + ix]) * g;
+      for (int u = 0; u < 2; ++u) {
+        const int pu = pos + 32 * u;
+        const bool live = pu < plane_out;
+        const int pc = live ? pu : pos;
+        const int oy = pc / a.Wo, ox = pc - oy * a.Wo;
+        g[u] = live ? Elem<T>::to_f32(dyp[pc]) : 0.0f;
+        const int iy0 = oy * S - a.ph, ix0 = ox * S - a.pw;
+#pragma unroll
+        for (int ky = 0; ky < K; ++ky) {
+          const int iy = iy0 + ky;
+          const bool row_in = (unsigned int)iy < (unsigned int)a.H;
+          const T *xr = xp + min(max(iy, 0), a.H - 1) * a.W;
+#pragma unroll
+          for (int kx = 0; kx < K; ++kx) {
+            const int ix = ix0 + kx;
+            const float v = Elem<T>::to_f32(xr[min(max(ix, 0), a.W - 1)]);
+            xv[u][ky * K + kx] = (row_in && (unsigned int)ix < (unsigned int)a.W) ? v : 0.0f;
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        bsum += g[u];
+#pragma unroll
+        for (int i = 0; i < KK; ++i) acc[i] = fmaf(xv[u][i], g[u], acc[i]);
+      }
     }
   }
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
   for (int i = 0; i <= KK; ++i) {
     float v = i < KK ? acc[i < KK ? i : 0] : bsum;
@@ -320,12 +386,61 @@ int launch_dwconv_backward(const dwbnq_conv_desc &d, int ho, int wo, const void 
   a.dw_ = d.dil_w;
   a.mult = d.multiplier;
   cudaError_t e = cudaSuccess;
+  // Stride 1, no dilation, multiplier 1, pad = (k - 1) / 2 on an odd square kernel, overwrite:
+  // the input gradient IS the forward convolution of dy with the kernel rotated by 180
+  // degrees (same padding), so it runs on the fused family's kernels (no bias, no BN, no
+  // quantizer) with the taps read back to front - at their speed. Its sum runs over the taps
+  // in the forward kernels' order, the reverse of the reference loop's: equal within rounding,
+  // not bit for bit. Every other case takes the direct kernel below, in the reference's order.
+  if (dx && !(accum_mask & 1) && d.stride_h == 1 && d.stride_w == 1 && d.dil_h == 1 && d.dil_w == 1 &&
+      d.multiplier == 1 && d.kh == d.kw && (d.kh % 2) == 1 && d.pad_h == d.kh / 2 && d.pad_w == d.kw / 2 && d.n > 0 &&
+      bwd_input_by_forward_enabled()) {
+    dwbnq_conv_desc g = d;  // dy has the shape of x here (same padding, stride 1)
+    FusedArgs fa;
+    std::memset(&fa, 0, sizeof(fa));
+    fa.x = dy;
+    fa.w = w;
+    fa.y = dx;
+    fa.n = d.n;
+    fa.C = fa.OC = d.c;
+    fa.H = fa.Ho = d.h;
+    fa.W = fa.Wo = d.w;
+    fa.kh = d.kh;
+    fa.kw = d.kw;
+    fa.sh = fa.sw = fa.dh = fa.dw = fa.mult = 1;
+    fa.ph = d.pad_h;
+    fa.pw = d.pad_w;
+    fa.w_flip = 1;
+    int dev = 0;
+    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return fail_cuda(e, "cudaGetDevice");
+    const int st = launch_fused(g, fa, QM_NONE, dev, stream);
+    if (st != DWBNQ_OK) return st;
+    dx = nullptr;  // done
+  }
   if (dx) {
     const long long total = d.n * (long long)d.c * d.h * d.w;
-    const dim3 grid(grid_for(total, 32)), block(kThreads);
+    const int per_cta = kThreads * 8;
+    long long ctas = (total + per_cta - 1) / per_cta;
+    const long long cap = (long long)sm_count(-1) * 32;
+    if (ctas > cap) ctas = cap;
+    const dim3 grid((unsigned int)(ctas < 1 ? 1 : ctas)), block(kThreads);
     const bool acc = (accum_mask & 1) != 0;
-    e = acc ? launch_pdl(dwconv_bwd_input_kernel<float, true>, grid, block, 0, stream, a, total)
-            : launch_pdl(dwconv_bwd_input_kernel<float, false>, grid, block, 0, stream, a, total);
+    const bool simple = d.kh == d.kw && d.dil_h == 1 && d.dil_w == 1 && d.multiplier == 1 && d.stride_h == d.stride_w &&
+                        (long long)d.h * d.w < 0x40000000LL && (long long)ho * wo < 0x40000000LL;
+    const int key = !simple ? 0 : (d.kh == 3 ? 30 : d.kh == 5 ? 50 : 0) + (d.stride_h == 1 ? 1 : d.stride_h == 2 ? 2 : -100);
+#define DWBNQ_BIN(KV, SV)                                                                                       \
+  e = acc ? launch_pdl(dwconv_bwd_input_kernel<float, KV, SV, true>, grid, block, 0, stream, a, total, per_cta) \
+          : launch_pdl(dwconv_bwd_input_kernel<float, KV, SV, false>, grid, block, 0, stream, a, total, per_cta)
+    if ((long long)d.h * d.w >= 0x40000000LL || (long long)ho * wo >= 0x40000000LL)
+      return fail(DWBNQ_ERR_UNSUPPORTED, "DepthwiseConvolution backward: planes of 2^30 elements or more");
+    switch (key) {
+      case 31: DWBNQ_BIN(3, 1); break;
+      case 32: DWBNQ_BIN(3, 2); break;
+      case 51: DWBNQ_BIN(5, 1); break;
+      case 52: DWBNQ_BIN(5, 2); break;
+      default: DWBNQ_BIN(0, 1); break;
+    }
+#undef DWBNQ_BIN
     if (e != cudaSuccess) return fail_cuda(e, "dwconv_bwd_input_kernel launch");
   }
   if (dw || db) {
@@ -340,15 +455,22 @@ int launch_dwconv_backward(const dwbnq_conv_desc &d, int ho, int wo, const void 
       zero_f32_kernel<<<grid_for(a.OC, 4), kThreads, 0, stream>>>(static_cast<float *>(db), a.OC);
       if ((e = cudaGetLastError()) != cudaSuccess) return fail_cuda(e, "zero_f32_kernel launch");
     }
-    const bool k3 = d.kh == 3 && d.kw == 3, k5 = d.kh == 5 && d.kw == 5;
-    if (k3 || k5) {
+    const bool fast = d.kh == d.kw && (d.kh == 3 || d.kh == 5) && d.stride_h == d.stride_w &&
+                      (d.stride_h == 1 || d.stride_h == 2) && d.dil_h == 1 && d.dil_w == 1 &&
+                      (long long)d.h * d.w < 0x40000000LL && d.n > 0;
+    if (fast) {
       // enough CTAs for eight per SM; a slice is at least one image
       long long slices = ((long long)sm_count(-1) * 8 + a.OC - 1) / a.OC;
-      if (slices > d.n) slices = d.n;
+      if (slices > (d.n + 7) / 8) slices = (d.n + 7) / 8;  // a warp per image: eight images keep a CTA's warps busy
       if (slices < 1) slices = 1;
       const dim3 grid((unsigned int)(a.OC * slices)), block(kThreads);
-      e = k3 ? launch_pdl(dwconv_bwd_weights_kernel<float, 3, 3>, grid, block, 0, stream, a, (int)slices)
-             : launch_pdl(dwconv_bwd_weights_kernel<float, 5, 5>, grid, block, 0, stream, a, (int)slices);
+      const int key = d.kh * 10 + d.stride_h;
+      if (key == 31) e = launch_pdl(dwconv_bwd_weights_kernel<float, 3, 1>, grid, block, 0, stream, a, (int)slices);
+      else if (key == 32) e = launch_pdl(dwconv_bwd_weights_kernel<float, 3, 2>, grid, block, 0, stream, a, (int)slices);
+      else if (key == 51) e = launch_pdl(dwconv_bwd_weights_kernel<float, 5, 1>, grid, block, 0, stream, a, (int)slices);
+      else e = launch_pdl(dwconv_bwd_weights_kernel<float, 5, 2>, grid, block, 0, stream, a, (int)slices);
+    } else if (d.n == 0) {
+      e = cudaSuccess;  // nothing to add to the (zeroed or kept) gradients
     } else {
       const dim3 grid((unsigned int)(a.OC * (kk + 1))), block(kThreads);
       dwconv_bwd_weights_any_kernel<float><<<grid, block, 0, stream>>>(a);

@@ -48,7 +48,13 @@ struct FusedArgs {
   int code8;
   int code_in_signed;
   float code_in_delta;
+  // The taps are read back to front, w[kh*kw - 1 - i] for tap i: the convolution with the
+  // kernel rotated by 180 degrees, which is the input gradient of a stride-1 convolution.
+  int w_flip;
 };
+
+// Index of tap i of kk in the weight array.
+__device__ __forceinline__ int tap_index(const FusedArgs &a, int i, int kk) { return a.w_flip ? kk - 1 - i : i; }
 
 // One input element as fp32: a T value, or (8-bit storage) a code times its step.
 template <typename T>
@@ -109,7 +115,7 @@ __device__ __forceinline__ float conv_point(const FusedArgs &a, long long n, int
       const int ix = ox * a.sw + kx * a.dw - a.pw;
       if (iy >= 0 && iy < a.H && ix >= 0 && ix < a.W) {
         const float xv = load_x<T>(a, a.x, xbase + (long long)iy * a.W + ix);
-        const float wv = Elem<T>::to_f32(wp[ky * a.kw + kx]);
+        const float wv = Elem<T>::to_f32(wp[tap_index(a, ky * a.kw + kx, a.kh * a.kw)]);
         acc = __fadd_rn(acc, __fmul_rn(wv, xv));
       }
     }
@@ -453,7 +459,7 @@ __global__ void __launch_bounds__(256, tiled_min_blocks(sizeof(T), K, MODE))
     bool exact = false;
 #pragma unroll
     for (int i = 0; i < PL::KK; ++i) {
-      const float wv = Elem<T>::to_f32(w[ch * PL::KK + i]);
+      const float wv = Elem<T>::to_f32(w[ch * PL::KK + tap_index(a, i, PL::KK)]);
       rec[2 * i] = wv;
       rec[2 * i + 1] = wv;
       exact = exact || !(fabsf(wv) <= 3.402823466e38f);

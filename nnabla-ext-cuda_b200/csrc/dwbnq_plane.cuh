@@ -344,7 +344,7 @@ __global__ void __launch_bounds__(32, 16)
     const T *w = static_cast<const T *>(a.w) + (long long)ch * 9;
 #pragma unroll
     for (int i = 0; i < 9; ++i) {
-      const float wv = Elem<T>::to_f32(w[i]);
+      const float wv = Elem<T>::to_f32(w[tap_index(a, i, 9)]);
       exact = exact || !(fabsf(wv) <= 3.402823466e38f);
       w2[i] = splat2(wv);
       pin(w2[i]);
@@ -607,14 +607,14 @@ __global__ void __launch_bounds__(32, K == 5 ? 12 : 16)
     if (W_SMEM) {
       // every thread checks all weights of its plane; the plane's threads share the stores
       for (int i = 0; i < KK; ++i) {
-        const float wv = Elem<T>::to_f32(w[i]);
+        const float wv = Elem<T>::to_f32(w[tap_index(a, i, KK)]);
         exact = exact || !(fabsf(wv) <= 3.402823466e38f);
         if (i % TPP == lane % TPP) wsm[pl * KK + i] = splat2(wv);
       }
     } else {
 #pragma unroll
       for (int i = 0; i < KK; ++i) {
-        const float wv = Elem<T>::to_f32(w[i]);
+        const float wv = Elem<T>::to_f32(w[tap_index(a, i, KK)]);
         exact = exact || !(fabsf(wv) <= 3.402823466e38f);
         w2[i] = splat2(wv);
         pin(w2[i]);
@@ -887,7 +887,7 @@ __global__ void __launch_bounds__(32, 16)
     const T *w1 = static_cast<const T *>(a.w) + (long long)ch1 * 9;
 #pragma unroll
     for (int i = 0; i < 9; ++i) {
-      w2[i] = pack2(Elem<T>::to_f32(w0[i]), Elem<T>::to_f32(w1[i]));
+      w2[i] = pack2(Elem<T>::to_f32(w0[tap_index(a, i, 9)]), Elem<T>::to_f32(w1[tap_index(a, i, 9)]));
       pin(w2[i]);
     }
   }
@@ -1115,7 +1115,7 @@ __global__ void __launch_bounds__(32, 7)
     const T *w = static_cast<const T *>(a.w) + (long long)ch * 9;
 #pragma unroll
     for (int i = 0; i < 9; ++i) {
-      wr[i] = Elem<T>::to_f32(w[i]);
+      wr[i] = Elem<T>::to_f32(w[tap_index(a, i, 9)]);
       exact = exact || !(fabsf(wr[i]) <= 3.402823466e38f);
       pin(wr[i]);
     }

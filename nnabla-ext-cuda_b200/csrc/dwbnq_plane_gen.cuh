@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(32, 16)
     const T *w = static_cast<const T *>(a.w) + (long long)ch * 9;
 #pragma unroll
     for (int i = 0; i < 9; ++i) {
-      const float wv = Elem<T>::to_f32(w[i]);
+      const float wv = Elem<T>::to_f32(w[tap_index(a, i, 9)]);
       exact = exact || !(fabsf(wv) <= 3.402823466e38f);
       w2[i] = splat2(wv);
       pin(w2[i]);

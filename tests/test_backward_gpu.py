@@ -1,8 +1,11 @@
 """Training side through the C ABI against the CPU oracle: the straight-through backward of
-FixedPointQuantize and Pow2Quantize and DepthwiseConvolution's input gradient are compared bit
-for bit (same operations, same order); the weight and bias gradients, whose fp32 sum has no
-fixed association (block reduction + atomic adds here, a block tree in the reference), within
-a tolerance scaled by the sum of the magnitudes of the terms."""
+FixedPointQuantize and Pow2Quantize and the direct input-gradient kernel of
+DepthwiseConvolution are compared bit for bit (same operations, same order). Two things are
+compared within a tolerance scaled by the sum of the magnitudes of the terms: the weight and
+bias gradients, whose fp32 sum has no fixed association (block reduction + atomic adds here, a
+block tree in the reference), and the input gradient of a stride-1 "same" convolution when it
+is overwritten, which runs as the forward kernels on the rotated kernel (taps summed in the
+forward order, the reverse of the reference loop's)."""
 import numpy as np
 import pytest
 import torch
@@ -11,6 +14,10 @@ from dwbnq import _lib as L
 from dwbnq import ops
 
 pytestmark = pytest.mark.gpu
+
+import os  # noqa: E402
+
+ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
 
 
 def dev(a, device):
@@ -22,6 +29,18 @@ def same_bits(got, want, what):
     nan = np.isnan(want)
     assert np.array_equal(np.isnan(got), nan), what
     assert np.array_equal(got.view(np.uint32)[~nan], want.view(np.uint32)[~nan]), what
+
+
+def by_forward(k, s, p, dil, mult):
+    """The case dwbnq_dwconv_bwd hands to the forward kernels (when dx is overwritten)."""
+    return s == 1 and dil == 1 and mult == 1 and k % 2 == 1 and p == k // 2
+
+
+def check_dx(got, want, mag, exact, what):
+    if exact:
+        same_bits(got, want, what)
+    else:
+        assert np.all(np.abs(got - want) <= 2e-6 * mag + 1e-30), what
 
 
 def _x_for_quantizers(rng, n):
@@ -94,9 +113,9 @@ def test_depthwise_convolution_backward(oracle, cuda_device, geom):
     tx, tw, tdy = dev(x, cuda_device), dev(w, cuda_device), dev(dy, cuda_device)
     dx, dw, db = ops.depthwise_convolution_backward(tx, tw, tdy, 1, (p, p), (s, s), (dil, dil), mult)
     torch.cuda.synchronize()
-    same_bits(dx.cpu().numpy(), wdx, "dx %s" % (geom,))
     # tolerance of a sum of N rounded products: a few ulps of the sum of magnitudes
-    mag_w = oracle.dwconv_bwd(np.abs(x), np.abs(w), np.abs(dy), (s, s), (p, p), (dil, dil), mult)[1]
+    mag_x, mag_w, _ = oracle.dwconv_bwd(np.abs(x), np.abs(w), np.abs(dy), (s, s), (p, p), (dil, dil), mult)
+    check_dx(dx.cpu().numpy(), wdx, mag_x, not by_forward(k, s, p, dil, mult), "dx %s" % (geom,))
     assert np.all(np.abs(dw.cpu().numpy() - wdw) <= 4e-6 * mag_w + 1e-30), geom
     assert np.all(np.abs(db.cpu().numpy() - wdb) <= 4e-6 * np.abs(dy).sum(axis=(0, 2, 3)) + 1e-30), geom
     # accumulation onto existing gradients, and gradients that are not asked for
@@ -111,7 +130,7 @@ def test_depthwise_convolution_backward(oracle, cuda_device, geom):
     only_dx = ops.depthwise_convolution_backward(tx, tw, tdy, 1, (p, p), (s, s), (dil, dil), mult,
                                                  need=(True, False, False))
     assert only_dx[1] is None and only_dx[2] is None
-    same_bits(only_dx[0].cpu().numpy(), wdx, "dx alone")
+    check_dx(only_dx[0].cpu().numpy(), wdx, mag_x, not by_forward(k, s, p, dil, mult), "dx alone")
     only_db = ops.depthwise_convolution_backward(tx, tw, tdy, 1, (p, p), (s, s), (dil, dil), mult,
                                                  need=(False, False, True))
     assert np.all(np.abs(only_db[2].cpu().numpy() - wdb) <= 4e-6 * np.abs(dy).sum(axis=(0, 2, 3)) + 1e-30)
@@ -129,11 +148,38 @@ def test_depthwise_convolution_backward_cfg1_layer_sizes(oracle, cuda_device):
         wdx, wdw, wdb = oracle.dwconv_bwd(x, w, dy, (s, s), (1, 1), nthreads=oracle.max_threads())
         dx, dw, db = ops.depthwise_convolution_backward(dev(x, cuda_device), dev(w, cuda_device), dev(dy, cuda_device),
                                                         1, (1, 1), (s, s))
-        same_bits(dx.cpu().numpy(), wdx, "dx cfg1 %d" % hw)
+        mag_x = oracle.dwconv_bwd(np.abs(x), np.abs(w), np.abs(dy), (s, s), (1, 1), nthreads=oracle.max_threads())[0]
+        check_dx(dx.cpu().numpy(), wdx, mag_x, s != 1, "dx cfg1 %d" % hw)
         scale = np.sqrt(16 * ho * ho)  # random signs: the sum of magnitudes grows like N, the error like sqrt(N)
         assert np.all(np.abs(dw.cpu().numpy() - wdw) <= 2e-6 * 16 * ho * ho / scale + 1e-5 * np.abs(wdw))
         assert np.all(np.abs(db.cpu().numpy() - wdb) <= 2e-6 * 16 * ho * ho / scale + 1e-5 * np.abs(wdb))
     ops.check_device_flag()
+
+
+def test_direct_input_gradient_is_bit_exact_when_forced(oracle, cuda_device):
+    """DWBNQ_BWD_INPUT_DIRECT=1 (read once per process: a child process) keeps the stride-1
+    input gradient on the direct kernel, whose sum runs in the reference's order."""
+    import os
+    import subprocess
+    import sys
+    code = (
+        "import sys, numpy as np, torch\n"
+        "sys.path[:0] = [%r, %r]\n"
+        "from dwbnq import ops\n"
+        "from oracle import oracle\n"
+        "rng = np.random.default_rng(3)\n"
+        "for k, hw in ((3, 28), (5, 14), (3, 9)):\n"
+        "    x = rng.standard_normal((4, 16, hw, hw)).astype(np.float32)\n"
+        "    w = rng.standard_normal((16, k, k)).astype(np.float32)\n"
+        "    dy = rng.standard_normal((4, 16, hw, hw)).astype(np.float32)\n"
+        "    want = oracle.dwconv_bwd(x, w, dy, (1, 1), (k // 2, k // 2))[0]\n"
+        "    t = lambda a: torch.from_numpy(a).cuda()\n"
+        "    got = ops.depthwise_convolution_backward(t(x), t(w), t(dy), 1, (k // 2,) * 2, (1, 1), need=(True, False, False))[0]\n"
+        "    assert np.array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32)), (k, hw)\n"
+        "print('direct-ok')\n") % (ROOT, os.path.join(ROOT, "nnabla-ext-cuda_b200", "python"))
+    r = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, DWBNQ_BWD_INPUT_DIRECT="1"),
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "direct-ok" in r.stdout, r.stderr[-2000:]
 
 
 def test_backward_argument_errors(cuda_device):

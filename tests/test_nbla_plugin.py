@@ -259,7 +259,7 @@ def test_backward_of_the_registered_classes(harness, oracle, cuda_device):
                                  _p(db), 1, 2, 1, 1, 0b111, 0)
     assert rc == 0, harness.stub_last_error()
     torch.cuda.synchronize()
-    np.testing.assert_array_equal(dx.cpu().numpy(), wdx)
+    np.testing.assert_array_equal(dx.cpu().numpy(), wdx)  # stride 2: the direct kernel, the reference's order
     np.testing.assert_allclose(dw.cpu().numpy(), wdw, rtol=1e-4, atol=1e-4)
     np.testing.assert_allclose(db.cpu().numpy(), wdb, rtol=1e-4, atol=1e-4)
     # only the weights, accumulated
