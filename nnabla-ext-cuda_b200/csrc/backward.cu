@@ -210,7 +210,8 @@ __global__ void __launch_bounds__(kThreads)
 // time and its lanes walk over the output positions of that plane 32 at a time, so dy and the
 // K x K input values under each position are read as coalesced rows (the nine or twenty-five
 // shifted reads of a row hit L1). Each lane accumulates x * dy for every tap in registers, plus
-// dy for the bias. Warp shuffles and shared memory reduce the CTA's partial sums, which are added to the
+// dy for the bias. Positions whose K x K window lies inside the image (all but a border) are
+// enumerated on their own and load without tests; the border positions test every tap. Warp shuffles and shared memory reduce the CTA's partial sums, which are added to the
 // gradients with one atomic per value: the gradients must be zero (or hold the value to
 // accumulate onto) when the kernel starts.
 template <typename T, int K, int S>
@@ -236,33 +237,34 @@ __global__ void __launch_bounds__(kThreads, K == 3 ? 4 : 2)
 #pragma unroll
   for (int i = 0; i < KK; ++i) acc[i] = 0.0f;
   float bsum = 0.0f;
+  // output rows / columns whose window lies wholly inside the image
+  const int oy_lo = min(a.Ho, (a.ph + S - 1) / S), ox_lo = min(a.Wo, (a.pw + S - 1) / S);
+  const int oy_hi = max(oy_lo, min(a.Ho, a.H - K + a.ph >= 0 ? (a.H - K + a.ph) / S + 1 : 0));
+  const int ox_hi = max(ox_lo, min(a.Wo, a.W - K + a.pw >= 0 ? (a.W - K + a.pw) / S + 1 : 0));
+  const int w_int = ox_hi - ox_lo, n_int = (oy_hi - oy_lo) * w_int;
+  const int n_top = oy_lo * a.Wo, n_bot = (a.Ho - oy_hi) * a.Wo;
+  const int w_edge = a.Wo - w_int, n_edge = n_top + n_bot + (oy_hi - oy_lo) * w_edge;
   for (long long n = n0 + warp; n < n1; n += kThreads / 32) {
     const T *dyp = dy + (n * a.OC + oc) * plane_out;
     const T *xp = x + (n * a.C + ic) * plane_in;
-    // Two positions per trip, every load unconditional (row and column clamped into the image,
-    // the value replaced by zero where the tap lies outside): no branch stands between the
-    // loads of a trip, so they are all in flight together.
-    for (int pos = lane; pos < plane_out; pos += 64) {
+    // Interior positions (the whole K x K window inside the image: rows [oy_lo, oy_hi), columns
+    // [ox_lo, ox_hi)): loads without any test, two positions per trip so that their loads are in
+    // flight together.
+    for (int idx = lane; idx < n_int; idx += 64) {
       float g[2], xv[2][KK];
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
-        const int pu = pos + 32 * u;
-        const bool live = pu < plane_out;
-        const int pc = live ? pu : pos;
-        const int oy = pc / a.Wo, ox = pc - oy * a.Wo;
-        g[u] = live ? Elem<T>::to_f32(dyp[pc]) : 0.0f;
-        const int iy0 = oy * S - a.ph, ix0 = ox * S - a.pw;
+        const int iu = idx + 32 * u;
+        const bool live = iu < n_int;
+        const int ic2 = live ? iu : idx;
+        const int r = ic2 / w_int;
+        const int oy = oy_lo + r, ox = ox_lo + (ic2 - r * w_int);
+        g[u] = live ? Elem<T>::to_f32(dyp[oy * a.Wo + ox]) : 0.0f;
+        const T *xw = xp + (oy * S - a.ph) * a.W + (ox * S - a.pw);
 #pragma unroll
         for (int ky = 0; ky < K; ++ky) {
-          const int iy = iy0 + ky;
-          const bool row_in = (unsigned int)iy < (unsigned int)a.H;
-          const T *xr = xp + min(max(iy, 0), a.H - 1) * a.W;
 #pragma unroll
-          for (int kx = 0; kx < K; ++kx) {
-            const int ix = ix0 + kx;
-            const float v = Elem<T>::to_f32(xr[min(max(ix, 0), a.W - 1)]);
-            xv[u][ky * K + kx] = (row_in && (unsigned int)ix < (unsigned int)a.W) ? v : 0.0f;
-          }
+          for (int kx = 0; kx < K; ++kx) xv[u][ky * K + kx] = Elem<T>::to_f32(xw[ky * a.W + kx]);
         }
       }
 #pragma unroll
@@ -270,6 +272,35 @@ __global__ void __launch_bounds__(kThreads, K == 3 ? 4 : 2)
         bsum += g[u];
 #pragma unroll
         for (int i = 0; i < KK; ++i) acc[i] = fmaf(xv[u][i], g[u], acc[i]);
+      }
+    }
+    // Border positions: rows above / below the interior in full, and the columns left / right of
+    // it on the interior rows; every tap tested.
+    for (int e = lane; e < n_edge; e += 32) {
+      int oy, ox;
+      if (e < n_top) {
+        oy = e / a.Wo;
+        ox = e - oy * a.Wo;
+      } else if (e < n_top + n_bot) {
+        const int t = e - n_top;
+        oy = oy_hi + t / a.Wo;
+        ox = t - (t / a.Wo) * a.Wo;
+      } else {
+        const int t = e - n_top - n_bot;
+        const int r = t / w_edge, j = t - r * w_edge;
+        oy = oy_lo + r;
+        ox = j < ox_lo ? j : ox_hi + (j - ox_lo);
+      }
+      const float g = Elem<T>::to_f32(dyp[oy * a.Wo + ox]);
+      bsum += g;
+      const int iy0 = oy * S - a.ph, ix0 = ox * S - a.pw;
+#pragma unroll
+      for (int ky = 0; ky < K; ++ky) {
+#pragma unroll
+        for (int kx = 0; kx < K; ++kx) {
+          if ((unsigned int)(iy0 + ky) < (unsigned int)a.H && (unsigned int)(ix0 + kx) < (unsigned int)a.W)
+            acc[ky * K + kx] = fmaf(Elem<T>::to_f32(xp[(iy0 + ky) * a.W + ix0 + kx]), g, acc[ky * K + kx]);
+        }
       }
     }
   }
