@@ -1,7 +1,8 @@
 /*
  * dwbnq - C ABI of the B200 (sm_100a) quantized depthwise-CNN inference path:
  * DepthwiseConvolution forward -> BatchNormalization (batch_stat=false) ->
- * FixedPointQuantize | Pow2Quantize | MinMaxQuantize forward.
+ * FixedPointQuantize | Pow2Quantize | MinMaxQuantize forward, plus the pointwise
+ * convolutions around it.
  *
  * Conventions (they mirror how nnabla-ext-cuda's function classes touch memory):
  *  - every data pointer is a DEVICE pointer owned by the caller and valid for the
@@ -299,6 +300,67 @@ int dwbnq_fused_fwd_code8(const dwbnq_conv_desc *desc, float bn_eps, const dwbnq
 int dwbnq_fused_plan(const dwbnq_conv_desc *desc, const void *x, const void *y,
                      int *path_out, int *planes_per_cta, int *rows_per_tile,
                      int *threads, int64_t *ctas, int *smem_bytes);
+/* ---- the pointwise (1x1) convolutions either side of a depthwise layer ------------------ */
+
+/* How an fp32 contraction is evaluated on the tensor cores.
+ *  DWBNQ_PW_MATH_FP32: every product is formed from the TF32 halves of both factors in
+ *    three tensor-core passes (hi*hi + lo*hi + hi*lo, fp32 accumulation), which keeps the
+ *    result within a few units of 1e-6 of sum|w||x| - the accuracy class of the fp32
+ *    GEMM the reference runs by default (it disables TF32 unless NNABLA_CUDA_ALLOW_TF32
+ *    is set, src/nbla/cuda/init.cpp.tmpl:76-83);
+ *  DWBNQ_PW_MATH_TF32: one pass on operands truncated to TF32, what the reference
+ *    computes when NNABLA_CUDA_ALLOW_TF32=1. */
+typedef enum dwbnq_pw_math { DWBNQ_PW_MATH_FP32 = 0, DWBNQ_PW_MATH_TF32 = 1 } dwbnq_pw_math;
+/* Activation between BatchNormalization and the quantizer: ReLU is max(0, x)
+ * (src/nbla/cuda/function/generic/relu.cu:31-41), ReLU6 is min(max(x, 0), 6)
+ * (src/nbla/cuda/function/generic/relu6.cu:25-26). */
+typedef enum dwbnq_act { DWBNQ_ACT_NONE = 0, DWBNQ_ACT_RELU = 1, DWBNQ_ACT_RELU6 = 2 } dwbnq_act;
+
+/* Geometry of Convolution(ctx, base_axis, pad, stride, dilation, group, channel_last)
+ * (include/nbla/cuda/function/convolution.hpp:27-33) restricted to the pointwise case the
+ * MobileNet blocks use around each depthwise layer: kernel 1x1, pad 0, stride 1,
+ * dilation 1, group 1, NCHW. Anything else stays with the reference's own kernels. */
+typedef struct dwbnq_pwconv_desc {
+  int32_t dtype;      /* dwbnq_dtype                                   */
+  int32_t c_in;       /* input channels                                */
+  int32_t c_out;      /* output channels                               */
+  int32_t h, w;       /* spatial size (input = output)                 */
+  int64_t n;          /* product of the axes before base_axis          */
+  int32_t math;       /* dwbnq_pw_math (fp32 tensors only)             */
+  int32_t act;        /* dwbnq_act, applied after BN, before quantizer */
+} dwbnq_pwconv_desc;
+
+/* Bytes of device scratch the pointwise entry points need (per-channel coefficients and
+ * the TF32 halves of the weights); 256-byte aligned, contents irrelevant on entry. */
+size_t dwbnq_pwconv_workspace_bytes(const dwbnq_pwconv_desc *desc);
+
+/* ConvolutionCuda<T>::forward_impl for the pointwise case: the reference runs one GEMM per
+ * image on the im2col buffer and then adds the bias with a rank-1 GEMM
+ * (src/nbla/cuda/function/generic/convolution.cu:56-87; the cuDNN class does the same with
+ * cudnnConvolutionForward + cudnnAddTensor, src/nbla/cuda/cudnn/function/generic/
+ * convolution.cu:135), so y = (sum over input channels of w * x) + b with the order of the
+ * sum unspecified. x [n,c_in,h,w]; w [c_out,c_in,1,1]; b [c_out] or NULL; y [n,c_out,h,w]. */
+int dwbnq_pwconv_fwd(const dwbnq_pwconv_desc *desc, const void *x, const void *w, const void *b,
+                     void *y, void *workspace, int device, void *stream);
+
+/* y = Quantize(act(BN_inference(Convolution_1x1(x)))) in one kernel: BatchNormalization,
+ * the activation and FixedPointQuantize / Pow2Quantize run on the accumulators before the
+ * only store. Given the convolution result, BN, activation and quantizer are the exact
+ * arithmetic of the separate classes (as in dwbnq_fused_fwd); the convolution itself is
+ * exact only up to the order of its sum, so a value that lands within rounding distance of
+ * a quantization threshold may come out one step away from another implementation's.
+ * bn_mean == NULL skips BatchNormalization; q == NULL or kind NONE skips the quantizer;
+ * MINMAX is not available here (run dwbnq_minmaxq_fwd on the result). */
+int dwbnq_pwconv_fused_fwd(const dwbnq_pwconv_desc *desc, float bn_eps, const dwbnq_quant_desc *q,
+                           const void *x, const void *w, const void *b, const void *bn_beta,
+                           const void *bn_gamma, const void *bn_mean, const void *bn_var,
+                           void *y, void *workspace, int device, void *stream);
+
+/* Which kernel the pointwise entry points would use: 1 = the tcgen05 kernel (fp32 tensors,
+ * h*w and c_in multiples of 4, 16-byte aligned x and w: what the TMA loads need), 0 = the
+ * plain FMA kernel (fp16 tensors and every other shape). Diagnostic only. */
+int dwbnq_pwconv_plan(const dwbnq_pwconv_desc *desc, const void *x, const void *w, int *path_out);
+
 /* ---- communicator: the one exchange the path needs (per-channel min/max) ----------- */
 
 /* NCCL is loaded with dlopen at first use, like the reference does

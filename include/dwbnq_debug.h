@@ -28,6 +28,10 @@ int dwbnq_set_forced_path(int path);
  * per tile, threads per CTA; the fourth value is reserved (pass 0). Values that do not fit
  * the shared-memory budget fall back to the generic kernel. */
 int dwbnq_set_tuning(int planes_per_cta, int row_blocks_per_tile, int threads, int rows_per_patch);
+/* Restricts the kernel dwbnq_pwconv_fwd / dwbnq_pwconv_fused_fwd choose for this thread's
+ * calls: -1 automatic, 0 the plain FMA kernel, 1 the tcgen05 kernel (a shape it cannot take
+ * then fails with DWBNQ_ERR_UNSUPPORTED). DWBNQ_PW_FORCE=simt|tc sets the default. */
+int dwbnq_set_forced_pw_path(int path);
 /* Launches one warp that waits, with the bounded wait every copy-engine kernel of the
  * library uses, on a shared-memory barrier that nothing ever completes, with the limit
  * shortened to `limit_us` microseconds. The wait runs out, the kernel records it in the

@@ -220,6 +220,57 @@ size_t dwbnq_workspace_bytes(int32_t channels) {
   return (b + 255) / 256 * 256;
 }
 
+size_t dwbnq_pwconv_workspace_bytes(const dwbnq_pwconv_desc *desc) {
+  clear_error();
+  if (pwconv_validate(desc) != DWBNQ_OK) return 0;
+  return pwconv_workspace_bytes(*desc);
+}
+
+int dwbnq_pwconv_fused_fwd(const dwbnq_pwconv_desc *desc, float bn_eps, const dwbnq_quant_desc *q, const void *x,
+                           const void *w, const void *b, const void *bn_beta, const void *bn_gamma,
+                           const void *bn_mean, const void *bn_var, void *y, void *workspace, int device,
+                           void *stream) {
+  clear_error();
+  NvtxRange nvtx_range("dwbnq_pwconv_fused_fwd");
+  int st = pwconv_validate(desc);
+  if (st != DWBNQ_OK) return st;
+  int dev;
+  st = enter_device(device, &dev);
+  if (st != DWBNQ_OK) return st;
+  return launch_pwconv(*desc, bn_eps, q, x, w, b, bn_beta, bn_gamma, bn_mean, bn_var, y, workspace, dev,
+                       static_cast<cudaStream_t>(stream));
+}
+
+int dwbnq_pwconv_fwd(const dwbnq_pwconv_desc *desc, const void *x, const void *w, const void *b, void *y,
+                     void *workspace, int device, void *stream) {
+  clear_error();
+  NvtxRange nvtx_range("dwbnq_pwconv_fwd");
+  int st = pwconv_validate(desc);
+  if (st != DWBNQ_OK) return st;
+  if (desc->act != DWBNQ_ACT_NONE) return fail(DWBNQ_ERR_INVALID_ARG, "dwbnq_pwconv_fwd takes no activation (act = %d)", desc->act);
+  int dev;
+  st = enter_device(device, &dev);
+  if (st != DWBNQ_OK) return st;
+  return launch_pwconv(*desc, 0.0f, nullptr, x, w, b, nullptr, nullptr, nullptr, nullptr, y, workspace, dev,
+                       static_cast<cudaStream_t>(stream));
+}
+
+int dwbnq_pwconv_plan(const dwbnq_pwconv_desc *desc, const void *x, const void *w, int *path_out) {
+  clear_error();
+  int st = pwconv_validate(desc);
+  if (st != DWBNQ_OK) return st;
+  if (!path_out) return fail(DWBNQ_ERR_INVALID_ARG, "path_out is null");
+  *path_out = pwconv_path(*desc, x, w);
+  return DWBNQ_OK;
+}
+
+int dwbnq_set_forced_pw_path(int path) {
+  clear_error();
+  if (path < -1 || path > 1) return fail(DWBNQ_ERR_INVALID_ARG, "pointwise path %d is not -1, 0 or 1", path);
+  set_forced_pw_path(path);
+  return DWBNQ_OK;
+}
+
 int dwbnq_set_forced_path(int path) {
   clear_error();
   if (path < PATH_AUTO || path > PATH_PLANE_GEN) return fail(DWBNQ_ERR_INVALID_ARG, "path %d is not -1..5", path);

@@ -131,6 +131,18 @@ int launch_dwconv_backward(const dwbnq_conv_desc &d, int ho, int wo, const void 
 // Smallest float bit pattern a > 0 with 2^round(log2f(a)) >= v (host libm, bisection).
 uint32_t pow2_first_pattern_reaching(float v);
 
+// ---- pointwise convolution (pointwise.cu) ------------------------------------------------------
+int pwconv_validate(const dwbnq_pwconv_desc *d);
+size_t pwconv_workspace_bytes(const dwbnq_pwconv_desc &d);
+// 1 = the tcgen05 kernel, 0 = the plain FMA kernel (thread's forced choice included).
+int pwconv_path(const dwbnq_pwconv_desc &d, const void *x, const void *w);
+void set_forced_pw_path(int p);
+// Prepares the per-channel coefficients (and the TF32 halves of w) in `workspace`, then runs
+// the convolution with the fused epilogue. BN is skipped when mean is null; q may be null.
+int launch_pwconv(const dwbnq_pwconv_desc &d, float bn_eps, const dwbnq_quant_desc *q, const void *x, const void *w,
+                  const void *b, const void *beta, const void *gamma, const void *mean, const void *var, void *y,
+                  void *workspace, int dev, cudaStream_t stream);
+
 // ---- communicator (comm.cpp) --------------------------------------------------------------
 int comm_allreduce_max(void *comm, float *buf, long long count, cudaStream_t stream,
                        int timeout_ms);

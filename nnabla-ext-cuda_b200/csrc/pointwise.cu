@@ -1,0 +1,706 @@
+// Pointwise (1x1) convolution, optionally fused with BatchNormalization inference, an
+// activation and FixedPointQuantize / Pow2Quantize: y[n][co][p] = epilogue(sum_ci w[co][ci] *
+// x[n][ci][p] + b[co]) for NCHW tensors, p running over the h*w positions of an image.
+//
+// The tensor-core kernel is written for sm_100a directly (tcgen05.mma with the accumulator
+// in tensor memory, TMA tiled loads, mbarrier pipelines):
+//  * per image the product is D[position][co] = X^T[position][ci] * W^T[ci][co]: the A operand
+//    is a tile of 128 positions (MN-major in shared memory, exactly how NCHW stores it), the B
+//    operand the weights (K-major), so the 128 TMEM lanes are positions and the columns are
+//    output channels. A warp that reads the accumulator back holds, per column, 32 consecutive
+//    positions of one channel: BN / activation / quantizer run in registers with warp-uniform
+//    per-channel coefficients and every store is one coalesced 128-byte line - no staging of
+//    the output in shared memory;
+//  * one CTA per SM walks over (channel tile, image, position tile) triples; warp 0 issues
+//    the TMA loads, warp 1 the MMAs, warps 2-3 split the fp32 activations into TF32 halves for
+//    the three-pass mode, warps 4-11 are the epilogue; two accumulator buffers in TMEM let the
+//    epilogue of one tile overlap the loads and MMAs of the next;
+//  * every wait on an mbarrier is bounded in time; a wait that runs out records it in the
+//    device flag, the roles leave their loops, and the CTA frees its tensor memory and returns.
+// Shapes the TMA loads cannot take (h*w or c_in not a multiple of 4, fp16 tensors) run on a
+// plain FMA kernel with the same epilogue.
+#include <cstdlib>
+#include <cstring>
+
+#include "dwbnq_internal.h"
+
+namespace dwbnq {
+
+namespace {
+
+constexpr int kPwThreads = 384;
+constexpr int kPwFirstEpiWarp = 4, kPwEpiWarps = 8;
+constexpr int kPwPosTile = 128;            // accumulator rows = TMEM lanes
+constexpr int kPwKChunk = 32;              // fp32 elements of c_in per pipeline stage
+constexpr int kPwXBytes = kPwPosTile * kPwKChunk * 4;  // 4 boxes of [32 k][32 positions]
+constexpr int kPwMaxStages = 8;
+constexpr int kPwMaxCoTile = 256;          // two accumulators of 256 columns fill the 512 of TMEM
+constexpr int kPwSmemMax = 227 * 1024 - 1024;  // dynamic shared memory the kernel may ask for
+constexpr unsigned long long kPwWaitNs = 2000000000ull;
+
+enum PwEpi : int { PW_EPI_BIAS = 0, PW_EPI_BN_FPQ = 1, PW_EPI_GENERIC = 2 };
+
+// Per pair of output channels, everything the epilogue needs (one 64-byte shared-memory row).
+struct __align__(16) PwPair {
+  f32x2 bias, nmean, scale, rcp, nstd, beta;
+  float stdvar_lo, stdvar_hi, glo, pad;
+};
+
+struct PwArgs {
+  int HW, Ci, Co;
+  long long N;
+  int npad;       // accumulator columns per channel tile (multiple of 32, <= 256)
+  int co_tiles, pos_tiles, kchunks;
+  long long total_tiles;
+  int stages, stage_bytes;
+  const float *coef;  // [5][co_tiles * npad]: bias, mean, scale, stdvar, beta
+  float *y;
+  int *flag;
+  int has_bn, act, qkind;
+  QuantArgs q;
+};
+
+// ---- sm_100a PTX wrappers ------------------------------------------------------------------
+
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *tm, int x, int y, unsigned long long *bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"(tm), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+// Bounded waits of this kernel. Every tile passes through several barriers in a row (loads ->
+// MMA -> epilogue -> MMA -> loads), so the poll carries no suspend-time hint: a parked thread's
+// wake-up latency would be paid at each hop.
+__device__ __forceinline__ bool pw_try_wait(unsigned long long *bar, unsigned int parity) {
+  unsigned int ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool pw_wait_lane(unsigned long long *bar, unsigned int parity) {
+  if (pw_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+#pragma unroll 1
+  for (unsigned int i = 0; i < (1u << 28); ++i) {
+    if (pw_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 63u && global_timer_ns() - t0 > kPwWaitNs) break;
+  }
+  return false;
+}
+// Warp-uniform form: every lane has seen the phase, or every lane gives up.
+__device__ __forceinline__ bool pw_wait(unsigned long long *bar, unsigned int parity) {
+  bool ok = pw_wait_lane(bar, parity);
+  if (!__all_sync(0xffffffffu, ok)) {
+    if (__any_sync(0xffffffffu, ok) && !ok) ok = pw_try_wait(bar, parity);
+    ok = __all_sync(0xffffffffu, ok);
+  }
+  return ok;
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// The barrier receives one arrival once every MMA this thread has issued so far is complete.
+__device__ __forceinline__ void tc_commit(unsigned long long *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// D[128 x N] (+)= A[128 x 8] * B[N x 8]^T, TF32 operands from shared memory, fp32 accumulator in TMEM.
+__device__ __forceinline__ void tc_mma_tf32(unsigned int tmem_d, unsigned long long da, unsigned long long db,
+                                            unsigned int idesc, unsigned int accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// 16 consecutive accumulator columns of this thread's lane (issue only; wait with tc_ld_wait).
+__device__ __forceinline__ void tc_ld16(unsigned int taddr, unsigned int *r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of tcgen05.mma (addresses and offsets in bytes; the fields
+// hold them divided by 16). layout 2 = 128-byte swizzle, 1 = 128-byte swizzle of 32-byte
+// units, the only form the hardware takes for an MN-major operand of 32-bit elements.
+__device__ __forceinline__ unsigned long long pw_smem_desc(unsigned int addr, unsigned int lbo, unsigned int sbo,
+                                                          unsigned int layout) {
+  return (unsigned long long)((addr >> 4) & 0x3fffu) | ((unsigned long long)((lbo >> 4) & 0x3fffu) << 16) |
+         ((unsigned long long)((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46) | ((unsigned long long)layout << 61);
+}
+// A: 128 positions x 8 channels of a stage's activation buffer. The buffer is four TMA boxes
+// of [32 channels][32 positions] fp32 (4 KiB each, 128-byte rows, 32-byte units swizzled by
+// row mod 4): consecutive groups of 32 positions are 4096 bytes apart (leading offset), the
+// two groups of 4 channels one MMA consumes 512 bytes (stride offset).
+__device__ __forceinline__ unsigned long long pw_desc_a(unsigned int buf, int kstep) {
+  return pw_smem_desc(buf + kstep * 1024, 4096, 512, 1);
+}
+// B: N channels-out x 8 channels-in of a stage's weight buffer, one TMA box of [N][32] fp32
+// (128-byte rows, 16-byte units swizzled by row mod 8): groups of 8 rows are 1024 bytes apart,
+// a step of 8 along c_in advances the start by 32 bytes inside the row.
+__device__ __forceinline__ unsigned long long pw_desc_b(unsigned int buf, int kstep) {
+  return pw_smem_desc(buf + kstep * 32, 16, 1024, 2);
+}
+
+// ---- epilogue --------------------------------------------------------------------------------
+
+__device__ __forceinline__ float pw_act(float v, int act) {
+  if (act == DWBNQ_ACT_RELU6) return fminf(fmaxf(v, 0.0f), 6.0f);
+  if (act == DWBNQ_ACT_RELU) return fmaxf(0.0f, v);
+  return v;
+}
+
+// Two adjacent channels of one position: accumulators in, final values out.
+template <int EPI>
+__device__ __forceinline__ void pw_finish_pair(float a0, float a1, const PwPair &cp, const PwArgs &a, f32x2 nz,
+                                               const FpqPacked &fq, float &r0, float &r1) {
+  f32x2 v = add2(pack2(a0, a1), cp.bias);
+  if (EPI == PW_EPI_BN_FPQ || (EPI == PW_EPI_GENERIC && a.has_bn)) {
+    BnPacked b;
+    b.nmean = cp.nmean; b.scale = cp.scale; b.rcp = cp.rcp; b.nstd = cp.nstd; b.beta = cp.beta; b.nz = nz;
+    b.stdvar = cp.stdvar_lo; b.stdvar_hi = cp.stdvar_hi; b.glo = cp.glo;
+    bn_apply_packed<1>(&v, b);
+  }
+  unpack2(v, r0, r1);
+  if (a.act) { r0 = pw_act(r0, a.act); r1 = pw_act(r1, a.act); }
+  if (EPI == PW_EPI_BN_FPQ) {
+    unpack2(fpq_apply_fast_unsigned2(r0, r1, a.q, fq), r0, r1);
+  } else if (EPI == PW_EPI_GENERIC) {
+    if (a.qkind == DWBNQ_Q_FPQ) { r0 = fpq_apply(r0, a.q); r1 = fpq_apply(r1, a.q); }
+    else if (a.qkind == DWBNQ_Q_POW2) { r0 = pow2_apply(r0, a.q); r1 = pow2_apply(r1, a.q); }
+  }
+}
+
+__device__ __forceinline__ PwPair pw_make_pair(const PwArgs &a, int cpad, int c) {
+  // c is even and c + 1 < cpad; padded channels hold neutral coefficients
+  const BnCoef lo{a.coef[cpad + c], a.coef[2 * cpad + c], a.coef[3 * cpad + c], a.coef[4 * cpad + c]};
+  const BnCoef hi{a.coef[cpad + c + 1], a.coef[2 * cpad + c + 1], a.coef[3 * cpad + c + 1], a.coef[4 * cpad + c + 1]};
+  const BnPacked b = make_bn_packed2(lo, hi, 0ull);
+  PwPair p;
+  p.bias = pack2(a.coef[c], a.coef[c + 1]);
+  p.nmean = b.nmean; p.scale = b.scale; p.rcp = b.rcp; p.nstd = b.nstd; p.beta = b.beta;
+  p.stdvar_lo = b.stdvar; p.stdvar_hi = b.stdvar_hi; p.glo = b.glo; p.pad = 0.0f;
+  return p;
+}
+
+// ---- the tcgen05 kernel ------------------------------------------------------------------------
+
+template <bool MATH3, int EPI>
+__global__ void __launch_bounds__(kPwThreads, 1)
+pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+             const __grid_constant__ CUtensorMap tm_wlo, const PwArgs a) {
+  extern __shared__ unsigned char pw_smem_raw[];
+  // full / empty / split per stage, then accumulator full[2] / empty[2]
+  __shared__ unsigned long long bars[3 * kPwMaxStages + 4];
+  __shared__ unsigned int tmem_base_s;
+  __shared__ int abort_s;
+  unsigned long long *full = bars, *empty = bars + kPwMaxStages, *split = bars + 2 * kPwMaxStages;
+  unsigned long long *acc_full = bars + 3 * kPwMaxStages, *acc_empty = acc_full + 2;
+  const unsigned int base = (smem_u32(pw_smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
+  unsigned char *sm = pw_smem_raw + (base - smem_u32(pw_smem_raw));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wbytes = a.npad * 128;
+  const int off_xlo = kPwXBytes, off_w = MATH3 ? 2 * kPwXBytes : kPwXBytes, off_wlo = off_w + wbytes;
+  // after the stages: one coefficient table per epilogue warp
+  PwPair *tables = reinterpret_cast<PwPair *>(sm + (size_t)a.stages * a.stage_bytes);
+  unsigned int tmem_cols = 32;
+  while ((int)tmem_cols < 2 * a.npad) tmem_cols <<= 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < a.stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+      mbar_init(&split[s], 64);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], kPwEpiWarps);
+    }
+    abort_s = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
+                 "r"(tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned int tmem_base = tmem_base_s;
+  const long long per_ct = a.N * a.pos_tiles;
+  volatile int *abort_v = &abort_s;
+
+  if (warp == 0) {
+    // ---- producer: one lane issues the TMA loads of every (tile, c_in chunk) ----
+    if (lane == 0) {
+      unsigned int it = 0;
+      const unsigned int bytes = kPwXBytes + wbytes * (MATH3 ? 2 : 1);
+      bool ok = true;
+      for (long long t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
+        const int ct = (int)(t / per_ct);
+        const long long r = t - (long long)ct * per_ct;
+        const int n = (int)(r / a.pos_tiles), pt = (int)(r - (long long)n * a.pos_tiles);
+        for (int kc = 0; kc < a.kchunks; ++kc, ++it) {
+          const int s = it % a.stages;
+          const unsigned int ph = (it / a.stages) & 1u;
+          if (!pw_wait_lane(&empty[s], ph ^ 1u) || *abort_v) { ok = false; break; }
+          unsigned char *st = sm + (size_t)s * a.stage_bytes;
+          mbar_expect_tx(&full[s], bytes);
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            tma_load_3d(st + q * 4096, &tm_x, pt * kPwPosTile + q * 32, kc * kPwKChunk, n, &full[s]);
+          tma_load_2d(st + off_w, &tm_w, kc * kPwKChunk, ct * a.npad, &full[s]);
+          if (MATH3) tma_load_2d(st + off_wlo, &tm_wlo, kc * kPwKChunk, ct * a.npad, &full[s]);
+        }
+      }
+      if (!ok && !*abort_v) { atomicExch(a.flag, 1); *abort_v = 1; }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ----
+    // instruction descriptor: fp32 accumulator, TF32 A and B, A MN-major, B K-major, N, M = 128
+    const unsigned int idesc = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | ((unsigned)(a.npad >> 3) << 17) | (8u << 24);
+    unsigned int it = 0, tile_i = 0;
+    bool ok = true;
+    for (long long t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x, ++tile_i) {
+      const unsigned int b = tile_i & 1u, aph = (tile_i >> 1) & 1u;
+      ok = pw_wait(&acc_empty[b], aph ^ 1u);
+      tc_fence_after();
+      for (int kc = 0; ok && kc < a.kchunks; ++kc, ++it) {
+        const int s = it % a.stages;
+        const unsigned int ph = (it / a.stages) & 1u;
+        ok = pw_wait(&full[s], ph);
+        if (ok && MATH3) ok = pw_wait(&split[s], ph);
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          const unsigned int sb = base + (unsigned)s * a.stage_bytes;
+          const int krem = a.Ci - kc * kPwKChunk;
+          const int ksteps = krem >= kPwKChunk ? kPwKChunk / 8 : (krem + 7) >> 3;  // rows past c_in are zero-filled
+          const unsigned int d = tmem_base + b * a.npad;
+          for (int j = 0; j < ksteps; ++j) {
+            const unsigned long long da = pw_desc_a(sb, j), db = pw_desc_b(sb + off_w, j);
+            tc_mma_tf32(d, da, db, idesc, (kc | j) ? 1u : 0u);
+            if (MATH3) {
+              tc_mma_tf32(d, pw_desc_a(sb + off_xlo, j), db, idesc, 1u);
+              tc_mma_tf32(d, da, pw_desc_b(sb + off_wlo, j), idesc, 1u);
+            }
+          }
+          tc_commit(&empty[s]);
+          if (kc == a.kchunks - 1) tc_commit(&acc_full[b]);
+        }
+        __syncwarp();
+      }
+      if (*abort_v) ok = false;
+    }
+    if (!ok && lane == 0 && !*abort_v) { atomicExch(a.flag, 1); *abort_v = 1; }
+  } else if (warp < kPwFirstEpiWarp) {
+    // ---- three-pass mode: x -> (x with the low 13 mantissa bits cleared, the exact rest) ----
+    if (MATH3) {
+      const int tid = threadIdx.x - 64;
+      unsigned int it = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
+        for (int kc = 0; kc < a.kchunks; ++kc, ++it) {
+          const int s = it % a.stages;
+          const unsigned int ph = (it / a.stages) & 1u;
+          ok = pw_wait(&full[s], ph) && !*abort_v;
+          if (!ok) break;
+          uint4 *xh = reinterpret_cast<uint4 *>(sm + (size_t)s * a.stage_bytes);
+          uint4 *xl = reinterpret_cast<uint4 *>(sm + (size_t)s * a.stage_bytes + off_xlo);
+#pragma unroll 4
+          for (int i = tid; i < kPwXBytes / 16; i += 64) {
+            const uint4 v = xh[i];
+            uint4 h, l;
+            h.x = v.x & 0xffffe000u; h.y = v.y & 0xffffe000u; h.z = v.z & 0xffffe000u; h.w = v.w & 0xffffe000u;
+            l.x = __float_as_uint(__fsub_rn(__uint_as_float(v.x), __uint_as_float(h.x)));
+            l.y = __float_as_uint(__fsub_rn(__uint_as_float(v.y), __uint_as_float(h.y)));
+            l.z = __float_as_uint(__fsub_rn(__uint_as_float(v.z), __uint_as_float(h.z)));
+            l.w = __float_as_uint(__fsub_rn(__uint_as_float(v.w), __uint_as_float(h.w)));
+            xh[i] = h;
+            xl[i] = l;
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // visible to the tensor core's reads
+          mbar_arrive(&split[s]);
+        }
+      }
+      if (!ok && lane == 0 && !*abort_v) { atomicExch(a.flag, 1); *abort_v = 1; }
+    }
+  } else {
+    // ---- epilogue: warp (quarter, half) owns lanes [32 quarter, +32) and half of the columns ----
+    const int ew = warp - kPwFirstEpiWarp, quarter = warp & 3, half = ew >> 2;
+    const int cols_half = a.npad >> 1;  // multiple of 16
+    const int cpad = a.co_tiles * a.npad;
+    PwPair *table = tables + (size_t)ew * (kPwMaxCoTile / 4);
+    const f32x2 nz = negzero2();
+    const FpqPacked fq = make_fpq_packed(a.q);
+    unsigned int tile_i = 0;
+    int cur_ct = -1;
+    for (long long t = blockIdx.x; t < a.total_tiles; t += gridDim.x, ++tile_i) {
+      const int ct = (int)(t / per_ct);
+      const long long r = t - (long long)ct * per_ct;
+      const long long n = r / a.pos_tiles;
+      const int pt = (int)(r - n * a.pos_tiles);
+      const unsigned int b = tile_i & 1u, aph = (tile_i >> 1) & 1u;
+      const int cbase = ct * a.npad + half * cols_half;  // first channel of this warp
+      if (ct != cur_ct) {
+        cur_ct = ct;
+        __syncwarp();
+        for (int i = lane; i < (cols_half >> 1); i += 32) table[i] = pw_make_pair(a, cpad, cbase + 2 * i);
+        __syncwarp();
+      }
+      if (!pw_wait(&acc_full[b], aph) || *abort_v) {
+        if (lane == 0 && !*abort_v) { atomicExch(a.flag, 1); *abort_v = 1; }
+        break;
+      }
+      tc_fence_after();
+      const int p = pt * kPwPosTile + quarter * 32 + lane;
+      const bool p_ok = p < a.HW;
+      const unsigned int taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + b * a.npad + half * cols_half;
+      float *yp = a.y + ((size_t)n * a.Co + cbase) * a.HW + (p_ok ? p : 0);
+      const bool full_c = cbase + cols_half <= a.Co;
+      for (int c0 = 0; c0 < cols_half; c0 += 32) {
+        unsigned int acc0[16], acc1[16];
+        const bool two = c0 + 16 < cols_half;  // warp-uniform
+        tc_ld16(taddr + c0, acc0);
+        if (two) tc_ld16(taddr + c0 + 16, acc1);
+        tc_ld_wait();
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+          if (h2 && !two) break;
+          const int cc = c0 + 16 * h2;
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) {
+            const PwPair cp = table[(cc + i) >> 1];
+            float r0, r1;
+            pw_finish_pair<EPI>(__uint_as_float(h2 ? acc1[i] : acc0[i]), __uint_as_float(h2 ? acc1[i + 1] : acc0[i + 1]), cp, a,
+                                nz, fq, r0, r1);
+            if (p_ok) {
+              if (full_c || cbase + cc + i < a.Co) yp[(size_t)(cc + i) * a.HW] = r0;
+              if (full_c || cbase + cc + i + 1 < a.Co) yp[(size_t)(cc + i + 1) * a.HW] = r1;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[b]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+  }
+}
+
+// ---- preparation: per-channel coefficients and the TF32 halves of the weights --------------------
+
+template <typename T>
+__global__ void pw_prepare_kernel(const T *w, const T *b, const T *beta, const T *gamma, const T *mean, const T *var,
+                                  float eps, int Co, int cpad, long long wsize, float *coef, float *w_hi, float *w_lo) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < cpad) {
+    const bool in = i < Co;
+    coef[i] = (in && b) ? Elem<T>::to_f32(b[i]) : 0.0f;
+    coef[cpad + i] = (in && mean) ? Elem<T>::to_f32(mean[i]) : 0.0f;
+    coef[2 * cpad + i] = (in && gamma) ? Elem<T>::to_f32(gamma[i]) : 1.0f;
+    coef[3 * cpad + i] = (in && var) ? bn_stdvar(Elem<T>::to_f32(var[i]), eps) : 1.0f;
+    coef[4 * cpad + i] = (in && beta) ? Elem<T>::to_f32(beta[i]) : 0.0f;
+  }
+  if (w_hi && i < wsize) {
+    const float v = Elem<T>::to_f32(w[i]);
+    const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+    w_hi[i] = h;
+    w_lo[i] = __fsub_rn(v, h);
+  }
+}
+
+// ---- plain FMA kernel (any shape, fp32 / fp16 tensors) -------------------------------------------
+// 64 output channels x 64 positions per CTA, 4 x 4 outputs per thread, c_in in chunks of 16.
+
+struct PwSimtArgs {
+  const void *x, *w;
+  void *y;
+  const float *coef;
+  int HW, Ci, Co, cpad, pos_tiles;
+  int has_bn, act, qkind;
+  QuantArgs q;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) pw_simt_kernel(const PwSimtArgs a) {
+  __shared__ float ws[16][64 + 4], xs[16][64 + 4];
+  const T *x = static_cast<const T *>(a.x);
+  const T *w = static_cast<const T *>(a.w);
+  T *y = static_cast<T *>(a.y);
+  const long long n = blockIdx.x / a.pos_tiles;
+  const int p0 = (int)(blockIdx.x - n * a.pos_tiles) * 64, c0 = blockIdx.y * 64;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+  const T *xn = x + (size_t)n * a.Ci * a.HW;
+  for (int k0 = 0; k0 < a.Ci; k0 += 16) {
+    for (int e = threadIdx.x; e < 16 * 64; e += 256) {
+      const int k = e >> 6, j = e & 63;  // xs: positions contiguous in memory
+      xs[k][j] = (k0 + k < a.Ci && p0 + j < a.HW) ? Elem<T>::to_f32(xn[(size_t)(k0 + k) * a.HW + p0 + j]) : 0.0f;
+      const int kk = e & 15, c = e >> 4;  // ws: c_in contiguous in memory
+      ws[kk][c] = (k0 + kk < a.Ci && c0 + c < a.Co) ? Elem<T>::to_f32(w[(size_t)(c0 + c) * a.Ci + k0 + kk]) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      float wv[4], xv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { wv[i] = ws[k][ty * 4 + i]; xv[i] = xs[k][tx * 4 + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = __fmaf_rn(wv[i], xv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = c0 + ty * 4 + i;
+    if (c >= a.Co) continue;
+    const BnCoef bc{a.coef[a.cpad + c], a.coef[2 * a.cpad + c], a.coef[3 * a.cpad + c], a.coef[4 * a.cpad + c]};
+    const float bias = a.coef[c];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int p = p0 + tx * 4 + j;
+      if (p >= a.HW) continue;
+      float v = __fadd_rn(acc[i][j], bias);
+      if (a.has_bn) v = bn_apply(v, bc);
+      v = pw_act(v, a.act);
+      if (a.qkind == DWBNQ_Q_FPQ) v = fpq_apply(v, a.q);
+      else if (a.qkind == DWBNQ_Q_POW2) v = pow2_apply(v, a.q);
+      y[((size_t)n * a.Co + c) * a.HW + p] = Elem<T>::from_f32(v);
+    }
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------------
+
+typedef CUresult (*PwEncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                               const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+PwEncodeFn pw_encode_fn() {
+  static PwEncodeFn fn = [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      p = nullptr;
+    }
+    return reinterpret_cast<PwEncodeFn>(p);
+  }();
+  return fn;
+}
+
+constexpr int kPwPathUnset = -2;
+thread_local int t_forced_pw = kPwPathUnset;
+
+int forced_pw_path() {
+  static const int env_default = [] {
+    const char *e = std::getenv("DWBNQ_PW_FORCE");
+    if (e && !std::strcmp(e, "simt")) return 0;
+    if (e && !std::strcmp(e, "tc")) return 1;
+    return -1;
+  }();
+  return t_forced_pw == kPwPathUnset ? env_default : t_forced_pw;
+}
+
+inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+struct PwGeom {
+  int npad, co_tiles, cpad;
+};
+PwGeom pw_geom(int Co) {
+  PwGeom g;
+  g.npad = (Co + 31) / 32 * 32;
+  if (g.npad > kPwMaxCoTile) g.npad = kPwMaxCoTile;
+  g.co_tiles = (Co + g.npad - 1) / g.npad;
+  g.cpad = g.co_tiles * g.npad;
+  return g;
+}
+
+int validate_pw(const dwbnq_pwconv_desc *d) {
+  if (!d) return fail(DWBNQ_ERR_INVALID_ARG, "pointwise conv desc is null");
+  if (d->dtype != DWBNQ_F32 && d->dtype != DWBNQ_F16)
+    return fail(DWBNQ_ERR_INVALID_ARG, "dtype %d is neither DWBNQ_F32 nor DWBNQ_F16", d->dtype);
+  if (d->n < 0 || d->c_in <= 0 || d->c_out <= 0 || d->h <= 0 || d->w <= 0)
+    return fail(DWBNQ_ERR_INVALID_ARG, "shape [%lld,%d->%d,%d,%d] is not positive", (long long)d->n, d->c_in, d->c_out, d->h, d->w);
+  if (d->math != DWBNQ_PW_MATH_FP32 && d->math != DWBNQ_PW_MATH_TF32)
+    return fail(DWBNQ_ERR_INVALID_ARG, "math %d is not a dwbnq_pw_math", d->math);
+  if (d->act < DWBNQ_ACT_NONE || d->act > DWBNQ_ACT_RELU6) return fail(DWBNQ_ERR_INVALID_ARG, "act %d is not a dwbnq_act", d->act);
+  if ((long long)d->h * d->w > 0x7fffffffLL || d->n > 0x7fffffffLL)
+    return fail(DWBNQ_ERR_UNSUPPORTED, "plane or batch beyond 2^31 - 1 elements");
+  return DWBNQ_OK;
+}
+
+bool pw_tc_eligible(const dwbnq_pwconv_desc &d, const void *x, const void *w) {
+  const long long hw = (long long)d.h * d.w;
+  return d.dtype == DWBNQ_F32 && hw % 4 == 0 && d.c_in % 4 == 0 && ((uintptr_t)x & 15) == 0 &&
+         (d.math == DWBNQ_PW_MATH_FP32 || ((uintptr_t)w & 15) == 0);
+}
+
+template <bool MATH3>
+cudaError_t launch_pw_tc(int epi, dim3 grid, size_t smem, cudaStream_t stream, const CUtensorMap &tx, const CUtensorMap &tw,
+                         const CUtensorMap &twl, const PwArgs &a) {
+  void (*k)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const PwArgs) =
+      epi == PW_EPI_BIAS ? pw_tc_kernel<MATH3, PW_EPI_BIAS>
+                         : epi == PW_EPI_BN_FPQ ? pw_tc_kernel<MATH3, PW_EPI_BN_FPQ> : pw_tc_kernel<MATH3, PW_EPI_GENERIC>;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kPwSmemMax);
+  if (e != cudaSuccess) return e;
+  k<<<grid, kPwThreads, smem, stream>>>(tx, tw, twl, a);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+int launch_pwconv(const dwbnq_pwconv_desc &d, float bn_eps, const dwbnq_quant_desc *q, const void *x, const void *w,
+                  const void *b, const void *beta, const void *gamma, const void *mean, const void *var, void *y,
+                  void *workspace, int dev, cudaStream_t stream) {
+  const int kind = q ? q->kind : DWBNQ_Q_NONE;
+  if (kind != DWBNQ_Q_NONE && kind != DWBNQ_Q_FPQ && kind != DWBNQ_Q_POW2)
+    return fail(DWBNQ_ERR_UNSUPPORTED, "pointwise convolution fuses FixedPointQuantize or Pow2Quantize only (kind %d)", kind);
+  if (mean && !var) return fail(DWBNQ_ERR_INVALID_ARG, "bn_var is null although bn_mean is given");
+  if (d.n == 0) return DWBNQ_OK;
+  if (!x || !w || !y || !workspace) return fail(DWBNQ_ERR_INVALID_ARG, "x, w, y and workspace must not be null");
+  if ((uintptr_t)workspace & 255) return fail(DWBNQ_ERR_INVALID_ARG, "workspace must be 256-byte aligned");
+  const int elem = d.dtype == DWBNQ_F32 ? 4 : 2;
+  if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & (elem - 1)) return fail(DWBNQ_ERR_INVALID_ARG, "tensor pointers must be element-aligned");
+
+  QuantArgs qa;
+  std::memset(&qa, 0, sizeof(qa));
+  int st = DWBNQ_OK;
+  if (kind == DWBNQ_Q_FPQ) st = fill_fpq(&qa, q->sign, q->n, q->delta);
+  else if (kind == DWBNQ_Q_POW2) st = fill_pow2(&qa, q->sign, q->with_zero, q->n, q->m, dev);
+  if (st != DWBNQ_OK) return st;
+
+  const PwGeom g = pw_geom(d.c_out);
+  const int HW = d.h * d.w;
+  const long long wsize = (long long)d.c_in * d.c_out;
+  float *coef = static_cast<float *>(workspace);
+  float *w_hi = reinterpret_cast<float *>(static_cast<char *>(workspace) + align256((size_t)5 * g.cpad * 4));
+  float *w_lo = reinterpret_cast<float *>(reinterpret_cast<char *>(w_hi) + align256((size_t)wsize * 4));
+
+  const int forced = forced_pw_path();
+  const bool eligible = pw_tc_eligible(d, x, w);
+  if (forced == 1 && !eligible) return fail(DWBNQ_ERR_UNSUPPORTED, "the tcgen05 kernel cannot take this shape / alignment");
+  const bool tc = forced == 0 ? false : eligible;
+  const bool math3 = tc && d.math == DWBNQ_PW_MATH_FP32;
+
+  {
+    const long long work = math3 ? (wsize > g.cpad ? wsize : g.cpad) : g.cpad;
+    const unsigned blocks = (unsigned)((work + 255) / 256);
+    if (d.dtype == DWBNQ_F32)
+      pw_prepare_kernel<float><<<blocks, 256, 0, stream>>>(
+          static_cast<const float *>(w), static_cast<const float *>(b), static_cast<const float *>(beta),
+          static_cast<const float *>(gamma), static_cast<const float *>(mean), static_cast<const float *>(var), bn_eps,
+          d.c_out, g.cpad, wsize, coef, math3 ? w_hi : nullptr, w_lo);
+    else
+      pw_prepare_kernel<__half><<<blocks, 256, 0, stream>>>(
+          static_cast<const __half *>(w), static_cast<const __half *>(b), static_cast<const __half *>(beta),
+          static_cast<const __half *>(gamma), static_cast<const __half *>(mean), static_cast<const __half *>(var), bn_eps,
+          d.c_out, g.cpad, wsize, coef, nullptr, nullptr);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail_cuda(e, "pw_prepare_kernel launch");
+  }
+
+  if (!tc) {
+    PwSimtArgs a;
+    std::memset(&a, 0, sizeof(a));
+    a.x = x; a.w = w; a.y = y; a.coef = coef;
+    a.HW = HW; a.Ci = d.c_in; a.Co = d.c_out; a.cpad = g.cpad;
+    a.pos_tiles = (HW + 63) / 64;
+    a.has_bn = mean != nullptr; a.act = d.act; a.qkind = kind; a.q = qa;
+    const long long gx = d.n * a.pos_tiles;
+    if (gx > 0x7fffffffLL) return fail(DWBNQ_ERR_UNSUPPORTED, "batch x position tiles beyond 2^31 - 1");
+    const dim3 grid((unsigned)gx, (unsigned)((d.c_out + 63) / 64));
+    if (d.dtype == DWBNQ_F32) pw_simt_kernel<float><<<grid, 256, 0, stream>>>(a);
+    else pw_simt_kernel<__half><<<grid, 256, 0, stream>>>(a);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail_cuda(e, "pw_simt_kernel launch");
+    return DWBNQ_OK;
+  }
+
+  PwArgs a;
+  std::memset(&a, 0, sizeof(a));
+  a.HW = HW; a.Ci = d.c_in; a.Co = d.c_out; a.N = d.n;
+  a.npad = g.npad; a.co_tiles = g.co_tiles;
+  a.pos_tiles = (HW + kPwPosTile - 1) / kPwPosTile;
+  a.kchunks = (d.c_in + kPwKChunk - 1) / kPwKChunk;
+  a.total_tiles = (long long)a.co_tiles * d.n * a.pos_tiles;
+  a.stage_bytes = (kPwXBytes + g.npad * 128) * (math3 ? 2 : 1);
+  const int table_bytes = kPwEpiWarps * (kPwMaxCoTile / 4) * (int)sizeof(PwPair);
+  a.stages = (kPwSmemMax - 1024 - table_bytes) / a.stage_bytes;
+  if (a.stages > kPwMaxStages) a.stages = kPwMaxStages;
+  if (a.stages < 2) return fail(DWBNQ_ERR_UNSUPPORTED, "pipeline stage of %d bytes does not fit twice", a.stage_bytes);
+  a.coef = coef;
+  a.y = static_cast<float *>(y);
+  st = device_flag_ptr(dev, &a.flag);
+  if (st != DWBNQ_OK) return st;
+  a.has_bn = mean != nullptr; a.act = d.act; a.qkind = kind; a.q = qa;
+
+  PwEncodeFn enc = pw_encode_fn();
+  if (!enc) return fail(DWBNQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  CUtensorMap tx, tw, twl;
+  {
+    const cuuint64_t gdim[3] = {(cuuint64_t)HW, (cuuint64_t)d.c_in, (cuuint64_t)d.n};
+    const cuuint64_t gstr[2] = {(cuuint64_t)HW * 4, (cuuint64_t)HW * d.c_in * 4};
+    const cuuint32_t box[3] = {32, (cuuint32_t)kPwKChunk, 1}, es[3] = {1, 1, 1};
+    const CUresult r = enc(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void *>(x), gdim, gstr, box, es,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(DWBNQ_ERR_CUDA, "cuTensorMapEncodeTiled(x) failed with CUresult %d", (int)r);
+  }
+  for (int k = 0; k < 2; ++k) {
+    const void *src = math3 ? (k ? w_lo : w_hi) : w;
+    const cuuint64_t gdim[2] = {(cuuint64_t)d.c_in, (cuuint64_t)d.c_out};
+    const cuuint64_t gstr[1] = {(cuuint64_t)d.c_in * 4};
+    const cuuint32_t box[2] = {(cuuint32_t)kPwKChunk, (cuuint32_t)g.npad}, es[2] = {1, 1};
+    const CUresult r = enc(k ? &twl : &tw, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(src), gdim, gstr, box, es,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(DWBNQ_ERR_CUDA, "cuTensorMapEncodeTiled(w) failed with CUresult %d", (int)r);
+  }
+  int epi = PW_EPI_GENERIC;
+  if (!a.has_bn && kind == DWBNQ_Q_NONE) epi = PW_EPI_BIAS;
+  else if (a.has_bn && kind == DWBNQ_Q_FPQ && qa.fpq_fast && !(qa.fpq_min < 0.0f)) epi = PW_EPI_BN_FPQ;
+  const size_t smem = (size_t)a.stages * a.stage_bytes + table_bytes + 1024;
+  const int sms = sm_count(dev);
+  const long long grid = a.total_tiles < sms ? a.total_tiles : sms;
+  const cudaError_t e = math3 ? launch_pw_tc<true>(epi, dim3((unsigned)grid), smem, stream, tx, tw, twl, a)
+                              : launch_pw_tc<false>(epi, dim3((unsigned)grid), smem, stream, tx, tw, twl, a);
+  if (e != cudaSuccess) return fail_cuda(e, "pw_tc_kernel launch");
+  return DWBNQ_OK;
+}
+
+size_t pwconv_workspace_bytes(const dwbnq_pwconv_desc &d) {
+  const PwGeom g = pw_geom(d.c_out);
+  return align256((size_t)5 * g.cpad * 4) + 2 * align256((size_t)d.c_in * d.c_out * 4);
+}
+int pwconv_validate(const dwbnq_pwconv_desc *d) { return validate_pw(d); }
+int pwconv_path(const dwbnq_pwconv_desc &d, const void *x, const void *w) {
+  const int forced = forced_pw_path();
+  return forced == 0 ? 0 : (pw_tc_eligible(d, x, w) ? 1 : 0);
+}
+void set_forced_pw_path(int p) { t_forced_pw = p; }
+
+}  // namespace dwbnq

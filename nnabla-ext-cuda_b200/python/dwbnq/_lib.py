@@ -37,6 +37,16 @@ class MinMaxPtrs(ctypes.Structure):
                 ("ql_min", ctypes.c_void_p), ("ql_max", ctypes.c_void_p)]
 
 
+class PwConvDesc(ctypes.Structure):
+    _fields_ = [("dtype", ctypes.c_int32), ("c_in", ctypes.c_int32), ("c_out", ctypes.c_int32),
+                ("h", ctypes.c_int32), ("w", ctypes.c_int32), ("n", ctypes.c_int64),
+                ("math", ctypes.c_int32), ("act", ctypes.c_int32)]
+
+
+PW_MATH_FP32, PW_MATH_TF32 = 0, 1
+ACT_NONE, ACT_RELU, ACT_RELU6 = 0, 1, 2
+
+
 class Code8Desc(ctypes.Structure):
     _fields_ = [("in_signed", ctypes.c_int32), ("in_delta", ctypes.c_float)]
 
@@ -81,6 +91,12 @@ SIGNATURES = {
     "dwbnq_dequantize_linear_code8_fwd": (_int, [_int, _i64, _flt, _int, _int, _vp, _vp, _int, _vp]),
     "dwbnq_fused_fwd_code8": (_int, [_P(ConvDesc), _flt, _P(QuantDesc), _P(Code8Desc), _vp, _vp, _vp, _vp, _vp,
                                      _vp, _vp, _vp, _int, _vp]),
+    "dwbnq_pwconv_workspace_bytes": (ctypes.c_size_t, [_P(PwConvDesc)]),
+    "dwbnq_pwconv_fwd": (_int, [_P(PwConvDesc), _vp, _vp, _vp, _vp, _vp, _int, _vp]),
+    "dwbnq_pwconv_fused_fwd": (_int, [_P(PwConvDesc), _flt, _P(QuantDesc), _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                      _int, _vp]),
+    "dwbnq_pwconv_plan": (_int, [_P(PwConvDesc), _vp, _vp, _P(_int)]),
+    "dwbnq_set_forced_pw_path": (_int, [_int]),
     "dwbnq_fused_plan": (_int, [_P(ConvDesc), _vp, _vp, _P(_int), _P(_int), _P(_int), _P(_int),
                                 _P(_i64), _P(_int)]),
     "dwbnq_set_forced_path": (_int, [_int]),

@@ -313,6 +313,70 @@ def fused_dw_bn_quant_code8(x_codes, in_delta, w, b, beta, gamma, mean, variance
     return y
 
 
+_ACTS = {None: L.ACT_NONE, "none": L.ACT_NONE, "relu": L.ACT_RELU, "relu6": L.ACT_RELU6}
+_MATHS = {"fp32": L.PW_MATH_FP32, "tf32": L.PW_MATH_TF32}
+
+
+def pwconv_desc(x, w, base_axis=1, math="fp32", act=None):
+    """PwConvDesc for x [..., c_in, h, w] and a Convolution weight w [c_out, c_in, 1, 1] (or [c_out, c_in])."""
+    if x.dim() != base_axis + 3:
+        raise ValueError("pointwise convolution takes [..., c_in, h, w]")
+    if w.dim() not in (2, 4) or (w.dim() == 4 and tuple(w.shape[2:]) != (1, 1)) or w.shape[1] != x.shape[base_axis]:
+        raise ValueError("weight %s is not a 1x1 kernel over %d input channels" % (tuple(w.shape), x.shape[base_axis]))
+    if x.dtype != w.dtype:
+        raise TypeError("x and w must have one dtype")
+    n = 1
+    for s in x.shape[:base_axis]:
+        n *= int(s)
+    d = L.PwConvDesc(dtype=_dtype_code(x), c_in=int(w.shape[1]), c_out=int(w.shape[0]), h=int(x.shape[base_axis + 1]),
+                     w=int(x.shape[base_axis + 2]), n=n, math=_MATHS[math], act=_ACTS[act])
+    return d, tuple(x.shape[:base_axis]) + (int(w.shape[0]),) + tuple(x.shape[base_axis + 1:])
+
+
+def pwconv_workspace(x, w, base_axis=1):
+    """A workspace tensor of the size the pointwise entry points ask for."""
+    d, _ = pwconv_desc(x, w, base_axis)
+    nbytes = int(L.lib().dwbnq_pwconv_workspace_bytes(ctypes.byref(d)))
+    return torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+
+
+def pointwise_convolution(x, w, b=None, base_axis=1, math="fp32", ws=None, out=None):
+    """Convolution with a 1x1 kernel (pad 0, stride 1, dilation 1, group 1): y = w * x + b."""
+    dev = _chk_cuda(x, w, b, out, ws)
+    d, oshape = pwconv_desc(x, w, base_axis, math)
+    ws = ws if ws is not None else pwconv_workspace(x, w, base_axis)
+    y = out if out is not None else torch.empty(oshape, dtype=x.dtype, device=dev)
+    L.check(L.lib().dwbnq_pwconv_fwd(ctypes.byref(d), _ptr(x), _ptr(w), _ptr(b), _ptr(y), _ptr(ws), dev.index, _stream(dev)))
+    return y
+
+
+def fused_pw_bn_quant(x, w, b, beta, gamma, mean, variance, eps=1e-5, quant=None, act=None, base_axis=1, math="fp32",
+                      ws=None, out=None):
+    """quantizer(act(BN_inference(pointwise_convolution(x)))) in one kernel. ``mean is None`` skips
+    BatchNormalization; ``act`` is None, "relu" or "relu6"; ``quant`` a "fpq" / "pow2" dict or None."""
+    dev = _chk_cuda(x, w, b, beta, gamma, mean, variance, out, ws)
+    d, oshape = pwconv_desc(x, w, base_axis, math, act)
+    q = quant_desc(quant)
+    ws = ws if ws is not None else pwconv_workspace(x, w, base_axis)
+    y = out if out is not None else torch.empty(oshape, dtype=x.dtype, device=dev)
+    L.check(L.lib().dwbnq_pwconv_fused_fwd(ctypes.byref(d), float(eps), ctypes.byref(q), _ptr(x), _ptr(w), _ptr(b), _ptr(beta),
+                                           _ptr(gamma), _ptr(mean), _ptr(variance), _ptr(y), _ptr(ws), dev.index,
+                                           _stream(dev)))
+    return y
+
+
+def pwconv_plan(x, w, base_axis=1, math="fp32"):
+    """1 when the tcgen05 kernel takes this call, 0 for the plain FMA kernel (diagnostic)."""
+    d, _ = pwconv_desc(x, w, base_axis, math)
+    path = ctypes.c_int()
+    L.check(L.lib().dwbnq_pwconv_plan(ctypes.byref(d), _ptr(x), _ptr(w), ctypes.byref(path)))
+    return path.value
+
+
+def set_forced_pw_path(path):
+    L.check(L.lib().dwbnq_set_forced_pw_path(int(path)))
+
+
 def fused_plan(x, w, y=None, base_axis=1, pad=None, stride=None, dilation=None, multiplier=1):
     """Kernel family and tile geometry the library would choose (diagnostic)."""
     d, _ = conv_desc(x, w, base_axis, pad, stride, dilation, multiplier)

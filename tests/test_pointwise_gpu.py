@@ -1,0 +1,221 @@
+"""Pointwise (1x1) convolution with the fused BN / activation / quantizer epilogue, through the
+C ABI, against the CPU oracle.
+
+The order of a convolution's sum is the implementation's own (the reference leaves it to its
+GEMM library), so the convolution is checked within a stated tolerance of the sum accumulated
+in double, relative to sum |w||x|:
+  * three-pass TF32 (math "fp32"): 4e-6 - 2^-21 per product from the truncated low halves
+    plus the dropped lo*lo term, and the fp32 accumulation;
+  * single-pass TF32: 2^-9 (both factors truncated to 11 significant bits);
+  * the FMA kernel: (c_in + 4) * 2^-24, an fp32 accumulation in any order.
+Everything after the sum is exact arithmetic: the fused result must equal, bit for bit, the
+oracle's BN -> activation -> quantizer applied to the convolution the same kernel returns
+unfused. The fused result is also bracketed by the oracle epilogue of (double sum -/+
+tolerance), which ties it to the inputs without relying on the kernel's own convolution."""
+import numpy as np
+import pytest
+import torch
+
+from dwbnq import _lib as L
+from dwbnq import ops
+
+pytestmark = pytest.mark.gpu
+
+FPQ_U = {"kind": "fpq", "sign": False, "n": 8, "delta": 2.0 ** -3}
+FPQ_S = {"kind": "fpq", "sign": True, "n": 8, "delta": 2.0 ** -4}
+FPQ_ODD = {"kind": "fpq", "sign": False, "n": 6, "delta": 0.0371}
+POW2 = {"kind": "pow2", "sign": True, "with_zero": True, "n": 8, "m": 1}
+
+
+def dev(a, device):
+    return None if a is None else torch.from_numpy(np.ascontiguousarray(a)).to(device)
+
+
+def make(rng, n, ci, co, h, w, bias=True, dtype=np.float32):
+    d = {
+        "x": np.minimum(np.maximum(rng.standard_normal((n, ci, h, w), dtype=np.float32) * 2, -1), 6),
+        "w": (rng.standard_normal((co, ci, 1, 1), dtype=np.float32) / np.sqrt(ci)).astype(np.float32),
+        "b": (rng.standard_normal(co, dtype=np.float32) * 0.3) if bias else None,
+        "mean": rng.standard_normal(co, dtype=np.float32) * 0.3,
+        "var": (0.5 + rng.random(co, dtype=np.float32)),
+        "gamma": (0.8 + 0.4 * rng.random(co, dtype=np.float32)) * np.where(rng.random(co) < 0.1, -1, 1).astype(np.float32),
+        "beta": rng.standard_normal(co, dtype=np.float32) * 0.3,
+    }
+    return {k: (None if v is None else v.astype(dtype)) for k, v in d.items()}
+
+
+def conv_tolerance(path, math, ci):
+    if path == 0:
+        return (ci + 4) * 2.0 ** -24
+    return 4e-6 if math == "fp32" else 2.0 ** -9
+
+
+def f32(a):
+    return None if a is None else np.asarray(a, dtype=np.float32)
+
+
+def check_conv(oracle, got, d, tol, half=False):
+    _, acc64, mag = oracle.pwconv(f32(d["x"]), f32(d["w"]), f32(d["b"]), nthreads=oracle.max_threads())
+    err = np.abs(got.astype(np.float64) - acc64.astype(np.float64))
+    bound = tol * mag.astype(np.float64) + 1e-30
+    if half:
+        bound = bound + np.abs(acc64) * 2.0 ** -11 + 2.0 ** -25
+    worst = float((err / bound).max())
+    assert worst <= 1.0, "convolution off by %.3g times the tolerance" % worst
+    return acc64, mag
+
+
+def bracket(oracle, acc64, mag, tol, d, eps, act, quant):
+    lo = oracle.pw_epilogue(acc64 - (tol * mag).astype(np.float32) - 1e-30, f32(d["beta"]), f32(d["gamma"]), f32(d["mean"]),
+                            f32(d["var"]), eps, act, quant)
+    hi = oracle.pw_epilogue(acc64 + (tol * mag).astype(np.float32) + 1e-30, f32(d["beta"]), f32(d["gamma"]), f32(d["mean"]),
+                            f32(d["var"]), eps, act, quant)
+    return np.minimum(lo, hi), np.maximum(lo, hi)
+
+
+SHAPES = [
+    # n, ci, co, h, w
+    (2, 32, 64, 16, 16),     # one k chunk, one channel tile, full tiles
+    (3, 24, 144, 12, 10),    # c_in not a multiple of 32, 144 channels -> 160 columns, ragged positions
+    (1, 96, 24, 28, 28),     # 24 channels in a 32-column tile
+    (2, 20, 40, 6, 6),       # c_in multiple of 4 only, one partial tile
+    (1, 4, 8, 2, 2),         # smallest TMA-able shape
+    (2, 192, 320, 14, 14),   # two channel tiles (256 + 64), six k chunks
+    (1, 960, 160, 14, 14),   # more k chunks than pipeline stages
+    (2, 64, 384, 14, 14),    # 384 = 256 + 128
+    (5, 16, 96, 28, 28),     # several tiles per CTA in a small grid
+]
+
+
+@pytest.mark.parametrize("math", ["fp32", "tf32"])
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_tensor_core_kernel(oracle, cuda_device, shape, math):
+    n, ci, co, h, w = shape
+    rng = np.random.default_rng(sum(shape))
+    d = make(rng, *shape)
+    t = {k: dev(v, cuda_device) for k, v in d.items()}
+    assert ops.pwconv_plan(t["x"], t["w"], math=math) == 1
+    tol = conv_tolerance(1, math, ci)
+    conv = ops.pointwise_convolution(t["x"], t["w"], t["b"], math=math)
+    torch.cuda.synchronize()
+    ops.check_device_flag()
+    got_conv = conv.cpu().numpy()
+    acc64, mag = check_conv(oracle, got_conv, d, tol)
+    eps = 1e-5
+    for quant, act, bn in ((FPQ_U, "relu6", True), (FPQ_U, None, True), (FPQ_S, None, True), (POW2, "relu", True),
+                           (None, "relu6", True), (FPQ_U, None, False), (FPQ_ODD, "relu6", True)):
+        m, v, g, be = (t["mean"], t["var"], t["gamma"], t["beta"]) if bn else (None,) * 4
+        y = ops.fused_pw_bn_quant(t["x"], t["w"], t["b"], be, g, m, v, eps, quant, act, math=math)
+        torch.cuda.synchronize()
+        ops.check_device_flag()
+        got = y.cpu().numpy()
+        dd = d if bn else dict(d, mean=None, var=None, gamma=None, beta=None)
+        want = oracle.pw_epilogue(got_conv, dd["beta"], dd["gamma"], dd["mean"], dd["var"], eps, act, quant)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (quant, act, bn)
+        lo, hi = bracket(oracle, acc64, mag, tol, dd, eps, act, quant)
+        assert np.all((got >= lo) & (got <= hi)), (quant, act, bn)
+
+
+def test_no_bias_and_partial_bn_vectors(oracle, cuda_device):
+    rng = np.random.default_rng(5)
+    d = make(rng, 2, 32, 48, 8, 8, bias=False)
+    t = {k: dev(v, cuda_device) for k, v in d.items()}
+    conv = ops.pointwise_convolution(t["x"], t["w"], None).cpu().numpy()
+    check_conv(oracle, conv, d, 4e-6)
+    for beta, gamma in ((None, t["gamma"]), (t["beta"], None), (None, None)):
+        y = ops.fused_pw_bn_quant(t["x"], t["w"], None, beta, gamma, t["mean"], t["var"], 1e-3, FPQ_U, "relu6")
+        want = oracle.pw_epilogue(conv, None if beta is None else d["beta"], None if gamma is None else d["gamma"],
+                                  d["mean"], d["var"], 1e-3, "relu6", FPQ_U)
+        assert np.array_equal(y.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    ops.check_device_flag()
+
+
+FMA_SHAPES = [(2, 32, 64, 7, 7), (3, 30, 50, 5, 9), (1, 3, 5, 1, 1), (2, 160, 70, 7, 7), (2, 17, 130, 14, 14)]
+
+
+@pytest.mark.parametrize("shape", FMA_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_fma_kernel_takes_every_other_shape(oracle, cuda_device, shape):
+    n, ci, co, h, w = shape
+    rng = np.random.default_rng(sum(shape))
+    d = make(rng, *shape)
+    t = {k: dev(v, cuda_device) for k, v in d.items()}
+    assert ops.pwconv_plan(t["x"], t["w"]) == 0
+    tol = conv_tolerance(0, "fp32", ci)
+    got_conv = ops.pointwise_convolution(t["x"], t["w"], t["b"]).cpu().numpy()
+    acc64, mag = check_conv(oracle, got_conv, d, tol)
+    for quant, act in ((FPQ_U, "relu6"), (POW2, None), (None, "relu")):
+        y = ops.fused_pw_bn_quant(t["x"], t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], 1e-5, quant, act)
+        want = oracle.pw_epilogue(got_conv, d["beta"], d["gamma"], d["mean"], d["var"], 1e-5, act, quant)
+        assert np.array_equal(y.cpu().numpy().view(np.uint32), want.view(np.uint32)), (quant, act)
+    ops.check_device_flag()
+
+
+def test_fp16_tensors(oracle, cuda_device):
+    rng = np.random.default_rng(11)
+    for shape in ((2, 32, 64, 14, 14), (1, 24, 40, 7, 7)):
+        d = make(rng, *shape, dtype=np.float16)
+        t = {k: dev(v, cuda_device) for k, v in d.items()}
+        assert ops.pwconv_plan(t["x"], t["w"]) == 0
+        tol = conv_tolerance(0, "fp32", shape[1])
+        got = ops.pointwise_convolution(t["x"], t["w"], t["b"])
+        assert got.dtype == torch.float16
+        acc64, mag = check_conv(oracle, got.cpu().numpy().astype(np.float32), d, tol, half=True)
+        y = ops.fused_pw_bn_quant(t["x"], t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], 1e-5, FPQ_U, "relu6")
+        lo, hi = bracket(oracle, acc64, mag, tol, d, 1e-5, "relu6", FPQ_U)
+        g = y.cpu().numpy()
+        assert np.all((g >= lo.astype(np.float16)) & (g <= hi.astype(np.float16)))
+    ops.check_device_flag()
+
+
+def test_forced_kernel_choice_and_the_two_kernels_agree(oracle, cuda_device):
+    rng = np.random.default_rng(2)
+    d = make(rng, 2, 64, 96, 14, 14)
+    t = {k: dev(v, cuda_device) for k, v in d.items()}
+    try:
+        ops.set_forced_pw_path(0)
+        assert ops.pwconv_plan(t["x"], t["w"]) == 0
+        fma = ops.pointwise_convolution(t["x"], t["w"], t["b"]).cpu().numpy()
+        ops.set_forced_pw_path(1)
+        tc = ops.pointwise_convolution(t["x"], t["w"], t["b"]).cpu().numpy()
+        odd = dev(rng.standard_normal((1, 64, 7, 7), dtype=np.float32), cuda_device)
+        with pytest.raises(L.DwbnqError) as e:
+            ops.pointwise_convolution(odd, t["w"], t["b"])
+        assert e.value.status == 2
+    finally:
+        ops.set_forced_pw_path(-1)
+    _, acc64, mag = oracle.pwconv(d["x"], d["w"], d["b"])
+    assert np.all(np.abs(fma - tc) <= (4e-6 + 68 * 2.0 ** -24) * mag)
+    ops.check_device_flag()
+
+
+def test_argument_errors(cuda_device):
+    x = torch.zeros(1, 8, 4, 4, device=cuda_device)
+    w = torch.zeros(16, 8, 1, 1, device=cuda_device)
+    with pytest.raises(ValueError):
+        ops.pointwise_convolution(x, torch.zeros(16, 8, 3, 3, device=cuda_device))
+    with pytest.raises(L.DwbnqError) as e:  # MinMaxQuantize cannot be fused here
+        ops.fused_pw_bn_quant(x, w, None, None, None, None, None, quant={"kind": "minmax"})
+    assert e.value.status == 2
+    d, _ = ops.pwconv_desc(x, w)
+    d.math = 7
+    assert L.lib().dwbnq_pwconv_workspace_bytes(d) == 0
+    # an empty batch is a no-op
+    y = ops.pointwise_convolution(torch.zeros(0, 8, 4, 4, device=cuda_device), w)
+    assert tuple(y.shape) == (0, 16, 4, 4)
+
+
+@pytest.mark.parametrize("layer", [(112, 32, 16), (56, 96, 24), (28, 144, 32), (14, 384, 64), (14, 96, 576)],
+                         ids=lambda l: "%dx%d_%dto%d" % (l[0], l[0], l[1], l[2]))
+def test_mobilenet_layers_at_eight_images(oracle, cuda_device, layer):
+    hw, ci, co = layer
+    rng = np.random.default_rng(hw + ci)
+    d = make(rng, 8, ci, co, hw, hw)
+    t = {k: dev(v, cuda_device) for k, v in d.items()}
+    ws = ops.pwconv_workspace(t["x"], t["w"])
+    conv = ops.pointwise_convolution(t["x"], t["w"], t["b"], ws=ws).cpu().numpy()
+    check_conv(oracle, conv, d, 4e-6)
+    y = ops.fused_pw_bn_quant(t["x"], t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], 1e-5, FPQ_U, "relu6", ws=ws)
+    want = oracle.pw_epilogue(conv, d["beta"], d["gamma"], d["mean"], d["var"], 1e-5, "relu6", FPQ_U,
+                              nthreads=oracle.max_threads())
+    assert np.array_equal(y.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    ops.check_device_flag()
