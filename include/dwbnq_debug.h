@@ -32,6 +32,10 @@ int dwbnq_set_tuning(int planes_per_cta, int row_blocks_per_tile, int threads, i
  * calls: -1 automatic, 0 the plain FMA kernel, 1 the tcgen05 kernel (a shape it cannot take
  * then fails with DWBNQ_ERR_UNSUPPORTED). DWBNQ_PW_FORCE=simt|tc sets the default. */
 int dwbnq_set_forced_pw_path(int path);
+/* Upper bound on the CTAs of the tcgen05 pointwise kernel for this thread's calls (0 = one per
+ * SM): with a few CTAs a small tensor already makes every CTA walk through many tiles, which
+ * is what exercises the reuse of pipeline stages and accumulator buffers. */
+int dwbnq_set_pw_max_ctas(int ctas);
 /* Launches one warp that waits, with the bounded wait every copy-engine kernel of the
  * library uses, on a shared-memory barrier that nothing ever completes, with the limit
  * shortened to `limit_us` microseconds. The wait runs out, the kernel records it in the

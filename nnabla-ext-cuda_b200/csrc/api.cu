@@ -271,6 +271,13 @@ int dwbnq_set_forced_pw_path(int path) {
   return DWBNQ_OK;
 }
 
+int dwbnq_set_pw_max_ctas(int ctas) {
+  clear_error();
+  if (ctas < 0) return fail(DWBNQ_ERR_INVALID_ARG, "ctas %d is negative", ctas);
+  set_pw_max_ctas(ctas);
+  return DWBNQ_OK;
+}
+
 int dwbnq_set_forced_path(int path) {
   clear_error();
   if (path < PATH_AUTO || path > PATH_PLANE_GEN) return fail(DWBNQ_ERR_INVALID_ARG, "path %d is not -1..5", path);

@@ -137,6 +137,7 @@ size_t pwconv_workspace_bytes(const dwbnq_pwconv_desc &d);
 // 1 = the tcgen05 kernel, 0 = the plain FMA kernel (thread's forced choice included).
 int pwconv_path(const dwbnq_pwconv_desc &d, const void *x, const void *w);
 void set_forced_pw_path(int p);
+void set_pw_max_ctas(int n);
 // Prepares the per-channel coefficients (and the TF32 halves of w) in `workspace`, then runs
 // the convolution with the fused epilogue. BN is skipped when mean is null; q may be null.
 int launch_pwconv(const dwbnq_pwconv_desc &d, float bn_eps, const dwbnq_quant_desc *q, const void *x, const void *w,

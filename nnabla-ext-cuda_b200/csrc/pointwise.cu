@@ -28,8 +28,11 @@ namespace dwbnq {
 
 namespace {
 
-constexpr int kPwThreads = 384;
-constexpr int kPwFirstEpiWarp = 4, kPwEpiWarps = 8;
+constexpr int kPwFirstEpiWarp = 4, kPwEpiGroups = 4, kPwEpiWarps = 4 * kPwEpiGroups;
+constexpr int kPwThreads = 32 * (kPwFirstEpiWarp + kPwEpiWarps);
+constexpr int kPwTmemCols = 512;           // the whole tensor memory of the SM (one CTA per SM)
+constexpr int kPwMaxAcc = 8;               // accumulator buffers in flight
+constexpr int kPwMaxCout = 4096;           // channel pairs of the coefficient table: 48 bytes each
 constexpr int kPwPosTile = 128;            // accumulator rows = TMEM lanes
 constexpr int kPwKChunk = 32;              // fp32 elements of c_in per pipeline stage
 constexpr int kPwXBytes = kPwPosTile * kPwKChunk * 4;  // 4 boxes of [32 k][32 positions]
@@ -40,10 +43,9 @@ constexpr unsigned long long kPwWaitNs = 2000000000ull;
 
 enum PwEpi : int { PW_EPI_BIAS = 0, PW_EPI_BN_FPQ = 1, PW_EPI_GENERIC = 2 };
 
-// Per pair of output channels, everything the epilogue needs (one 64-byte shared-memory row).
+// Per pair of output channels, everything the epilogue needs (three 16-byte shared-memory words).
 struct __align__(16) PwPair {
   f32x2 bias, nmean, scale, rcp, nstd, beta;
-  float stdvar_lo, stdvar_hi, glo, pad;
 };
 
 struct PwArgs {
@@ -53,6 +55,8 @@ struct PwArgs {
   int co_tiles, pos_tiles, kchunks;
   long long total_tiles;
   int stages, stage_bytes;
+  int nacc;       // accumulator buffers of npad columns in TMEM, a multiple of ngroups
+  int ngroups;    // epilogue groups in use (<= kPwEpiGroups): buffer b always belongs to group b % ngroups
   const float *coef;  // [5][co_tiles * npad]: bias, mean, scale, stdvar, beta
   float *y;
   int *flag;
@@ -118,16 +122,21 @@ __device__ __forceinline__ void tc_mma_tf32(unsigned int tmem_d, unsigned long l
       "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// 16 consecutive accumulator columns of this thread's lane (issue only; wait with tc_ld_wait).
-__device__ __forceinline__ void tc_ld16(unsigned int taddr, unsigned int *r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
+// 8 consecutive accumulator columns of this thread's lane (issue only; tc_ld_wait8 completes it).
+__device__ __forceinline__ void tc_ld8(unsigned int taddr, unsigned int *r) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
 }
-__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Waits for this thread's outstanding TMEM loads. The loaded registers are operands, so the
+// compiler cannot move a use of them above the wait.
+__device__ __forceinline__ void tc_ld_wait8(unsigned int *r) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])
+               :
+               : "memory");
+}
 
 // Shared-memory matrix descriptor of tcgen05.mma (addresses and offsets in bytes; the fields
 // hold them divided by 16). layout 2 = 128-byte swizzle, 1 = 128-byte swizzle of 32-byte
@@ -159,28 +168,7 @@ __device__ __forceinline__ float pw_act(float v, int act) {
   return v;
 }
 
-// Two adjacent channels of one position: accumulators in, final values out.
-template <int EPI>
-__device__ __forceinline__ void pw_finish_pair(float a0, float a1, const PwPair &cp, const PwArgs &a, f32x2 nz,
-                                               const FpqPacked &fq, float &r0, float &r1) {
-  f32x2 v = add2(pack2(a0, a1), cp.bias);
-  if (EPI == PW_EPI_BN_FPQ || (EPI == PW_EPI_GENERIC && a.has_bn)) {
-    BnPacked b;
-    b.nmean = cp.nmean; b.scale = cp.scale; b.rcp = cp.rcp; b.nstd = cp.nstd; b.beta = cp.beta; b.nz = nz;
-    b.stdvar = cp.stdvar_lo; b.stdvar_hi = cp.stdvar_hi; b.glo = cp.glo;
-    bn_apply_packed<1>(&v, b);
-  }
-  unpack2(v, r0, r1);
-  if (a.act) { r0 = pw_act(r0, a.act); r1 = pw_act(r1, a.act); }
-  if (EPI == PW_EPI_BN_FPQ) {
-    unpack2(fpq_apply_fast_unsigned2(r0, r1, a.q, fq), r0, r1);
-  } else if (EPI == PW_EPI_GENERIC) {
-    if (a.qkind == DWBNQ_Q_FPQ) { r0 = fpq_apply(r0, a.q); r1 = fpq_apply(r1, a.q); }
-    else if (a.qkind == DWBNQ_Q_POW2) { r0 = pow2_apply(r0, a.q); r1 = pow2_apply(r1, a.q); }
-  }
-}
-
-__device__ __forceinline__ PwPair pw_make_pair(const PwArgs &a, int cpad, int c) {
+__device__ __forceinline__ PwPair pw_make_pair(const PwArgs &a, int cpad, int c, bool *safe) {
   // c is even and c + 1 < cpad; padded channels hold neutral coefficients
   const BnCoef lo{a.coef[cpad + c], a.coef[2 * cpad + c], a.coef[3 * cpad + c], a.coef[4 * cpad + c]};
   const BnCoef hi{a.coef[cpad + c + 1], a.coef[2 * cpad + c + 1], a.coef[3 * cpad + c + 1], a.coef[4 * cpad + c + 1]};
@@ -188,8 +176,67 @@ __device__ __forceinline__ PwPair pw_make_pair(const PwArgs &a, int cpad, int c)
   PwPair p;
   p.bias = pack2(a.coef[c], a.coef[c + 1]);
   p.nmean = b.nmean; p.scale = b.scale; p.rcp = b.rcp; p.nstd = b.nstd; p.beta = b.beta;
-  p.stdvar_lo = b.stdvar; p.stdvar_hi = b.stdvar_hi; p.glo = b.glo; p.pad = 0.0f;
+  *safe = b.glo == DWBNQ_DIV_GUARD_LO;
   return p;
+}
+
+// Eight adjacent channels (four pairs) of one position: accumulators in, final values out.
+// BN divides through the packed reciprocal sequence of bn_apply_packed; one range test covers
+// the unit, and a unit that fails it (or a launch whose stdvar leaves the range the sequence
+// is proven for) takes the IEEE division.
+template <int EPI>
+__device__ __forceinline__ void pw_finish_unit(const unsigned int *acc, const PwPair *tp, const PwArgs &a, f32x2 nz,
+                                               const FpqPacked &fq, bool bn_safe, float *r) {
+  f32x2 v[4];
+  const bool bn = EPI == PW_EPI_BN_FPQ || (EPI == PW_EPI_GENERIC && a.has_bn);
+  if (bn) {
+    f32x2 t[4], nstd[4];
+    float mx = 0.0f, mn = __uint_as_float(0x7f800000u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const PwPair cp = tp[i];
+      const f32x2 s = add2(pack2(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1])), cp.bias);
+      t[i] = mul2(add2(s, cp.nmean), cp.scale, nz);
+      float lo, hi;
+      unpack2(t[i], lo, hi);
+      mx = max3f(mx, fabsf(lo), fabsf(hi));
+      mn = min3f(mn, fabsf(lo), fabsf(hi));
+      f32x2 q = mul2(t[i], cp.rcp, nz);
+      f32x2 e = fma2(q, cp.nstd, t[i]);
+      q = fma2(e, cp.rcp, q);
+      e = fma2(q, cp.nstd, t[i]);
+      v[i] = fma2(e, cp.rcp, q);
+      nstd[i] = cp.nstd;
+    }
+    if (!(bn_safe && mn > DWBNQ_DIV_GUARD_LO && mx < DWBNQ_DIV_GUARD_HI)) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float slo, shi;
+        unpack2(nstd[i], slo, shi);
+        v[i] = bn_div_cold(t[i], -slo, -shi);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = add2(v[i], tp[i].beta);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      v[i] = add2(pack2(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1])), tp[i].bias);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float r0, r1;
+    unpack2(v[i], r0, r1);
+    if (a.act) { r0 = pw_act(r0, a.act); r1 = pw_act(r1, a.act); }
+    if (EPI == PW_EPI_BN_FPQ) {
+      unpack2(fpq_apply_fast_unsigned2(r0, r1, a.q, fq), r0, r1);
+    } else if (EPI == PW_EPI_GENERIC) {
+      if (a.qkind == DWBNQ_Q_FPQ) { r0 = fpq_apply(r0, a.q); r1 = fpq_apply(r1, a.q); }
+      else if (a.qkind == DWBNQ_Q_POW2) { r0 = pow2_apply(r0, a.q); r1 = pow2_apply(r1, a.q); }
+    }
+    r[2 * i] = r0;
+    r[2 * i + 1] = r1;
+  }
 }
 
 // ---- the tcgen05 kernel ------------------------------------------------------------------------
@@ -199,21 +246,20 @@ __global__ void __launch_bounds__(kPwThreads, 1)
 pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
              const __grid_constant__ CUtensorMap tm_wlo, const PwArgs a) {
   extern __shared__ unsigned char pw_smem_raw[];
-  // full / empty / split per stage, then accumulator full[2] / empty[2]
-  __shared__ unsigned long long bars[3 * kPwMaxStages + 4];
+  // full / empty / split per stage, then accumulator full / empty per buffer
+  __shared__ unsigned long long bars[3 * kPwMaxStages + 2 * kPwMaxAcc];
   __shared__ unsigned int tmem_base_s;
-  __shared__ int abort_s;
+  __shared__ int abort_s, unsafe_s;
   unsigned long long *full = bars, *empty = bars + kPwMaxStages, *split = bars + 2 * kPwMaxStages;
-  unsigned long long *acc_full = bars + 3 * kPwMaxStages, *acc_empty = acc_full + 2;
+  unsigned long long *acc_full = bars + 3 * kPwMaxStages, *acc_empty = acc_full + kPwMaxAcc;
   const unsigned int base = (smem_u32(pw_smem_raw) + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
   unsigned char *sm = pw_smem_raw + (base - smem_u32(pw_smem_raw));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wbytes = a.npad * 128;
   const int off_xlo = kPwXBytes, off_w = MATH3 ? 2 * kPwXBytes : kPwXBytes, off_wlo = off_w + wbytes;
-  // after the stages: one coefficient table per epilogue warp
-  PwPair *tables = reinterpret_cast<PwPair *>(sm + (size_t)a.stages * a.stage_bytes);
-  unsigned int tmem_cols = 32;
-  while ((int)tmem_cols < 2 * a.npad) tmem_cols <<= 1;
+  const int cpad = a.co_tiles * a.npad;
+  // after the stages: the coefficient table of every channel pair
+  PwPair *table = reinterpret_cast<PwPair *>(sm + (size_t)a.stages * a.stage_bytes);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < a.stages; ++s) {
@@ -221,18 +267,29 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
       mbar_init(&empty[s], 1);
       mbar_init(&split[s], 64);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < a.nacc; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], kPwEpiWarps);
+      mbar_init(&acc_empty[b], 4);  // the four warps of one epilogue group
     }
     abort_s = 0;
+    unsafe_s = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
-                 "r"(tmem_cols)
+                 "r"(kPwTmemCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  __syncthreads();
+  {
+    bool all_safe = true;
+    for (int i = threadIdx.x; i < (cpad >> 1); i += kPwThreads) {
+      bool safe;
+      table[i] = pw_make_pair(a, cpad, 2 * i, &safe);
+      all_safe = all_safe && safe;
+    }
+    if (!all_safe) atomicOr(&unsafe_s, 1);
   }
   tc_fence_before();
   __syncthreads();
@@ -273,7 +330,7 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
     unsigned int it = 0, tile_i = 0;
     bool ok = true;
     for (long long t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x, ++tile_i) {
-      const unsigned int b = tile_i & 1u, aph = (tile_i >> 1) & 1u;
+      const unsigned int b = tile_i % a.nacc, aph = (tile_i / a.nacc) & 1u;
       ok = pw_wait(&acc_empty[b], aph ^ 1u);
       tc_fence_after();
       for (int kc = 0; ok && kc < a.kchunks; ++kc, ++it) {
@@ -337,28 +394,23 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
       if (!ok && lane == 0 && !*abort_v) { atomicExch(a.flag, 1); *abort_v = 1; }
     }
   } else {
-    // ---- epilogue: warp (quarter, half) owns lanes [32 quarter, +32) and half of the columns ----
-    const int ew = warp - kPwFirstEpiWarp, quarter = warp & 3, half = ew >> 2;
-    const int cols_half = a.npad >> 1;  // multiple of 16
-    const int cpad = a.co_tiles * a.npad;
-    PwPair *table = tables + (size_t)ew * (kPwMaxCoTile / 4);
+    // ---- epilogue: groups of four warps; group g takes the tiles g, g + ngroups, ... of this CTA,
+    // warp (group, quarter) the 32 positions in TMEM lanes [32 quarter, +32) with every column.
+    // The buffer count is a multiple of ngroups, so every use of a buffer is awaited by the same
+    // group in order: a barrier is never waited on more than one phase ahead (a parity wait
+    // cannot tell phase k from phase k + 2) ----
+    const int ew = warp - kPwFirstEpiWarp, quarter = warp & 3, group = ew >> 2;
     const f32x2 nz = negzero2();
     const FpqPacked fq = make_fpq_packed(a.q);
+    const bool bn_safe = unsafe_s == 0;
     unsigned int tile_i = 0;
-    int cur_ct = -1;
     for (long long t = blockIdx.x; t < a.total_tiles; t += gridDim.x, ++tile_i) {
+      if ((int)(tile_i % (unsigned)a.ngroups) != group) continue;
       const int ct = (int)(t / per_ct);
       const long long r = t - (long long)ct * per_ct;
       const long long n = r / a.pos_tiles;
       const int pt = (int)(r - n * a.pos_tiles);
-      const unsigned int b = tile_i & 1u, aph = (tile_i >> 1) & 1u;
-      const int cbase = ct * a.npad + half * cols_half;  // first channel of this warp
-      if (ct != cur_ct) {
-        cur_ct = ct;
-        __syncwarp();
-        for (int i = lane; i < (cols_half >> 1); i += 32) table[i] = pw_make_pair(a, cpad, cbase + 2 * i);
-        __syncwarp();
-      }
+      const unsigned int b = tile_i % a.nacc, aph = (tile_i / a.nacc) & 1u;
       if (!pw_wait(&acc_full[b], aph) || *abort_v) {
         if (lane == 0 && !*abort_v) { atomicExch(a.flag, 1); *abort_v = 1; }
         break;
@@ -366,28 +418,44 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
       tc_fence_after();
       const int p = pt * kPwPosTile + quarter * 32 + lane;
       const bool p_ok = p < a.HW;
-      const unsigned int taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + b * a.npad + half * cols_half;
-      float *yp = a.y + ((size_t)n * a.Co + cbase) * a.HW + (p_ok ? p : 0);
-      const bool full_c = cbase + cols_half <= a.Co;
-      for (int c0 = 0; c0 < cols_half; c0 += 32) {
-        unsigned int acc0[16], acc1[16];
-        const bool two = c0 + 16 < cols_half;  // warp-uniform
-        tc_ld16(taddr + c0, acc0);
-        if (two) tc_ld16(taddr + c0 + 16, acc1);
-        tc_ld_wait();
+      const int c_first = ct * a.npad;
+      int c_valid = a.Co - c_first;  // channels of this tile that exist
+      if (c_valid > a.npad) c_valid = a.npad;
+      const int units = (c_valid + 7) >> 3;  // warp-uniform
+      const unsigned int taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + b * a.npad;
+      float *img = a.y + ((size_t)n * a.Co + c_first) * a.HW + (p_ok ? p : 0);
+      const PwPair *tp = table + (c_first >> 1);
+      unsigned int acc0[8], acc1[8];
+      tc_ld8(taddr, acc0);
+      for (int u = 0; u < units; u += 2) {
+        tc_ld_wait8(acc0);
+        if (u + 1 < units) tc_ld8(taddr + (u + 1) * 8, acc1);
+        float res[8];
+        pw_finish_unit<EPI>(acc0, tp + u * 4, a, nz, fq, bn_safe, res);
+        if (p_ok) {
+          const int c0 = u * 8;
+          if (c0 + 8 <= c_valid) {
 #pragma unroll
-        for (int h2 = 0; h2 < 2; ++h2) {
-          if (h2 && !two) break;
-          const int cc = c0 + 16 * h2;
+            for (int i = 0; i < 8; ++i) img[(unsigned)((c0 + i) * a.HW)] = res[i];
+          } else {
 #pragma unroll
-          for (int i = 0; i < 16; i += 2) {
-            const PwPair cp = table[(cc + i) >> 1];
-            float r0, r1;
-            pw_finish_pair<EPI>(__uint_as_float(h2 ? acc1[i] : acc0[i]), __uint_as_float(h2 ? acc1[i + 1] : acc0[i + 1]), cp, a,
-                                nz, fq, r0, r1);
-            if (p_ok) {
-              if (full_c || cbase + cc + i < a.Co) yp[(size_t)(cc + i) * a.HW] = r0;
-              if (full_c || cbase + cc + i + 1 < a.Co) yp[(size_t)(cc + i + 1) * a.HW] = r1;
+            for (int i = 0; i < 8; ++i)
+              if (c0 + i < c_valid) img[(unsigned)((c0 + i) * a.HW)] = res[i];
+          }
+        }
+        if (u + 1 < units) {
+          tc_ld_wait8(acc1);
+          if (u + 2 < units) tc_ld8(taddr + (u + 2) * 8, acc0);
+          pw_finish_unit<EPI>(acc1, tp + (u + 1) * 4, a, nz, fq, bn_safe, res);
+          if (p_ok) {
+            const int c0 = (u + 1) * 8;
+            if (c0 + 8 <= c_valid) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) img[(unsigned)((c0 + i) * a.HW)] = res[i];
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                if (c0 + i < c_valid) img[(unsigned)((c0 + i) * a.HW)] = res[i];
             }
           }
         }
@@ -400,7 +468,7 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kPwTmemCols) : "memory");
   }
 }
 
@@ -413,7 +481,8 @@ __global__ void pw_prepare_kernel(const T *w, const T *b, const T *beta, const T
   if (i < cpad) {
     const bool in = i < Co;
     coef[i] = (in && b) ? Elem<T>::to_f32(b[i]) : 0.0f;
-    coef[cpad + i] = (in && mean) ? Elem<T>::to_f32(mean[i]) : 0.0f;
+    coef[cpad + i] = in ? (mean ? Elem<T>::to_f32(mean[i]) : 0.0f) : -1.0f;  // a padded column normalises 0 to 1
+
     coef[2 * cpad + i] = (in && gamma) ? Elem<T>::to_f32(gamma[i]) : 1.0f;
     coef[3 * cpad + i] = (in && var) ? bn_stdvar(Elem<T>::to_f32(var[i]), eps) : 1.0f;
     coef[4 * cpad + i] = (in && beta) ? Elem<T>::to_f32(beta[i]) : 0.0f;
@@ -514,6 +583,7 @@ PwEncodeFn pw_encode_fn() {
 
 constexpr int kPwPathUnset = -2;
 thread_local int t_forced_pw = kPwPathUnset;
+thread_local int t_pw_max_ctas = 0;  // 0 = one CTA per SM
 
 int forced_pw_path() {
   static const int env_default = [] {
@@ -555,7 +625,8 @@ int validate_pw(const dwbnq_pwconv_desc *d) {
 
 bool pw_tc_eligible(const dwbnq_pwconv_desc &d, const void *x, const void *w) {
   const long long hw = (long long)d.h * d.w;
-  return d.dtype == DWBNQ_F32 && hw % 4 == 0 && d.c_in % 4 == 0 && ((uintptr_t)x & 15) == 0 &&
+  return d.dtype == DWBNQ_F32 && hw % 4 == 0 && d.c_in % 4 == 0 && d.c_out <= kPwMaxCout && ((uintptr_t)x & 15) == 0 &&
+         (long long)d.c_out * hw <= 0x7fffffffLL &&
          (d.math == DWBNQ_PW_MATH_FP32 || ((uintptr_t)w & 15) == 0);
 }
 
@@ -648,7 +719,12 @@ int launch_pwconv(const dwbnq_pwconv_desc &d, float bn_eps, const dwbnq_quant_de
   a.kchunks = (d.c_in + kPwKChunk - 1) / kPwKChunk;
   a.total_tiles = (long long)a.co_tiles * d.n * a.pos_tiles;
   a.stage_bytes = (kPwXBytes + g.npad * 128) * (math3 ? 2 : 1);
-  const int table_bytes = kPwEpiWarps * (kPwMaxCoTile / 4) * (int)sizeof(PwPair);
+  const int table_bytes = (g.cpad / 2) * (int)sizeof(PwPair);
+  {
+    const int fit = kPwTmemCols / g.npad < kPwMaxAcc ? kPwTmemCols / g.npad : kPwMaxAcc;
+    a.ngroups = fit < kPwEpiGroups ? fit : kPwEpiGroups;
+    a.nacc = fit / a.ngroups * a.ngroups;
+  }
   a.stages = (kPwSmemMax - 1024 - table_bytes) / a.stage_bytes;
   if (a.stages > kPwMaxStages) a.stages = kPwMaxStages;
   if (a.stages < 2) return fail(DWBNQ_ERR_UNSUPPORTED, "pipeline stage of %d bytes does not fit twice", a.stage_bytes);
@@ -685,7 +761,8 @@ int launch_pwconv(const dwbnq_pwconv_desc &d, float bn_eps, const dwbnq_quant_de
   else if (a.has_bn && kind == DWBNQ_Q_FPQ && qa.fpq_fast && !(qa.fpq_min < 0.0f)) epi = PW_EPI_BN_FPQ;
   const size_t smem = (size_t)a.stages * a.stage_bytes + table_bytes + 1024;
   const int sms = sm_count(dev);
-  const long long grid = a.total_tiles < sms ? a.total_tiles : sms;
+  long long grid = a.total_tiles < sms ? a.total_tiles : sms;
+  if (t_pw_max_ctas > 0 && grid > t_pw_max_ctas) grid = t_pw_max_ctas;
   const cudaError_t e = math3 ? launch_pw_tc<true>(epi, dim3((unsigned)grid), smem, stream, tx, tw, twl, a)
                               : launch_pw_tc<false>(epi, dim3((unsigned)grid), smem, stream, tx, tw, twl, a);
   if (e != cudaSuccess) return fail_cuda(e, "pw_tc_kernel launch");
@@ -702,5 +779,6 @@ int pwconv_path(const dwbnq_pwconv_desc &d, const void *x, const void *w) {
   return forced == 0 ? 0 : (pw_tc_eligible(d, x, w) ? 1 : 0);
 }
 void set_forced_pw_path(int p) { t_forced_pw = p; }
+void set_pw_max_ctas(int n) { t_pw_max_ctas = n; }
 
 }  // namespace dwbnq

@@ -377,6 +377,10 @@ def set_forced_pw_path(path):
     L.check(L.lib().dwbnq_set_forced_pw_path(int(path)))
 
 
+def set_pw_max_ctas(ctas):
+    L.check(L.lib().dwbnq_set_pw_max_ctas(int(ctas)))
+
+
 def fused_plan(x, w, y=None, base_axis=1, pad=None, stride=None, dilation=None, multiplier=1):
     """Kernel family and tile geometry the library would choose (diagnostic)."""
     d, _ = conv_desc(x, w, base_axis, pad, stride, dilation, multiplier)

@@ -188,6 +188,28 @@ def test_forced_kernel_choice_and_the_two_kernels_agree(oracle, cuda_device):
     ops.check_device_flag()
 
 
+@pytest.mark.parametrize("co", [16, 96, 144, 200, 384], ids=lambda c: "co%d" % c)
+@pytest.mark.parametrize("math", ["fp32", "tf32"])
+def test_many_tiles_per_cta(oracle, cuda_device, co, math):
+    """Three CTAs walk through 60 to 120 tiles each: every pipeline stage and every accumulator
+    buffer is reused many times, with the plain (fast) and the fused (slower) epilogue, for every
+    buffer count the channel tile widths give (8, 4, 3, 2 buffers)."""
+    rng = np.random.default_rng(co)
+    d = make(rng, 12, 40, co, 36, 40)  # 1440 positions = 11.25 tiles per image
+    t = {k: dev(v, cuda_device) for k, v in d.items()}
+    try:
+        ops.set_pw_max_ctas(3)
+        conv = ops.pointwise_convolution(t["x"], t["w"], t["b"], math=math).cpu().numpy()
+        y = ops.fused_pw_bn_quant(t["x"], t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], 1e-5, FPQ_U, "relu6",
+                                  math=math).cpu().numpy()
+    finally:
+        ops.set_pw_max_ctas(0)
+    ops.check_device_flag()
+    check_conv(oracle, conv, d, conv_tolerance(1, math, 40))
+    want = oracle.pw_epilogue(conv, d["beta"], d["gamma"], d["mean"], d["var"], 1e-5, "relu6", FPQ_U)
+    assert np.array_equal(y.view(np.uint32), want.view(np.uint32))
+
+
 def test_argument_errors(cuda_device):
     x = torch.zeros(1, 8, 4, 4, device=cuda_device)
     w = torch.zeros(16, 8, 1, 1, device=cuda_device)
