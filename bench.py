@@ -324,6 +324,35 @@ def run_standalone_ops(args):
     print(json.dumps(line), flush=True)
 
 
+def run_pointwise(args):
+    """Workload pw1 alone: the 33 pointwise layers around cfg1's depthwise layers at batch B
+    (default 256), one JSON line in the bench format; `layers` holds the per-layer rows and the
+    two summary rows. --only-layers restricts the pass (profiling)."""
+    import torch
+    from dwbnq import ops, workloads
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the dwbnq path has no CPU fallback")
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    peak, peak_kind = measured_peak()
+    n = args.batch or 256
+    if args.only_layers:
+        keep = {int(i) for i in args.only_layers.split(",")}
+        full = workloads.pw1
+        workloads.pw1 = lambda b=256: [sp for i, sp in enumerate(full(b)) if i in keep]
+    rows = pointwise_rows(torch, ops, workloads, device, n, peak)
+    tot = [r for r in rows if r["workload"].startswith("pw1: ") and r["workload"].endswith("fp32")][0]
+    line = {"metric": "images_per_s", "value": tot["images_per_s"], "unit": "images/s", "n_gpus": 1, "steps": 10,
+            "warmup": 2, "ms_per_step": tot["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "pw1: the pointwise convolutions of MobileNetV2 around the depthwise layers, batch %d, "
+                                   "each fused with BN, activation and FixedPointQuantize" % n,
+                       "l2": "L2 flushed before every timed launch"},
+            "roofline": {"bound": "hbm", "achieved": tot["gbs"], "peak": peak, "unit": "GB/s", "frac": tot["frac"],
+                         "traffic": None, "peak_kind": peak_kind}, "gpu_launches": 2 * len(rows) - 4, "layers": rows}
+    print(json.dumps(line), flush=True)
+
+
 def bind_to_gpu_numa_node(torch, index):
     """Restricts this process to the CPUs of the NUMA node its GPU hangs off, so that the
     pinned host buffers of the end-to-end pass (allocated afterwards, first touched here) are
@@ -351,6 +380,71 @@ def bind_to_gpu_numa_node(torch, index):
 
 FAMILY = {0: "fused_generic_kernel", 1: "fused_tiled_kernel (cooperative fill)", 2: "fused_tiled_kernel (TMA)",
           3: "fused_tiled_kernel (bulk copy)", 4: "fused_plane_* kernels", 5: "fused_plane_gen_kernel"}
+
+
+def pointwise_rows(torch, ops, workloads, device, batch, peak):
+    """The 33 pointwise convolutions around cfg1's depthwise layers (workload pw1), each fused with
+    BN, its activation and its FixedPointQuantize, one layer at a time with its own seeded input
+    resident in HBM. Every launch is replayed from a CUDA graph with L2 flushed before it (the
+    deeper layers move less than L2 holds); median of 10. Per-layer rows for the fp32-accurate
+    three-pass TF32 mode, and a summary row for it and for the single-pass TF32 mode."""
+    rows, totals = [], {"fp32": [0.0, 0, 0.0], "tf32": [0.0, 0, 0.0]}
+    for spec in workloads.pw1(batch):
+        d = workloads.make_pointwise_data(spec)
+        t = {k: torch.from_numpy(v).to(device) for k, v in d.items()}
+        del d
+        y = torch.empty((batch, spec.c_out, spec.h, spec.h), dtype=torch.float32, device=device)
+        ws = ops.pwconv_workspace(t["x"], t["w"])
+        path = ops.pwconv_plan(t["x"], t["w"])
+        for math in ("fp32", "tf32"):
+            if math == "tf32" and path == 0:
+                ms = rows[-1]["ms"]  # the FMA kernel has one mode
+            else:
+                def call():
+                    ops.fused_pw_bn_quant(t["x"], t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], spec.bn_eps,
+                                          spec.quant, spec.act, math=math, ws=ws, out=y)
+                call()
+                g = torch.cuda.CUDAGraph()
+                cap = torch.cuda.Stream(device)
+                cap.wait_stream(torch.cuda.current_stream(device))
+                with torch.cuda.stream(cap):
+                    call()
+                    with torch.cuda.graph(g, stream=cap):
+                        call()
+                torch.cuda.current_stream(device).wait_stream(cap)
+                g.replay()
+                torch.cuda.synchronize()
+                ts = []
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                for _ in range(10):
+                    flush_l2(torch, device)
+                    e0.record()
+                    g.replay()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    ts.append(e0.elapsed_time(e1))
+                ms = float(np.median(ts))
+                del g
+            nbytes = spec.algorithmic_bytes(4, batch)
+            totals[math][0] += ms
+            totals[math][1] += nbytes
+            totals[math][2] += spec.flops(batch)
+            if math == "fp32":
+                rows.append({"workload": "%s %d->%d @%dx%d" % (spec.name, spec.c_in, spec.c_out, spec.h, spec.h), "dtype": "f32",
+                             "batch": batch, "ms": ms, "images_per_s": batch / (ms / 1e3), "gbs": nbytes / ms / 1e6,
+                             "frac": nbytes / ms / 1e6 / peak, "tflops": spec.flops(batch) / ms / 1e9,
+                             "algorithmic_bytes": nbytes,
+                             "kernel": "pw_tc_kernel (tcgen05, three TF32 passes)" if path == 1 else "pw_simt_kernel (FMA)",
+                             "timing": "median of 10 CUDA-graph replays, L2 flushed before each"})
+        del t, y, ws
+        torch.cuda.empty_cache()
+    ops.check_device_flag()
+    for math, (ms, nbytes, fl) in totals.items():
+        rows.append({"workload": "pw1: 33 pointwise layers, math %s" % math, "dtype": "f32", "batch": batch, "ms": ms,
+                     "images_per_s": batch / (ms / 1e3), "gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak,
+                     "tflops": fl / ms / 1e9, "algorithmic_bytes": nbytes, "kernel": "sum of the per-layer medians",
+                     "timing": "median of 10 CUDA-graph replays per layer, L2 flushed before each"})
+    return rows
 
 
 def other_workloads(torch, ops, workloads, device, cfg1_layers, args):
@@ -451,6 +545,8 @@ def other_workloads(torch, ops, workloads, device, cfg1_layers, args):
                     "images_per_s": 256 / (r["ms"] / 1e3), "gbs": r["gbs"], "frac": r["gbs"] / peak,
                     "algorithmic_bytes": r["bytes"], "kernel": "training-side kernel on [256,96,56,56]",
                     "timing": "median of 10 launches, L2 flushed before each"})
+    torch.cuda.empty_cache()
+    out.extend(pointwise_rows(torch, ops, workloads, device, 256, peak))
     torch.cuda.empty_cache()
     return out
 
@@ -805,7 +901,7 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
-    ap.add_argument("--workload", default="cfg1", choices=["cfg0", "cfg1", "cfg2", "cfg3", "cfg4", "cfg1q8", "ops"])
+    ap.add_argument("--workload", default="cfg1", choices=["cfg0", "cfg1", "cfg2", "cfg3", "cfg4", "cfg1q8", "ops", "pw1"])
     ap.add_argument("--batch", type=int, default=None, help="images per GPU (default: the workload's batch)")
     ap.add_argument("--dtype", default="f32", choices=["f32", "f16"])
     ap.add_argument("--cpu-sample", type=int, default=None, help="images per CPU-baseline pass")
@@ -825,16 +921,18 @@ def main():
     ap.add_argument("--force-path", type=int, default=None, help="profiling only: kernel family 0..4")
     ap.add_argument("--tune", default="", help="profiling only: planner override P,row_blocks,threads,rows_per_patch")
     args = ap.parse_args()
-    defaults = {"cfg0": 32, "cfg1": 256, "cfg2": 128, "cfg3": 512, "cfg4": 256, "cfg1q8": 256, "ops": 256}
+    defaults = {"cfg0": 32, "cfg1": 256, "cfg2": 128, "cfg3": 512, "cfg4": 256, "cfg1q8": 256, "ops": 256, "pw1": 256}
     if args.batch is None:
         args.batch = defaults[args.workload]
     if args.warmup < 3:
         args.warmup = 3
     if args.cpu_sample is None:
         args.cpu_sample = {"cfg0": 32, "cfg1": 64, "cfg2": 32, "cfg3": 128, "cfg4": 64, "cfg1q8": 64,
-                           "ops": 0}[args.workload]
+                           "ops": 0, "pw1": 0}[args.workload]
     if args.workload == "ops":
         run_standalone_ops(args)
+    elif args.workload == "pw1":
+        run_pointwise(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

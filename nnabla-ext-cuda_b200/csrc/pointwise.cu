@@ -12,9 +12,9 @@
 //    per-channel coefficients and every store is one coalesced 128-byte line - no staging of
 //    the output in shared memory;
 //  * one CTA per SM walks over (channel tile, image, position tile) triples; warp 0 issues
-//    the TMA loads, warp 1 the MMAs, warps 2-3 split the fp32 activations into TF32 halves for
-//    the three-pass mode, warps 4-11 are the epilogue; two accumulator buffers in TMEM let the
-//    epilogue of one tile overlap the loads and MMAs of the next;
+//    the TMA loads, warp 1 the MMAs, warps 2-5 split the fp32 activations into TF32 halves for
+//    the three-pass mode, warps 6-21 are the epilogue (four groups of four warps, each group a
+//    tile of its own); up to eight accumulator buffers in TMEM decouple the MMAs from the epilogue;
 //  * every wait on an mbarrier is bounded in time; a wait that runs out records it in the
 //    device flag, the roles leave their loops, and the CTA frees its tensor memory and returns.
 // Shapes the TMA loads cannot take (h*w or c_in not a multiple of 4, fp16 tensors) run on a
@@ -28,7 +28,7 @@ namespace dwbnq {
 
 namespace {
 
-constexpr int kPwFirstEpiWarp = 4, kPwEpiGroups = 4, kPwEpiWarps = 4 * kPwEpiGroups;
+constexpr int kPwSplitWarps = 4, kPwFirstEpiWarp = 2 + kPwSplitWarps, kPwEpiGroups = 4, kPwEpiWarps = 4 * kPwEpiGroups;
 constexpr int kPwThreads = 32 * (kPwFirstEpiWarp + kPwEpiWarps);
 constexpr int kPwTmemCols = 512;           // the whole tensor memory of the SM (one CTA per SM)
 constexpr int kPwMaxAcc = 8;               // accumulator buffers in flight
@@ -41,7 +41,12 @@ constexpr int kPwMaxCoTile = 256;          // two accumulators of 256 columns fi
 constexpr int kPwSmemMax = 227 * 1024 - 1024;  // dynamic shared memory the kernel may ask for
 constexpr unsigned long long kPwWaitNs = 2000000000ull;
 
-enum PwEpi : int { PW_EPI_BIAS = 0, PW_EPI_BN_FPQ = 1, PW_EPI_GENERIC = 2 };
+// Epilogue variants compiled separately (a run-time switch inside the unrolled loops costs more
+// instructions than the arithmetic): bias only; BN + unsigned power-of-two FixedPointQuantize
+// with or without ReLU6 in between (after ReLU6 the quantizer's clamps are redundant when its
+// range reaches 6); BN + signed power-of-two FixedPointQuantize (the linear projection of an
+// inverted residual); everything else with run-time switches.
+enum PwEpi : int { PW_EPI_BIAS = 0, PW_EPI_BN_FPQ = 1, PW_EPI_BN_RELU6_FPQ = 2, PW_EPI_BN_FPQS = 3, PW_EPI_GENERIC = 4 };
 
 // Per pair of output channels, everything the epilogue needs (three 16-byte shared-memory words).
 struct __align__(16) PwPair {
@@ -53,7 +58,7 @@ struct PwArgs {
   long long N;
   int npad;       // accumulator columns per channel tile (multiple of 32, <= 256)
   int co_tiles, pos_tiles, kchunks;
-  long long total_tiles;
+  int total_tiles, per_ct;  // per_ct = N * pos_tiles
   int stages, stage_bytes;
   int nacc;       // accumulator buffers of npad columns in TMEM, a multiple of ngroups
   int ngroups;    // epilogue groups in use (<= kPwEpiGroups): buffer b always belongs to group b % ngroups
@@ -73,15 +78,15 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *tm, in
       "l"(tm), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
-// Bounded waits of this kernel. Every tile passes through several barriers in a row (loads ->
-// MMA -> epilogue -> MMA -> loads), so the poll carries no suspend-time hint: a parked thread's
-// wake-up latency would be paid at each hop.
+// Bounded waits of this kernel. Most of the twenty-odd warps of a CTA wait most of the time;
+// the poll carries a suspend-time hint so that a waiting warp is parked by the hardware and
+// leaves the issue slots to the warps that compute (a bare spin took about a third of them).
 __device__ __forceinline__ bool pw_try_wait(unsigned long long *bar, unsigned int parity) {
   unsigned int ok;
   asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(20000u)
       : "memory");
   return ok != 0;
 }
@@ -91,7 +96,7 @@ __device__ __forceinline__ bool pw_wait_lane(unsigned long long *bar, unsigned i
 #pragma unroll 1
   for (unsigned int i = 0; i < (1u << 28); ++i) {
     if (pw_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 63u && global_timer_ns() - t0 > kPwWaitNs) break;
+    if (global_timer_ns() - t0 > kPwWaitNs) break;
   }
   return false;
 }
@@ -188,7 +193,7 @@ template <int EPI>
 __device__ __forceinline__ void pw_finish_unit(const unsigned int *acc, const PwPair *tp, const PwArgs &a, f32x2 nz,
                                                const FpqPacked &fq, bool bn_safe, float *r) {
   f32x2 v[4];
-  const bool bn = EPI == PW_EPI_BN_FPQ || (EPI == PW_EPI_GENERIC && a.has_bn);
+  const bool bn = EPI == PW_EPI_BN_FPQ || EPI == PW_EPI_BN_RELU6_FPQ || EPI == PW_EPI_BN_FPQS || (EPI == PW_EPI_GENERIC && a.has_bn);
   if (bn) {
     f32x2 t[4], nstd[4];
     float mx = 0.0f, mn = __uint_as_float(0x7f800000u);
@@ -227,10 +232,18 @@ __device__ __forceinline__ void pw_finish_unit(const unsigned int *acc, const Pw
   for (int i = 0; i < 4; ++i) {
     float r0, r1;
     unpack2(v[i], r0, r1);
-    if (a.act) { r0 = pw_act(r0, a.act); r1 = pw_act(r1, a.act); }
-    if (EPI == PW_EPI_BN_FPQ) {
+    if (EPI == PW_EPI_BN_RELU6_FPQ) {
+      r0 = fminf(fmaxf(r0, 0.0f), 6.0f);
+      r1 = fminf(fmaxf(r1, 0.0f), 6.0f);
+      const f32x2 kp = add2_rm(fma2_rm(pack2(r0, r1), fq.inv, fq.half), fq.magic);
+      unpack2(fma2(kp, fq.delta, fq.nmagic), r0, r1);
+    } else if (EPI == PW_EPI_BN_FPQ) {
       unpack2(fpq_apply_fast_unsigned2(r0, r1, a.q, fq), r0, r1);
+    } else if (EPI == PW_EPI_BN_FPQS) {
+      r0 = fpq_apply_fast<true>(r0, a.q);
+      r1 = fpq_apply_fast<true>(r1, a.q);
     } else if (EPI == PW_EPI_GENERIC) {
+      if (a.act) { r0 = pw_act(r0, a.act); r1 = pw_act(r1, a.act); }
       if (a.qkind == DWBNQ_Q_FPQ) { r0 = fpq_apply(r0, a.q); r1 = fpq_apply(r1, a.q); }
       else if (a.qkind == DWBNQ_Q_POW2) { r0 = pow2_apply(r0, a.q); r1 = pow2_apply(r1, a.q); }
     }
@@ -265,7 +278,7 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
     for (int s = 0; s < a.stages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
-      mbar_init(&split[s], 64);
+      mbar_init(&split[s], 32 * kPwSplitWarps);
     }
     for (int b = 0; b < a.nacc; ++b) {
       mbar_init(&acc_full[b], 1);
@@ -295,7 +308,6 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
   __syncthreads();
   tc_fence_after();
   const unsigned int tmem_base = tmem_base_s;
-  const long long per_ct = a.N * a.pos_tiles;
   volatile int *abort_v = &abort_s;
 
   if (warp == 0) {
@@ -304,10 +316,10 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
       unsigned int it = 0;
       const unsigned int bytes = kPwXBytes + wbytes * (MATH3 ? 2 : 1);
       bool ok = true;
-      for (long long t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
-        const int ct = (int)(t / per_ct);
-        const long long r = t - (long long)ct * per_ct;
-        const int n = (int)(r / a.pos_tiles), pt = (int)(r - (long long)n * a.pos_tiles);
+      for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
+        const int ct = t / a.per_ct;
+        const int r = t - ct * a.per_ct;
+        const int n = r / a.pos_tiles, pt = r - n * a.pos_tiles;
         for (int kc = 0; kc < a.kchunks; ++kc, ++it) {
           const int s = it % a.stages;
           const unsigned int ph = (it / a.stages) & 1u;
@@ -329,7 +341,7 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
     const unsigned int idesc = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | ((unsigned)(a.npad >> 3) << 17) | (8u << 24);
     unsigned int it = 0, tile_i = 0;
     bool ok = true;
-    for (long long t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x, ++tile_i) {
+    for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x, ++tile_i) {
       const unsigned int b = tile_i % a.nacc, aph = (tile_i / a.nacc) & 1u;
       ok = pw_wait(&acc_empty[b], aph ^ 1u);
       tc_fence_after();
@@ -367,7 +379,7 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
       const int tid = threadIdx.x - 64;
       unsigned int it = 0;
       bool ok = true;
-      for (long long t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
+      for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
         for (int kc = 0; kc < a.kchunks; ++kc, ++it) {
           const int s = it % a.stages;
           const unsigned int ph = (it / a.stages) & 1u;
@@ -376,7 +388,7 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
           uint4 *xh = reinterpret_cast<uint4 *>(sm + (size_t)s * a.stage_bytes);
           uint4 *xl = reinterpret_cast<uint4 *>(sm + (size_t)s * a.stage_bytes + off_xlo);
 #pragma unroll 4
-          for (int i = tid; i < kPwXBytes / 16; i += 64) {
+          for (int i = tid; i < kPwXBytes / 16; i += 32 * kPwSplitWarps) {
             const uint4 v = xh[i];
             uint4 h, l;
             h.x = v.x & 0xffffe000u; h.y = v.y & 0xffffe000u; h.z = v.z & 0xffffe000u; h.w = v.w & 0xffffe000u;
@@ -404,12 +416,11 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
     const FpqPacked fq = make_fpq_packed(a.q);
     const bool bn_safe = unsafe_s == 0;
     unsigned int tile_i = 0;
-    for (long long t = blockIdx.x; t < a.total_tiles; t += gridDim.x, ++tile_i) {
+    for (int t = blockIdx.x; t < a.total_tiles; t += gridDim.x, ++tile_i) {
       if ((int)(tile_i % (unsigned)a.ngroups) != group) continue;
-      const int ct = (int)(t / per_ct);
-      const long long r = t - (long long)ct * per_ct;
-      const long long n = r / a.pos_tiles;
-      const int pt = (int)(r - n * a.pos_tiles);
+      const int ct = t / a.per_ct;
+      const int r = t - ct * a.per_ct;
+      const int n = r / a.pos_tiles, pt = r - n * a.pos_tiles;
       const unsigned int b = tile_i % a.nacc, aph = (tile_i / a.nacc) & 1u;
       if (!pw_wait(&acc_full[b], aph) || *abort_v) {
         if (lane == 0 && !*abort_v) { atomicExch(a.flag, 1); *abort_v = 1; }
@@ -424,6 +435,7 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
       const int units = (c_valid + 7) >> 3;  // warp-uniform
       const unsigned int taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + b * a.npad;
       float *img = a.y + ((size_t)n * a.Co + c_first) * a.HW + (p_ok ? p : 0);
+      const size_t unit_stride = (size_t)8 * a.HW;
       const PwPair *tp = table + (c_first >> 1);
       unsigned int acc0[8], acc1[8];
       tc_ld8(taddr, acc0);
@@ -434,13 +446,14 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
         pw_finish_unit<EPI>(acc0, tp + u * 4, a, nz, fq, bn_safe, res);
         if (p_ok) {
           const int c0 = u * 8;
+          float *q = img + (size_t)u * unit_stride;
           if (c0 + 8 <= c_valid) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) img[(unsigned)((c0 + i) * a.HW)] = res[i];
+            for (int i = 0; i < 8; ++i) q[(unsigned)(i * a.HW)] = res[i];
           } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-              if (c0 + i < c_valid) img[(unsigned)((c0 + i) * a.HW)] = res[i];
+              if (c0 + i < c_valid) q[(unsigned)(i * a.HW)] = res[i];
           }
         }
         if (u + 1 < units) {
@@ -449,13 +462,14 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
           pw_finish_unit<EPI>(acc1, tp + (u + 1) * 4, a, nz, fq, bn_safe, res);
           if (p_ok) {
             const int c0 = (u + 1) * 8;
+            float *q = img + (size_t)(u + 1) * unit_stride;
             if (c0 + 8 <= c_valid) {
 #pragma unroll
-              for (int i = 0; i < 8; ++i) img[(unsigned)((c0 + i) * a.HW)] = res[i];
+              for (int i = 0; i < 8; ++i) q[(unsigned)(i * a.HW)] = res[i];
             } else {
 #pragma unroll
               for (int i = 0; i < 8; ++i)
-                if (c0 + i < c_valid) img[(unsigned)((c0 + i) * a.HW)] = res[i];
+                if (c0 + i < c_valid) q[(unsigned)(i * a.HW)] = res[i];
             }
           }
         }
@@ -635,9 +649,20 @@ cudaError_t launch_pw_tc(int epi, dim3 grid, size_t smem, cudaStream_t stream, c
                          const CUtensorMap &twl, const PwArgs &a) {
   void (*k)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const PwArgs) =
       epi == PW_EPI_BIAS ? pw_tc_kernel<MATH3, PW_EPI_BIAS>
-                         : epi == PW_EPI_BN_FPQ ? pw_tc_kernel<MATH3, PW_EPI_BN_FPQ> : pw_tc_kernel<MATH3, PW_EPI_GENERIC>;
-  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kPwSmemMax);
-  if (e != cudaSuccess) return e;
+      : epi == PW_EPI_BN_FPQ ? pw_tc_kernel<MATH3, PW_EPI_BN_FPQ>
+      : epi == PW_EPI_BN_RELU6_FPQ ? pw_tc_kernel<MATH3, PW_EPI_BN_RELU6_FPQ>
+      : epi == PW_EPI_BN_FPQS ? pw_tc_kernel<MATH3, PW_EPI_BN_FPQS> : pw_tc_kernel<MATH3, PW_EPI_GENERIC>;
+  static thread_local const void *attr_done[10] = {nullptr};  // per host thread; per device it is re-applied lazily
+  static thread_local int attr_dev[10] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int slot = (MATH3 ? 5 : 0) + epi;
+  if (attr_done[slot] != (const void *)k || attr_dev[slot] != dev + 1) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kPwSmemMax);
+    if (e != cudaSuccess) return e;
+    attr_done[slot] = (const void *)k;
+    attr_dev[slot] = dev + 1;
+  }
   k<<<grid, kPwThreads, smem, stream>>>(tx, tw, twl, a);
   return cudaGetLastError();
 }
@@ -717,7 +742,12 @@ int launch_pwconv(const dwbnq_pwconv_desc &d, float bn_eps, const dwbnq_quant_de
   a.npad = g.npad; a.co_tiles = g.co_tiles;
   a.pos_tiles = (HW + kPwPosTile - 1) / kPwPosTile;
   a.kchunks = (d.c_in + kPwKChunk - 1) / kPwKChunk;
-  a.total_tiles = (long long)a.co_tiles * d.n * a.pos_tiles;
+  {
+    const long long total = (long long)a.co_tiles * d.n * a.pos_tiles;
+    if (total > 0x7fffffffLL) return fail(DWBNQ_ERR_UNSUPPORTED, "more than 2^31 - 1 tiles");
+    a.total_tiles = (int)total;
+    a.per_ct = (int)(d.n * a.pos_tiles);
+  }
   a.stage_bytes = (kPwXBytes + g.npad * 128) * (math3 ? 2 : 1);
   const int table_bytes = (g.cpad / 2) * (int)sizeof(PwPair);
   {
@@ -733,7 +763,6 @@ int launch_pwconv(const dwbnq_pwconv_desc &d, float bn_eps, const dwbnq_quant_de
   st = device_flag_ptr(dev, &a.flag);
   if (st != DWBNQ_OK) return st;
   a.has_bn = mean != nullptr; a.act = d.act; a.qkind = kind; a.q = qa;
-
   PwEncodeFn enc = pw_encode_fn();
   if (!enc) return fail(DWBNQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   CUtensorMap tx, tw, twl;
@@ -757,11 +786,16 @@ int launch_pwconv(const dwbnq_pwconv_desc &d, float bn_eps, const dwbnq_quant_de
     if (r != CUDA_SUCCESS) return fail(DWBNQ_ERR_CUDA, "cuTensorMapEncodeTiled(w) failed with CUresult %d", (int)r);
   }
   int epi = PW_EPI_GENERIC;
-  if (!a.has_bn && kind == DWBNQ_Q_NONE) epi = PW_EPI_BIAS;
-  else if (a.has_bn && kind == DWBNQ_Q_FPQ && qa.fpq_fast && !(qa.fpq_min < 0.0f)) epi = PW_EPI_BN_FPQ;
+  const bool fpq_u = kind == DWBNQ_Q_FPQ && qa.fpq_fast && qa.fpq_min == 0.0f;
+  if (!a.has_bn && kind == DWBNQ_Q_NONE && d.act == DWBNQ_ACT_NONE) epi = PW_EPI_BIAS;
+  else if (a.has_bn && fpq_u && d.act == DWBNQ_ACT_NONE) epi = PW_EPI_BN_FPQ;
+  else if (a.has_bn && kind == DWBNQ_Q_FPQ && qa.fpq_fast && qa.fpq_min < 0.0f && d.act == DWBNQ_ACT_NONE) epi = PW_EPI_BN_FPQS;
+  // ReLU6 yields a value in [0, 6] (a NaN becomes 0): inside an unsigned range that reaches 6 the
+  // quantizer's own clamps change nothing
+  else if (a.has_bn && fpq_u && d.act == DWBNQ_ACT_RELU6 && qa.fpq_max >= 6.0f) epi = PW_EPI_BN_RELU6_FPQ;
   const size_t smem = (size_t)a.stages * a.stage_bytes + table_bytes + 1024;
   const int sms = sm_count(dev);
-  long long grid = a.total_tiles < sms ? a.total_tiles : sms;
+  int grid = a.total_tiles < sms ? a.total_tiles : sms;
   if (t_pw_max_ctas > 0 && grid > t_pw_max_ctas) grid = t_pw_max_ctas;
   const cudaError_t e = math3 ? launch_pw_tc<true>(epi, dim3((unsigned)grid), smem, stream, tx, tw, twl, a)
                               : launch_pw_tc<false>(epi, dim3((unsigned)grid), smem, stream, tx, tw, twl, a);

@@ -17,6 +17,10 @@ Workloads (ids follow the benchmark's config list):
   cfg3  x[512,192,28,28]~N(0,2) with 0.1% outliers~U(-20,20), 3x3 s2 p1, BN,
         MinMaxQuantize(per-channel over axes (0,2,3), ql=[0,255], x_min_max, no ema)
   cfg4  cfg1 cast to float16
+  pw1   the 33 pointwise (1x1) convolutions that sit either side of cfg1's depthwise layers in
+        MobileNetV2: 16 expansions (BN, ReLU6, unsigned FixedPointQuantize as in cfg1; input
+        x~N(0,1), the signed output of a projection) and 17 linear projections (BN, signed
+        FixedPointQuantize n=8, delta=2^-4; input x~ReLU6(N(0,1)) like cfg1's), W~N(0,1/c_in)
 """
 import os
 from concurrent.futures import ThreadPoolExecutor
@@ -28,6 +32,22 @@ import numpy as np
 MOBILENETV2_DW = ([(32, 112, 1), (96, 112, 2), (144, 56, 1), (144, 56, 2)] + [(192, 28, 1)] * 2 +
                   [(192, 28, 2)] + [(384, 14, 1)] * 4 + [(576, 14, 1)] * 2 + [(576, 14, 2)] +
                   [(960, 7, 1)] * 3)
+
+# (c_in, c_out, height = width, kind) of the pointwise layers around them: block i expands
+# c_in -> 6 c_in at the block's input resolution (the first block has no expansion) and
+# projects 6 c_in -> c_out at the depthwise layer's output resolution.
+_MBV2_BLOCK_IO = ([(32, 16), (16, 24), (24, 24), (24, 32), (32, 32), (32, 32), (32, 64)] + [(64, 64)] * 3 + [(64, 96)] +
+                  [(96, 96)] * 2 + [(96, 160)] + [(160, 160)] * 2 + [(160, 320)])
+
+
+def mobilenetv2_pointwise():
+    out = []
+    for (cin, cout), (cdw, h, stride) in zip(_MBV2_BLOCK_IO, MOBILENETV2_DW):
+        if cdw != cin:
+            out.append((cin, cdw, h, "expand"))
+        out.append((cdw, cout, h // stride, "project"))
+    return out
+
 
 FPQ_CFG0 = {"kind": "fpq", "sign": True, "n": 8, "delta": 2.0 ** -4}
 FPQ_CFG1 = {"kind": "fpq", "sign": False, "n": 8, "delta": 2.0 ** -3}
@@ -163,3 +183,56 @@ def quant_for_ops(spec, tensors=None):
         for k_ in ("qr_min", "qr_max", "ql_min", "ql_max"):
             q[k_] = tensors[k_]
     return q
+
+
+@dataclass
+class PointwiseSpec:
+    name: str
+    n: int
+    c_in: int
+    c_out: int
+    h: int
+    kind: str  # "expand": BN, ReLU6, unsigned FPQ; "project": BN, signed FPQ
+    seed: int = 0
+    bn_eps: float = 1e-5
+
+    @property
+    def act(self):
+        return "relu6" if self.kind == "expand" else None
+
+    @property
+    def quant(self):
+        return dict(FPQ_CFG1) if self.kind == "expand" else dict(FPQ_CFG0)
+
+    def algorithmic_bytes(self, itemsize=4, n=None):
+        n = self.n if n is None else n
+        return itemsize * (n * (self.c_in + self.c_out) * self.h * self.h + self.c_in * self.c_out + 5 * self.c_out)
+
+    def flops(self, n=None):
+        n = self.n if n is None else n
+        return 2.0 * n * self.h * self.h * self.c_in * self.c_out
+
+
+def pw1(n=256):
+    return [PointwiseSpec("pw1.l%02d.%s" % (i, kind), n, ci, co, h, kind, seed=100 + i)
+            for i, (ci, co, h, kind) in enumerate(mobilenetv2_pointwise())]
+
+
+def make_pointwise_data(spec, n=None, dtype=np.float32):
+    """Parameters from the layer's generator in the order W, b, mean, var, gamma, beta, then x."""
+    n = spec.n if n is None else n
+    rng = np.random.default_rng(spec.seed)
+    co, ci = spec.c_out, spec.c_in
+    d = {
+        "w": _normal(rng, (co, ci, 1, 1), 1.0 / ci),
+        "b": _normal(rng, (co,), 0.1),
+        "mean": _normal(rng, (co,), 0.1),
+        "var": _uniform(rng, (co,), 0.5, 1.5),
+        "gamma": _uniform(rng, (co,), 0.8, 1.2),
+        "beta": _normal(rng, (co,), 0.1),
+    }
+    x = rng.standard_normal((n, ci, spec.h, spec.h), dtype=np.float32)
+    if spec.kind == "project":
+        x = np.minimum(np.maximum(x, 0.0), 6.0)
+    d["x"] = x
+    return {k: np.ascontiguousarray(v, dtype=dtype) for k, v in d.items()}
