@@ -28,7 +28,7 @@ namespace dwbnq {
 
 namespace {
 
-constexpr int kPwSplitWarps = 4, kPwFirstEpiWarp = 2 + kPwSplitWarps, kPwEpiGroups = 4, kPwEpiWarps = 4 * kPwEpiGroups;
+constexpr int kPwXWarps = 8, kPwFirstEpiWarp = 2 + kPwXWarps, kPwEpiGroups = 4, kPwEpiWarps = 4 * kPwEpiGroups;
 constexpr int kPwThreads = 32 * (kPwFirstEpiWarp + kPwEpiWarps);
 constexpr int kPwTmemCols = 512;           // the whole tensor memory of the SM (one CTA per SM)
 constexpr int kPwMaxAcc = 8;               // accumulator buffers in flight
@@ -63,6 +63,8 @@ struct PwArgs {
   int nacc;       // accumulator buffers of npad columns in TMEM, a multiple of ngroups
   int ngroups;    // epilogue groups in use (<= kPwEpiGroups): buffer b always belongs to group b % ngroups
   const float *coef;  // [5][co_tiles * npad]: bias, mean, scale, stdvar, beta
+  const float *x;     // gather mode: the activations, read with plain loads
+  long long total_pos;  // gather mode: N * HW, the flattened positions
   float *y;
   int *flag;
   int has_bn, act, qkind;
@@ -254,7 +256,7 @@ __device__ __forceinline__ void pw_finish_unit(const unsigned int *acc, const Pw
 
 // ---- the tcgen05 kernel ------------------------------------------------------------------------
 
-template <bool MATH3, int EPI>
+template <bool GATHER, bool MATH3, int EPI>
 __global__ void __launch_bounds__(kPwThreads, 1)
 pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
              const __grid_constant__ CUtensorMap tm_wlo, const PwArgs a) {
@@ -278,7 +280,7 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
     for (int s = 0; s < a.stages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
-      mbar_init(&split[s], 32 * kPwSplitWarps);
+      mbar_init(&split[s], 32 * kPwXWarps);
     }
     for (int b = 0; b < a.nacc; ++b) {
       mbar_init(&acc_full[b], 1);
@@ -314,21 +316,23 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
     // ---- producer: one lane issues the TMA loads of every (tile, c_in chunk) ----
     if (lane == 0) {
       unsigned int it = 0;
-      const unsigned int bytes = kPwXBytes + wbytes * (MATH3 ? 2 : 1);
+      const unsigned int bytes = (GATHER ? 0 : kPwXBytes) + wbytes * (MATH3 ? 2 : 1);
       bool ok = true;
       for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
         const int ct = t / a.per_ct;
         const int r = t - ct * a.per_ct;
-        const int n = r / a.pos_tiles, pt = r - n * a.pos_tiles;
+        const int n = GATHER ? 0 : r / a.pos_tiles, pt = GATHER ? r : r - n * a.pos_tiles;
         for (int kc = 0; kc < a.kchunks; ++kc, ++it) {
           const int s = it % a.stages;
           const unsigned int ph = (it / a.stages) & 1u;
           if (!pw_wait_lane(&empty[s], ph ^ 1u) || *abort_v) { ok = false; break; }
           unsigned char *st = sm + (size_t)s * a.stage_bytes;
           mbar_expect_tx(&full[s], bytes);
+          if (!GATHER) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
-            tma_load_3d(st + q * 4096, &tm_x, pt * kPwPosTile + q * 32, kc * kPwKChunk, n, &full[s]);
+            for (int q = 0; q < 4; ++q)
+              tma_load_3d(st + q * 4096, &tm_x, pt * kPwPosTile + q * 32, kc * kPwKChunk, n, &full[s]);
+          }
           tma_load_2d(st + off_w, &tm_w, kc * kPwKChunk, ct * a.npad, &full[s]);
           if (MATH3) tma_load_2d(st + off_wlo, &tm_wlo, kc * kPwKChunk, ct * a.npad, &full[s]);
         }
@@ -349,7 +353,7 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
         const int s = it % a.stages;
         const unsigned int ph = (it / a.stages) & 1u;
         ok = pw_wait(&full[s], ph);
-        if (ok && MATH3) ok = pw_wait(&split[s], ph);
+        if (ok && (MATH3 || GATHER)) ok = pw_wait(&split[s], ph);
         if (!ok) break;
         tc_fence_after();
         if (lane == 0) {
@@ -374,9 +378,56 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
     }
     if (!ok && lane == 0 && !*abort_v) { atomicExch(a.flag, 1); *abort_v = 1; }
   } else if (warp < kPwFirstEpiWarp) {
-    // ---- three-pass mode: x -> (x with the low 13 mantissa bits cleared, the exact rest) ----
-    if (MATH3) {
-      const int tid = threadIdx.x - 64;
+    // ---- X workers (eight warps) ----
+    const int tid = threadIdx.x - 64;
+    if (GATHER) {
+      // Plain loads in place of TMA: the 128 rows of a tile are consecutive positions of the
+      // batch flattened over (image, position), so a tile may straddle images and no lane is
+      // wasted on planes whose size is not a multiple of 128 (or of 4, which TMA needs). Thread
+      // (m, half) loads 16 of the chunk's 32 channels of position m - a warp reads 32
+      // consecutive floats per channel - and stores the TF32 halves straight into the swizzled
+      // operand layout the TMA path produces (32-byte units of a 128-byte row, XOR row mod 4).
+      const int m = tid & 127, kh = tid >> 7;
+      const unsigned int sw_base = (unsigned)((m >> 5) * 4096 + (m & 7) * 4);
+      const unsigned int unit = (unsigned)((m >> 3) & 3);
+      unsigned int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
+        const int pt = t % a.per_ct;
+        const long long g = (long long)pt * kPwPosTile + m;
+        const bool valid = g < a.total_pos;
+        const long long n = valid ? g / a.HW : 0;
+        const int p = valid ? (int)(g - n * a.HW) : 0;
+        const float *xp = a.x + (size_t)n * a.Ci * a.HW + p;
+        for (int kc = 0; kc < a.kchunks; ++kc, ++it) {
+          const int s = it % a.stages;
+          const unsigned int ph = (it / a.stages) & 1u;
+          const int k0 = kc * kPwKChunk + kh * 16;
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = (valid && k0 + j < a.Ci) ? __ldg(xp + (size_t)(k0 + j) * a.HW) : 0.0f;
+          ok = pw_wait(&empty[s], ph ^ 1u) && !*abort_v;
+          if (!ok) break;
+          unsigned char *xh = sm + (size_t)s * a.stage_bytes;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int k = kh * 16 + j;
+            const unsigned int off = sw_base + (unsigned)k * 128u + ((unit ^ (unsigned)(k & 3)) << 5);
+            if (MATH3) {
+              const float h = __uint_as_float(__float_as_uint(v[j]) & 0xffffe000u);
+              *reinterpret_cast<float *>(xh + off) = h;
+              *reinterpret_cast<float *>(xh + off_xlo + off) = __fsub_rn(v[j], h);
+            } else {
+              *reinterpret_cast<float *>(xh + off) = v[j];
+            }
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // visible to the tensor core's reads
+          mbar_arrive(&split[s]);
+        }
+      }
+      if (!ok && lane == 0 && !*abort_v) { atomicExch(a.flag, 1); *abort_v = 1; }
+    } else if (MATH3) {
+      // three-pass mode: x -> (x with the low 13 mantissa bits cleared, the exact rest), in place
       unsigned int it = 0;
       bool ok = true;
       for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
@@ -387,8 +438,8 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
           if (!ok) break;
           uint4 *xh = reinterpret_cast<uint4 *>(sm + (size_t)s * a.stage_bytes);
           uint4 *xl = reinterpret_cast<uint4 *>(sm + (size_t)s * a.stage_bytes + off_xlo);
-#pragma unroll 4
-          for (int i = tid; i < kPwXBytes / 16; i += 32 * kPwSplitWarps) {
+#pragma unroll
+          for (int i = tid; i < kPwXBytes / 16; i += 32 * kPwXWarps) {
             const uint4 v = xh[i];
             uint4 h, l;
             h.x = v.x & 0xffffe000u; h.y = v.y & 0xffffe000u; h.z = v.z & 0xffffe000u; h.w = v.w & 0xffffe000u;
@@ -420,15 +471,25 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
       if ((int)(tile_i % (unsigned)a.ngroups) != group) continue;
       const int ct = t / a.per_ct;
       const int r = t - ct * a.per_ct;
-      const int n = r / a.pos_tiles, pt = r - n * a.pos_tiles;
+      long long n;
+      int p;
+      bool p_ok;
+      if (GATHER) {
+        const long long g = (long long)r * kPwPosTile + quarter * 32 + lane;
+        p_ok = g < a.total_pos;
+        n = p_ok ? g / a.HW : 0;
+        p = p_ok ? (int)(g - n * a.HW) : 0;
+      } else {
+        n = r / a.pos_tiles;
+        p = (r - (int)n * a.pos_tiles) * kPwPosTile + quarter * 32 + lane;
+        p_ok = p < a.HW;
+      }
       const unsigned int b = tile_i % a.nacc, aph = (tile_i / a.nacc) & 1u;
       if (!pw_wait(&acc_full[b], aph) || *abort_v) {
         if (lane == 0 && !*abort_v) { atomicExch(a.flag, 1); *abort_v = 1; }
         break;
       }
       tc_fence_after();
-      const int p = pt * kPwPosTile + quarter * 32 + lane;
-      const bool p_ok = p < a.HW;
       const int c_first = ct * a.npad;
       int c_valid = a.Co - c_first;  // channels of this tile that exist
       if (c_valid > a.npad) c_valid = a.npad;
@@ -615,9 +676,12 @@ struct PwGeom {
   int npad, co_tiles, cpad;
 };
 PwGeom pw_geom(int Co) {
+  // Channel tiles of at most 128 columns: four accumulator buffers then fit in TMEM, which keeps
+  // all four epilogue groups busy (a 256-column tile leaves room for two). The tiles are equal,
+  // rounded up to the 32 columns the epilogue's units and the MMA shape want.
   PwGeom g;
-  g.npad = (Co + 31) / 32 * 32;
-  if (g.npad > kPwMaxCoTile) g.npad = kPwMaxCoTile;
+  const int tiles = (Co + 127) / 128;
+  g.npad = ((Co + tiles - 1) / tiles + 31) / 32 * 32;
   g.co_tiles = (Co + g.npad - 1) / g.npad;
   g.cpad = g.co_tiles * g.npad;
   return g;
@@ -637,31 +701,36 @@ int validate_pw(const dwbnq_pwconv_desc *d) {
   return DWBNQ_OK;
 }
 
+// Whether the activations can come in through TMA (plane pitch and base 16-byte aligned), or
+// have to be gathered with plain loads.
+bool pw_tma_x(const dwbnq_pwconv_desc &d, const void *x) {
+  return ((long long)d.h * d.w) % 4 == 0 && ((uintptr_t)x & 15) == 0;
+}
 bool pw_tc_eligible(const dwbnq_pwconv_desc &d, const void *x, const void *w) {
   const long long hw = (long long)d.h * d.w;
-  return d.dtype == DWBNQ_F32 && hw % 4 == 0 && d.c_in % 4 == 0 && d.c_out <= kPwMaxCout && ((uintptr_t)x & 15) == 0 &&
-         (long long)d.c_out * hw <= 0x7fffffffLL &&
+  return d.dtype == DWBNQ_F32 && d.c_in % 4 == 0 && d.c_out <= kPwMaxCout && (long long)d.c_out * hw <= 0x7fffffffLL &&
+         d.n * hw <= (1LL << 40) &&
          (d.math == DWBNQ_PW_MATH_FP32 || ((uintptr_t)w & 15) == 0);
 }
 
-template <bool MATH3>
+template <bool GATHER, bool MATH3>
 cudaError_t launch_pw_tc(int epi, dim3 grid, size_t smem, cudaStream_t stream, const CUtensorMap &tx, const CUtensorMap &tw,
                          const CUtensorMap &twl, const PwArgs &a) {
   void (*k)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const PwArgs) =
-      epi == PW_EPI_BIAS ? pw_tc_kernel<MATH3, PW_EPI_BIAS>
-      : epi == PW_EPI_BN_FPQ ? pw_tc_kernel<MATH3, PW_EPI_BN_FPQ>
-      : epi == PW_EPI_BN_RELU6_FPQ ? pw_tc_kernel<MATH3, PW_EPI_BN_RELU6_FPQ>
-      : epi == PW_EPI_BN_FPQS ? pw_tc_kernel<MATH3, PW_EPI_BN_FPQS> : pw_tc_kernel<MATH3, PW_EPI_GENERIC>;
-  static thread_local const void *attr_done[10] = {nullptr};  // per host thread; per device it is re-applied lazily
-  static thread_local int attr_dev[10] = {0};
+      epi == PW_EPI_BIAS ? pw_tc_kernel<GATHER, MATH3, PW_EPI_BIAS>
+      : epi == PW_EPI_BN_FPQ ? pw_tc_kernel<GATHER, MATH3, PW_EPI_BN_FPQ>
+      : epi == PW_EPI_BN_RELU6_FPQ ? pw_tc_kernel<GATHER, MATH3, PW_EPI_BN_RELU6_FPQ>
+      : epi == PW_EPI_BN_FPQS ? pw_tc_kernel<GATHER, MATH3, PW_EPI_BN_FPQS> : pw_tc_kernel<GATHER, MATH3, PW_EPI_GENERIC>;
+  // the opt-in to large dynamic shared memory is per function and per device
+  static thread_local const void *attr_done[5] = {nullptr};
+  static thread_local int attr_dev[5] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
-  const int slot = (MATH3 ? 5 : 0) + epi;
-  if (attr_done[slot] != (const void *)k || attr_dev[slot] != dev + 1) {
+  if (attr_done[epi] != (const void *)k || attr_dev[epi] != dev + 1) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kPwSmemMax);
     if (e != cudaSuccess) return e;
-    attr_done[slot] = (const void *)k;
-    attr_dev[slot] = dev + 1;
+    attr_done[epi] = (const void *)k;
+    attr_dev[epi] = dev + 1;
   }
   k<<<grid, kPwThreads, smem, stream>>>(tx, tw, twl, a);
   return cudaGetLastError();
@@ -742,11 +811,25 @@ int launch_pwconv(const dwbnq_pwconv_desc &d, float bn_eps, const dwbnq_quant_de
   a.npad = g.npad; a.co_tiles = g.co_tiles;
   a.pos_tiles = (HW + kPwPosTile - 1) / kPwPosTile;
   a.kchunks = (d.c_in + kPwKChunk - 1) / kPwKChunk;
+  a.x = static_cast<const float *>(x);
+  a.total_pos = d.n * HW;
+  // Gathered when TMA cannot take the plane, or when the per-image tiling would leave more than
+  // a tenth of the accumulator rows empty (196 positions fill 1.53 tiles of 128).
+  bool gather = !pw_tma_x(d, x) || (long long)a.pos_tiles * kPwPosTile * 10 > (long long)HW * 11;
   {
-    const long long total = (long long)a.co_tiles * d.n * a.pos_tiles;
+    static const int env = [] {
+      const char *e = std::getenv("DWBNQ_PW_GATHER");
+      return e && (e[0] == '0' || e[0] == '1') ? e[0] - '0' : -1;
+    }();
+    if (env == 1) gather = true;
+    if (env == 0 && pw_tma_x(d, x)) gather = false;
+  }
+  {
+    const long long per_ct = gather ? (a.total_pos + kPwPosTile - 1) / kPwPosTile : d.n * a.pos_tiles;
+    const long long total = (long long)a.co_tiles * per_ct;
     if (total > 0x7fffffffLL) return fail(DWBNQ_ERR_UNSUPPORTED, "more than 2^31 - 1 tiles");
     a.total_tiles = (int)total;
-    a.per_ct = (int)(d.n * a.pos_tiles);
+    a.per_ct = (int)per_ct;
   }
   a.stage_bytes = (kPwXBytes + g.npad * 128) * (math3 ? 2 : 1);
   const int table_bytes = (g.cpad / 2) * (int)sizeof(PwPair);
@@ -766,7 +849,8 @@ int launch_pwconv(const dwbnq_pwconv_desc &d, float bn_eps, const dwbnq_quant_de
   PwEncodeFn enc = pw_encode_fn();
   if (!enc) return fail(DWBNQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   CUtensorMap tx, tw, twl;
-  {
+  std::memset(&tx, 0, sizeof(tx));
+  if (!gather) {
     const cuuint64_t gdim[3] = {(cuuint64_t)HW, (cuuint64_t)d.c_in, (cuuint64_t)d.n};
     const cuuint64_t gstr[2] = {(cuuint64_t)HW * 4, (cuuint64_t)HW * d.c_in * 4};
     const cuuint32_t box[3] = {32, (cuuint32_t)kPwKChunk, 1}, es[3] = {1, 1, 1};
@@ -797,8 +881,11 @@ int launch_pwconv(const dwbnq_pwconv_desc &d, float bn_eps, const dwbnq_quant_de
   const int sms = sm_count(dev);
   int grid = a.total_tiles < sms ? a.total_tiles : sms;
   if (t_pw_max_ctas > 0 && grid > t_pw_max_ctas) grid = t_pw_max_ctas;
-  const cudaError_t e = math3 ? launch_pw_tc<true>(epi, dim3((unsigned)grid), smem, stream, tx, tw, twl, a)
-                              : launch_pw_tc<false>(epi, dim3((unsigned)grid), smem, stream, tx, tw, twl, a);
+  const dim3 gd((unsigned)grid);
+  const cudaError_t e = gather ? (math3 ? launch_pw_tc<true, true>(epi, gd, smem, stream, tx, tw, twl, a)
+                                        : launch_pw_tc<true, false>(epi, gd, smem, stream, tx, tw, twl, a))
+                               : (math3 ? launch_pw_tc<false, true>(epi, gd, smem, stream, tx, tw, twl, a)
+                                        : launch_pw_tc<false, false>(epi, gd, smem, stream, tx, tw, twl, a));
   if (e != cudaSuccess) return fail_cuda(e, "pw_tc_kernel launch");
   return DWBNQ_OK;
 }

@@ -84,6 +84,13 @@ SHAPES = [
     (1, 960, 160, 14, 14),   # more k chunks than pipeline stages
     (2, 64, 384, 14, 14),    # 384 = 256 + 128
     (5, 16, 96, 28, 28),     # several tiles per CTA in a small grid
+    # planes TMA cannot take, or that would fill the 128-row tiles badly: rows gathered across images
+    (2, 32, 64, 7, 7),
+    (5, 160, 70, 7, 7),
+    (3, 64, 96, 14, 14),
+    (2, 8, 16, 5, 9),
+    (1, 4, 8, 1, 1),
+    (7, 96, 160, 3, 3),
 ]
 
 
@@ -130,7 +137,7 @@ def test_no_bias_and_partial_bn_vectors(oracle, cuda_device):
     ops.check_device_flag()
 
 
-FMA_SHAPES = [(2, 32, 64, 7, 7), (3, 30, 50, 5, 9), (1, 3, 5, 1, 1), (2, 160, 70, 7, 7), (2, 17, 130, 14, 14)]
+FMA_SHAPES = [(3, 30, 50, 5, 9), (1, 3, 5, 1, 1), (2, 17, 130, 14, 14), (2, 6, 16, 8, 8)]  # c_in not a multiple of 4
 
 
 @pytest.mark.parametrize("shape", FMA_SHAPES, ids=lambda s: "x".join(map(str, s)))
@@ -177,9 +184,9 @@ def test_forced_kernel_choice_and_the_two_kernels_agree(oracle, cuda_device):
         fma = ops.pointwise_convolution(t["x"], t["w"], t["b"]).cpu().numpy()
         ops.set_forced_pw_path(1)
         tc = ops.pointwise_convolution(t["x"], t["w"], t["b"]).cpu().numpy()
-        odd = dev(rng.standard_normal((1, 64, 7, 7), dtype=np.float32), cuda_device)
+        odd = dev(rng.standard_normal((1, 30, 7, 7), dtype=np.float32), cuda_device)
         with pytest.raises(L.DwbnqError) as e:
-            ops.pointwise_convolution(odd, t["w"], t["b"])
+            ops.pointwise_convolution(odd, dev(rng.standard_normal((8, 30, 1, 1), dtype=np.float32), cuda_device), None)
         assert e.value.status == 2
     finally:
         ops.set_forced_pw_path(-1)
@@ -188,14 +195,16 @@ def test_forced_kernel_choice_and_the_two_kernels_agree(oracle, cuda_device):
     ops.check_device_flag()
 
 
+@pytest.mark.parametrize("plane", [(36, 40), (14, 14), (7, 7)], ids=lambda s: "%dx%d" % s)
 @pytest.mark.parametrize("co", [16, 96, 144, 200, 384], ids=lambda c: "co%d" % c)
 @pytest.mark.parametrize("math", ["fp32", "tf32"])
-def test_many_tiles_per_cta(oracle, cuda_device, co, math):
+def test_many_tiles_per_cta(oracle, cuda_device, co, math, plane):
     """Three CTAs walk through 60 to 120 tiles each: every pipeline stage and every accumulator
     buffer is reused many times, with the plain (fast) and the fused (slower) epilogue, for every
     buffer count the channel tile widths give (8, 4, 3, 2 buffers)."""
     rng = np.random.default_rng(co)
-    d = make(rng, 12, 40, co, 36, 40)  # 1440 positions = 11.25 tiles per image
+    # 1440 positions = 11.25 tiles per image through TMA; 14x14 planes gathered across images
+    d = make(rng, 12 * 1440 // (plane[0] * plane[1]), 40, co, *plane)
     t = {k: dev(v, cuda_device) for k, v in d.items()}
     try:
         ops.set_pw_max_ctas(3)
