@@ -280,7 +280,7 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
     for (int s = 0; s < a.stages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
-      mbar_init(&split[s], 32 * kPwXWarps);
+      mbar_init(&split[s], kPwXWarps);  // one arrival per X-worker warp
     }
     for (int b = 0; b < a.nacc; ++b) {
       mbar_init(&acc_full[b], 1);
@@ -390,40 +390,74 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
       const int m = tid & 127, kh = tid >> 7;
       const unsigned int sw_base = (unsigned)((m >> 5) * 4096 + (m & 7) * 4);
       const unsigned int unit = (unsigned)((m >> 3) & 3);
-      unsigned int it = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
-        const int pt = t % a.per_ct;
-        const long long g = (long long)pt * kPwPosTile + m;
-        const bool valid = g < a.total_pos;
-        const long long n = valid ? g / a.HW : 0;
-        const int p = valid ? (int)(g - n * a.HW) : 0;
-        const float *xp = a.x + (size_t)n * a.Ci * a.HW + p;
-        for (int kc = 0; kc < a.kchunks; ++kc, ++it) {
-          const int s = it % a.stages;
-          const unsigned int ph = (it / a.stages) & 1u;
-          const int k0 = kc * kPwKChunk + kh * 16;
-          float v[16];
+      // The loads of a chunk are issued one chunk ahead of its stores (two register sets), so the
+      // memory latency of chunk i + 1 runs under the barrier wait, the stores and the MMAs of
+      // chunk i; the load cursor runs through the (tile, chunk) sequence on its own.
+      int t_l = blockIdx.x, kc_l = 0;
+      bool valid_l = false;
+      const float *xp_l = a.x;
+      auto locate = [&]() {
+        const long long g = (long long)(t_l % a.per_ct) * kPwPosTile + m;
+        valid_l = g < a.total_pos;
+        const long long n = valid_l ? g / a.HW : 0;
+        xp_l = a.x + (size_t)n * a.Ci * a.HW + (valid_l ? (int)(g - n * a.HW) : 0);
+      };
+      const size_t plane = (size_t)a.HW;
+      auto load = [&](float(&v)[16]) {
+        const int k0 = kc_l * kPwKChunk + kh * 16;
+        const float *q = xp_l + (size_t)k0 * plane;
+        if (valid_l && k0 + 16 <= a.Ci) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = (valid && k0 + j < a.Ci) ? __ldg(xp + (size_t)(k0 + j) * a.HW) : 0.0f;
-          ok = pw_wait(&empty[s], ph ^ 1u) && !*abort_v;
-          if (!ok) break;
-          unsigned char *xh = sm + (size_t)s * a.stage_bytes;
+          for (int j = 0; j < 16; ++j) v[j] = __ldg(q + j * plane);
+        } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int k = kh * 16 + j;
-            const unsigned int off = sw_base + (unsigned)k * 128u + ((unit ^ (unsigned)(k & 3)) << 5);
-            if (MATH3) {
-              const float h = __uint_as_float(__float_as_uint(v[j]) & 0xffffe000u);
-              *reinterpret_cast<float *>(xh + off) = h;
-              *reinterpret_cast<float *>(xh + off_xlo + off) = __fsub_rn(v[j], h);
-            } else {
-              *reinterpret_cast<float *>(xh + off) = v[j];
-            }
-          }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // visible to the tensor core's reads
-          mbar_arrive(&split[s]);
+          for (int j = 0; j < 16; ++j) v[j] = (valid_l && k0 + j < a.Ci) ? __ldg(q + j * plane) : 0.0f;
         }
+        if (++kc_l == a.kchunks) {
+          kc_l = 0;
+          t_l += gridDim.x;
+          if (t_l < a.total_tiles) locate();
+        }
+      };
+      auto store = [&](const float(&v)[16], unsigned int it) -> bool {
+        const int s = it % a.stages;
+        const unsigned int ph = (it / a.stages) & 1u;
+        if (!pw_wait(&empty[s], ph ^ 1u) || *abort_v) return false;
+        // row k = 16 kh + j of the chunk: k mod 4 = j mod 4, so four base addresses serve all rows
+        unsigned char *xh = sm + (size_t)s * a.stage_bytes + sw_base + kh * 2048;
+        unsigned char *const rb[4] = {xh + ((unit ^ 0u) << 5), xh + ((unit ^ 1u) << 5), xh + ((unit ^ 2u) << 5),
+                                      xh + ((unit ^ 3u) << 5)};
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float *dst = reinterpret_cast<float *>(rb[j & 3] + j * 128);
+          if (MATH3) {
+            const float h = __uint_as_float(__float_as_uint(v[j]) & 0xffffe000u);
+            *dst = h;
+            *reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(dst) + off_xlo) = __fsub_rn(v[j], h);
+          } else {
+            *dst = v[j];
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // visible to the tensor core's reads
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&split[s]);
+        return true;
+      };
+      float va[16], vb[16];
+      bool ok = true, have_a = t_l < a.total_tiles, have_b = false;
+      if (have_a) {
+        locate();
+        load(va);
+      }
+      for (unsigned int it = 0; have_a; it += 2) {
+        have_b = t_l < a.total_tiles;
+        if (have_b) load(vb);
+        ok = store(va, it);
+        if (!ok || !have_b) break;
+        have_a = t_l < a.total_tiles;
+        if (have_a) load(va);
+        ok = store(vb, it + 1);
+        if (!ok) break;
       }
       if (!ok && lane == 0 && !*abort_v) { atomicExch(a.flag, 1); *abort_v = 1; }
     } else if (MATH3) {
@@ -451,7 +485,8 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
             xl[i] = l;
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // visible to the tensor core's reads
-          mbar_arrive(&split[s]);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&split[s]);
         }
       }
       if (!ok && lane == 0 && !*abort_v) { atomicExch(a.flag, 1); *abort_v = 1; }
