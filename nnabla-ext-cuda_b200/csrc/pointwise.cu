@@ -315,68 +315,83 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
   if (warp == 0) {
     // ---- producer: one lane issues the TMA loads of every (tile, c_in chunk) ----
     if (lane == 0) {
-      unsigned int it = 0;
+      // (stage, phase) advance with a counter: this one thread's instruction stream is the
+      // latency of the whole load pipeline, so nothing in it divides or recomputes addresses
+      int s = 0;
+      unsigned int ph = 0;
       const unsigned int bytes = (GATHER ? 0 : kPwXBytes) + wbytes * (MATH3 ? 2 : 1);
+      const unsigned int full0 = smem_u32(&full[0]), empty0 = smem_u32(&empty[0]);
       bool ok = true;
       for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
         const int ct = t / a.per_ct;
         const int r = t - ct * a.per_ct;
         const int n = GATHER ? 0 : r / a.pos_tiles, pt = GATHER ? r : r - n * a.pos_tiles;
-        for (int kc = 0; kc < a.kchunks; ++kc, ++it) {
-          const int s = it % a.stages;
-          const unsigned int ph = (it / a.stages) & 1u;
+        const int c0 = ct * a.npad, p0 = pt * kPwPosTile;
+        for (int kc = 0; kc < a.kchunks; ++kc) {
           if (!pw_wait_lane(&empty[s], ph ^ 1u) || *abort_v) { ok = false; break; }
           unsigned char *st = sm + (size_t)s * a.stage_bytes;
           mbar_expect_tx(&full[s], bytes);
           if (!GATHER) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q)
-              tma_load_3d(st + q * 4096, &tm_x, pt * kPwPosTile + q * 32, kc * kPwKChunk, n, &full[s]);
+            for (int q = 0; q < 4; ++q) tma_load_3d(st + q * 4096, &tm_x, p0 + q * 32, kc * kPwKChunk, n, &full[s]);
           }
-          tma_load_2d(st + off_w, &tm_w, kc * kPwKChunk, ct * a.npad, &full[s]);
-          if (MATH3) tma_load_2d(st + off_wlo, &tm_wlo, kc * kPwKChunk, ct * a.npad, &full[s]);
+          tma_load_2d(st + off_w, &tm_w, kc * kPwKChunk, c0, &full[s]);
+          if (MATH3) tma_load_2d(st + off_wlo, &tm_wlo, kc * kPwKChunk, c0, &full[s]);
+          if (++s == a.stages) { s = 0; ph ^= 1u; }
         }
       }
+      (void)full0; (void)empty0;
       if (!ok && !*abort_v) { atomicExch(a.flag, 1); *abort_v = 1; }
     }
   } else if (warp == 1) {
-    // ---- MMA issuer ----
-    // instruction descriptor: fp32 accumulator, TF32 A and B, A MN-major, B K-major, N, M = 128
-    const unsigned int idesc = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | ((unsigned)(a.npad >> 3) << 17) | (8u << 24);
-    unsigned int it = 0, tile_i = 0;
-    bool ok = true;
-    for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x, ++tile_i) {
-      const unsigned int b = tile_i % a.nacc, aph = (tile_i / a.nacc) & 1u;
-      ok = pw_wait(&acc_empty[b], aph ^ 1u);
-      tc_fence_after();
-      for (int kc = 0; ok && kc < a.kchunks; ++kc, ++it) {
-        const int s = it % a.stages;
-        const unsigned int ph = (it / a.stages) & 1u;
-        ok = pw_wait(&full[s], ph);
-        if (ok && (MATH3 || GATHER)) ok = pw_wait(&split[s], ph);
-        if (!ok) break;
+    // ---- MMA issuer: one thread. Its instruction stream is serial, so the descriptors of a
+    // stage are the stage-0 descriptors plus a multiple of the stage size (the address field
+    // counts 16-byte units and cannot carry into the next field: shared memory ends below
+    // 2^18), and stages / buffers advance with counters ----
+    if (lane == 0) {
+      // instruction descriptor: fp32 accumulator, TF32 A and B, A MN-major, B K-major, N, M = 128
+      const unsigned int idesc = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | ((unsigned)(a.npad >> 3) << 17) | (8u << 24);
+      const unsigned long long da0 = pw_desc_a(base, 0), dal0 = pw_desc_a(base + off_xlo, 0);
+      const unsigned long long db0 = pw_desc_b(base + off_w, 0), dbl0 = pw_desc_b(base + off_wlo, 0);
+      const unsigned long long stage_step = (unsigned long long)(a.stage_bytes >> 4);
+      const int last_steps = ((a.Ci - (a.kchunks - 1) * kPwKChunk) + 7) >> 3;  // rows past c_in are zero-filled
+      int s = 0, b = 0;
+      unsigned int ph = 0, aph = 0;
+      unsigned long long so = 0;  // s * stage_step
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
+        ok = pw_wait_lane(&acc_empty[b], aph ^ 1u);
         tc_fence_after();
-        if (lane == 0) {
-          const unsigned int sb = base + (unsigned)s * a.stage_bytes;
-          const int krem = a.Ci - kc * kPwKChunk;
-          const int ksteps = krem >= kPwKChunk ? kPwKChunk / 8 : (krem + 7) >> 3;  // rows past c_in are zero-filled
-          const unsigned int d = tmem_base + b * a.npad;
+        const unsigned int d = tmem_base + b * a.npad;
+        for (int kc = 0; ok && kc < a.kchunks; ++kc) {
+          ok = pw_wait_lane(&full[s], ph);
+          if (ok && (MATH3 || GATHER)) ok = pw_wait_lane(&split[s], ph);
+          if (!ok) break;
+          tc_fence_after();
+          const int ksteps = kc == a.kchunks - 1 ? last_steps : kPwKChunk / 8;
+          unsigned long long da = da0 + so, db = db0 + so, dal = dal0 + so, dbl = dbl0 + so;
+          unsigned int acc = kc ? 1u : 0u;
+#pragma unroll 1
           for (int j = 0; j < ksteps; ++j) {
-            const unsigned long long da = pw_desc_a(sb, j), db = pw_desc_b(sb + off_w, j);
-            tc_mma_tf32(d, da, db, idesc, (kc | j) ? 1u : 0u);
+            tc_mma_tf32(d, da, db, idesc, acc);
             if (MATH3) {
-              tc_mma_tf32(d, pw_desc_a(sb + off_xlo, j), db, idesc, 1u);
-              tc_mma_tf32(d, da, pw_desc_b(sb + off_wlo, j), idesc, 1u);
+              tc_mma_tf32(d, dal, db, idesc, 1u);
+              tc_mma_tf32(d, da, dbl, idesc, 1u);
             }
+            acc = 1u;
+            da += 64; dal += 64;  // 8 rows of 128 bytes
+            db += 2; dbl += 2;    // 32 bytes along the row
           }
           tc_commit(&empty[s]);
           if (kc == a.kchunks - 1) tc_commit(&acc_full[b]);
+          so += stage_step;
+          if (++s == a.stages) { s = 0; ph ^= 1u; so = 0; }
         }
-        __syncwarp();
+        if (++b == a.nacc) { b = 0; aph ^= 1u; }
+        if (*abort_v) ok = false;
       }
-      if (*abort_v) ok = false;
+      if (!ok && !*abort_v) { atomicExch(a.flag, 1); *abort_v = 1; }
     }
-    if (!ok && lane == 0 && !*abort_v) { atomicExch(a.flag, 1); *abort_v = 1; }
   } else if (warp < kPwFirstEpiWarp) {
     // ---- X workers (eight warps) ----
     const int tid = threadIdx.x - 64;
@@ -419,9 +434,9 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
           if (t_l < a.total_tiles) locate();
         }
       };
-      auto store = [&](const float(&v)[16], unsigned int it) -> bool {
-        const int s = it % a.stages;
-        const unsigned int ph = (it / a.stages) & 1u;
+      int s = 0;
+      unsigned int ph = 0;
+      auto store = [&](const float(&v)[16]) -> bool {
         if (!pw_wait(&empty[s], ph ^ 1u) || *abort_v) return false;
         // row k = 16 kh + j of the chunk: k mod 4 = j mod 4, so four base addresses serve all rows
         unsigned char *xh = sm + (size_t)s * a.stage_bytes + sw_base + kh * 2048;
@@ -441,6 +456,7 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // visible to the tensor core's reads
         __syncwarp();
         if (lane == 0) mbar_arrive(&split[s]);
+        if (++s == a.stages) { s = 0; ph ^= 1u; }
         return true;
       };
       float va[16], vb[16];
@@ -449,25 +465,24 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
         locate();
         load(va);
       }
-      for (unsigned int it = 0; have_a; it += 2) {
+      while (have_a) {
         have_b = t_l < a.total_tiles;
         if (have_b) load(vb);
-        ok = store(va, it);
+        ok = store(va);
         if (!ok || !have_b) break;
         have_a = t_l < a.total_tiles;
         if (have_a) load(va);
-        ok = store(vb, it + 1);
+        ok = store(vb);
         if (!ok) break;
       }
       if (!ok && lane == 0 && !*abort_v) { atomicExch(a.flag, 1); *abort_v = 1; }
     } else if (MATH3) {
       // three-pass mode: x -> (x with the low 13 mantissa bits cleared, the exact rest), in place
-      unsigned int it = 0;
+      int s = 0;
+      unsigned int ph = 0;
       bool ok = true;
       for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
-        for (int kc = 0; kc < a.kchunks; ++kc, ++it) {
-          const int s = it % a.stages;
-          const unsigned int ph = (it / a.stages) & 1u;
+        for (int kc = 0; kc < a.kchunks; ++kc) {
           ok = pw_wait(&full[s], ph) && !*abort_v;
           if (!ok) break;
           uint4 *xh = reinterpret_cast<uint4 *>(sm + (size_t)s * a.stage_bytes);
@@ -487,6 +502,7 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // visible to the tensor core's reads
           __syncwarp();
           if (lane == 0) mbar_arrive(&split[s]);
+          if (++s == a.stages) { s = 0; ph ^= 1u; }
         }
       }
       if (!ok && lane == 0 && !*abort_v) { atomicExch(a.flag, 1); *abort_v = 1; }
@@ -501,9 +517,12 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
     const f32x2 nz = negzero2();
     const FpqPacked fq = make_fpq_packed(a.q);
     const bool bn_safe = unsafe_s == 0;
-    unsigned int tile_i = 0;
-    for (int t = blockIdx.x; t < a.total_tiles; t += gridDim.x, ++tile_i) {
-      if ((int)(tile_i % (unsigned)a.ngroups) != group) continue;
+    int b = group;  // tile i of this CTA lives in buffer i mod nacc; the group's tiles are ngroups apart
+    unsigned int aph = 0;
+    const long long t_step = (long long)gridDim.x * a.ngroups;
+    for (long long tl = (long long)blockIdx.x + (long long)group * gridDim.x; group < a.ngroups && tl < a.total_tiles;
+         tl += t_step) {
+      const int t = (int)tl;
       const int ct = t / a.per_ct;
       const int r = t - ct * a.per_ct;
       long long n;
@@ -519,7 +538,6 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
         p = (r - (int)n * a.pos_tiles) * kPwPosTile + quarter * 32 + lane;
         p_ok = p < a.HW;
       }
-      const unsigned int b = tile_i % a.nacc, aph = (tile_i / a.nacc) & 1u;
       if (!pw_wait(&acc_full[b], aph) || *abort_v) {
         if (lane == 0 && !*abort_v) { atomicExch(a.flag, 1); *abort_v = 1; }
         break;
@@ -573,6 +591,8 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[b]);
+      b += a.ngroups;
+      if (b >= a.nacc) { b -= a.nacc; aph ^= 1u; }
     }
   }
   tc_fence_before();

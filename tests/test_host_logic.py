@@ -250,3 +250,36 @@ def test_planner_invariants_over_random_descriptors(dwlib):
             groups = -(-n * c // p.value)
             assert ctas.value % groups == 0 and (ctas.value // groups) * th.value >= ho, (h, w, k, s, path.value)
     assert {dwlib.PATH_GENERIC, dwlib.PATH_PLANE, dwlib.PATH_PLANE_GEN}.issubset(seen), seen
+
+
+def test_pointwise_descriptor_validation_workspace_and_plan(dwlib):
+    lib = dwlib.lib()
+    P = dwlib.PwConvDesc
+    good = P(dtype=dwlib.F32, c_in=32, c_out=96, h=14, w=14, n=4, math=dwlib.PW_MATH_FP32, act=dwlib.ACT_RELU6)
+    # coefficients of the 96 channels (one tile of 96 columns) + the two TF32 halves of w
+    assert lib.dwbnq_pwconv_workspace_bytes(ctypes.byref(good)) == 2048 + 2 * 32 * 96 * 4
+    wide = P(dtype=dwlib.F32, c_in=8, c_out=300, h=2, w=2, n=1)  # three tiles of 128 columns (100 -> 128)
+    assert lib.dwbnq_pwconv_workspace_bytes(ctypes.byref(wide)) == 5 * 384 * 4 + 2 * ((8 * 300 * 4 + 255) // 256 * 256)
+    fake, path = ctypes.c_void_p(4096), ctypes.c_int(-1)
+    assert lib.dwbnq_pwconv_plan(ctypes.byref(good), fake, fake, ctypes.byref(path)) == dwlib.OK and path.value == 1
+    for bad in (P(dtype=dwlib.F16, c_in=32, c_out=96, h=14, w=14, n=4),   # fp16 tensors
+                P(dtype=dwlib.F32, c_in=30, c_out=96, h=14, w=14, n=4)):  # weight rows not 16-byte multiples
+        assert lib.dwbnq_pwconv_plan(ctypes.byref(bad), fake, fake, ctypes.byref(path)) == dwlib.OK and path.value == 0
+    # a 7x7 plane is gathered, an unaligned x too: still the tensor-core kernel
+    odd = P(dtype=dwlib.F32, c_in=32, c_out=96, h=7, w=7, n=4)
+    assert lib.dwbnq_pwconv_plan(ctypes.byref(odd), ctypes.c_void_p(4100), fake, ctypes.byref(path)) == dwlib.OK
+    assert path.value == 1
+    for kw in ({"dtype": 3}, {"c_in": 0}, {"c_out": -1}, {"h": 0}, {"n": -1}, {"math": 2}, {"act": 3}):
+        args = dict(dtype=dwlib.F32, c_in=32, c_out=96, h=14, w=14, n=4)
+        args.update(kw)
+        d = P(**args)
+        assert lib.dwbnq_pwconv_workspace_bytes(ctypes.byref(d)) == 0
+        assert lib.dwbnq_pwconv_fwd(ctypes.byref(d), fake, fake, None, fake, fake, -1, None) == dwlib.ERR_INVALID_ARG
+        assert lib.dwbnq_last_error_string()
+    assert lib.dwbnq_pwconv_fwd(None, fake, fake, None, fake, fake, -1, None) == dwlib.ERR_INVALID_ARG
+    assert lib.dwbnq_pwconv_fwd(ctypes.byref(good), fake, fake, None, fake, fake, -1, None) == dwlib.ERR_INVALID_ARG  # act
+    assert lib.dwbnq_set_forced_pw_path(2) == dwlib.ERR_INVALID_ARG
+    assert lib.dwbnq_set_pw_max_ctas(-1) == dwlib.ERR_INVALID_ARG
+    if lib.dwbnq_device_count() == 0:  # no CPU fallback
+        ok = P(dtype=dwlib.F32, c_in=32, c_out=96, h=14, w=14, n=4)
+        assert lib.dwbnq_pwconv_fwd(ctypes.byref(ok), fake, fake, None, fake, fake, -1, None) == dwlib.ERR_CUDA

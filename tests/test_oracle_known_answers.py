@@ -207,3 +207,40 @@ def test_quantize_linear_known_answers(oracle):
     v = np.array([0.03, 0.0625, 0.19, 40.0, -1.0], np.float32)
     codes = oracle.quantize_linear(v, 0.125, 0, "HALF_AWAY_FROM_ZERO", 0, 255)
     np.testing.assert_array_equal(oracle.dequantize_linear(codes, 0.125, 0), oracle.fpq(v, False, 8, 0.125))
+
+
+def test_pointwise_convolution_known_answers(oracle):
+    """A 1x1 convolution worked by hand: y[co][p] = sum_ci w[co][ci] x[ci][p] + b[co], the bias
+    added after the sum; the double accumulation, the fp32 accumulation and sum |w||x| + |b|."""
+    x = np.array([[[[1.0, -2.0]], [[0.5, 4.0]], [[3.0, 0.25]]]], dtype=np.float32)  # [1, 3, 1, 2]
+    w = np.array([[2.0, -1.0, 0.5], [0.0, 0.25, -4.0]], dtype=np.float32)
+    b = np.array([0.125, -1.0], dtype=np.float32)
+    acc32, acc64, mag = oracle.pwconv(x, w, b)
+    want = np.array([[[[2 - 0.5 + 1.5 + 0.125, -4 - 4 + 0.125 + 0.125]], [[0.125 - 12 - 1, 1 - 1 - 1]]]], dtype=np.float32)
+    np.testing.assert_array_equal(acc32, want)
+    np.testing.assert_array_equal(acc64, want)
+    np.testing.assert_array_equal(mag[0, 0, 0], [2 + 0.5 + 1.5 + 0.125, 4 + 4 + 0.125 + 0.125])
+    # the weight may come as [co, ci, 1, 1]; no bias
+    a32, _, m = oracle.pwconv(x, w.reshape(2, 3, 1, 1), None)
+    np.testing.assert_array_equal(a32, want - b[None, :, None, None])
+    # fp32 accumulation in ascending channel order: 2^24 + 1 is lost, then -2^24 leaves 0
+    xx = np.array([[[[1.0]], [[1.0]], [[1.0]]]], dtype=np.float32)
+    ww = np.array([[16777216.0, 1.0, -16777216.0]], dtype=np.float32)
+    a32, a64, _ = oracle.pwconv(xx, ww, None)
+    assert a32.item() == 0.0 and a64.item() == 1.0
+
+
+def test_activations_and_pointwise_epilogue(oracle):
+    v = np.array([-1.0, -0.0, 0.5, 6.0, 7.5, np.nan, np.inf, -np.inf], dtype=np.float32)
+    np.testing.assert_array_equal(oracle.act(v, "relu6"), [0, 0, 0.5, 6, 6, 0, 6, 0])
+    np.testing.assert_array_equal(oracle.act(v, "relu"), [0, 0, 0.5, 6, 7.5, 0, np.inf, 0])
+    np.testing.assert_array_equal(oracle.act(v, None).view(np.uint32), v.view(np.uint32))
+    # BN -> ReLU6 -> unsigned FixedPointQuantize equals the three oracle functions in sequence
+    rng = np.random.default_rng(0)
+    conv = rng.standard_normal((2, 3, 4, 5), dtype=np.float32) * 3
+    beta, gamma, mean, var = (rng.standard_normal(3, dtype=np.float32), np.array([1.5, -0.5, 1.0], np.float32),
+                              rng.standard_normal(3, dtype=np.float32), np.array([0.5, 1.0, 2.0], np.float32))
+    q = {"kind": "fpq", "sign": False, "n": 8, "delta": 0.125}
+    want = oracle.fpq(oracle.act(oracle.bn_infer(conv, beta, gamma, mean, var, 1e-5), "relu6"), False, 8, 0.125)
+    np.testing.assert_array_equal(oracle.pw_epilogue(conv, beta, gamma, mean, var, 1e-5, "relu6", q), want)
+    np.testing.assert_array_equal(oracle.pw_epilogue(conv, None, None, None, None, 1e-5, None, None), conv)
