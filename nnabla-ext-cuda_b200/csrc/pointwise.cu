@@ -730,12 +730,16 @@ inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 struct PwGeom {
   int npad, co_tiles, cpad;
 };
-PwGeom pw_geom(int Co) {
+PwGeom pw_geom(int Co, int Ci) {
   // Channel tiles of at most 128 columns: four accumulator buffers then fit in TMEM, which keeps
-  // all four epilogue groups busy (a 256-column tile leaves room for two). The tiles are equal,
-  // rounded up to the 32 columns the epilogue's units and the MMA shape want.
+  // all four epilogue groups busy (a 256-column tile leaves room for two). With a long sum
+  // (c_in >= 256) the MMA thread is the busy one - an MMA costs it the same ~30 ns whether it is
+  // 32 or 128 columns wide, and every chunk of every tile a commit - so the tiles go up to 256
+  // columns there. The tiles are equal, rounded up to the 32 columns the epilogue's units and
+  // the MMA shape want.
   PwGeom g;
-  const int tiles = (Co + 127) / 128;
+  const int widest = Ci >= 256 ? kPwMaxCoTile : 128;
+  const int tiles = (Co + widest - 1) / widest;
   g.npad = ((Co + tiles - 1) / tiles + 31) / 32 * 32;
   g.co_tiles = (Co + g.npad - 1) / g.npad;
   g.cpad = g.co_tiles * g.npad;
@@ -813,7 +817,7 @@ int launch_pwconv(const dwbnq_pwconv_desc &d, float bn_eps, const dwbnq_quant_de
   else if (kind == DWBNQ_Q_POW2) st = fill_pow2(&qa, q->sign, q->with_zero, q->n, q->m, dev);
   if (st != DWBNQ_OK) return st;
 
-  const PwGeom g = pw_geom(d.c_out);
+  const PwGeom g = pw_geom(d.c_out, d.c_in);
   const int HW = d.h * d.w;
   const long long wsize = (long long)d.c_in * d.c_out;
   float *coef = static_cast<float *>(workspace);
@@ -946,7 +950,7 @@ int launch_pwconv(const dwbnq_pwconv_desc &d, float bn_eps, const dwbnq_quant_de
 }
 
 size_t pwconv_workspace_bytes(const dwbnq_pwconv_desc &d) {
-  const PwGeom g = pw_geom(d.c_out);
+  const PwGeom g = pw_geom(d.c_out, d.c_in);
   return align256((size_t)5 * g.cpad * 4) + 2 * align256((size_t)d.c_in * d.c_out * 4);
 }
 int pwconv_validate(const dwbnq_pwconv_desc *d) { return validate_pw(d); }
