@@ -349,7 +349,7 @@ def run_pointwise(args):
                                    "each fused with BN, activation and FixedPointQuantize" % n,
                        "l2": "L2 flushed before every timed launch"},
             "roofline": {"bound": "hbm", "achieved": tot["gbs"], "peak": peak, "unit": "GB/s", "frac": tot["frac"],
-                         "traffic": None, "peak_kind": peak_kind}, "gpu_launches": 2 * len(rows) - 4, "layers": rows}
+                         "traffic": None, "peak_kind": peak_kind}, "gpu_launches": 2 * sum(1 for r in rows if r["workload"].startswith("pw1.l")), "layers": rows}
     print(json.dumps(line), flush=True)
 
 
@@ -389,6 +389,24 @@ def pointwise_rows(torch, ops, workloads, device, batch, peak):
     deeper layers move less than L2 holds); median of 10. Per-layer rows for the fp32-accurate
     three-pass TF32 mode, and a summary row for it and for the single-pass TF32 mode."""
     rows, totals = [], {"fp32": [0.0, 0, 0.0], "tf32": [0.0, 0, 0.0]}
+    lib_ms = {"conv": 0.0, "chain": 0.0}
+    import torch.nn.functional as F
+    tf32_was = torch.backends.cudnn.allow_tf32
+    torch.backends.cudnn.allow_tf32 = False
+
+    def median_ms(fn, reps=5):
+        fn()
+        ts = []
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(reps):
+            flush_l2(torch, device)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return float(np.median(ts))
+
     for spec in workloads.pw1(batch):
         d = workloads.make_pointwise_data(spec)
         t = {k: torch.from_numpy(v).to(device) for k, v in d.items()}
@@ -436,9 +454,30 @@ def pointwise_rows(torch, ops, workloads, device, batch, peak):
                              "algorithmic_bytes": nbytes,
                              "kernel": "pw_tc_kernel (tcgen05, three TF32 passes)" if path == 1 else "pw_simt_kernel (FMA)",
                              "timing": "median of 10 CUDA-graph replays, L2 flushed before each"})
+        # library baseline: the convolution as cuDNN runs it in fp32 (TF32 off, as the reference
+        # defaults), then BN, activation and quantizer as the separate passes the reference makes
+        lib_ms["conv"] += median_ms(lambda: F.conv2d(t["x"], t["w"], t["b"]))
+        q = spec.quant
+
+        def chain():
+            v = F.conv2d(t["x"], t["w"], t["b"])
+            ops.batch_normalization(v, t["beta"], t["gamma"], t["mean"], t["var"], eps=spec.bn_eps, out=v)
+            if spec.act == "relu6":
+                v.clamp_(0.0, 6.0)
+            ops.fixed_point_quantize(v, q["sign"], q["n"], q["delta"], out=v)
+        lib_ms["chain"] += median_ms(chain)
         del t, y, ws
         torch.cuda.empty_cache()
+    torch.backends.cudnn.allow_tf32 = tf32_was
     ops.check_device_flag()
+    nb_all, fl_all = totals["fp32"][1], totals["fp32"][2]
+    for key, what in (("conv", "torch conv2d alone (cuDNN fp32, TF32 off)"),
+                      ("chain", "torch conv2d (cuDNN fp32) + BN + ReLU6 + FixedPointQuantize as separate passes")):
+        ms = lib_ms[key]
+        rows.append({"workload": "pw1 library baseline: " + what, "dtype": "f32", "batch": batch, "ms": ms,
+                     "images_per_s": batch / (ms / 1e3), "gbs": nb_all / ms / 1e6, "frac": nb_all / ms / 1e6 / peak,
+                     "tflops": fl_all / ms / 1e9, "algorithmic_bytes": nb_all, "kernel": "library kernels, for comparison only",
+                     "timing": "median of 5 eager calls per layer, L2 flushed before each (host launch overhead included)"})
     for math, (ms, nbytes, fl) in totals.items():
         rows.append({"workload": "pw1: 33 pointwise layers, math %s" % math, "dtype": "f32", "batch": batch, "ms": ms,
                      "images_per_s": batch / (ms / 1e3), "gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak,
