@@ -22,7 +22,9 @@
 //
 // Besides the five registered classes the plugin holds FusedDwBnQuantCuda, the single
 // function object a graph converter substitutes for a whole dw-conv -> BN -> quantizer
-// chain, and its factory dwbnq_nbla_create_fused().
+// chain, and its factory dwbnq_nbla_create_fused(); and FusedPwBnQuantCuda with
+// dwbnq_nbla_create_fused_pw() for the pointwise convolution -> BN -> activation -> quantizer
+// chains either side of it.
 #include <dwbnq.h>
 
 #include <nbla/cuda/common.hpp>
@@ -436,6 +438,101 @@ protected:
   DWBNQ_NO_BACKWARD("FusedDwBnQuantCuda")
 };
 
+// ---- the pointwise chain ------------------------------------------------------------------
+// Convolution (1x1, pad 0, stride 1, dilation 1, group 1) -> BatchNormalization
+// (batch_stat = false) -> [ReLU | ReLU6] -> FixedPointQuantize | Pow2Quantize as one function
+// object, the counterpart of FusedDwBnQuantCuda for the convolutions either side of a depthwise
+// layer. Inputs [x, w, (b), (beta), (gamma), mean, var], one output. The accuracy mode of the
+// sum follows the switch the reference has for its GEMMs: three TF32 passes (fp32 class)
+// unless TF32 is allowed (NNABLA_CUDA_ALLOW_TF32, src/nbla/cuda/init.cpp.tmpl:76-83).
+template <typename T>
+class FusedPwBnQuantCuda
+    : public BaseFunction<int, bool, float, bool, bool, int, int, bool, bool, int, int, float, bool> {
+public:
+  typedef typename CudaType<T>::type Tc;
+  typedef BaseFunction<int, bool, float, bool, bool, int, int, bool, bool, int, int, float, bool> Base;
+  FusedPwBnQuantCuda(const Context &ctx, int base_axis, bool with_bias, float bn_eps, bool no_scale, bool no_bias,
+                     int act, int quant_kind, bool sign, bool with_zero, int n, int m, float delta, bool allow_tf32)
+      : Base(ctx, base_axis, with_bias, bn_eps, no_scale, no_bias, act, quant_kind, sign, with_zero, n, m, delta,
+             allow_tf32),
+        base_axis_(base_axis), with_bias_(with_bias), bn_eps_(bn_eps), no_scale_(no_scale), no_bias_(no_bias),
+        act_(act), allow_tf32_(allow_tf32), device_(std::stoi(ctx.device_id)) {
+    q_ = dwbnq_quant_desc();
+    q_.kind = quant_kind;
+    q_.sign = sign;
+    q_.with_zero = with_zero;
+    q_.n = n;
+    q_.m = m;
+    q_.delta = delta;
+  }
+  virtual ~FusedPwBnQuantCuda() {}
+  virtual shared_ptr<Function> copy() const {
+    return shared_ptr<Function>(new FusedPwBnQuantCuda<T>(this->ctx_, base_axis_, with_bias_, bn_eps_, no_scale_,
+                                                          no_bias_, act_, q_.kind, q_.sign != 0, q_.with_zero != 0,
+                                                          q_.n, q_.m, q_.delta, allow_tf32_));
+  }
+  virtual vector<dtypes> in_types() { return vector<dtypes>(n_inputs(), get_dtype<T>()); }
+  virtual vector<dtypes> out_types() { return vector<dtypes>{get_dtype<T>()}; }
+  virtual int min_inputs() { return n_inputs(); }
+  virtual int min_outputs() { return 1; }
+  virtual string name() { return "FusedPwBnQuantCuda"; }
+  virtual vector<string> allowed_array_classes() { return SingletonManager::get<Cuda>()->array_classes(); }
+
+protected:
+  int base_axis_;
+  bool with_bias_;
+  float bn_eps_;
+  bool no_scale_, no_bias_;
+  int act_;
+  bool allow_tf32_;
+  int device_;
+  dwbnq_quant_desc q_;
+  dwbnq_pwconv_desc desc_;
+  Variable workspace_;
+  int n_inputs() const { return 2 + (with_bias_ ? 1 : 0) + (no_bias_ ? 0 : 1) + (no_scale_ ? 0 : 1) + 2; }
+  virtual void setup_impl(const Variables &inputs, const Variables &outputs) {
+    NBLA_CHECK((int)inputs.size() == n_inputs(), error_code::value, "FusedPwBnQuantCuda expects %d inputs, got %d",
+               n_inputs(), (int)inputs.size());
+    const Shape_t xs = inputs[0]->shape(), ws = inputs[1]->shape();
+    NBLA_CHECK((int)xs.size() == base_axis_ + 3, error_code::value, "a 2-D convolution input [.., c_in, h, w] is expected");
+    NBLA_CHECK(ws.size() == 4 && ws[2] == 1 && ws[3] == 1 && ws[1] == xs[base_axis_], error_code::value,
+               "the weight must be [c_out, c_in, 1, 1] over the input's %d channels", (int)xs[base_axis_]);
+    desc_ = dwbnq_pwconv_desc();
+    desc_.dtype = DType<T>::value;
+    desc_.c_in = (int)ws[1];
+    desc_.c_out = (int)ws[0];
+    desc_.h = (int)xs[base_axis_ + 1];
+    desc_.w = (int)xs[base_axis_ + 2];
+    desc_.n = 1;
+    for (int i = 0; i < base_axis_; ++i) desc_.n *= xs[i];
+    desc_.math = allow_tf32_ ? DWBNQ_PW_MATH_TF32 : DWBNQ_PW_MATH_FP32;
+    desc_.act = act_;
+    const size_t bytes = dwbnq_pwconv_workspace_bytes(&desc_);
+    if (bytes == 0) check(DWBNQ_ERR_INVALID_ARG, "FusedPwBnQuantCuda::setup");
+    Shape_t ys(xs.begin(), xs.begin() + base_axis_);
+    ys.push_back(ws[0]);
+    ys.push_back(xs[base_axis_ + 1]);
+    ys.push_back(xs[base_axis_ + 2]);
+    outputs[0]->reshape(ys, true);
+    workspace_.reshape(Shape_t{(Size_t)(bytes / sizeof(float))}, true);
+  }
+  virtual void forward_impl(const Variables &inputs, const Variables &outputs) {
+    int i = 0;
+    const Tc *x = inputs[i++]->get_data_pointer<Tc>(this->ctx_);
+    const Tc *w = inputs[i++]->get_data_pointer<Tc>(this->ctx_);
+    const Tc *b = with_bias_ ? inputs[i++]->get_data_pointer<Tc>(this->ctx_) : nullptr;
+    const Tc *beta = no_bias_ ? nullptr : inputs[i++]->get_data_pointer<Tc>(this->ctx_);
+    const Tc *gamma = no_scale_ ? nullptr : inputs[i++]->get_data_pointer<Tc>(this->ctx_);
+    const Tc *rm = inputs[i++]->get_data_pointer<Tc>(this->ctx_);
+    const Tc *rv = inputs[i++]->get_data_pointer<Tc>(this->ctx_);
+    Tc *y = outputs[0]->cast_data_and_get_pointer<Tc>(this->ctx_, true);
+    float *ws = workspace_.cast_data_and_get_pointer<float>(this->ctx_, true);
+    check(dwbnq_pwconv_fused_fwd(&desc_, bn_eps_, &q_, x, w, b, beta, gamma, rm, rv, y, ws, device_, nullptr),
+          "FusedPwBnQuantCuda::forward");
+  }
+  DWBNQ_NO_BACKWARD("FusedPwBnQuantCuda")
+};
+
 }  // namespace dwbnq_nbla
 
 // Factory of the fused function object, for the graph converter that replaces a matched
@@ -467,6 +564,30 @@ extern "C" void *dwbnq_nbla_create_fused(int half, int device, int base_axis, in
   return static_cast<Function *>(new FusedDwBnQuantCuda<float>(
       ctx, base_axis, p, s, d, multiplier, with_bias != 0, bn_eps, no_scale != 0, no_bias != 0, quant_kind,
       sign != 0, with_zero != 0, n, m, delta, decay, x_min_max != 0, ema != 0, mm_eps));
+}
+
+// Factory of the pointwise function object (the converter that replaces a matched
+// Convolution 1x1 -> BatchNormalization -> [ReLU | ReLU6] -> quantizer chain calls it). act is a
+// dwbnq_act, quant_kind a dwbnq_quant_kind other than MINMAX; returns NULL on a bad argument.
+extern "C" void *dwbnq_nbla_create_fused_pw(int half, int device, int base_axis, int with_bias, float bn_eps,
+                                            int no_scale, int no_bias, int act, int quant_kind, int sign,
+                                            int with_zero, int n, int m, float delta, int allow_tf32) {
+  using namespace nbla;
+  using namespace dwbnq_nbla;
+  if (base_axis < 0 || device < 0 || act < DWBNQ_ACT_NONE || act > DWBNQ_ACT_RELU6 || quant_kind < DWBNQ_Q_NONE ||
+      quant_kind > DWBNQ_Q_POW2)
+    return nullptr;
+  Context ctx;
+  ctx.backend = {half ? "cuda:half" : "cuda:float"};
+  ctx.array_class = "CudaCachedArray";
+  ctx.device_id = std::to_string(device);
+  if (half)
+    return static_cast<Function *>(new FusedPwBnQuantCuda<Half>(ctx, base_axis, with_bias != 0, bn_eps, no_scale != 0,
+                                                                no_bias != 0, act, quant_kind, sign != 0,
+                                                                with_zero != 0, n, m, delta, allow_tf32 != 0));
+  return static_cast<Function *>(new FusedPwBnQuantCuda<float>(ctx, base_axis, with_bias != 0, bn_eps, no_scale != 0,
+                                                               no_bias != 0, act, quant_kind, sign != 0, with_zero != 0,
+                                                               n, m, delta, allow_tf32 != 0));
 }
 
 // Replaces the five registry entries for "cuda:float" and "cuda:half". Call once, after

@@ -1,5 +1,6 @@
-"""Graph pass: DepthwiseConvolution -> BatchNormalization(batch_stat=False) -> quantizer
-becomes one fused node, and a small executor that runs such graphs through libdwbnq.
+"""Graph passes: DepthwiseConvolution -> BatchNormalization(batch_stat=False) -> quantizer
+becomes one fused node, so does pointwise Convolution -> BatchNormalization -> [ReLU | ReLU6] ->
+quantizer (``fuse_pw_bn_quant``); and a small executor that runs such graphs through libdwbnq.
 
 nnabla's graph converters (``nnabla.experimental.graph_converters``, e.g.
 BatchNormalizationFolding) walk a function list and rewrite conv -> BN chains whose
@@ -18,6 +19,8 @@ from collections import Counter
 
 QUANTIZERS = ("FixedPointQuantize", "Pow2Quantize", "MinMaxQuantize")
 FUSED = "FusedDwBnQuant"
+FUSED_PW = "FusedPwBnQuant"
+ACTIVATIONS = {"ReLU": "relu", "ReLU6": "relu6"}
 
 
 def _consumers(nodes):
@@ -90,6 +93,71 @@ def fuse_dw_bn_quant(nodes, graph_outputs=(), shapes=None):
         out.append(fused)
     # keep topological order: a fused node sits where its convolution was; everything it
     # needs (parameters) is a graph input or was produced earlier
+    return out
+
+
+def _is_pointwise(conv, shapes):
+    """Convolution with a 1x1 kernel, pad 0, stride 1, dilation 1, group 1, NCHW: the weight's
+    shape (``shapes``) decides the kernel size; without it the node is left alone."""
+    a = conv["args"]
+    if a.get("group", 1) != 1 or a.get("channel_last", False) or not shapes or len(conv["inputs"]) < 2:
+        return False
+    w = shapes.get(conv["inputs"][1])
+    if w is None or len(w) != 4 or tuple(int(v) for v in w[2:]) != (1, 1):
+        return False
+    one = lambda v, d: all(int(e) == d for e in (v if v is not None else (d, d)))
+    return one(a.get("pad"), 0) and one(a.get("stride"), 1) and one(a.get("dilation"), 1)
+
+
+def fuse_pw_bn_quant(nodes, graph_outputs=(), shapes=None):
+    """Every pointwise Convolution -> BN(inference) -> [ReLU | ReLU6] -> FixedPointQuantize |
+    Pow2Quantize chain whose intermediates have no other consumer becomes one FusedPwBnQuant
+    node (activation and quantizer are optional; a MinMaxQuantize is never absorbed: it needs the
+    whole tensor's range first). Run it after or before ``fuse_dw_bn_quant``: the two passes
+    match disjoint operators."""
+    nodes = list(nodes)
+    uses = _consumers(nodes)
+    keep = set(graph_outputs)
+    consumer_of = {}
+    for i, n in enumerate(nodes):
+        for v in n["inputs"]:
+            consumer_of.setdefault(v, []).append(i)
+
+    def sole_consumer(var):
+        if var in keep or uses[var] != 1:
+            return None
+        return consumer_of[var][0]
+
+    removed, out = set(), []
+    for i, conv in enumerate(nodes):
+        if i in removed:
+            continue
+        if conv["op"] != "Convolution" or not _is_pointwise(conv, shapes):
+            out.append(conv)
+            continue
+        base_axis = conv["args"].get("base_axis", 1)
+        j = sole_consumer(conv["outputs"][0])
+        if j is None or nodes[j]["op"] != "BatchNormalization" or nodes[j]["inputs"][0] != conv["outputs"][0] \
+                or not _bn_is_fusable(nodes[j], base_axis):
+            out.append(conv)
+            continue
+        bn = nodes[j]
+        fused = {"op": FUSED_PW, "conv_args": dict(conv["args"]), "bn_args": dict(bn["args"]), "act": None, "quant": None,
+                 "inputs": list(conv["inputs"]) + list(bn["inputs"][1:]), "n_conv_inputs": len(conv["inputs"]),
+                 "outputs": list(bn["outputs"])}
+        removed.add(j)
+        k = sole_consumer(fused["outputs"][0])
+        if k is not None and nodes[k]["op"] in ACTIVATIONS and nodes[k]["inputs"][0] == fused["outputs"][0]:
+            fused["act"] = ACTIVATIONS[nodes[k]["op"]]
+            fused["outputs"] = list(nodes[k]["outputs"])
+            removed.add(k)
+            k = sole_consumer(fused["outputs"][0])
+        if k is not None and nodes[k]["op"] in ("FixedPointQuantize", "Pow2Quantize") \
+                and nodes[k]["inputs"][0] == fused["outputs"][0]:
+            fused["quant"] = {"op": nodes[k]["op"], "args": dict(nodes[k]["args"])}
+            fused["outputs"] = list(nodes[k]["outputs"])
+            removed.add(k)
+        out.append(fused)
     return out
 
 
@@ -166,6 +234,28 @@ def execute(nodes, tensors, comm=None, check=False):
             y = ops.fused_dw_bn_quant(i[0], i[1], b, beta, gamma, mean, var, ba.get("eps", 1e-5), ca.get("pad"),
                                       ca.get("stride"), ca.get("dilation"), ca.get("multiplier", 1), quant,
                                       ca.get("base_axis", 1), comm=comm)
+        elif n["op"] in ACTIVATIONS:
+            y = i[0].clamp(min=0.0) if n["op"] == "ReLU" else i[0].clamp(0.0, 6.0)
+        elif n["op"] == "Convolution":
+            b = i[2] if len(i) > 2 else None
+            y = ops.pointwise_convolution(i[0], i[1], b, a.get("base_axis", 1))
+        elif n["op"] == FUSED_PW:
+            nc = n["n_conv_inputs"]
+            ca, ba = n["conv_args"], n["bn_args"]
+            b = i[2] if nc > 2 else None
+            n_bn = 4 - int(ba.get("no_bias", False)) - int(ba.get("no_scale", False))
+            beta, gamma, mean, var = _bn_inputs(i[nc:nc + n_bn], ba)
+            quant = None
+            if n["quant"]:
+                qa = n["quant"]["args"]
+                if n["quant"]["op"] == "FixedPointQuantize":
+                    quant = {"kind": "fpq", "sign": qa.get("sign", True), "n": qa.get("n", 8),
+                             "delta": qa.get("delta", 2.0 ** -4)}
+                else:
+                    quant = {"kind": "pow2", "sign": qa.get("sign", True), "with_zero": qa.get("with_zero", True),
+                             "n": qa.get("n", 8), "m": qa.get("m", 1)}
+            y = ops.fused_pw_bn_quant(i[0], i[1], b, beta, gamma, mean, var, ba.get("eps", 1e-5), quant, n["act"],
+                                      ca.get("base_axis", 1))
         else:
             raise NotImplementedError("operator %r is outside the dwbnq path" % (n["op"],))
         t[n["outputs"][0]] = y

@@ -6,6 +6,9 @@
 #include <nbla/stub_core.hpp>
 
 extern "C" void dwbnq_register_nbla(void);
+extern "C" void *dwbnq_nbla_create_fused_pw(int half, int device, int base_axis, int with_bias, float bn_eps, int no_scale,
+                                            int no_bias, int act, int quant_kind, int sign, int with_zero, int n, int m,
+                                            float delta, int allow_tf32);
 extern "C" void *dwbnq_nbla_create_fused(int half, int device, int base_axis, int spatial_dims, const int *pad,
                                          const int *stride, const int *dilation, int multiplier, int with_bias,
                                          float bn_eps, int no_scale, int no_bias, int quant_kind, int sign,
@@ -169,6 +172,39 @@ int stub_fused(int half, int device, const int64_t *xs, const int64_t *ws, int n
     g->forward(in, out);
     const nbla::Shape_t ys = vy.shape();
     for (int i = 0; i < nd; ++i) out_shape[i] = i < (int)ys.size() ? ys[i] : -1;
+  });
+}
+// The pointwise function object: ptrs = {x, w, b, beta, gamma, mean, var}, null for an absent
+// optional input; ws is [c_out, c_in, 1, 1].
+int stub_fused_pw(int half, int device, const int64_t *xs, const int64_t *ws, void *const *ptrs, void *y, float bn_eps,
+                  int act, int quant_kind, int sign, int with_zero, int n, int m, float delta, int allow_tf32,
+                  int64_t *out_shape, int *n_inputs, int *copies_ok) {
+  return guarded([&] {
+    nbla::Function *raw = static_cast<nbla::Function *>(
+        dwbnq_nbla_create_fused_pw(half, device, 1, ptrs[2] != nullptr, bn_eps, ptrs[4] == nullptr, ptrs[3] == nullptr, act,
+                                   quant_kind, sign, with_zero, n, m, delta, allow_tf32));
+    if (!raw) throw std::runtime_error("factory returned null");
+    std::unique_ptr<nbla::Function> f(raw);
+    nbla::Shape_t ps(4, 1);
+    ps[1] = ws[0];
+    nbla::Variable vx(shp(xs, 4), ptrs[0]), vw(shp(ws, 4), ptrs[1]), vb(nbla::Shape_t{ws[0]}, ptrs[2]);
+    nbla::Variable vbeta(ps, ptrs[3]), vgamma(ps, ptrs[4]), vmean(ps, ptrs[5]), vvar(ps, ptrs[6]);
+    nbla::Variable vy(nbla::Shape_t{}, y);
+    nbla::Variables in{&vx, &vw};
+    if (ptrs[2]) in.push_back(&vb);
+    if (ptrs[3]) in.push_back(&vbeta);
+    if (ptrs[4]) in.push_back(&vgamma);
+    in.push_back(&vmean);
+    in.push_back(&vvar);
+    *n_inputs = f->min_inputs();
+    nbla::Variables out{&vy};
+    std::shared_ptr<nbla::Function> g = f->copy();
+    *copies_ok = g && g->name() == f->name() && g->min_inputs() == f->min_inputs() &&
+                 g->in_types().size() == (size_t)f->min_inputs() && g->out_types().size() == 1;
+    g->setup(in, out);
+    g->forward(in, out);
+    const nbla::Shape_t ys = vy.shape();
+    for (int i = 0; i < 4; ++i) out_shape[i] = i < (int)ys.size() ? ys[i] : -1;
   });
 }
 int stub_fused_backward_is_refused(int device) {

@@ -198,3 +198,92 @@ def test_graph_runner_replays_the_fused_layers(oracle, cuda_device):
                                   (spec.stride,) * 2, (spec.pad,) * 2, q, nthreads=oracle.max_threads())
         got = out["y"].cpu().numpy()
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), scale
+
+
+def _pw_chain(act="ReLU6", quant_op="FixedPointQuantize", quant_args=None, conv_args=None, extra_consumer=None):
+    nodes = [
+        {"op": "Convolution", "inputs": ["x", "w", "b"], "outputs": ["c"],
+         "args": dict({"base_axis": 1, "pad": (0, 0), "stride": (1, 1), "dilation": (1, 1), "group": 1,
+                       "channel_last": False}, **(conv_args or {}))},
+        {"op": "BatchNormalization", "inputs": ["c", "beta", "gamma", "mean", "var"], "outputs": ["n"],
+         "args": {"axes": [1], "decay_rate": 0.9, "eps": 1e-5, "batch_stat": False}},
+    ]
+    last = "n"
+    if act:
+        nodes.append({"op": act, "inputs": [last], "outputs": ["a"], "args": {}})
+        last = "a"
+    if quant_op:
+        nodes.append({"op": quant_op, "inputs": [last], "outputs": ["y"], "args": quant_args or {}})
+    if extra_consumer:
+        nodes.append({"op": "FixedPointQuantize", "inputs": [extra_consumer], "outputs": ["z"], "args": {}})
+    return nodes
+
+
+PW_SHAPES = {"x": (2, 8, 14, 14), "w": (16, 8, 1, 1)}
+
+
+def test_pointwise_chain_is_fused_into_one_node():
+    for act, qop in (("ReLU6", "FixedPointQuantize"), ("ReLU", "Pow2Quantize"), (None, "FixedPointQuantize"),
+                     ("ReLU6", None), (None, None)):
+        out_name = "y" if qop else ("a" if act else "n")
+        fused = graph.fuse_pw_bn_quant(_pw_chain(act, qop), [out_name], PW_SHAPES)
+        assert [n["op"] for n in fused] == [graph.FUSED_PW], (act, qop)
+        f = fused[0]
+        assert f["outputs"] == [out_name]
+        assert f["act"] == {"ReLU6": "relu6", "ReLU": "relu", None: None}[act]
+        assert (f["quant"] or {}).get("op") == qop
+        assert f["inputs"] == ["x", "w", "b", "beta", "gamma", "mean", "var"]
+
+
+def test_pointwise_patterns_that_must_not_fuse():
+    ops_of = lambda nodes: [n["op"] for n in nodes]
+    # a 3x3 kernel, a stride, padding, groups, channel-last, or no shape information: left alone
+    for shapes, args in ((dict(PW_SHAPES, w=(16, 8, 3, 3)), {}), (PW_SHAPES, {"stride": (2, 2)}), (PW_SHAPES, {"pad": (1, 1)}),
+                         (PW_SHAPES, {"group": 2}), (PW_SHAPES, {"channel_last": True}), (None, {})):
+        nodes = _pw_chain(conv_args=args)
+        assert ops_of(graph.fuse_pw_bn_quant(nodes, ["y"], shapes)) == ops_of(nodes)
+    # MinMaxQuantize stays a node of its own behind the fused convolution + BN + activation
+    nodes = _pw_chain("ReLU6", None) + [{"op": "MinMaxQuantize", "inputs": ["a", "q0", "q1", "q2", "q3"], "outputs": ["y"],
+                                         "args": {}}]
+    assert ops_of(graph.fuse_pw_bn_quant(nodes, ["y"], PW_SHAPES)) == [graph.FUSED_PW, "MinMaxQuantize"]
+    # an intermediate with a second consumer (or that is a graph output) ends the fused chain there
+    assert ops_of(graph.fuse_pw_bn_quant(_pw_chain(extra_consumer="a"), ["y", "z"], PW_SHAPES)) == \
+        [graph.FUSED_PW, "FixedPointQuantize", "FixedPointQuantize"]
+    assert ops_of(graph.fuse_pw_bn_quant(_pw_chain(extra_consumer="c"), ["y", "z"], PW_SHAPES)) == ops_of(
+        _pw_chain(extra_consumer="c"))
+    fused = graph.fuse_pw_bn_quant(_pw_chain(), ["y", "n"], PW_SHAPES)
+    assert ops_of(fused) == [graph.FUSED_PW, "ReLU6", "FixedPointQuantize"] and fused[0]["act"] is None
+    # batch statistics: not the inference form
+    nodes = _pw_chain()
+    nodes[1]["args"]["batch_stat"] = True
+    assert ops_of(graph.fuse_pw_bn_quant(nodes, ["y"], PW_SHAPES)) == ops_of(nodes)
+    # the two passes compose: an inverted residual's expansion, depthwise layer and projection
+    block = _pw_chain()
+    for n in block:
+        n["inputs"] = [("e_" + v) if v != "x" else v for v in n["inputs"]]
+        n["outputs"] = ["e_" + v for v in n["outputs"]]
+    block += [dict(n, inputs=[("d_" + v) if v != "x" else "e_y" for v in n["inputs"]], outputs=["d_" + v for v in n["outputs"]])
+              for n in _chain("FixedPointQuantize")]
+    shapes = {"x": (2, 8, 14, 14), "e_w": (16, 8, 1, 1), "d_w": (16, 3, 3)}
+    both = graph.fuse_dw_bn_quant(graph.fuse_pw_bn_quant(block, ["d_y"], shapes), ["d_y"], shapes)
+    assert ops_of(both) == [graph.FUSED_PW, graph.FUSED]
+
+
+@pytest.mark.gpu
+def test_fused_pointwise_graph_equals_unfused_graph(oracle, cuda_device):
+    import torch
+    from dwbnq import workloads
+    for spec in (workloads.pw1(3)[7], workloads.pw1(2)[26]):  # an expansion on 28x28, a projection on 7x7
+        d = workloads.make_pointwise_data(spec)
+        qop_args = {"sign": spec.quant["sign"], "n": 8, "delta": spec.quant["delta"]}
+        nodes = _pw_chain("ReLU6" if spec.act else None, "FixedPointQuantize", qop_args)
+        names = ["x", "w", "b", "beta", "gamma", "mean", "var"]
+        fresh = lambda: {k: torch.from_numpy(d[k].copy()).to(cuda_device) for k in names}
+        t_unfused = graph.execute(nodes, fresh(), check=True)
+        fused = graph.fuse_pw_bn_quant(nodes, ["y"], {k: tuple(d[k].shape) for k in names})
+        assert [n["op"] for n in fused] == [graph.FUSED_PW]
+        t_fused = graph.execute(fused, fresh(), check=True)
+        assert torch.equal(t_unfused["y"].view(torch.int32), t_fused["y"].view(torch.int32)), spec.name
+        want = oracle.pw_epilogue(t_unfused["c"].cpu().numpy(), d["beta"], d["gamma"], d["mean"], d["var"], 1e-5, spec.act,
+                                  spec.quant)
+        assert np.array_equal(t_fused["y"].cpu().numpy().view(np.uint32), want.view(np.uint32)), spec.name

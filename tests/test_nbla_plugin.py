@@ -3,7 +3,8 @@ for nnabla core's C++ interface (tests/nbla_stub: nnabla itself cannot be instal
 driven end to end: registration under the reference's (function, backend) keys, class names,
 the forward of each of the five functions on device buffers against the CPU oracle, the fused
 function object a graph converter substitutes for a dw-conv -> BN -> quantizer chain (through
-its extern "C" factory, float and half, every quantizer), and the refusal of backward. What this cannot show - link compatibility with a real libnnabla - stays
+its extern "C" factory, float and half, every quantizer), the function object for the pointwise
+convolution -> BN -> activation -> quantizer chain, and the refusal of backward. What this cannot show - link compatibility with a real libnnabla - stays
 open until the plugin is built in an nnabla tree."""
 import ctypes
 import os
@@ -142,6 +143,80 @@ def test_forward_of_the_five_functions(harness, oracle, cuda_device, half):
     if not half:
         np.testing.assert_array_equal(qr_min.cpu().numpy(), wmin)
         np.testing.assert_array_equal(qr_max.cpu().numpy(), wmax)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("half", [0, 1], ids=["float", "half"])
+def test_fused_pointwise_function_object(harness, oracle, cuda_device, half):
+    """FusedPwBnQuantCuda through dwbnq_nbla_create_fused_pw: Convolution 1x1 -> BN -> activation ->
+    quantizer as one function object; output shape from setup, a copy() run instead of the
+    original. The result is bracketed by the oracle's epilogue of (double sum -/+ tolerance); for
+    float it is also bit-identical to the oracle's epilogue of the library's own convolution."""
+    import torch
+    from dwbnq import ops
+    rng = np.random.default_rng(17)
+    dt = torch.float16 if half else torch.float32
+    n, ci, co, hw = 3, 24, 40, 14
+    dev_index = cuda_device.index or 0
+
+    def rnd16(a):
+        return a.astype(np.float16).astype(np.float32) if half else a
+
+    x = rnd16(np.clip(rng.standard_normal((n, ci, hw, hw)) * 2, -1, 6).astype(np.float32))
+    w = rnd16((rng.standard_normal((co, ci, 1, 1)) / np.sqrt(ci)).astype(np.float32))
+    vec = {k: rnd16((rng.random(co) + 0.5).astype(np.float32)) for k in ("b", "beta", "gamma", "mean", "var")}
+    to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(cuda_device).to(dt)
+    tx, tw = to(x), to(w)
+    tv = {k: to(v) for k, v in vec.items()}
+    scratch = torch.empty(1 << 20, device=cuda_device, dtype=torch.uint8)
+    harness.stub_set_scratch(_p(scratch))
+    _, acc64, mag = oracle.pwconv(x, w, vec["b"])
+    tol = (ci + 4) * 2.0 ** -24 if half else 4e-6
+    cases = [  # (act name, act code, quant dict, kind, allow_tf32, with b/beta/gamma)
+        ("relu6", 2, {"kind": "fpq", "sign": False, "n": 8, "delta": 2.0 ** -3}, 1, 0, (True, True, True)),
+        (None, 0, {"kind": "fpq", "sign": True, "n": 8, "delta": 2.0 ** -4}, 1, 0, (True, True, True)),
+        ("relu", 1, {"kind": "pow2", "sign": True, "with_zero": True, "n": 8, "m": 1}, 2, 0, (True, False, True)),
+        ("relu6", 2, None, 0, 1, (True, True, False)),
+    ]
+    for act, act_code, q, kind, tf32, (use_b, use_beta, use_gamma) in cases:
+        y = torch.full((n, co, hw, hw), float("nan"), device=cuda_device, dtype=dt)
+        ptrs = [tx, tw, tv["b"] if use_b else None, tv["beta"] if use_beta else None, tv["gamma"] if use_gamma else None,
+                tv["mean"], tv["var"]]
+        arr = (ctypes.c_void_p * 7)(*[_p(t) for t in ptrs])
+        out_shape = (ctypes.c_int64 * 4)()
+        n_inputs, copies_ok = ctypes.c_int(), ctypes.c_int()
+        qa = q or {}
+        rc = harness.stub_fused_pw(half, dev_index, _shape(tx), _shape(tw), arr, _p(y), ctypes.c_float(1e-5), act_code, kind,
+                                   int(qa.get("sign", 0)), int(qa.get("with_zero", 0)), int(qa.get("n", 8)),
+                                   int(qa.get("m", 0)), ctypes.c_float(qa.get("delta", 0.0)), tf32, out_shape,
+                                   ctypes.byref(n_inputs), ctypes.byref(copies_ok))
+        assert rc == 0, harness.stub_last_error()
+        torch.cuda.synchronize()
+        assert list(out_shape) == [n, co, hw, hw]
+        assert n_inputs.value == 4 + use_b + use_beta + use_gamma
+        assert copies_ok.value == 1
+        beta = vec["beta"] if use_beta else None
+        gamma = vec["gamma"] if use_gamma else None
+        t = (2.0 ** -9 if tf32 else tol)
+        lo = oracle.pw_epilogue(acc64 - (t * mag).astype(np.float32), beta, gamma, vec["mean"], vec["var"], 1e-5, act, q)
+        hi = oracle.pw_epilogue(acc64 + (t * mag).astype(np.float32), beta, gamma, vec["mean"], vec["var"], 1e-5, act, q)
+        lo, hi = np.minimum(lo, hi), np.maximum(lo, hi)
+        got = y.float().cpu().numpy()
+        if half:
+            lo, hi = lo.astype(np.float16).astype(np.float32), hi.astype(np.float16).astype(np.float32)
+        assert np.all((got >= lo) & (got <= hi)), (act, kind, half)
+        if not half:
+            conv = ops.pointwise_convolution(tx, tw, tv["b"], math="tf32" if tf32 else "fp32").cpu().numpy()
+            want = oracle.pw_epilogue(conv, beta, gamma, vec["mean"], vec["var"], 1e-5, act, q)
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (act, kind)
+
+
+def test_fused_pointwise_factory_rejects_bad_arguments(harness):
+    f = harness.dwbnq_nbla_create_fused_pw
+    f.restype = ctypes.c_void_p
+    assert f(0, 0, 1, 1, ctypes.c_float(1e-5), 0, 0, 3, 1, 0, 0, 8, 0, ctypes.c_float(0.125), 0) is None   # act
+    assert f(0, 0, 1, 1, ctypes.c_float(1e-5), 0, 0, 0, 3, 0, 0, 8, 0, ctypes.c_float(0.125), 0) is None   # MinMax
+    assert f(0, -1, 1, 1, ctypes.c_float(1e-5), 0, 0, 0, 1, 0, 0, 8, 0, ctypes.c_float(0.125), 0) is None  # device
 
 
 @pytest.mark.gpu
