@@ -349,7 +349,7 @@ def run_pointwise(args):
                                    "each fused with BN, activation and FixedPointQuantize" % n,
                        "l2": "L2 flushed before every timed launch"},
             "roofline": {"bound": "hbm", "achieved": tot["gbs"], "peak": peak, "unit": "GB/s", "frac": tot["frac"],
-                         "traffic": None, "peak_kind": peak_kind}, "gpu_launches": 2 * sum(1 for r in rows if r["workload"].startswith("pw1.l")), "layers": rows}
+                         "traffic": None, "peak_kind": peak_kind}, "gpu_launches": sum(1 for r in rows if r["workload"].startswith("pw1.l")), "layers": rows}
     print(json.dumps(line), flush=True)
 
 
@@ -385,7 +385,8 @@ FAMILY = {0: "fused_generic_kernel", 1: "fused_tiled_kernel (cooperative fill)",
 def pointwise_rows(torch, ops, workloads, device, batch, peak):
     """The 33 pointwise convolutions around cfg1's depthwise layers (workload pw1), each fused with
     BN, its activation and its FixedPointQuantize, one layer at a time with its own seeded input
-    resident in HBM. Every launch is replayed from a CUDA graph with L2 flushed before it (the
+    resident in HBM; the layer's parameters are prepared once (dwbnq_pwconv_prepare) and a timed
+    step is the one kernel of dwbnq_pwconv_fused_fwd_prepared. Every launch is replayed from a CUDA graph with L2 flushed before it (the
     deeper layers move less than L2 holds); median of 10. Per-layer rows for the fp32-accurate
     three-pass TF32 mode, and a summary row for it and for the single-pass TF32 mode."""
     rows, totals = [], {"fp32": [0.0, 0, 0.0], "tf32": [0.0, 0, 0.0]}
@@ -418,9 +419,12 @@ def pointwise_rows(torch, ops, workloads, device, batch, peak):
             if math == "tf32" and path == 0:
                 ms = rows[-1]["ms"]  # the FMA kernel has one mode
             else:
+                # inference: the parameters are prepared once (dwbnq_pwconv_prepare), a step is one launch
+                ops.pwconv_prepare(t["x"], t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], spec.bn_eps,
+                                   act=spec.act, math=math, ws=ws)
+
                 def call():
-                    ops.fused_pw_bn_quant(t["x"], t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], spec.bn_eps,
-                                          spec.quant, spec.act, math=math, ws=ws, out=y)
+                    ops.fused_pw_bn_quant_prepared(t["x"], t["w"], ws, True, spec.quant, spec.act, math=math, out=y)
                 call()
                 g = torch.cuda.CUDAGraph()
                 cap = torch.cuda.Stream(device)

@@ -356,9 +356,24 @@ int dwbnq_pwconv_fused_fwd(const dwbnq_pwconv_desc *desc, float bn_eps, const dw
                            const void *bn_gamma, const void *bn_mean, const void *bn_var,
                            void *y, void *workspace, int device, void *stream);
 
-/* Which kernel the pointwise entry points would use: 1 = the tcgen05 kernel (fp32 tensors,
- * h*w and c_in multiples of 4, 16-byte aligned x and w: what the TMA loads need), 0 = the
- * plain FMA kernel (fp16 tensors and every other shape). Diagnostic only. */
+/* The two halves of dwbnq_pwconv_fused_fwd for a caller whose parameters do not change between
+ * calls (inference): dwbnq_pwconv_prepare writes the workspace - the per-channel coefficients
+ * (bias, mean, gamma, sqrt(var + eps), beta) and the fp32 weights or their TF32 halves - once,
+ * the way the reference's function objects do their one-time work in setup_impl;
+ * dwbnq_pwconv_fused_fwd_prepared then runs the layer on that workspace with one kernel launch
+ * and reads neither w nor the vectors. `desc` must be the same in both calls; has_bn states
+ * whether dwbnq_pwconv_prepare was given bn_mean / bn_var. Results are identical to
+ * dwbnq_pwconv_fused_fwd, which is these two calls in sequence. */
+int dwbnq_pwconv_prepare(const dwbnq_pwconv_desc *desc, float bn_eps, const void *w, const void *b,
+                         const void *bn_beta, const void *bn_gamma, const void *bn_mean,
+                         const void *bn_var, void *workspace, int device, void *stream);
+int dwbnq_pwconv_fused_fwd_prepared(const dwbnq_pwconv_desc *desc, const dwbnq_quant_desc *q, int has_bn,
+                                    const void *x, void *y, void *workspace, int device, void *stream);
+
+/* Which kernel the pointwise entry points would use: 1 = the tcgen05 kernel (fp32 tensors, c_in
+ * a multiple of 4; planes whose size is not a multiple of 4, or an x that is not 16-byte
+ * aligned, are gathered with plain loads instead of TMA), 0 = the plain FMA kernel (fp16
+ * tensors, other c_in). Diagnostic only. */
 int dwbnq_pwconv_plan(const dwbnq_pwconv_desc *desc, const void *x, const void *w, int *path_out);
 
 /* ---- communicator: the one exchange the path needs (per-channel min/max) ----------- */

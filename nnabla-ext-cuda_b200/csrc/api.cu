@@ -255,6 +255,31 @@ int dwbnq_pwconv_fwd(const dwbnq_pwconv_desc *desc, const void *x, const void *w
                        static_cast<cudaStream_t>(stream));
 }
 
+int dwbnq_pwconv_prepare(const dwbnq_pwconv_desc *desc, float bn_eps, const void *w, const void *b, const void *bn_beta,
+                         const void *bn_gamma, const void *bn_mean, const void *bn_var, void *workspace, int device,
+                         void *stream) {
+  clear_error();
+  NvtxRange nvtx_range("dwbnq_pwconv_prepare");
+  int st = pwconv_validate(desc);
+  if (st != DWBNQ_OK) return st;
+  int dev;
+  st = enter_device(device, &dev);
+  if (st != DWBNQ_OK) return st;
+  return pwconv_prepare(*desc, bn_eps, w, b, bn_beta, bn_gamma, bn_mean, bn_var, workspace, static_cast<cudaStream_t>(stream));
+}
+
+int dwbnq_pwconv_fused_fwd_prepared(const dwbnq_pwconv_desc *desc, const dwbnq_quant_desc *q, int has_bn, const void *x,
+                                    void *y, void *workspace, int device, void *stream) {
+  clear_error();
+  NvtxRange nvtx_range("dwbnq_pwconv_fused_fwd_prepared");
+  int st = pwconv_validate(desc);
+  if (st != DWBNQ_OK) return st;
+  int dev;
+  st = enter_device(device, &dev);
+  if (st != DWBNQ_OK) return st;
+  return pwconv_run(*desc, q, has_bn, x, y, workspace, dev, static_cast<cudaStream_t>(stream));
+}
+
 int dwbnq_pwconv_plan(const dwbnq_pwconv_desc *desc, const void *x, const void *w, int *path_out) {
   clear_error();
   int st = pwconv_validate(desc);

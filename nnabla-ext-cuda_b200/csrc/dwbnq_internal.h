@@ -138,6 +138,11 @@ size_t pwconv_workspace_bytes(const dwbnq_pwconv_desc &d);
 int pwconv_path(const dwbnq_pwconv_desc &d, const void *x, const void *w);
 void set_forced_pw_path(int p);
 void set_pw_max_ctas(int n);
+// The two halves of launch_pwconv: fill the workspace from the parameters; run on a filled one.
+int pwconv_prepare(const dwbnq_pwconv_desc &d, float bn_eps, const void *w, const void *b, const void *beta,
+                   const void *gamma, const void *mean, const void *var, void *workspace, cudaStream_t stream);
+int pwconv_run(const dwbnq_pwconv_desc &d, const dwbnq_quant_desc *q, int has_bn, const void *x, void *y,
+               void *workspace, int dev, cudaStream_t stream);
 // Prepares the per-channel coefficients (and the TF32 halves of w) in `workspace`, then runs
 // the convolution with the fused epilogue. BN is skipped when mean is null; q may be null.
 int launch_pwconv(const dwbnq_pwconv_desc &d, float bn_eps, const dwbnq_quant_desc *q, const void *x, const void *w,

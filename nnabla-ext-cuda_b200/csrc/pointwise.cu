@@ -360,12 +360,16 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
       unsigned long long so = 0;  // s * stage_step
       bool ok = true;
       for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
-        ok = pw_wait_lane(&acc_empty[b], aph ^ 1u);
-        tc_fence_after();
         const unsigned int d = tmem_base + b * a.npad;
         for (int kc = 0; ok && kc < a.kchunks; ++kc) {
-          ok = pw_wait_lane(&full[s], ph);
-          if (ok && (MATH3 || GATHER)) ok = pw_wait_lane(&split[s], ph);
+          // the polls of a chunk's barriers are issued together (each is a shared-memory round trip
+          // of ~150 cycles for this one thread); a poll that fails goes to the bounded wait
+          const bool r0 = kc ? true : pw_try_wait(&acc_empty[b], aph ^ 1u);
+          const bool r1 = pw_try_wait(&full[s], ph);
+          const bool r2 = (MATH3 || GATHER) ? pw_try_wait(&split[s], ph) : true;
+          if (!r0) ok = pw_wait_lane(&acc_empty[b], aph ^ 1u);
+          if (ok && !r1) ok = pw_wait_lane(&full[s], ph);
+          if (ok && !r2) ok = pw_wait_lane(&split[s], ph);
           if (!ok) break;
           tc_fence_after();
           const int ksteps = kc == a.kchunks - 1 ? last_steps : kPwKChunk / 8;
@@ -617,11 +621,15 @@ __global__ void pw_prepare_kernel(const T *w, const T *b, const T *beta, const T
     coef[3 * cpad + i] = (in && var) ? bn_stdvar(Elem<T>::to_f32(var[i]), eps) : 1.0f;
     coef[4 * cpad + i] = (in && beta) ? Elem<T>::to_f32(beta[i]) : 0.0f;
   }
-  if (w_hi && i < wsize) {
+  if (i < wsize) {
     const float v = Elem<T>::to_f32(w[i]);
-    const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
-    w_hi[i] = h;
-    w_lo[i] = __fsub_rn(v, h);
+    if (w_lo) {  // the two TF32 halves
+      const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+      w_hi[i] = h;
+      w_lo[i] = __fsub_rn(v, h);
+    } else {  // the fp32 value itself
+      w_hi[i] = v;
+    }
   }
 }
 
@@ -629,7 +637,8 @@ __global__ void pw_prepare_kernel(const T *w, const T *b, const T *beta, const T
 // 64 output channels x 64 positions per CTA, 4 x 4 outputs per thread, c_in in chunks of 16.
 
 struct PwSimtArgs {
-  const void *x, *w;
+  const void *x;
+  const float *w;  // fp32 copy in the workspace
   void *y;
   const float *coef;
   int HW, Ci, Co, cpad, pos_tiles;
@@ -641,7 +650,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) pw_simt_kernel(const PwSimtArgs a) {
   __shared__ float ws[16][64 + 4], xs[16][64 + 4];
   const T *x = static_cast<const T *>(a.x);
-  const T *w = static_cast<const T *>(a.w);
+  const float *w = a.w;
   T *y = static_cast<T *>(a.y);
   const long long n = blockIdx.x / a.pos_tiles;
   const int p0 = (int)(blockIdx.x - n * a.pos_tiles) * 64, c0 = blockIdx.y * 64;
@@ -657,7 +666,7 @@ __global__ void __launch_bounds__(256) pw_simt_kernel(const PwSimtArgs a) {
       const int k = e >> 6, j = e & 63;  // xs: positions contiguous in memory
       xs[k][j] = (k0 + k < a.Ci && p0 + j < a.HW) ? Elem<T>::to_f32(xn[(size_t)(k0 + k) * a.HW + p0 + j]) : 0.0f;
       const int kk = e & 15, c = e >> 4;  // ws: c_in contiguous in memory
-      ws[kk][c] = (k0 + kk < a.Ci && c0 + c < a.Co) ? Elem<T>::to_f32(w[(size_t)(c0 + c) * a.Ci + k0 + kk]) : 0.0f;
+      ws[kk][c] = (k0 + kk < a.Ci && c0 + c < a.Co) ? w[(size_t)(c0 + c) * a.Ci + k0 + kk] : 0.0f;
     }
     __syncthreads();
 #pragma unroll
@@ -768,8 +777,7 @@ bool pw_tma_x(const dwbnq_pwconv_desc &d, const void *x) {
 bool pw_tc_eligible(const dwbnq_pwconv_desc &d, const void *x, const void *w) {
   const long long hw = (long long)d.h * d.w;
   return d.dtype == DWBNQ_F32 && d.c_in % 4 == 0 && d.c_out <= kPwMaxCout && (long long)d.c_out * hw <= 0x7fffffffLL &&
-         d.n * hw <= (1LL << 40) &&
-         (d.math == DWBNQ_PW_MATH_FP32 || ((uintptr_t)w & 15) == 0);
+         d.n * hw <= (1LL << 40);
 }
 
 template <bool GATHER, bool MATH3>
@@ -795,20 +803,76 @@ cudaError_t launch_pw_tc(int epi, dim3 grid, size_t smem, cudaStream_t stream, c
   return cudaGetLastError();
 }
 
+// Which kernel and which arithmetic a descriptor gets: the same answer at preparation and at
+// every forward call (the forced choice of include/dwbnq_debug.h must not change in between).
+struct PwMode {
+  bool tc, math3;
+};
+PwMode pw_mode(const dwbnq_pwconv_desc &d, const void *x, int *status) {
+  const int forced = forced_pw_path();
+  const bool eligible = pw_tc_eligible(d, x, nullptr);
+  *status = DWBNQ_OK;
+  if (forced == 1 && !eligible) *status = fail(DWBNQ_ERR_UNSUPPORTED, "the tcgen05 kernel cannot take this shape / alignment");
+  PwMode m;
+  m.tc = forced == 0 ? false : eligible;
+  m.math3 = m.tc && d.math == DWBNQ_PW_MATH_FP32;
+  return m;
+}
+
+struct PwWorkspace {
+  float *coef, *w_a, *w_b;  // coefficients; fp32 weights (or their TF32 high halves); the low halves
+};
+PwWorkspace pw_workspace(const dwbnq_pwconv_desc &d, void *workspace) {
+  const PwGeom g = pw_geom(d.c_out, d.c_in);
+  PwWorkspace w;
+  w.coef = static_cast<float *>(workspace);
+  w.w_a = reinterpret_cast<float *>(static_cast<char *>(workspace) + align256((size_t)5 * g.cpad * 4));
+  w.w_b = reinterpret_cast<float *>(reinterpret_cast<char *>(w.w_a) + align256((size_t)d.c_in * d.c_out * 4));
+  return w;
+}
+
 }  // namespace
 
-int launch_pwconv(const dwbnq_pwconv_desc &d, float bn_eps, const dwbnq_quant_desc *q, const void *x, const void *w,
-                  const void *b, const void *beta, const void *gamma, const void *mean, const void *var, void *y,
-                  void *workspace, int dev, cudaStream_t stream) {
+int pwconv_prepare(const dwbnq_pwconv_desc &d, float bn_eps, const void *w, const void *b, const void *beta,
+                   const void *gamma, const void *mean, const void *var, void *workspace, cudaStream_t stream) {
+  if (mean && !var) return fail(DWBNQ_ERR_INVALID_ARG, "bn_var is null although bn_mean is given");
+  if (!w || !workspace) return fail(DWBNQ_ERR_INVALID_ARG, "w and workspace must not be null");
+  if ((uintptr_t)workspace & 255) return fail(DWBNQ_ERR_INVALID_ARG, "workspace must be 256-byte aligned");
+  const int elem = d.dtype == DWBNQ_F32 ? 4 : 2;
+  if ((uintptr_t)w & (elem - 1)) return fail(DWBNQ_ERR_INVALID_ARG, "w must be element-aligned");
+  int st;
+  const PwMode m = pw_mode(d, reinterpret_cast<const void *>(16), &st);  // the arithmetic does not depend on x
+  if (st != DWBNQ_OK) return st;
+  const PwGeom g = pw_geom(d.c_out, d.c_in);
+  const PwWorkspace ws = pw_workspace(d, workspace);
+  const long long wsize = (long long)d.c_in * d.c_out;
+  const long long work = wsize > g.cpad ? wsize : g.cpad;
+  const unsigned blocks = (unsigned)((work + 255) / 256);
+  if (d.dtype == DWBNQ_F32)
+    pw_prepare_kernel<float><<<blocks, 256, 0, stream>>>(
+        static_cast<const float *>(w), static_cast<const float *>(b), static_cast<const float *>(beta),
+        static_cast<const float *>(gamma), static_cast<const float *>(mean), static_cast<const float *>(var), bn_eps,
+        d.c_out, g.cpad, wsize, ws.coef, ws.w_a, m.math3 ? ws.w_b : nullptr);
+  else
+    pw_prepare_kernel<__half><<<blocks, 256, 0, stream>>>(
+        static_cast<const __half *>(w), static_cast<const __half *>(b), static_cast<const __half *>(beta),
+        static_cast<const __half *>(gamma), static_cast<const __half *>(mean), static_cast<const __half *>(var), bn_eps,
+        d.c_out, g.cpad, wsize, ws.coef, ws.w_a, nullptr);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail_cuda(e, "pw_prepare_kernel launch");
+  return DWBNQ_OK;
+}
+
+int pwconv_run(const dwbnq_pwconv_desc &d, const dwbnq_quant_desc *q, int has_bn, const void *x, void *y,
+               void *workspace, int dev, cudaStream_t stream) {
   const int kind = q ? q->kind : DWBNQ_Q_NONE;
   if (kind != DWBNQ_Q_NONE && kind != DWBNQ_Q_FPQ && kind != DWBNQ_Q_POW2)
     return fail(DWBNQ_ERR_UNSUPPORTED, "pointwise convolution fuses FixedPointQuantize or Pow2Quantize only (kind %d)", kind);
-  if (mean && !var) return fail(DWBNQ_ERR_INVALID_ARG, "bn_var is null although bn_mean is given");
   if (d.n == 0) return DWBNQ_OK;
-  if (!x || !w || !y || !workspace) return fail(DWBNQ_ERR_INVALID_ARG, "x, w, y and workspace must not be null");
+  if (!x || !y || !workspace) return fail(DWBNQ_ERR_INVALID_ARG, "x, y and workspace must not be null");
   if ((uintptr_t)workspace & 255) return fail(DWBNQ_ERR_INVALID_ARG, "workspace must be 256-byte aligned");
   const int elem = d.dtype == DWBNQ_F32 ? 4 : 2;
-  if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)y) & (elem - 1)) return fail(DWBNQ_ERR_INVALID_ARG, "tensor pointers must be element-aligned");
+  if (((uintptr_t)x | (uintptr_t)y) & (elem - 1)) return fail(DWBNQ_ERR_INVALID_ARG, "tensor pointers must be element-aligned");
 
   QuantArgs qa;
   std::memset(&qa, 0, sizeof(qa));
@@ -819,38 +883,17 @@ int launch_pwconv(const dwbnq_pwconv_desc &d, float bn_eps, const dwbnq_quant_de
 
   const PwGeom g = pw_geom(d.c_out, d.c_in);
   const int HW = d.h * d.w;
-  const long long wsize = (long long)d.c_in * d.c_out;
-  float *coef = static_cast<float *>(workspace);
-  float *w_hi = reinterpret_cast<float *>(static_cast<char *>(workspace) + align256((size_t)5 * g.cpad * 4));
-  float *w_lo = reinterpret_cast<float *>(reinterpret_cast<char *>(w_hi) + align256((size_t)wsize * 4));
-
-  const int forced = forced_pw_path();
-  const bool eligible = pw_tc_eligible(d, x, w);
-  if (forced == 1 && !eligible) return fail(DWBNQ_ERR_UNSUPPORTED, "the tcgen05 kernel cannot take this shape / alignment");
-  const bool tc = forced == 0 ? false : eligible;
-  const bool math3 = tc && d.math == DWBNQ_PW_MATH_FP32;
-
-  {
-    const long long work = math3 ? (wsize > g.cpad ? wsize : g.cpad) : g.cpad;
-    const unsigned blocks = (unsigned)((work + 255) / 256);
-    if (d.dtype == DWBNQ_F32)
-      pw_prepare_kernel<float><<<blocks, 256, 0, stream>>>(
-          static_cast<const float *>(w), static_cast<const float *>(b), static_cast<const float *>(beta),
-          static_cast<const float *>(gamma), static_cast<const float *>(mean), static_cast<const float *>(var), bn_eps,
-          d.c_out, g.cpad, wsize, coef, math3 ? w_hi : nullptr, w_lo);
-    else
-      pw_prepare_kernel<__half><<<blocks, 256, 0, stream>>>(
-          static_cast<const __half *>(w), static_cast<const __half *>(b), static_cast<const __half *>(beta),
-          static_cast<const __half *>(gamma), static_cast<const __half *>(mean), static_cast<const __half *>(var), bn_eps,
-          d.c_out, g.cpad, wsize, coef, nullptr, nullptr);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return fail_cuda(e, "pw_prepare_kernel launch");
-  }
+  const PwWorkspace wsp = pw_workspace(d, workspace);
+  float *coef = wsp.coef, *w_hi = wsp.w_a, *w_lo = wsp.w_b;
+  const PwMode mode = pw_mode(d, x, &st);
+  if (st != DWBNQ_OK) return st;
+  const bool tc = mode.tc, math3 = mode.math3;
+  const void *mean = has_bn ? coef : nullptr;  // only its presence matters below
 
   if (!tc) {
     PwSimtArgs a;
     std::memset(&a, 0, sizeof(a));
-    a.x = x; a.w = w; a.y = y; a.coef = coef;
+    a.x = x; a.w = w_hi; a.y = y; a.coef = coef;
     a.HW = HW; a.Ci = d.c_in; a.Co = d.c_out; a.cpad = g.cpad;
     a.pos_tiles = (HW + 63) / 64;
     a.has_bn = mean != nullptr; a.act = d.act; a.qkind = kind; a.q = qa;
@@ -919,7 +962,7 @@ int launch_pwconv(const dwbnq_pwconv_desc &d, float bn_eps, const dwbnq_quant_de
     if (r != CUDA_SUCCESS) return fail(DWBNQ_ERR_CUDA, "cuTensorMapEncodeTiled(x) failed with CUresult %d", (int)r);
   }
   for (int k = 0; k < 2; ++k) {
-    const void *src = math3 ? (k ? w_lo : w_hi) : w;
+    const void *src = (k && math3) ? w_lo : w_hi;
     const cuuint64_t gdim[2] = {(cuuint64_t)d.c_in, (cuuint64_t)d.c_out};
     const cuuint64_t gstr[1] = {(cuuint64_t)d.c_in * 4};
     const cuuint32_t box[2] = {(cuuint32_t)kPwKChunk, (cuuint32_t)g.npad}, es[2] = {1, 1};
@@ -949,6 +992,15 @@ int launch_pwconv(const dwbnq_pwconv_desc &d, float bn_eps, const dwbnq_quant_de
   return DWBNQ_OK;
 }
 
+int launch_pwconv(const dwbnq_pwconv_desc &d, float bn_eps, const dwbnq_quant_desc *q, const void *x, const void *w,
+                  const void *b, const void *beta, const void *gamma, const void *mean, const void *var, void *y,
+                  void *workspace, int dev, cudaStream_t stream) {
+  if (d.n == 0) return DWBNQ_OK;
+  const int st = pwconv_prepare(d, bn_eps, w, b, beta, gamma, mean, var, workspace, stream);
+  if (st != DWBNQ_OK) return st;
+  return pwconv_run(d, q, mean != nullptr, x, y, workspace, dev, stream);
+}
+
 size_t pwconv_workspace_bytes(const dwbnq_pwconv_desc &d) {
   const PwGeom g = pw_geom(d.c_out, d.c_in);
   return align256((size_t)5 * g.cpad * 4) + 2 * align256((size_t)d.c_in * d.c_out * 4);
@@ -956,7 +1008,8 @@ size_t pwconv_workspace_bytes(const dwbnq_pwconv_desc &d) {
 int pwconv_validate(const dwbnq_pwconv_desc *d) { return validate_pw(d); }
 int pwconv_path(const dwbnq_pwconv_desc &d, const void *x, const void *w) {
   const int forced = forced_pw_path();
-  return forced == 0 ? 0 : (pw_tc_eligible(d, x, w) ? 1 : 0);
+  (void)w;
+  return forced == 0 ? 0 : (pw_tc_eligible(d, x, nullptr) ? 1 : 0);
 }
 void set_forced_pw_path(int p) { t_forced_pw = p; }
 void set_pw_max_ctas(int n) { t_pw_max_ctas = n; }

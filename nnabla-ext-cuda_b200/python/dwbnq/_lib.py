@@ -95,6 +95,8 @@ SIGNATURES = {
     "dwbnq_pwconv_fwd": (_int, [_P(PwConvDesc), _vp, _vp, _vp, _vp, _vp, _int, _vp]),
     "dwbnq_pwconv_fused_fwd": (_int, [_P(PwConvDesc), _flt, _P(QuantDesc), _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                       _int, _vp]),
+    "dwbnq_pwconv_prepare": (_int, [_P(PwConvDesc), _flt, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _vp]),
+    "dwbnq_pwconv_fused_fwd_prepared": (_int, [_P(PwConvDesc), _P(QuantDesc), _int, _vp, _vp, _vp, _int, _vp]),
     "dwbnq_pwconv_plan": (_int, [_P(PwConvDesc), _vp, _vp, _P(_int)]),
     "dwbnq_set_forced_pw_path": (_int, [_int]),
     "dwbnq_set_pw_max_ctas": (_int, [_int]),

@@ -365,6 +365,29 @@ def fused_pw_bn_quant(x, w, b, beta, gamma, mean, variance, eps=1e-5, quant=None
     return y
 
 
+def pwconv_prepare(x, w, b, beta, gamma, mean, variance, eps=1e-5, act=None, base_axis=1, math="fp32", ws=None):
+    """One-time part of fused_pw_bn_quant for parameters that do not change between calls: fills
+    (and returns) the workspace; ``x`` only gives the shape."""
+    dev = _chk_cuda(w, b, beta, gamma, mean, variance, ws)
+    d, _ = pwconv_desc(x, w, base_axis, math, act)
+    ws = ws if ws is not None else pwconv_workspace(x, w, base_axis)
+    L.check(L.lib().dwbnq_pwconv_prepare(ctypes.byref(d), float(eps), _ptr(w), _ptr(b), _ptr(beta), _ptr(gamma), _ptr(mean),
+                                         _ptr(variance), _ptr(ws), dev.index, _stream(dev)))
+    return ws
+
+
+def fused_pw_bn_quant_prepared(x, w_shape_like, ws, has_bn=True, quant=None, act=None, base_axis=1, math="fp32", out=None):
+    """The per-call part: one kernel launch on a workspace ``pwconv_prepare`` filled with the same
+    ``act`` and ``math``. ``w_shape_like`` is the weight (or anything with its shape and dtype)."""
+    dev = _chk_cuda(x, ws, out)
+    d, oshape = pwconv_desc(x, w_shape_like, base_axis, math, act)
+    q = quant_desc(quant)
+    y = out if out is not None else torch.empty(oshape, dtype=x.dtype, device=dev)
+    L.check(L.lib().dwbnq_pwconv_fused_fwd_prepared(ctypes.byref(d), ctypes.byref(q), int(bool(has_bn)), _ptr(x), _ptr(y),
+                                                    _ptr(ws), dev.index, _stream(dev)))
+    return y
+
+
 def pwconv_plan(x, w, base_axis=1, math="fp32"):
     """1 when the tcgen05 kernel takes this call, 0 for the plain FMA kernel (diagnostic)."""
     d, _ = pwconv_desc(x, w, base_axis, math)

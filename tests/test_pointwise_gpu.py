@@ -219,6 +219,33 @@ def test_many_tiles_per_cta(oracle, cuda_device, co, math, plane):
     assert np.array_equal(y.view(np.uint32), want.view(np.uint32))
 
 
+@pytest.mark.parametrize("shape", [(3, 32, 96, 28, 28), (4, 384, 64, 14, 14), (5, 160, 200, 7, 7), (2, 30, 50, 5, 9)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_prepared_workspace_gives_the_same_result(oracle, cuda_device, shape):
+    """dwbnq_pwconv_prepare once, then dwbnq_pwconv_fused_fwd_prepared on several inputs: bit-identical
+    to the one-call form, which is the two in sequence; the parameters are not read again (they
+    are overwritten between the calls here)."""
+    rng = np.random.default_rng(sum(shape))
+    d = make(rng, *shape)
+    t = {k: dev(v, cuda_device) for k, v in d.items()}
+    for math in ("fp32", "tf32"):
+        for quant, act, bn in ((FPQ_U, "relu6", True), (FPQ_S, None, True), (POW2, "relu", False)):
+            m, v, g, be = (t["mean"], t["var"], t["gamma"], t["beta"]) if bn else (None,) * 4
+            want = ops.fused_pw_bn_quant(t["x"], t["w"], t["b"], be, g, m, v, 1e-4, quant, act, math=math)
+            w2, b2 = t["w"].clone(), t["b"].clone()
+            ws = ops.pwconv_prepare(t["x"], w2, b2, be, g, m, v, 1e-4, act=act, math=math)
+            torch.cuda.synchronize()
+            w2.fill_(float("nan"))
+            b2.fill_(float("nan"))
+            got = ops.fused_pw_bn_quant_prepared(t["x"], t["w"], ws, bn, quant, act, math=math)
+            assert torch.equal(got.view(torch.int32), want.view(torch.int32)), (math, quant, act, bn)
+            x2 = (t["x"] * 0.5 + 0.25).contiguous()
+            want2 = ops.fused_pw_bn_quant(x2, t["w"], t["b"], be, g, m, v, 1e-4, quant, act, math=math)
+            got2 = ops.fused_pw_bn_quant_prepared(x2, t["w"], ws, bn, quant, act, math=math)
+            assert torch.equal(got2.view(torch.int32), want2.view(torch.int32)), (math, quant, act, bn)
+    ops.check_device_flag()
+
+
 def test_argument_errors(cuda_device):
     x = torch.zeros(1, 8, 4, 4, device=cuda_device)
     w = torch.zeros(16, 8, 1, 1, device=cuda_device)
