@@ -391,12 +391,24 @@ def pointwise_rows(torch, ops, workloads, device, batch, peak):
     three-pass TF32 mode, and a summary row for it and for the single-pass TF32 mode."""
     rows, totals = [], {"fp32": [0.0, 0, 0.0], "tf32": [0.0, 0, 0.0]}
     lib_ms = {"conv": 0.0, "chain": 0.0}
+    half_ms = 0.0
     import torch.nn.functional as F
     tf32_was = torch.backends.cudnn.allow_tf32
     torch.backends.cudnn.allow_tf32 = False
 
-    def median_ms(fn, reps=5):
+    def median_ms(fn, reps=5, graph=False):
         fn()
+        if graph:
+            g = torch.cuda.CUDAGraph()
+            cap = torch.cuda.Stream(device)
+            cap.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(cap):
+                fn()
+                with torch.cuda.graph(g, stream=cap):
+                    fn()
+            torch.cuda.current_stream(device).wait_stream(cap)
+            fn = g.replay
+            fn()
         ts = []
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         for _ in range(reps):
@@ -458,6 +470,14 @@ def pointwise_rows(torch, ops, workloads, device, batch, peak):
                              "algorithmic_bytes": nbytes,
                              "kernel": "pw_tc_kernel (tcgen05, three TF32 passes)" if path == 1 else "pw_simt_kernel (FMA)",
                              "timing": "median of 10 CUDA-graph replays, L2 flushed before each"})
+        # the same layer on binary16 tensors (one exact TF32 pass, rows gathered): summary row only
+        th = {k: v.half() for k, v in t.items()}
+        yh = torch.empty((batch, spec.c_out, spec.h, spec.h), dtype=torch.float16, device=device)
+        ops.pwconv_prepare(th["x"], th["w"], th["b"], th["beta"], th["gamma"], th["mean"], th["var"], spec.bn_eps,
+                           act=spec.act, ws=ws)
+        half_ms += median_ms(lambda: ops.fused_pw_bn_quant_prepared(th["x"], th["w"], ws, True, spec.quant, spec.act, out=yh),
+                             reps=7, graph=True)
+        del th, yh
         # library baseline: the convolution as cuDNN runs it in fp32 (TF32 off, as the reference
         # defaults), then BN, activation and quantizer as the separate passes the reference makes
         lib_ms["conv"] += median_ms(lambda: F.conv2d(t["x"], t["w"], t["b"]))
@@ -482,6 +502,10 @@ def pointwise_rows(torch, ops, workloads, device, batch, peak):
                      "images_per_s": batch / (ms / 1e3), "gbs": nb_all / ms / 1e6, "frac": nb_all / ms / 1e6 / peak,
                      "tflops": fl_all / ms / 1e9, "algorithmic_bytes": nb_all, "kernel": "library kernels, for comparison only",
                      "timing": "median of 5 eager calls per layer, L2 flushed before each (host launch overhead included)"})
+    rows.append({"workload": "pw1: 33 pointwise layers, fp16 tensors", "dtype": "f16", "batch": batch, "ms": half_ms,
+                 "images_per_s": batch / (half_ms / 1e3), "gbs": nb_all / 2 / half_ms / 1e6, "frac": nb_all / 2 / half_ms / 1e6 / peak,
+                 "tflops": fl_all / half_ms / 1e9, "algorithmic_bytes": nb_all // 2, "kernel": "pw_tc_kernel<half> (one exact TF32 pass)",
+                 "timing": "median of 7 CUDA-graph replays per layer, L2 flushed before each"})
     for math, (ms, nbytes, fl) in totals.items():
         rows.append({"workload": "pw1: 33 pointwise layers, math %s" % math, "dtype": "f32", "batch": batch, "ms": ms,
                      "images_per_s": batch / (ms / 1e3), "gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak,

@@ -326,7 +326,7 @@ typedef struct dwbnq_pwconv_desc {
   int32_t c_out;      /* output channels                               */
   int32_t h, w;       /* spatial size (input = output)                 */
   int64_t n;          /* product of the axes before base_axis          */
-  int32_t math;       /* dwbnq_pw_math (fp32 tensors only)             */
+  int32_t math;       /* dwbnq_pw_math (ignored for fp16 tensors)      */
   int32_t act;        /* dwbnq_act, applied after BN, before quantizer */
 } dwbnq_pwconv_desc;
 
@@ -370,10 +370,11 @@ int dwbnq_pwconv_prepare(const dwbnq_pwconv_desc *desc, float bn_eps, const void
 int dwbnq_pwconv_fused_fwd_prepared(const dwbnq_pwconv_desc *desc, const dwbnq_quant_desc *q, int has_bn,
                                     const void *x, void *y, void *workspace, int device, void *stream);
 
-/* Which kernel the pointwise entry points would use: 1 = the tcgen05 kernel (fp32 tensors, c_in
- * a multiple of 4; planes whose size is not a multiple of 4, or an x that is not 16-byte
- * aligned, are gathered with plain loads instead of TMA), 0 = the plain FMA kernel (fp16
- * tensors, other c_in). Diagnostic only. */
+/* Which kernel the pointwise entry points would use: 1 = the tcgen05 kernel (c_in a multiple of
+ * 4; planes whose size is not a multiple of 4, an x that is not 16-byte aligned and fp16 tensors
+ * are gathered with plain loads instead of TMA; fp16 tensors always run ONE TF32 pass, which is
+ * exact for binary16 factors, whatever `math` says), 0 = the plain FMA kernel (other c_in).
+ * Diagnostic only. */
 int dwbnq_pwconv_plan(const dwbnq_pwconv_desc *desc, const void *x, const void *w, int *path_out);
 
 /* ---- communicator: the one exchange the path needs (per-channel min/max) ----------- */

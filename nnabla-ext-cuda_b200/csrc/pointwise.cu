@@ -63,9 +63,9 @@ struct PwArgs {
   int nacc;       // accumulator buffers of npad columns in TMEM, a multiple of ngroups
   int ngroups;    // epilogue groups in use (<= kPwEpiGroups): buffer b always belongs to group b % ngroups
   const float *coef;  // [5][co_tiles * npad]: bias, mean, scale, stdvar, beta
-  const float *x;     // gather mode: the activations, read with plain loads
+  const void *x;      // gather mode: the activations (fp32 or fp16), read with plain loads
   long long total_pos;  // gather mode: N * HW, the flattened positions
-  float *y;
+  void *y;            // fp32 or fp16 like x
   int *flag;
   int has_bn, act, qkind;
   QuantArgs q;
@@ -256,7 +256,9 @@ __device__ __forceinline__ void pw_finish_unit(const unsigned int *acc, const Pw
 
 // ---- the tcgen05 kernel ------------------------------------------------------------------------
 
-template <bool GATHER, bool MATH3, int EPI>
+// T: the tensors' element type. fp16 tensors come in through the gather path only and run the single
+// pass: a binary16 value has 11 significant bits, so it is exact in TF32 and so is every product.
+template <typename T, bool GATHER, bool MATH3, int EPI>
 __global__ void __launch_bounds__(kPwThreads, 1)
 pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
              const __grid_constant__ CUtensorMap tm_wlo, const PwArgs a) {
@@ -414,23 +416,24 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
       // chunk i; the load cursor runs through the (tile, chunk) sequence on its own.
       int t_l = blockIdx.x, kc_l = 0;
       bool valid_l = false;
-      const float *xp_l = a.x;
+      const T *const xbase = static_cast<const T *>(a.x);
+      const T *xp_l = xbase;
       auto locate = [&]() {
         const long long g = (long long)(t_l % a.per_ct) * kPwPosTile + m;
         valid_l = g < a.total_pos;
         const long long n = valid_l ? g / a.HW : 0;
-        xp_l = a.x + (size_t)n * a.Ci * a.HW + (valid_l ? (int)(g - n * a.HW) : 0);
+        xp_l = xbase + (size_t)n * a.Ci * a.HW + (valid_l ? (int)(g - n * a.HW) : 0);
       };
       const size_t plane = (size_t)a.HW;
       auto load = [&](float(&v)[16]) {
         const int k0 = kc_l * kPwKChunk + kh * 16;
-        const float *q = xp_l + (size_t)k0 * plane;
+        const T *q = xp_l + (size_t)k0 * plane;
         if (valid_l && k0 + 16 <= a.Ci) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = __ldg(q + j * plane);
+          for (int j = 0; j < 16; ++j) v[j] = Elem<T>::to_f32(__ldg(q + j * plane));
         } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = (valid_l && k0 + j < a.Ci) ? __ldg(q + j * plane) : 0.0f;
+          for (int j = 0; j < 16; ++j) v[j] = (valid_l && k0 + j < a.Ci) ? Elem<T>::to_f32(__ldg(q + j * plane)) : 0.0f;
         }
         if (++kc_l == a.kchunks) {
           kc_l = 0;
@@ -552,7 +555,7 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
       if (c_valid > a.npad) c_valid = a.npad;
       const int units = (c_valid + 7) >> 3;  // warp-uniform
       const unsigned int taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + b * a.npad;
-      float *img = a.y + ((size_t)n * a.Co + c_first) * a.HW + (p_ok ? p : 0);
+      T *img = static_cast<T *>(a.y) + ((size_t)n * a.Co + c_first) * a.HW + (p_ok ? p : 0);
       const size_t unit_stride = (size_t)8 * a.HW;
       const PwPair *tp = table + (c_first >> 1);
       unsigned int acc0[8], acc1[8];
@@ -564,14 +567,14 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
         pw_finish_unit<EPI>(acc0, tp + u * 4, a, nz, fq, bn_safe, res);
         if (p_ok) {
           const int c0 = u * 8;
-          float *q = img + (size_t)u * unit_stride;
+          T *q = img + (size_t)u * unit_stride;
           if (c0 + 8 <= c_valid) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) q[(unsigned)(i * a.HW)] = res[i];
+            for (int i = 0; i < 8; ++i) q[(unsigned)(i * a.HW)] = Elem<T>::from_f32(res[i]);
           } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-              if (c0 + i < c_valid) q[(unsigned)(i * a.HW)] = res[i];
+              if (c0 + i < c_valid) q[(unsigned)(i * a.HW)] = Elem<T>::from_f32(res[i]);
           }
         }
         if (u + 1 < units) {
@@ -580,14 +583,14 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
           pw_finish_unit<EPI>(acc1, tp + (u + 1) * 4, a, nz, fq, bn_safe, res);
           if (p_ok) {
             const int c0 = (u + 1) * 8;
-            float *q = img + (size_t)(u + 1) * unit_stride;
+            T *q = img + (size_t)(u + 1) * unit_stride;
             if (c0 + 8 <= c_valid) {
 #pragma unroll
-              for (int i = 0; i < 8; ++i) q[(unsigned)(i * a.HW)] = res[i];
+              for (int i = 0; i < 8; ++i) q[(unsigned)(i * a.HW)] = Elem<T>::from_f32(res[i]);
             } else {
 #pragma unroll
               for (int i = 0; i < 8; ++i)
-                if (c0 + i < c_valid) q[(unsigned)(i * a.HW)] = res[i];
+                if (c0 + i < c_valid) q[(unsigned)(i * a.HW)] = Elem<T>::from_f32(res[i]);
             }
           }
         }
@@ -776,18 +779,18 @@ bool pw_tma_x(const dwbnq_pwconv_desc &d, const void *x) {
 }
 bool pw_tc_eligible(const dwbnq_pwconv_desc &d, const void *x, const void *w) {
   const long long hw = (long long)d.h * d.w;
-  return d.dtype == DWBNQ_F32 && d.c_in % 4 == 0 && d.c_out <= kPwMaxCout && (long long)d.c_out * hw <= 0x7fffffffLL &&
+  return d.c_in % 4 == 0 && d.c_out <= kPwMaxCout && (long long)d.c_out * hw <= 0x7fffffffLL &&
          d.n * hw <= (1LL << 40);
 }
 
-template <bool GATHER, bool MATH3>
+template <typename T, bool GATHER, bool MATH3>
 cudaError_t launch_pw_tc(int epi, dim3 grid, size_t smem, cudaStream_t stream, const CUtensorMap &tx, const CUtensorMap &tw,
                          const CUtensorMap &twl, const PwArgs &a) {
   void (*k)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const PwArgs) =
-      epi == PW_EPI_BIAS ? pw_tc_kernel<GATHER, MATH3, PW_EPI_BIAS>
-      : epi == PW_EPI_BN_FPQ ? pw_tc_kernel<GATHER, MATH3, PW_EPI_BN_FPQ>
-      : epi == PW_EPI_BN_RELU6_FPQ ? pw_tc_kernel<GATHER, MATH3, PW_EPI_BN_RELU6_FPQ>
-      : epi == PW_EPI_BN_FPQS ? pw_tc_kernel<GATHER, MATH3, PW_EPI_BN_FPQS> : pw_tc_kernel<GATHER, MATH3, PW_EPI_GENERIC>;
+      epi == PW_EPI_BIAS ? pw_tc_kernel<T, GATHER, MATH3, PW_EPI_BIAS>
+      : epi == PW_EPI_BN_FPQ ? pw_tc_kernel<T, GATHER, MATH3, PW_EPI_BN_FPQ>
+      : epi == PW_EPI_BN_RELU6_FPQ ? pw_tc_kernel<T, GATHER, MATH3, PW_EPI_BN_RELU6_FPQ>
+      : epi == PW_EPI_BN_FPQS ? pw_tc_kernel<T, GATHER, MATH3, PW_EPI_BN_FPQS> : pw_tc_kernel<T, GATHER, MATH3, PW_EPI_GENERIC>;
   // the opt-in to large dynamic shared memory is per function and per device
   static thread_local const void *attr_done[5] = {nullptr};
   static thread_local int attr_dev[5] = {0};
@@ -815,7 +818,8 @@ PwMode pw_mode(const dwbnq_pwconv_desc &d, const void *x, int *status) {
   if (forced == 1 && !eligible) *status = fail(DWBNQ_ERR_UNSUPPORTED, "the tcgen05 kernel cannot take this shape / alignment");
   PwMode m;
   m.tc = forced == 0 ? false : eligible;
-  m.math3 = m.tc && d.math == DWBNQ_PW_MATH_FP32;
+  // binary16 factors are exact in TF32: one pass gives exact products
+  m.math3 = m.tc && d.dtype == DWBNQ_F32 && d.math == DWBNQ_PW_MATH_FP32;
   return m;
 }
 
@@ -913,18 +917,18 @@ int pwconv_run(const dwbnq_pwconv_desc &d, const dwbnq_quant_desc *q, int has_bn
   a.npad = g.npad; a.co_tiles = g.co_tiles;
   a.pos_tiles = (HW + kPwPosTile - 1) / kPwPosTile;
   a.kchunks = (d.c_in + kPwKChunk - 1) / kPwKChunk;
-  a.x = static_cast<const float *>(x);
+  a.x = x;
   a.total_pos = d.n * HW;
   // Gathered when TMA cannot take the plane, or when the per-image tiling would leave more than
   // a tenth of the accumulator rows empty (196 positions fill 1.53 tiles of 128).
-  bool gather = !pw_tma_x(d, x) || (long long)a.pos_tiles * kPwPosTile * 10 > (long long)HW * 11;
+  bool gather = d.dtype == DWBNQ_F16 || !pw_tma_x(d, x) || (long long)a.pos_tiles * kPwPosTile * 10 > (long long)HW * 11;
   {
     static const int env = [] {
       const char *e = std::getenv("DWBNQ_PW_GATHER");
       return e && (e[0] == '0' || e[0] == '1') ? e[0] - '0' : -1;
     }();
     if (env == 1) gather = true;
-    if (env == 0 && pw_tma_x(d, x)) gather = false;
+    if (env == 0 && pw_tma_x(d, x) && d.dtype == DWBNQ_F32) gather = false;
   }
   {
     const long long per_ct = gather ? (a.total_pos + kPwPosTile - 1) / kPwPosTile : d.n * a.pos_tiles;
@@ -944,7 +948,7 @@ int pwconv_run(const dwbnq_pwconv_desc &d, const dwbnq_quant_desc *q, int has_bn
   if (a.stages > kPwMaxStages) a.stages = kPwMaxStages;
   if (a.stages < 2) return fail(DWBNQ_ERR_UNSUPPORTED, "pipeline stage of %d bytes does not fit twice", a.stage_bytes);
   a.coef = coef;
-  a.y = static_cast<float *>(y);
+  a.y = y;
   st = device_flag_ptr(dev, &a.flag);
   if (st != DWBNQ_OK) return st;
   a.has_bn = mean != nullptr; a.act = d.act; a.qkind = kind; a.q = qa;
@@ -984,10 +988,12 @@ int pwconv_run(const dwbnq_pwconv_desc &d, const dwbnq_quant_desc *q, int has_bn
   int grid = a.total_tiles < sms ? a.total_tiles : sms;
   if (t_pw_max_ctas > 0 && grid > t_pw_max_ctas) grid = t_pw_max_ctas;
   const dim3 gd((unsigned)grid);
-  const cudaError_t e = gather ? (math3 ? launch_pw_tc<true, true>(epi, gd, smem, stream, tx, tw, twl, a)
-                                        : launch_pw_tc<true, false>(epi, gd, smem, stream, tx, tw, twl, a))
-                               : (math3 ? launch_pw_tc<false, true>(epi, gd, smem, stream, tx, tw, twl, a)
-                                        : launch_pw_tc<false, false>(epi, gd, smem, stream, tx, tw, twl, a));
+  const cudaError_t e = d.dtype == DWBNQ_F16
+                            ? launch_pw_tc<__half, true, false>(epi, gd, smem, stream, tx, tw, twl, a)
+                            : gather ? (math3 ? launch_pw_tc<float, true, true>(epi, gd, smem, stream, tx, tw, twl, a)
+                                              : launch_pw_tc<float, true, false>(epi, gd, smem, stream, tx, tw, twl, a))
+                                     : (math3 ? launch_pw_tc<float, false, true>(epi, gd, smem, stream, tx, tw, twl, a)
+                                              : launch_pw_tc<float, false, false>(epi, gd, smem, stream, tx, tw, twl, a));
   if (e != cudaSuccess) return fail_cuda(e, "pw_tc_kernel launch");
   return DWBNQ_OK;
 }

@@ -264,7 +264,9 @@ def test_pointwise_descriptor_validation_workspace_and_plan(dwlib):
     assert lib.dwbnq_pwconv_workspace_bytes(ctypes.byref(deep)) == 5 * 320 * 4 + 2 * 512 * 300 * 4
     fake, path = ctypes.c_void_p(4096), ctypes.c_int(-1)
     assert lib.dwbnq_pwconv_plan(ctypes.byref(good), fake, fake, ctypes.byref(path)) == dwlib.OK and path.value == 1
-    for bad in (P(dtype=dwlib.F16, c_in=32, c_out=96, h=14, w=14, n=4),   # fp16 tensors
+    half = P(dtype=dwlib.F16, c_in=32, c_out=96, h=14, w=14, n=4)  # fp16 tensors: gathered, one exact TF32 pass
+    assert lib.dwbnq_pwconv_plan(ctypes.byref(half), fake, fake, ctypes.byref(path)) == dwlib.OK and path.value == 1
+    for bad in (P(dtype=dwlib.F16, c_in=30, c_out=96, h=14, w=14, n=4),
                 P(dtype=dwlib.F32, c_in=30, c_out=96, h=14, w=14, n=4)):  # weight rows not 16-byte multiples
         assert lib.dwbnq_pwconv_plan(ctypes.byref(bad), fake, fake, ctypes.byref(path)) == dwlib.OK and path.value == 0
     # a 7x7 plane is gathered, an unaligned x too: still the tensor-core kernel
