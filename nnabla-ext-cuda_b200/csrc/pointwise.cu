@@ -11,14 +11,17 @@
 //    positions of one channel: BN / activation / quantizer run in registers with warp-uniform
 //    per-channel coefficients and every store is one coalesced 128-byte line - no staging of
 //    the output in shared memory;
-//  * one CTA per SM walks over (channel tile, image, position tile) triples; warp 0 issues
-//    the TMA loads, warp 1 the MMAs, warps 2-5 split the fp32 activations into TF32 halves for
-//    the three-pass mode, warps 6-21 are the epilogue (four groups of four warps, each group a
-//    tile of its own); up to eight accumulator buffers in TMEM decouple the MMAs from the epilogue;
+//  * one CTA per SM walks over (channel tile, 128 positions) pairs; warp 0 issues the TMA
+//    loads, warp 1 the MMAs, warps 2-9 bring the activations into operand form - they split the
+//    TMA-loaded fp32 values into TF32 halves for the three-pass mode, or, in gather mode, load
+//    them with plain loads (planes TMA cannot take or would tile badly, fp16 tensors), rows
+//    flattened over (image, position) - and warps 10-25 are the epilogue (four groups of four
+//    warps, each group a tile of its own); up to eight accumulator buffers in TMEM decouple the
+//    MMAs from the epilogue;
 //  * every wait on an mbarrier is bounded in time; a wait that runs out records it in the
 //    device flag, the roles leave their loops, and the CTA frees its tensor memory and returns.
-// Shapes the TMA loads cannot take (h*w or c_in not a multiple of 4, fp16 tensors) run on a
-// plain FMA kernel with the same epilogue.
+// c_in that is not a multiple of 4 (the weight rows must be 16-byte multiples for their TMA
+// loads) runs on a plain FMA kernel with the same epilogue.
 #include <cstdlib>
 #include <cstring>
 
