@@ -123,7 +123,9 @@ int dwbnq_check_device_flag(int device);
 /* Output spatial size the base class computes in setup_impl:
  * o = (i + 2p - d(k-1) - 1) / s + 1. Fails with DWBNQ_ERR_INVALID_ARG on a bad desc
  * and DWBNQ_ERR_UNSUPPORTED when c*multiplier*kh*kw > 65536, the limit the reference
- * enforces (depthwise_convolution.cu:381). */
+ * enforces (depthwise_convolution.cu:381), or when a padded input plane or an output plane
+ * holds more than 2^31-1 elements (planes are indexed with 32-bit integers). ho and wo may
+ * each be NULL (not written). */
 int dwbnq_conv_out_shape(const dwbnq_conv_desc *desc, int32_t *ho, int32_t *wo);
 /* max_ / min_ members of FixedPointQuantize for (sign, n, delta). */
 int dwbnq_fpq_range(int sign, int n, float delta, float *max_out, float *min_out);

@@ -172,7 +172,10 @@ int dwbnq_check_device_flag(int device) {
   if (v) {
     const int zero = 0;
     cudaMemcpy(p, &zero, sizeof(int), cudaMemcpyHostToDevice);
-    return fail(DWBNQ_ERR_DEVICE_FLAG, "a kernel gave up a bounded wait on device %d (flag %d)", dev, v);
+    return fail(DWBNQ_ERR_DEVICE_FLAG,
+                "a kernel recorded an error on device %d (flag %d: 1 = a bounded wait ran out, 2 = an index left its "
+                "tensor in the bounds-checked build)",
+                dev, v);
   }
   return DWBNQ_OK;
 }

@@ -51,6 +51,22 @@ struct QuantArgs {
   unsigned int *mm_enc_min, *mm_enc_max;
 };
 
+// Bounds-checked debug build (make debug: -DDWBNQ_BOUNDS_CHECK, libdwbnq_debug.so): every global
+// access whose index is computed by the kernel itself - not by the TMA / bulk-copy hardware,
+// which clips by construction - is tested against its tensor's extent first. An index outside
+// records 2 in the device flag and the access is skipped; nothing traps. In the normal build the
+// macro is `true` and costs nothing.
+#ifdef DWBNQ_BOUNDS_CHECK
+__device__ __forceinline__ bool bounds_ok(long long i, long long n, int *flag) {
+  if (i >= 0 && i < n) return true;
+  if (flag) atomicExch(flag, 2);
+  return false;
+}
+#define DWBNQ_IN_BOUNDS(index, extent, flag) ::dwbnq::bounds_ok((long long)(index), (long long)(extent), (flag))
+#else
+#define DWBNQ_IN_BOUNDS(index, extent, flag) true
+#endif
+
 // Programmatic dependent launch (no-ops when the launch does not carry the attribute): a grid
 // lets its successor in the stream become resident early, and itself touches global memory
 // only after its predecessor has completed and flushed.

@@ -114,6 +114,10 @@ __device__ __forceinline__ float conv_point(const FusedArgs &a, long long n, int
     for (int kx = 0; kx < a.kw; ++kx) {
       const int ix = ox * a.sw + kx * a.dw - a.pw;
       if (iy >= 0 && iy < a.H && ix >= 0 && ix < a.W) {
+        if (!DWBNQ_IN_BOUNDS(xbase + (long long)iy * a.W + ix, a.n * a.C * (long long)a.H * a.W, a.flag) ||
+            !DWBNQ_IN_BOUNDS((long long)oc * a.kh * a.kw + tap_index(a, ky * a.kw + kx, a.kh * a.kw),
+                             (long long)a.OC * a.kh * a.kw, a.flag))
+          continue;
         const float xv = load_x<T>(a, a.x, xbase + (long long)iy * a.W + ix);
         const float wv = Elem<T>::to_f32(wp[tap_index(a, ky * a.kw + kx, a.kh * a.kw)]);
         acc = __fadd_rn(acc, __fmul_rn(wv, xv));
@@ -198,7 +202,7 @@ __global__ void __launch_bounds__(256) fused_generic_kernel(const FusedArgs a,
     const float v = prequant_point<T>(a, n, oc, oy, ox);
     if (QM == QM_MM_REDUCE) {
       reduce_minmax_to_global(a.q, oc, v, valid);
-    } else if (valid) {
+    } else if (valid && DWBNQ_IN_BOUNDS(o, total, a.flag)) {
       const float r = quant_apply<QM>(v, a.q, load_mm<QM>(a, oc));
       if ((QM == QM_FPQ || QM == QM_FPQ_LEAN) && a.code8) static_cast<signed char *>(a.y)[o] = (signed char)fpq_code(r, a.q);
       else y[o] = Elem<T>::from_f32(r);

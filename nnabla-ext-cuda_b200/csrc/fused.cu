@@ -46,13 +46,19 @@ EncodeTiledFn encode_tiled_fn() {
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 inline int round_up(int a, int b) { return ceil_div(a, b) * b; }
 
+constexpr int kGenericThreads = 256;
+// Grid of the generic kernel: one thread per output, grid-stride beyond 64 CTAs per SM.
+long long generic_blocks(long long total, int sms) {
+  long long blocks = (total + kGenericThreads - 1) / kGenericThreads;
+  const long long cap = (long long)sms * 64;
+  if (blocks > cap) blocks = cap;
+  return blocks < 1 ? 1 : blocks;
+}
+
 template <typename T>
 cudaError_t launch_generic_t(int qm, const FusedArgs &a, long long total, int sms, cudaStream_t stream) {
-  const int threads = 256;
-  long long blocks = (total + threads - 1) / threads;
-  const long long cap = (long long)sms * 64;  // grid-stride beyond 64 CTAs per SM
-  if (blocks > cap) blocks = cap;
-  if (blocks < 1) blocks = 1;
+  const int threads = kGenericThreads;
+  const long long blocks = generic_blocks(total, sms);
   switch (qm) {
     case QM_NONE: fused_generic_kernel<T, QM_NONE><<<(unsigned)blocks, threads, 0, stream>>>(a, total); break;
     case QM_FPQ: fused_generic_kernel<T, QM_FPQ><<<(unsigned)blocks, threads, 0, stream>>>(a, total); break;
@@ -116,8 +122,14 @@ int validate_conv(const dwbnq_conv_desc *d, int *ho, int *wo) {
   if ((long long)d->c * d->multiplier * d->kh * d->kw > 65536)
     return fail(DWBNQ_ERR_UNSUPPORTED,
                 "GPU implementation limit reached: output-channels x filter-size can not be more than 65536");
-  if (ho) *ho = (int)(eh / d->stride_h + 1);
-  if (wo) *wo = (int)(ew / d->stride_w + 1);
+  // The kernels index one plane (and one padded plane) with 32-bit integers.
+  const long long oh = eh / d->stride_h + 1, ow = ew / d->stride_w + 1;
+  const long long ph = (long long)d->h + 2LL * d->pad_h, pw = (long long)d->w + 2LL * d->pad_w;
+  if (ph > INT32_MAX || pw > INT32_MAX || ph * pw > INT32_MAX || oh * ow > INT32_MAX)
+    return fail(DWBNQ_ERR_UNSUPPORTED, "padded plane %lldx%lld / output plane %lldx%lld exceeds 2^31-1 elements", ph, pw,
+                oh, ow);
+  if (ho) *ho = (int)oh;
+  if (wo) *wo = (int)ow;
   return DWBNQ_OK;
 }
 
@@ -147,7 +159,24 @@ long long gcd_ll(long long a, long long b) { return b ? gcd_ll(b, a % b) : a; }
 
 }  // namespace
 
+namespace {
+int make_plan_tiled(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan);
+}
+
 int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan) {
+  int st = make_plan_tiled(d, x, y, plan);
+  if (st != DWBNQ_OK || plan->path != PATH_GENERIC) return st;
+  int Ho = 0, Wo = 0;
+  validate_conv(&d, &Ho, &Wo);
+  plan->threads = kGenericThreads;
+  plan->ctas = generic_blocks(d.n * d.c * d.multiplier * Ho * Wo, sm_count(-1));
+  plan->smem = 0;
+  return DWBNQ_OK;
+}
+
+namespace {
+
+int make_plan_tiled(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan) {
   int Ho, Wo;
   int st = validate_conv(&d, &Ho, &Wo);
   if (st != DWBNQ_OK) return st;
@@ -348,6 +377,8 @@ int make_plan(const dwbnq_conv_desc &d, const void *x, const void *y, Plan *plan
   plan->ctas = c.n_tiles;
   return DWBNQ_OK;
 }
+
+}  // namespace
 
 int launch_fused(const dwbnq_conv_desc &d, FusedArgs &a, int qm, int device, cudaStream_t stream) {
   Plan plan;

@@ -433,10 +433,14 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
         const T *q = xp_l + (size_t)k0 * plane;
         if (valid_l && k0 + 16 <= a.Ci) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = Elem<T>::to_f32(__ldg(q + j * plane));
+          for (int j = 0; j < 16; ++j)
+            v[j] = DWBNQ_IN_BOUNDS((q + j * plane) - xbase, a.total_pos * a.Ci, a.flag) ? Elem<T>::to_f32(__ldg(q + j * plane)) : 0.0f;
         } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = (valid_l && k0 + j < a.Ci) ? Elem<T>::to_f32(__ldg(q + j * plane)) : 0.0f;
+          for (int j = 0; j < 16; ++j)
+            v[j] = (valid_l && k0 + j < a.Ci && DWBNQ_IN_BOUNDS((q + j * plane) - xbase, a.total_pos * a.Ci, a.flag))
+                       ? Elem<T>::to_f32(__ldg(q + j * plane))
+                       : 0.0f;
         }
         if (++kc_l == a.kchunks) {
           kc_l = 0;
@@ -561,6 +565,7 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
       T *img = static_cast<T *>(a.y) + ((size_t)n * a.Co + c_first) * a.HW + (p_ok ? p : 0);
       const size_t unit_stride = (size_t)8 * a.HW;
       const PwPair *tp = table + (c_first >> 1);
+      if (!DWBNQ_IN_BOUNDS((c_first >> 1) + units * 4 - 1, cpad >> 1, a.flag)) break;
       unsigned int acc0[8], acc1[8];
       tc_ld8(taddr, acc0);
       for (int u = 0; u < units; u += 2) {
@@ -573,11 +578,13 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
           T *q = img + (size_t)u * unit_stride;
           if (c0 + 8 <= c_valid) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) q[(unsigned)(i * a.HW)] = Elem<T>::from_f32(res[i]);
+            for (int i = 0; i < 8; ++i) if (DWBNQ_IN_BOUNDS((q + (unsigned)(i * a.HW)) - static_cast<T *>(a.y), a.total_pos * a.Co, a.flag))
+                  q[(unsigned)(i * a.HW)] = Elem<T>::from_f32(res[i]);
           } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-              if (c0 + i < c_valid) q[(unsigned)(i * a.HW)] = Elem<T>::from_f32(res[i]);
+              if (c0 + i < c_valid) if (DWBNQ_IN_BOUNDS((q + (unsigned)(i * a.HW)) - static_cast<T *>(a.y), a.total_pos * a.Co, a.flag))
+                  q[(unsigned)(i * a.HW)] = Elem<T>::from_f32(res[i]);
           }
         }
         if (u + 1 < units) {
@@ -589,11 +596,13 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
             T *q = img + (size_t)(u + 1) * unit_stride;
             if (c0 + 8 <= c_valid) {
 #pragma unroll
-              for (int i = 0; i < 8; ++i) q[(unsigned)(i * a.HW)] = Elem<T>::from_f32(res[i]);
+              for (int i = 0; i < 8; ++i) if (DWBNQ_IN_BOUNDS((q + (unsigned)(i * a.HW)) - static_cast<T *>(a.y), a.total_pos * a.Co, a.flag))
+                  q[(unsigned)(i * a.HW)] = Elem<T>::from_f32(res[i]);
             } else {
 #pragma unroll
               for (int i = 0; i < 8; ++i)
-                if (c0 + i < c_valid) q[(unsigned)(i * a.HW)] = Elem<T>::from_f32(res[i]);
+                if (c0 + i < c_valid) if (DWBNQ_IN_BOUNDS((q + (unsigned)(i * a.HW)) - static_cast<T *>(a.y), a.total_pos * a.Co, a.flag))
+                  q[(unsigned)(i * a.HW)] = Elem<T>::from_f32(res[i]);
             }
           }
         }
@@ -648,6 +657,7 @@ struct PwSimtArgs {
   void *y;
   const float *coef;
   int HW, Ci, Co, cpad, pos_tiles;
+  int *flag;
   int has_bn, act, qkind;
   QuantArgs q;
 };
@@ -670,7 +680,10 @@ __global__ void __launch_bounds__(256) pw_simt_kernel(const PwSimtArgs a) {
   for (int k0 = 0; k0 < a.Ci; k0 += 16) {
     for (int e = threadIdx.x; e < 16 * 64; e += 256) {
       const int k = e >> 6, j = e & 63;  // xs: positions contiguous in memory
-      xs[k][j] = (k0 + k < a.Ci && p0 + j < a.HW) ? Elem<T>::to_f32(xn[(size_t)(k0 + k) * a.HW + p0 + j]) : 0.0f;
+      xs[k][j] = (k0 + k < a.Ci && p0 + j < a.HW &&
+                  DWBNQ_IN_BOUNDS((xn - x) + (long long)(k0 + k) * a.HW + p0 + j, (long long)gridDim.x / a.pos_tiles * a.Ci * a.HW, a.flag))
+                     ? Elem<T>::to_f32(xn[(size_t)(k0 + k) * a.HW + p0 + j])
+                     : 0.0f;
       const int kk = e & 15, c = e >> 4;  // ws: c_in contiguous in memory
       ws[kk][c] = (k0 + kk < a.Ci && c0 + c < a.Co) ? w[(size_t)(c0 + c) * a.Ci + k0 + kk] : 0.0f;
     }
@@ -702,7 +715,8 @@ __global__ void __launch_bounds__(256) pw_simt_kernel(const PwSimtArgs a) {
       v = pw_act(v, a.act);
       if (a.qkind == DWBNQ_Q_FPQ) v = fpq_apply(v, a.q);
       else if (a.qkind == DWBNQ_Q_POW2) v = pow2_apply(v, a.q);
-      y[((size_t)n * a.Co + c) * a.HW + p] = Elem<T>::from_f32(v);
+      if (DWBNQ_IN_BOUNDS(((long long)n * a.Co + c) * a.HW + p, (long long)gridDim.x / a.pos_tiles * a.Co * a.HW, a.flag))
+        y[((size_t)n * a.Co + c) * a.HW + p] = Elem<T>::from_f32(v);
     }
   }
 }
@@ -904,6 +918,8 @@ int pwconv_run(const dwbnq_pwconv_desc &d, const dwbnq_quant_desc *q, int has_bn
     a.HW = HW; a.Ci = d.c_in; a.Co = d.c_out; a.cpad = g.cpad;
     a.pos_tiles = (HW + 63) / 64;
     a.has_bn = mean != nullptr; a.act = d.act; a.qkind = kind; a.q = qa;
+    st = device_flag_ptr(dev, &a.flag);
+    if (st != DWBNQ_OK) return st;
     const long long gx = d.n * a.pos_tiles;
     if (gx > 0x7fffffffLL) return fail(DWBNQ_ERR_UNSUPPORTED, "batch x position tiles beyond 2^31 - 1");
     const dim3 grid((unsigned)gx, (unsigned)((d.c_out + 63) / 64));

@@ -7,7 +7,8 @@ import ctypes
 import os
 
 _PKG_ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), "..", ".."))
-LIB_PATH = os.path.join(_PKG_ROOT, "libdwbnq.so")
+# DWBNQ_LIBRARY selects another build of the same ABI (the bounds-checked libdwbnq_debug.so)
+LIB_PATH = os.environ.get("DWBNQ_LIBRARY") or os.path.join(_PKG_ROOT, "libdwbnq.so")
 
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_NCCL, ERR_TIMEOUT, ERR_DEVICE_FLAG = range(7)
 F32, F16 = 0, 1
