@@ -2,7 +2,7 @@
 """Benchmark of the fused dw-conv + BN-inference + quantize path.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl own|reference]
-                  [--workload cfg1|cfg0|cfg2|cfg3|cfg4|cfg1q8|ops] [--batch B] [--scaling weak|strong]
+                  [--workload cfg1|cfg0|cfg2|cfg3|cfg4|cfg1q8|ops|pw1|body] [--batch B] [--scaling weak|strong]
 
 A "step" is one pass of the workload's layer stack over one batch of seeded synthetic
 input (cfg1: the 17 depthwise layers of MobileNetV2 at 224x224, batch 256 per GPU, fp32,
@@ -353,6 +353,63 @@ def run_pointwise(args):
     print(json.dumps(line), flush=True)
 
 
+def body_row(torch, ops, workloads, device, batch, peak, reps=10):
+    """The 50 layers of MobileNetV2's body as ONE network: the unfused function list nnabla would
+    build (166 functions), fused by the two graph passes into 17 FusedDwBnQuant + 33
+    FusedPwBnQuant nodes, every layer reading the previous layer's output; pointwise parameters
+    prepared once, the 50 launches replayed from a CUDA graph, L2 flushed before each replay."""
+    from dwbnq import graph
+    nodes, host, x_in, x_out, _ = workloads.body_graph(batch)
+    shapes = {k: v.shape for k, v in host.items()}
+    fused = graph.fuse_pw_bn_quant(graph.fuse_dw_bn_quant(nodes, [x_out], shapes), [x_out], shapes)
+    tensors = {k: torch.from_numpy(v).to(device) for k, v in host.items()}
+    del host
+    runner = graph.GraphRunner(fused, tensors)
+    runner.replay()
+    runner.synchronize()
+    ts = []
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(reps):
+        flush_l2(torch, device)
+        e0.record()
+        runner.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    runner.synchronize()
+    ms = float(np.median(ts))
+    nbytes = sum(sp.algorithmic_bytes(4, batch) for _, sp in workloads.mobilenetv2_body(batch))
+    flops = sum(sp.flops(batch) for kind, sp in workloads.mobilenetv2_body(batch) if kind == "pw")
+    out_shape = tuple(tensors[x_out].shape)
+    del runner, tensors
+    torch.cuda.empty_cache()
+    return {"workload": "body: MobileNetV2's 50 depthwise + pointwise layers chained (each reads the previous output), "
+                        "fused by the graph passes", "dtype": "f32", "batch": batch, "ms": ms, "best_ms": float(min(ts)),
+            "images_per_s": batch / (ms / 1e3), "gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak,
+            "tflops": flops / ms / 1e9, "algorithmic_bytes": nbytes, "launches": len(fused), "output": list(out_shape),
+            "kernel": "fused_plane_* (17 launches) + pw_tc_kernel (33 launches)",
+            "timing": "median of %d CUDA-graph replays of the 50 launches, L2 flushed before each" % reps}
+
+
+def run_body(args):
+    """Workload body alone: one JSON line in the bench format."""
+    import torch
+    from dwbnq import ops, workloads
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the dwbnq path has no CPU fallback")
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    peak, peak_kind = measured_peak()
+    row = body_row(torch, ops, workloads, device, args.batch, peak)
+    line = {"metric": "images_per_s", "value": row["images_per_s"], "unit": "images/s", "n_gpus": 1, "steps": 10,
+            "warmup": 3, "ms_per_step": row["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": {"workload": row["workload"], "batch": args.batch,
+                                                            "l2": "L2 flushed before every timed replay"},
+            "roofline": {"bound": "hbm", "achieved": row["gbs"], "peak": peak, "unit": "GB/s", "frac": row["frac"],
+                         "traffic": None, "peak_kind": peak_kind}, "gpu_launches": row["launches"], "layers": [row]}
+    print(json.dumps(line), flush=True)
+
+
 def bind_to_gpu_numa_node(torch, index):
     """Restricts this process to the CPUs of the NUMA node its GPU hangs off, so that the
     pinned host buffers of the end-to-end pass (allocated afterwards, first touched here) are
@@ -614,6 +671,7 @@ def other_workloads(torch, ops, workloads, device, cfg1_layers, args):
                     "timing": "median of 10 launches, L2 flushed before each"})
     torch.cuda.empty_cache()
     out.extend(pointwise_rows(torch, ops, workloads, device, 256, peak))
+    out.append(body_row(torch, ops, workloads, device, 256, peak))
     torch.cuda.empty_cache()
     return out
 
@@ -968,7 +1026,7 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
-    ap.add_argument("--workload", default="cfg1", choices=["cfg0", "cfg1", "cfg2", "cfg3", "cfg4", "cfg1q8", "ops", "pw1"])
+    ap.add_argument("--workload", default="cfg1", choices=["cfg0", "cfg1", "cfg2", "cfg3", "cfg4", "cfg1q8", "ops", "pw1", "body"])
     ap.add_argument("--batch", type=int, default=None, help="images per GPU (default: the workload's batch)")
     ap.add_argument("--dtype", default="f32", choices=["f32", "f16"])
     ap.add_argument("--cpu-sample", type=int, default=None, help="images per CPU-baseline pass")
@@ -988,18 +1046,20 @@ def main():
     ap.add_argument("--force-path", type=int, default=None, help="profiling only: kernel family 0..4")
     ap.add_argument("--tune", default="", help="profiling only: planner override P,row_blocks,threads,rows_per_patch")
     args = ap.parse_args()
-    defaults = {"cfg0": 32, "cfg1": 256, "cfg2": 128, "cfg3": 512, "cfg4": 256, "cfg1q8": 256, "ops": 256, "pw1": 256}
+    defaults = {"cfg0": 32, "cfg1": 256, "cfg2": 128, "cfg3": 512, "cfg4": 256, "cfg1q8": 256, "ops": 256, "pw1": 256, "body": 256}
     if args.batch is None:
         args.batch = defaults[args.workload]
     if args.warmup < 3:
         args.warmup = 3
     if args.cpu_sample is None:
         args.cpu_sample = {"cfg0": 32, "cfg1": 64, "cfg2": 32, "cfg3": 128, "cfg4": 64, "cfg1q8": 64,
-                           "ops": 0, "pw1": 0}[args.workload]
+                           "ops": 0, "pw1": 0, "body": 0}[args.workload]
     if args.workload == "ops":
         run_standalone_ops(args)
     elif args.workload == "pw1":
         run_pointwise(args)
+    elif args.workload == "body":
+        run_body(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -254,8 +254,11 @@ def execute(nodes, tensors, comm=None, check=False):
                 else:
                     quant = {"kind": "pow2", "sign": qa.get("sign", True), "with_zero": qa.get("with_zero", True),
                              "n": qa.get("n", 8), "m": qa.get("m", 1)}
-            y = ops.fused_pw_bn_quant(i[0], i[1], b, beta, gamma, mean, var, ba.get("eps", 1e-5), quant, n["act"],
-                                      ca.get("base_axis", 1))
+            if n.get("prepared_ws") is not None:  # parameters already in the workspace: one launch
+                y = ops.fused_pw_bn_quant_prepared(i[0], i[1], n["prepared_ws"], True, quant, n["act"], ca.get("base_axis", 1))
+            else:
+                y = ops.fused_pw_bn_quant(i[0], i[1], b, beta, gamma, mean, var, ba.get("eps", 1e-5), quant, n["act"],
+                                          ca.get("base_axis", 1))
         else:
             raise NotImplementedError("operator %r is outside the dwbnq path" % (n["op"],))
         t[n["outputs"][0]] = y
@@ -264,16 +267,60 @@ def execute(nodes, tensors, comm=None, check=False):
     return t
 
 
+def prepare_pointwise(nodes, tensors):
+    """For parameters that stay as they are between runs (inference): returns a copy of the node
+    list in which every FusedPwBnQuant node owns a workspace already filled from its weights,
+    bias and BN vectors (``dwbnq_pwconv_prepare``), so that ``execute`` launches one kernel per
+    such node instead of two. The nodes' inputs must have reached ``tensors`` with their run-time
+    shapes: the graph input and the parameters are enough, shapes follow from the weights."""
+    from . import ops
+    import torch
+
+    out, shape_of = [], {k: tuple(v.shape) for k, v in tensors.items() if v is not None}
+    for n in nodes:
+        n = dict(n)
+        if n["op"] == FUSED_PW:
+            nc, ba, ca = n["n_conv_inputs"], n["bn_args"], n["conv_args"]
+            i = [None] + [tensors[v] if v is not None else None for v in n["inputs"][1:]]  # x: only its shape
+            n_bn = 4 - int(ba.get("no_bias", False)) - int(ba.get("no_scale", False))
+            beta, gamma, mean, var = _bn_inputs(i[nc:nc + n_bn], ba)
+            x_shape = shape_of[n["inputs"][0]]
+            x_like = torch.empty(x_shape, dtype=i[1].dtype, device="meta")
+            n["prepared_ws"] = ops.pwconv_prepare(x_like, i[1], i[2] if nc > 2 else None, beta, gamma, mean, var,
+                                                  ba.get("eps", 1e-5), n["act"], ca.get("base_axis", 1))
+        # output shapes of the operators this library knows, for the nodes further down
+        src = shape_of.get(n["inputs"][0])
+        if src is not None:
+            if n["op"] in (FUSED_PW, "Convolution"):
+                w = shape_of[n["inputs"][1]]
+                a = n.get("conv_args", n.get("args", {}))
+                ax = a.get("base_axis", 1)
+                shape_of[n["outputs"][0]] = src[:ax] + (w[0],) + src[ax + 1:]
+            elif n["op"] in (FUSED, "DepthwiseConvolution"):
+                w = shape_of[n["inputs"][1]]
+                a = n.get("conv_args", n.get("args", {}))
+                ax = a.get("base_axis", 1)
+                pad, stride, dil = (a.get(k) or d for k, d in (("pad", (0, 0)), ("stride", (1, 1)), ("dilation", (1, 1))))
+                sp = tuple((src[ax + 1 + j] + 2 * pad[j] - dil[j] * (w[-len(pad) + j] - 1) - 1) // stride[j] + 1
+                           for j in range(len(pad)))
+                shape_of[n["outputs"][0]] = src[:ax] + (src[ax] * a.get("multiplier", 1),) + sp
+            else:
+                shape_of[n["outputs"][0]] = src
+        out.append(n)
+    return out
+
+
 class GraphRunner:
     """A node list captured once into a CUDA graph and replayed: the host launches one graph
     instead of one kernel per node (what matters at small batches, where the kernels are
     shorter than their launches). The tensors dict passed in is the graph's memory: write new
     inputs into its tensors in place (``copy_``), call ``replay()``, read the outputs from it.
+    Parameters are taken as constant (``prepare_pointwise``) unless ``prepare=False``.
     Nodes that need a communicator are not captured (run them with ``execute``)."""
 
-    def __init__(self, nodes, tensors, warmup=2):
+    def __init__(self, nodes, tensors, warmup=2, prepare=True):
         import torch
-        self.nodes, self.tensors = list(nodes), tensors
+        self.nodes, self.tensors = (prepare_pointwise(nodes, tensors) if prepare else list(nodes)), tensors
         dev = next(t.device for t in tensors.values() if t is not None)
         side = torch.cuda.Stream(dev)
         side.wait_stream(torch.cuda.current_stream(dev))

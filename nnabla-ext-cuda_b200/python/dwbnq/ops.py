@@ -337,7 +337,7 @@ def pwconv_workspace(x, w, base_axis=1):
     """A workspace tensor of the size the pointwise entry points ask for."""
     d, _ = pwconv_desc(x, w, base_axis)
     nbytes = int(L.lib().dwbnq_pwconv_workspace_bytes(ctypes.byref(d)))
-    return torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    return torch.empty(nbytes, dtype=torch.uint8, device=w.device)
 
 
 def pointwise_convolution(x, w, b=None, base_axis=1, math="fp32", ws=None, out=None):

@@ -236,3 +236,59 @@ def make_pointwise_data(spec, n=None, dtype=np.float32):
         x = np.minimum(np.maximum(x, 0.0), 6.0)
     d["x"] = x
     return {k: np.ascontiguousarray(v, dtype=dtype) for k, v in d.items()}
+
+
+def mobilenetv2_body(n=256):
+    """The 50 convolution layers of MobileNetV2's inverted-residual stack in network order:
+    [("dw", LayerSpec) | ("pw", PointwiseSpec), ...] - cfg1's depthwise layers with pw1's
+    projections and expansions between them (residual additions left out: each layer feeds the
+    next). The input is [n, 32, 112, 112], the output [n, 320, 7, 7]."""
+    dws, pws = cfg1(n), pw1(n)
+    order, p = [("dw", dws[0]), ("pw", pws[0])], 1
+    for dw in dws[1:]:
+        order += [("pw", pws[p]), ("dw", dw), ("pw", pws[p + 1])]
+        p += 2
+    assert p == len(pws)
+    for (_, a), (_, b) in zip(order, order[1:]):
+        a_out = (a.c, a.ho) if isinstance(a, LayerSpec) else (a.c_out, a.h)
+        b_in = (b.c, b.h) if isinstance(b, LayerSpec) else (b.c_in, b.h)
+        assert a_out == b_in, (a.name, b.name)
+    return order
+
+
+def body_graph(n=256, dtype=np.float32):
+    """The body as the unfused function list nnabla would build (DepthwiseConvolution |
+    Convolution -> BatchNormalization(batch_stat=False) -> [ReLU6] -> FixedPointQuantize per
+    layer, 166 functions), with its seeded parameters. Returns (nodes, tensors, input name,
+    output name, [name of each layer's output]); ``tensors`` holds the parameters of every
+    layer and the input "x0" (cfg1's first-layer input) as numpy arrays."""
+    nodes, tensors, layer_outputs = [], {}, []
+    order = mobilenetv2_body(n)
+    cur = "x0"
+    tensors[cur] = make_layer_data(order[0][1], n, dtype=dtype)["x"]
+    for li, (kind, spec) in enumerate(order):
+        p = "L%02d" % li
+        data = (make_layer_data(LayerSpec(**dict(spec.__dict__, n=0)), 0, dtype=dtype) if kind == "dw"
+                else make_pointwise_data(PointwiseSpec(**dict(spec.__dict__, n=0)), 0, dtype=dtype))
+        for k_ in ("w", "b", "beta", "gamma", "mean", "var"):
+            tensors["%s.%s" % (p, k_)] = data[k_]
+        if kind == "dw":
+            nodes.append({"op": "DepthwiseConvolution", "inputs": [cur, p + ".w", p + ".b"], "outputs": [p + ".c"],
+                          "args": {"base_axis": 1, "pad": (spec.pad, spec.pad), "stride": (spec.stride, spec.stride),
+                                   "dilation": (1, 1), "multiplier": 1}})
+        else:
+            nodes.append({"op": "Convolution", "inputs": [cur, p + ".w", p + ".b"], "outputs": [p + ".c"],
+                          "args": {"base_axis": 1, "pad": (0, 0), "stride": (1, 1), "dilation": (1, 1), "group": 1}})
+        nodes.append({"op": "BatchNormalization", "inputs": [p + ".c", p + ".beta", p + ".gamma", p + ".mean", p + ".var"],
+                      "outputs": [p + ".bn"], "args": {"axes": [1], "decay_rate": 0.9, "eps": spec.bn_eps,
+                                                       "batch_stat": False}})
+        last = p + ".bn"
+        if kind == "pw" and spec.act == "relu6":
+            nodes.append({"op": "ReLU6", "inputs": [last], "outputs": [p + ".a"], "args": {}})
+            last = p + ".a"
+        q = spec.quant
+        nodes.append({"op": "FixedPointQuantize", "inputs": [last], "outputs": [p + ".q"],
+                      "args": {"sign": q["sign"], "n": q["n"], "delta": q["delta"]}})
+        cur = p + ".q"
+        layer_outputs.append(cur)
+    return nodes, tensors, "x0", cur, layer_outputs
