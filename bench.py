@@ -659,6 +659,46 @@ def other_workloads(torch, ops, workloads, device, cfg1_layers, args):
         tens = [{k: v.half() for k, v in l[2].items()} for l in cfg1_layers]
         timed("cfg4", "f16", 256, specs, tens, flush=False)
         del tens
+        # cfg1q8 = cfg1 with one-byte activations in and out (FixedPointQuantize codes), fp32 parameters
+        in_delta = 2.0 ** -5
+        lay8 = []
+        for sp, _, t, *_ in cfg1_layers:
+            xq = torch.clamp(torch.floor(t["x"] / in_delta + 0.5), 0, 255).to(torch.uint8)
+            y8 = torch.empty((256, sp.c, sp.ho, sp.wo), dtype=torch.uint8, device=device)
+            lay8.append((sp, t, xq, y8, workloads.quant_for_ops(sp, t)))
+
+        def step8():
+            for sp, t, xq, y8, q in lay8:
+                ops.fused_dw_bn_quant_code8(xq, in_delta, t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], sp.bn_eps,
+                                            pad=(sp.pad, sp.pad), stride=(sp.stride, sp.stride), quant=q, out=y8)
+        for _ in range(3):
+            step8()
+        g8 = torch.cuda.CUDAGraph()
+        cap = torch.cuda.Stream(device)
+        cap.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(cap):
+            step8()
+            with torch.cuda.graph(g8, stream=cap):
+                step8()
+        torch.cuda.current_stream(device).wait_stream(cap)
+        for _ in range(3):
+            g8.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(50):
+            g8.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ops.check_device_flag()
+        ms8 = e0.elapsed_time(e1) / 50
+        nb8 = sum(sp.algorithmic_bytes(1, 256) for sp in specs)
+        out.append({"workload": "cfg1q8", "dtype": "f32 arithmetic, u8 storage", "batch": 256, "ms": ms8,
+                    "images_per_s": 256 / (ms8 / 1e3), "gbs": nb8 / ms8 / 1e6, "frac": nb8 / ms8 / 1e6 / peak,
+                    "algorithmic_bytes": nb8, "kernel": "fused_plane_* kernels, 8-bit storage (17 launches)",
+                    "timing": "mean of 50 CUDA-graph replays",
+                    "note": "a quarter of cfg1's bytes: bound by the fp32 arithmetic, not by HBM"})
+        del lay8, g8
     for r in standalone_op_rows(torch, ops, device, 256, False, 3, 10):
         out.append({"workload": "op: " + r["layer"], "dtype": "f32", "batch": 256, "ms": r["ms"],
                     "images_per_s": 256 / (r["ms"] / 1e3), "gbs": r["gbs"], "frac": r["gbs"] / peak,

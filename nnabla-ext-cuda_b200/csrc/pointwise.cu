@@ -49,6 +49,10 @@ constexpr unsigned long long kPwWaitNs = 2000000000ull;
 // with or without ReLU6 in between (after ReLU6 the quantizer's clamps are redundant when its
 // range reaches 6); BN + signed power-of-two FixedPointQuantize (the linear projection of an
 // inverted residual); everything else with run-time switches.
+// How the activations reach shared memory: TMA boxes per image; plain loads with the rows
+// flattened over (image, position), one element or - where the plane size is a multiple of 4
+// and the base aligned - four consecutive positions per load.
+enum PwXMode : int { PW_X_TMA = 0, PW_X_GATHER = 1, PW_X_GATHER4 = 2 };
 enum PwEpi : int { PW_EPI_BIAS = 0, PW_EPI_BN_FPQ = 1, PW_EPI_BN_RELU6_FPQ = 2, PW_EPI_BN_FPQS = 3, PW_EPI_GENERIC = 4 };
 
 // Per pair of output channels, everything the epilogue needs (three 16-byte shared-memory words).
@@ -131,6 +135,14 @@ __device__ __forceinline__ void tc_mma_tf32(unsigned int tmem_d, unsigned long l
       " tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
       "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+// Four consecutive elements as floats (16-byte load of fp32, 8-byte load of fp16).
+__device__ __forceinline__ float4 pw_load4(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
+__device__ __forceinline__ float4 pw_load4(const __half *p) {
+  const uint2 r = __ldg(reinterpret_cast<const uint2 *>(p));
+  const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&r.x));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&r.y));
+  return make_float4(a.x, a.y, b.x, b.y);
 }
 // 8 consecutive accumulator columns of this thread's lane (issue only; tc_ld_wait8 completes it).
 __device__ __forceinline__ void tc_ld8(unsigned int taddr, unsigned int *r) {
@@ -261,10 +273,11 @@ __device__ __forceinline__ void pw_finish_unit(const unsigned int *acc, const Pw
 
 // T: the tensors' element type. fp16 tensors come in through the gather path only and run the single
 // pass: a binary16 value has 11 significant bits, so it is exact in TF32 and so is every product.
-template <typename T, bool GATHER, bool MATH3, int EPI>
+template <typename T, int XMODE, bool MATH3, int EPI>
 __global__ void __launch_bounds__(kPwThreads, 1)
 pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
              const __grid_constant__ CUtensorMap tm_wlo, const PwArgs a) {
+  constexpr bool GATHER = XMODE != PW_X_TMA;  // rows = positions flattened over (image, position)
   extern __shared__ unsigned char pw_smem_raw[];
   // full / empty / split per stage, then accumulator full / empty per buffer
   __shared__ unsigned long long bars[3 * kPwMaxStages + 2 * kPwMaxAcc];
@@ -404,7 +417,90 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
   } else if (warp < kPwFirstEpiWarp) {
     // ---- X workers (eight warps) ----
     const int tid = threadIdx.x - 64;
-    if (GATHER) {
+    if (XMODE == PW_X_GATHER4) {
+      // The gather below with four positions per load. A timeline of the one-element form showed
+      // the eight worker warps, not the MMA thread, setting the pace of the gathered layers (about
+      // 1850 cycles per chunk: 16 loads and 32 stores per thread, each a warp instruction for 128
+      // bytes). Here thread (position group pg, channel lane cw) loads positions 4 pg .. 4 pg + 3 of
+      // channels cw, cw + 8, cw + 16, cw + 24 of the chunk - a warp reads 512 consecutive bytes of one
+      // channel row - and stores each as one 16-byte vector: four consecutive positions are 16
+      // consecutive bytes of the swizzled layout too, and k mod 4 = cw mod 4 for all four channels.
+      // A group of four never straddles two images (the plane size is a multiple of 4).
+      const int pg = tid & 31, cw = tid >> 5;
+      const unsigned int sw4 = (unsigned)((pg >> 3) * 4096 + cw * 128 + (pg & 1) * 16) +
+                               (((((unsigned)pg >> 1) & 3u) ^ ((unsigned)cw & 3u)) << 5);
+      int t_l = blockIdx.x, kc_l = 0;
+      bool valid_l = false;
+      const T *const xbase = static_cast<const T *>(a.x);
+      const T *xp_l = xbase;
+      auto locate = [&]() {
+        const long long g = (long long)(t_l % a.per_ct) * kPwPosTile + 4 * pg;
+        valid_l = g < a.total_pos;
+        const long long n = valid_l ? g / a.HW : 0;
+        xp_l = xbase + (size_t)n * a.Ci * a.HW + (valid_l ? (int)(g - n * a.HW) : 0);
+      };
+      const size_t plane = (size_t)a.HW;
+      auto load = [&](float4(&v)[4]) {
+        const int k0 = kc_l * kPwKChunk + cw;
+        const T *q = xp_l + (size_t)k0 * plane;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const T *qi = q + (size_t)(8 * i) * plane;
+          v[i] = (valid_l && k0 + 8 * i < a.Ci && DWBNQ_IN_BOUNDS((qi + 3) - xbase, a.total_pos * a.Ci, a.flag))
+                     ? pw_load4(qi)
+                     : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+        if (++kc_l == a.kchunks) {
+          kc_l = 0;
+          t_l += gridDim.x;
+          if (t_l < a.total_tiles) locate();
+        }
+      };
+      int s = 0;
+      unsigned int ph = 0;
+      auto store = [&](const float4(&v)[4]) -> bool {
+        if (!pw_wait(&empty[s], ph ^ 1u) || *abort_v) return false;
+        unsigned char *xh = sm + (size_t)s * a.stage_bytes + sw4;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float4 *dst = reinterpret_cast<float4 *>(xh + i * 1024);
+          if (MATH3) {
+            float4 h;
+            h.x = __uint_as_float(__float_as_uint(v[i].x) & 0xffffe000u);
+            h.y = __uint_as_float(__float_as_uint(v[i].y) & 0xffffe000u);
+            h.z = __uint_as_float(__float_as_uint(v[i].z) & 0xffffe000u);
+            h.w = __uint_as_float(__float_as_uint(v[i].w) & 0xffffe000u);
+            *dst = h;
+            *reinterpret_cast<float4 *>(reinterpret_cast<unsigned char *>(dst) + off_xlo) =
+                make_float4(__fsub_rn(v[i].x, h.x), __fsub_rn(v[i].y, h.y), __fsub_rn(v[i].z, h.z), __fsub_rn(v[i].w, h.w));
+          } else {
+            *dst = v[i];
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // visible to the tensor core's reads
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&split[s]);
+        if (++s == a.stages) { s = 0; ph ^= 1u; }
+        return true;
+      };
+      float4 va[4], vb[4];
+      bool ok = true, have_a = t_l < a.total_tiles, have_b = false;
+      if (have_a) {
+        locate();
+        load(va);
+      }
+      while (have_a) {
+        have_b = t_l < a.total_tiles;
+        if (have_b) load(vb);
+        ok = store(va);
+        if (!ok || !have_b) break;
+        have_a = t_l < a.total_tiles;
+        if (have_a) load(va);
+        ok = store(vb);
+        if (!ok) break;
+      }
+      if (!ok && lane == 0 && !*abort_v) { atomicExch(a.flag, 1); *abort_v = 1; }
+    } else if (GATHER) {
       // Plain loads in place of TMA: the 128 rows of a tile are consecutive positions of the
       // batch flattened over (image, position), so a tile may straddle images and no lane is
       // wasted on planes whose size is not a multiple of 128 (or of 4, which TMA needs). Thread
@@ -800,7 +896,7 @@ bool pw_tc_eligible(const dwbnq_pwconv_desc &d, const void *x, const void *w) {
          d.n * hw <= (1LL << 40);
 }
 
-template <typename T, bool GATHER, bool MATH3>
+template <typename T, int GATHER, bool MATH3>
 cudaError_t launch_pw_tc(int epi, dim3 grid, size_t smem, cudaStream_t stream, const CUtensorMap &tx, const CUtensorMap &tw,
                          const CUtensorMap &twl, const PwArgs &a) {
   void (*k)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const PwArgs) =
@@ -940,13 +1036,17 @@ int pwconv_run(const dwbnq_pwconv_desc &d, const dwbnq_quant_desc *q, int has_bn
   a.total_pos = d.n * HW;
   // Gathered when TMA cannot take the plane, or when the per-image tiling would leave more than
   // a tenth of the accumulator rows empty (196 positions fill 1.53 tiles of 128).
+  // four positions per load where every group of four lies in one image and is aligned
+  const bool vec4 = HW % 4 == 0 && ((uintptr_t)x & (d.dtype == DWBNQ_F16 ? 7 : 15)) == 0;
+  bool scalar_gather = !vec4;  // DWBNQ_PW_GATHER=2 forces the one-element gather
   bool gather = d.dtype == DWBNQ_F16 || !pw_tma_x(d, x) || (long long)a.pos_tiles * kPwPosTile * 10 > (long long)HW * 11;
   {
     static const int env = [] {
       const char *e = std::getenv("DWBNQ_PW_GATHER");
-      return e && (e[0] == '0' || e[0] == '1') ? e[0] - '0' : -1;
+      return e && (e[0] == '0' || e[0] == '1' || e[0] == '2') ? e[0] - '0' : -1;
     }();
-    if (env == 1) gather = true;
+    if (env == 1 || env == 2) gather = true;
+    if (env == 2) scalar_gather = true;
     if (env == 0 && pw_tma_x(d, x) && d.dtype == DWBNQ_F32) gather = false;
   }
   {
@@ -1008,11 +1108,15 @@ int pwconv_run(const dwbnq_pwconv_desc &d, const dwbnq_quant_desc *q, int has_bn
   if (t_pw_max_ctas > 0 && grid > t_pw_max_ctas) grid = t_pw_max_ctas;
   const dim3 gd((unsigned)grid);
   const cudaError_t e = d.dtype == DWBNQ_F16
-                            ? launch_pw_tc<__half, true, false>(epi, gd, smem, stream, tx, tw, twl, a)
-                            : gather ? (math3 ? launch_pw_tc<float, true, true>(epi, gd, smem, stream, tx, tw, twl, a)
-                                              : launch_pw_tc<float, true, false>(epi, gd, smem, stream, tx, tw, twl, a))
-                                     : (math3 ? launch_pw_tc<float, false, true>(epi, gd, smem, stream, tx, tw, twl, a)
-                                              : launch_pw_tc<float, false, false>(epi, gd, smem, stream, tx, tw, twl, a));
+                            ? (scalar_gather ? launch_pw_tc<__half, PW_X_GATHER, false>(epi, gd, smem, stream, tx, tw, twl, a)
+                                             : launch_pw_tc<__half, PW_X_GATHER4, false>(epi, gd, smem, stream, tx, tw, twl, a))
+                        : gather && scalar_gather
+                            ? (math3 ? launch_pw_tc<float, PW_X_GATHER, true>(epi, gd, smem, stream, tx, tw, twl, a)
+                                     : launch_pw_tc<float, PW_X_GATHER, false>(epi, gd, smem, stream, tx, tw, twl, a))
+                        : gather ? (math3 ? launch_pw_tc<float, PW_X_GATHER4, true>(epi, gd, smem, stream, tx, tw, twl, a)
+                                          : launch_pw_tc<float, PW_X_GATHER4, false>(epi, gd, smem, stream, tx, tw, twl, a))
+                                 : (math3 ? launch_pw_tc<float, PW_X_TMA, true>(epi, gd, smem, stream, tx, tw, twl, a)
+                                          : launch_pw_tc<float, PW_X_TMA, false>(epi, gd, smem, stream, tx, tw, twl, a));
   if (e != cudaSuccess) return fail_cuda(e, "pw_tc_kernel launch");
   return DWBNQ_OK;
 }
