@@ -69,6 +69,7 @@ struct PwArgs {
   int stages, stage_bytes;
   int nacc;       // accumulator buffers of npad columns in TMEM, a multiple of ngroups
   int ngroups;    // epilogue groups in use (<= kPwEpiGroups): buffer b always belongs to group b % ngroups
+  int col_split;  // 1: every group works on every tile, a quarter of its columns each (few tiles per CTA)
   const float *coef;  // [5][co_tiles * npad]: bias, mean, scale, stdvar, beta
   const void *x;      // gather mode: the activations (fp32 or fp16), read with plain loads
   long long total_pos;  // gather mode: N * HW, the flattened positions
@@ -302,7 +303,7 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
     }
     for (int b = 0; b < a.nacc; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4);  // the four warps of one epilogue group
+      mbar_init(&acc_empty[b], a.col_split ? 4 * kPwEpiGroups : 4);  // the warps that read the buffer
     }
     abort_s = 0;
     unsafe_s = 0;
@@ -622,16 +623,22 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
     // warp (group, quarter) the 32 positions in TMEM lanes [32 quarter, +32) with every column.
     // The buffer count is a multiple of ngroups, so every use of a buffer is awaited by the same
     // group in order: a barrier is never waited on more than one phase ahead (a parity wait
-    // cannot tell phase k from phase k + 2) ----
+    // cannot tell phase k from phase k + 2).
+    // With few tiles per CTA (col_split) that would leave most groups idle and one group alone
+    // with the last tile - 7 us for 160 columns, a seventh of such a launch - so there every group
+    // takes every tile, in order, and a quarter of its column units; all sixteen warps release
+    // the buffer ----
     const int ew = warp - kPwFirstEpiWarp, quarter = warp & 3, group = ew >> 2;
     const f32x2 nz = negzero2();
     const FpqPacked fq = make_fpq_packed(a.q);
     const bool bn_safe = unsafe_s == 0;
-    int b = group;  // tile i of this CTA lives in buffer i mod nacc; the group's tiles are ngroups apart
+    const bool cs = a.col_split != 0;
+    const int b_step = cs ? 1 : a.ngroups;
+    int b = cs ? 0 : group;  // tile i of this CTA lives in buffer i mod nacc; the group's tiles are b_step apart
     unsigned int aph = 0;
-    const long long t_step = (long long)gridDim.x * a.ngroups;
-    for (long long tl = (long long)blockIdx.x + (long long)group * gridDim.x; group < a.ngroups && tl < a.total_tiles;
-         tl += t_step) {
+    const long long t_step = (long long)gridDim.x * b_step;
+    for (long long tl = (long long)blockIdx.x + (cs ? 0LL : (long long)group * gridDim.x);
+         (cs || group < a.ngroups) && tl < a.total_tiles; tl += t_step) {
       const int t = (int)tl;
       const int ct = t / a.per_ct;
       const int r = t - ct * a.per_ct;
@@ -662,11 +669,17 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
       const size_t unit_stride = (size_t)8 * a.HW;
       const PwPair *tp = table + (c_first >> 1);
       if (!DWBNQ_IN_BOUNDS((c_first >> 1) + units * 4 - 1, cpad >> 1, a.flag)) break;
+      int u0 = 0, u1 = units;  // this group's column units
+      if (cs) {
+        const int per_group = (units + kPwEpiGroups - 1) / kPwEpiGroups;
+        u0 = group * per_group < units ? group * per_group : units;
+        u1 = u0 + per_group < units ? u0 + per_group : units;
+      }
       unsigned int acc0[8], acc1[8];
-      tc_ld8(taddr, acc0);
-      for (int u = 0; u < units; u += 2) {
+      if (u0 < u1) tc_ld8(taddr + u0 * 8, acc0);
+      for (int u = u0; u < u1; u += 2) {
         tc_ld_wait8(acc0);
-        if (u + 1 < units) tc_ld8(taddr + (u + 1) * 8, acc1);
+        if (u + 1 < u1) tc_ld8(taddr + (u + 1) * 8, acc1);
         float res[8];
         pw_finish_unit<EPI>(acc0, tp + u * 4, a, nz, fq, bn_safe, res);
         if (p_ok) {
@@ -683,9 +696,9 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
                   q[(unsigned)(i * a.HW)] = Elem<T>::from_f32(res[i]);
           }
         }
-        if (u + 1 < units) {
+        if (u + 1 < u1) {
           tc_ld_wait8(acc1);
-          if (u + 2 < units) tc_ld8(taddr + (u + 2) * 8, acc0);
+          if (u + 2 < u1) tc_ld8(taddr + (u + 2) * 8, acc0);
           pw_finish_unit<EPI>(acc1, tp + (u + 1) * 4, a, nz, fq, bn_safe, res);
           if (p_ok) {
             const int c0 = (u + 1) * 8;
@@ -706,7 +719,7 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[b]);
-      b += a.ngroups;
+      b += b_step;
       if (b >= a.nacc) { b -= a.nacc; aph ^= 1u; }
     }
   }
@@ -1106,6 +1119,8 @@ int pwconv_run(const dwbnq_pwconv_desc &d, const dwbnq_quant_desc *q, int has_bn
   const int sms = sm_count(dev);
   int grid = a.total_tiles < sms ? a.total_tiles : sms;
   if (t_pw_max_ctas > 0 && grid > t_pw_max_ctas) grid = t_pw_max_ctas;
+  // up to six tiles per CTA of at least 64 columns: the groups share each tile's columns
+  a.col_split = g.npad >= 64 && (long long)a.total_tiles <= 6LL * grid;
   const dim3 gd((unsigned)grid);
   const cudaError_t e = d.dtype == DWBNQ_F16
                             ? (scalar_gather ? launch_pw_tc<__half, PW_X_GATHER, false>(epi, gd, smem, stream, tx, tw, twl, a)

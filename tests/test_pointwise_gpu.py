@@ -229,6 +229,30 @@ def test_many_tiles_per_cta(oracle, cuda_device, co, math, plane):
     assert np.array_equal(y.view(np.uint32), want.view(np.uint32))
 
 
+@pytest.mark.parametrize("shape,ctas", [((5, 256, 160, 16, 16), 2), ((3, 64, 96, 14, 14), 1), ((2, 960, 160, 7, 7), 0),
+                                        ((6, 40, 200, 8, 16), 1), ((4, 320, 72, 12, 12), 1)],
+                         ids=lambda v: "x".join(map(str, v)) if isinstance(v, tuple) else "ctas%d" % v)
+def test_few_tiles_per_cta_share_the_columns(oracle, cuda_device, shape, ctas):
+    """At most six tiles per CTA and 64 or more columns per tile: the four epilogue groups split every
+    tile's column units (20, 12, 16 + 9, 9 units: even and ragged quarters, a group without any)
+    and walk through the accumulator buffers together, more tiles than buffers (phases wrap)."""
+    rng = np.random.default_rng(sum(shape))
+    d = make(rng, *shape)
+    t = {k: dev(v, cuda_device) for k, v in d.items()}
+    try:
+        ops.set_pw_max_ctas(ctas)
+        for math in ("fp32", "tf32"):
+            conv = ops.pointwise_convolution(t["x"], t["w"], t["b"], math=math).cpu().numpy()
+            y = ops.fused_pw_bn_quant(t["x"], t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], 1e-5, FPQ_S, None,
+                                      math=math).cpu().numpy()
+            ops.check_device_flag()
+            check_conv(oracle, conv, d, conv_tolerance(1, math, shape[1]))
+            want = oracle.pw_epilogue(conv, d["beta"], d["gamma"], d["mean"], d["var"], 1e-5, None, FPQ_S)
+            assert np.array_equal(y.view(np.uint32), want.view(np.uint32)), math
+    finally:
+        ops.set_pw_max_ctas(0)
+
+
 @pytest.mark.parametrize("shape", [(3, 32, 96, 28, 28), (4, 384, 64, 14, 14), (5, 160, 200, 7, 7), (2, 30, 50, 5, 9)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_prepared_workspace_gives_the_same_result(oracle, cuda_device, shape):
