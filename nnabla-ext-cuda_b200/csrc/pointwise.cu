@@ -315,19 +315,14 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  __syncthreads();
-  {
-    bool all_safe = true;
-    for (int i = threadIdx.x; i < (cpad >> 1); i += kPwThreads) {
-      bool safe;
-      table[i] = pw_make_pair(a, cpad, 2 * i, &safe);
-      all_safe = all_safe && safe;
-    }
-    if (!all_safe) atomicOr(&unsafe_s, 1);
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // Launched with programmatic stream serialization: up to here (no global access) the CTA may
+  // run while its predecessor in the stream drains; everything below follows the predecessor's
+  // completion. The successor may become resident as soon as this grid's CTAs leave their SMs.
+  pdl_launch_dependents();
+  pdl_wait_for_predecessor();
   const unsigned int tmem_base = tmem_base_s;
   volatile int *abort_v = &abort_s;
 
@@ -629,6 +624,18 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
     // takes every tile, in order, and a quarter of its column units; all sixteen warps release
     // the buffer ----
     const int ew = warp - kPwFirstEpiWarp, quarter = warp & 3, group = ew >> 2;
+    {
+      // the coefficient table is the epilogue's alone: its sixteen warps build it while the loads
+      // and the first MMAs are already under way, and meet at a barrier of their own
+      bool all_safe = true;
+      for (int i = threadIdx.x - 32 * kPwFirstEpiWarp; i < (cpad >> 1); i += 32 * kPwEpiWarps) {
+        bool safe;
+        table[i] = pw_make_pair(a, cpad, 2 * i, &safe);
+        all_safe = all_safe && safe;
+      }
+      if (!all_safe) atomicOr(&unsafe_s, 1);
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * kPwEpiWarps) : "memory");
+    }
     const f32x2 nz = negzero2();
     const FpqPacked fq = make_fpq_packed(a.q);
     const bool bn_safe = unsafe_s == 0;
@@ -928,8 +935,7 @@ cudaError_t launch_pw_tc(int epi, dim3 grid, size_t smem, cudaStream_t stream, c
     attr_done[epi] = (const void *)k;
     attr_dev[epi] = dev + 1;
   }
-  k<<<grid, kPwThreads, smem, stream>>>(tx, tw, twl, a);
-  return cudaGetLastError();
+  return launch_pdl(k, grid, dim3(kPwThreads), smem, stream, tx, tw, twl, a);
 }
 
 // Which kernel and which arithmetic a descriptor gets: the same answer at preparation and at
