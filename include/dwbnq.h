@@ -363,7 +363,9 @@ int dwbnq_pwconv_fused_fwd(const dwbnq_pwconv_desc *desc, float bn_eps, const dw
  * (bias, mean, gamma, sqrt(var + eps), beta) and the fp32 weights or their TF32 halves - once,
  * the way the reference's function objects do their one-time work in setup_impl;
  * dwbnq_pwconv_fused_fwd_prepared then runs the layer on that workspace with one kernel launch
- * and reads neither w nor the vectors. `desc` must be the same in both calls; has_bn states
+ * and reads neither w nor the vectors. `desc` must be the same in both calls except for n, h
+ * and w: the workspace depends on dtype, c_in, c_out, math and act only, so one prepared
+ * workspace serves every batch size and plane size. has_bn states
  * whether dwbnq_pwconv_prepare was given bn_mean / bn_var. Results are identical to
  * dwbnq_pwconv_fused_fwd, which is these two calls in sequence. */
 int dwbnq_pwconv_prepare(const dwbnq_pwconv_desc *desc, float bn_eps, const void *w, const void *b,

@@ -70,7 +70,8 @@ struct PwArgs {
   int nacc;       // accumulator buffers of npad columns in TMEM, a multiple of ngroups
   int ngroups;    // epilogue groups in use (<= kPwEpiGroups): buffer b always belongs to group b % ngroups
   int col_split;  // 1: every group works on every tile, a quarter of its columns each (few tiles per CTA)
-  const float *coef;  // [5][co_tiles * npad]: bias, mean, scale, stdvar, beta
+  const float *coef;  // [5][cstride]: bias, mean, scale, stdvar, beta
+  int cstride;        // >= co_tiles * npad
   const void *x;      // gather mode: the activations (fp32 or fp16), read with plain loads
   long long total_pos;  // gather mode: N * HW, the flattened positions
   void *y;            // fp32 or fp16 like x
@@ -630,7 +631,7 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
       bool all_safe = true;
       for (int i = threadIdx.x - 32 * kPwFirstEpiWarp; i < (cpad >> 1); i += 32 * kPwEpiWarps) {
         bool safe;
-        table[i] = pw_make_pair(a, cpad, 2 * i, &safe);
+        table[i] = pw_make_pair(a, a.cstride, 2 * i, &safe);
         all_safe = all_safe && safe;
       }
       if (!all_safe) atomicOr(&unsafe_s, 1);
@@ -875,20 +876,42 @@ inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 struct PwGeom {
   int npad, co_tiles, cpad;
 };
-PwGeom pw_geom(int Co, int Ci) {
-  // Channel tiles of at most 128 columns: four accumulator buffers then fit in TMEM, which keeps
-  // all four epilogue groups busy (a 256-column tile leaves room for two). With a long sum
-  // (c_in >= 256) the MMA thread is the busy one - an MMA costs it the same ~30 ns whether it is
-  // 32 or 128 columns wide, and every chunk of every tile a commit - so the tiles go up to 256
-  // columns there. The tiles are equal, rounded up to the 32 columns the epilogue's units and
-  // the MMA shape want.
+// Equal channel tiles of at most `widest` columns, rounded up to the 32 columns the epilogue's
+// units and the MMA shape want.
+PwGeom pw_tiles(int Co, int widest) {
   PwGeom g;
-  const int widest = Ci >= 256 ? kPwMaxCoTile : 128;
   const int tiles = (Co + widest - 1) / widest;
   g.npad = ((Co + tiles - 1) / tiles + 31) / 32 * 32;
   g.co_tiles = (Co + g.npad - 1) / g.npad;
   g.cpad = g.co_tiles * g.npad;
   return g;
+}
+// Stride of the coefficient vectors in the workspace: covers either tiling, depends on c_out alone
+// (a workspace prepared once serves every batch size).
+int pw_coef_stride(int Co) {
+  const int a = pw_tiles(Co, 128).cpad, b = pw_tiles(Co, kPwMaxCoTile).cpad;
+  return a > b ? a : b;
+}
+// Channel tiles of up to 128 or up to 256 columns, whichever the launch finishes sooner with.
+// A tile costs the longer of its sum (every chunk of 32 input channels about 1850 cycles of loads,
+// splits and MMAs - wider tiles do that work for fewer tiles) and its epilogue (about 500 cycles
+// per unit of 8 valid columns with all sixteen warps busy); the launch takes as many rounds of
+// tiles as the SMs need for all of them. Measured on the layers of MobileNetV2 at 256 images:
+// 160 -> 960 on 7x7 1.26x and 96 -> 576 on 14x14 1.21x with 240 / 192 columns, 64 -> 384 on
+// 14x14 0.95x with 192 (six rounds of 24 units against eight of 16) - the estimate ranks all three.
+// Ties go to the wide tile for long sums (c_in >= 256), else to the narrow one.
+PwGeom pw_geom(int Co, int Ci, long long total_pos, int sms) {
+  const PwGeom narrow = pw_tiles(Co, 128), wide = pw_tiles(Co, kPwMaxCoTile);
+  if (narrow.npad == wide.npad) return narrow;
+  const long long pos_tiles = (total_pos + kPwPosTile - 1) / kPwPosTile;
+  const long long kloop = (long long)((Ci + kPwKChunk - 1) / kPwKChunk) * 1850;
+  auto cost = [&](const PwGeom &g) {
+    const long long rounds = (g.co_tiles * pos_tiles + sms - 1) / sms;
+    const long long epi = (long long)((Co + g.co_tiles - 1) / g.co_tiles + 7) / 8 * 500;
+    return rounds * (kloop > epi ? kloop : epi);
+  };
+  const long long cn = cost(narrow), cw = cost(wide);
+  return (Ci >= 256 ? cw <= cn : cw * 100 < cn * 97) ? wide : narrow;
 }
 
 int validate_pw(const dwbnq_pwconv_desc *d) {
@@ -959,10 +982,9 @@ struct PwWorkspace {
   float *coef, *w_a, *w_b;  // coefficients; fp32 weights (or their TF32 high halves); the low halves
 };
 PwWorkspace pw_workspace(const dwbnq_pwconv_desc &d, void *workspace) {
-  const PwGeom g = pw_geom(d.c_out, d.c_in);
   PwWorkspace w;
   w.coef = static_cast<float *>(workspace);
-  w.w_a = reinterpret_cast<float *>(static_cast<char *>(workspace) + align256((size_t)5 * g.cpad * 4));
+  w.w_a = reinterpret_cast<float *>(static_cast<char *>(workspace) + align256((size_t)5 * pw_coef_stride(d.c_out) * 4));
   w.w_b = reinterpret_cast<float *>(reinterpret_cast<char *>(w.w_a) + align256((size_t)d.c_in * d.c_out * 4));
   return w;
 }
@@ -979,21 +1001,21 @@ int pwconv_prepare(const dwbnq_pwconv_desc &d, float bn_eps, const void *w, cons
   int st;
   const PwMode m = pw_mode(d, reinterpret_cast<const void *>(16), &st);  // the arithmetic does not depend on x
   if (st != DWBNQ_OK) return st;
-  const PwGeom g = pw_geom(d.c_out, d.c_in);
+  const int cstride = pw_coef_stride(d.c_out);
   const PwWorkspace ws = pw_workspace(d, workspace);
   const long long wsize = (long long)d.c_in * d.c_out;
-  const long long work = wsize > g.cpad ? wsize : g.cpad;
+  const long long work = wsize > cstride ? wsize : cstride;
   const unsigned blocks = (unsigned)((work + 255) / 256);
   if (d.dtype == DWBNQ_F32)
     pw_prepare_kernel<float><<<blocks, 256, 0, stream>>>(
         static_cast<const float *>(w), static_cast<const float *>(b), static_cast<const float *>(beta),
         static_cast<const float *>(gamma), static_cast<const float *>(mean), static_cast<const float *>(var), bn_eps,
-        d.c_out, g.cpad, wsize, ws.coef, ws.w_a, m.math3 ? ws.w_b : nullptr);
+        d.c_out, cstride, wsize, ws.coef, ws.w_a, m.math3 ? ws.w_b : nullptr);
   else
     pw_prepare_kernel<__half><<<blocks, 256, 0, stream>>>(
         static_cast<const __half *>(w), static_cast<const __half *>(b), static_cast<const __half *>(beta),
         static_cast<const __half *>(gamma), static_cast<const __half *>(mean), static_cast<const __half *>(var), bn_eps,
-        d.c_out, g.cpad, wsize, ws.coef, ws.w_a, nullptr);
+        d.c_out, cstride, wsize, ws.coef, ws.w_a, nullptr);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail_cuda(e, "pw_prepare_kernel launch");
   return DWBNQ_OK;
@@ -1017,8 +1039,8 @@ int pwconv_run(const dwbnq_pwconv_desc &d, const dwbnq_quant_desc *q, int has_bn
   else if (kind == DWBNQ_Q_POW2) st = fill_pow2(&qa, q->sign, q->with_zero, q->n, q->m, dev);
   if (st != DWBNQ_OK) return st;
 
-  const PwGeom g = pw_geom(d.c_out, d.c_in);
   const int HW = d.h * d.w;
+  const PwGeom g = pw_geom(d.c_out, d.c_in, d.n * HW, sm_count(dev));
   const PwWorkspace wsp = pw_workspace(d, workspace);
   float *coef = wsp.coef, *w_hi = wsp.w_a, *w_lo = wsp.w_b;
   const PwMode mode = pw_mode(d, x, &st);
@@ -1030,7 +1052,7 @@ int pwconv_run(const dwbnq_pwconv_desc &d, const dwbnq_quant_desc *q, int has_bn
     PwSimtArgs a;
     std::memset(&a, 0, sizeof(a));
     a.x = x; a.w = w_hi; a.y = y; a.coef = coef;
-    a.HW = HW; a.Ci = d.c_in; a.Co = d.c_out; a.cpad = g.cpad;
+    a.HW = HW; a.Ci = d.c_in; a.Co = d.c_out; a.cpad = pw_coef_stride(d.c_out);
     a.pos_tiles = (HW + 63) / 64;
     a.has_bn = mean != nullptr; a.act = d.act; a.qkind = kind; a.q = qa;
     st = device_flag_ptr(dev, &a.flag);
@@ -1086,6 +1108,7 @@ int pwconv_run(const dwbnq_pwconv_desc &d, const dwbnq_quant_desc *q, int has_bn
   if (a.stages > kPwMaxStages) a.stages = kPwMaxStages;
   if (a.stages < 2) return fail(DWBNQ_ERR_UNSUPPORTED, "pipeline stage of %d bytes does not fit twice", a.stage_bytes);
   a.coef = coef;
+  a.cstride = pw_coef_stride(d.c_out);
   a.y = y;
   st = device_flag_ptr(dev, &a.flag);
   if (st != DWBNQ_OK) return st;
@@ -1125,8 +1148,9 @@ int pwconv_run(const dwbnq_pwconv_desc &d, const dwbnq_quant_desc *q, int has_bn
   const int sms = sm_count(dev);
   int grid = a.total_tiles < sms ? a.total_tiles : sms;
   if (t_pw_max_ctas > 0 && grid > t_pw_max_ctas) grid = t_pw_max_ctas;
-  // up to six tiles per CTA of at least 64 columns: the groups share each tile's columns
-  a.col_split = g.npad >= 64 && (long long)a.total_tiles <= 6LL * grid;
+  // tiles of at least 64 columns, up to six per CTA or too wide for four accumulator buffers (a group
+  // per buffer would leave groups idle): the groups share each tile's columns
+  a.col_split = g.npad >= 64 && ((long long)a.total_tiles <= 6LL * grid || a.ngroups < kPwEpiGroups);
   const dim3 gd((unsigned)grid);
   const cudaError_t e = d.dtype == DWBNQ_F16
                             ? (scalar_gather ? launch_pw_tc<__half, PW_X_GATHER, false>(epi, gd, smem, stream, tx, tw, twl, a)
@@ -1152,8 +1176,7 @@ int launch_pwconv(const dwbnq_pwconv_desc &d, float bn_eps, const dwbnq_quant_de
 }
 
 size_t pwconv_workspace_bytes(const dwbnq_pwconv_desc &d) {
-  const PwGeom g = pw_geom(d.c_out, d.c_in);
-  return align256((size_t)5 * g.cpad * 4) + 2 * align256((size_t)d.c_in * d.c_out * 4);
+  return align256((size_t)5 * pw_coef_stride(d.c_out) * 4) + 2 * align256((size_t)d.c_in * d.c_out * 4);
 }
 int pwconv_validate(const dwbnq_pwconv_desc *d) { return validate_pw(d); }
 int pwconv_path(const dwbnq_pwconv_desc &d, const void *x, const void *w) {

@@ -258,10 +258,15 @@ def test_pointwise_descriptor_validation_workspace_and_plan(dwlib):
     good = P(dtype=dwlib.F32, c_in=32, c_out=96, h=14, w=14, n=4, math=dwlib.PW_MATH_FP32, act=dwlib.ACT_RELU6)
     # coefficients of the 96 channels (one tile of 96 columns) + the two TF32 halves of w
     assert lib.dwbnq_pwconv_workspace_bytes(ctypes.byref(good)) == 2048 + 2 * 32 * 96 * 4
-    wide = P(dtype=dwlib.F32, c_in=8, c_out=300, h=2, w=2, n=1)  # three tiles of 128 columns (100 -> 128)
+    # the coefficient stride covers both tilings of 300 channels (three tiles of 128 columns, two of 160)
+    # and depends on c_out alone: a workspace prepared once serves every batch size and either tiling
+    wide = P(dtype=dwlib.F32, c_in=8, c_out=300, h=2, w=2, n=1)
     assert lib.dwbnq_pwconv_workspace_bytes(ctypes.byref(wide)) == 5 * 384 * 4 + 2 * ((8 * 300 * 4 + 255) // 256 * 256)
-    deep = P(dtype=dwlib.F32, c_in=512, c_out=300, h=2, w=2, n=1)  # a long sum: two tiles of 160 columns (150 -> 160)
-    assert lib.dwbnq_pwconv_workspace_bytes(ctypes.byref(deep)) == 5 * 320 * 4 + 2 * 512 * 300 * 4
+    deep = P(dtype=dwlib.F32, c_in=512, c_out=300, h=2, w=2, n=1)
+    assert lib.dwbnq_pwconv_workspace_bytes(ctypes.byref(deep)) == 5 * 384 * 4 + 2 * 512 * 300 * 4
+    for n in (1, 7, 256, 100000):
+        again = P(dtype=dwlib.F32, c_in=512, c_out=300, h=14, w=14, n=n)
+        assert lib.dwbnq_pwconv_workspace_bytes(ctypes.byref(again)) == 5 * 384 * 4 + 2 * 512 * 300 * 4
     fake, path = ctypes.c_void_p(4096), ctypes.c_int(-1)
     assert lib.dwbnq_pwconv_plan(ctypes.byref(good), fake, fake, ctypes.byref(path)) == dwlib.OK and path.value == 1
     half = P(dtype=dwlib.F16, c_in=32, c_out=96, h=14, w=14, n=4)  # fp16 tensors: gathered, one exact TF32 pass

@@ -229,6 +229,29 @@ def test_many_tiles_per_cta(oracle, cuda_device, co, math, plane):
     assert np.array_equal(y.view(np.uint32), want.view(np.uint32))
 
 
+def test_one_prepared_workspace_serves_every_batch_size(oracle, cuda_device):
+    """The channel tiling is chosen per launch (160 -> 960 on 7x7: eight tiles of 128 columns for two
+    images, four of 240 for 256 images); the workspace does not depend on it: prepared once, used at
+    both batch sizes, bit-identical to the one-call form, and the small batch checked against the oracle."""
+    rng = np.random.default_rng(77)
+    d = make(rng, 256, 160, 960, 7, 7)
+    t = {k: dev(v, cuda_device) for k, v in d.items()}
+    small = t["x"][:2].contiguous()
+    ws = ops.pwconv_prepare(small, t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], 1e-5, act="relu6")
+    for x in (small, t["x"]):
+        got = ops.fused_pw_bn_quant_prepared(x, t["w"], ws, True, FPQ_U, "relu6")
+        want = ops.fused_pw_bn_quant(x, t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], 1e-5, FPQ_U, "relu6")
+        torch.cuda.synchronize()
+        ops.check_device_flag()
+        assert torch.equal(got.view(torch.int32), want.view(torch.int32)), tuple(x.shape)
+    for x in (small, t["x"][:40].contiguous()):
+        conv = ops.pointwise_convolution(x, t["w"], t["b"]).cpu().numpy()
+        check_conv(oracle, conv, dict(d, x=x.cpu().numpy()), conv_tolerance(1, "fp32", 160))
+        y = ops.fused_pw_bn_quant_prepared(x, t["w"], ws, True, FPQ_U, "relu6").cpu().numpy()
+        want = oracle.pw_epilogue(conv, d["beta"], d["gamma"], d["mean"], d["var"], 1e-5, "relu6", FPQ_U)
+        assert np.array_equal(y.view(np.uint32), want.view(np.uint32))
+
+
 @pytest.mark.parametrize("shape,ctas", [((5, 256, 160, 16, 16), 2), ((3, 64, 96, 14, 14), 1), ((2, 960, 160, 7, 7), 0),
                                         ((6, 40, 200, 8, 16), 1), ((4, 320, 72, 12, 12), 1)],
                          ids=lambda v: "x".join(map(str, v)) if isinstance(v, tuple) else "ctas%d" % v)
