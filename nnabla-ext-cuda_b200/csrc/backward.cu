@@ -324,6 +324,115 @@ __global__ void __launch_bounds__(kThreads, K == 3 ? 4 : 2)
   }
 }
 
+// 3 x 3, stride 1, pad 1 (the output plane is the input plane's size; any multiplier): the common
+// layer, with a register window in place of nine loads per output. A lane owns four output columns
+// of a band of rows and slides three rows of the six input columns under them down the band: per
+// row one 16-byte load of x (plus the two neighbours), one of dy, 36 fused multiply-adds onto the
+// nine sums. Lanes = (band, column block): 14 blocks x 2 bands on a 56-wide plane, 7 x 4 on 28,
+// 4 x 8 on 14. VEC: rows are 16-byte aligned (W a multiple of 4, aligned tensors); otherwise the
+// same window from single loads, the last block's missing columns read as zero. A warp per image,
+// CTAs = (channel, slice of the batch), reduction and atomics as in the kernel above.
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads, 4) dwconv_bwd_weights_rows_kernel(const BwdArgs a, const int slices) {
+  __shared__ float red[kThreads / 32][10];
+  const float *x = static_cast<const float *>(a.x);
+  const float *dy = static_cast<const float *>(a.dy);
+  pdl_launch_dependents();
+  pdl_wait_for_predecessor();
+  const int oc = blockIdx.x / slices;
+  const int slice = blockIdx.x % slices;
+  const int ic = oc / a.mult;
+  const int H = a.H, W = a.W, plane = H * W;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long per = (a.n + slices - 1) / slices;
+  const long long n0 = (long long)slice * per;
+  const long long n1 = n0 + per < a.n ? n0 + per : a.n;
+  const int ncb = (W + 3) >> 2;
+  int bands = ncb >= 32 ? 1 : 32 / ncb;
+  if (bands > H) bands = H;
+  const int rows_per_band = (H + bands - 1) / bands;
+  const int items = ncb * bands;
+  float acc[9];
+#pragma unroll
+  for (int i = 0; i < 9; ++i) acc[i] = 0.0f;
+  float bsum = 0.0f;
+  for (long long n = n0 + warp; n < n1; n += kThreads / 32) {
+    const float *dyp = dy + (n * a.OC + oc) * plane;
+    const float *xp = x + (n * a.C + ic) * plane;
+    for (int item = lane; item < items; item += 32) {
+      const int band = item / ncb, c0 = (item - band * ncb) * 4;
+      const int r0 = band * rows_per_band;
+      const int r1 = r0 + rows_per_band < H ? r0 + rows_per_band : H;
+      // input columns c0 - 1 .. c0 + 4 of row iy; zero outside the plane
+      auto load_row = [&](int iy, float(&r)[6]) {
+        if ((unsigned int)iy >= (unsigned int)H) {
+#pragma unroll
+          for (int j = 0; j < 6; ++j) r[j] = 0.0f;
+          return;
+        }
+        const float *p = xp + iy * W + c0;
+        if (VEC) {
+          const float4 v = __ldg(reinterpret_cast<const float4 *>(p));
+          r[1] = v.x; r[2] = v.y; r[3] = v.z; r[4] = v.w;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) r[1 + j] = c0 + j < W ? __ldg(p + j) : 0.0f;
+        }
+        r[0] = c0 > 0 ? __ldg(p - 1) : 0.0f;
+        r[5] = c0 + 4 < W ? __ldg(p + 4) : 0.0f;
+      };
+      float top[6], mid[6], bot[6];
+      load_row(r0 - 1, top);
+      load_row(r0, mid);
+      for (int oy = r0; oy < r1; ++oy) {
+        load_row(oy + 1, bot);
+        float g[4];
+        const float *q = dyp + oy * W + c0;
+        if (VEC) {
+          const float4 v = __ldg(reinterpret_cast<const float4 *>(q));
+          g[0] = v.x; g[1] = v.y; g[2] = v.z; g[3] = v.w;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) g[j] = c0 + j < W ? __ldg(q + j) : 0.0f;
+        }
+        bsum += (g[0] + g[1]) + (g[2] + g[3]);
+#pragma unroll
+        for (int kx = 0; kx < 3; ++kx) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[kx] = fmaf(top[j + kx], g[j], acc[kx]);
+            acc[3 + kx] = fmaf(mid[j + kx], g[j], acc[3 + kx]);
+            acc[6 + kx] = fmaf(bot[j + kx], g[j], acc[6 + kx]);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 6; ++j) {
+          top[j] = mid[j];
+          mid[j] = bot[j];
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i <= 9; ++i) {
+    float v = i < 9 ? acc[i < 9 ? i : 0] : bsum;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) red[warp][i] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x <= 9) {
+    float v = 0.0f;
+#pragma unroll
+    for (int wv = 0; wv < kThreads / 32; ++wv) v += red[wv][threadIdx.x];
+    if (threadIdx.x < 9) {
+      if (a.dw) atomicAdd(static_cast<float *>(a.dw) + (long long)oc * 9 + threadIdx.x, v);
+    } else if (a.db) {
+      atomicAdd(static_cast<float *>(a.db) + oc, v);
+    }
+  }
+}
+
 // Any kernel size: one CTA per weight value (and one more per channel for the bias), the
 // reference's own decomposition. Slow path for kernels other than 3x3 and 5x5.
 template <typename T>
@@ -490,13 +599,34 @@ int launch_dwconv_backward(const dwbnq_conv_desc &d, int ho, int wo, const void 
                       (d.stride_h == 1 || d.stride_h == 2) && d.dil_h == 1 && d.dil_w == 1 &&
                       (long long)d.h * d.w < 0x40000000LL && d.n > 0;
     if (fast) {
-      // enough CTAs for eight per SM; a slice is at least one image
-      long long slices = ((long long)sm_count(-1) * 8 + a.OC - 1) / a.OC;
-      if (slices > (d.n + 7) / 8) slices = (d.n + 7) / 8;  // a warp per image: eight images keep a CTA's warps busy
-      if (slices < 1) slices = 1;
+      // A CTA is (channel, slice of the batch), a warp per image. The slice count is the one whose
+      // CTAs fill whole waves of the resident slots (four CTAs per SM) and whose images fill whole
+      // rounds of a CTA's eight warps: the product of the two fill ratios, searched over the
+      // counts that leave every warp about a thousand outputs or more - below that the CTA's
+      // reduction and atomics outweigh its sums (fewest slices on ties).
+      long long slices = 1;
+      {
+        const long long slots = (long long)sm_count(-1) * 4, warps = kThreads / 32;
+        double best = -1.0;
+        const long long most = d.n < 2048 ? d.n : 2048;
+        const long long plane_out = (long long)ho * wo;
+        const long long min_per = warps * (plane_out >= 1024 ? 1 : (1024 + plane_out - 1) / plane_out);
+        for (long long s = 1; s <= most; ++s) {
+          const long long per = (d.n + s - 1) / s;       // images of a full slice
+          if (s > 1 && per < min_per) break;
+          const long long busy = (d.n + per - 1) / per;  // slices that have images
+          const long long ctas = busy * a.OC, waves = (ctas + slots - 1) / slots;
+          const double fill = (double)ctas / (double)(waves * slots) * (double)per / (double)((per + warps - 1) / warps * warps);
+          if (fill > best + 1e-9) { best = fill; slices = s; }
+        }
+      }
       const dim3 grid((unsigned int)(a.OC * slices)), block(kThreads);
       const int key = d.kh * 10 + d.stride_h;
-      if (key == 31) e = launch_pdl(dwconv_bwd_weights_kernel<float, 3, 1>, grid, block, 0, stream, a, (int)slices);
+      const bool same_size = key == 31 && d.pad_h == 1 && d.pad_w == 1;
+      const bool rows16 = d.w % 4 == 0 && (((uintptr_t)x | (uintptr_t)dy) & 15) == 0;
+      if (same_size && rows16) e = launch_pdl(dwconv_bwd_weights_rows_kernel<true>, grid, block, 0, stream, a, (int)slices);
+      else if (same_size) e = launch_pdl(dwconv_bwd_weights_rows_kernel<false>, grid, block, 0, stream, a, (int)slices);
+      else if (key == 31) e = launch_pdl(dwconv_bwd_weights_kernel<float, 3, 1>, grid, block, 0, stream, a, (int)slices);
       else if (key == 32) e = launch_pdl(dwconv_bwd_weights_kernel<float, 3, 2>, grid, block, 0, stream, a, (int)slices);
       else if (key == 51) e = launch_pdl(dwconv_bwd_weights_kernel<float, 5, 1>, grid, block, 0, stream, a, (int)slices);
       else e = launch_pdl(dwconv_bwd_weights_kernel<float, 5, 2>, grid, block, 0, stream, a, (int)slices);

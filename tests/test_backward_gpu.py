@@ -98,7 +98,11 @@ def test_pow2_quantize_backward(oracle, cuda_device, fine):
 GEOMS = [  # n, c, h, w, k, stride, pad, dil, mult
     (3, 8, 14, 14, 3, 1, 1, 1, 1), (2, 6, 28, 28, 3, 2, 1, 1, 1), (2, 5, 15, 9, 5, 1, 2, 1, 1),
     (2, 4, 16, 16, 5, 2, 2, 1, 1), (2, 3, 12, 13, 3, 1, 2, 2, 2), (1, 4, 10, 10, 4, 3, 1, 1, 1),
-    (2, 3, 9, 9, 2, 2, 0, 1, 3)]
+    (2, 3, 9, 9, 2, 2, 0, 1, 3),
+    # 3x3 stride 1 pad 1: the register-window weight-gradient kernel, 16-byte rows and not, one band and
+    # several, more column blocks than lanes, a plane smaller than a block, a multiplier
+    (2, 5, 12, 16, 3, 1, 1, 1, 1), (2, 3, 9, 40, 3, 1, 1, 1, 2), (1, 2, 5, 132, 3, 1, 1, 1, 1), (3, 2, 3, 3, 3, 1, 1, 1, 1),
+    (2, 4, 7, 7, 3, 1, 1, 1, 1), (9, 2, 28, 28, 3, 1, 1, 1, 1), (2, 2, 1, 6, 3, 1, 1, 1, 1)]
 
 
 @pytest.mark.parametrize("geom", GEOMS, ids=lambda g: "x".join(str(v) for v in g))
@@ -140,7 +144,7 @@ def test_depthwise_convolution_backward(oracle, cuda_device, geom):
 def test_depthwise_convolution_backward_cfg1_layer_sizes(oracle, cuda_device):
     """Two layer shapes of the MobileNetV2 stack at 16 images: many slices per channel."""
     rng = np.random.default_rng(5)
-    for c, hw, s in ((96, 112, 2), (384, 14, 1)):
+    for c, hw, s in ((96, 112, 2), (384, 14, 1), (144, 56, 1)):
         x = rng.standard_normal((16, c, hw, hw)).astype(np.float32)
         w = (rng.standard_normal((c, 3, 3)) / 3).astype(np.float32)
         ho = oracle.conv_out_size(hw, 3, s, 1)
