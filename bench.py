@@ -532,8 +532,10 @@ def pointwise_rows(torch, ops, workloads, device, batch, peak):
         yh = torch.empty((batch, spec.c_out, spec.h, spec.h), dtype=torch.float16, device=device)
         ops.pwconv_prepare(th["x"], th["w"], th["b"], th["beta"], th["gamma"], th["mean"], th["var"], spec.bn_eps,
                            act=spec.act, ws=ws)
-        half_ms += median_ms(lambda: ops.fused_pw_bn_quant_prepared(th["x"], th["w"], ws, True, spec.quant, spec.act, out=yh),
-                             reps=7, graph=True)
+        ms16 = median_ms(lambda: ops.fused_pw_bn_quant_prepared(th["x"], th["w"], ws, True, spec.quant, spec.act, out=yh),
+                         reps=7, graph=True)
+        half_ms += ms16
+        rows[-1]["ms_f16"] = ms16
         del th, yh
         # library baseline: the convolution as cuDNN runs it in fp32 (TF32 off, as the reference
         # defaults), then BN, activation and quantizer as the separate passes the reference makes
