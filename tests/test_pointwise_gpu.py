@@ -334,3 +334,33 @@ def test_mobilenet_layers_at_eight_images(oracle, cuda_device, layer):
                               nthreads=oracle.max_threads())
     assert np.array_equal(y.cpu().numpy().view(np.uint32), want.view(np.uint32))
     ops.check_device_flag()
+
+
+@pytest.mark.parametrize("index", [1, 4, 14, 21, 27, 28, 32], ids=lambda i: "pw1.l%02d" % i)
+def test_full_size_layers_of_the_bench_workload(oracle, cuda_device, index):
+    """The bench's own layers at its own batch (256 images: the tile widths, the shared-column
+    epilogue and the number of tiles per CTA are chosen from the batch, so small batches take other
+    routes): sampled images of the convolution against the oracle within the stated tolerance, and
+    the whole fused output bit for bit against the library's standalone BatchNormalization ->
+    ReLU6 -> FixedPointQuantize (each bit-exact against the oracle in its own tests) applied to
+    the convolution the same kernel returns unfused."""
+    from dwbnq import workloads
+    spec = workloads.pw1(256)[index]
+    d = workloads.make_pointwise_data(spec)
+    t = {k: dev(v, cuda_device) for k, v in d.items()}
+    conv = ops.pointwise_convolution(t["x"], t["w"], t["b"])
+    y = ops.fused_pw_bn_quant(t["x"], t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], spec.bn_eps, spec.quant,
+                              spec.act)
+    torch.cuda.synchronize()
+    ops.check_device_flag()
+    pick = [0, 1, 127, 255]
+    sub = dict(d, x=np.ascontiguousarray(d["x"][pick]))
+    check_conv(oracle, conv[pick].cpu().numpy(), sub, conv_tolerance(1, "fp32", spec.c_in))
+    chain = ops.batch_normalization(conv, t["beta"], t["gamma"], t["mean"], t["var"], eps=spec.bn_eps, batch_stat=False)
+    if spec.act == "relu6":
+        chain = chain.clamp(0.0, 6.0)
+    q = spec.quant
+    chain = ops.fixed_point_quantize(chain, q["sign"], q["n"], q["delta"])
+    assert torch.equal(y.view(torch.int32), chain.view(torch.int32))
+    want = oracle.pw_epilogue(conv[pick].cpu().numpy(), d["beta"], d["gamma"], d["mean"], d["var"], spec.bn_eps, spec.act, q)
+    assert np.array_equal(y[pick].cpu().numpy().view(np.uint32), want.view(np.uint32))
