@@ -36,6 +36,13 @@ int dwbnq_set_forced_pw_path(int path);
  * SM): with a few CTAs a small tensor already makes every CTA walk through many tiles, which
  * is what exercises the reuse of pipeline stages and accumulator buffers. */
 int dwbnq_set_pw_max_ctas(int ctas);
+/* Host only: the launch shape the tcgen05 pointwise kernel would get for `desc` with activations
+ * at `x` (only its alignment is looked at) on a device of `sms` SMs. out8 receives: columns per
+ * channel tile, channel tiles, activation path (0 = TMA boxes, 1 = one-element gather, 2 =
+ * four-position gather), tiles, CTAs, pipeline stages, accumulator buffers in tensor memory, and
+ * whether the epilogue groups share each tile's columns. DWBNQ_ERR_UNSUPPORTED for a descriptor
+ * that goes to the plain FMA kernel. */
+int dwbnq_debug_pwconv_tiling(const dwbnq_pwconv_desc *desc, const void *x, int sms, int *out8);
 /* Launches one warp that waits, with the bounded wait every copy-engine kernel of the
  * library uses, on a shared-memory barrier that nothing ever completes, with the limit
  * shortened to `limit_us` microseconds. The wait runs out, the kernel records it in the

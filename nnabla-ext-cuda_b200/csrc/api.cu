@@ -292,6 +292,15 @@ int dwbnq_pwconv_plan(const dwbnq_pwconv_desc *desc, const void *x, const void *
   return DWBNQ_OK;
 }
 
+int dwbnq_debug_pwconv_tiling(const dwbnq_pwconv_desc *desc, const void *x, int sms, int *out8) {
+  clear_error();
+  int st = pwconv_validate(desc);
+  if (st != DWBNQ_OK) return st;
+  if (!out8) return fail(DWBNQ_ERR_INVALID_ARG, "out8 is null");
+  if (sms <= 0) return fail(DWBNQ_ERR_INVALID_ARG, "sms %d is not positive", sms);
+  return pwconv_tiling(*desc, x, sms, out8);
+}
+
 int dwbnq_set_forced_pw_path(int path) {
   clear_error();
   if (path < -1 || path > 1) return fail(DWBNQ_ERR_INVALID_ARG, "pointwise path %d is not -1, 0 or 1", path);

@@ -136,6 +136,10 @@ int pwconv_validate(const dwbnq_pwconv_desc *d);
 size_t pwconv_workspace_bytes(const dwbnq_pwconv_desc &d);
 // 1 = the tcgen05 kernel, 0 = the plain FMA kernel (thread's forced choice included).
 int pwconv_path(const dwbnq_pwconv_desc &d, const void *x, const void *w);
+// Launch shape of the tcgen05 kernel for a descriptor on a device of `sms` SMs (diagnostic):
+// columns per channel tile, channel tiles, activation path (0 TMA, 1 one-element gather, 2
+// four-position gather), tiles, CTAs, pipeline stages, accumulator buffers, shared-column epilogue.
+int pwconv_tiling(const dwbnq_pwconv_desc &d, const void *x, int sms, int out[8]);
 void set_forced_pw_path(int p);
 void set_pw_max_ctas(int n);
 // The two halves of launch_pwconv: fill the workspace from the parameters; run on a filled one.

@@ -897,7 +897,7 @@ int pw_coef_stride(int Co) {
 // splits and MMAs - wider tiles do that work for fewer tiles) and its epilogue (about 500 cycles
 // per unit of 8 valid columns with all sixteen warps busy); the launch takes as many rounds of
 // tiles as the SMs need for all of them. Measured on the layers of MobileNetV2 at 256 images:
-// 160 -> 960 on 7x7 1.26x and 96 -> 576 on 14x14 1.21x with 240 / 192 columns, 64 -> 384 on
+// 160 -> 960 on 7x7 1.26x and 96 -> 576 on 14x14 1.21x with 256 (240 used) / 192 columns, 64 -> 384 on
 // 14x14 0.95x with 192 (six rounds of 24 units against eight of 16) - the estimate ranks all three.
 // Ties go to the wide tile for long sums (c_in >= 256), else to the narrow one.
 PwGeom pw_geom(int Co, int Ci, long long total_pos, int sms) {
@@ -978,6 +978,66 @@ PwMode pw_mode(const dwbnq_pwconv_desc &d, const void *x, int *status) {
   return m;
 }
 
+// Everything about a launch of the tcgen05 kernel that follows from the descriptor, the
+// alignment of x, the arithmetic and the device's SM count (max_ctas > 0 caps the grid: a test hook).
+struct PwShape {
+  PwGeom g;
+  int xmode;       // PwXMode
+  int pos_tiles, kchunks, per_ct, total_tiles;
+  int stage_bytes, table_bytes, stages;
+  int ngroups, nacc, grid, col_split;
+};
+int pw_shape(const dwbnq_pwconv_desc &d, const void *x, bool math3, int sms, int max_ctas, PwShape *out) {
+  PwShape s;
+  std::memset(&s, 0, sizeof(s));
+  const int HW = d.h * d.w;
+  const long long total_pos = d.n * HW;
+  s.g = pw_geom(d.c_out, d.c_in, total_pos, sms);
+  s.pos_tiles = (HW + kPwPosTile - 1) / kPwPosTile;
+  s.kchunks = (d.c_in + kPwKChunk - 1) / kPwKChunk;
+  // Gathered when TMA cannot take the plane, or when the per-image tiling would leave more than
+  // a tenth of the accumulator rows empty (196 positions fill 1.53 tiles of 128); four positions
+  // per load where every group of four lies in one image and is aligned.
+  const bool vec4 = HW % 4 == 0 && ((uintptr_t)x & (d.dtype == DWBNQ_F16 ? 7 : 15)) == 0;
+  bool scalar_gather = !vec4;
+  bool gather = d.dtype == DWBNQ_F16 || !pw_tma_x(d, x) || (long long)s.pos_tiles * kPwPosTile * 10 > (long long)HW * 11;
+  {
+    // DWBNQ_PW_GATHER: 0 = TMA wherever it can be used, 1 = always gather, 2 = the one-element gather
+    static const int env = [] {
+      const char *e = std::getenv("DWBNQ_PW_GATHER");
+      return e && (e[0] == '0' || e[0] == '1' || e[0] == '2') ? e[0] - '0' : -1;
+    }();
+    if (env == 1 || env == 2) gather = true;
+    if (env == 2) scalar_gather = true;
+    if (env == 0 && pw_tma_x(d, x) && d.dtype == DWBNQ_F32) gather = false;
+  }
+  s.xmode = !gather ? PW_X_TMA : scalar_gather ? PW_X_GATHER : PW_X_GATHER4;
+  {
+    const long long per_ct = gather ? (total_pos + kPwPosTile - 1) / kPwPosTile : d.n * s.pos_tiles;
+    const long long total = (long long)s.g.co_tiles * per_ct;
+    if (total > 0x7fffffffLL) return fail(DWBNQ_ERR_UNSUPPORTED, "more than 2^31 - 1 tiles");
+    s.total_tiles = (int)total;
+    s.per_ct = (int)per_ct;
+  }
+  s.stage_bytes = (kPwXBytes + s.g.npad * 128) * (math3 ? 2 : 1);
+  s.table_bytes = (s.g.cpad / 2) * (int)sizeof(PwPair);
+  {
+    const int fit = kPwTmemCols / s.g.npad < kPwMaxAcc ? kPwTmemCols / s.g.npad : kPwMaxAcc;
+    s.ngroups = fit < kPwEpiGroups ? fit : kPwEpiGroups;
+    s.nacc = fit / s.ngroups * s.ngroups;
+  }
+  s.stages = (kPwSmemMax - 1024 - s.table_bytes) / s.stage_bytes;
+  if (s.stages > kPwMaxStages) s.stages = kPwMaxStages;
+  if (s.stages < 2) return fail(DWBNQ_ERR_UNSUPPORTED, "pipeline stage of %d bytes does not fit twice", s.stage_bytes);
+  s.grid = s.total_tiles < sms ? s.total_tiles : sms;
+  if (max_ctas > 0 && s.grid > max_ctas) s.grid = max_ctas;
+  // tiles of at least 64 columns, up to six per CTA or too wide for four accumulator buffers (a group
+  // per buffer would leave groups idle): the groups share each tile's columns
+  s.col_split = s.g.npad >= 64 && ((long long)s.total_tiles <= 6LL * s.grid || s.ngroups < kPwEpiGroups);
+  *out = s;
+  return DWBNQ_OK;
+}
+
 struct PwWorkspace {
   float *coef, *w_a, *w_b;  // coefficients; fp32 weights (or their TF32 high halves); the low halves
 };
@@ -1040,7 +1100,6 @@ int pwconv_run(const dwbnq_pwconv_desc &d, const dwbnq_quant_desc *q, int has_bn
   if (st != DWBNQ_OK) return st;
 
   const int HW = d.h * d.w;
-  const PwGeom g = pw_geom(d.c_out, d.c_in, d.n * HW, sm_count(dev));
   const PwWorkspace wsp = pw_workspace(d, workspace);
   float *coef = wsp.coef, *w_hi = wsp.w_a, *w_lo = wsp.w_b;
   const PwMode mode = pw_mode(d, x, &st);
@@ -1067,46 +1126,27 @@ int pwconv_run(const dwbnq_pwconv_desc &d, const dwbnq_quant_desc *q, int has_bn
     return DWBNQ_OK;
   }
 
+  PwShape sh;
+  st = pw_shape(d, x, math3, sm_count(dev), t_pw_max_ctas, &sh);
+  if (st != DWBNQ_OK) return st;
+  const PwGeom g = sh.g;
+  const bool gather = sh.xmode != PW_X_TMA, scalar_gather = sh.xmode == PW_X_GATHER;
   PwArgs a;
   std::memset(&a, 0, sizeof(a));
   a.HW = HW; a.Ci = d.c_in; a.Co = d.c_out; a.N = d.n;
   a.npad = g.npad; a.co_tiles = g.co_tiles;
-  a.pos_tiles = (HW + kPwPosTile - 1) / kPwPosTile;
-  a.kchunks = (d.c_in + kPwKChunk - 1) / kPwKChunk;
+  a.pos_tiles = sh.pos_tiles;
+  a.kchunks = sh.kchunks;
   a.x = x;
   a.total_pos = d.n * HW;
-  // Gathered when TMA cannot take the plane, or when the per-image tiling would leave more than
-  // a tenth of the accumulator rows empty (196 positions fill 1.53 tiles of 128).
-  // four positions per load where every group of four lies in one image and is aligned
-  const bool vec4 = HW % 4 == 0 && ((uintptr_t)x & (d.dtype == DWBNQ_F16 ? 7 : 15)) == 0;
-  bool scalar_gather = !vec4;  // DWBNQ_PW_GATHER=2 forces the one-element gather
-  bool gather = d.dtype == DWBNQ_F16 || !pw_tma_x(d, x) || (long long)a.pos_tiles * kPwPosTile * 10 > (long long)HW * 11;
-  {
-    static const int env = [] {
-      const char *e = std::getenv("DWBNQ_PW_GATHER");
-      return e && (e[0] == '0' || e[0] == '1' || e[0] == '2') ? e[0] - '0' : -1;
-    }();
-    if (env == 1 || env == 2) gather = true;
-    if (env == 2) scalar_gather = true;
-    if (env == 0 && pw_tma_x(d, x) && d.dtype == DWBNQ_F32) gather = false;
-  }
-  {
-    const long long per_ct = gather ? (a.total_pos + kPwPosTile - 1) / kPwPosTile : d.n * a.pos_tiles;
-    const long long total = (long long)a.co_tiles * per_ct;
-    if (total > 0x7fffffffLL) return fail(DWBNQ_ERR_UNSUPPORTED, "more than 2^31 - 1 tiles");
-    a.total_tiles = (int)total;
-    a.per_ct = (int)per_ct;
-  }
-  a.stage_bytes = (kPwXBytes + g.npad * 128) * (math3 ? 2 : 1);
-  const int table_bytes = (g.cpad / 2) * (int)sizeof(PwPair);
-  {
-    const int fit = kPwTmemCols / g.npad < kPwMaxAcc ? kPwTmemCols / g.npad : kPwMaxAcc;
-    a.ngroups = fit < kPwEpiGroups ? fit : kPwEpiGroups;
-    a.nacc = fit / a.ngroups * a.ngroups;
-  }
-  a.stages = (kPwSmemMax - 1024 - table_bytes) / a.stage_bytes;
-  if (a.stages > kPwMaxStages) a.stages = kPwMaxStages;
-  if (a.stages < 2) return fail(DWBNQ_ERR_UNSUPPORTED, "pipeline stage of %d bytes does not fit twice", a.stage_bytes);
+  a.total_tiles = sh.total_tiles;
+  a.per_ct = sh.per_ct;
+  a.stage_bytes = sh.stage_bytes;
+  const int table_bytes = sh.table_bytes;
+  a.ngroups = sh.ngroups;
+  a.nacc = sh.nacc;
+  a.stages = sh.stages;
+  a.col_split = sh.col_split;
   a.coef = coef;
   a.cstride = pw_coef_stride(d.c_out);
   a.y = y;
@@ -1145,13 +1185,7 @@ int pwconv_run(const dwbnq_pwconv_desc &d, const dwbnq_quant_desc *q, int has_bn
   // quantizer's own clamps change nothing
   else if (a.has_bn && fpq_u && d.act == DWBNQ_ACT_RELU6 && qa.fpq_max >= 6.0f) epi = PW_EPI_BN_RELU6_FPQ;
   const size_t smem = (size_t)a.stages * a.stage_bytes + table_bytes + 1024;
-  const int sms = sm_count(dev);
-  int grid = a.total_tiles < sms ? a.total_tiles : sms;
-  if (t_pw_max_ctas > 0 && grid > t_pw_max_ctas) grid = t_pw_max_ctas;
-  // tiles of at least 64 columns, up to six per CTA or too wide for four accumulator buffers (a group
-  // per buffer would leave groups idle): the groups share each tile's columns
-  a.col_split = g.npad >= 64 && ((long long)a.total_tiles <= 6LL * grid || a.ngroups < kPwEpiGroups);
-  const dim3 gd((unsigned)grid);
+  const dim3 gd((unsigned)sh.grid);
   const cudaError_t e = d.dtype == DWBNQ_F16
                             ? (scalar_gather ? launch_pw_tc<__half, PW_X_GATHER, false>(epi, gd, smem, stream, tx, tw, twl, a)
                                              : launch_pw_tc<__half, PW_X_GATHER4, false>(epi, gd, smem, stream, tx, tw, twl, a))
@@ -1183,6 +1217,18 @@ int pwconv_path(const dwbnq_pwconv_desc &d, const void *x, const void *w) {
   const int forced = forced_pw_path();
   (void)w;
   return forced == 0 ? 0 : (pw_tc_eligible(d, x, nullptr) ? 1 : 0);
+}
+int pwconv_tiling(const dwbnq_pwconv_desc &d, const void *x, int sms, int out[8]) {
+  int st;
+  const PwMode m = pw_mode(d, x, &st);
+  if (st != DWBNQ_OK) return st;
+  if (!m.tc) return fail(DWBNQ_ERR_UNSUPPORTED, "the descriptor goes to the plain FMA kernel, which has no tiling to report");
+  PwShape s;
+  st = pw_shape(d, x, m.math3, sms, t_pw_max_ctas, &s);
+  if (st != DWBNQ_OK) return st;
+  out[0] = s.g.npad; out[1] = s.g.co_tiles; out[2] = s.xmode; out[3] = s.total_tiles;
+  out[4] = s.grid; out[5] = s.stages; out[6] = s.nacc; out[7] = s.col_split;
+  return DWBNQ_OK;
 }
 void set_forced_pw_path(int p) { t_forced_pw = p; }
 void set_pw_max_ctas(int n) { t_pw_max_ctas = n; }

@@ -101,6 +101,7 @@ SIGNATURES = {
     "dwbnq_pwconv_plan": (_int, [_P(PwConvDesc), _vp, _vp, _P(_int)]),
     "dwbnq_set_forced_pw_path": (_int, [_int]),
     "dwbnq_set_pw_max_ctas": (_int, [_int]),
+    "dwbnq_debug_pwconv_tiling": (_int, [ctypes.POINTER(PwConvDesc), _vp, _int, ctypes.POINTER(_int)]),
     "dwbnq_fused_plan": (_int, [_P(ConvDesc), _vp, _vp, _P(_int), _P(_int), _P(_int), _P(_int),
                                 _P(_i64), _P(_int)]),
     "dwbnq_set_forced_path": (_int, [_int]),

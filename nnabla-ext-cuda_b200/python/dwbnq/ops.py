@@ -396,6 +396,14 @@ def pwconv_plan(x, w, base_axis=1, math="fp32"):
     return path.value
 
 
+def pwconv_tiling(desc, x_address=4096, sms=148):
+    """Launch shape of the tcgen05 pointwise kernel for a PwConvDesc (host only, diagnostic)."""
+    out = (ctypes.c_int * 8)()
+    L.check(L.lib().dwbnq_debug_pwconv_tiling(ctypes.byref(desc), ctypes.c_void_p(x_address), int(sms), out))
+    keys = ("columns", "channel_tiles", "x_path", "tiles", "ctas", "stages", "accumulators", "shared_columns")
+    return dict(zip(keys, list(out)))
+
+
 def set_forced_pw_path(path):
     L.check(L.lib().dwbnq_set_forced_pw_path(int(path)))
 

@@ -36,7 +36,7 @@ int main(void) {
   int32_t ho, wo;
   float a, b, c;
   static uint32_t table[277];
-  int path, ppc, rpt, thr, smem, i;
+  int path, ppc, rpt, thr, smem, i, shape[8];
   int64_t ctas;
 
   EXPECT(dwbnq_version() == DWBNQ_ABI_VERSION);
@@ -171,12 +171,27 @@ int main(void) {
     EXPECT(dwbnq_pwconv_prepare(&e, 1e-5f, fake, NULL, NULL, NULL, NULL, NULL, fake, -1, NULL) != DWBNQ_OK);
     EXPECT(dwbnq_pwconv_fused_fwd_prepared(&e, &q, 0, fake, fake, fake, -1, NULL) != DWBNQ_OK);
     EXPECT(dwbnq_pwconv_plan(&e, fake, fake, &path) != DWBNQ_OK);
+    EXPECT(dwbnq_debug_pwconv_tiling(&e, fake, 148, shape) != DWBNQ_OK);
   }
   for (p.c_out = 1; p.c_out <= 2100; p.c_out += 37)
     for (p.c_in = 4; p.c_in <= 1100; p.c_in += 132) {
       EXPECT(dwbnq_pwconv_workspace_bytes(&p) >= (size_t)(5 * p.c_out + 2 * p.c_in * p.c_out) * 4);
       EXPECT(dwbnq_pwconv_plan(&p, (char *)fake + 4, fake, &path) == DWBNQ_OK && path == 1);
+      for (p.n = 1; p.n <= 4096; p.n *= 8) { /* launch shapes over batch sizes and SM counts (host only) */
+        int sms;
+        for (sms = 1; sms <= 148; sms += 49) {
+          const int st = dwbnq_debug_pwconv_tiling(&p, (char *)fake + (p.n & 4), sms, shape);
+          EXPECT(st == DWBNQ_OK ? (shape[0] % 32 == 0 && shape[0] <= 256 && shape[0] * shape[1] >= p.c_out && shape[3] >= 1 &&
+                                   shape[4] >= 1 && shape[4] <= sms && shape[5] >= 2 && shape[5] <= 8 &&
+                                   shape[6] * shape[0] <= 512 && shape[6] >= 1)
+                                : IS_STATUS(st));
+        }
+      }
+      p.n = 4;
     }
+  EXPECT(dwbnq_debug_pwconv_tiling(NULL, fake, 148, shape) != DWBNQ_OK);
+  EXPECT(dwbnq_debug_pwconv_tiling(&p, fake, 0, shape) != DWBNQ_OK);
+  EXPECT(dwbnq_debug_pwconv_tiling(&p, fake, 148, NULL) != DWBNQ_OK);
   EXPECT(dwbnq_set_forced_pw_path(3) != DWBNQ_OK && dwbnq_set_forced_pw_path(-1) == DWBNQ_OK);
   EXPECT(dwbnq_set_pw_max_ctas(-1) != DWBNQ_OK && dwbnq_set_pw_max_ctas(0) == DWBNQ_OK);
   puts("pointwise");

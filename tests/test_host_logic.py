@@ -292,3 +292,38 @@ def test_pointwise_descriptor_validation_workspace_and_plan(dwlib):
     if lib.dwbnq_device_count() == 0:  # no CPU fallback
         ok = P(dtype=dwlib.F32, c_in=32, c_out=96, h=14, w=14, n=4)
         assert lib.dwbnq_pwconv_fwd(ctypes.byref(ok), fake, fake, None, fake, fake, -1, None) == dwlib.ERR_CUDA
+
+
+def test_pointwise_launch_shapes_of_the_mobilenet_layers(dwlib):
+    """The host-side choices behind a pointwise launch, read back through the debug entry (no device):
+    activation path, channel-tile width by the duration estimate, shared-column epilogue."""
+    from dwbnq import ops, workloads
+    P = dwlib.PwConvDesc
+    shape = {}
+    for sp in workloads.pw1(256):
+        d = P(dtype=dwlib.F32, c_in=sp.c_in, c_out=sp.c_out, h=sp.h, w=sp.h, n=256, math=dwlib.PW_MATH_FP32, act=dwlib.ACT_NONE)
+        shape[(sp.c_in, sp.c_out, sp.h)] = ops.pwconv_tiling(d)
+    TMA, ONE, FOUR = 0, 1, 2
+    for (ci, co, h), s in shape.items():
+        assert s["x_path"] == (TMA if h in (112, 56) else ONE if h == 7 else FOUR), (ci, co, h, s)
+        assert s["columns"] % 32 == 0 and s["columns"] * s["channel_tiles"] >= co and 2 <= s["stages"] <= 8
+        assert s["ctas"] == min(148, s["tiles"]) and s["accumulators"] * s["columns"] <= 512
+    # tile widths the estimate picks at this batch (measured: 1.26x, 1.21x, 0.95x - kept narrow - for the three)
+    assert shape[(160, 960, 7)]["columns"] == 256 and shape[(160, 960, 7)]["shared_columns"] == 1
+    assert shape[(96, 576, 14)]["columns"] == 192 and shape[(96, 576, 14)]["shared_columns"] == 1
+    assert shape[(64, 384, 14)]["columns"] == 128 and shape[(64, 384, 14)]["shared_columns"] == 0
+    assert shape[(960, 160, 7)]["columns"] == 160 and shape[(960, 160, 7)]["tiles"] == 98
+    assert shape[(960, 160, 7)]["shared_columns"] == 1           # one tile per CTA
+    assert shape[(16, 96, 112)]["shared_columns"] == 0 and shape[(16, 96, 112)]["accumulators"] == 4
+    assert shape[(384, 64, 14)]["shared_columns"] == 1 and shape[(384, 64, 14)]["tiles"] == 392
+    # the same layer at two images: narrow tiles again (eight of 128 columns), whatever was prepared
+    small = P(dtype=dwlib.F32, c_in=160, c_out=960, h=7, w=7, n=2, math=dwlib.PW_MATH_FP32)
+    assert ops.pwconv_tiling(small)["columns"] == 128
+    # fp16 tensors are gathered everywhere; an unaligned x or a plane that is no multiple of 4 takes one element per load
+    half = P(dtype=dwlib.F16, c_in=32, c_out=96, h=56, w=56, n=8)
+    assert ops.pwconv_tiling(half)["x_path"] == FOUR and ops.pwconv_tiling(half, x_address=4100)["x_path"] == ONE
+    odd = P(dtype=dwlib.F32, c_in=32, c_out=96, h=56, w=56, n=8)
+    assert ops.pwconv_tiling(odd)["x_path"] == TMA and ops.pwconv_tiling(odd, x_address=4100)["x_path"] == ONE
+    # a descriptor for the FMA kernel has no tiling
+    with pytest.raises(dwlib.DwbnqError):
+        ops.pwconv_tiling(P(dtype=dwlib.F32, c_in=30, c_out=96, h=14, w=14, n=4))

@@ -231,7 +231,7 @@ def test_many_tiles_per_cta(oracle, cuda_device, co, math, plane):
 
 def test_one_prepared_workspace_serves_every_batch_size(oracle, cuda_device):
     """The channel tiling is chosen per launch (160 -> 960 on 7x7: eight tiles of 128 columns for two
-    images, four of 240 for 256 images); the workspace does not depend on it: prepared once, used at
+    images, four of 256 - 240 used - for 256 images); the workspace does not depend on it: prepared once, used at
     both batch sizes, bit-identical to the one-call form, and the small batch checked against the oracle."""
     rng = np.random.default_rng(77)
     d = make(rng, 256, 160, 960, 7, 7)
