@@ -146,6 +146,15 @@ __device__ __forceinline__ float4 pw_load4(const __half *p) {
   const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&r.y));
   return make_float4(a.x, a.y, b.x, b.y);
 }
+// D[128 x N] (+)= A[128 x 16] * B[N x 16]^T, binary16 operands, fp32 accumulator.
+__device__ __forceinline__ void tc_mma_f16(unsigned int tmem_d, unsigned long long da, unsigned long long db,
+                                           unsigned int idesc, unsigned int accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // 8 consecutive accumulator columns of this thread's lane (issue only; tc_ld_wait8 completes it).
 __device__ __forceinline__ void tc_ld8(unsigned int taddr, unsigned int *r) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
@@ -176,6 +185,15 @@ __device__ __forceinline__ unsigned long long pw_smem_desc(unsigned int addr, un
 // two groups of 4 channels one MMA consumes 512 bytes (stride offset).
 __device__ __forceinline__ unsigned long long pw_desc_a(unsigned int buf, int kstep) {
   return pw_smem_desc(buf + kstep * 1024, 4096, 512, 1);
+}
+// A for binary16 tensors (kind::f16, 16 channels per MMA): two TMA boxes of [64 channels][64
+// positions] binary16 per stage (128-byte rows in the ordinary 128-byte swizzle, layout type 2):
+// the two groups of 64 positions are 8192 bytes apart (leading offset), groups of 8 channels 1024
+// bytes (stride offset); a step of 16 channels advances the start by 2048 bytes. (Found with a
+// probe over descriptor fields against a CPU product; the weights' [N][64] box takes the same
+// descriptor as the fp32 one, its 16-channel step being 32 bytes too.)
+__device__ __forceinline__ unsigned long long pw_desc_a16(unsigned int buf, int kstep) {
+  return pw_smem_desc(buf + kstep * 2048, 8192, 1024, 2);
 }
 // B: N channels-out x 8 channels-in of a stage's weight buffer, one TMA box of [N][32] fp32
 // (128-byte rows, 16-byte units swizzled by row mod 8): groups of 8 rows are 1024 bytes apart,
@@ -280,6 +298,9 @@ __global__ void __launch_bounds__(kPwThreads, 1)
 pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
              const __grid_constant__ CUtensorMap tm_wlo, const PwArgs a) {
   constexpr bool GATHER = XMODE != PW_X_TMA;  // rows = positions flattened over (image, position)
+  // binary16 tensors through TMA: operands stay binary16 (kind::f16), 64 channels per stage, no X workers
+  constexpr bool F16MMA = XMODE == PW_X_TMA && sizeof(T) == 2;
+  constexpr int KCHUNK = F16MMA ? 64 : kPwKChunk;
   extern __shared__ unsigned char pw_smem_raw[];
   // full / empty / split per stage, then accumulator full / empty per buffer
   __shared__ unsigned long long bars[3 * kPwMaxStages + 2 * kPwMaxAcc];
@@ -346,12 +367,15 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
           if (!pw_wait_lane(&empty[s], ph ^ 1u) || *abort_v) { ok = false; break; }
           unsigned char *st = sm + (size_t)s * a.stage_bytes;
           mbar_expect_tx(&full[s], bytes);
-          if (!GATHER) {
+          if (F16MMA) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) tma_load_3d(st + q * 4096, &tm_x, p0 + q * 32, kc * kPwKChunk, n, &full[s]);
+            for (int q = 0; q < 2; ++q) tma_load_3d(st + q * 8192, &tm_x, p0 + q * 64, kc * KCHUNK, n, &full[s]);
+          } else if (!GATHER) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) tma_load_3d(st + q * 4096, &tm_x, p0 + q * 32, kc * KCHUNK, n, &full[s]);
           }
-          tma_load_2d(st + off_w, &tm_w, kc * kPwKChunk, c0, &full[s]);
-          if (MATH3) tma_load_2d(st + off_wlo, &tm_wlo, kc * kPwKChunk, c0, &full[s]);
+          tma_load_2d(st + off_w, &tm_w, kc * KCHUNK, c0, &full[s]);
+          if (MATH3) tma_load_2d(st + off_wlo, &tm_wlo, kc * KCHUNK, c0, &full[s]);
           if (++s == a.stages) { s = 0; ph ^= 1u; }
         }
       }
@@ -365,11 +389,14 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
     // 2^18), and stages / buffers advance with counters ----
     if (lane == 0) {
       // instruction descriptor: fp32 accumulator, TF32 A and B, A MN-major, B K-major, N, M = 128
-      const unsigned int idesc = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | ((unsigned)(a.npad >> 3) << 17) | (8u << 24);
-      const unsigned long long da0 = pw_desc_a(base, 0), dal0 = pw_desc_a(base + off_xlo, 0);
+      // (binary16 operands: formats 0, 16 channels per instruction)
+      const unsigned int idesc = (1u << 4) | (F16MMA ? 0u : (2u << 7) | (2u << 10)) | (1u << 15) |
+                                 ((unsigned)(a.npad >> 3) << 17) | (8u << 24);
+      const unsigned long long da0 = F16MMA ? pw_desc_a16(base, 0) : pw_desc_a(base, 0), dal0 = pw_desc_a(base + off_xlo, 0);
       const unsigned long long db0 = pw_desc_b(base + off_w, 0), dbl0 = pw_desc_b(base + off_wlo, 0);
       const unsigned long long stage_step = (unsigned long long)(a.stage_bytes >> 4);
-      const int last_steps = ((a.Ci - (a.kchunks - 1) * kPwKChunk) + 7) >> 3;  // rows past c_in are zero-filled
+      constexpr int KSTEP = F16MMA ? 16 : 8;  // channels per MMA
+      const int last_steps = ((a.Ci - (a.kchunks - 1) * KCHUNK) + KSTEP - 1) / KSTEP;  // rows past c_in are zero-filled
       int s = 0, b = 0;
       unsigned int ph = 0, aph = 0;
       unsigned long long so = 0;  // s * stage_step
@@ -387,19 +414,20 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
           if (ok && !r2) ok = pw_wait_lane(&split[s], ph);
           if (!ok) break;
           tc_fence_after();
-          const int ksteps = kc == a.kchunks - 1 ? last_steps : kPwKChunk / 8;
+          const int ksteps = kc == a.kchunks - 1 ? last_steps : KCHUNK / KSTEP;
           unsigned long long da = da0 + so, db = db0 + so, dal = dal0 + so, dbl = dbl0 + so;
           unsigned int acc = kc ? 1u : 0u;
 #pragma unroll 1
           for (int j = 0; j < ksteps; ++j) {
-            tc_mma_tf32(d, da, db, idesc, acc);
+            if (F16MMA) tc_mma_f16(d, da, db, idesc, acc);
+            else tc_mma_tf32(d, da, db, idesc, acc);
             if (MATH3) {
               tc_mma_tf32(d, dal, db, idesc, 1u);
               tc_mma_tf32(d, da, dbl, idesc, 1u);
             }
             acc = 1u;
-            da += 64; dal += 64;  // 8 rows of 128 bytes
-            db += 2; dbl += 2;    // 32 bytes along the row
+            da += F16MMA ? 128 : 64; dal += 64;  // 8 rows of 128 bytes (binary16: 16 rows)
+            db += 2; dbl += 2;                   // 32 bytes along the row
           }
           tc_commit(&empty[s]);
           if (kc == a.kchunks - 1) tc_commit(&acc_full[b]);
@@ -742,7 +770,8 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
 
 template <typename T>
 __global__ void pw_prepare_kernel(const T *w, const T *b, const T *beta, const T *gamma, const T *mean, const T *var,
-                                  float eps, int Co, int cpad, long long wsize, float *coef, float *w_hi, float *w_lo) {
+                                  float eps, int Co, int cpad, long long wsize, float *coef, float *w_hi, float *w_lo,
+                                  T *w_same) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < cpad) {
     const bool in = i < Co;
@@ -755,6 +784,7 @@ __global__ void pw_prepare_kernel(const T *w, const T *b, const T *beta, const T
   }
   if (i < wsize) {
     const float v = Elem<T>::to_f32(w[i]);
+    if (w_same) w_same[i] = w[i];  // binary16 tensors: the weights as they are, for the kind::f16 path
     if (w_lo) {  // the two TF32 halves
       const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
       w_hi[i] = h;
@@ -1000,7 +1030,13 @@ int pw_shape(const dwbnq_pwconv_desc &d, const void *x, bool math3, int sms, int
   // per load where every group of four lies in one image and is aligned.
   const bool vec4 = HW % 4 == 0 && ((uintptr_t)x & (d.dtype == DWBNQ_F16 ? 7 : 15)) == 0;
   bool scalar_gather = !vec4;
-  bool gather = d.dtype == DWBNQ_F16 || !pw_tma_x(d, x) || (long long)s.pos_tiles * kPwPosTile * 10 > (long long)HW * 11;
+  bool gather = !pw_tma_x(d, x) || (long long)s.pos_tiles * kPwPosTile * 10 > (long long)HW * 11;
+  if (d.dtype == DWBNQ_F16) {
+    // binary16 tensors go through TMA (and stay binary16 in the MMA) where the rows of x and w are
+    // multiples of 16 bytes; no worker touches them there, which is worth up to a seventh of empty rows (28 x 28)
+    gather = HW % 8 != 0 || d.c_in % 8 != 0 || ((uintptr_t)x & 15) != 0 ||
+             (long long)s.pos_tiles * kPwPosTile * 6 > (long long)HW * 7;
+  }
   {
     // DWBNQ_PW_GATHER: 0 = TMA wherever it can be used, 1 = always gather, 2 = the one-element gather
     static const int env = [] {
@@ -1011,6 +1047,7 @@ int pw_shape(const dwbnq_pwconv_desc &d, const void *x, bool math3, int sms, int
     if (env == 2) scalar_gather = true;
     if (env == 0 && pw_tma_x(d, x) && d.dtype == DWBNQ_F32) gather = false;
   }
+  if (!gather && d.dtype == DWBNQ_F16) s.kchunks = (d.c_in + 63) / 64;  // 64 binary16 channels per stage
   s.xmode = !gather ? PW_X_TMA : scalar_gather ? PW_X_GATHER : PW_X_GATHER4;
   {
     const long long per_ct = gather ? (total_pos + kPwPosTile - 1) / kPwPosTile : d.n * s.pos_tiles;
@@ -1070,12 +1107,12 @@ int pwconv_prepare(const dwbnq_pwconv_desc &d, float bn_eps, const void *w, cons
     pw_prepare_kernel<float><<<blocks, 256, 0, stream>>>(
         static_cast<const float *>(w), static_cast<const float *>(b), static_cast<const float *>(beta),
         static_cast<const float *>(gamma), static_cast<const float *>(mean), static_cast<const float *>(var), bn_eps,
-        d.c_out, cstride, wsize, ws.coef, ws.w_a, m.math3 ? ws.w_b : nullptr);
+        d.c_out, cstride, wsize, ws.coef, ws.w_a, m.math3 ? ws.w_b : nullptr, nullptr);
   else
     pw_prepare_kernel<__half><<<blocks, 256, 0, stream>>>(
         static_cast<const __half *>(w), static_cast<const __half *>(b), static_cast<const __half *>(beta),
         static_cast<const __half *>(gamma), static_cast<const __half *>(mean), static_cast<const __half *>(var), bn_eps,
-        d.c_out, cstride, wsize, ws.coef, ws.w_a, nullptr);
+        d.c_out, cstride, wsize, ws.coef, ws.w_a, nullptr, reinterpret_cast<__half *>(ws.w_b));
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail_cuda(e, "pw_prepare_kernel launch");
   return DWBNQ_OK;
@@ -1157,7 +1194,24 @@ int pwconv_run(const dwbnq_pwconv_desc &d, const dwbnq_quant_desc *q, int has_bn
   if (!enc) return fail(DWBNQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   CUtensorMap tx, tw, twl;
   std::memset(&tx, 0, sizeof(tx));
-  if (!gather) {
+  const bool f16mma = !gather && d.dtype == DWBNQ_F16;  // binary16 operands through TMA, kind::f16
+  if (f16mma) {
+    const cuuint64_t gdim[3] = {(cuuint64_t)HW, (cuuint64_t)d.c_in, (cuuint64_t)d.n};
+    const cuuint64_t gstr[2] = {(cuuint64_t)HW * 2, (cuuint64_t)HW * d.c_in * 2};
+    const cuuint32_t box[3] = {64, 64, 1}, es[3] = {1, 1, 1};
+    CUresult r = enc(&tx, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(x), gdim, gstr, box, es,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(DWBNQ_ERR_CUDA, "cuTensorMapEncodeTiled(x, binary16) failed with CUresult %d", (int)r);
+    const cuuint64_t wdim[2] = {(cuuint64_t)d.c_in, (cuuint64_t)d.c_out};
+    const cuuint64_t wstr[1] = {(cuuint64_t)d.c_in * 2};
+    const cuuint32_t wbox[2] = {64, (cuuint32_t)g.npad}, wes[2] = {1, 1};
+    r = enc(&tw, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, w_lo /* the binary16 copy */, wdim, wstr, wbox, wes,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(DWBNQ_ERR_CUDA, "cuTensorMapEncodeTiled(w, binary16) failed with CUresult %d", (int)r);
+    twl = tw;
+  } else if (!gather) {
     const cuuint64_t gdim[3] = {(cuuint64_t)HW, (cuuint64_t)d.c_in, (cuuint64_t)d.n};
     const cuuint64_t gstr[2] = {(cuuint64_t)HW * 4, (cuuint64_t)HW * d.c_in * 4};
     const cuuint32_t box[3] = {32, (cuuint32_t)kPwKChunk, 1}, es[3] = {1, 1, 1};
@@ -1166,7 +1220,7 @@ int pwconv_run(const dwbnq_pwconv_desc &d, const dwbnq_quant_desc *q, int has_bn
                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(DWBNQ_ERR_CUDA, "cuTensorMapEncodeTiled(x) failed with CUresult %d", (int)r);
   }
-  for (int k = 0; k < 2; ++k) {
+  for (int k = 0; k < 2 && !f16mma; ++k) {
     const void *src = (k && math3) ? w_lo : w_hi;
     const cuuint64_t gdim[2] = {(cuuint64_t)d.c_in, (cuuint64_t)d.c_out};
     const cuuint64_t gstr[1] = {(cuuint64_t)d.c_in * 4};
@@ -1186,7 +1240,8 @@ int pwconv_run(const dwbnq_pwconv_desc &d, const dwbnq_quant_desc *q, int has_bn
   else if (a.has_bn && fpq_u && d.act == DWBNQ_ACT_RELU6 && qa.fpq_max >= 6.0f) epi = PW_EPI_BN_RELU6_FPQ;
   const size_t smem = (size_t)a.stages * a.stage_bytes + table_bytes + 1024;
   const dim3 gd((unsigned)sh.grid);
-  const cudaError_t e = d.dtype == DWBNQ_F16
+  const cudaError_t e = f16mma ? launch_pw_tc<__half, PW_X_TMA, false>(epi, gd, smem, stream, tx, tw, twl, a)
+                        : d.dtype == DWBNQ_F16
                             ? (scalar_gather ? launch_pw_tc<__half, PW_X_GATHER, false>(epi, gd, smem, stream, tx, tw, twl, a)
                                              : launch_pw_tc<__half, PW_X_GATHER4, false>(epi, gd, smem, stream, tx, tw, twl, a))
                         : gather && scalar_gather

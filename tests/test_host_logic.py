@@ -319,9 +319,15 @@ def test_pointwise_launch_shapes_of_the_mobilenet_layers(dwlib):
     # the same layer at two images: narrow tiles again (eight of 128 columns), whatever was prepared
     small = P(dtype=dwlib.F32, c_in=160, c_out=960, h=7, w=7, n=2, math=dwlib.PW_MATH_FP32)
     assert ops.pwconv_tiling(small)["columns"] == 128
-    # fp16 tensors are gathered everywhere; an unaligned x or a plane that is no multiple of 4 takes one element per load
+    # fp16 tensors: TMA (and binary16 MMAs) where rows are multiples of 16 bytes, else gathered - four positions per
+    # load on planes that are multiples of 4 (14 x 14), one element on the others or behind an unaligned x
     half = P(dtype=dwlib.F16, c_in=32, c_out=96, h=56, w=56, n=8)
-    assert ops.pwconv_tiling(half)["x_path"] == FOUR and ops.pwconv_tiling(half, x_address=4100)["x_path"] == ONE
+    assert ops.pwconv_tiling(half)["x_path"] == TMA and ops.pwconv_tiling(half, x_address=4100)["x_path"] == ONE
+    assert ops.pwconv_tiling(half, x_address=4104)["x_path"] == FOUR
+    assert ops.pwconv_tiling(P(dtype=dwlib.F16, c_in=32, c_out=96, h=28, w=28, n=8))["x_path"] == TMA
+    assert ops.pwconv_tiling(P(dtype=dwlib.F16, c_in=64, c_out=96, h=14, w=14, n=8))["x_path"] == FOUR
+    assert ops.pwconv_tiling(P(dtype=dwlib.F16, c_in=160, c_out=96, h=7, w=7, n=8))["x_path"] == ONE
+    assert ops.pwconv_tiling(P(dtype=dwlib.F16, c_in=20, c_out=96, h=56, w=56, n=8))["x_path"] == FOUR  # w rows of 40 bytes
     odd = P(dtype=dwlib.F32, c_in=32, c_out=96, h=56, w=56, n=8)
     assert ops.pwconv_tiling(odd)["x_path"] == TMA and ops.pwconv_tiling(odd, x_address=4100)["x_path"] == ONE
     # a descriptor for the FMA kernel has no tiling

@@ -158,9 +158,10 @@ def test_fma_kernel_takes_every_other_shape(oracle, cuda_device, shape):
 
 
 def test_fp16_tensors(oracle, cuda_device):
-    """binary16 tensors: on the tensor-core kernel (gathered rows, ONE TF32 pass - a binary16 factor
-    has 11 significant bits, so every product is exact and only the fp32 accumulation rounds) when
-    c_in is a multiple of 4, else on the FMA kernel; fp32 epilogue, one rounding to binary16 at the store."""
+    """binary16 tensors: on the tensor-core kernel (gathered rows and ONE TF32 pass - a binary16 factor
+    has 11 significant bits, so every product is exact and only the fp32 accumulation rounds - or, with
+    16-byte rows, TMA loads and binary16 MMAs) when c_in is a multiple of 4, else on the FMA kernel;
+    fp32 epilogue, one rounding to binary16 at the store."""
     rng = np.random.default_rng(11)
     for shape, path in (((2, 32, 64, 14, 14), 1), ((1, 24, 40, 7, 7), 1), ((3, 64, 200, 28, 28), 1), ((2, 30, 24, 6, 6), 0)):
         d = make(rng, *shape, dtype=np.float16)
@@ -181,6 +182,52 @@ def test_fp16_tensors(oracle, cuda_device):
         y2 = ops.fused_pw_bn_quant_prepared(t["x"], t["w"], ws, True, FPQ_U, "relu6")
         y1 = ops.fused_pw_bn_quant(t["x"], t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], 1e-5, FPQ_U, "relu6")
         assert torch.equal(y1.view(torch.int16), y2.view(torch.int16))
+    ops.check_device_flag()
+
+
+@pytest.mark.parametrize("shape,ctas", [((2, 24, 40, 8, 16), 0), ((2, 96, 24, 56, 56), 0), ((1, 144, 320, 16, 24), 0),
+                                        ((3, 32, 96, 112, 112), 0), ((2, 384, 64, 16, 8), 0), ((4, 64, 200, 28, 28), 2),
+                                        ((9, 72, 16, 24, 24), 3)],
+                         ids=lambda v: "x".join(map(str, v)) if isinstance(v, tuple) else "ctas%d" % v)
+def test_fp16_tensors_through_tma_and_binary16_mmas(oracle, cuda_device, shape, ctas):
+    """binary16 tensors whose rows are multiples of 16 bytes: TMA loads of x and w as they are,
+    tcgen05.mma.kind::f16 (products of binary16 factors are exact in the fp32 accumulator), 64
+    channels per stage - one, two and more stages per sum, a last stage of 8 to 48 channels, planes
+    that end inside a tile, several tiles per CTA. Random data within the accumulation's tolerance;
+    small-integer data (every sum exact) bit for bit."""
+    n, ci, co, h, w = shape
+    rng = np.random.default_rng(sum(shape))
+    d = make(rng, *shape, dtype=np.float16)
+    t = {k: dev(v, cuda_device) for k, v in d.items()}
+    desc, _ = ops.pwconv_desc(t["x"], t["w"])
+    assert ops.pwconv_tiling(desc, t["x"].data_ptr())["x_path"] == 0
+    tol = (ci + 4) * 2.0 ** -23
+    try:
+        ops.set_pw_max_ctas(ctas)
+        got = ops.pointwise_convolution(t["x"], t["w"], t["b"])
+        acc64, mag = check_conv(oracle, got.cpu().numpy().astype(np.float32), d, tol, half=True)
+        for quant, act in ((FPQ_U, "relu6"), (FPQ_S, None)):
+            y = ops.fused_pw_bn_quant(t["x"], t["w"], t["b"], t["beta"], t["gamma"], t["mean"], t["var"], 1e-5, quant, act)
+            lo, hi = bracket(oracle, acc64, mag, tol, d, 1e-5, act, quant)
+            g = y.cpu().numpy()
+            assert np.all((g >= lo.astype(np.float16)) & (g <= hi.astype(np.float16))), (shape, quant, act)
+        # the gathered path on the same tensors (an x that starts 8 bytes into its buffer) agrees to the last bit
+        # of the fp32 sums' tolerance, and exactly on exactly summable data
+        xi = (rng.integers(-40, 56, (n, ci, h, w)) / 8.0).astype(np.float16)
+        wi = (rng.integers(-31, 32, (co, ci, 1, 1)) / 16.0).astype(np.float16)
+        bi = (rng.integers(-24, 25, co) / 8.0).astype(np.float16)
+        exact = np.einsum("nchw,oc->nohw", xi.astype(np.float64), wi[:, :, 0, 0].astype(np.float64)) + \
+            bi.astype(np.float64)[None, :, None, None]
+        conv = ops.pointwise_convolution(dev(xi, cuda_device), dev(wi, cuda_device), dev(bi, cuda_device))
+        assert np.array_equal(conv.cpu().numpy().view(np.uint16), exact.astype(np.float16).view(np.uint16))
+        buf = torch.empty(xi.size + 4, dtype=torch.float16, device=cuda_device)
+        shifted = buf[4:].view(xi.shape)
+        shifted.copy_(dev(xi, cuda_device))
+        assert ops.pwconv_tiling(desc, shifted.data_ptr())["x_path"] != 0
+        conv2 = ops.pointwise_convolution(shifted, dev(wi, cuda_device), dev(bi, cuda_device))
+        assert torch.equal(conv.view(torch.int16), conv2.view(torch.int16))
+    finally:
+        ops.set_pw_max_ctas(0)
     ops.check_device_flag()
 
 
