@@ -527,7 +527,8 @@ def pointwise_rows(torch, ops, workloads, device, batch, peak):
                              "algorithmic_bytes": nbytes,
                              "kernel": "pw_tc_kernel (tcgen05, three TF32 passes)" if path == 1 else "pw_simt_kernel (FMA)",
                              "timing": "median of 10 CUDA-graph replays, L2 flushed before each"})
-        # the same layer on binary16 tensors (one exact TF32 pass, rows gathered): summary row only
+        # the same layer on binary16 tensors (binary16 MMAs behind TMA where rows are 16-byte multiples, else one exact
+        # TF32 pass on gathered rows): per-layer time beside the fp32 row, and a summary row
         th = {k: v.half() for k, v in t.items()}
         yh = torch.empty((batch, spec.c_out, spec.h, spec.h), dtype=torch.float16, device=device)
         ops.pwconv_prepare(th["x"], th["w"], th["b"], th["beta"], th["gamma"], th["mean"], th["var"], spec.bn_eps,
@@ -563,7 +564,7 @@ def pointwise_rows(torch, ops, workloads, device, batch, peak):
                      "timing": "median of 5 eager calls per layer, L2 flushed before each (host launch overhead included)"})
     rows.append({"workload": "pw1: 33 pointwise layers, fp16 tensors", "dtype": "f16", "batch": batch, "ms": half_ms,
                  "images_per_s": batch / (half_ms / 1e3), "gbs": nb_all / 2 / half_ms / 1e6, "frac": nb_all / 2 / half_ms / 1e6 / peak,
-                 "tflops": fl_all / half_ms / 1e9, "algorithmic_bytes": nb_all // 2, "kernel": "pw_tc_kernel<half> (one exact TF32 pass)",
+                 "tflops": fl_all / half_ms / 1e9, "algorithmic_bytes": nb_all // 2, "kernel": "pw_tc_kernel<half> (kind::f16 behind TMA on 16-byte rows, else gathered with one exact TF32 pass)",
                  "timing": "median of 7 CUDA-graph replays per layer, L2 flushed before each"})
     for math, (ms, nbytes, fl) in totals.items():
         rows.append({"workload": "pw1: 33 pointwise layers, math %s" % math, "dtype": "f32", "batch": batch, "ms": ms,

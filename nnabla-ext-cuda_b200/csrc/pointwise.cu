@@ -14,10 +14,13 @@
 //  * one CTA per SM walks over (channel tile, 128 positions) pairs; warp 0 issues the TMA
 //    loads, warp 1 the MMAs, warps 2-9 bring the activations into operand form - they split the
 //    TMA-loaded fp32 values into TF32 halves for the three-pass mode, or, in gather mode, load
-//    them with plain loads (planes TMA cannot take or would tile badly, fp16 tensors), rows
-//    flattened over (image, position) - and warps 10-25 are the epilogue (four groups of four
-//    warps, each group a tile of its own); up to eight accumulator buffers in TMEM decouple the
-//    MMAs from the epilogue;
+//    them with plain loads (planes TMA cannot take or would tile badly), rows flattened over
+//    (image, position) - and warps 10-25 are the epilogue (four groups of four warps, each
+//    group a tile of its own, or all four sharing a tile's columns when a CTA has few tiles);
+//    up to eight accumulator buffers in TMEM decouple the MMAs from the epilogue;
+//  * binary16 tensors whose rows are multiples of 16 bytes stay binary16 all the way: TMA loads
+//    of x and w, tcgen05.mma.kind::f16, 64 channels per stage and no worker pass; the others are
+//    gathered and converted (exactly) for one TF32 pass;
 //  * every wait on an mbarrier is bounded in time; a wait that runs out records it in the
 //    device flag, the roles leave their loops, and the CTA frees its tensor memory and returns.
 // c_in that is not a multiple of 4 (the weight rows must be 16-byte multiples for their TMA
@@ -49,7 +52,7 @@ constexpr unsigned long long kPwWaitNs = 2000000000ull;
 // with or without ReLU6 in between (after ReLU6 the quantizer's clamps are redundant when its
 // range reaches 6); BN + signed power-of-two FixedPointQuantize (the linear projection of an
 // inverted residual); everything else with run-time switches.
-// How the activations reach shared memory: TMA boxes per image; plain loads with the rows
+// How the activations reach shared memory: TMA boxes per image (fp32, or binary16 as it is); plain loads with the rows
 // flattened over (image, position), one element or - where the plane size is a multiple of 4
 // and the base aligned - four consecutive positions per load.
 enum PwXMode : int { PW_X_TMA = 0, PW_X_GATHER = 1, PW_X_GATHER4 = 2 };
