@@ -353,7 +353,7 @@ def run_pointwise(args):
     print(json.dumps(line), flush=True)
 
 
-def body_row(torch, ops, workloads, device, batch, peak, reps=10):
+def body_row(torch, ops, workloads, device, batch, peak, reps=10, half=False):
     """The 50 layers of MobileNetV2's body as ONE network: the unfused function list nnabla would
     build (166 functions), fused by the two graph passes into 17 FusedDwBnQuant + 33
     FusedPwBnQuant nodes, every layer reading the previous layer's output; pointwise parameters
@@ -363,6 +363,8 @@ def body_row(torch, ops, workloads, device, batch, peak, reps=10):
     shapes = {k: v.shape for k, v in host.items()}
     fused = graph.fuse_pw_bn_quant(graph.fuse_dw_bn_quant(nodes, [x_out], shapes), [x_out], shapes)
     tensors = {k: torch.from_numpy(v).to(device) for k, v in host.items()}
+    if half:  # binary16 tensors (the 8-bit activations are exact in binary16; the parameters are rounded to it)
+        tensors = {k: v.half() for k, v in tensors.items()}
     del host
     runner = graph.GraphRunner(fused, tensors)
     runner.replay()
@@ -378,13 +380,14 @@ def body_row(torch, ops, workloads, device, batch, peak, reps=10):
         ts.append(e0.elapsed_time(e1))
     runner.synchronize()
     ms = float(np.median(ts))
-    nbytes = sum(sp.algorithmic_bytes(4, batch) for _, sp in workloads.mobilenetv2_body(batch))
+    nbytes = sum(sp.algorithmic_bytes(2 if half else 4, batch) for _, sp in workloads.mobilenetv2_body(batch))
     flops = sum(sp.flops(batch) for kind, sp in workloads.mobilenetv2_body(batch) if kind == "pw")
     out_shape = tuple(tensors[x_out].shape)
     del runner, tensors
     torch.cuda.empty_cache()
     return {"workload": "body: MobileNetV2's 50 depthwise + pointwise layers chained (each reads the previous output), "
-                        "fused by the graph passes", "dtype": "f32", "batch": batch, "ms": ms, "best_ms": float(min(ts)),
+                        "fused by the graph passes" + (", binary16 tensors" if half else ""),
+            "dtype": "f16" if half else "f32", "batch": batch, "ms": ms, "best_ms": float(min(ts)),
             "images_per_s": batch / (ms / 1e3), "gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak,
             "tflops": flops / ms / 1e9, "algorithmic_bytes": nbytes, "launches": len(fused), "output": list(out_shape),
             "kernel": "fused_plane_* (17 launches) + pw_tc_kernel (33 launches)",
@@ -400,10 +403,10 @@ def run_body(args):
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(device)
     peak, peak_kind = measured_peak()
-    row = body_row(torch, ops, workloads, device, args.batch, peak)
+    row = body_row(torch, ops, workloads, device, args.batch, peak, half=args.dtype == "f16")
     line = {"metric": "images_per_s", "value": row["images_per_s"], "unit": "images/s", "n_gpus": 1, "steps": 10,
             "warmup": 3, "ms_per_step": row["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic", "config": {"workload": row["workload"], "batch": args.batch,
+            "dtype": row["dtype"], "data": "synthetic", "config": {"workload": row["workload"], "batch": args.batch,
                                                             "l2": "L2 flushed before every timed replay"},
             "roofline": {"bound": "hbm", "achieved": row["gbs"], "peak": peak, "unit": "GB/s", "frac": row["frac"],
                          "traffic": None, "peak_kind": peak_kind}, "gpu_launches": row["launches"], "layers": [row]}
@@ -715,6 +718,7 @@ def other_workloads(torch, ops, workloads, device, cfg1_layers, args):
     torch.cuda.empty_cache()
     out.extend(pointwise_rows(torch, ops, workloads, device, 256, peak))
     out.append(body_row(torch, ops, workloads, device, 256, peak))
+    out.append(body_row(torch, ops, workloads, device, 256, peak, half=True))
     torch.cuda.empty_cache()
     return out
 
