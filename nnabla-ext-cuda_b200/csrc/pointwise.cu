@@ -359,7 +359,6 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
       int s = 0;
       unsigned int ph = 0;
       const unsigned int bytes = (GATHER ? 0 : kPwXBytes) + wbytes * (MATH3 ? 2 : 1);
-      const unsigned int full0 = smem_u32(&full[0]), empty0 = smem_u32(&empty[0]);
       bool ok = true;
       for (int t = blockIdx.x; ok && t < a.total_tiles; t += gridDim.x) {
         const int ct = t / a.per_ct;
@@ -382,7 +381,6 @@ pw_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ C
           if (++s == a.stages) { s = 0; ph ^= 1u; }
         }
       }
-      (void)full0; (void)empty0;
       if (!ok && !*abort_v) { atomicExch(a.flag, 1); *abort_v = 1; }
     }
   } else if (warp == 1) {
