@@ -2,7 +2,7 @@
 """Benchmark of the fused dw-conv + BN-inference + quantize path.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl own|reference]
-                  [--workload cfg1|cfg0|cfg2|cfg3|cfg4|cfg1q8|ops|pw1|body] [--batch B] [--scaling weak|strong]
+                  [--workload cfg1|cfg0|cfg2|cfg3|cfg4|cfg1q8|ops|bwd|pw1|body] [--batch B] [--scaling weak|strong]
 
 A "step" is one pass of the workload's layer stack over one batch of seeded synthetic
 input (cfg1: the 17 depthwise layers of MobileNetV2 at 224x224, batch 256 per GPU, fp32,
@@ -310,14 +310,18 @@ def run_standalone_ops(args):
     itemsize = 2 if half else 4
     n, c, hw = args.batch, 96, 56
     peak, peak_kind = measured_peak()
-    rows = standalone_op_rows(torch, ops, device, n, half, args.warmup, max(3, min(args.steps, 20)))
+    if args.workload == "bwd":  # the training-side kernels on the same activation (fp32)
+        rows = backward_op_rows(torch, ops, device, n, args.warmup, max(3, min(args.steps, 20)))
+    else:
+        rows = standalone_op_rows(torch, ops, device, n, half, args.warmup, max(3, min(args.steps, 20)))
     total_ms = sum(r["ms"] for r in rows)
     bytes_all = sum(r["bytes"] for r in rows)
     achieved = bytes_all / total_ms / 1e6
     line = {"metric": "images_per_s", "value": n / (total_ms / 1e3), "unit": "images/s", "n_gpus": 1,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
-            "config": {"workload": "ops: the five standalone operators on [%d,%d,%d,%d]" % (n, c, hw, hw),
+            "config": {"workload": ("bwd: the backward kernels on [%d,%d,%d,%d]" if args.workload == "bwd" else
+                                    "ops: the five standalone operators on [%d,%d,%d,%d]") % (n, c, hw, hw),
                        "l2": "L2 flushed before every timed launch"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": None, "peak_kind": peak_kind}, "gpu_launches": None, "layers": rows}
@@ -1071,9 +1075,9 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
-    ap.add_argument("--workload", default="cfg1", choices=["cfg0", "cfg1", "cfg2", "cfg3", "cfg4", "cfg1q8", "ops", "pw1", "body"])
+    ap.add_argument("--workload", default="cfg1", choices=["cfg0", "cfg1", "cfg2", "cfg3", "cfg4", "cfg1q8", "ops", "bwd", "pw1", "body"])
     ap.add_argument("--batch", type=int, default=None, help="images per GPU (default: the workload's batch)")
     ap.add_argument("--dtype", default="f32", choices=["f32", "f16"])
     ap.add_argument("--cpu-sample", type=int, default=None, help="images per CPU-baseline pass")
@@ -1093,15 +1097,15 @@ def main():
     ap.add_argument("--force-path", type=int, default=None, help="profiling only: kernel family 0..4")
     ap.add_argument("--tune", default="", help="profiling only: planner override P,row_blocks,threads,rows_per_patch")
     args = ap.parse_args()
-    defaults = {"cfg0": 32, "cfg1": 256, "cfg2": 128, "cfg3": 512, "cfg4": 256, "cfg1q8": 256, "ops": 256, "pw1": 256, "body": 256}
+    defaults = {"cfg0": 32, "cfg1": 256, "cfg2": 128, "cfg3": 512, "cfg4": 256, "cfg1q8": 256, "ops": 256, "bwd": 256, "pw1": 256, "body": 256}
     if args.batch is None:
         args.batch = defaults[args.workload]
     if args.warmup < 3:
         args.warmup = 3
     if args.cpu_sample is None:
         args.cpu_sample = {"cfg0": 32, "cfg1": 64, "cfg2": 32, "cfg3": 128, "cfg4": 64, "cfg1q8": 64,
-                           "ops": 0, "pw1": 0, "body": 0}[args.workload]
-    if args.workload == "ops":
+                           "ops": 0, "bwd": 0, "pw1": 0, "body": 0}[args.workload]
+    if args.workload in ("ops", "bwd"):
         run_standalone_ops(args)
     elif args.workload == "pw1":
         run_pointwise(args)
