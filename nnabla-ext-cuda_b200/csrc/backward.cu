@@ -433,6 +433,109 @@ __global__ void __launch_bounds__(kThreads, 4) dwconv_bwd_weights_rows_kernel(co
   }
 }
 
+// The same register window for 3 x 3, stride 2, pad 1: a lane's four output columns read the nine
+// input columns 8 cb - 1 .. 8 cb + 7, and an output row the input rows 2 oy - 1, 2 oy, 2 oy + 1, of
+// which the first is the last one of the row above: two new rows of x (two 16-byte loads and the
+// left neighbour each) and one row of dy per 36 multiply-adds. VECX / VECY: the rows of x / of dy
+// are 16-byte aligned.
+template <bool VECX, bool VECY>
+__global__ void __launch_bounds__(kThreads, 4) dwconv_bwd_weights_rows_s2_kernel(const BwdArgs a, const int slices) {
+  __shared__ float red[kThreads / 32][10];
+  const float *x = static_cast<const float *>(a.x);
+  const float *dy = static_cast<const float *>(a.dy);
+  pdl_launch_dependents();
+  pdl_wait_for_predecessor();
+  const int oc = blockIdx.x / slices;
+  const int slice = blockIdx.x % slices;
+  const int ic = oc / a.mult;
+  const int H = a.H, W = a.W, Ho = a.Ho, Wo = a.Wo;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long per = (a.n + slices - 1) / slices;
+  const long long n0 = (long long)slice * per;
+  const long long n1 = n0 + per < a.n ? n0 + per : a.n;
+  const int ncb = (Wo + 3) >> 2;
+  int bands = ncb >= 32 ? 1 : 32 / ncb;
+  if (bands > Ho) bands = Ho;
+  const int rows_per_band = (Ho + bands - 1) / bands;
+  const int items = ncb * bands;
+  float acc[9];
+#pragma unroll
+  for (int i = 0; i < 9; ++i) acc[i] = 0.0f;
+  float bsum = 0.0f;
+  for (long long n = n0 + warp; n < n1; n += kThreads / 32) {
+    const float *dyp = dy + (n * a.OC + oc) * ((long long)Ho * Wo);
+    const float *xp = x + (n * a.C + ic) * ((long long)H * W);
+    for (int item = lane; item < items; item += 32) {
+      const int band = item / ncb, cb = item - band * ncb;
+      const int c0 = cb * 4, i0 = cb * 8;  // first output column, input column under its middle tap
+      const int r0 = band * rows_per_band;
+      const int r1 = r0 + rows_per_band < Ho ? r0 + rows_per_band : Ho;
+      // input columns i0 - 1 .. i0 + 7 of row iy; zero outside the plane
+      auto load_row = [&](int iy, float(&r)[9]) {
+        if ((unsigned int)iy >= (unsigned int)H) {
+#pragma unroll
+          for (int j = 0; j < 9; ++j) r[j] = 0.0f;
+          return;
+        }
+        const float *p = xp + iy * W + i0;
+        if (VECX && i0 + 8 <= W) {
+          const float4 u = __ldg(reinterpret_cast<const float4 *>(p)), v = __ldg(reinterpret_cast<const float4 *>(p + 4));
+          r[1] = u.x; r[2] = u.y; r[3] = u.z; r[4] = u.w; r[5] = v.x; r[6] = v.y; r[7] = v.z; r[8] = v.w;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) r[1 + j] = i0 + j < W ? __ldg(p + j) : 0.0f;
+        }
+        r[0] = i0 > 0 ? __ldg(p - 1) : 0.0f;
+      };
+      float top[9], mid[9], bot[9];
+      load_row(2 * r0 - 1, top);
+      for (int oy = r0; oy < r1; ++oy) {
+        load_row(2 * oy, mid);
+        load_row(2 * oy + 1, bot);
+        float g[4];
+        const float *q = dyp + oy * Wo + c0;
+        if (VECY) {
+          const float4 v = __ldg(reinterpret_cast<const float4 *>(q));
+          g[0] = v.x; g[1] = v.y; g[2] = v.z; g[3] = v.w;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) g[j] = c0 + j < Wo ? __ldg(q + j) : 0.0f;
+        }
+        bsum += (g[0] + g[1]) + (g[2] + g[3]);
+#pragma unroll
+        for (int kx = 0; kx < 3; ++kx) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[kx] = fmaf(top[2 * j + kx], g[j], acc[kx]);
+            acc[3 + kx] = fmaf(mid[2 * j + kx], g[j], acc[3 + kx]);
+            acc[6 + kx] = fmaf(bot[2 * j + kx], g[j], acc[6 + kx]);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 9; ++j) top[j] = bot[j];
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i <= 9; ++i) {
+    float v = i < 9 ? acc[i < 9 ? i : 0] : bsum;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) red[warp][i] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x <= 9) {
+    float v = 0.0f;
+#pragma unroll
+    for (int wv = 0; wv < kThreads / 32; ++wv) v += red[wv][threadIdx.x];
+    if (threadIdx.x < 9) {
+      if (a.dw) atomicAdd(static_cast<float *>(a.dw) + (long long)oc * 9 + threadIdx.x, v);
+    } else if (a.db) {
+      atomicAdd(static_cast<float *>(a.db) + oc, v);
+    }
+  }
+}
+
 // Any kernel size: one CTA per weight value (and one more per channel for the bias), the
 // reference's own decomposition. Slow path for kernels other than 3x3 and 5x5.
 template <typename T>
@@ -626,7 +729,12 @@ int launch_dwconv_backward(const dwbnq_conv_desc &d, int ho, int wo, const void 
       const bool rows16 = d.w % 4 == 0 && (((uintptr_t)x | (uintptr_t)dy) & 15) == 0;
       if (same_size && rows16) e = launch_pdl(dwconv_bwd_weights_rows_kernel<true>, grid, block, 0, stream, a, (int)slices);
       else if (same_size) e = launch_pdl(dwconv_bwd_weights_rows_kernel<false>, grid, block, 0, stream, a, (int)slices);
-      else if (key == 31) e = launch_pdl(dwconv_bwd_weights_kernel<float, 3, 1>, grid, block, 0, stream, a, (int)slices);
+      else if (key == 32 && d.pad_h == 1 && d.pad_w == 1) {
+        const bool vx = rows16, vy = wo % 4 == 0 && rows16;
+        e = vx ? (vy ? launch_pdl(dwconv_bwd_weights_rows_s2_kernel<true, true>, grid, block, 0, stream, a, (int)slices)
+                     : launch_pdl(dwconv_bwd_weights_rows_s2_kernel<true, false>, grid, block, 0, stream, a, (int)slices))
+               : launch_pdl(dwconv_bwd_weights_rows_s2_kernel<false, false>, grid, block, 0, stream, a, (int)slices);
+      } else if (key == 31) e = launch_pdl(dwconv_bwd_weights_kernel<float, 3, 1>, grid, block, 0, stream, a, (int)slices);
       else if (key == 32) e = launch_pdl(dwconv_bwd_weights_kernel<float, 3, 2>, grid, block, 0, stream, a, (int)slices);
       else if (key == 51) e = launch_pdl(dwconv_bwd_weights_kernel<float, 5, 1>, grid, block, 0, stream, a, (int)slices);
       else e = launch_pdl(dwconv_bwd_weights_kernel<float, 5, 2>, grid, block, 0, stream, a, (int)slices);

@@ -102,7 +102,11 @@ GEOMS = [  # n, c, h, w, k, stride, pad, dil, mult
     # 3x3 stride 1 pad 1: the register-window weight-gradient kernel, 16-byte rows and not, one band and
     # several, more column blocks than lanes, a plane smaller than a block, a multiplier
     (2, 5, 12, 16, 3, 1, 1, 1, 1), (2, 3, 9, 40, 3, 1, 1, 1, 2), (1, 2, 5, 132, 3, 1, 1, 1, 1), (3, 2, 3, 3, 3, 1, 1, 1, 1),
-    (2, 4, 7, 7, 3, 1, 1, 1, 1), (9, 2, 28, 28, 3, 1, 1, 1, 1), (2, 2, 1, 6, 3, 1, 1, 1, 1)]
+    (2, 4, 7, 7, 3, 1, 1, 1, 1), (9, 2, 28, 28, 3, 1, 1, 1, 1), (2, 2, 1, 6, 3, 1, 1, 1, 1),
+    # 3x3 stride 2 pad 1: the same window over nine input columns; odd and even planes, 16-byte rows of x only /
+    # of x and dy / of neither, more column blocks than lanes, a multiplier
+    (2, 3, 9, 13, 3, 2, 1, 1, 1), (3, 4, 56, 56, 3, 2, 1, 1, 1), (2, 3, 14, 14, 3, 2, 1, 1, 2), (1, 2, 5, 264, 3, 2, 1, 1, 1),
+    (2, 2, 1, 1, 3, 2, 1, 1, 1), (9, 2, 7, 12, 3, 2, 1, 1, 1)]
 
 
 @pytest.mark.parametrize("geom", GEOMS, ids=lambda g: "x".join(str(v) for v in g))
