@@ -332,7 +332,7 @@ __global__ void __launch_bounds__(kThreads, K == 3 ? 4 : 2)
 // 4 x 8 on 14. VEC: rows are 16-byte aligned (W a multiple of 4, aligned tensors); otherwise the
 // same window from single loads, the last block's missing columns read as zero. A warp per image,
 // CTAs = (channel, slice of the batch), reduction and atomics as in the kernel above.
-template <bool VEC>
+template <bool VEC, int NC>
 __global__ void __launch_bounds__(kThreads, 4) dwconv_bwd_weights_rows_kernel(const BwdArgs a, const int slices) {
   __shared__ float red[kThreads / 32][10];
   const float *x = static_cast<const float *>(a.x);
@@ -347,7 +347,7 @@ __global__ void __launch_bounds__(kThreads, 4) dwconv_bwd_weights_rows_kernel(co
   const long long per = (a.n + slices - 1) / slices;
   const long long n0 = (long long)slice * per;
   const long long n1 = n0 + per < a.n ? n0 + per : a.n;
-  const int ncb = (W + 3) >> 2;
+  const int ncb = (W + NC - 1) / NC;
   int bands = ncb >= 32 ? 1 : 32 / ncb;
   if (bands > H) bands = H;
   const int rows_per_band = (H + bands - 1) / bands;
@@ -360,53 +360,61 @@ __global__ void __launch_bounds__(kThreads, 4) dwconv_bwd_weights_rows_kernel(co
     const float *dyp = dy + (n * a.OC + oc) * plane;
     const float *xp = x + (n * a.C + ic) * plane;
     for (int item = lane; item < items; item += 32) {
-      const int band = item / ncb, c0 = (item - band * ncb) * 4;
+      const int band = item / ncb, c0 = (item - band * ncb) * NC;
       const int r0 = band * rows_per_band;
       const int r1 = r0 + rows_per_band < H ? r0 + rows_per_band : H;
-      // input columns c0 - 1 .. c0 + 4 of row iy; zero outside the plane
-      auto load_row = [&](int iy, float(&r)[6]) {
+      const bool whole = VEC && c0 + NC <= W;  // the block's 16-byte vectors lie inside the row
+      // input columns c0 - 1 .. c0 + NC of row iy; zero outside the plane
+      auto load_row = [&](int iy, float(&r)[NC + 2]) {
         if ((unsigned int)iy >= (unsigned int)H) {
 #pragma unroll
-          for (int j = 0; j < 6; ++j) r[j] = 0.0f;
+          for (int j = 0; j < NC + 2; ++j) r[j] = 0.0f;
           return;
         }
         const float *p = xp + iy * W + c0;
-        if (VEC) {
-          const float4 v = __ldg(reinterpret_cast<const float4 *>(p));
-          r[1] = v.x; r[2] = v.y; r[3] = v.z; r[4] = v.w;
+        if (whole) {
+#pragma unroll
+          for (int v4 = 0; v4 < NC / 4; ++v4) {
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(p) + v4);
+            r[1 + 4 * v4] = v.x; r[2 + 4 * v4] = v.y; r[3 + 4 * v4] = v.z; r[4 + 4 * v4] = v.w;
+          }
         } else {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) r[1 + j] = c0 + j < W ? __ldg(p + j) : 0.0f;
+          for (int j = 0; j < NC; ++j) r[1 + j] = c0 + j < W ? __ldg(p + j) : 0.0f;
         }
         r[0] = c0 > 0 ? __ldg(p - 1) : 0.0f;
-        r[5] = c0 + 4 < W ? __ldg(p + 4) : 0.0f;
+        r[NC + 1] = c0 + NC < W ? __ldg(p + NC) : 0.0f;
       };
-      float top[6], mid[6], bot[6];
+      float top[NC + 2], mid[NC + 2], bot[NC + 2];
       load_row(r0 - 1, top);
       load_row(r0, mid);
       for (int oy = r0; oy < r1; ++oy) {
         load_row(oy + 1, bot);
-        float g[4];
+        float g[NC];
         const float *q = dyp + oy * W + c0;
-        if (VEC) {
-          const float4 v = __ldg(reinterpret_cast<const float4 *>(q));
-          g[0] = v.x; g[1] = v.y; g[2] = v.z; g[3] = v.w;
+        if (whole) {
+#pragma unroll
+          for (int v4 = 0; v4 < NC / 4; ++v4) {
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(q) + v4);
+            g[4 * v4] = v.x; g[4 * v4 + 1] = v.y; g[4 * v4 + 2] = v.z; g[4 * v4 + 3] = v.w;
+          }
         } else {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) g[j] = c0 + j < W ? __ldg(q + j) : 0.0f;
+          for (int j = 0; j < NC; ++j) g[j] = c0 + j < W ? __ldg(q + j) : 0.0f;
         }
-        bsum += (g[0] + g[1]) + (g[2] + g[3]);
+#pragma unroll
+        for (int j = 0; j < NC; j += 4) bsum += (g[j] + g[j + 1]) + (g[j + 2] + g[j + 3]);
 #pragma unroll
         for (int kx = 0; kx < 3; ++kx) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
+          for (int j = 0; j < NC; ++j) {
             acc[kx] = fmaf(top[j + kx], g[j], acc[kx]);
             acc[3 + kx] = fmaf(mid[j + kx], g[j], acc[3 + kx]);
             acc[6 + kx] = fmaf(bot[j + kx], g[j], acc[6 + kx]);
           }
         }
 #pragma unroll
-        for (int j = 0; j < 6; ++j) {
+        for (int j = 0; j < NC + 2; ++j) {
           top[j] = mid[j];
           mid[j] = bot[j];
         }
@@ -727,8 +735,12 @@ int launch_dwconv_backward(const dwbnq_conv_desc &d, int ho, int wo, const void 
       const int key = d.kh * 10 + d.stride_h;
       const bool same_size = key == 31 && d.pad_h == 1 && d.pad_w == 1;
       const bool rows16 = d.w % 4 == 0 && (((uintptr_t)x | (uintptr_t)dy) & 15) == 0;
-      if (same_size && rows16) e = launch_pdl(dwconv_bwd_weights_rows_kernel<true>, grid, block, 0, stream, a, (int)slices);
-      else if (same_size) e = launch_pdl(dwconv_bwd_weights_rows_kernel<false>, grid, block, 0, stream, a, (int)slices);
+      // eight output columns per lane on planes wide enough to keep a warp's lanes busy with them (twice the
+      // loads in flight per lane), four on the narrow ones
+      if (same_size && rows16 && d.w >= 32) e = launch_pdl(dwconv_bwd_weights_rows_kernel<true, 8>, grid, block, 0, stream, a, (int)slices);
+      else if (same_size && rows16) e = launch_pdl(dwconv_bwd_weights_rows_kernel<true, 4>, grid, block, 0, stream, a, (int)slices);
+      else if (same_size && d.w >= 32) e = launch_pdl(dwconv_bwd_weights_rows_kernel<false, 8>, grid, block, 0, stream, a, (int)slices);
+      else if (same_size) e = launch_pdl(dwconv_bwd_weights_rows_kernel<false, 4>, grid, block, 0, stream, a, (int)slices);
       else if (key == 32 && d.pad_h == 1 && d.pad_w == 1) {
         const bool vx = rows16, vy = wo % 4 == 0 && rows16;
         e = vx ? (vy ? launch_pdl(dwconv_bwd_weights_rows_s2_kernel<true, true>, grid, block, 0, stream, a, (int)slices)
